@@ -1,0 +1,144 @@
+/*
+ * "torq-b200-ops": the per-dispatch executable format of the B200 backend.
+ *
+ * It is the sibling of the reference's `torq-fb` flatbuffer
+ * (runtime/schemas/torq_executable_def.fbs:11,99-197). Where `torq-fb` carries
+ * NPU bit-streams, XRAM segments and host actions, this format carries one
+ * record per TorqHL-level layer op, with the operand/attribute lists of
+ * compiler/torq/Dialect/TorqHL/TorqHLOps.td (conv2d :119-143, depthwise :145-170,
+ * fully_connected :172-190, avg_pool2d :192-208, add :48-69, mul :101-117,
+ * table :311-327, maxpool2d :435-453, resize NN :959-968) PLUS the TOSA
+ * multiplier[]/shift[] arrays of the tosa.rescale that followed the op, so that
+ * the exact host arithmetic (requant mode A) is representable.
+ *
+ * Layout of a blob (little endian, every section 16-byte aligned):
+ *   tb200_ops_header_t
+ *   tb200_tensor_t  tensors[n_tensors]
+ *   tb200_op_t      ops[n_ops]
+ *   int32_t         input_tensor_ids[n_inputs]
+ *   int32_t         output_tensor_ids[n_outputs]
+ *   uint8_t         constants[const_bytes]      (tensor.const_offset indexes here)
+ *
+ * Activations are NHWC (rank-4) or [rows, cols] (rank-2); conv weights are OHWI,
+ * depthwise weights are [KH, KW, C, 1] exactly as the TOSA fixtures of the
+ * reference have them (tests/testdata/tosa_ops/dw_peeling.mlir).
+ */
+#ifndef TORQ_B200_OPS_H_
+#define TORQ_B200_OPS_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TB200_OPS_MAGIC 0x4f323042u /* "B02O" */
+#define TB200_OPS_VERSION 1u
+#define TB200_OPS_FORMAT_STRING "torq-b200-ops"
+
+/* Element types; numbering follows runtime/schemas/torq_executable_def.fbs:63-75
+ * for the types both formats name. */
+enum tb200_dtype {
+  TB200_I8 = 0,
+  TB200_I16 = 1,
+  TB200_I32 = 2,
+  TB200_F32 = 3,
+  TB200_BF16 = 4,
+  TB200_I64 = 5,
+};
+
+enum tb200_tensor_kind {
+  TB200_TENSOR_ACTIVATION = 0, /* intermediate, lives in the executable's arena */
+  TB200_TENSOR_INPUT = 1,      /* bound by the caller at dispatch */
+  TB200_TENSOR_OUTPUT = 2,     /* bound by the caller at dispatch */
+  TB200_TENSOR_CONSTANT = 3,   /* bytes in the constants section */
+  TB200_TENSOR_STATE = 4,      /* persistent across dispatches (KV cache); zeroed at create */
+};
+
+enum tb200_op_kind {
+  TB200_OP_CONV2D = 1,        /* torq_hl.conv2d            */
+  TB200_OP_DEPTHWISE = 2,     /* torq_hl.depthwise_conv2d  */
+  TB200_OP_FC = 3,            /* torq_hl.fully_connected / torq_hl.matmul with constant B */
+  TB200_OP_MAXPOOL = 4,       /* torq_hl.maxpool2d         */
+  TB200_OP_AVGPOOL = 5,       /* torq_hl.avg_pool2d (any window; whole-frame = global) */
+  TB200_OP_ADD = 6,           /* torq_hl.add : rescale,rescale -> add -> rescale */
+  TB200_OP_MUL = 7,           /* torq_hl.mul : rescale,rescale -> mul -> rescale */
+  TB200_OP_TABLE = 8,         /* torq_hl.table : out = table[x + 128] */
+  TB200_OP_RESCALE = 9,       /* standalone tosa.rescale i8->i8 (torq_hl.fma form) */
+  TB200_OP_RESIZE_NN2X = 10,  /* torq_hl.resize_nearest_neighbor, 2x replicate */
+  TB200_OP_CONCAT = 11,       /* channel concat of in0,in1 with per-input rescale */
+  TB200_OP_SUB = 12,          /* as ADD with in1 negated after its rescale */
+  TB200_OP_MATMUL_I32 = 13,   /* raw torq_hl.matmul: int8 x int8 -> int32, no rescale */
+  TB200_OP_RESHAPE = 14,      /* tosa.reshape: out0 is a view of in0's bytes, no launch */
+  /* decoder (bf16 activations, int8 per-output-channel weights) */
+  TB200_OP_EMBED = 32,        /* gather rows of an int8 table, dequant, * f0 */
+  TB200_OP_RMSNORM = 33,      /* y = x * rsqrt(mean(x^2) + f0) * (1 + w)  (bf16) */
+  TB200_OP_GEMV_W8 = 34,      /* y[b,n] = (sum_k x[b,k] * W[n,k]) * scale[n]  (fp32 acc) */
+  TB200_OP_ROPE_KV = 35,      /* q/k per-head RMSNorm + rotary, append k,v to cache */
+  TB200_OP_ATTN_DECODE = 36,  /* single-query GQA attention over the cache */
+  TB200_OP_GEGLU = 37,        /* y = gelu_tanh(gate) * up */
+  TB200_OP_ADD_BF16 = 38,     /* residual add */
+  TB200_OP_ARGMAX = 39,       /* greedy token id from logits */
+};
+
+enum tb200_requant_mode {
+  TB200_REQUANT_TOSA = 0, /* (A) TOSA apply_scale_32, the host/llvm-cpu arithmetic */
+  TB200_REQUANT_NPU = 1,  /* (B) common shift, round-to-nearest ties to +inf
+                             (compiler/torq/Utils/Kernel.h:607-635) */
+};
+
+typedef struct tb200_ops_header {
+  uint32_t magic;
+  uint32_t version;
+  uint32_t n_tensors;
+  uint32_t n_ops;
+  uint32_t n_inputs;
+  uint32_t n_outputs;
+  uint64_t tensors_offset;
+  uint64_t ops_offset;
+  uint64_t inputs_offset;
+  uint64_t outputs_offset;
+  uint64_t const_offset;
+  uint64_t const_bytes;
+  uint64_t total_bytes;
+} tb200_ops_header_t;
+
+typedef struct tb200_tensor {
+  uint32_t dtype;
+  uint32_t kind;
+  uint32_t rank;        /* 1..4 */
+  int32_t shape[4];     /* unused trailing dims are 1 */
+  uint32_t reserved;
+  uint64_t const_offset; /* TB200_TENSOR_CONSTANT only */
+  uint64_t const_bytes;
+} tb200_tensor_t;
+
+typedef struct tb200_op {
+  uint32_t kind;
+  uint32_t flags;
+  int32_t in0, in1, in2;  /* tensor ids, -1 = unused */
+  int32_t out0, out1;
+  int32_t weights;        /* constant tensor ids, -1 = none */
+  int32_t bias;           /* i32[OC] or i32[1] */
+  int32_t multiplier;     /* i32[OC] or i32[1] */
+  int32_t shift;          /* i8[OC] or i8[1] */
+  int32_t table;          /* i8[256] */
+  int32_t kh, kw, stride_h, stride_w, dil_h, dil_w;
+  int32_t pad_t, pad_b, pad_l, pad_r; /* TOSA order top,bottom,left,right */
+  int32_t in0_zp, in1_zp, weight_zp, out_zp;
+  int32_t clamp_min, clamp_max;
+  int32_t per_channel;    /* multiplier/shift have OC entries */
+  int32_t double_round;   /* tosa.rescale rounding_mode == DOUBLE_ROUND */
+  int32_t requant_mode;   /* enum tb200_requant_mode */
+  int32_t in0_mult, in0_shift; /* input-side rescale of ADD/MUL/CONCAT (scalar) */
+  int32_t in1_mult, in1_shift;
+  int32_t out_mult, out_shift; /* output rescale of elementwise ops (scalar) */
+  int32_t pad_value;      /* MAXPOOL: constant of the folded tosa.pad */
+  int32_t i0, i1, i2, i3; /* op-specific (decoder: heads, kv heads, head_dim, window) */
+  float f0, f1, f2, f3;   /* op-specific (eps, rope theta, scale) */
+} tb200_op_t;
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TORQ_B200_OPS_H_ */

@@ -1,0 +1,199 @@
+"""Second, independent restatement of the oracle in numpy (int64 arithmetic).
+
+TEST INFRASTRUCTURE ONLY. PARITY UNPINNED (no golden outputs exist in the
+reference; see tosa_oracle.h). Its one purpose: tosa_oracle.c and this file are
+written separately and must agree bit-for-bit on seeded cases, so that a slip
+in either restatement shows before a GPU kernel is compared with them.
+
+Arithmetic order follows
+compiler/torq/Conversions/LinalgToTorqHL/PatternUtils.cpp:426-451,3441-3451
+(extsi -> subi(zp) -> apply_scale -> addi(zp) -> maxsi -> minsi -> trunci) and
+TOSA 1.0.1 apply_scale_32.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+
+def wrap32(v):
+    """int32 wrap-around of an int64 array (compiler/torq/Utils/ConversionUtils.cpp:40-45)."""
+    v = np.asarray(v, dtype=np.int64)
+    return ((v + (1 << 31)) & 0xFFFFFFFF) - (1 << 31)
+
+
+def apply_scale_32(value, multiplier, shift, double_round=True):
+    value = np.asarray(value, dtype=np.int64)
+    multiplier = np.asarray(multiplier, dtype=np.int64)
+    shift = np.asarray(shift, dtype=np.int64)
+    rnd = np.left_shift(np.int64(1), shift - 1)
+    if double_round:
+        extra = np.where(value >= 0, np.int64(1 << 30), np.int64(-(1 << 30)))
+        rnd = rnd + np.where(shift > 31, extra, 0)
+    r = value * multiplier + rnd
+    r = np.right_shift(r, shift)  # arithmetic on int64
+    return wrap32(r)
+
+
+def reciprocal_scale(count: int):
+    """compiler/torq/Conversions/TosaToTorqHL/Patterns.cpp:796-805."""
+    k = (count - 1).bit_length()
+    numerator = ((1 << 30) + 1) << k
+    return numerator // count, 30 + k
+
+
+def quantize_multiplier(real: float):
+    if real == 0.0:
+        return 0, 2
+    q, e = math.frexp(real)
+    f = q * (1 << 31)  # llround semantics: ties away from zero
+    m = int(math.floor(f + 0.5)) if f >= 0 else -int(math.floor(-f + 0.5))
+    if m == (1 << 31):
+        m //= 2
+        e += 1
+    s = 31 - e
+    if s > 62:
+        m >>= s - 62
+        s = 62
+    return m, s
+
+
+def requant(acc, multiplier, shift, out_zp, clamp_min, clamp_max, double_round=True, mode=0):
+    """acc [..., OC] int64 (already wrapped to int32 range)."""
+    multiplier = np.asarray(multiplier, dtype=np.int64)
+    shift = np.asarray(shift, dtype=np.int64)
+    if mode == 0:
+        r = apply_scale_32(acc, multiplier, shift, double_round)
+    else:  # compiler/torq/Utils/Kernel.h:607-635
+        sh = int(shift.min())
+        scale = np.right_shift(multiplier, shift - sh)
+        r = wrap32(np.right_shift(acc * scale + (1 << (sh - 1)), sh))
+    r = wrap32(r + out_zp)
+    return np.clip(r, clamp_min, clamp_max).astype(np.int8)
+
+
+def _out_dim(i, k, s, d, p0, p1):
+    return (i + p0 + p1 - d * (k - 1) - 1) // s + 1
+
+
+def conv2d(x, w, bias, multiplier, shift, out_zp, clamp_min, clamp_max, stride=(1, 1), dilation=(1, 1),
+           pad=(0, 0, 0, 0), input_zp=0, weight_zp=0, double_round=True, mode=0):
+    x = np.asarray(x, np.int64)
+    w = np.asarray(w, np.int64)
+    N, H, W, IC = x.shape
+    OC, KH, KW, _ = w.shape
+    OH = _out_dim(H, KH, stride[0], dilation[0], pad[0], pad[1])
+    OW = _out_dim(W, KW, stride[1], dilation[1], pad[2], pad[3])
+    # literal padding with input_zp: padded taps then contribute exactly zero
+    xp = np.full((N, H + pad[0] + pad[1], W + pad[2] + pad[3], IC), input_zp, np.int64)
+    xp[:, pad[0]:pad[0] + H, pad[2]:pad[2] + W, :] = x
+    acc = np.zeros((N, OH, OW, OC), np.int64)
+    for kh in range(KH):
+        for kw in range(KW):
+            ys = kh * dilation[0]
+            xs = kw * dilation[1]
+            patch = xp[:, ys:ys + (OH - 1) * stride[0] + 1:stride[0], xs:xs + (OW - 1) * stride[1] + 1:stride[1], :]
+            acc += np.einsum("nhwc,oc->nhwo", patch - input_zp, w[:, kh, kw, :] - weight_zp)
+    acc = wrap32(wrap32(acc) + np.asarray(bias, np.int64))
+    return requant(acc, multiplier, shift, out_zp, clamp_min, clamp_max, double_round, mode)
+
+
+def depthwise(x, w, bias, multiplier, shift, out_zp, clamp_min, clamp_max, stride=(1, 1), dilation=(1, 1),
+              pad=(0, 0, 0, 0), input_zp=0, weight_zp=0, double_round=True, mode=0):
+    x = np.asarray(x, np.int64)
+    w = np.asarray(w, np.int64)
+    N, H, W, C = x.shape
+    KH, KW, _, M = w.shape
+    OH = _out_dim(H, KH, stride[0], dilation[0], pad[0], pad[1])
+    OW = _out_dim(W, KW, stride[1], dilation[1], pad[2], pad[3])
+    xp = np.full((N, H + pad[0] + pad[1], W + pad[2] + pad[3], C), input_zp, np.int64)
+    xp[:, pad[0]:pad[0] + H, pad[2]:pad[2] + W, :] = x
+    acc = np.zeros((N, OH, OW, C, M), np.int64)
+    for kh in range(KH):
+        for kw in range(KW):
+            ys = kh * dilation[0]
+            xs = kw * dilation[1]
+            patch = xp[:, ys:ys + (OH - 1) * stride[0] + 1:stride[0], xs:xs + (OW - 1) * stride[1] + 1:stride[1], :]
+            acc += (patch - input_zp)[..., None] * (w[kh, kw] - weight_zp)[None, None, None]
+    acc = acc.reshape(N, OH, OW, C * M)
+    acc = wrap32(wrap32(acc) + np.asarray(bias, np.int64))
+    return requant(acc, multiplier, shift, out_zp, clamp_min, clamp_max, double_round, mode)
+
+
+def fully_connected(a, w, bias, multiplier, shift, out_zp, clamp_min, clamp_max, input_zp=0, weight_zp=0,
+                    double_round=True, mode=0):
+    a = np.asarray(a, np.int64) - input_zp
+    w = np.asarray(w, np.int64) - weight_zp
+    acc = wrap32(wrap32(a @ w.T) + np.asarray(bias, np.int64))
+    return requant(acc, multiplier, shift, out_zp, clamp_min, clamp_max, double_round, mode)
+
+
+def matmul_i32(a, b, a_zp=0, b_zp=0):
+    return wrap32((np.asarray(a, np.int64) - a_zp) @ (np.asarray(b, np.int64) - b_zp)).astype(np.int32)
+
+
+def _windows(x, kernel, stride, pad, fill):
+    N, H, W, C = x.shape
+    OH = _out_dim(H, kernel[0], stride[0], 1, pad[0], pad[1])
+    OW = _out_dim(W, kernel[1], stride[1], 1, pad[2], pad[3])
+    xp = np.full((N, H + pad[0] + pad[1], W + pad[2] + pad[3], C), fill, np.int64)
+    xp[:, pad[0]:pad[0] + H, pad[2]:pad[2] + W, :] = x
+    for kh in range(kernel[0]):
+        for kw in range(kernel[1]):
+            yield xp[:, kh:kh + (OH - 1) * stride[0] + 1:stride[0], kw:kw + (OW - 1) * stride[1] + 1:stride[1], :]
+
+
+def maxpool(x, kernel, stride, pad=(0, 0, 0, 0), pad_value=-128):
+    x = np.asarray(x, np.int64)
+    out = None
+    for win in _windows(x, kernel, stride, pad, pad_value):
+        out = win.copy() if out is None else np.maximum(out, win)
+    return out.astype(np.int8)
+
+
+def avgpool(x, kernel, stride, pad=(0, 0, 0, 0), input_zp=0, output_zp=0):
+    x = np.asarray(x, np.int64)
+    acc = None
+    cnt = None
+    ones = np.ones_like(x)
+    for win, one in zip(_windows(x - input_zp, kernel, stride, pad, 0), _windows(ones, kernel, stride, pad, 0)):
+        acc = win.copy() if acc is None else acc + win
+        cnt = one.copy() if cnt is None else cnt + one
+    acc = wrap32(acc)
+    mult = np.zeros_like(cnt)
+    sh = np.zeros_like(cnt)
+    for c in np.unique(cnt):
+        m, s = reciprocal_scale(int(c))
+        mult[cnt == c] = m
+        sh[cnt == c] = s
+    r = wrap32(apply_scale_32(acc, mult, sh, False) + output_zp)
+    return np.clip(r, -128, 127).astype(np.int8)
+
+
+def binary(kind, a, b, a_zp, a_mult, a_shift, b_zp, b_mult, b_shift, out_mult, out_shift, out_zp,
+           double_round=True, clamp_min=-128, clamp_max=127):
+    ra = apply_scale_32(np.asarray(a, np.int64) - a_zp, a_mult, a_shift, double_round)
+    rb = apply_scale_32(np.asarray(b, np.int64) - b_zp, b_mult, b_shift, double_round)
+    v = wrap32({"add": ra + rb, "sub": ra - rb, "mul": ra * rb}[kind])
+    r = wrap32(apply_scale_32(v, out_mult, out_shift, double_round) + out_zp)
+    return np.clip(r, clamp_min, clamp_max).astype(np.int8)
+
+
+def table(x, tbl):
+    return np.asarray(tbl, np.int8)[np.asarray(x, np.int64) + 128]
+
+
+def rescale(x, multiplier, shift, input_zp, out_zp, clamp_min=-128, clamp_max=127, double_round=True, mode=0):
+    return requant(np.asarray(x, np.int64) - input_zp, multiplier, shift, out_zp, clamp_min, clamp_max,
+                   double_round, mode)
+
+
+def resize_nn2x(x):
+    return np.repeat(np.repeat(np.asarray(x, np.int8), 2, axis=1), 2, axis=2)
+
+
+def concat2(a, b, a_zp, a_mult, a_shift, b_zp, b_mult, b_shift, out_zp, double_round=True):
+    ra = rescale(a, a_mult, a_shift, a_zp, out_zp, double_round=double_round)
+    rb = rescale(b, b_mult, b_shift, b_zp, out_zp, double_round=double_round)
+    return np.concatenate([ra, rb], axis=-1)

@@ -1,0 +1,249 @@
+// Bandwidth-bound layer kernels: pooling, rescaled add/sub/mul, 256-entry table,
+// standalone rescale (also the building block of a rescaled concat), 2x nearest
+// resize. 128-bit accesses wherever the channel count allows; grids sized in
+// whole multiples of the SM count with grid-stride loops.
+#include "kernels.h"
+
+namespace tb200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline unsigned grid_for(long long work_items, int per_block = kThreads) {
+  long long blocks = (work_items + per_block - 1) / per_block;
+  const long long cap = 148LL * 16;  // 148 SMs x resident blocks; the loops stride over the rest
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned)blocks;
+}
+
+// ---- max pool: torq_hl.maxpool2d (PoolingPattern.cpp:128-258) ----
+template <int VEC>  // channels per thread: 16 (uint4) or 1
+__global__ void __launch_bounds__(kThreads) maxpool_kernel(PoolArgs a) {
+  const int groups = a.C / VEC;
+  const long long total = (long long)a.N * a.OH * a.OW * groups;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    int g = (int)(idx % groups);
+    long long p = idx / groups;
+    int ow = (int)(p % a.OW);
+    long long t = p / a.OW;
+    int oh = (int)(t % a.OH);
+    int n = (int)(t / a.OH);
+    const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.C + g * VEC;
+    if (VEC == 16) {
+      uint32_t best[4] = {0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u};
+      const uint32_t padw = (uint32_t)(a.pad_value & 0xff) * 0x01010101u;
+      for (int kh = 0; kh < a.KH; kh++) {
+        int ih = oh * a.stride_h - a.pad_t + kh;
+        for (int kw = 0; kw < a.KW; kw++) {
+          int iw = ow * a.stride_w - a.pad_l + kw;
+          uint4 v;
+          if (ih < 0 || ih >= a.H || iw < 0 || iw >= a.W) v = make_uint4(padw, padw, padw, padw);
+          else v = *reinterpret_cast<const uint4*>(xin + ((size_t)ih * a.W + iw) * a.C);
+          best[0] = __vmaxs4(best[0], v.x);
+          best[1] = __vmaxs4(best[1], v.y);
+          best[2] = __vmaxs4(best[2], v.z);
+          best[3] = __vmaxs4(best[3], v.w);
+        }
+      }
+      *reinterpret_cast<uint4*>(a.out + (size_t)p * a.C + g * 16) = make_uint4(best[0], best[1], best[2], best[3]);
+    } else {
+      int best = -128;
+      for (int kh = 0; kh < a.KH; kh++) {
+        int ih = oh * a.stride_h - a.pad_t + kh;
+        for (int kw = 0; kw < a.KW; kw++) {
+          int iw = ow * a.stride_w - a.pad_l + kw;
+          int v = (ih < 0 || ih >= a.H || iw < 0 || iw >= a.W) ? a.pad_value
+                                                               : (int)xin[((size_t)ih * a.W + iw) * a.C];
+          best = max(best, v);
+        }
+      }
+      a.out[(size_t)p * a.C + g] = (int8_t)best;
+    }
+  }
+}
+
+// reciprocal_scale of the TOSA spec (compiler/torq/Conversions/TosaToTorqHL/Patterns.cpp:796-805)
+__device__ __forceinline__ void reciprocal_scale(uint32_t count, int32_t& mult, int32_t& shift) {
+  int k = 32 - __clz((int)(count - 1));
+  if (count == 1) k = 0;
+  long long numerator = ((1ll << 30) + 1) << k;
+  mult = (int32_t)(numerator / (long long)count);
+  shift = 30 + k;
+}
+
+// ---- average pool: tosa.avg_pool2d acc_type=i32; count excludes padding ----
+template <int VEC>  // 4 or 1 channels per thread
+__global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
+  const int groups = a.C / VEC;
+  const long long total = (long long)a.N * a.OH * a.OW * groups;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    int g = (int)(idx % groups);
+    long long p = idx / groups;
+    int ow = (int)(p % a.OW);
+    long long t = p / a.OW;
+    int oh = (int)(t % a.OH);
+    int n = (int)(t / a.OH);
+    const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.C + g * VEC;
+    int acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; j++) acc[j] = 0;
+    uint32_t count = 0;
+    for (int kh = 0; kh < a.KH; kh++) {
+      int ih = oh * a.stride_h - a.pad_t + kh;
+      if (ih < 0 || ih >= a.H) continue;
+      for (int kw = 0; kw < a.KW; kw++) {
+        int iw = ow * a.stride_w - a.pad_l + kw;
+        if (iw < 0 || iw >= a.W) continue;
+        count++;
+        if (VEC == 4) {
+          uint32_t v = *reinterpret_cast<const uint32_t*>(xin + ((size_t)ih * a.W + iw) * a.C);
+#pragma unroll
+          for (int j = 0; j < VEC; j++) acc[j] += sx8(v, j) - a.input_zp;
+        } else {
+          acc[0] += (int)xin[((size_t)ih * a.W + iw) * a.C] - a.input_zp;
+        }
+      }
+    }
+    int32_t mult, shift;
+    reciprocal_scale(count ? count : 1u, mult, shift);
+    int q[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; j++) q[j] = requant(acc[j], mult, shift, false, a.output_zp, -128, 127);
+    if (VEC == 4) *reinterpret_cast<uint32_t*>(a.out + (size_t)p * a.C + g * 4) = pack4(q[0], q[1], q[2], q[3]);
+    else a.out[(size_t)p * a.C + g] = (int8_t)q[0];
+  }
+}
+
+// ---- add / sub / mul in TOSA form (ElementWiseBinaryPattern.cpp:385-570, MulPattern.cpp:229-238) ----
+__device__ __forceinline__ int binary_one(const BinaryArgs& a, int av, int bv) {
+  const bool dr = a.double_round != 0;
+  int ra = apply_scale_32(av - a.a_zp, a.a_mult, a.a_shift, dr);
+  int rb = apply_scale_32(bv - a.b_zp, a.b_mult, a.b_shift, dr);
+  int v = a.kind == 0 ? ra + rb : a.kind == 1 ? ra - rb : ra * rb;
+  return requant(v, a.out_mult, a.out_shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
+}
+
+__global__ void __launch_bounds__(kThreads) binary_kernel(BinaryArgs a) {
+  const long long nvec = a.n >> 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (long long i = tid; i < nvec; i += stride) {
+    uint4 va = reinterpret_cast<const uint4*>(a.a)[i];
+    uint4 vb = reinterpret_cast<const uint4*>(a.b)[i];
+    uint32_t wa[4] = {va.x, va.y, va.z, va.w};
+    uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
+    uint32_t wo[4];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      int q[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) q[j] = binary_one(a, sx8(wa[w], j), sx8(wb[w], j));
+      wo[w] = pack4(q[0], q[1], q[2], q[3]);
+    }
+    reinterpret_cast<uint4*>(a.out)[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+  }
+  for (long long i = (nvec << 4) + tid; i < a.n; i += stride)
+    a.out[i] = (int8_t)binary_one(a, a.a[i], a.b[i]);
+}
+
+// ---- table: out = table[x + 128] (ExtractPattern.cpp:97-135) ----
+__global__ void __launch_bounds__(kThreads) table_kernel(const int8_t* __restrict__ x,
+                                                         const int8_t* __restrict__ table,
+                                                         int8_t* __restrict__ out, long long n) {
+  __shared__ uint8_t lut[256];
+  // index by the raw byte: entry for byte b is table[(int8)b + 128]
+  lut[threadIdx.x] = (uint8_t)table[(int)(int8_t)threadIdx.x + 128];
+  __syncthreads();
+  const long long nvec = n >> 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (long long i = tid; i < nvec; i += stride) {
+    uint4 v = reinterpret_cast<const uint4*>(x)[i];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      uint32_t r = 0;
+#pragma unroll
+      for (int j = 0; j < 4; j++) r |= (uint32_t)lut[(w[k] >> (8 * j)) & 0xff] << (8 * j);
+      w[k] = r;
+    }
+    reinterpret_cast<uint4*>(out)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  for (long long i = (nvec << 4) + tid; i < n; i += stride) out[i] = (int8_t)lut[(uint8_t)x[i]];
+}
+
+// ---- standalone rescale i8 -> i8 (PatternUtils.cpp:426-435,3441-3451) ----
+__global__ void __launch_bounds__(kThreads) rescale_kernel(RescaleArgs a) {
+  const long long total = a.rows * a.C;
+  const bool dr = a.double_round != 0;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(idx % a.C);
+    long long r = idx / a.C;
+    ChanParams cp = a.chan[a.per_channel ? c : 0];
+    int v = (int)a.x[idx] - a.input_zp;
+    a.out[(size_t)r * a.out_row_stride + a.out_col_offset + c] =
+        (int8_t)requant(v, cp.mult, cp.shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
+  }
+}
+
+// ---- nearest 2x (PatternUtils.cpp:489-491): out[y,x] = in[y/2, x/2] ----
+__global__ void __launch_bounds__(kThreads) resize_nn2x_kernel(const int8_t* __restrict__ x,
+                                                               int8_t* __restrict__ out, int N, int H,
+                                                               int W, int C) {
+  const long long total = (long long)N * 2 * H * 2 * W * C;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(idx % C);
+    long long p = idx / C;
+    int ow = (int)(p % (2 * W));
+    long long t = p / (2 * W);
+    int oh = (int)(t % (2 * H));
+    int n = (int)(t / (2 * H));
+    out[idx] = x[(((size_t)n * H + (oh >> 1)) * W + (ow >> 1)) * C + c];
+  }
+}
+
+}  // namespace
+
+void launch_maxpool(const PoolArgs& a, cudaStream_t stream) {
+  if ((a.C & 15) == 0) {
+    long long total = (long long)a.N * a.OH * a.OW * (a.C / 16);
+    maxpool_kernel<16><<<grid_for(total), kThreads, 0, stream>>>(a);
+  } else {
+    long long total = (long long)a.N * a.OH * a.OW * a.C;
+    maxpool_kernel<1><<<grid_for(total), kThreads, 0, stream>>>(a);
+  }
+}
+
+void launch_avgpool(const PoolArgs& a, cudaStream_t stream) {
+  if ((a.C & 3) == 0) {
+    long long total = (long long)a.N * a.OH * a.OW * (a.C / 4);
+    avgpool_kernel<4><<<grid_for(total), kThreads, 0, stream>>>(a);
+  } else {
+    long long total = (long long)a.N * a.OH * a.OW * a.C;
+    avgpool_kernel<1><<<grid_for(total), kThreads, 0, stream>>>(a);
+  }
+}
+
+void launch_binary(const BinaryArgs& a, cudaStream_t stream) {
+  binary_kernel<<<grid_for((a.n + 15) / 16), kThreads, 0, stream>>>(a);
+}
+
+void launch_table(const int8_t* x, const int8_t* table, int8_t* out, long long n, cudaStream_t stream) {
+  table_kernel<<<grid_for((n + 15) / 16), kThreads, 0, stream>>>(x, table, out, n);
+}
+
+void launch_rescale(const RescaleArgs& a, cudaStream_t stream) {
+  rescale_kernel<<<grid_for(a.rows * a.C), kThreads, 0, stream>>>(a);
+}
+
+void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream) {
+  resize_nn2x_kernel<<<grid_for((long long)N * 4 * H * W * C), kThreads, 0, stream>>>(x, out, N, H, W, C);
+}
+
+}  // namespace tb200

@@ -1,0 +1,75 @@
+// Host-callable launchers of the layer kernels. Every launcher only enqueues
+// work on `stream`; none allocates or synchronises.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace tb200 {
+
+struct ConvArgs {
+  const int8_t* x;        // NHWC
+  const int8_t* w;        // packed [OC][Kpad], K order (kh, kw, ic), zero padded
+  const ChanParams* chan; // [OC]
+  int8_t* out;            // NHWC
+  int N, H, W, IC, OC, KH, KW, OH, OW;
+  int stride_h, stride_w, dil_h, dil_w, pad_t, pad_l;
+  int K, Kpad;            // KH*KW*IC and its padded row length
+  int input_zp, weight_zp, out_zp, clamp_min, clamp_max;
+  int double_round;
+};
+void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream);
+
+struct DwArgs {
+  const int8_t* x;        // NHWC
+  const int8_t* w;        // [KH][KW][C][M]
+  const ChanParams* chan; // [C*M], bias unmodified (taps outside the image are skipped)
+  int8_t* out;
+  int N, H, W, C, M, KH, KW, OH, OW;
+  int stride_h, stride_w, dil_h, dil_w, pad_t, pad_l;
+  int input_zp, weight_zp, out_zp, clamp_min, clamp_max;
+  int double_round;
+};
+void launch_depthwise(const DwArgs& a, cudaStream_t stream);
+
+// raw int8 x int8 -> int32 matmul, b is [K][N]
+void launch_matmul_i32(const int8_t* a, const int8_t* b, int32_t* out, int M, int K, int N, int a_zp,
+                       int b_zp, cudaStream_t stream);
+
+struct PoolArgs {
+  const int8_t* x;
+  int8_t* out;
+  int N, H, W, C, KH, KW, OH, OW, stride_h, stride_w, pad_t, pad_l;
+  int pad_value;            // max pool
+  int input_zp, output_zp;  // avg pool
+};
+void launch_maxpool(const PoolArgs& a, cudaStream_t stream);
+void launch_avgpool(const PoolArgs& a, cudaStream_t stream);
+
+struct BinaryArgs {
+  const int8_t* a;
+  const int8_t* b;
+  int8_t* out;
+  long long n;
+  int kind;  // 0 add, 1 sub, 2 mul
+  int a_zp, a_mult, a_shift, b_zp, b_mult, b_shift, out_mult, out_shift, out_zp;
+  int double_round, clamp_min, clamp_max;
+};
+void launch_binary(const BinaryArgs& a, cudaStream_t stream);
+
+void launch_table(const int8_t* x, const int8_t* table, int8_t* out, long long n, cudaStream_t stream);
+
+struct RescaleArgs {
+  const int8_t* x;
+  int8_t* out;
+  const ChanParams* chan;  // [C] or [1]
+  long long rows;
+  int C, per_channel, input_zp, out_zp, clamp_min, clamp_max, double_round;
+  int out_row_stride, out_col_offset;  // lets a concat write into a wider row
+};
+void launch_rescale(const RescaleArgs& a, cudaStream_t stream);
+
+void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream);
+
+}  // namespace tb200

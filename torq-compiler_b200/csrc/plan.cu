@@ -1,0 +1,532 @@
+// See plan.h. Validation mirrors what the reference checks when it matches an
+// op (kernel size, strides, operand ranks) and reports INVALID_ARGUMENT /
+// UNIMPLEMENTED instead of silently taking another path.
+#include "plan.h"
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdlib>
+#include <cstring>
+
+#include "../../include/torq_b200.h"
+#include "kernels.h"
+
+namespace tb200 {
+
+namespace {
+
+struct Builder {
+  const std::vector<tb200_tensor_t>& tensors;
+  const std::vector<tb200_op_t>& ops;
+  const std::vector<uint8_t>& constants;
+  Plan& plan;
+  std::string& err;
+  int status = TB200_OK;
+
+  int fail(int st, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    err = buf;
+    status = st;
+    return st;
+  }
+
+  bool valid_id(int id) const { return id >= 0 && id < (int)tensors.size(); }
+
+  size_t add_const(const void* data, size_t bytes) {
+    size_t off = (plan.const_image.size() + 255) & ~(size_t)255;
+    plan.const_image.resize(off + bytes);
+    memcpy(plan.const_image.data() + off, data, bytes);
+    return off;
+  }
+
+  template <typename T>
+  const T* const_data(int id, size_t min_elems, const char* what, int op_index) {
+    if (!valid_id(id) || tensors[id].kind != TB200_TENSOR_CONSTANT) {
+      fail(TB200_INVALID_ARGUMENT, "op %d: %s is not a constant tensor", op_index, what);
+      return nullptr;
+    }
+    const auto& t = tensors[id];
+    if (t.const_bytes < min_elems * sizeof(T)) {
+      fail(TB200_INVALID_ARGUMENT, "op %d: %s holds %llu bytes, needs %zu", op_index, what,
+           (unsigned long long)t.const_bytes, min_elems * sizeof(T));
+      return nullptr;
+    }
+    return reinterpret_cast<const T*>(constants.data() + t.const_offset);
+  }
+
+  size_t numel(int id) const {
+    const auto& t = tensors[id];
+    size_t n = 1;
+    for (uint32_t i = 0; i < t.rank; i++) n *= (size_t)t.shape[i];
+    return n;
+  }
+
+  bool act_i8(int id, uint32_t rank) const {
+    return valid_id(id) && tensors[id].dtype == TB200_I8 && tensors[id].rank == rank &&
+           tensors[id].kind != TB200_TENSOR_CONSTANT;
+  }
+
+  // Per-channel epilogue parameters from bias[], multiplier[], shift[] of the op.
+  // Mode (B) (compiler/torq/Utils/Kernel.h:607-635) becomes the same device code
+  // with scale[c] = M[c] >> (S[c] - min S), shift = min S and single rounding
+  // (compiler/torq/Conversions/LinalgToTorqHL/PatternUtils.cpp:3536-3549).
+  bool chan_params(const tb200_op_t& op, int op_index, int OC, const int32_t* wsum, long long K,
+                   bool fold_zp, std::vector<ChanParams>& out, int& double_round) {
+    int nscale = op.per_channel ? OC : 1;
+    const int32_t* mult = const_data<int32_t>(op.multiplier, nscale, "multiplier", op_index);
+    const int8_t* shift = const_data<int8_t>(op.shift, nscale, "shift", op_index);
+    if (!mult || !shift) return false;
+    const int32_t* bias = nullptr;
+    int bias_len = 0;
+    if (op.bias >= 0) {
+      if (!valid_id(op.bias)) {
+        fail(TB200_INVALID_ARGUMENT, "op %d: bad bias id", op_index);
+        return false;
+      }
+      bias_len = (int)numel(op.bias);
+      if (bias_len != 1 && bias_len != OC) {
+        fail(TB200_INVALID_ARGUMENT, "op %d: bias has %d entries, expected 1 or %d", op_index, bias_len, OC);
+        return false;
+      }
+      bias = const_data<int32_t>(op.bias, bias_len, "bias", op_index);
+      if (!bias) return false;
+    }
+    int min_shift = 127;
+    for (int i = 0; i < nscale; i++) {
+      if (shift[i] < 2 || shift[i] > 62) {
+        fail(TB200_INVALID_ARGUMENT, "op %d: rescale shift %d outside [2,62]", op_index, (int)shift[i]);
+        return false;
+      }
+      min_shift = std::min(min_shift, (int)shift[i]);
+    }
+    double_round = op.double_round;
+    if (op.requant_mode == TB200_REQUANT_NPU) double_round = 0;
+    else if (op.requant_mode != TB200_REQUANT_TOSA) {
+      fail(TB200_INVALID_ARGUMENT, "op %d: unknown requant mode %d", op_index, op.requant_mode);
+      return false;
+    }
+    out.resize(OC);
+    for (int c = 0; c < OC; c++) {
+      int i = op.per_channel ? c : 0;
+      ChanParams p;
+      uint32_t b = bias ? (uint32_t)bias[bias_len == 1 ? 0 : c] : 0u;
+      p.wsum = wsum ? wsum[c] : 0;
+      if (fold_zp && wsum) {
+        // bias - izp * sum(w) + K * izp * wzp, modulo 2^32
+        b -= (uint32_t)op.in0_zp * (uint32_t)wsum[c];
+        b += (uint32_t)(K & 0xffffffffll) * (uint32_t)op.in0_zp * (uint32_t)op.weight_zp;
+      }
+      p.bias = (int32_t)b;
+      if (op.requant_mode == TB200_REQUANT_NPU) {
+        p.mult = mult[i] >> (shift[i] - min_shift);
+        p.shift = min_shift;
+      } else {
+        p.mult = mult[i];
+        p.shift = shift[i];
+      }
+      out[c] = p;
+    }
+    return true;
+  }
+};
+
+int conv_out_dim(int i, int k, int s, int d, int p0, int p1) { return (i + p0 + p1 - d * (k - 1) - 1) / s + 1; }
+
+bool force_simt() {
+  const char* e = getenv("TB200_FORCE_SIMT");
+  return e && *e && *e != '0';
+}
+
+}  // namespace
+
+int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb200_op_t>& ops,
+               const std::vector<uint8_t>& constants, Plan& plan, std::string& err) {
+  Builder b{tensors, ops, constants, plan, err};
+  const int nt = (int)tensors.size();
+  (void)force_simt;
+
+  // ---- tensor placement: io slots, state prefix, liveness-packed activations ----
+  plan.tensor_loc.assign(nt, Loc{});
+  std::vector<int> first_def(nt, -1), last_use(nt, -1), root(nt);
+  for (int id = 0; id < nt; id++) root[id] = id;
+  for (int i = 0; i < (int)ops.size(); i++) {
+    const auto& op = ops[i];
+    int ins[3] = {op.in0, op.in1, op.in2};
+    int outs[2] = {op.out0, op.out1};
+    for (int id : ins)
+      if (id >= 0) {
+        if (!b.valid_id(id)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input tensor id %d out of range", i, id);
+        last_use[root[id]] = i;
+      }
+    for (int id : outs)
+      if (id >= 0) {
+        if (!b.valid_id(id)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: output tensor id %d out of range", i, id);
+        if (tensors[id].kind == TB200_TENSOR_CONSTANT || tensors[id].kind == TB200_TENSOR_INPUT)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d writes tensor %d which is not writable", i, id);
+        if (first_def[id] < 0) first_def[id] = i;
+        last_use[id] = std::max(last_use[id], i);
+      }
+    if (op.kind == TB200_OP_RESHAPE) {
+      // a view: shares the storage (and the lifetime) of what it reshapes
+      if (op.in0 < 0 || op.out0 < 0 || tensors[op.out0].kind != TB200_TENSOR_ACTIVATION ||
+          tensors[op.in0].kind == TB200_TENSOR_CONSTANT)
+        return b.fail(TB200_INVALID_ARGUMENT, "op %d: reshape wants a non-constant input and an intermediate result", i);
+      root[op.out0] = root[op.in0];
+    }
+  }
+  auto bytes_of = [&](int id) {
+    size_t n = b.numel(id);
+    switch (tensors[id].dtype) {
+      case TB200_I8: return n;
+      case TB200_I16: case TB200_BF16: return n * 2;
+      case TB200_I64: return n * 8;
+      default: return n * 4;
+    }
+  };
+  size_t cursor = 0;
+  for (int id = 0; id < nt; id++)
+    if (tensors[id].kind == TB200_TENSOR_STATE) {
+      plan.tensor_loc[id] = Loc{Loc::ARENA, cursor};
+      cursor += (bytes_of(id) + 255) & ~(size_t)255;
+    }
+  plan.state_bytes = cursor;
+  {
+    struct Block { size_t off, size; int id; };
+    std::vector<Block> live;
+    size_t high = cursor;
+    const size_t base = cursor;
+    for (int i = 0; i < (int)ops.size(); i++) {
+      int outs[2] = {ops[i].out0, ops[i].out1};
+      for (int id : outs) {
+        if (id < 0 || tensors[id].kind != TB200_TENSOR_ACTIVATION || first_def[id] != i) continue;
+        if (plan.tensor_loc[id].kind != Loc::NONE || root[id] != id) continue;
+        size_t need = (bytes_of(id) + 255) & ~(size_t)255;
+        std::sort(live.begin(), live.end(), [](const Block& x, const Block& y) { return x.off < y.off; });
+        size_t pos = base;
+        for (const auto& blk : live) {
+          if (blk.off >= pos + need) break;
+          pos = std::max(pos, blk.off + blk.size);
+        }
+        live.push_back({pos, need, id});
+        plan.tensor_loc[id] = Loc{Loc::ARENA, pos};
+        high = std::max(high, pos + need);
+      }
+      live.erase(std::remove_if(live.begin(), live.end(), [&](const Block& blk) { return last_use[blk.id] <= i; }),
+                 live.end());
+    }
+    plan.arena_bytes = high;
+  }
+  {
+    // io slots are assigned by the order of the blob's input/output lists, which the
+    // caller of build_plan cannot see here; tensors carry their slot in `reserved`.
+    for (int id = 0; id < nt; id++)
+      if (tensors[id].kind == TB200_TENSOR_INPUT || tensors[id].kind == TB200_TENSOR_OUTPUT)
+        plan.tensor_loc[id] = Loc{Loc::IO, tensors[id].reserved};
+    for (int id = 0; id < nt; id++)
+      if (root[id] != id) plan.tensor_loc[id] = plan.tensor_loc[root[id]];
+  }
+
+  // ---- one step per op ----
+  for (int i = 0; i < (int)ops.size(); i++) {
+    const auto& op = ops[i];
+    Step step;
+    auto loc = [&](int id) { return id >= 0 ? plan.tensor_loc[id] : Loc{}; };
+    for (int id : {op.in0, op.in1, op.in2})
+      if (id >= 0 && tensors[id].kind != TB200_TENSOR_CONSTANT && plan.tensor_loc[id].kind == Loc::NONE)
+        return b.fail(TB200_INVALID_ARGUMENT, "op %d reads tensor %d before anything wrote it", i, id);
+
+    switch (op.kind) {
+      case TB200_OP_CONV2D:
+      case TB200_OP_FC: {
+        const bool fc = op.kind == TB200_OP_FC;
+        int N, H, W, IC, OC, KH, KW, OH, OW;
+        if (fc) {
+          if (!b.act_i8(op.in0, 2) || !b.act_i8(op.out0, 2) || !b.valid_id(op.weights) || tensors[op.weights].rank != 2)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: fully_connected wants int8 [M,K] x [N,K] -> [M,N]", i);
+          N = tensors[op.in0].shape[0]; H = W = 1; IC = tensors[op.in0].shape[1];
+          OC = tensors[op.weights].shape[0]; KH = KW = 1; OH = OW = 1;
+          if (tensors[op.weights].shape[1] != IC || tensors[op.out0].shape[0] != N || tensors[op.out0].shape[1] != OC)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: fully_connected shape mismatch", i);
+        } else {
+          if (!b.act_i8(op.in0, 4) || !b.act_i8(op.out0, 4) || !b.valid_id(op.weights) || tensors[op.weights].rank != 4)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: conv2d wants int8 NHWC input/output and OHWI weights", i);
+          const auto& x = tensors[op.in0]; const auto& w = tensors[op.weights]; const auto& o = tensors[op.out0];
+          N = x.shape[0]; H = x.shape[1]; W = x.shape[2]; IC = x.shape[3];
+          OC = w.shape[0]; KH = w.shape[1]; KW = w.shape[2];
+          if (w.shape[3] != IC) return b.fail(TB200_INVALID_ARGUMENT, "op %d: weight IC %d != input IC %d", i, w.shape[3], IC);
+          if (op.stride_h < 1 || op.stride_w < 1 || op.dil_h < 1 || op.dil_w < 1 || op.pad_t < 0 || op.pad_b < 0 ||
+              op.pad_l < 0 || op.pad_r < 0)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad stride/dilation/pad", i);
+          OH = conv_out_dim(H, KH, op.stride_h, op.dil_h, op.pad_t, op.pad_b);
+          OW = conv_out_dim(W, KW, op.stride_w, op.dil_w, op.pad_l, op.pad_r);
+          if (o.shape[0] != N || o.shape[1] != OH || o.shape[2] != OW || o.shape[3] != OC)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: conv2d output shape is not %dx%dx%dx%d", i, N, OH, OW, OC);
+        }
+        const long long K = (long long)KH * KW * IC;
+        const int8_t* w = b.const_data<int8_t>(op.weights, (size_t)OC * K, "weights", i);
+        if (!w) return b.status;
+        const int Kpad = (int)((K + 31) / 32 * 32);
+        std::vector<int8_t> packed((size_t)OC * Kpad, 0);
+        std::vector<int32_t> wsum(OC, 0);
+        for (int oc = 0; oc < OC; oc++) {
+          memcpy(packed.data() + (size_t)oc * Kpad, w + (size_t)oc * K, (size_t)K);
+          int32_t s = 0;
+          for (long long k = 0; k < K; k++) s += w[(size_t)oc * K + k];
+          wsum[oc] = s;
+        }
+        std::vector<ChanParams> cp;
+        int dr = 0;
+        if (!b.chan_params(op, i, OC, wsum.data(), K, true, cp, dr)) return b.status;
+        ConvArgs a{};
+        a.N = N; a.H = H; a.W = W; a.IC = IC; a.OC = OC; a.KH = KH; a.KW = KW; a.OH = OH; a.OW = OW;
+        a.stride_h = fc ? 1 : op.stride_h; a.stride_w = fc ? 1 : op.stride_w;
+        a.dil_h = fc ? 1 : op.dil_h; a.dil_w = fc ? 1 : op.dil_w;
+        a.pad_t = fc ? 0 : op.pad_t; a.pad_l = fc ? 0 : op.pad_l;
+        a.K = (int)K; a.Kpad = Kpad;
+        a.input_zp = op.in0_zp; a.weight_zp = op.weight_zp; a.out_zp = op.out_zp;
+        a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max; a.double_round = dr;
+        if (op.in0_zp < -128 || op.in0_zp > 127) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input_zp outside int8", i);
+        size_t w_off = b.add_const(packed.data(), packed.size());
+        size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "conv2d_simt";
+        step.launch = [=](const ExecContext& c) {
+          ConvArgs k = a;
+          k.x = (const int8_t*)lx.resolve(c);
+          k.out = (int8_t*)lo.resolve(c);
+          k.w = (const int8_t*)(c.consts + w_off);
+          k.chan = (const ChanParams*)(c.consts + c_off);
+          launch_conv2d_simt(k, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_DEPTHWISE: {
+        if (!b.act_i8(op.in0, 4) || !b.act_i8(op.out0, 4) || !b.valid_id(op.weights) || tensors[op.weights].rank != 4)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: depthwise wants int8 NHWC input/output and [KH,KW,C,M] weights", i);
+        const auto& x = tensors[op.in0]; const auto& w = tensors[op.weights]; const auto& o = tensors[op.out0];
+        DwArgs a{};
+        a.N = x.shape[0]; a.H = x.shape[1]; a.W = x.shape[2]; a.C = x.shape[3];
+        a.KH = w.shape[0]; a.KW = w.shape[1]; a.M = w.shape[3];
+        if (w.shape[2] != a.C) return b.fail(TB200_INVALID_ARGUMENT, "op %d: depthwise weight C mismatch", i);
+        if (op.stride_h < 1 || op.stride_w < 1 || op.dil_h < 1 || op.dil_w < 1 || op.pad_t < 0 || op.pad_b < 0 ||
+            op.pad_l < 0 || op.pad_r < 0)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad stride/dilation/pad", i);
+        a.OH = conv_out_dim(a.H, a.KH, op.stride_h, op.dil_h, op.pad_t, op.pad_b);
+        a.OW = conv_out_dim(a.W, a.KW, op.stride_w, op.dil_w, op.pad_l, op.pad_r);
+        const int OC = a.C * a.M;
+        if (o.shape[0] != a.N || o.shape[1] != a.OH || o.shape[2] != a.OW || o.shape[3] != OC)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: depthwise output shape mismatch", i);
+        const int8_t* wd = b.const_data<int8_t>(op.weights, (size_t)a.KH * a.KW * OC, "weights", i);
+        if (!wd) return b.status;
+        std::vector<ChanParams> cp;
+        int dr = 0;
+        if (!b.chan_params(op, i, OC, nullptr, 0, false, cp, dr)) return b.status;
+        a.stride_h = op.stride_h; a.stride_w = op.stride_w; a.dil_h = op.dil_h; a.dil_w = op.dil_w;
+        a.pad_t = op.pad_t; a.pad_l = op.pad_l;
+        a.input_zp = op.in0_zp; a.weight_zp = op.weight_zp; a.out_zp = op.out_zp;
+        a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max; a.double_round = dr;
+        size_t w_off = b.add_const(wd, (size_t)a.KH * a.KW * OC);
+        size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "depthwise";
+        step.launch = [=](const ExecContext& c) {
+          DwArgs k = a;
+          k.x = (const int8_t*)lx.resolve(c);
+          k.out = (int8_t*)lo.resolve(c);
+          k.w = (const int8_t*)(c.consts + w_off);
+          k.chan = (const ChanParams*)(c.consts + c_off);
+          launch_depthwise(k, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_MATMUL_I32: {
+        if (!b.act_i8(op.in0, 2) || !b.valid_id(op.weights) || tensors[op.weights].rank != 2 || !b.valid_id(op.out0) ||
+            tensors[op.out0].dtype != TB200_I32 || tensors[op.out0].rank != 2)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul wants int8 [M,K] x const int8 [K,N] -> int32 [M,N]", i);
+        int M = tensors[op.in0].shape[0], K = tensors[op.in0].shape[1], N = tensors[op.weights].shape[1];
+        if (tensors[op.weights].shape[0] != K || tensors[op.out0].shape[0] != M || tensors[op.out0].shape[1] != N)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul shape mismatch", i);
+        const int8_t* wd = b.const_data<int8_t>(op.weights, (size_t)K * N, "weights", i);
+        if (!wd) return b.status;
+        size_t w_off = b.add_const(wd, (size_t)K * N);
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        int azp = op.in0_zp, bzp = op.weight_zp;
+        step.kernel_name = "matmul_i32";
+        step.launch = [=](const ExecContext& c) {
+          launch_matmul_i32((const int8_t*)lx.resolve(c), (const int8_t*)(c.consts + w_off), (int32_t*)lo.resolve(c),
+                            M, K, N, azp, bzp, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_MAXPOOL:
+      case TB200_OP_AVGPOOL: {
+        if (!b.act_i8(op.in0, 4) || !b.act_i8(op.out0, 4))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: pooling wants int8 NHWC input/output", i);
+        const auto& x = tensors[op.in0]; const auto& o = tensors[op.out0];
+        PoolArgs a{};
+        a.N = x.shape[0]; a.H = x.shape[1]; a.W = x.shape[2]; a.C = x.shape[3];
+        a.KH = op.kh; a.KW = op.kw; a.stride_h = op.stride_h; a.stride_w = op.stride_w;
+        a.pad_t = op.pad_t; a.pad_l = op.pad_l;
+        if (a.KH < 1 || a.KW < 1 || a.stride_h < 1 || a.stride_w < 1 || op.pad_t < 0 || op.pad_b < 0 || op.pad_l < 0 ||
+            op.pad_r < 0)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad pooling window", i);
+        a.OH = conv_out_dim(a.H, a.KH, a.stride_h, 1, op.pad_t, op.pad_b);
+        a.OW = conv_out_dim(a.W, a.KW, a.stride_w, 1, op.pad_l, op.pad_r);
+        if (o.shape[0] != a.N || o.shape[1] != a.OH || o.shape[2] != a.OW || o.shape[3] != a.C)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: pooling output shape mismatch", i);
+        a.pad_value = op.pad_value; a.input_zp = op.in0_zp; a.output_zp = op.out_zp;
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        const bool is_max = op.kind == TB200_OP_MAXPOOL;
+        step.kernel_name = is_max ? "maxpool" : "avgpool";
+        step.launch = [=](const ExecContext& c) {
+          PoolArgs k = a;
+          k.x = (const int8_t*)lx.resolve(c);
+          k.out = (int8_t*)lo.resolve(c);
+          if (is_max) launch_maxpool(k, c.stream);
+          else launch_avgpool(k, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_ADD:
+      case TB200_OP_SUB:
+      case TB200_OP_MUL: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.in1) || !b.valid_id(op.out0) || tensors[op.in0].dtype != TB200_I8 ||
+            tensors[op.in1].dtype != TB200_I8 || tensors[op.out0].dtype != TB200_I8)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: elementwise op wants int8 operands", i);
+        size_t n = b.numel(op.in0);
+        if (b.numel(op.in1) != n || b.numel(op.out0) != n)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: elementwise operands differ in size (no broadcast)", i);
+        for (int s : {op.in0_shift, op.in1_shift, op.out_shift})
+          if (s < 2 || s > 62) return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale shift %d outside [2,62]", i, s);
+        BinaryArgs a{};
+        a.n = (long long)n;
+        a.kind = op.kind == TB200_OP_ADD ? 0 : op.kind == TB200_OP_SUB ? 1 : 2;
+        a.a_zp = op.in0_zp; a.a_mult = op.in0_mult; a.a_shift = op.in0_shift;
+        a.b_zp = op.in1_zp; a.b_mult = op.in1_mult; a.b_shift = op.in1_shift;
+        a.out_mult = op.out_mult; a.out_shift = op.out_shift; a.out_zp = op.out_zp;
+        a.double_round = op.double_round; a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
+        Loc la = loc(op.in0), lb = loc(op.in1), lo = loc(op.out0);
+        step.kernel_name = "binary_rescale";
+        step.launch = [=](const ExecContext& c) {
+          BinaryArgs k = a;
+          k.a = (const int8_t*)la.resolve(c);
+          k.b = (const int8_t*)lb.resolve(c);
+          k.out = (int8_t*)lo.resolve(c);
+          launch_binary(k, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_TABLE: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || tensors[op.in0].dtype != TB200_I8 ||
+            tensors[op.out0].dtype != TB200_I8 || b.numel(op.in0) != b.numel(op.out0))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: table wants int8 input/output of equal size", i);
+        const int8_t* tbl = b.const_data<int8_t>(op.table, 256, "table", i);
+        if (!tbl) return b.status;
+        size_t t_off = b.add_const(tbl, 256);
+        long long n = (long long)b.numel(op.in0);
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "table";
+        step.launch = [=](const ExecContext& c) {
+          launch_table((const int8_t*)lx.resolve(c), (const int8_t*)(c.consts + t_off), (int8_t*)lo.resolve(c), n,
+                       c.stream);
+        };
+        break;
+      }
+      case TB200_OP_RESCALE: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || tensors[op.in0].dtype != TB200_I8 ||
+            tensors[op.out0].dtype != TB200_I8 || b.numel(op.in0) != b.numel(op.out0))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale wants int8 input/output of equal size", i);
+        const auto& x = tensors[op.in0];
+        int C = x.shape[x.rank - 1];
+        std::vector<ChanParams> cp;
+        int dr = 0;
+        if (!b.chan_params(op, i, op.per_channel ? C : 1, nullptr, 0, false, cp, dr)) return b.status;
+        RescaleArgs a{};
+        a.rows = (long long)(b.numel(op.in0) / C); a.C = C; a.per_channel = op.per_channel;
+        a.input_zp = op.in0_zp; a.out_zp = op.out_zp; a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
+        a.double_round = dr; a.out_row_stride = C; a.out_col_offset = 0;
+        size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "rescale";
+        step.launch = [=](const ExecContext& c) {
+          RescaleArgs k = a;
+          k.x = (const int8_t*)lx.resolve(c);
+          k.out = (int8_t*)lo.resolve(c);
+          k.chan = (const ChanParams*)(c.consts + c_off);
+          launch_rescale(k, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_CONCAT: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.in1) || !b.valid_id(op.out0) || tensors[op.in0].dtype != TB200_I8 ||
+            tensors[op.in1].dtype != TB200_I8 || tensors[op.out0].dtype != TB200_I8)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: concat wants int8 operands", i);
+        const auto& x0 = tensors[op.in0]; const auto& x1 = tensors[op.in1]; const auto& o = tensors[op.out0];
+        int C0 = x0.shape[x0.rank - 1], C1 = x1.shape[x1.rank - 1], CO = o.shape[o.rank - 1];
+        size_t rows = b.numel(op.in0) / C0;
+        if (C0 + C1 != CO || b.numel(op.in1) / C1 != rows || b.numel(op.out0) / CO != rows)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: concat (channel axis) shape mismatch", i);
+        for (int s : {op.in0_shift, op.in1_shift})
+          if (s < 2 || s > 62) return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale shift %d outside [2,62]", i, s);
+        ChanParams p0{0, op.in0_mult, op.in0_shift, 0}, p1{0, op.in1_mult, op.in1_shift, 0};
+        size_t c0_off = b.add_const(&p0, sizeof(p0));
+        size_t c1_off = b.add_const(&p1, sizeof(p1));
+        RescaleArgs a0{}, a1{};
+        a0.rows = a1.rows = (long long)rows;
+        a0.C = C0; a1.C = C1;
+        a0.input_zp = op.in0_zp; a1.input_zp = op.in1_zp;
+        a0.out_zp = a1.out_zp = op.out_zp;
+        a0.clamp_min = a1.clamp_min = -128; a0.clamp_max = a1.clamp_max = 127;
+        a0.double_round = a1.double_round = op.double_round;
+        a0.out_row_stride = a1.out_row_stride = CO;
+        a0.out_col_offset = 0; a1.out_col_offset = C0;
+        Loc l0 = loc(op.in0), l1 = loc(op.in1), lo = loc(op.out0);
+        step.kernel_name = "concat_rescale";
+        step.launches = 2;
+        step.launch = [=](const ExecContext& c) {
+          RescaleArgs k0 = a0, k1 = a1;
+          k0.x = (const int8_t*)l0.resolve(c); k1.x = (const int8_t*)l1.resolve(c);
+          k0.out = k1.out = (int8_t*)lo.resolve(c);
+          k0.chan = (const ChanParams*)(c.consts + c0_off);
+          k1.chan = (const ChanParams*)(c.consts + c1_off);
+          launch_rescale(k0, c.stream);
+          launch_rescale(k1, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_RESIZE_NN2X: {
+        if (!b.act_i8(op.in0, 4) || !b.act_i8(op.out0, 4))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: resize wants int8 NHWC input/output", i);
+        const auto& x = tensors[op.in0]; const auto& o = tensors[op.out0];
+        int N = x.shape[0], H = x.shape[1], W = x.shape[2], C = x.shape[3];
+        if (o.shape[0] != N || o.shape[1] != 2 * H || o.shape[2] != 2 * W || o.shape[3] != C)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: resize output must be 2x the input frame", i);
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "resize_nn2x";
+        step.launch = [=](const ExecContext& c) {
+          launch_resize_nn2x((const int8_t*)lx.resolve(c), (int8_t*)lo.resolve(c), N, H, W, C, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_RESHAPE: {
+        if (bytes_of(op.in0) != bytes_of(op.out0) || tensors[op.in0].dtype != tensors[op.out0].dtype)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: reshape changes the byte count", i);
+        step.kernel_name = "view";
+        step.launches = 0;
+        step.launch = [](const ExecContext&) {};
+        break;
+      }
+      default:
+        return b.fail(TB200_UNIMPLEMENTED, "op %d: kind %u is not implemented", i, op.kind);
+    }
+    plan.launch_count += step.launches;
+    plan.steps.push_back(std::move(step));
+  }
+  return TB200_OK;
+}
+
+}  // namespace tb200

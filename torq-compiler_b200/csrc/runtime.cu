@@ -1,0 +1,544 @@
+// Execution engine behind the C ABI of include/torq_b200.h: device, buffers,
+// executable (parse + constant upload + launch plans + activation arena) and
+// stream-ordered dispatch. It plays the part of runtime/driver/TorqExecutable.cc
+// (initialize :655-752, executeDispatch :1025-1125) with the NPU action
+// interpreter replaced by a list of CUDA launches. There is no CPU fallback:
+// every failure surfaces as a status.
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/torq_b200.h"
+#include "../../include/torq_b200_ops.h"
+#include "kernels.h"
+#include "plan.h"
+
+using namespace tb200;
+
+struct tb200_device {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  std::string last_error;
+  std::mutex submit_mutex;  // one submission at a time, like the reference's
+                            // per-executable mutex (TorqExecutable.cc:1043-1045)
+  FILE* profile_csv = nullptr;
+  uint64_t invocation_id = 0;
+  std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
+};
+
+struct tb200_buffer {
+  tb200_device* dev = nullptr;
+  void* ptr = nullptr;
+  uint64_t bytes = 0;
+  int memory_type = 0;
+  bool owned = true;
+};
+
+namespace {
+
+int fail(tb200_device* dev, int status, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (dev) dev->last_error = buf;
+  return status;
+}
+
+#define CUDA_OK(dev, expr)                                                                   \
+  do {                                                                                       \
+    cudaError_t e_ = (expr);                                                                 \
+    if (e_ != cudaSuccess)                                                                   \
+      return fail(dev, e_ == cudaErrorMemoryAllocation ? TB200_RESOURCE_EXHAUSTED : TB200_INTERNAL, \
+                  "%s failed: %s", #expr, cudaGetErrorString(e_));                          \
+  } while (0)
+
+size_t dtype_size(uint32_t d) {
+  switch (d) {
+    case TB200_I8: return 1;
+    case TB200_I16: return 2;
+    case TB200_BF16: return 2;
+    case TB200_I32: return 4;
+    case TB200_F32: return 4;
+    case TB200_I64: return 8;
+    default: return 0;
+  }
+}
+
+uint64_t tensor_bytes(const tb200_tensor_t& t) {
+  uint64_t n = dtype_size(t.dtype);
+  for (uint32_t i = 0; i < 4; i++) n *= (uint64_t)(i < t.rank ? t.shape[i] : 1);
+  return n;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ status / device
+
+extern "C" const char* tb200_status_string(int s) {
+  static const char* names[] = {"OK", "CANCELLED", "UNKNOWN", "INVALID_ARGUMENT", "DEADLINE_EXCEEDED",
+                                "NOT_FOUND", "ALREADY_EXISTS", "PERMISSION_DENIED", "RESOURCE_EXHAUSTED",
+                                "FAILED_PRECONDITION", "ABORTED", "OUT_OF_RANGE", "UNIMPLEMENTED",
+                                "INTERNAL", "UNAVAILABLE", "DATA_LOSS"};
+  if (s < 0 || s > 15) return "?";
+  return names[s];
+}
+
+extern "C" int tb200_device_create(int ordinal, tb200_device_t** out) {
+  if (!out) return TB200_INVALID_ARGUMENT;
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) return TB200_UNAVAILABLE;  // no CPU fallback exists
+  if (ordinal < 0 || ordinal >= count) return TB200_NOT_FOUND;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, ordinal) != cudaSuccess) return TB200_INTERNAL;
+  if (prop.major != 10) return TB200_UNAVAILABLE;  // kernels are built for sm_100a only
+  if (cudaSetDevice(ordinal) != cudaSuccess) return TB200_INTERNAL;
+  auto* d = new tb200_device();
+  d->ordinal = ordinal;
+  if (cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking) != cudaSuccess) {
+    delete d;
+    return TB200_INTERNAL;
+  }
+  *out = d;
+  return TB200_OK;
+}
+
+extern "C" int tb200_device_destroy(tb200_device_t* d) {
+  if (!d) return TB200_INVALID_ARGUMENT;
+  cudaSetDevice(d->ordinal);
+  cudaStreamSynchronize(d->stream);
+  cudaStreamDestroy(d->stream);
+  if (d->profile_csv) fclose(d->profile_csv);
+  delete d;
+  return TB200_OK;
+}
+
+extern "C" int tb200_device_query_i64(tb200_device_t* d, const char* category, const char* key,
+                                      int64_t* out) {
+  if (!d || !category || !key || !out) return TB200_INVALID_ARGUMENT;
+  *out = 0;
+  if (!strcmp(category, "hal.executable.format")) {
+    *out = !strcmp(key, TB200_OPS_FORMAT_STRING) ? 1 : 0;
+    return TB200_OK;
+  }
+  if (!strcmp(category, "hal.device") || !strcmp(category, "hal.dispatch")) {
+    if (!strcmp(key, "concurrency")) {
+      *out = 1;
+      return TB200_OK;
+    }
+  }
+  return fail(d, TB200_NOT_FOUND, "unknown device configuration key value '%s :: %s'", category, key);
+}
+
+extern "C" const char* tb200_last_error(tb200_device_t* d) { return d ? d->last_error.c_str() : ""; }
+
+extern "C" int tb200_device_set_profile_csv(tb200_device_t* d, const char* path) {
+  if (!d) return TB200_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(d->submit_mutex);
+  if (d->profile_csv) {
+    fclose(d->profile_csv);
+    d->profile_csv = nullptr;
+  }
+  if (path && *path) {
+    d->profile_csv = fopen(path, "w");
+    if (!d->profile_csv) return fail(d, TB200_PERMISSION_DENIED, "cannot open %s", path);
+    fprintf(d->profile_csv, "dispatch_name,invocation_id,action_id,timestamp_us,event\n");
+  }
+  return TB200_OK;
+}
+
+// ------------------------------------------------------------------ buffers
+
+extern "C" int tb200_buffer_alloc(tb200_device_t* d, uint64_t bytes, int memory_type, tb200_buffer_t** out) {
+  if (!d || !out) return TB200_INVALID_ARGUMENT;
+  *out = nullptr;
+  cudaSetDevice(d->ordinal);
+  void* p = nullptr;
+  uint64_t n = bytes ? bytes : 16;
+  if (memory_type == TB200_MEMORY_DEVICE_LOCAL) {
+    CUDA_OK(d, cudaMalloc(&p, n));
+  } else if (memory_type == TB200_MEMORY_HOST_PINNED) {
+    CUDA_OK(d, cudaHostAlloc(&p, n, cudaHostAllocDefault));
+  } else {
+    return fail(d, TB200_INVALID_ARGUMENT, "unknown memory type %d", memory_type);
+  }
+  auto* b = new tb200_buffer();
+  b->dev = d;
+  b->ptr = p;
+  b->bytes = bytes;
+  b->memory_type = memory_type;
+  *out = b;
+  return TB200_OK;
+}
+
+extern "C" int tb200_buffer_import(tb200_device_t* d, void* device_pointer, uint64_t bytes,
+                                   tb200_buffer_t** out) {
+  if (!d || !out || !device_pointer) return TB200_INVALID_ARGUMENT;
+  auto* b = new tb200_buffer();
+  b->dev = d;
+  b->ptr = device_pointer;
+  b->bytes = bytes;
+  b->memory_type = TB200_MEMORY_DEVICE_LOCAL;
+  b->owned = false;
+  *out = b;
+  return TB200_OK;
+}
+
+extern "C" int tb200_buffer_free(tb200_buffer_t* b) {
+  if (!b) return TB200_INVALID_ARGUMENT;
+  if (b->owned) {
+    cudaSetDevice(b->dev->ordinal);
+    cudaStreamSynchronize(b->dev->stream);
+    if (b->memory_type == TB200_MEMORY_DEVICE_LOCAL) cudaFree(b->ptr);
+    else cudaFreeHost(b->ptr);
+  }
+  delete b;
+  return TB200_OK;
+}
+
+extern "C" int tb200_buffer_upload(tb200_buffer_t* b, uint64_t offset, const void* host, uint64_t bytes) {
+  if (!b || (!host && bytes)) return TB200_INVALID_ARGUMENT;
+  if (offset + bytes > b->bytes) return fail(b->dev, TB200_OUT_OF_RANGE, "upload beyond end of buffer");
+  cudaSetDevice(b->dev->ordinal);
+  CUDA_OK(b->dev, cudaMemcpyAsync((char*)b->ptr + offset, host, bytes, cudaMemcpyDefault, b->dev->stream));
+  return TB200_OK;
+}
+
+extern "C" int tb200_buffer_download(tb200_buffer_t* b, uint64_t offset, void* host, uint64_t bytes) {
+  if (!b || (!host && bytes)) return TB200_INVALID_ARGUMENT;
+  if (offset + bytes > b->bytes) return fail(b->dev, TB200_OUT_OF_RANGE, "download beyond end of buffer");
+  cudaSetDevice(b->dev->ordinal);
+  CUDA_OK(b->dev, cudaMemcpyAsync(host, (const char*)b->ptr + offset, bytes, cudaMemcpyDefault, b->dev->stream));
+  return TB200_OK;
+}
+
+extern "C" void* tb200_buffer_pointer(tb200_buffer_t* b) { return b ? b->ptr : nullptr; }
+extern "C" uint64_t tb200_buffer_size(tb200_buffer_t* b) { return b ? b->bytes : 0; }
+
+// ------------------------------------------------------------------ executable
+
+struct tb200_executable {
+  tb200_device* dev = nullptr;
+  std::vector<tb200_tensor_t> tensors;
+  std::vector<tb200_op_t> ops;
+  std::vector<int32_t> inputs, outputs;
+  std::vector<uint8_t> constants;  // host copy of the constants section
+  Plan plan;                       // launch list + arena layout (plan.h)
+  void* arena = nullptr;
+  void* const_dev = nullptr;       // derived constants (packed weights, channel params)
+  std::vector<tb200_buffer_t*> staging_in, staging_out;  // for tb200_invoke_host
+};
+
+extern "C" int tb200_executable_create(tb200_device_t* d, const void* bytes, size_t n_bytes,
+                                       tb200_executable_t** out) {
+  if (!d || !bytes || !out) return TB200_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (n_bytes < sizeof(tb200_ops_header_t)) return fail(d, TB200_INVALID_ARGUMENT, "blob shorter than its header");
+  tb200_ops_header_t h;
+  memcpy(&h, bytes, sizeof(h));
+  if (h.magic != TB200_OPS_MAGIC)
+    return fail(d, TB200_INVALID_ARGUMENT, "not a %s executable (bad magic)", TB200_OPS_FORMAT_STRING);
+  if (h.version != TB200_OPS_VERSION)
+    return fail(d, TB200_UNAVAILABLE, "executable version %u is not compatible with runtime version %u",
+                h.version, TB200_OPS_VERSION);
+  if (h.total_bytes > n_bytes) return fail(d, TB200_INVALID_ARGUMENT, "blob truncated: %llu > %zu",
+                                           (unsigned long long)h.total_bytes, n_bytes);
+  auto in_range = [&](uint64_t off, uint64_t len) { return off <= n_bytes && len <= n_bytes - off; };
+  if (!in_range(h.tensors_offset, (uint64_t)h.n_tensors * sizeof(tb200_tensor_t)) ||
+      !in_range(h.ops_offset, (uint64_t)h.n_ops * sizeof(tb200_op_t)) ||
+      !in_range(h.inputs_offset, (uint64_t)h.n_inputs * 4) ||
+      !in_range(h.outputs_offset, (uint64_t)h.n_outputs * 4) || !in_range(h.const_offset, h.const_bytes))
+    return fail(d, TB200_INVALID_ARGUMENT, "section outside the blob");
+
+  auto* ex = new tb200_executable();
+  ex->dev = d;
+  const char* base = (const char*)bytes;
+  ex->tensors.resize(h.n_tensors);
+  memcpy(ex->tensors.data(), base + h.tensors_offset, h.n_tensors * sizeof(tb200_tensor_t));
+  ex->ops.resize(h.n_ops);
+  memcpy(ex->ops.data(), base + h.ops_offset, h.n_ops * sizeof(tb200_op_t));
+  ex->inputs.resize(h.n_inputs);
+  memcpy(ex->inputs.data(), base + h.inputs_offset, h.n_inputs * 4);
+  ex->outputs.resize(h.n_outputs);
+  memcpy(ex->outputs.data(), base + h.outputs_offset, h.n_outputs * 4);
+  ex->constants.assign(base + h.const_offset, base + h.const_offset + h.const_bytes);
+
+  std::string err;
+  int st = TB200_OK;
+  for (size_t i = 0; i < ex->tensors.size() && st == TB200_OK; i++) {
+    const auto& t = ex->tensors[i];
+    if (t.rank < 1 || t.rank > 4 || dtype_size(t.dtype) == 0) st = fail(d, TB200_INVALID_ARGUMENT, "tensor %zu: bad rank/dtype", i);
+    for (uint32_t k = 0; k < t.rank && st == TB200_OK; k++)
+      if (t.shape[k] <= 0) st = fail(d, TB200_INVALID_ARGUMENT, "tensor %zu: non-positive extent", i);
+    if (st == TB200_OK && t.kind == TB200_TENSOR_CONSTANT &&
+        (t.const_offset > h.const_bytes || t.const_bytes > h.const_bytes - t.const_offset ||
+         t.const_bytes < tensor_bytes(t)))
+      st = fail(d, TB200_INVALID_ARGUMENT, "tensor %zu: constant outside the constants section", i);
+  }
+  for (int32_t id : ex->inputs)
+    if (st == TB200_OK && (id < 0 || id >= (int)h.n_tensors || ex->tensors[id].kind != TB200_TENSOR_INPUT))
+      st = fail(d, TB200_INVALID_ARGUMENT, "input list names tensor %d which is not an input", id);
+  for (int32_t id : ex->outputs)
+    if (st == TB200_OK && (id < 0 || id >= (int)h.n_tensors || ex->tensors[id].kind != TB200_TENSOR_OUTPUT))
+      st = fail(d, TB200_INVALID_ARGUMENT, "output list names tensor %d which is not an output", id);
+  if (st != TB200_OK) {
+    delete ex;
+    return st;
+  }
+
+  // io slot of a bound tensor = its position among inputs, then outputs
+  for (size_t i = 0; i < ex->inputs.size(); i++) ex->tensors[ex->inputs[i]].reserved = (uint32_t)i;
+  for (size_t i = 0; i < ex->outputs.size(); i++)
+    ex->tensors[ex->outputs[i]].reserved = (uint32_t)(ex->inputs.size() + i);
+  cudaSetDevice(d->ordinal);
+  st = build_plan(ex->tensors, ex->ops, ex->constants, ex->plan, err);
+  if (st != TB200_OK) {
+    fail(d, st, "%s", err.c_str());
+    delete ex;
+    return st;
+  }
+  // device memory: activation arena + derived constants, one allocation each
+  cudaError_t e = cudaSuccess;
+  if (ex->plan.arena_bytes) e = cudaMalloc(&ex->arena, ex->plan.arena_bytes);
+  if (e == cudaSuccess && !ex->plan.const_image.empty()) {
+    e = cudaMalloc(&ex->const_dev, ex->plan.const_image.size());
+    if (e == cudaSuccess)
+      e = cudaMemcpyAsync(ex->const_dev, ex->plan.const_image.data(), ex->plan.const_image.size(),
+                          cudaMemcpyHostToDevice, d->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
+  }
+  if (e == cudaSuccess && ex->plan.state_bytes) {
+    // persistent state tensors live at the front of the arena and start at zero
+    e = cudaMemsetAsync(ex->arena, 0, ex->plan.state_bytes, d->stream);
+  }
+  if (e != cudaSuccess) {
+    st = fail(d, e == cudaErrorMemoryAllocation ? TB200_RESOURCE_EXHAUSTED : TB200_INTERNAL,
+              "executable memory: %s", cudaGetErrorString(e));
+    if (ex->arena) cudaFree(ex->arena);
+    if (ex->const_dev) cudaFree(ex->const_dev);
+    delete ex;
+    return st;
+  }
+  *out = ex;
+  return TB200_OK;
+}
+
+extern "C" int tb200_executable_destroy(tb200_executable_t* ex) {
+  if (!ex) return TB200_INVALID_ARGUMENT;
+  cudaSetDevice(ex->dev->ordinal);
+  cudaStreamSynchronize(ex->dev->stream);
+  for (auto* b : ex->staging_in) tb200_buffer_free(b);
+  for (auto* b : ex->staging_out) tb200_buffer_free(b);
+  if (ex->arena) cudaFree(ex->arena);
+  if (ex->const_dev) cudaFree(ex->const_dev);
+  delete ex;
+  return TB200_OK;
+}
+
+extern "C" int tb200_executable_io_count(tb200_executable_t* ex, uint32_t* n_in, uint32_t* n_out) {
+  if (!ex) return TB200_INVALID_ARGUMENT;
+  if (n_in) *n_in = (uint32_t)ex->inputs.size();
+  if (n_out) *n_out = (uint32_t)ex->outputs.size();
+  return TB200_OK;
+}
+
+extern "C" int tb200_executable_io_info(tb200_executable_t* ex, int is_output, uint32_t index,
+                                        tb200_io_info_t* info) {
+  if (!ex || !info) return TB200_INVALID_ARGUMENT;
+  const auto& ids = is_output ? ex->outputs : ex->inputs;
+  if (index >= ids.size()) return fail(ex->dev, TB200_OUT_OF_RANGE, "io index %u out of range", index);
+  const auto& t = ex->tensors[ids[index]];
+  info->dtype = t.dtype;
+  info->rank = t.rank;
+  for (int i = 0; i < 4; i++) info->shape[i] = (uint32_t)i < t.rank ? t.shape[i] : 1;
+  info->bytes = tensor_bytes(t);
+  return TB200_OK;
+}
+
+extern "C" uint32_t tb200_executable_op_count(tb200_executable_t* ex) { return ex ? (uint32_t)ex->ops.size() : 0; }
+extern "C" uint32_t tb200_executable_launch_count(tb200_executable_t* ex) {
+  return ex ? (uint32_t)ex->plan.launch_count : 0;
+}
+extern "C" const char* tb200_executable_op_kernel(tb200_executable_t* ex, uint32_t index) {
+  if (!ex || index >= ex->plan.steps.size()) return "";
+  return ex->plan.steps[index].kernel_name;
+}
+
+namespace {
+
+// Resolve the binding list (inputs then outputs) to device addresses, with the
+// checks of torq_command_buffer.c:488-495 and TorqExecutable.cc:512-531.
+int resolve_bindings(tb200_executable* ex, const tb200_binding_t* bindings, size_t n, std::vector<void*>& io) {
+  tb200_device* d = ex->dev;
+  size_t want = ex->inputs.size() + ex->outputs.size();
+  if (n != want) return fail(d, TB200_INVALID_ARGUMENT, "expected %zu bindings, got %zu", want, n);
+  if (n && !bindings) return TB200_INVALID_ARGUMENT;
+  io.resize(n);
+  for (size_t i = 0; i < n; i++) {
+    const auto& b = bindings[i];
+    if (!b.buffer || !b.buffer->ptr) return fail(d, TB200_INVALID_ARGUMENT, "binding %zu is NULL", i);
+    int32_t tid = i < ex->inputs.size() ? ex->inputs[i] : ex->outputs[i - ex->inputs.size()];
+    uint64_t need = tensor_bytes(ex->tensors[tid]);
+    if (b.offset > b.buffer->bytes) return fail(d, TB200_OUT_OF_RANGE, "binding %zu offset beyond buffer", i);
+    uint64_t len = b.length ? b.length : b.buffer->bytes - b.offset;
+    if (len > b.buffer->bytes - b.offset || len < need)
+      return fail(d, TB200_OUT_OF_RANGE, "binding %zu: %llu bytes bound, tensor needs %llu", i,
+                  (unsigned long long)len, (unsigned long long)need);
+    if (b.offset & 15) return fail(d, TB200_INVALID_ARGUMENT, "binding %zu offset must be 16-byte aligned", i);
+    if (b.buffer->memory_type != TB200_MEMORY_DEVICE_LOCAL)
+      return fail(d, TB200_FAILED_PRECONDITION, "binding %zu is not device-local memory", i);
+    io[i] = (char*)b.buffer->ptr + b.offset;
+  }
+  return TB200_OK;
+}
+
+double now_us(tb200_device* d) {
+  return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - d->t0).count();
+}
+
+int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cudaEvent_t>* events) {
+  tb200_device* d = ex->dev;
+  ExecContext ctx;
+  ctx.arena = (char*)ex->arena;
+  ctx.consts = (char*)ex->const_dev;
+  ctx.io = io.data();
+  ctx.stream = d->stream;
+  for (size_t i = 0; i < ex->plan.steps.size(); i++) {
+    if (events) cudaEventRecord((*events)[i], d->stream);
+    ex->plan.steps[i].launch(ctx);
+  }
+  if (events) cudaEventRecord((*events)[ex->plan.steps.size()], d->stream);
+  CUDA_OK(d, cudaGetLastError());
+  return TB200_OK;
+}
+
+}  // namespace
+
+extern "C" int tb200_dispatch(tb200_executable_t* ex, const tb200_binding_t* bindings, size_t n) {
+  if (!ex) return TB200_INVALID_ARGUMENT;
+  tb200_device* d = ex->dev;
+  std::lock_guard<std::mutex> lock(d->submit_mutex);
+  cudaSetDevice(d->ordinal);
+  std::vector<void*> io;
+  int st = resolve_bindings(ex, bindings, n, io);
+  if (st != TB200_OK) return st;
+  if (!d->profile_csv) return run_plan(ex, io, nullptr);
+
+  // profiled dispatch: bracket every op with events and write the reference's CSV schema
+  size_t ns = ex->plan.steps.size();
+  std::vector<cudaEvent_t> ev(ns + 1);
+  for (auto& e : ev) cudaEventCreate(&e);
+  uint64_t inv = d->invocation_id++;
+  double t_begin = now_us(d);
+  fprintf(d->profile_csv, "dispatch,%llu,-1,%.3f,DISPATCH_BEGIN\n", (unsigned long long)inv, t_begin);
+  st = run_plan(ex, io, &ev);
+  if (st == TB200_OK) {
+    cudaStreamSynchronize(d->stream);
+    float acc_ms = 0.f;
+    for (size_t i = 0; i < ns; i++) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+      fprintf(d->profile_csv, "%s,%llu,%zu,%.3f,OP_BEGIN\n", ex->plan.steps[i].kernel_name,
+              (unsigned long long)inv, i, t_begin + acc_ms * 1e3);
+      acc_ms += ms;
+      fprintf(d->profile_csv, "%s,%llu,%zu,%.3f,OP_END\n", ex->plan.steps[i].kernel_name,
+              (unsigned long long)inv, i, t_begin + acc_ms * 1e3);
+    }
+    fprintf(d->profile_csv, "dispatch,%llu,-1,%.3f,DISPATCH_END\n", (unsigned long long)inv, now_us(d));
+    fflush(d->profile_csv);
+  }
+  for (auto& e : ev) cudaEventDestroy(e);
+  return st;
+}
+
+extern "C" int tb200_wait(tb200_device_t* d, uint64_t timeout_ns) {
+  if (!d) return TB200_INVALID_ARGUMENT;
+  cudaSetDevice(d->ordinal);
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::nanoseconds(timeout_ns);
+  for (;;) {
+    cudaError_t e = cudaStreamQuery(d->stream);
+    if (e == cudaSuccess) return TB200_OK;
+    if (e != cudaErrorNotReady) return fail(d, TB200_INTERNAL, "stream failed: %s", cudaGetErrorString(e));
+    if (std::chrono::steady_clock::now() >= deadline)
+      return fail(d, TB200_DEADLINE_EXCEEDED, "device did not finish within %llu ns", (unsigned long long)timeout_ns);
+  }
+}
+
+extern "C" int tb200_invoke_host(tb200_executable_t* ex, const void* const* host_inputs,
+                                 void* const* host_outputs) {
+  if (!ex || (!host_inputs && !ex->inputs.empty()) || (!host_outputs && !ex->outputs.empty()))
+    return TB200_INVALID_ARGUMENT;
+  tb200_device* d = ex->dev;
+  size_t ni = ex->inputs.size(), no = ex->outputs.size();
+  if (ex->staging_in.empty() && ex->staging_out.empty()) {
+    for (size_t i = 0; i < ni; i++) {
+      tb200_buffer_t* b = nullptr;
+      int st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->inputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
+      if (st != TB200_OK) return st;
+      ex->staging_in.push_back(b);
+    }
+    for (size_t i = 0; i < no; i++) {
+      tb200_buffer_t* b = nullptr;
+      int st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->outputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
+      if (st != TB200_OK) return st;
+      ex->staging_out.push_back(b);
+    }
+  }
+  std::vector<tb200_binding_t> bind(ni + no);
+  for (size_t i = 0; i < ni; i++) {
+    if (!host_inputs[i]) return fail(d, TB200_INVALID_ARGUMENT, "host input %zu is NULL", i);
+    int st = tb200_buffer_upload(ex->staging_in[i], 0, host_inputs[i], ex->staging_in[i]->bytes);
+    if (st != TB200_OK) return st;
+    bind[i] = {ex->staging_in[i], 0, 0};
+  }
+  for (size_t i = 0; i < no; i++) bind[ni + i] = {ex->staging_out[i], 0, 0};
+  int st = tb200_dispatch(ex, bind.data(), bind.size());
+  if (st != TB200_OK) return st;
+  for (size_t i = 0; i < no; i++) {
+    if (!host_outputs[i]) return fail(d, TB200_INVALID_ARGUMENT, "host output %zu is NULL", i);
+    st = tb200_buffer_download(ex->staging_out[i], 0, host_outputs[i], ex->staging_out[i]->bytes);
+    if (st != TB200_OK) return st;
+  }
+  CUDA_OK(d, cudaStreamSynchronize(d->stream));
+  return TB200_OK;
+}
+
+extern "C" int tb200_executable_profile_ops(tb200_executable_t* ex, const tb200_binding_t* bindings,
+                                            size_t n, int warmup, int iters, float* ms, uint32_t cap) {
+  if (!ex || !ms || iters <= 0) return TB200_INVALID_ARGUMENT;
+  tb200_device* d = ex->dev;
+  size_t ns = ex->plan.steps.size();
+  if (cap < ns) return fail(d, TB200_OUT_OF_RANGE, "ms array holds %u entries, executable has %zu ops", cap, ns);
+  std::lock_guard<std::mutex> lock(d->submit_mutex);
+  cudaSetDevice(d->ordinal);
+  std::vector<void*> io;
+  int st = resolve_bindings(ex, bindings, n, io);
+  if (st != TB200_OK) return st;
+  for (int i = 0; i < warmup; i++)
+    if ((st = run_plan(ex, io, nullptr)) != TB200_OK) return st;
+  std::vector<cudaEvent_t> ev(ns + 1);
+  for (auto& e : ev) cudaEventCreate(&e);
+  for (size_t i = 0; i < ns; i++) ms[i] = 0.f;
+  for (int it = 0; it < iters && st == TB200_OK; it++) {
+    st = run_plan(ex, io, &ev);
+    if (st != TB200_OK) break;
+    cudaStreamSynchronize(d->stream);
+    for (size_t i = 0; i < ns; i++) {
+      float t = 0.f;
+      cudaEventElapsedTime(&t, ev[i], ev[i + 1]);
+      ms[i] += t / iters;
+    }
+  }
+  for (auto& e : ev) cudaEventDestroy(e);
+  return st;
+}

@@ -1,0 +1,332 @@
+"""Builder and serializer of `torq-b200-ops` executables (include/torq_b200_ops.h).
+
+It stands where the reference's serializer stands
+(compiler/torq/Serialization/Serialization.cpp:265-306 writes the `torq-fb`
+flatbuffer per dispatch): one record per TorqHL-level op, constants in one blob.
+The Graph also keeps every op as a plain Python record (`Graph.ops`) so that a
+checker can replay the same graph through another engine.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+
+MAGIC = 0x4F323042
+VERSION = 1
+FORMAT_STRING = "torq-b200-ops"
+
+DTYPES = {"i8": 0, "i16": 1, "i32": 2, "f32": 3, "bf16": 4, "i64": 5}
+DTYPE_SIZE = {"i8": 1, "i16": 2, "i32": 4, "f32": 4, "bf16": 2, "i64": 8}
+NP_DTYPE = {"i8": np.int8, "i16": np.int16, "i32": np.int32, "f32": np.float32, "bf16": np.uint16, "i64": np.int64}
+
+ACTIVATION, INPUT, OUTPUT, CONSTANT, STATE = 0, 1, 2, 3, 4
+
+OP_KINDS = {
+    "conv2d": 1, "depthwise": 2, "fc": 3, "maxpool": 4, "avgpool": 5, "add": 6, "mul": 7, "table": 8,
+    "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
+    "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
+    "add_bf16": 38, "argmax": 39,
+}
+
+
+class Header(C.Structure):
+    _fields_ = [("magic", C.c_uint32), ("version", C.c_uint32), ("n_tensors", C.c_uint32), ("n_ops", C.c_uint32),
+                ("n_inputs", C.c_uint32), ("n_outputs", C.c_uint32), ("tensors_offset", C.c_uint64),
+                ("ops_offset", C.c_uint64), ("inputs_offset", C.c_uint64), ("outputs_offset", C.c_uint64),
+                ("const_offset", C.c_uint64), ("const_bytes", C.c_uint64), ("total_bytes", C.c_uint64)]
+
+
+class TensorRec(C.Structure):
+    _fields_ = [("dtype", C.c_uint32), ("kind", C.c_uint32), ("rank", C.c_uint32), ("shape", C.c_int32 * 4),
+                ("reserved", C.c_uint32), ("const_offset", C.c_uint64), ("const_bytes", C.c_uint64)]
+
+
+_OP_INT_FIELDS = ["in0", "in1", "in2", "out0", "out1", "weights", "bias", "multiplier", "shift", "table",
+                  "kh", "kw", "stride_h", "stride_w", "dil_h", "dil_w", "pad_t", "pad_b", "pad_l", "pad_r",
+                  "in0_zp", "in1_zp", "weight_zp", "out_zp", "clamp_min", "clamp_max", "per_channel",
+                  "double_round", "requant_mode", "in0_mult", "in0_shift", "in1_mult", "in1_shift", "out_mult",
+                  "out_shift", "pad_value", "i0", "i1", "i2", "i3"]
+
+
+class OpRec(C.Structure):
+    _fields_ = ([("kind", C.c_uint32), ("flags", C.c_uint32)] + [(n, C.c_int32) for n in _OP_INT_FIELDS] +
+                [("f0", C.c_float), ("f1", C.c_float), ("f2", C.c_float), ("f3", C.c_float)])
+
+
+assert C.sizeof(Header) == 80 and C.sizeof(TensorRec) == 48 and C.sizeof(OpRec) == 184
+
+
+@dataclass
+class TensorRef:
+    id: int
+    shape: tuple
+    dtype: str
+    kind: int
+    data: Any = None  # numpy array for constants
+
+    @property
+    def nbytes(self) -> int:
+        return int(np.prod(self.shape)) * DTYPE_SIZE[self.dtype]
+
+
+@dataclass
+class Op:
+    kind: str
+    inputs: list
+    outputs: list
+    consts: dict = field(default_factory=dict)   # name -> TensorRef
+    attrs: dict = field(default_factory=dict)    # C field name -> int/float
+
+
+def _out_dim(i, k, s, d, p0, p1):
+    return (i + p0 + p1 - d * (k - 1) - 1) // s + 1
+
+
+class Graph:
+    """A dispatch: tensors, ops in execution order, inputs and outputs."""
+
+    def __init__(self):
+        self.tensors: list[TensorRef] = []
+        self.ops: list[Op] = []
+        self.inputs: list[TensorRef] = []
+        self.outputs: list[TensorRef] = []
+
+    # ---- tensors -------------------------------------------------------
+    def _tensor(self, shape, dtype, kind, data=None) -> TensorRef:
+        shape = tuple(int(s) for s in shape)
+        if not 1 <= len(shape) <= 4:
+            raise ValueError(f"rank {len(shape)} not supported")
+        t = TensorRef(len(self.tensors), shape, dtype, kind, data)
+        self.tensors.append(t)
+        return t
+
+    def input(self, shape, dtype="i8") -> TensorRef:
+        t = self._tensor(shape, dtype, INPUT)
+        self.inputs.append(t)
+        return t
+
+    def state(self, shape, dtype) -> TensorRef:
+        return self._tensor(shape, dtype, STATE)
+
+    def const(self, array, dtype=None) -> TensorRef:
+        a = np.ascontiguousarray(array)
+        if dtype is None:
+            dtype = {np.dtype(np.int8): "i8", np.dtype(np.int32): "i32", np.dtype(np.float32): "f32",
+                     np.dtype(np.int16): "i16", np.dtype(np.uint16): "bf16", np.dtype(np.int64): "i64"}[a.dtype]
+        a = a.astype(NP_DTYPE[dtype], copy=False)
+        shape = a.shape if a.ndim else (1,)
+        return self._tensor(shape, dtype, CONSTANT, a.reshape(shape))
+
+    def output(self, t: TensorRef) -> TensorRef:
+        if t.kind != ACTIVATION:
+            raise ValueError("only an op result can be made an output")
+        t.kind = OUTPUT
+        self.outputs.append(t)
+        return t
+
+    def _emit(self, kind, inputs, out_shape, out_dtype="i8", consts=None, **attrs) -> TensorRef:
+        out = self._tensor(out_shape, out_dtype, ACTIVATION)
+        self.ops.append(Op(kind, list(inputs), [out], dict(consts or {}), attrs))
+        return out
+
+    # ---- requant helper --------------------------------------------------
+    def _requant_consts(self, multiplier, shift, oc):
+        m = np.atleast_1d(np.asarray(multiplier)).astype(np.int32)
+        s = np.atleast_1d(np.asarray(shift)).astype(np.int8)
+        if m.shape != s.shape or m.size not in (1, oc):
+            raise ValueError("multiplier/shift must have 1 or OC entries")
+        return self.const(m, "i32"), self.const(s, "i8"), int(m.size > 1)
+
+    # ---- int8 layer ops ----------------------------------------------------
+    def conv2d(self, x, weights, bias, multiplier, shift, *, stride=(1, 1), dilation=(1, 1), pad=(0, 0, 0, 0),
+               input_zp=0, weight_zp=0, out_zp=0, clamp=(-128, 127), double_round=True, requant_mode=0):
+        """torq_hl.conv2d: x NHWC int8, weights OHWI int8, pad = (top, bottom, left, right)."""
+        w = np.asarray(weights, np.int8)
+        N, H, W, IC = x.shape
+        OC, KH, KW, IC2 = w.shape
+        if IC != IC2:
+            raise ValueError("weight IC mismatch")
+        OH = _out_dim(H, KH, stride[0], dilation[0], pad[0], pad[1])
+        OW = _out_dim(W, KW, stride[1], dilation[1], pad[2], pad[3])
+        mt, st, pc = self._requant_consts(multiplier, shift, OC)
+        consts = {"weights": self.const(w), "bias": self.const(np.atleast_1d(bias).astype(np.int32)),
+                  "multiplier": mt, "shift": st}
+        return self._emit("conv2d", [x], (N, OH, OW, OC), consts=consts, kh=KH, kw=KW, stride_h=stride[0],
+                          stride_w=stride[1], dil_h=dilation[0], dil_w=dilation[1], pad_t=pad[0], pad_b=pad[1],
+                          pad_l=pad[2], pad_r=pad[3], in0_zp=input_zp, weight_zp=weight_zp, out_zp=out_zp,
+                          clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc, double_round=int(double_round),
+                          requant_mode=requant_mode)
+
+    def depthwise_conv2d(self, x, weights, bias, multiplier, shift, *, stride=(1, 1), dilation=(1, 1),
+                         pad=(0, 0, 0, 0), input_zp=0, weight_zp=0, out_zp=0, clamp=(-128, 127),
+                         double_round=True, requant_mode=0):
+        """torq_hl.depthwise_conv2d: weights [KH, KW, C, M]."""
+        w = np.asarray(weights, np.int8)
+        N, H, W, Cc = x.shape
+        KH, KW, C2, M = w.shape
+        if Cc != C2:
+            raise ValueError("weight C mismatch")
+        OH = _out_dim(H, KH, stride[0], dilation[0], pad[0], pad[1])
+        OW = _out_dim(W, KW, stride[1], dilation[1], pad[2], pad[3])
+        mt, st, pc = self._requant_consts(multiplier, shift, Cc * M)
+        consts = {"weights": self.const(w), "bias": self.const(np.atleast_1d(bias).astype(np.int32)),
+                  "multiplier": mt, "shift": st}
+        return self._emit("depthwise", [x], (N, OH, OW, Cc * M), consts=consts, kh=KH, kw=KW, stride_h=stride[0],
+                          stride_w=stride[1], dil_h=dilation[0], dil_w=dilation[1], pad_t=pad[0], pad_b=pad[1],
+                          pad_l=pad[2], pad_r=pad[3], in0_zp=input_zp, weight_zp=weight_zp, out_zp=out_zp,
+                          clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc, double_round=int(double_round),
+                          requant_mode=requant_mode)
+
+    def fully_connected(self, x, weights, bias, multiplier, shift, *, input_zp=0, weight_zp=0, out_zp=0,
+                        clamp=(-128, 127), double_round=True, requant_mode=0):
+        """torq_hl.fully_connected: x [M, K], weights [N, K] ("[O, I]")."""
+        w = np.asarray(weights, np.int8)
+        M, K = x.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise ValueError("weight K mismatch")
+        mt, st, pc = self._requant_consts(multiplier, shift, N)
+        consts = {"weights": self.const(w), "bias": self.const(np.atleast_1d(bias).astype(np.int32)),
+                  "multiplier": mt, "shift": st}
+        return self._emit("fc", [x], (M, N), consts=consts, in0_zp=input_zp, weight_zp=weight_zp, out_zp=out_zp,
+                          clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc, double_round=int(double_round),
+                          requant_mode=requant_mode)
+
+    def matmul_i32(self, a, b, *, a_zp=0, b_zp=0):
+        """raw torq_hl.matmul: a [M, K] int8, constant b [K, N] int8 -> int32."""
+        bw = np.asarray(b, np.int8)
+        return self._emit("matmul_i32", [a], (a.shape[0], bw.shape[1]), "i32", consts={"weights": self.const(bw)},
+                          in0_zp=a_zp, weight_zp=b_zp)
+
+    def maxpool2d(self, x, kernel, stride, pad=(0, 0, 0, 0), pad_value=-128):
+        N, H, W, Cc = x.shape
+        OH = _out_dim(H, kernel[0], stride[0], 1, pad[0], pad[1])
+        OW = _out_dim(W, kernel[1], stride[1], 1, pad[2], pad[3])
+        return self._emit("maxpool", [x], (N, OH, OW, Cc), kh=kernel[0], kw=kernel[1], stride_h=stride[0],
+                          stride_w=stride[1], pad_t=pad[0], pad_b=pad[1], pad_l=pad[2], pad_r=pad[3],
+                          pad_value=pad_value)
+
+    def avg_pool2d(self, x, kernel, stride, pad=(0, 0, 0, 0), input_zp=0, output_zp=0):
+        N, H, W, Cc = x.shape
+        OH = _out_dim(H, kernel[0], stride[0], 1, pad[0], pad[1])
+        OW = _out_dim(W, kernel[1], stride[1], 1, pad[2], pad[3])
+        return self._emit("avgpool", [x], (N, OH, OW, Cc), kh=kernel[0], kw=kernel[1], stride_h=stride[0],
+                          stride_w=stride[1], pad_t=pad[0], pad_b=pad[1], pad_l=pad[2], pad_r=pad[3],
+                          in0_zp=input_zp, out_zp=output_zp)
+
+    def _binary(self, kind, a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round):
+        if a.shape != b.shape:
+            raise ValueError("elementwise operands must have equal shapes")
+        return self._emit(kind, [a, b], a.shape, in0_zp=a_zp, in0_mult=a_ms[0], in0_shift=a_ms[1], in1_zp=b_zp,
+                          in1_mult=b_ms[0], in1_shift=b_ms[1], out_mult=out_ms[0], out_shift=out_ms[1],
+                          out_zp=out_zp, clamp_min=clamp[0], clamp_max=clamp[1], double_round=int(double_round))
+
+    def add(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True):
+        """torq_hl.add in TOSA form; *_ms = (multiplier, shift)."""
+        return self._binary("add", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round)
+
+    def sub(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True):
+        return self._binary("sub", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round)
+
+    def mul(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True):
+        return self._binary("mul", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round)
+
+    def table(self, x, table):
+        t = np.asarray(table, np.int8)
+        if t.size != 256:
+            raise ValueError("table must have 256 entries")
+        return self._emit("table", [x], x.shape, consts={"table": self.const(t)})
+
+    def rescale(self, x, multiplier, shift, *, input_zp=0, out_zp=0, clamp=(-128, 127), double_round=True,
+                requant_mode=0):
+        mt, st, pc = self._requant_consts(multiplier, shift, x.shape[-1])
+        return self._emit("rescale", [x], x.shape, consts={"multiplier": mt, "shift": st}, in0_zp=input_zp,
+                          out_zp=out_zp, clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc,
+                          double_round=int(double_round), requant_mode=requant_mode)
+
+    def resize_nearest_2x(self, x):
+        N, H, W, Cc = x.shape
+        return self._emit("resize_nn2x", [x], (N, 2 * H, 2 * W, Cc))
+
+    def concat(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_zp, double_round=True):
+        """channel concat with an i8->i8 rescale on each input."""
+        if a.shape[:-1] != b.shape[:-1]:
+            raise ValueError("concat operands differ outside the channel axis")
+        return self._emit("concat", [a, b], a.shape[:-1] + (a.shape[-1] + b.shape[-1],), in0_zp=a_zp,
+                          in0_mult=a_ms[0], in0_shift=a_ms[1], in1_zp=b_zp, in1_mult=b_ms[0], in1_shift=b_ms[1],
+                          out_zp=out_zp, double_round=int(double_round))
+
+    def reshape(self, x, shape):
+        """tosa.reshape: the result is a view of the same bytes (no kernel runs)."""
+        if int(np.prod(shape)) != int(np.prod(x.shape)):
+            raise ValueError("reshape changes the element count")
+        return self._emit("reshape", [x], shape, x.dtype)
+
+    # ---- serialisation ------------------------------------------------------
+    def serialize(self) -> bytes:
+        const_blob = bytearray()
+        trecs = []
+        for t in self.tensors:
+            r = TensorRec()
+            r.dtype, r.kind, r.rank = DTYPES[t.dtype], t.kind, len(t.shape)
+            for i in range(4):
+                r.shape[i] = t.shape[i] if i < len(t.shape) else 1
+            if t.kind == CONSTANT:
+                pad = (-len(const_blob)) % 16
+                const_blob.extend(b"\0" * pad)
+                raw = t.data.tobytes()
+                r.const_offset, r.const_bytes = len(const_blob), len(raw)
+                const_blob.extend(raw)
+            trecs.append(bytes(r))
+        orecs = []
+        for op in self.ops:
+            r = OpRec()
+            r.kind = OP_KINDS[op.kind]
+            for n in _OP_INT_FIELDS[:10]:
+                setattr(r, n, -1)
+            for i, t in enumerate(op.inputs):
+                setattr(r, f"in{i}", t.id)
+            for i, t in enumerate(op.outputs):
+                setattr(r, f"out{i}", t.id)
+            for name, t in op.consts.items():
+                setattr(r, name, t.id)
+            r.dil_h = r.dil_w = r.stride_h = r.stride_w = 1
+            r.clamp_min, r.clamp_max, r.out_shift, r.in0_shift, r.in1_shift = -128, 127, 2, 2, 2
+            for k, v in op.attrs.items():
+                setattr(r, k, v)
+            orecs.append(bytes(r))
+
+        def align(n):
+            return (n + 15) & ~15
+
+        h = Header()
+        h.magic, h.version = MAGIC, VERSION
+        h.n_tensors, h.n_ops, h.n_inputs, h.n_outputs = len(trecs), len(orecs), len(self.inputs), len(self.outputs)
+        off = align(C.sizeof(Header))
+        h.tensors_offset = off
+        off = align(off + len(trecs) * C.sizeof(TensorRec))
+        h.ops_offset = off
+        off = align(off + len(orecs) * C.sizeof(OpRec))
+        h.inputs_offset = off
+        off = align(off + 4 * len(self.inputs))
+        h.outputs_offset = off
+        off = align(off + 4 * len(self.outputs))
+        h.const_offset, h.const_bytes = off, len(const_blob)
+        h.total_bytes = off + len(const_blob)
+        out = bytearray(h.total_bytes)
+        out[0:C.sizeof(Header)] = bytes(h)
+        p = h.tensors_offset
+        for b in trecs:
+            out[p:p + len(b)] = b
+            p += len(b)
+        p = h.ops_offset
+        for b in orecs:
+            out[p:p + len(b)] = b
+            p += len(b)
+        out[h.inputs_offset:h.inputs_offset + 4 * len(self.inputs)] = np.array([t.id for t in self.inputs], np.int32).tobytes()
+        out[h.outputs_offset:h.outputs_offset + 4 * len(self.outputs)] = np.array([t.id for t in self.outputs], np.int32).tobytes()
+        out[h.const_offset:h.const_offset + len(const_blob)] = const_blob
+        return bytes(out)
