@@ -69,6 +69,10 @@ int tb200_device_destroy(tb200_device_t* device);
  * ("hal.dispatch","concurrency") -> 1; anything else NOT_FOUND. */
 int tb200_device_query_i64(tb200_device_t* device, const char* category, const char* key,
                            int64_t* out_value);
+/* The cudaStream_t every transfer and dispatch of this device is queued on, so a
+ * caller can record its own events on it or order other work after it (role of the
+ * HAL semaphore a queue_execute signals, runtime/driver/torq_device.c:487-526). */
+void* tb200_device_stream(tb200_device_t* device);
 /* Text of the most recent failure on this device (thread-unsafe convenience). */
 const char* tb200_last_error(tb200_device_t* device);
 const char* tb200_status_string(int status);

@@ -1,0 +1,211 @@
+"""Per-op parity of the CUDA path against the CPU oracle, bit-exact, through the C ABI.
+Cases mirror the attribute combinations of the reference's TOSA fixtures
+(tests/testdata/tosa_ops, tests/testdata/gen_ops) and its seeded input generator
+(python/torq/testing/iree.py:1262-1285: seed 1234)."""
+import numpy as np
+import pytest
+
+from gpu_exec import run_graph_gpu
+from oracle_exec import run_graph
+from torq_b200.oplist import Graph
+from torq_b200.quant import quantize_multiplier, quantize_multipliers
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(device, g, inputs, host_call=False):
+    want = run_graph(g, inputs)
+    got = run_graph_gpu(device, g, inputs, host_call=host_call)
+    for w, o in zip(want, got):
+        assert w.shape == o.shape
+        bad = np.flatnonzero(w.ravel() != o.ravel())
+        assert bad.size == 0, f"{bad.size} of {w.size} differ; first at {bad[:5]}: want {w.ravel()[bad[:5]]} got {o.ravel()[bad[:5]]}"
+        assert len(np.unique(w)) > 2 or w.size < 8
+    return got
+
+
+CONV_CASES = [
+    # x shape, OC, kernel, stride, dilation, pad(t,b,l,r), izp, wzp
+    ((1, 8, 8, 1), 1, (3, 3), (1, 1), (1, 1), (1, 1, 1, 1), -128, 0),       # gen_ops/conv2d_8x8.mlir
+    ((1, 15, 17, 3), 8, (5, 5), (2, 2), (1, 1), (2, 2, 2, 2), 3, 0),        # conv_5x5_odd_frame_stride2 class
+    ((2, 9, 11, 5), 7, (3, 3), (2, 1), (1, 1), (1, 1, 0, 1), -3, 0),
+    ((1, 13, 13, 4), 6, (5, 5), (2, 2), (1, 1), (2, 2, 2, 2), 7, 3),        # weight zero point
+    ((1, 10, 12, 8), 16, (3, 3), (1, 1), (2, 2), (2, 2, 2, 2), 0, 0),       # dilation
+    ((3, 6, 6, 16), 24, (1, 1), (1, 1), (1, 1), (0, 0, 0, 0), -5, 0),       # 1x1 = matmul as conv
+    ((1, 56, 56, 64), 64, (3, 3), (1, 1), (1, 1), (1, 1, 1, 1), -3, 0),     # single-conv benchmark config
+    ((2, 14, 14, 96), 576, (1, 1), (1, 1), (1, 1), (0, 0, 0, 0), 9, 0),
+    ((1, 224, 224, 3), 32, (3, 3), (2, 2), (1, 1), (0, 1, 0, 1), -4, 0),    # MobileNetV2 stem
+    ((1, 7, 7, 100), 130, (1, 1), (1, 1), (1, 1), (0, 0, 0, 0), 2, -1),
+]
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv2d(device, case, mode):
+    shape, OC, k, stride, dil, pad, izp, wzp = case
+    rng = np.random.default_rng(1234)
+    x = rng.integers(-128, 128, shape, dtype=np.int8)
+    w = rng.integers(-127, 128, (OC,) + k + (shape[3],), dtype=np.int8)
+    bias = np.round(rng.normal(0, 2000, OC)).astype(np.int32)
+    K = k[0] * k[1] * shape[3]
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, OC) * 40.0 / (np.sqrt(K) * 74 * 74))
+    g = Graph()
+    y = g.conv2d(g.input(shape), w, bias, m, s, stride=stride, dilation=dil, pad=pad, input_zp=izp, weight_zp=wzp,
+                 out_zp=5, clamp=(-128, 127), requant_mode=mode)
+    g.output(y)
+    _check(device, g, [x])
+
+
+def test_conv2d_per_tensor_scale_and_relu6_clamp(device):
+    rng = np.random.default_rng(1234)
+    x = rng.integers(-128, 128, (1, 8, 8, 1), dtype=np.int8)
+    w = np.array([[[[119], [23], [-114]], [[115], [-127], [125]], [[7], [-35], [-13]]]], np.int8)  # conv2d_8x8.mlir
+    g = Graph()
+    y = g.conv2d(g.input(x.shape), w, np.zeros(1, np.int32), [2003370132], [39], pad=(1, 1, 1, 1), input_zp=-128,
+                 out_zp=-128, clamp=(-128, 127))
+    g.output(y)
+    _check(device, g, [x])
+    g = Graph()
+    y = g.conv2d(g.input(x.shape), w, np.array([77], np.int32), [2003370132], [37], pad=(1, 1, 1, 1), input_zp=-128,
+                 out_zp=-10, clamp=(-10, 90))
+    g.output(y)
+    _check(device, g, [x])
+
+
+DW_CASES = [
+    ((1, 56, 56, 11), (5, 5), 1, (1, 1), (2, 2, 2, 2), -128),   # tosa_ops/dw_peeling.mlir shape
+    ((2, 9, 8, 8), (3, 3), 1, (2, 2), (0, 1, 0, 1), 4),
+    ((1, 7, 7, 3), (3, 3), 2, (1, 1), (1, 1, 1, 1), -1),
+    ((1, 12, 12, 4), (4, 4), 1, (2, 2), (1, 1, 1, 1), 0),       # dw_4x4_stride2 class
+    ((1, 23, 23, 16), (21, 21), 1, (2, 2), (10, 10, 10, 10), 6),  # dw_21x21_odd_frame_stride2 class
+    ((2, 28, 28, 192), (3, 3), 1, (1, 1), (1, 1, 1, 1), -7),
+    ((2, 28, 28, 144), (3, 3), 1, (2, 2), (0, 1, 0, 1), 10),
+]
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("case", DW_CASES)
+def test_depthwise(device, case, mode):
+    shape, k, M, stride, pad, izp = case
+    rng = np.random.default_rng(1234)
+    x = rng.integers(-128, 128, shape, dtype=np.int8)
+    w = rng.integers(-127, 128, k + (shape[3], M), dtype=np.int8)
+    OC = shape[3] * M
+    bias = np.round(rng.normal(0, 1000, OC)).astype(np.int32)
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, OC) * 40.0 / (np.sqrt(k[0] * k[1]) * 74 * 74))
+    g = Graph()
+    y = g.depthwise_conv2d(g.input(shape), w, bias, m, s, stride=stride, pad=pad, input_zp=izp, out_zp=28,
+                           requant_mode=mode)
+    g.output(y)
+    _check(device, g, [x])
+
+
+@pytest.mark.parametrize("M,K,N,azp", [(1, 512, 512, 0), (64, 512, 512, -7), (512, 1024, 1024, 0), (5, 40, 9, -7),
+                                       (33, 100, 130, 3), (256, 1280, 1000, -2)])
+def test_fully_connected(device, M, K, N, azp):
+    rng = np.random.default_rng(1234)
+    a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    bias = np.round(rng.normal(0, 1000, N)).astype(np.int32)
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, N) * 40.0 / (np.sqrt(K) * 74 * 74))
+    g = Graph()
+    y = g.fully_connected(g.input((M, K)), w, bias, m, s, input_zp=azp, out_zp=-3)
+    g.output(y)
+    _check(device, g, [a])
+
+
+def test_matmul_int32(device):
+    rng = np.random.default_rng(1234)
+    a = rng.integers(-128, 128, (17, 70), dtype=np.int8)
+    b = rng.integers(-128, 128, (70, 13), dtype=np.int8)
+    g = Graph()
+    g.output(g.matmul_i32(g.input(a.shape), b, a_zp=-7, b_zp=2))
+    _check(device, g, [a])
+
+
+@pytest.mark.parametrize("shape,kernel,stride,pad", [
+    ((2, 112, 112, 64), (3, 3), (2, 2), (0, 1, 0, 1)),   # maxpool2d-stride2-k3x3-pad-112x112x64.mlir
+    ((1, 20, 20, 48), (5, 5), (1, 1), (2, 2, 2, 2)),     # SPPF window
+    ((2, 11, 12, 6), (2, 2), (2, 2), (0, 0, 0, 0)),
+    ((1, 7, 7, 128), (7, 7), (1, 1), (0, 0, 0, 0)),      # avgpool2d.mlir (global)
+])
+def test_pools(device, shape, kernel, stride, pad):
+    rng = np.random.default_rng(1234)
+    x = rng.integers(-128, 128, shape, dtype=np.int8)
+    g = Graph()
+    g.output(g.maxpool2d(g.input(shape), kernel, stride, pad, pad_value=-100))
+    _check(device, g, [x])
+    g = Graph()
+    g.output(g.avg_pool2d(g.input(shape), kernel, stride, pad, input_zp=4, output_zp=-3))
+    _check(device, g, [x])
+
+
+@pytest.mark.parametrize("shape", [(1, 56, 56, 24), (3, 7, 5, 3), (2, 28, 28, 32)])
+def test_add_sub_mul(device, shape):
+    rng = np.random.default_rng(1234)
+    a = rng.integers(-128, 128, shape, dtype=np.int8)
+    b = rng.integers(-128, 128, shape, dtype=np.int8)
+    for kind in ("add", "sub"):
+        g = Graph()
+        fn = getattr(g, kind)
+        # constants of tests/testdata/tosa_ops/add-single-rescale.mlir: shift 49 takes the double-round branch
+        g.output(fn(g.input(shape), g.input(shape), a_zp=-3, a_ms=(1 << 30, 11), b_zp=5, b_ms=(1 << 30, 11),
+                    out_ms=(1093202297, 49), out_zp=-2))
+        _check(device, g, [a, b])
+    g = Graph()
+    g.output(g.mul(g.input(shape), g.input(shape), a_zp=3, a_ms=(1 << 30, 30), b_zp=-4, b_ms=(1 << 30, 30),
+                   out_ms=quantize_multiplier(1.0 / 150), out_zp=1, clamp=(-100, 100)))
+    _check(device, g, [a, b])
+
+
+def test_table_rescale_resize_concat(device):
+    rng = np.random.default_rng(1234)
+    shape = (2, 13, 9, 20)
+    x = rng.integers(-128, 128, shape, dtype=np.int8)
+    # sigmoid table from seeded scales
+    s_in, zp_in, s_out, zp_out = 0.05, -3, 1.0 / 256, -128
+    idx = np.arange(-128, 128)
+    tbl = np.clip(np.round(1.0 / (1.0 + np.exp(-s_in * (idx - zp_in))) / s_out) + zp_out, -128, 127).astype(np.int8)
+    g = Graph()
+    g.output(g.table(g.input(shape), tbl))
+    _check(device, g, [x])
+
+    m, s = quantize_multipliers(rng.uniform(0.3, 1.9, 20))
+    g = Graph()
+    g.output(g.rescale(g.input(shape), m, s, input_zp=5, out_zp=3))
+    _check(device, g, [x])
+    g = Graph()
+    g.output(g.rescale(g.input(shape), [1518500250], [30], input_zp=-7, out_zp=0, clamp=(-50, 50)))
+    _check(device, g, [x])
+
+    g = Graph()
+    g.output(g.resize_nearest_2x(g.input(shape)))
+    _check(device, g, [x])
+
+    z = rng.integers(-128, 128, (2, 13, 9, 12), dtype=np.int8)
+    g = Graph()
+    g.output(g.concat(g.input(shape), g.input(z.shape), a_zp=3, a_ms=(1500000000, 31), b_zp=-5,
+                      b_ms=(1200000000, 30), out_zp=7))
+    _check(device, g, [x, z])
+
+
+def test_chain_with_intermediates_and_host_call(device):
+    """conv -> depthwise -> conv + residual add: exercises the arena and tb200_invoke_host."""
+    rng = np.random.default_rng(1234)
+    shape = (2, 14, 14, 16)
+    x = rng.integers(-128, 128, shape, dtype=np.int8)
+    g = Graph()
+    xin = g.input(shape)
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, 96) * 40.0 / (4 * 74 * 74))
+    h = g.conv2d(xin, rng.integers(-127, 128, (96, 1, 1, 16), dtype=np.int8), np.zeros(96, np.int32), m, s,
+                 input_zp=2, out_zp=-128, clamp=(-128, 127))
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, 96) * 40.0 / (3 * 74 * 74))
+    h = g.depthwise_conv2d(h, rng.integers(-127, 128, (3, 3, 96, 1), dtype=np.int8), np.zeros(96, np.int32), m, s,
+                           pad=(1, 1, 1, 1), input_zp=-128, out_zp=-128)
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, 16) * 40.0 / (10 * 74 * 74))
+    h = g.conv2d(h, rng.integers(-127, 128, (16, 1, 1, 96), dtype=np.int8), np.zeros(16, np.int32), m, s,
+                 input_zp=-128, out_zp=4)
+    y = g.add(xin, h, a_zp=2, a_ms=(1 << 30, 11), b_zp=4, b_ms=(1 << 30, 11), out_ms=(1093202297, 49), out_zp=-2)
+    g.output(y)
+    _check(device, g, [x])
+    _check(device, g, [x], host_call=True)

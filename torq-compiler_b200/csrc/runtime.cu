@@ -140,6 +140,8 @@ extern "C" int tb200_device_query_i64(tb200_device_t* d, const char* category, c
   return fail(d, TB200_NOT_FOUND, "unknown device configuration key value '%s :: %s'", category, key);
 }
 
+extern "C" void* tb200_device_stream(tb200_device_t* d) { return d ? (void*)d->stream : nullptr; }
+
 extern "C" const char* tb200_last_error(tb200_device_t* d) { return d ? d->last_error.c_str() : ""; }
 
 extern "C" int tb200_device_set_profile_csv(tb200_device_t* d, const char* path) {

@@ -50,6 +50,7 @@ _SIGNATURES = {
     "tb200_device_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
     "tb200_device_destroy": (C.c_int, [C.c_void_p]),
     "tb200_device_query_i64": (C.c_int, [C.c_void_p, C.c_char_p, C.c_char_p, C.POINTER(C.c_int64)]),
+    "tb200_device_stream": (C.c_void_p, [C.c_void_p]),
     "tb200_last_error": (C.c_char_p, [C.c_void_p]),
     "tb200_status_string": (C.c_char_p, [C.c_int]),
     "tb200_device_set_profile_csv": (C.c_int, [C.c_void_p, C.c_char_p]),
@@ -109,6 +110,11 @@ class Device:
     def _check(self, st: int):
         if st != OK:
             raise TorqB200Error(st, (self._lib.tb200_last_error(self._h) or b"").decode())
+
+    @property
+    def stream(self) -> int:
+        """cudaStream_t handle of the device's stream (for event timing / interop)."""
+        return self._lib.tb200_device_stream(self._h) or 0
 
     def query_i64(self, category: str, key: str) -> int:
         v = C.c_int64()
