@@ -70,6 +70,26 @@ struct RescaleArgs {
 };
 void launch_rescale(const RescaleArgs& a, cudaStream_t stream);
 
+// ---- tensor-core GEMM (gemm_tcgen05.cu) ----
+struct GemmTcArgs {
+  const int8_t* a;        // [M, K] int8, row pitch lda bytes (multiple of 16)
+  long long lda;
+  const int8_t* w;        // packed [n_tiles * BN][Kpad], Kpad a multiple of 128, zero padded
+  const ChanParams* chan; // [n_tiles * BN]
+  int8_t* out;            // [M, N] int8, row pitch ldc bytes
+  long long ldc;
+  long long M;
+  int N, K, Kpad, BN, n_tiles;
+  int out_zp, clamp_min, clamp_max, double_round;
+  int* status;            // device status word: a kernel whose bounded wait expires writes a code here
+};
+struct GemmTcState;       // cached tensor maps of one GEMM step
+GemmTcState* gemm_tc_state_new();
+void gemm_tc_state_free(GemmTcState* s);
+void gemm_tc_tiling(int N, int& BN, int& n_tiles);
+bool gemm_tc_supported(long long M, int N, int K, long long lda);
+cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t stream);
+
 void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream);
 
 }  // namespace tb200

@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 
 #include "../../include/torq_b200.h"
 #include "kernels.h"
@@ -147,7 +148,6 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
                const std::vector<uint8_t>& constants, Plan& plan, std::string& err) {
   Builder b{tensors, ops, constants, plan, err};
   const int nt = (int)tensors.size();
-  (void)force_simt;
 
   // ---- tensor placement: io slots, state prefix, liveness-packed activations ----
   plan.tensor_loc.assign(nt, Loc{});
@@ -269,11 +269,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         const long long K = (long long)KH * KW * IC;
         const int8_t* w = b.const_data<int8_t>(op.weights, (size_t)OC * K, "weights", i);
         if (!w) return b.status;
-        const int Kpad = (int)((K + 31) / 32 * 32);
-        std::vector<int8_t> packed((size_t)OC * Kpad, 0);
+        if (op.in0_zp < -128 || op.in0_zp > 127) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input_zp outside int8", i);
         std::vector<int32_t> wsum(OC, 0);
         for (int oc = 0; oc < OC; oc++) {
-          memcpy(packed.data() + (size_t)oc * Kpad, w + (size_t)oc * K, (size_t)K);
           int32_t s = 0;
           for (long long k = 0; k < K; k++) s += w[(size_t)oc * K + k];
           wsum[oc] = s;
@@ -281,6 +279,41 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         std::vector<ChanParams> cp;
         int dr = 0;
         if (!b.chan_params(op, i, OC, wsum.data(), K, true, cp, dr)) return b.status;
+
+        // 1x1 / fully_connected with symmetric weights: row-major GEMM on the tensor cores
+        const bool pointwise = fc || (KH == 1 && KW == 1 && op.stride_h == 1 && op.stride_w == 1 && op.pad_t == 0 &&
+                                      op.pad_b == 0 && op.pad_l == 0 && op.pad_r == 0);
+        const long long M = (long long)N * OH * OW;
+        if (pointwise && op.weight_zp == 0 && !force_simt() && gemm_tc_supported(M, OC, (int)K, K)) {
+          GemmTcArgs ga{};
+          gemm_tc_tiling(OC, ga.BN, ga.n_tiles);
+          ga.M = M; ga.N = OC; ga.K = (int)K; ga.Kpad = (int)((K + 127) / 128 * 128);
+          ga.lda = K; ga.ldc = OC;
+          ga.out_zp = op.out_zp; ga.clamp_min = op.clamp_min; ga.clamp_max = op.clamp_max; ga.double_round = dr;
+          const int rows = ga.n_tiles * ga.BN;
+          std::vector<int8_t> wp((size_t)rows * ga.Kpad, 0);
+          for (int oc = 0; oc < OC; oc++) memcpy(wp.data() + (size_t)oc * ga.Kpad, w + (size_t)oc * K, (size_t)K);
+          cp.resize(rows, ChanParams{0, 0, 2, 0});
+          size_t w_off = b.add_const(wp.data(), wp.size());
+          size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+          Loc lx = loc(op.in0), lo = loc(op.out0);
+          std::shared_ptr<GemmTcState> st(gemm_tc_state_new(), gemm_tc_state_free);
+          step.kernel_name = "gemm_i8_tcgen05";
+          step.launch = [=](const ExecContext& c) {
+            GemmTcArgs k = ga;
+            k.a = (const int8_t*)lx.resolve(c);
+            k.out = (int8_t*)lo.resolve(c);
+            k.w = (const int8_t*)(c.consts + w_off);
+            k.chan = (const ChanParams*)(c.consts + c_off);
+            k.status = c.status;
+            launch_gemm_i8_tc(k, st.get(), c.stream);
+          };
+          break;
+        }
+
+        const int Kpad = (int)((K + 31) / 32 * 32);
+        std::vector<int8_t> packed((size_t)OC * Kpad, 0);
+        for (int oc = 0; oc < OC; oc++) memcpy(packed.data() + (size_t)oc * Kpad, w + (size_t)oc * K, (size_t)K);
         ConvArgs a{};
         a.N = N; a.H = H; a.W = W; a.IC = IC; a.OC = OC; a.KH = KH; a.KW = KW; a.OH = OH; a.OW = OW;
         a.stride_h = fc ? 1 : op.stride_h; a.stride_w = fc ? 1 : op.stride_w;
@@ -289,7 +322,6 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         a.K = (int)K; a.Kpad = Kpad;
         a.input_zp = op.in0_zp; a.weight_zp = op.weight_zp; a.out_zp = op.out_zp;
         a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max; a.double_round = dr;
-        if (op.in0_zp < -128 || op.in0_zp > 127) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input_zp outside int8", i);
         size_t w_off = b.add_const(packed.data(), packed.size());
         size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
         Loc lx = loc(op.in0), lo = loc(op.out0);

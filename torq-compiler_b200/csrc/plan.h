@@ -20,6 +20,7 @@ struct ExecContext {
   char* consts;
   void* const* io;  // inputs then outputs
   cudaStream_t stream;
+  int* status;      // device status word (0 = fine)
 };
 
 // Where a tensor lives at dispatch time.

@@ -30,6 +30,7 @@ struct tb200_device {
                             // per-executable mutex (TorqExecutable.cc:1043-1045)
   FILE* profile_csv = nullptr;
   uint64_t invocation_id = 0;
+  int* status_word = nullptr;  // device word a kernel writes when one of its bounded waits expires
   std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
 };
 
@@ -109,6 +110,11 @@ extern "C" int tb200_device_create(int ordinal, tb200_device_t** out) {
     delete d;
     return TB200_INTERNAL;
   }
+  if (cudaMalloc(&d->status_word, sizeof(int)) != cudaSuccess || cudaMemset(d->status_word, 0, sizeof(int)) != cudaSuccess) {
+    cudaStreamDestroy(d->stream);
+    delete d;
+    return TB200_RESOURCE_EXHAUSTED;
+  }
   *out = d;
   return TB200_OK;
 }
@@ -118,6 +124,7 @@ extern "C" int tb200_device_destroy(tb200_device_t* d) {
   cudaSetDevice(d->ordinal);
   cudaStreamSynchronize(d->stream);
   cudaStreamDestroy(d->stream);
+  cudaFree(d->status_word);
   if (d->profile_csv) fclose(d->profile_csv);
   delete d;
   return TB200_OK;
@@ -415,6 +422,7 @@ int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cud
   ctx.consts = (char*)ex->const_dev;
   ctx.io = io.data();
   ctx.stream = d->stream;
+  ctx.status = d->status_word;
   for (size_t i = 0; i < ex->plan.steps.size(); i++) {
     if (events) cudaEventRecord((*events)[i], d->stream);
     ex->plan.steps[i].launch(ctx);
@@ -469,7 +477,17 @@ extern "C" int tb200_wait(tb200_device_t* d, uint64_t timeout_ns) {
   auto deadline = std::chrono::steady_clock::now() + std::chrono::nanoseconds(timeout_ns);
   for (;;) {
     cudaError_t e = cudaStreamQuery(d->stream);
-    if (e == cudaSuccess) return TB200_OK;
+    if (e == cudaSuccess) {
+      // the stream drained: did a kernel give up on one of its bounded waits?
+      int code = 0;
+      if (cudaMemcpy(&code, d->status_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return fail(d, TB200_INTERNAL, "cannot read the device status word");
+      if (code != 0) {
+        cudaMemset(d->status_word, 0, sizeof(int));
+        return fail(d, TB200_ABORTED, "a kernel's bounded wait expired (code %d); results of this dispatch are invalid", code);
+      }
+      return TB200_OK;
+    }
     if (e != cudaErrorNotReady) return fail(d, TB200_INTERNAL, "stream failed: %s", cudaGetErrorString(e));
     if (std::chrono::steady_clock::now() >= deadline)
       return fail(d, TB200_DEADLINE_EXCEEDED, "device did not finish within %llu ns", (unsigned long long)timeout_ns);
