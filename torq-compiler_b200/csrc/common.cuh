@@ -5,15 +5,22 @@
 
 namespace tb200 {
 
-// Per-output-channel epilogue constants, one 16-byte load per channel.
+// Per-output-channel epilogue constants (32 bytes, two 16-byte loads).
 // bias already holds every input-zero-point correction that can be folded
 // (bias - izp * sum(w) [+ K * izp * wzp]); mult/shift are the tosa.rescale pair
 // (requant mode A) or the common-shift pair derived from it (mode B).
+// rnd and dmul pre-compute the rounding of apply_scale_32 so that the epilogue is
+//   t = acc * mult + rnd + [acc < 0] * dmul ;  r = t >> shift
+// with rnd = 2^(S-1) (+ 2^30 when DOUBLE_ROUND applies, i.e. S > 31) and
+// dmul = -2^31 in that case (so a negative acc sees 2^30 - 2^31 = -2^30), else 0.
 struct __align__(16) ChanParams {
   int32_t bias;
   int32_t mult;
   int32_t shift;
-  int32_t wsum;  // sum over K of raw weights (used by kernels that correct per border)
+  int32_t dmul;
+  long long rnd;
+  int32_t wsum;    // sum over K of raw weights (for kernels that correct per border class)
+  int32_t hshift;  // shift - 32 (meaningful when every shift of the op is >= 32)
 };
 
 // TOSA apply_scale_32. The reference matches the chain
@@ -29,6 +36,18 @@ __device__ __forceinline__ int32_t apply_scale_32(int32_t v, int32_t mult, int32
 __device__ __forceinline__ int32_t requant(int32_t acc, int32_t mult, int32_t shift, bool dround,
                                            int32_t ozp, int32_t cmin, int32_t cmax) {
   int32_t r = apply_scale_32(acc, mult, shift, dround) + ozp;  // int32 wraps on device
+  return max(cmin, min(cmax, r));
+}
+
+// Same result as requant() with the constants of ChanParams; HI = every shift of the op is >= 32,
+// which turns the 64-bit shift into one shift of the high word.
+template <bool HI>
+__device__ __forceinline__ int32_t requant_cp(int32_t acc, const ChanParams& cp, int32_t ozp, int32_t cmin,
+                                              int32_t cmax) {
+  long long t = (long long)acc * (long long)cp.mult + cp.rnd;
+  t += (long long)(int32_t)((uint32_t)acc >> 31) * (long long)cp.dmul;
+  int32_t r = HI ? ((int32_t)(t >> 32) >> cp.hshift) : (int32_t)(t >> cp.shift);
+  r += ozp;
   return max(cmin, min(cmax, r));
 }
 

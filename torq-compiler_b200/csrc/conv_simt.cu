@@ -146,9 +146,9 @@ __global__ void __launch_bounds__(256) conv2d_simt_kernel(ConvArgs a) {
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     if (oc0 + j < a.OC) cp[j] = a.chan[oc0 + j];
-    else cp[j] = ChanParams{0, 0, 2, 0};
+    else cp[j] = ChanParams{};
   }
-  const bool dr = a.double_round != 0;
+  const bool hi = a.hi_shift != 0;
   const bool vec_ok = ((a.OC & 3) == 0) && (oc0 + 3 < a.OC);
 #pragma unroll
   for (int i = 0; i < 4; i++) {
@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(256) conv2d_simt_kernel(ConvArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       int v = acc[i][j] - a.weight_zp * xsum[i] + cp[j].bias;
-      q[j] = requant(v, cp[j].mult, cp[j].shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
+      q[j] = hi ? requant_cp<true>(v, cp[j], a.out_zp, a.clamp_min, a.clamp_max)
+                : requant_cp<false>(v, cp[j], a.out_zp, a.clamp_min, a.clamp_max);
     }
     int8_t* o = a.out + (size_t)p * a.OC + oc0;
     if (vec_ok) {
@@ -171,68 +172,70 @@ __global__ void __launch_bounds__(256) conv2d_simt_kernel(ConvArgs a) {
   }
 }
 
-// Depthwise: one thread per (output pixel, VEC consecutive channels).
-// torq_hl.depthwise_conv2d (Conv2DPattern.cpp:627-637), weights [KH,KW,C,M].
-// Taps outside the image are skipped (they would contribute (izp - izp) * w).
-template <int VEC>
-__global__ void __launch_bounds__(256) depthwise_kernel(DwArgs a) {
-  const int OC = a.C * a.M;
-  const int groups = (VEC == 4) ? (a.C >> 2) : OC;
-  const long long total = (long long)a.N * a.OH * a.OW * groups;
-  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total) return;
-  int g = (int)(idx % groups);
-  long long p = idx / groups;
-  int ow = (int)(p % a.OW);
+// Few input channels (IC <= 4, K = KH*KW*IC <= 64), e.g. the 3x3x3 stem of an image
+// network: one thread per output pixel gathers its K patch bytes into KWORDS registers
+// once and runs every output channel against weights broadcast from shared memory.
+// Same arithmetic as conv2d_simt_kernel (izp staged for taps outside the image).
+template <int KWORDS>
+__global__ void __launch_bounds__(128) conv2d_smallic_kernel(ConvArgs a) {
+  extern __shared__ uint32_t w_s[];  // [OC][KWORDS]
+  for (int i = threadIdx.x; i < a.OC * KWORDS; i += blockDim.x) {
+    const int oc = i / KWORDS, kw = i - oc * KWORDS;
+    w_s[i] = (kw * 4 < a.Kpad) ? *reinterpret_cast<const uint32_t*>(a.w + (size_t)oc * a.Kpad + kw * 4) : 0u;
+  }
+  __syncthreads();
+  const long long P = (long long)a.N * a.OH * a.OW;
+  const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= P) return;
+  const int ow = (int)(p % a.OW);
   long long t = p / a.OW;
-  int oh = (int)(t % a.OH);
-  int n = (int)(t / a.OH);
-  const int ih0 = oh * a.stride_h - a.pad_t;
-  const int iw0 = ow * a.stride_w - a.pad_l;
-  const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.C;
-  const bool dr = a.double_round != 0;
+  const int oh = (int)(t % a.OH);
+  const int n = (int)(t / a.OH);
+  const int ih0 = oh * a.stride_h - a.pad_t, iw0 = ow * a.stride_w - a.pad_l;
+  const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.IC;
+  const uint32_t zp_byte = (uint32_t)(a.input_zp & 0xff);
 
-  if (VEC == 4) {
-    const int c = g * 4;
-    int acc[4] = {0, 0, 0, 0};
-    for (int kh = 0; kh < a.KH; kh++) {
-      int ih = ih0 + kh * a.dil_h;
-      if (ih < 0 || ih >= a.H) continue;
-      for (int kw = 0; kw < a.KW; kw++) {
-        int iw = iw0 + kw * a.dil_w;
-        if (iw < 0 || iw >= a.W) continue;
-        uint32_t xv = *reinterpret_cast<const uint32_t*>(xin + ((size_t)ih * a.W + iw) * a.C + c);
-        uint32_t wv = *reinterpret_cast<const uint32_t*>(a.w + ((size_t)kh * a.KW + kw) * a.C + c);
+  uint32_t patch[KWORDS];
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[j] += (sx8(xv, j) - a.input_zp) * (sx8(wv, j) - a.weight_zp);
+  for (int i = 0; i < KWORDS; i++) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+      const int k = 4 * i + b;
+      if (k < a.K) {
+        const int tap = k / a.IC, ic = k - tap * a.IC;
+        const int kh = tap / a.KW, kw = tap - kh * a.KW;
+        const int ih = ih0 + kh * a.dil_h, iw = iw0 + kw * a.dil_w;
+        const uint32_t byte = (ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
+                                  ? (uint32_t)(uint8_t)xin[((size_t)ih * a.W + iw) * a.IC + ic]
+                                  : zp_byte;
+        word |= byte << (8 * b);
       }
     }
+    patch[i] = word;
+  }
+  const bool hi = a.hi_shift != 0;
+  int8_t* o = a.out + (size_t)p * a.OC;
+  for (int oc0 = 0; oc0 < a.OC; oc0 += 4) {
     int q[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-      ChanParams cp = a.chan[c + j];
-      q[j] = requant(acc[j] + cp.bias, cp.mult, cp.shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
+      const int oc = min(oc0 + j, a.OC - 1);
+      int acc = 0;
+#pragma unroll
+      for (int i = 0; i < KWORDS; i++) acc = __dp4a((int)patch[i], (int)w_s[oc * KWORDS + i], acc);
+      const ChanParams cp = a.chan[oc];
+      acc += cp.bias;
+      q[j] = hi ? requant_cp<true>(acc, cp, a.out_zp, a.clamp_min, a.clamp_max)
+                : requant_cp<false>(acc, cp, a.out_zp, a.clamp_min, a.clamp_max);
     }
-    *reinterpret_cast<uint32_t*>(a.out + (size_t)p * OC + c) = pack4(q[0], q[1], q[2], q[3]);
-  } else {
-    const int oc = g;
-    const int c = oc / a.M;
-    const int m = oc - c * a.M;
-    int acc = 0;
-    for (int kh = 0; kh < a.KH; kh++) {
-      int ih = ih0 + kh * a.dil_h;
-      if (ih < 0 || ih >= a.H) continue;
-      for (int kw = 0; kw < a.KW; kw++) {
-        int iw = iw0 + kw * a.dil_w;
-        if (iw < 0 || iw >= a.W) continue;
-        int xv = xin[((size_t)ih * a.W + iw) * a.C + c];
-        int wv = a.w[(((size_t)kh * a.KW + kw) * a.C + c) * a.M + m];
-        acc += (xv - a.input_zp) * (wv - a.weight_zp);
-      }
+    if ((a.OC & 3) == 0) {
+      *reinterpret_cast<uint32_t*>(o + oc0) = pack4(q[0], q[1], q[2], q[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (oc0 + j < a.OC) o[oc0 + j] = (int8_t)q[j];
     }
-    ChanParams cp = a.chan[oc];
-    a.out[(size_t)p * OC + oc] =
-        (int8_t)requant(acc + cp.bias, cp.mult, cp.shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
   }
 }
 
@@ -252,23 +255,26 @@ __global__ void __launch_bounds__(256) matmul_i32_kernel(const int8_t* __restric
 
 }  // namespace
 
+const char* conv2d_simt_kernel_name(const ConvArgs& a) {
+  return (a.IC <= 4 && a.K <= 64 && a.OC <= 256 && a.weight_zp == 0) ? "conv2d_smallic_dp4a" : "conv2d_simt";
+}
+
 void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
   long long P = (long long)a.N * a.OH * a.OW;
+  if (a.IC <= 4 && a.K <= 64 && a.OC <= 256 && a.weight_zp == 0) {
+    const unsigned blocks = (unsigned)((P + 127) / 128);
+    const int kwords = (a.K + 3) / 4;
+    if (kwords <= 3) conv2d_smallic_kernel<3><<<blocks, 128, (size_t)a.OC * 3 * 4, stream>>>(a);
+    else if (kwords <= 7) conv2d_smallic_kernel<7><<<blocks, 128, (size_t)a.OC * 7 * 4, stream>>>(a);
+    else if (kwords <= 9) conv2d_smallic_kernel<9><<<blocks, 128, (size_t)a.OC * 9 * 4, stream>>>(a);
+    else conv2d_smallic_kernel<16><<<blocks, 128, (size_t)a.OC * 16 * 4, stream>>>(a);
+    return;
+  }
   dim3 grid((unsigned)((P + BM - 1) / BM), (unsigned)((a.OC + BN - 1) / BN));
   if ((a.IC & 3) == 0)
     conv2d_simt_kernel<true><<<grid, 256, 0, stream>>>(a);
   else
     conv2d_simt_kernel<false><<<grid, 256, 0, stream>>>(a);
-}
-
-void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
-  if (a.M == 1 && (a.C & 3) == 0) {
-    long long total = (long long)a.N * a.OH * a.OW * (a.C >> 2);
-    depthwise_kernel<4><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
-  } else {
-    long long total = (long long)a.N * a.OH * a.OW * a.C * a.M;
-    depthwise_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
-  }
 }
 
 void launch_matmul_i32(const int8_t* a, const int8_t* b, int32_t* out, int M, int K, int N, int a_zp,

@@ -40,7 +40,7 @@ struct GemmTcParams {
   int8_t* out;
   long long ldc;
   int M, N, BN, n_tiles, m_tiles, k_blocks, k_last_steps;
-  int out_zp, clamp_min, clamp_max, double_round;
+  int out_zp, clamp_min, clamp_max, hi_shift;
   int acc_stride, tmem_cols;
   int* status;
 };
@@ -227,7 +227,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int nchunks = p.BN >> 4;
     const int c_begin = half == 0 ? 0 : (nchunks + 1) / 2;
     const int c_end = half == 0 ? (nchunks + 1) / 2 : nchunks;
-    const bool dr = p.double_round != 0;
+    const bool hi = p.hi_shift != 0;
     const bool vec_ok = (p.ldc & 15) == 0;
     int loaded_n = -1;
     int it = 0;
@@ -258,7 +258,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             const ChanParams cp = cp_s[c * 16 + g * 4 + j];
-            qv[j] = requant((int)v[g * 4 + j] + cp.bias, cp.mult, cp.shift, dr, p.out_zp, p.clamp_min, p.clamp_max);
+            const int acc = (int)v[g * 4 + j] + cp.bias;
+            qv[j] = hi ? requant_cp<true>(acc, cp, p.out_zp, p.clamp_min, p.clamp_max)
+                       : requant_cp<false>(acc, cp, p.out_zp, p.clamp_min, p.clamp_max);
           }
           w4[g] = pack4(qv[0], qv[1], qv[2], qv[3]);
         }
@@ -378,7 +380,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   p.out_zp = a.out_zp;
   p.clamp_min = a.clamp_min;
   p.clamp_max = a.clamp_max;
-  p.double_round = a.double_round;
+  p.hi_shift = a.hi_shift;
   int stride = 32;
   while (stride < a.BN) stride <<= 1;
   p.acc_stride = stride;

@@ -18,8 +18,10 @@ struct ConvArgs {
   int K, Kpad;            // KH*KW*IC and its padded row length
   int input_zp, weight_zp, out_zp, clamp_min, clamp_max;
   int double_round;
+  int hi_shift;           // every rescale shift of the op is >= 32
 };
 void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream);
+const char* conv2d_simt_kernel_name(const ConvArgs& a);  // which CUDA-core kernel the launcher picks
 
 struct DwArgs {
   const int8_t* x;        // NHWC
@@ -30,8 +32,15 @@ struct DwArgs {
   int stride_h, stride_w, dil_h, dil_w, pad_t, pad_l;
   int input_zp, weight_zp, out_zp, clamp_min, clamp_max;
   int double_round;
+  int hi_shift;           // every rescale shift of the op is >= 32
+  const uint32_t* wq;     // 3x3 fast path: weights packed per row for dp4a (see depthwise.cu), else null
 };
 void launch_depthwise(const DwArgs& a, cudaStream_t stream);
+// 3x3, M == 1, C % 4 == 0, no dilation, stride 1 or 2, symmetric weights: the dp4a kernel applies;
+// its ChanParams::bias must have the input zero point folded (bias - izp * sum of the 9 taps).
+bool depthwise3x3_supported(const DwArgs& a);
+// Packs [3][3][C] weights into [3 rows][variants][C] words; returns the word count written.
+size_t depthwise3x3_pack(const int8_t* w, int C, int stride, uint32_t* out);
 
 // raw int8 x int8 -> int32 matmul, b is [K][N]
 void launch_matmul_i32(const int8_t* a, const int8_t* b, int32_t* out, int M, int K, int N, int a_zp,
@@ -81,6 +90,7 @@ struct GemmTcArgs {
   long long M;
   int N, K, Kpad, BN, n_tiles;
   int out_zp, clamp_min, clamp_max, double_round;
+  int hi_shift;           // every rescale shift of the op is >= 32
   int* status;            // device status word: a kernel whose bounded wait expires writes a code here
 };
 struct GemmTcState;       // cached tensor maps of one GEMM step

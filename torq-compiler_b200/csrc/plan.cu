@@ -4,7 +4,9 @@
 #include "plan.h"
 
 #include <algorithm>
+#include <climits>
 #include <cstdarg>
+#include <cstdint>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -111,9 +113,10 @@ struct Builder {
       return false;
     }
     out.resize(OC);
+    last_hi_shift = true;
     for (int c = 0; c < OC; c++) {
       int i = op.per_channel ? c : 0;
-      ChanParams p;
+      ChanParams p{};
       uint32_t b = bias ? (uint32_t)bias[bias_len == 1 ? 0 : c] : 0u;
       p.wsum = wsum ? wsum[c] : 0;
       if (fold_zp && wsum) {
@@ -129,9 +132,21 @@ struct Builder {
         p.mult = mult[i];
         p.shift = shift[i];
       }
+      fill_rounding(p, double_round != 0);
+      if (p.shift < 32) last_hi_shift = false;
       out[c] = p;
     }
     return true;
+  }
+
+  // set by chan_params: every shift of the op is >= 32 (the epilogue's one-word shift applies)
+  bool last_hi_shift = true;
+
+  static void fill_rounding(ChanParams& p, bool double_round) {
+    const bool second = double_round && p.shift > 31;
+    p.rnd = (1ll << (p.shift - 1)) + (second ? (1ll << 30) : 0ll);
+    p.dmul = second ? INT32_MIN : 0;
+    p.hshift = p.shift - 32;
   }
 };
 
@@ -290,10 +305,11 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           ga.M = M; ga.N = OC; ga.K = (int)K; ga.Kpad = (int)((K + 127) / 128 * 128);
           ga.lda = K; ga.ldc = OC;
           ga.out_zp = op.out_zp; ga.clamp_min = op.clamp_min; ga.clamp_max = op.clamp_max; ga.double_round = dr;
+          ga.hi_shift = b.last_hi_shift;
           const int rows = ga.n_tiles * ga.BN;
           std::vector<int8_t> wp((size_t)rows * ga.Kpad, 0);
           for (int oc = 0; oc < OC; oc++) memcpy(wp.data() + (size_t)oc * ga.Kpad, w + (size_t)oc * K, (size_t)K);
-          cp.resize(rows, ChanParams{0, 0, 2, 0});
+          { ChanParams z{}; z.shift = 34; z.hshift = 2; z.rnd = 1ll << 33; cp.resize(rows, z); }
           size_t w_off = b.add_const(wp.data(), wp.size());
           size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
           Loc lx = loc(op.in0), lo = loc(op.out0);
@@ -321,11 +337,11 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         a.pad_t = fc ? 0 : op.pad_t; a.pad_l = fc ? 0 : op.pad_l;
         a.K = (int)K; a.Kpad = Kpad;
         a.input_zp = op.in0_zp; a.weight_zp = op.weight_zp; a.out_zp = op.out_zp;
-        a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max; a.double_round = dr;
+        a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max; a.double_round = dr; a.hi_shift = b.last_hi_shift;
         size_t w_off = b.add_const(packed.data(), packed.size());
         size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
         Loc lx = loc(op.in0), lo = loc(op.out0);
-        step.kernel_name = "conv2d_simt";
+        step.kernel_name = conv2d_simt_kernel_name(a);
         step.launch = [=](const ExecContext& c) {
           ConvArgs k = a;
           k.x = (const int8_t*)lx.resolve(c);
@@ -354,23 +370,40 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: depthwise output shape mismatch", i);
         const int8_t* wd = b.const_data<int8_t>(op.weights, (size_t)a.KH * a.KW * OC, "weights", i);
         if (!wd) return b.status;
-        std::vector<ChanParams> cp;
-        int dr = 0;
-        if (!b.chan_params(op, i, OC, nullptr, 0, false, cp, dr)) return b.status;
         a.stride_h = op.stride_h; a.stride_w = op.stride_w; a.dil_h = op.dil_h; a.dil_w = op.dil_w;
         a.pad_t = op.pad_t; a.pad_l = op.pad_l;
         a.input_zp = op.in0_zp; a.weight_zp = op.weight_zp; a.out_zp = op.out_zp;
-        a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max; a.double_round = dr;
+        a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
+        if (op.in0_zp < -128 || op.in0_zp > 127) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input_zp outside int8", i);
+        // the 3x3 dp4a kernel stages izp for taps outside the image and wants -izp * sum(w) in the bias
+        const bool fast = depthwise3x3_supported(a) && !force_simt();
+        std::vector<int32_t> wsum;
+        if (fast) {
+          wsum.assign(OC, 0);
+          for (int t = 0; t < 9; t++)
+            for (int ch = 0; ch < OC; ch++) wsum[ch] += wd[(size_t)t * OC + ch];
+        }
+        std::vector<ChanParams> cp;
+        int dr = 0;
+        if (!b.chan_params(op, i, OC, fast ? wsum.data() : nullptr, 9, fast, cp, dr)) return b.status;
+        a.double_round = dr; a.hi_shift = b.last_hi_shift;
         size_t w_off = b.add_const(wd, (size_t)a.KH * a.KW * OC);
         size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+        size_t q_off = 0;
+        if (fast) {
+          std::vector<uint32_t> wq((size_t)3 * 2 * OC);
+          size_t nw = depthwise3x3_pack(wd, OC, op.stride_h, wq.data());
+          q_off = b.add_const(wq.data(), nw * sizeof(uint32_t));
+        }
         Loc lx = loc(op.in0), lo = loc(op.out0);
-        step.kernel_name = "depthwise";
+        step.kernel_name = fast ? "depthwise3x3_dp4a" : "depthwise";
         step.launch = [=](const ExecContext& c) {
           DwArgs k = a;
           k.x = (const int8_t*)lx.resolve(c);
           k.out = (int8_t*)lo.resolve(c);
           k.w = (const int8_t*)(c.consts + w_off);
           k.chan = (const ChanParams*)(c.consts + c_off);
+          k.wq = fast ? (const uint32_t*)(c.consts + q_off) : nullptr;
           launch_depthwise(k, c.stream);
         };
         break;
@@ -504,7 +537,10 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: concat (channel axis) shape mismatch", i);
         for (int s : {op.in0_shift, op.in1_shift})
           if (s < 2 || s > 62) return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale shift %d outside [2,62]", i, s);
-        ChanParams p0{0, op.in0_mult, op.in0_shift, 0}, p1{0, op.in1_mult, op.in1_shift, 0};
+        ChanParams p0{}, p1{};
+        p0.mult = op.in0_mult; p0.shift = op.in0_shift; p1.mult = op.in1_mult; p1.shift = op.in1_shift;
+        Builder::fill_rounding(p0, op.double_round != 0);
+        Builder::fill_rounding(p1, op.double_round != 0);
         size_t c0_off = b.add_const(&p0, sizeof(p0));
         size_t c1_off = b.add_const(&p1, sizeof(p1));
         RescaleArgs a0{}, a1{};
