@@ -135,6 +135,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer-table", default=None, help="write per-layer kernel, ms and GB/s to this CSV")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -226,17 +227,23 @@ def main():
     # ops and layer table line up except for the reshape view
     per_kernel = {}
     li = 0
+    table = ["layer,kernel,ms,algorithmic_MB,GBps,GMACps"]
     for k, ms in zip(kernels, op_ms):
         if k == "view":
             continue
         layer = real_layers[li]
         li += 1
         alg_bytes = (layer["in_bytes"] + layer["out_bytes"]) * B + layer["weight_bytes"]
+        table.append(f"{layer['name']},{k},{ms:.4f},{alg_bytes / 1e6:.2f},{alg_bytes / (ms * 1e-3) / 1e9:.0f},"
+                     f"{layer['macs'] * B / (ms * 1e-3) / 1e9:.0f}")
         d = per_kernel.setdefault(k, {"ms": 0.0, "bytes": 0, "macs": 0, "launches": 0})
         d["ms"] += float(ms)
         d["bytes"] += alg_bytes
         d["macs"] += layer["macs"] * B
         d["launches"] += 1
+    if args.layer_table:
+        with open(args.layer_table, "w") as f:
+            f.write("\n".join(table) + "\n")
     dom = max(per_kernel, key=lambda k: per_kernel[k]["ms"])
     peaks, peak_kind = measured_peaks()
     d = per_kernel[dom]

@@ -215,6 +215,8 @@ GEMM_CASES = [
     # M, K, N : the tensor-core path (K % 16 == 0); tails in M, N and K all appear
     (1, 16, 16), (127, 16, 24), (128, 32, 192), (129, 48, 16), (300, 144, 24), (1000, 160, 960), (513, 960, 320),
     (256, 320, 1280), (77, 1280, 1000), (4096, 64, 384), (2 * 56 * 56, 24 * 6, 24), (640, 576, 96), (64, 4096, 512),
+    # K not a multiple of 16: r rows are read as one (block-diagonal weights)
+    (2 * 56 * 56, 24, 144), (64, 40, 9), (256, 100, 130), (10, 8, 5), (1000, 24, 24),
 ]
 
 

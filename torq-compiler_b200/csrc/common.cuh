@@ -51,6 +51,28 @@ __device__ __forceinline__ int32_t requant_cp(int32_t acc, const ChanParams& cp,
   return max(cmin, min(cmax, r));
 }
 
+// apply_scale_32 part of requant_cp (no zero point, no clamp).
+template <bool HI>
+__device__ __forceinline__ int32_t scale_cp(int32_t acc, const ChanParams& cp) {
+  long long t = (long long)acc * (long long)cp.mult + cp.rnd;
+  t += (long long)(int32_t)((uint32_t)acc >> 31) * (long long)cp.dmul;
+  return HI ? ((int32_t)(t >> 32) >> cp.hshift) : (int32_t)(t >> cp.shift);
+}
+
+// Clamp four int32 values to [lo, hi] (a sub-range of int8, given replicated as s16x2)
+// and pack them into one word: saturating pack to s16x2, packed min/max, byte select.
+__device__ __forceinline__ uint32_t clamp_pack4(int32_t r0, int32_t r1, int32_t r2, int32_t r3, uint32_t lo2,
+                                                uint32_t hi2) {
+  uint32_t a, b;
+  asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(a) : "r"(r1), "r"(r0));
+  asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(b) : "r"(r3), "r"(r2));
+  asm("max.s16x2 %0, %0, %1;" : "+r"(a) : "r"(lo2));
+  asm("max.s16x2 %0, %0, %1;" : "+r"(b) : "r"(lo2));
+  asm("min.s16x2 %0, %0, %1;" : "+r"(a) : "r"(hi2));
+  asm("min.s16x2 %0, %0, %1;" : "+r"(b) : "r"(hi2));
+  return __byte_perm(a, b, 0x6420);
+}
+
 __device__ __forceinline__ int32_t sx8(uint32_t word, int j) {
   return (int32_t)(int8_t)(word >> (8 * j));
 }

@@ -13,8 +13,9 @@
 //                 128-byte swizzled, 4-stage ring guarded by full/empty mbarriers
 //   warp 1      : MMA issuer    - one elected lane issues tcgen05.mma (M=128, N=BN, K=32),
 //                 accumulators in TMEM, double buffered (2 x BN columns)
-//   warps 2..9  : epilogue      - tcgen05.ld 16 columns at a time, int64 requant on CUDA
-//                 cores, 16-byte stores; overlaps the next tile's MMAs
+//   warps 2..9  : epilogue      - two groups of 4 warps, group g drains accumulator stage g
+//                 (alternating tiles): tcgen05.ld 32 columns at a time with the next load in
+//                 flight, int64 requant on CUDA cores, 16-byte stores; overlaps the MMAs
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the device
 // status word and every role drains to the common exit, where TMEM is freed.
 #include <cuda.h>
@@ -40,7 +41,7 @@ struct GemmTcParams {
   int8_t* out;
   long long ldc;
   int M, N, BN, n_tiles, m_tiles, k_blocks, k_last_steps;
-  int out_zp, clamp_min, clamp_max, hi_shift;
+  int out_zp, clamp_min, clamp_max;
   int acc_stride, tmem_cols;
   int* status;
 };
@@ -130,12 +131,37 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "memory");
 }
 
+// Issue a 32-column load without waiting; tmem_ld_wait32 completes it. The wait names the
+// destination registers as operands so that no use of them can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+      "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t (&v)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                 "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]),
+                 "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]),
+                 "+r"(v[30]), "+r"(v[31])
+               :
+               : "memory");
+}
+
+template <bool HI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_acc_full[2], bar_acc_empty[2];
   __shared__ uint32_t tmem_slot;
-  __shared__ __align__(16) ChanParams cp_s[256];
+  __shared__ __align__(16) ChanParams cp_s[2][256];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -152,7 +178,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(smem_u32(&bar_acc_full[s]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[s]), kEpiWarps);
+      mbar_init(smem_u32(&bar_acc_empty[s]), kEpiWarps / 2);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -220,64 +246,85 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
   } else {
-    // ------------------------------------------------ epilogue (8 warps)
-    const int q = warp & 3;               // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;     // which half of the column chunks
-    const int e = threadIdx.x - 64;       // 0..255
-    const int nchunks = p.BN >> 4;
-    const int c_begin = half == 0 ? 0 : (nchunks + 1) / 2;
-    const int c_end = half == 0 ? (nchunks + 1) / 2 : nchunks;
-    const bool hi = p.hi_shift != 0;
+    // ------------------------------------------------ epilogue: two groups of 4 warps, alternating tiles
+    const int q = warp & 3;                // TMEM lane quarter this warp may read
+    const int group = (warp - 2) >> 2;     // group g drains accumulator stage g
+    const int e = (threadIdx.x - 64) & 127;
+    ChanParams* cps = cp_s[group];
+    const uint32_t lo2 = (uint32_t)(p.clamp_min & 0xffff) * 0x10001u;
+    const uint32_t hi2 = (uint32_t)(p.clamp_max & 0xffff) * 0x10001u;
     const bool vec_ok = (p.ldc & 15) == 0;
+    const int nfull = p.BN >> 5;
     int loaded_n = -1;
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, it++) {
+      if ((it & 1) != group) continue;
       const int m = t / p.n_tiles, n = t - m * p.n_tiles;
       if (n != loaded_n) {
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (e < p.BN) cp_s[e] = p.chan[n * p.BN + e];
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (group == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+        for (int i = e; i < p.BN; i += 128) cps[i] = p.chan[n * p.BN + i];
+        if (group == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
         loaded_n = n;
       }
-      const int as = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[as]), acc_phase, p.status, 4);
+      if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[group]), acc_phase, p.status, 4);
       if (!ok) continue;  // keep taking part in the named barriers above
       tc_fence_after();
       const int row = m * kBM + q * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * p.acc_stride);
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(group * p.acc_stride);
       int8_t* orow = p.out + (long long)row * p.ldc + (long long)n * p.BN;
-      for (int c = c_begin; c < c_end; c++) {
-        uint32_t v[16];
-        tmem_ld16(taddr + c * 16, v);
+      const int ncol0 = n * p.BN;
+
+      // requantise 16 accumulators starting at tile column c0 and store them
+      auto emit16 = [&](const uint32_t* v, int c0) {
         uint32_t w4[4];
 #pragma unroll
         for (int g = 0; g < 4; g++) {
-          int qv[4];
+          int r[4];
 #pragma unroll
           for (int j = 0; j < 4; j++) {
-            const ChanParams cp = cp_s[c * 16 + g * 4 + j];
-            const int acc = (int)v[g * 4 + j] + cp.bias;
-            qv[j] = hi ? requant_cp<true>(acc, cp, p.out_zp, p.clamp_min, p.clamp_max)
-                       : requant_cp<false>(acc, cp, p.out_zp, p.clamp_min, p.clamp_max);
+            const ChanParams cp = cps[c0 + g * 4 + j];
+            r[j] = scale_cp<HI>((int)v[g * 4 + j] + cp.bias, cp) + p.out_zp;
           }
-          w4[g] = pack4(qv[0], qv[1], qv[2], qv[3]);
+          w4[g] = clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
         }
         if (row < p.M) {
-          const int col0 = n * p.BN + c * 16;
-          if (vec_ok && col0 + 16 <= p.N) {
-            *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          if (vec_ok && ncol0 + c0 + 16 <= p.N) {
+            *reinterpret_cast<uint4*>(orow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (col0 + j < p.N) orow[c * 16 + j] = (int8_t)(w4[j >> 2] >> (8 * (j & 3)));
+              if (ncol0 + c0 + j < p.N) orow[c0 + j] = (int8_t)(w4[j >> 2] >> (8 * (j & 3)));
           }
         }
+      };
+
+      uint32_t va[32], vb[32];
+      if (nfull > 0) tmem_ld32_issue(taddr, va);
+      tmem_ld_wait32(va);
+      for (int c = 0; c < nfull; c += 2) {
+        if (c + 1 < nfull) tmem_ld32_issue(taddr + (c + 1) * 32, vb);
+        emit16(va, c * 32);
+        emit16(va + 16, c * 32 + 16);
+        tmem_ld_wait32(vb);
+        if (c + 1 < nfull) {
+          if (c + 2 < nfull) tmem_ld32_issue(taddr + (c + 2) * 32, va);
+          emit16(vb, (c + 1) * 32);
+          emit16(vb + 16, (c + 1) * 32 + 16);
+          tmem_ld_wait32(va);
+        }
+      }
+      if (p.BN & 16) {
+        uint32_t vt[16];
+        tmem_ld16(taddr + nfull * 32, vt);
+        emit16(vt, nfull * 32);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[as]));
+      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[group]));
     }
   }
 
@@ -380,7 +427,6 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   p.out_zp = a.out_zp;
   p.clamp_min = a.clamp_min;
   p.clamp_max = a.clamp_max;
-  p.hi_shift = a.hi_shift;
   int stride = 32;
   while (stride < a.BN) stride <<= 1;
   p.acc_stride = stride;
@@ -389,13 +435,16 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   const size_t smem = 1024 + (size_t)kStages * (kBM * kBK + (size_t)a.BN * kBK);
   static size_t smem_set = 0;
   if (smem > smem_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(197 * 1024));
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(197 * 1024));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(197 * 1024));
     if (e != cudaSuccess) return e;
     smem_set = 197 * 1024;
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_i8_tc_kernel<<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, p);
+  if (a.hi_shift) gemm_i8_tc_kernel<true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, p);
+  else gemm_i8_tc_kernel<false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, p);
   return cudaGetLastError();
 }
 

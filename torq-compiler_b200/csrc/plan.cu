@@ -299,16 +299,36 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         const bool pointwise = fc || (KH == 1 && KW == 1 && op.stride_h == 1 && op.stride_w == 1 && op.pad_t == 0 &&
                                       op.pad_b == 0 && op.pad_l == 0 && op.pad_r == 0);
         const long long M = (long long)N * OH * OW;
-        if (pointwise && op.weight_zp == 0 && !force_simt() && gemm_tc_supported(M, OC, (int)K, K)) {
+        // TMA wants a row pitch that is a multiple of 16 bytes. When K is not, r consecutive
+        // rows are read as one row of r*K bytes against block-diagonal weights: row m' of the
+        // product then holds the outputs of pixels r*m' .. r*m'+r-1 back to back, which is
+        // exactly their dense NHWC placement, so nothing else changes.
+        int rgroup = 1;
+        if (K % 16 != 0) {
+          int g16 = 16;
+          while (K % g16 != 0) g16 >>= 1;  // gcd(K, 16)
+          rgroup = 16 / g16;
+        }
+        if (pointwise && op.weight_zp == 0 && !force_simt() && rgroup <= 4 && M % rgroup == 0 &&
+            (long long)OC * rgroup <= 4096 && gemm_tc_supported(M / rgroup, OC * rgroup, (int)K * rgroup, K * rgroup)) {
           GemmTcArgs ga{};
-          gemm_tc_tiling(OC, ga.BN, ga.n_tiles);
-          ga.M = M; ga.N = OC; ga.K = (int)K; ga.Kpad = (int)((K + 127) / 128 * 128);
-          ga.lda = K; ga.ldc = OC;
+          const int Ng = OC * rgroup, Kg = (int)K * rgroup;
+          gemm_tc_tiling(Ng, ga.BN, ga.n_tiles);
+          ga.M = M / rgroup; ga.N = Ng; ga.K = Kg; ga.Kpad = (Kg + 127) / 128 * 128;
+          ga.lda = Kg; ga.ldc = Ng;
           ga.out_zp = op.out_zp; ga.clamp_min = op.clamp_min; ga.clamp_max = op.clamp_max; ga.double_round = dr;
           ga.hi_shift = b.last_hi_shift;
           const int rows = ga.n_tiles * ga.BN;
           std::vector<int8_t> wp((size_t)rows * ga.Kpad, 0);
-          for (int oc = 0; oc < OC; oc++) memcpy(wp.data() + (size_t)oc * ga.Kpad, w + (size_t)oc * K, (size_t)K);
+          for (int j = 0; j < rgroup; j++)
+            for (int oc = 0; oc < OC; oc++)
+              memcpy(wp.data() + (size_t)(j * OC + oc) * ga.Kpad + (size_t)j * K, w + (size_t)oc * K, (size_t)K);
+          {
+            std::vector<ChanParams> rep((size_t)Ng);
+            for (int j = 0; j < rgroup; j++)
+              for (int oc = 0; oc < OC; oc++) rep[(size_t)j * OC + oc] = cp[oc];
+            cp.swap(rep);
+          }
           { ChanParams z{}; z.shift = 34; z.hshift = 2; z.rnd = 1ll << 33; cp.resize(rows, z); }
           size_t w_off = b.add_const(wp.data(), wp.size());
           size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));

@@ -9,6 +9,7 @@
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <mutex>
@@ -246,6 +247,16 @@ struct tb200_executable {
   void* arena = nullptr;
   void* const_dev = nullptr;       // derived constants (packed weights, channel params)
   std::vector<tb200_buffer_t*> staging_in, staging_out;  // for tb200_invoke_host
+  // CUDA graphs of the whole launch list, one per distinct set of bound addresses
+  // (a dispatch with the same bindings replays its graph: one submission instead of
+  // one per kernel). Small LRU; TB200_NO_GRAPH=1 turns it off.
+  struct CachedGraph {
+    std::vector<void*> io;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t last_use = 0;
+  };
+  std::vector<CachedGraph> graphs;
+  uint64_t graph_clock = 0;
 };
 
 extern "C" int tb200_executable_create(tb200_device_t* d, const void* bytes, size_t n_bytes,
@@ -346,6 +357,7 @@ extern "C" int tb200_executable_destroy(tb200_executable_t* ex) {
   if (!ex) return TB200_INVALID_ARGUMENT;
   cudaSetDevice(ex->dev->ordinal);
   cudaStreamSynchronize(ex->dev->stream);
+  for (auto& g : ex->graphs) cudaGraphExecDestroy(g.exec);
   for (auto* b : ex->staging_in) tb200_buffer_free(b);
   for (auto* b : ex->staging_out) tb200_buffer_free(b);
   if (ex->arena) cudaFree(ex->arena);
@@ -432,6 +444,55 @@ int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cud
   return TB200_OK;
 }
 
+bool use_graphs() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("TB200_NO_GRAPH");
+    v = (e && *e && *e != '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// Replays (or first captures) the CUDA graph of the launch list for this set of addresses.
+int run_graph(tb200_executable* ex, const std::vector<void*>& io) {
+  tb200_device* d = ex->dev;
+  constexpr size_t kMaxGraphs = 8;
+  ex->graph_clock++;
+  for (auto& g : ex->graphs)
+    if (g.io == io) {
+      g.last_use = ex->graph_clock;
+      CUDA_OK(d, cudaGraphLaunch(g.exec, d->stream));
+      return TB200_OK;
+    }
+  // tensor maps and function attributes are set up by a first direct run, outside any capture
+  int st = run_plan(ex, io, nullptr);
+  if (st != TB200_OK) return st;
+  cudaGraph_t graph = nullptr;
+  CUDA_OK(d, cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
+  st = run_plan(ex, io, nullptr);
+  cudaError_t e = cudaStreamEndCapture(d->stream, &graph);
+  if (st != TB200_OK || e != cudaSuccess) {
+    if (graph) cudaGraphDestroy(graph);
+    return st != TB200_OK ? st : fail(d, TB200_INTERNAL, "graph capture failed: %s", cudaGetErrorString(e));
+  }
+  tb200_executable::CachedGraph cg;
+  cg.io = io;
+  cg.last_use = ex->graph_clock;
+  e = cudaGraphInstantiate(&cg.exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return fail(d, TB200_INTERNAL, "graph instantiate failed: %s", cudaGetErrorString(e));
+  if (ex->graphs.size() >= kMaxGraphs) {
+    size_t victim = 0;
+    for (size_t i = 1; i < ex->graphs.size(); i++)
+      if (ex->graphs[i].last_use < ex->graphs[victim].last_use) victim = i;
+    cudaGraphExecDestroy(ex->graphs[victim].exec);
+    ex->graphs.erase(ex->graphs.begin() + victim);
+  }
+  ex->graphs.push_back(cg);
+  // the direct run above already produced this dispatch's results
+  return TB200_OK;
+}
+
 }  // namespace
 
 extern "C" int tb200_dispatch(tb200_executable_t* ex, const tb200_binding_t* bindings, size_t n) {
@@ -442,7 +503,7 @@ extern "C" int tb200_dispatch(tb200_executable_t* ex, const tb200_binding_t* bin
   std::vector<void*> io;
   int st = resolve_bindings(ex, bindings, n, io);
   if (st != TB200_OK) return st;
-  if (!d->profile_csv) return run_plan(ex, io, nullptr);
+  if (!d->profile_csv) return use_graphs() ? run_graph(ex, io) : run_plan(ex, io, nullptr);
 
   // profiled dispatch: bracket every op with events and write the reference's CSV schema
   size_t ns = ex->plan.steps.size();
