@@ -31,8 +31,9 @@ __device__ __forceinline__ void transpose4x4(uint32_t p0, uint32_t p1, uint32_t 
   t[3] = __byte_perm(b, d, 0x7632);
 }
 
-template <int STRIDE>
-__global__ void __launch_bounds__(128) dw3x3_kernel(DwArgs a) {
+// HI33: every rescale shift of the op is >= 33 (compact constants, see gemm_tcgen05.cu).
+template <int STRIDE, bool HI33>
+__global__ void __launch_bounds__(128, 5) dw3x3_kernel(DwArgs a) {
   constexpr int TW = STRIDE == 1 ? 2 : 1;    // outputs per thread along W
   constexpr int NCOL = STRIDE == 1 ? 4 : 3;  // input columns per row load
   const int groups = a.C >> 2;
@@ -54,6 +55,8 @@ __global__ void __launch_bounds__(128) dw3x3_kernel(DwArgs a) {
   const int oh_end = min(a.OH, oh_begin + kRows);
   const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.C + c;
   const uint32_t zpw = (uint32_t)(a.input_zp & 0xff) * 0x01010101u;
+  const uint32_t lo2 = (uint32_t)(a.clamp_min & 0xffff) * 0x10001u;
+  const uint32_t hi2 = (uint32_t)(a.clamp_max & 0xffff) * 0x10001u;
 
   // weights: [3 rows][TW variants][C] words, this thread's 4 channels
   uint32_t wq[3][TW][4];
@@ -64,39 +67,57 @@ __global__ void __launch_bounds__(128) dw3x3_kernel(DwArgs a) {
       uint4 w = *reinterpret_cast<const uint4*>(a.wq + ((size_t)(kh * TW + v) * a.C + c));
       wq[kh][v][0] = w.x; wq[kh][v][1] = w.y; wq[kh][v][2] = w.z; wq[kh][v][3] = w.w;
     }
-  ChanParams cp[4];
+  // per-channel constants: {bias, mult, high word of rnd, shift - 32} (HI33) or the full record
+  int4 cq[4];
+  ChanParams cp[HI33 ? 1 : 4];
 #pragma unroll
-  for (int k = 0; k < 4; k++) cp[k] = a.chan[c + k];
+  for (int k = 0; k < 4; k++) {
+    const ChanParams t = a.chan[c + k];
+    if (HI33) cq[k] = make_int4(t.bias, t.mult, (int)(t.rnd >> 32), t.hshift);
+    else cp[k] = t;
+  }
 
-  auto load_row = [&](int ih, uint32_t (&t)[4]) {
-    if (ih < 0 || ih >= a.H) {
-      t[0] = t[1] = t[2] = t[3] = zpw;
-      return;
-    }
-    const int8_t* row = xin + (size_t)ih * a.W * a.C;
-    uint32_t p[4];
+  // raw pixel words of one input row (izp for anything outside the image)
+  auto fetch_row = [&](int ih, uint32_t (&p)[4]) {
+    const bool row_in = ih >= 0 && ih < a.H;
+    const int8_t* row = xin + (size_t)(row_in ? ih : 0) * a.W * a.C;
 #pragma unroll
     for (int k = 0; k < 4; k++) {
       const int iw = iw0 + k;
-      p[k] = (k < NCOL && iw >= 0 && iw < a.W) ? *reinterpret_cast<const uint32_t*>(row + (size_t)iw * a.C) : zpw;
+      p[k] = (k < NCOL && row_in && iw >= 0 && iw < a.W) ? *reinterpret_cast<const uint32_t*>(row + (size_t)iw * a.C) : zpw;
     }
-    transpose4x4(p[0], p[1], p[2], p[3], t);
   };
 
   uint32_t win[3][4];
-  const bool hi = a.hi_shift != 0;
-  if (STRIDE == 1) {
-    load_row(oh_begin - a.pad_t, win[0]);
-    load_row(oh_begin - a.pad_t + 1, win[1]);
+  uint32_t pend[2][4];  // rows fetched ahead of their use (1 for stride 1, 2 for stride 2)
+  {
+    uint32_t p[4];
+    if (STRIDE == 1) {
+      fetch_row(oh_begin - a.pad_t, p);
+      transpose4x4(p[0], p[1], p[2], p[3], win[0]);
+      fetch_row(oh_begin - a.pad_t + 1, p);
+      transpose4x4(p[0], p[1], p[2], p[3], win[1]);
+      fetch_row(oh_begin - a.pad_t + 2, pend[0]);
+    } else {
+      fetch_row(oh_begin * 2 - a.pad_t, p);
+      transpose4x4(p[0], p[1], p[2], p[3], win[0]);
+      fetch_row(oh_begin * 2 - a.pad_t + 1, pend[0]);
+      fetch_row(oh_begin * 2 - a.pad_t + 2, pend[1]);
+    }
   }
   for (int oh = oh_begin; oh < oh_end; oh++) {
     const int ih0 = oh * STRIDE - a.pad_t;
+    // consume the rows fetched during the previous iteration, then fetch the next ones
     if (STRIDE == 1) {
-      load_row(ih0 + 2, win[2]);
+      transpose4x4(pend[0][0], pend[0][1], pend[0][2], pend[0][3], win[2]);
+      if (oh + 1 < oh_end) fetch_row(ih0 + 3, pend[0]);
     } else {
-      if (oh == oh_begin) load_row(ih0, win[0]);
-      load_row(ih0 + 1, win[1]);
-      load_row(ih0 + 2, win[2]);
+      transpose4x4(pend[0][0], pend[0][1], pend[0][2], pend[0][3], win[1]);
+      transpose4x4(pend[1][0], pend[1][1], pend[1][2], pend[1][3], win[2]);
+      if (oh + 1 < oh_end) {
+        fetch_row(ih0 + 3, pend[0]);
+        fetch_row(ih0 + 4, pend[1]);
+      }
     }
     int8_t* orow = a.out + (((size_t)n * a.OH + oh) * a.OW + ow0) * a.C + c;
 #pragma unroll
@@ -105,13 +126,18 @@ __global__ void __launch_bounds__(128) dw3x3_kernel(DwArgs a) {
       int q[4];
 #pragma unroll
       for (int k = 0; k < 4; k++) {
-        int acc = cp[k].bias;
+        int acc = HI33 ? cq[k].x : cp[k].bias;
 #pragma unroll
         for (int kh = 0; kh < 3; kh++) acc = __dp4a((int)win[kh][k], (int)wq[kh][v][k], acc);
-        q[k] = hi ? requant_cp<true>(acc, cp[k], a.out_zp, a.clamp_min, a.clamp_max)
-                  : requant_cp<false>(acc, cp[k], a.out_zp, a.clamp_min, a.clamp_max);
+        if (HI33) {
+          long long tt = (long long)acc * (long long)cq[k].y + (((long long)cq[k].z << 32) | (long long)(uint32_t)a.rnd_lo);
+          tt += (long long)(int32_t)((uint32_t)acc >> 31) * (long long)a.dmul;
+          q[k] = ((int32_t)(tt >> 32) >> cq[k].w) + a.out_zp;
+        } else {
+          q[k] = scale_cp<false>(acc, cp[k]) + a.out_zp;
+        }
       }
-      *reinterpret_cast<uint32_t*>(orow + (size_t)v * a.C) = pack4(q[0], q[1], q[2], q[3]);
+      *reinterpret_cast<uint32_t*>(orow + (size_t)v * a.C) = clamp_pack4(q[0], q[1], q[2], q[3], lo2, hi2);
     }
     // roll the window
     if (STRIDE == 1) {
@@ -215,8 +241,13 @@ void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
     const int tw = a.stride_h == 1 ? 2 : 1;
     long long total = (long long)a.N * ((a.OH + kRows - 1) / kRows) * ((a.OW + tw - 1) / tw) * (a.C >> 2);
     unsigned blocks = (unsigned)((total + 127) / 128);
-    if (a.stride_h == 1) dw3x3_kernel<1><<<blocks, 128, 0, stream>>>(a);
-    else dw3x3_kernel<2><<<blocks, 128, 0, stream>>>(a);
+    if (a.stride_h == 1) {
+      if (a.hi33) dw3x3_kernel<1, true><<<blocks, 128, 0, stream>>>(a);
+      else dw3x3_kernel<1, false><<<blocks, 128, 0, stream>>>(a);
+    } else {
+      if (a.hi33) dw3x3_kernel<2, true><<<blocks, 128, 0, stream>>>(a);
+      else dw3x3_kernel<2, false><<<blocks, 128, 0, stream>>>(a);
+    }
   } else if (a.M == 1 && (a.C & 3) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C >> 2);
     depthwise_generic_kernel<4><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);

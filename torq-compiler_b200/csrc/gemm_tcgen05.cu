@@ -8,14 +8,23 @@
 // bias' already holds bias - izp * sum_k W[n,k] (1x1 convs have no padding, so the
 // input zero point folds into a per-channel constant).
 //
-// Structure (one persistent CTA per SM, 320 threads):
-//   warp 0      : TMA producer  - A tile 128 x 128 B and W tile BN x 128 B per K block,
-//                 128-byte swizzled, 4-stage ring guarded by full/empty mbarriers
-//   warp 1      : MMA issuer    - one elected lane issues tcgen05.mma (M=128, N=BN, K=32),
-//                 accumulators in TMEM, double buffered (2 x BN columns)
-//   warps 2..9  : epilogue      - two groups of 4 warps, group g drains accumulator stage g
-//                 (alternating tiles): tcgen05.ld 32 columns at a time with the next load in
-//                 flight, int64 requant on CUDA cores, 16-byte stores; overlaps the MMAs
+// These GEMMs are skinny (K = 16..1280 bytes per row, M in the millions) and bound by
+// HBM and by the integer epilogue, not by the tensor pipe. The structure follows from that:
+//   * one persistent CTA per SM, 576 threads;
+//   * warp 0 = TMA producer. The swizzle width follows K (32 / 64 / 128-byte rows), so a
+//     stage of A is 128 rows x 32..128 B and the ring holds up to 16 stages: many small
+//     loads in flight instead of a few padded ones;
+//   * when the whole weight matrix fits (<= 96 KB) it is loaded into shared memory once
+//     and stays; otherwise its tile travels with each A stage;
+//   * warp 1 = MMA issuer, one elected lane, accumulators in TMEM, 4 stages of <= 128 columns;
+//   * warps 2..17 = epilogue, the part that bounds the kernel (about a dozen integer
+//     instructions per output): 4 groups of 4 warps, group g drains accumulator stage g,
+//     so 16 warps keep the schedulers busy. tcgen05.ld 32 columns, int64 rescale on CUDA
+//     cores from 16-byte per-channel constants in shared memory, packed clamp; the int8
+//     tile is staged in shared memory and leaves with one TMA store, so global memory sees
+//     full lines instead of 16-byte pieces at a row stride;
+//   * single-thread roles carry no divisions: tile coordinates and ring indices advance
+//     incrementally.
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the device
 // status word and every role drains to the common exit, where TMEM is freed.
 #include <cuda.h>
@@ -29,11 +38,13 @@ namespace tb200 {
 
 namespace {
 
-constexpr int kStages = 4;
 constexpr int kBM = 128;
-constexpr int kBK = 128;  // bytes of K per stage = one 128-byte swizzle row
-constexpr int kEpiWarps = 8;
+constexpr int kMaxStages = 16;
+constexpr int kEpiGroups = 4;                    // each group = 4 warps = the 128 TMEM lanes of one accumulator
+constexpr int kEpiWarps = 4 * kEpiGroups;
 constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kSmemBudget = 196 * 1024;          // dynamic shared memory the kernel may use
+constexpr int kResidentWeightBytes = 64 * 1024;  // weights up to this size stay in shared memory
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 struct GemmTcParams {
@@ -41,8 +52,14 @@ struct GemmTcParams {
   int8_t* out;
   long long ldc;
   int M, N, BN, n_tiles, m_tiles, k_blocks, k_last_steps;
+  int row_bytes;        // 32, 64 or 128: bytes of K per shared-memory row (= swizzle width)
+  int stages;           // A (or A+W) ring depth
+  int w_resident;       // weights loaded once
   int out_zp, clamp_min, clamp_max;
-  int acc_stride, tmem_cols;
+  int rnd_lo, dmul;     // uniform parts of the rounding constants (HI33 kernels)
+  int acc_stride, acc_stages, tmem_cols;
+  int tma_store;        // stage the output tile in shared memory and write it with one TMA store
+  uint32_t staging_off; // byte offset of the staging buffers inside dynamic shared memory
   int* status;
 };
 
@@ -74,18 +91,27 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 // Bounded wait: false (and a code in the status word) if the phase does not complete in time.
+// The clock is only consulted after a few thousand polls, so the common case costs one poll.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int i = 0; i < 4096; i++)
+    if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; i++)
+    for (int i = 0; i < 256; i++)
       if (mbar_try_wait(bar, parity)) return true;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       if (*(volatile int*)status == 0) *(volatile int*)status = code;
       return false;
     }
   }
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0),
+               "r"(c1), "r"(src)
+               : "memory");
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
@@ -95,14 +121,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  // K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart
+// K-major operand in shared memory, rows of row_bytes (= the swizzle width), 8-row groups
+// 8 * row_bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int row_bytes) {
+  const uint64_t layout = row_bytes == 128 ? 2 : row_bytes == 64 ? 4 : 6;  // SWIZZLE_128B / 64B / 32B
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;            // leading byte offset (unused for this layout)
-  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
-  d |= (uint64_t)1 << 46;            // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  d |= (uint64_t)1 << 16;                          // leading byte offset (unused for these layouts)
+  d |= (uint64_t)((8 * row_bytes) >> 4) << 32;     // stride byte offset
+  d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
+  d |= layout << 61;
   return d;
 }
 
@@ -130,7 +158,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
-
 // Issue a 32-column load without waiting; tmem_ld_wait32 completes it. The wait names the
 // destination registers as operands so that no use of them can be scheduled ahead of it.
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&v)[32]) {
@@ -155,31 +182,39 @@ __device__ __forceinline__ void tmem_ld_wait32(uint32_t (&v)[32]) {
                : "memory");
 }
 
-template <bool HI>
+// HI33: every rescale shift of the op is >= 33, so the rounding constant's low word and the
+// negative-accumulator term are the same for all channels and a channel needs only
+// {bias, mult, high word of rnd, shift - 32}: one 16-byte shared-memory load per output.
+template <bool HI33>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmTcParams p) {
+gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmC, GemmTcParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_acc_full[2], bar_acc_empty[2];
+  __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_empty[kMaxStages], bar_acc_full[4], bar_acc_empty[4],
+      bar_w;
   __shared__ uint32_t tmem_slot;
-  __shared__ __align__(16) ChanParams cp_s[2][256];
+  __shared__ __align__(16) int4 cp_s[kEpiGroups][128];  // per epilogue group: {bias, mult, rnd_hi, shift - 32}
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t b_stage_bytes = (uint32_t)p.BN * kBK;
-  const uint32_t smem_a = smem_base;
-  const uint32_t smem_b = smem_base + kStages * kBM * kBK;
+  const uint32_t a_stage_bytes = (uint32_t)kBM * p.row_bytes;
+  const uint32_t w_tile_bytes = (uint32_t)p.BN * p.row_bytes;  // one (n tile, k block) of the weights
+  const uint32_t stage_bytes = a_stage_bytes + (p.w_resident ? 0u : w_tile_bytes);
+  const uint32_t smem_w = smem_base;  // resident weights: [n_tiles][k_blocks] tiles
+  const uint32_t smem_ring = smem_base + (p.w_resident ? (uint32_t)p.n_tiles * p.k_blocks * w_tile_bytes : 0u);
   const int total_tiles = p.m_tiles * p.n_tiles;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; s++) {
+    for (int s = 0; s < p.stages; s++) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    for (int s = 0; s < 2; s++) {
+    for (int s = 0; s < 4; s++) {
       mbar_init(smem_u32(&bar_acc_full[s]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[s]), kEpiWarps / 2);
+      mbar_init(smem_u32(&bar_acc_empty[s]), 4);
     }
+    mbar_init(smem_u32(&bar_w), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -194,24 +229,38 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
+  // tile t -> (n, m) with n the slow index: a CTA keeps one n tile (its constants) for a long run
   if (warp == 0) {
     // ------------------------------------------------ TMA producer
     if (lane == 0) {
+      if (p.w_resident) {
+        const uint32_t bw = smem_u32(&bar_w);
+        mbar_expect_tx(bw, (uint32_t)p.n_tiles * p.k_blocks * w_tile_bytes);
+        for (int n = 0; n < p.n_tiles; n++)
+          for (int kb = 0; kb < p.k_blocks; kb++)
+            tma_load_2d(smem_w + (uint32_t)(n * p.k_blocks + kb) * w_tile_bytes, &tmB, kb * p.row_bytes, n * p.BN, bw);
+      }
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int n = blockIdx.x / p.m_tiles, m = blockIdx.x - n * p.m_tiles;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int m = t / p.n_tiles, n = t - m * p.n_tiles;
         for (int kb = 0; kb < p.k_blocks; kb++) {
           if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1, p.status, 1))) break;
           const uint32_t full = smem_u32(&bar_full[s]);
-          mbar_expect_tx(full, kBM * kBK + b_stage_bytes);
-          tma_load_2d(smem_a + s * (kBM * kBK), &tmA, kb * kBK, m * kBM, full);
-          tma_load_2d(smem_b + s * b_stage_bytes, &tmB, kb * kBK, n * p.BN, full);
-          if (++s == kStages) {
+          const uint32_t dst = smem_ring + (uint32_t)s * stage_bytes;
+          mbar_expect_tx(full, stage_bytes);
+          tma_load_2d(dst, &tmA, kb * p.row_bytes, m * kBM, full);
+          if (!p.w_resident) tma_load_2d(dst + a_stage_bytes, &tmB, kb * p.row_bytes, n * p.BN, full);
+          if (++s == p.stages) {
             s = 0;
             phase ^= 1;
           }
+        }
+        m += gridDim.x;
+        while (m >= p.m_tiles) {
+          m -= p.m_tiles;
+          n++;
         }
       }
     }
@@ -219,113 +268,160 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      const int steps_full = p.row_bytes / 32;
       int s = 0;
       uint32_t phase = 0;
-      int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
-        const int as = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
+      if (p.w_resident) ok = mbar_wait(smem_u32(&bar_w), 0, p.status, 5);
+      int n = blockIdx.x / p.m_tiles, m = blockIdx.x - n * p.m_tiles;
+      int as = 0;
+      uint32_t acc_phase = 0;
+      const uint64_t desc0_ring = make_smem_desc(smem_ring, p.row_bytes);
+      const uint64_t desc0_w = make_smem_desc(p.w_resident ? smem_w : smem_ring + a_stage_bytes, p.row_bytes);
+      const uint32_t stage_units = stage_bytes >> 4, w_tile_units = w_tile_bytes >> 4;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         if (!(ok = mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2))) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(as * p.acc_stride);
         for (int kb = 0; kb < p.k_blocks; kb++) {
           if (!(ok = mbar_wait(smem_u32(&bar_full[s]), phase, p.status, 3))) break;
           tc_fence_after();
-          const int steps = (kb == p.k_blocks - 1) ? p.k_last_steps : (kBK / 32);
-          const uint64_t da = make_smem_desc(smem_a + s * (kBM * kBK));
-          const uint64_t db = make_smem_desc(smem_b + s * b_stage_bytes);
+          const int steps = (kb == p.k_blocks - 1) ? p.k_last_steps : steps_full;
+          const uint64_t da = desc0_ring + (uint64_t)((uint32_t)s * stage_units);
+          const uint64_t db = p.w_resident ? desc0_w + (uint64_t)((uint32_t)(n * p.k_blocks + kb) * w_tile_units)
+                                           : desc0_w + (uint64_t)((uint32_t)s * stage_units);
           for (int k = 0; k < steps; k++) mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-          mma_commit(smem_u32(&bar_empty[s]));  // frees the smem stage once the MMAs have read it
-          if (++s == kStages) {
+          mma_commit(smem_u32(&bar_empty[s]));  // frees the stage once the MMAs have read it
+          if (++s == p.stages) {
             s = 0;
             phase ^= 1;
           }
         }
         if (ok) mma_commit(smem_u32(&bar_acc_full[as]));
+        if (++as == p.acc_stages) {
+          as = 0;
+          acc_phase ^= 1;
+        }
+        m += gridDim.x;
+        while (m >= p.m_tiles) {
+          m -= p.m_tiles;
+          n++;
+        }
       }
     }
   } else {
-    // ------------------------------------------------ epilogue: two groups of 4 warps, alternating tiles
+    // ------------------------------------------------ epilogue: 4 groups of 4 warps; group g owns accumulator
+    // stage g and takes this CTA's tiles g, g + 4, g + 8, ...
     const int q = warp & 3;                // TMEM lane quarter this warp may read
-    const int group = (warp - 2) >> 2;     // group g drains accumulator stage g
+    const int group = (warp - 2) >> 2;
     const int e = (threadIdx.x - 64) & 127;
-    ChanParams* cps = cp_s[group];
+    int4* cps = cp_s[group];
     const uint32_t lo2 = (uint32_t)(p.clamp_min & 0xffff) * 0x10001u;
     const uint32_t hi2 = (uint32_t)(p.clamp_max & 0xffff) * 0x10001u;
     const bool vec_ok = (p.ldc & 15) == 0;
     const int nfull = p.BN >> 5;
+    const uint32_t tile_bytes = (uint32_t)kBM * p.BN;
+    // one staging tile per group for the TMA store of the output
+    uint8_t* const stage_tile = smem_raw + (smem_base - smem_u32(smem_raw)) + p.staging_off + (size_t)group * tile_bytes;
+    const int row_in_tile = q * 32 + lane;
+    uint8_t* const srow = stage_tile + (size_t)row_in_tile * p.BN;
+    const int bar_id = 1 + group;
+    auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory"); };
     int loaded_n = -1;
-    int it = 0;
+    uint32_t acc_phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, it++) {
-      if ((it & 1) != group) continue;
-      const int m = t / p.n_tiles, n = t - m * p.n_tiles;
-      if (n != loaded_n) {
-        if (group == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-        else asm volatile("bar.sync 2, 128;" ::: "memory");
-        for (int i = e; i < p.BN; i += 128) cps[i] = p.chan[n * p.BN + i];
-        if (group == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-        else asm volatile("bar.sync 2, 128;" ::: "memory");
+    const int t_first = blockIdx.x + group * gridDim.x;
+    int n = t_first / p.m_tiles, m = t_first - n * p.m_tiles;
+    for (int t = t_first; t < total_tiles; t += kEpiGroups * gridDim.x) {
+      const ChanParams* chan_n = p.chan + (size_t)n * p.BN;
+      if (HI33 && n != loaded_n) {
+        group_sync();
+        if (e < p.BN) {
+          const ChanParams c = chan_n[e];
+          cps[e] = make_int4(c.bias, c.mult, (int)(c.rnd >> 32), c.hshift);
+        }
+        group_sync();
         loaded_n = n;
       }
-      const uint32_t acc_phase = (it >> 1) & 1;
       if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[group]), acc_phase, p.status, 4);
-      if (!ok) continue;  // keep taking part in the named barriers above
-      tc_fence_after();
-      const int row = m * kBM + q * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(group * p.acc_stride);
-      int8_t* orow = p.out + (long long)row * p.ldc + (long long)n * p.BN;
-      const int ncol0 = n * p.BN;
-
-      // requantise 16 accumulators starting at tile column c0 and store them
-      auto emit16 = [&](const uint32_t* v, int c0) {
-        uint32_t w4[4];
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-          int r[4];
-#pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const ChanParams cp = cps[c0 + g * 4 + j];
-            r[j] = scale_cp<HI>((int)v[g * 4 + j] + cp.bias, cp) + p.out_zp;
-          }
-          w4[g] = clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
+      if (ok) {
+        tc_fence_after();
+        const int row = m * kBM + row_in_tile;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(group * p.acc_stride);
+        int8_t* orow = p.out + (long long)row * p.ldc + (long long)n * p.BN;
+        const int ncol0 = n * p.BN;
+        if (p.tma_store) {
+          // this group's previous store must have read the staging tile before it is overwritten
+          if (e == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          group_sync();
         }
-        if (row < p.M) {
-          if (vec_ok && ncol0 + c0 + 16 <= p.N) {
-            *reinterpret_cast<uint4*>(orow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; j++)
-              if (ncol0 + c0 + j < p.N) orow[c0 + j] = (int8_t)(w4[j >> 2] >> (8 * (j & 3)));
-          }
-        }
-      };
 
-      uint32_t va[32], vb[32];
-      if (nfull > 0) tmem_ld32_issue(taddr, va);
-      tmem_ld_wait32(va);
-      for (int c = 0; c < nfull; c += 2) {
-        if (c + 1 < nfull) tmem_ld32_issue(taddr + (c + 1) * 32, vb);
-        emit16(va, c * 32);
-        emit16(va + 16, c * 32 + 16);
-        tmem_ld_wait32(vb);
-        if (c + 1 < nfull) {
-          if (c + 2 < nfull) tmem_ld32_issue(taddr + (c + 2) * 32, va);
-          emit16(vb, (c + 1) * 32);
-          emit16(vb + 16, (c + 1) * 32 + 16);
-          tmem_ld_wait32(va);
+        // requantise 16 accumulators starting at tile column c0 and store them
+        auto emit16 = [&](const uint32_t* v, int c0) {
+          uint32_t w4[4];
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            int r[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              if (HI33) {
+                const int4 c = cps[c0 + g * 4 + j];
+                const int acc = (int)v[g * 4 + j] + c.x;
+                long long tt = (long long)acc * (long long)c.y + (((long long)c.z << 32) | (long long)(uint32_t)p.rnd_lo);
+                tt += (long long)(int32_t)((uint32_t)acc >> 31) * (long long)p.dmul;
+                r[j] = ((int32_t)(tt >> 32) >> c.w) + p.out_zp;
+              } else {
+                const ChanParams c = chan_n[c0 + g * 4 + j];
+                r[j] = scale_cp<false>((int)v[g * 4 + j] + c.bias, c) + p.out_zp;
+              }
+            }
+            w4[g] = clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
+          }
+          if (p.tma_store) {
+            *reinterpret_cast<uint4*>(srow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          } else if (row < p.M) {
+            if (vec_ok && ncol0 + c0 + 16 <= p.N) {
+              *reinterpret_cast<uint4*>(orow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; j++)
+                if (ncol0 + c0 + j < p.N) orow[c0 + j] = (int8_t)(w4[j >> 2] >> (8 * (j & 3)));
+            }
+          }
+        };
+
+        for (int c = 0; c < nfull; c++) {
+          uint32_t v[32];
+          tmem_ld32_issue(taddr + c * 32, v);
+          tmem_ld_wait32(v);
+          emit16(v, c * 32);
+          emit16(v + 16, c * 32 + 16);
+        }
+        if (p.BN & 16) {
+          uint32_t vt[16];
+          tmem_ld16(taddr + nfull * 32, vt);
+          emit16(vt, nfull * 32);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[group]));  // TMEM stage drained
+        if (p.tma_store) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // staged bytes -> visible to the TMA engine
+          group_sync();
+          if (e == 0) {
+            tma_store_2d(&tmC, ncol0, m * kBM, smem_u32(stage_tile));
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
         }
       }
-      if (p.BN & 16) {
-        uint32_t vt[16];
-        tmem_ld16(taddr + nfull * 32, vt);
-        emit16(vt, nfull * 32);
+      acc_phase ^= 1;
+      m += kEpiGroups * gridDim.x;
+      while (m >= p.m_tiles) {
+        m -= p.m_tiles;
+        n++;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[group]));
     }
+    if (p.tma_store && e == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ------------------------------------------------ common exit: free TMEM
@@ -357,16 +453,34 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D byte tensor [rows, cols] with a row pitch; box = [box_rows, 128 bytes], 128-byte swizzle.
-bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t box_rows) {
+// Output tensor [rows, cols] with a row pitch; box = [box_rows, box_cols], dense rows in shared memory.
+bool encode_2d_plain(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch,
+                     uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {pitch};
-  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 2-D byte tensor [rows, cols] with a row pitch; box = [box_rows, row_bytes], swizzle width = row_bytes.
+bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t box_rows,
+               int row_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {(cuuint32_t)row_bytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                  : CU_TENSOR_MAP_SWIZZLE_32B;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -383,68 +497,108 @@ int sm_count() {
 
 }  // namespace
 
-void gemm_tc_tiling(int N, int& BN, int& n_tiles) {
+GemmTcGeometry gemm_tc_geometry(int N, int K) {
+  GemmTcGeometry g{};
+  g.row_bytes = K <= 32 ? 32 : K <= 64 ? 64 : 128;
+  g.k_blocks = (K + g.row_bytes - 1) / g.row_bytes;
+  g.Kpad = g.k_blocks * g.row_bytes;
+  // N tiles of at most 128 columns (4 accumulator stages fit TMEM); least padding wins
   const int npad = (N + 15) / 16 * 16;
-  n_tiles = (npad + 255) / 256;
-  BN = ((npad + n_tiles - 1) / n_tiles + 15) / 16 * 16;
+  int best_tiles = 0, best_bn = 0, best_total = 1 << 30;
+  const int t0 = (npad + 127) / 128;
+  for (int tiles = t0; tiles <= t0 + 2; tiles++) {
+    const int bn = ((npad + tiles - 1) / tiles + 15) / 16 * 16;
+    if (bn * tiles < best_total) {
+      best_total = bn * tiles;
+      best_tiles = tiles;
+      best_bn = bn;
+    }
+  }
+  g.BN = best_bn;
+  g.n_tiles = best_tiles;
+  return g;
 }
 
 bool gemm_tc_supported(long long M, int N, int K, long long lda) {
-  return M >= 1 && N >= 1 && K >= 16 && (K % 16) == 0 && (lda % 16) == 0 && lda >= K;
+  return M >= 1 && M < (1ll << 31) && N >= 1 && K >= 16 && (K % 16) == 0 && (lda % 16) == 0 && lda >= K;
 }
 
 struct GemmTcState {
   const void* a = nullptr;
   const void* w = nullptr;
-  CUtensorMap tmA, tmB;
+  const void* c = nullptr;
+  CUtensorMap tmA, tmB, tmC;
 };
 
 GemmTcState* gemm_tc_state_new() { return new GemmTcState(); }
 void gemm_tc_state_free(GemmTcState* s) { delete s; }
 
 cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t stream) {
-  const int k_blocks = (a.K + kBK - 1) / kBK;
+  const GemmTcGeometry g = gemm_tc_geometry(a.N, a.K);
   if (st->a != a.a) {
-    if (!encode_2d(&st->tmA, a.a, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)a.lda, kBM)) return cudaErrorInvalidValue;
+    if (!encode_2d(&st->tmA, a.a, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)a.lda, kBM, g.row_bytes))
+      return cudaErrorInvalidValue;
     st->a = a.a;
   }
   if (st->w != a.w) {
-    if (!encode_2d(&st->tmB, a.w, (uint64_t)a.n_tiles * a.BN, (uint64_t)a.Kpad, (uint64_t)a.Kpad, (uint32_t)a.BN))
+    if (!encode_2d(&st->tmB, a.w, (uint64_t)g.n_tiles * g.BN, (uint64_t)g.Kpad, (uint64_t)g.Kpad, (uint32_t)g.BN,
+                   g.row_bytes))
       return cudaErrorInvalidValue;
     st->w = a.w;
   }
+  const bool tma_store = (a.ldc % 16) == 0 && ((uintptr_t)a.out % 16) == 0;
+  if (tma_store && st->c != a.out) {
+    if (!encode_2d_plain(&st->tmC, a.out, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldc, kBM, (uint32_t)g.BN))
+      return cudaErrorInvalidValue;
+    st->c = a.out;
+  }
   GemmTcParams p{};
+  p.tma_store = tma_store;
   p.chan = a.chan;
   p.out = a.out;
   p.ldc = a.ldc;
   p.M = (int)a.M;
   p.N = a.N;
-  p.BN = a.BN;
-  p.n_tiles = a.n_tiles;
+  p.BN = g.BN;
+  p.n_tiles = g.n_tiles;
   p.m_tiles = (int)((a.M + kBM - 1) / kBM);
-  p.k_blocks = k_blocks;
-  p.k_last_steps = ((a.K - (k_blocks - 1) * kBK) + 31) / 32;
+  p.k_blocks = g.k_blocks;
+  p.k_last_steps = ((a.K - (g.k_blocks - 1) * g.row_bytes) + 31) / 32;
+  p.row_bytes = g.row_bytes;
+  const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
+  p.w_resident = w_bytes <= (size_t)kResidentWeightBytes;
+  const size_t stage_bytes = (size_t)kBM * g.row_bytes + (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes);
+  const size_t staging_bytes = tma_store ? (size_t)kEpiGroups * kBM * g.BN : 0;  // one tile per group
+  const size_t ring_budget = (size_t)kSmemBudget - 1024 - (p.w_resident ? w_bytes : 0) - staging_bytes;
+  int stages = (int)(ring_budget / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return cudaErrorInvalidConfiguration;
+  p.stages = stages;
   p.out_zp = a.out_zp;
   p.clamp_min = a.clamp_min;
   p.clamp_max = a.clamp_max;
+  p.rnd_lo = a.rnd_lo;
+  p.dmul = a.dmul;
   int stride = 32;
-  while (stride < a.BN) stride <<= 1;
+  while (stride < g.BN) stride <<= 1;
   p.acc_stride = stride;
-  p.tmem_cols = 2 * stride;
+  p.acc_stages = kEpiGroups;  // BN <= 128, so 4 stages fit the 512 TMEM columns
+  p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
-  const size_t smem = 1024 + (size_t)kStages * (kBM * kBK + (size_t)a.BN * kBK);
-  static size_t smem_set = 0;
-  if (smem > smem_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(197 * 1024));
+  p.staging_off = (uint32_t)((p.w_resident ? w_bytes : 0) + (size_t)stages * stage_bytes);
+  const size_t smem = 1024 + p.staging_off + staging_bytes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(197 * 1024));
+      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return e;
-    smem_set = 197 * 1024;
+    attr_set = true;
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  if (a.hi_shift) gemm_i8_tc_kernel<true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, p);
-  else gemm_i8_tc_kernel<false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, p);
+  if (a.hi33) gemm_i8_tc_kernel<true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  else gemm_i8_tc_kernel<false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   return cudaGetLastError();
 }
 

@@ -33,6 +33,7 @@ struct DwArgs {
   int input_zp, weight_zp, out_zp, clamp_min, clamp_max;
   int double_round;
   int hi_shift;           // every rescale shift of the op is >= 32
+  int hi33, rnd_lo, dmul; // every shift >= 33: compact constants; uniform rounding parts (3x3 fast path)
   const uint32_t* wq;     // 3x3 fast path: weights packed per row for dp4a (see depthwise.cu), else null
 };
 void launch_depthwise(const DwArgs& a, cudaStream_t stream);
@@ -80,23 +81,31 @@ struct RescaleArgs {
 void launch_rescale(const RescaleArgs& a, cudaStream_t stream);
 
 // ---- tensor-core GEMM (gemm_tcgen05.cu) ----
+struct GemmTcGeometry {
+  int row_bytes;  // bytes of K per shared-memory row: 32, 64 or 128
+  int k_blocks;   // K blocks of row_bytes
+  int Kpad;       // k_blocks * row_bytes: row length of the packed weights
+  int BN;         // columns per N tile (multiple of 16, <= 128)
+  int n_tiles;
+};
+GemmTcGeometry gemm_tc_geometry(int N, int K);
 struct GemmTcArgs {
   const int8_t* a;        // [M, K] int8, row pitch lda bytes (multiple of 16)
   long long lda;
-  const int8_t* w;        // packed [n_tiles * BN][Kpad], Kpad a multiple of 128, zero padded
+  const int8_t* w;        // packed [n_tiles * BN][Kpad] per gemm_tc_geometry(N, K), zero padded
   const ChanParams* chan; // [n_tiles * BN]
   int8_t* out;            // [M, N] int8, row pitch ldc bytes
   long long ldc;
   long long M;
-  int N, K, Kpad, BN, n_tiles;
-  int out_zp, clamp_min, clamp_max, double_round;
-  int hi_shift;           // every rescale shift of the op is >= 32
+  int N, K;
+  int out_zp, clamp_min, clamp_max;
+  int hi33;               // every rescale shift >= 33: the 16-byte-constant epilogue applies
+  int rnd_lo, dmul;       // with hi33: low word of the rounding constant, negative-accumulator term
   int* status;            // device status word: a kernel whose bounded wait expires writes a code here
 };
 struct GemmTcState;       // cached tensor maps of one GEMM step
 GemmTcState* gemm_tc_state_new();
 void gemm_tc_state_free(GemmTcState* s);
-void gemm_tc_tiling(int N, int& BN, int& n_tiles);
 bool gemm_tc_supported(long long M, int N, int K, long long lda);
 cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t stream);
 

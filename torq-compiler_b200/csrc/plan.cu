@@ -114,6 +114,8 @@ struct Builder {
     }
     out.resize(OC);
     last_hi_shift = true;
+    last_min_shift = 64;
+    last_max_shift = 0;
     for (int c = 0; c < OC; c++) {
       int i = op.per_channel ? c : 0;
       ChanParams p{};
@@ -134,6 +136,8 @@ struct Builder {
       }
       fill_rounding(p, double_round != 0);
       if (p.shift < 32) last_hi_shift = false;
+      if (p.shift < last_min_shift) last_min_shift = p.shift;
+      if (p.shift > last_max_shift) last_max_shift = p.shift;
       out[c] = p;
     }
     return true;
@@ -141,6 +145,8 @@ struct Builder {
 
   // set by chan_params: every shift of the op is >= 32 (the epilogue's one-word shift applies)
   bool last_hi_shift = true;
+  int last_min_shift = 64;  // smallest effective shift of the op
+  int last_max_shift = 0;   // largest
 
   static void fill_rounding(ChanParams& p, bool double_round) {
     const bool second = double_round && p.shift > 31;
@@ -309,20 +315,32 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           while (K % g16 != 0) g16 >>= 1;  // gcd(K, 16)
           rgroup = 16 / g16;
         }
-        if (pointwise && op.weight_zp == 0 && !force_simt() && rgroup <= 4 && M % rgroup == 0 &&
+        // Short rows make poor TMA boxes (the copy engine works row by row): widen them the same
+        // way while the grouped row stays within one 128-byte swizzle row.
+        {
+          while (rgroup * 2 <= 8 && K * rgroup * 2 <= 128 && M % (rgroup * 2) == 0 && OC * rgroup * 2 <= 512)
+            rgroup *= 2;
+        }
+        if (pointwise && op.weight_zp == 0 && !force_simt() && rgroup <= 8 && M % rgroup == 0 &&
             (long long)OC * rgroup <= 4096 && gemm_tc_supported(M / rgroup, OC * rgroup, (int)K * rgroup, K * rgroup)) {
           GemmTcArgs ga{};
           const int Ng = OC * rgroup, Kg = (int)K * rgroup;
-          gemm_tc_tiling(Ng, ga.BN, ga.n_tiles);
-          ga.M = M / rgroup; ga.N = Ng; ga.K = Kg; ga.Kpad = (Kg + 127) / 128 * 128;
+          const GemmTcGeometry geo = gemm_tc_geometry(Ng, Kg);
+          ga.M = M / rgroup; ga.N = Ng; ga.K = Kg;
           ga.lda = Kg; ga.ldc = Ng;
-          ga.out_zp = op.out_zp; ga.clamp_min = op.clamp_min; ga.clamp_max = op.clamp_max; ga.double_round = dr;
-          ga.hi_shift = b.last_hi_shift;
-          const int rows = ga.n_tiles * ga.BN;
-          std::vector<int8_t> wp((size_t)rows * ga.Kpad, 0);
+          ga.out_zp = op.out_zp; ga.clamp_min = op.clamp_min; ga.clamp_max = op.clamp_max;
+          ga.hi33 = b.last_min_shift >= 33;
+          if (ga.hi33 && b.last_max_shift <= 55) {
+            // (t + (zp << S)) >> S == (t >> S) + zp: the output zero point rides in the rounding constant
+            for (auto& c : cp) c.rnd += (long long)op.out_zp << c.shift;
+            ga.out_zp = 0;
+          }
+          ga.rnd_lo = (int)(cp[0].rnd & 0xffffffffll); ga.dmul = cp[0].dmul;
+          const int rows = geo.n_tiles * geo.BN;
+          std::vector<int8_t> wp((size_t)rows * geo.Kpad, 0);
           for (int j = 0; j < rgroup; j++)
             for (int oc = 0; oc < OC; oc++)
-              memcpy(wp.data() + (size_t)(j * OC + oc) * ga.Kpad + (size_t)j * K, w + (size_t)oc * K, (size_t)K);
+              memcpy(wp.data() + (size_t)(j * OC + oc) * geo.Kpad + (size_t)j * K, w + (size_t)oc * K, (size_t)K);
           {
             std::vector<ChanParams> rep((size_t)Ng);
             for (int j = 0; j < rgroup; j++)
@@ -407,6 +425,11 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         int dr = 0;
         if (!b.chan_params(op, i, OC, fast ? wsum.data() : nullptr, 9, fast, cp, dr)) return b.status;
         a.double_round = dr; a.hi_shift = b.last_hi_shift;
+        a.hi33 = b.last_min_shift >= 33; a.rnd_lo = (int)(cp[0].rnd & 0xffffffffll); a.dmul = cp[0].dmul;
+        if (fast && a.hi33 && b.last_max_shift <= 55) {
+          for (auto& cc : cp) cc.rnd += (long long)op.out_zp << cc.shift;  // zero point rides in the rounding constant
+          a.out_zp = 0;
+        }
         size_t w_off = b.add_const(wd, (size_t)a.KH * a.KW * OC);
         size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
         size_t q_off = 0;
