@@ -173,10 +173,13 @@ __global__ void __launch_bounds__(256) conv2d_simt_kernel(ConvArgs a) {
 }
 
 // Few input channels (IC <= 4, K = KH*KW*IC <= 64), e.g. the 3x3x3 stem of an image
-// network: one thread per output pixel gathers its K patch bytes into KWORDS registers
-// once and runs every output channel against weights broadcast from shared memory.
-// Same arithmetic as conv2d_simt_kernel (izp staged for taps outside the image).
-template <int KWORDS>
+// network: a thread gathers the K patch bytes of kPix output pixels into registers once
+// and runs every output channel against weights broadcast from shared memory, so each
+// weight word read serves kPix pixels. Same arithmetic as conv2d_simt_kernel (izp staged
+// for taps outside the image).
+constexpr int kPix = 2;
+// S333: the 3x3 window over 3 channels, with the tap arithmetic folded at compile time.
+template <int KWORDS, bool S333>
 __global__ void __launch_bounds__(128) conv2d_smallic_kernel(ConvArgs a) {
   extern __shared__ uint32_t w_s[];  // [OC][KWORDS]
   for (int i = threadIdx.x; i < a.OC * KWORDS; i += blockDim.x) {
@@ -185,56 +188,84 @@ __global__ void __launch_bounds__(128) conv2d_smallic_kernel(ConvArgs a) {
   }
   __syncthreads();
   const long long P = (long long)a.N * a.OH * a.OW;
-  const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (p >= P) return;
-  const int ow = (int)(p % a.OW);
-  long long t = p / a.OW;
-  const int oh = (int)(t % a.OH);
-  const int n = (int)(t / a.OH);
-  const int ih0 = oh * a.stride_h - a.pad_t, iw0 = ow * a.stride_w - a.pad_l;
-  const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.IC;
+  // pixel i of this thread: block base + i * 128 + thread, so a warp's stores stay adjacent
+  const long long p_base = (long long)blockIdx.x * (128 * kPix) + threadIdx.x;
   const uint32_t zp_byte = (uint32_t)(a.input_zp & 0xff);
 
-  uint32_t patch[KWORDS];
+  uint32_t patch[kPix][KWORDS];
 #pragma unroll
-  for (int i = 0; i < KWORDS; i++) {
-    uint32_t word = 0;
+  for (int px = 0; px < kPix; px++) {
+    const long long p = p_base + px * 128;
+    const long long pp = p < P ? p : 0;
+    const int ow = (int)(pp % a.OW);
+    long long t = pp / a.OW;
+    const int oh = (int)(t % a.OH);
+    const int n = (int)(t / a.OH);
+    const int ih0 = oh * a.stride_h - a.pad_t, iw0 = ow * a.stride_w - a.pad_l;
+    const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.IC;
 #pragma unroll
-    for (int b = 0; b < 4; b++) {
-      const int k = 4 * i + b;
-      if (k < a.K) {
-        const int tap = k / a.IC, ic = k - tap * a.IC;
-        const int kh = tap / a.KW, kw = tap - kh * a.KW;
-        const int ih = ih0 + kh * a.dil_h, iw = iw0 + kw * a.dil_w;
-        const uint32_t byte = (ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
-                                  ? (uint32_t)(uint8_t)xin[((size_t)ih * a.W + iw) * a.IC + ic]
-                                  : zp_byte;
-        word |= byte << (8 * b);
+    for (int i = 0; i < KWORDS; i++) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        const int k = 4 * i + b;
+        if (S333) {
+          if (k < 27) {
+            constexpr int kdiv3[28] = {0, 0, 0, 1, 1, 1, 2, 2, 2, 3, 3, 3, 4, 4, 4, 5, 5, 5, 6, 6, 6, 7, 7, 7, 8, 8, 8, 9};
+            const int tap = kdiv3[k < 27 ? k : 27], ic = k - tap * 3;
+            const int kh = kdiv3[tap], kw = tap - kh * 3;
+            const int ih = ih0 + kh * a.dil_h, iw = iw0 + kw * a.dil_w;
+            const uint32_t byte = (ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
+                                      ? (uint32_t)(uint8_t)xin[((size_t)ih * a.W + iw) * 3 + ic]
+                                      : zp_byte;
+            word |= byte << (8 * b);
+          }
+        } else if (k < a.K) {
+          const int tap = k / a.IC, ic = k - tap * a.IC;
+          const int kh = tap / a.KW, kw = tap - kh * a.KW;
+          const int ih = ih0 + kh * a.dil_h, iw = iw0 + kw * a.dil_w;
+          const uint32_t byte = (ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
+                                    ? (uint32_t)(uint8_t)xin[((size_t)ih * a.W + iw) * a.IC + ic]
+                                    : zp_byte;
+          word |= byte << (8 * b);
+        }
       }
+      patch[px][i] = word;
     }
-    patch[i] = word;
   }
   const bool hi = a.hi_shift != 0;
-  int8_t* o = a.out + (size_t)p * a.OC;
   for (int oc0 = 0; oc0 < a.OC; oc0 += 4) {
-    int q[4];
+    int q[kPix][4];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int oc = min(oc0 + j, a.OC - 1);
-      int acc = 0;
+      int acc[kPix];
 #pragma unroll
-      for (int i = 0; i < KWORDS; i++) acc = __dp4a((int)patch[i], (int)w_s[oc * KWORDS + i], acc);
+      for (int px = 0; px < kPix; px++) acc[px] = 0;
+#pragma unroll
+      for (int i = 0; i < KWORDS; i++) {
+        const int w = (int)w_s[oc * KWORDS + i];
+#pragma unroll
+        for (int px = 0; px < kPix; px++) acc[px] = __dp4a((int)patch[px][i], w, acc[px]);
+      }
       const ChanParams cp = a.chan[oc];
-      acc += cp.bias;
-      q[j] = hi ? requant_cp<true>(acc, cp, a.out_zp, a.clamp_min, a.clamp_max)
-                : requant_cp<false>(acc, cp, a.out_zp, a.clamp_min, a.clamp_max);
-    }
-    if ((a.OC & 3) == 0) {
-      *reinterpret_cast<uint32_t*>(o + oc0) = pack4(q[0], q[1], q[2], q[3]);
-    } else {
 #pragma unroll
-      for (int j = 0; j < 4; j++)
-        if (oc0 + j < a.OC) o[oc0 + j] = (int8_t)q[j];
+      for (int px = 0; px < kPix; px++)
+        q[px][j] = hi ? requant_cp<true>(acc[px] + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max)
+                      : requant_cp<false>(acc[px] + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max);
+    }
+#pragma unroll
+    for (int px = 0; px < kPix; px++) {
+      const long long p = p_base + px * 128;
+      if (p >= P) continue;
+      int8_t* o = a.out + (size_t)p * a.OC;
+      if ((a.OC & 3) == 0) {
+        *reinterpret_cast<uint32_t*>(o + oc0) = pack4(q[px][0], q[px][1], q[px][2], q[px][3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (oc0 + j < a.OC) o[oc0 + j] = (int8_t)q[px][j];
+      }
     }
   }
 }
@@ -262,12 +293,14 @@ const char* conv2d_simt_kernel_name(const ConvArgs& a) {
 void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
   long long P = (long long)a.N * a.OH * a.OW;
   if (a.IC <= 4 && a.K <= 64 && a.OC <= 256 && a.weight_zp == 0) {
-    const unsigned blocks = (unsigned)((P + 127) / 128);
+    const unsigned blocks = (unsigned)((P + 128 * kPix - 1) / (128 * kPix));
     const int kwords = (a.K + 3) / 4;
-    if (kwords <= 3) conv2d_smallic_kernel<3><<<blocks, 128, (size_t)a.OC * 3 * 4, stream>>>(a);
-    else if (kwords <= 7) conv2d_smallic_kernel<7><<<blocks, 128, (size_t)a.OC * 7 * 4, stream>>>(a);
-    else if (kwords <= 9) conv2d_smallic_kernel<9><<<blocks, 128, (size_t)a.OC * 9 * 4, stream>>>(a);
-    else conv2d_smallic_kernel<16><<<blocks, 128, (size_t)a.OC * 16 * 4, stream>>>(a);
+    if (a.IC == 3 && a.KH == 3 && a.KW == 3)
+      conv2d_smallic_kernel<7, true><<<blocks, 128, (size_t)a.OC * 7 * 4, stream>>>(a);
+    else if (kwords <= 3) conv2d_smallic_kernel<3, false><<<blocks, 128, (size_t)a.OC * 3 * 4, stream>>>(a);
+    else if (kwords <= 7) conv2d_smallic_kernel<7, false><<<blocks, 128, (size_t)a.OC * 7 * 4, stream>>>(a);
+    else if (kwords <= 9) conv2d_smallic_kernel<9, false><<<blocks, 128, (size_t)a.OC * 9 * 4, stream>>>(a);
+    else conv2d_smallic_kernel<16, false><<<blocks, 128, (size_t)a.OC * 16 * 4, stream>>>(a);
     return;
   }
   dim3 grid((unsigned)((P + BM - 1) / BM), (unsigned)((a.OC + BN - 1) / BN));
