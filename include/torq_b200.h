@@ -127,6 +127,13 @@ int tb200_wait(tb200_device_t* device, uint64_t timeout_ns);
  * output, wait. Host pointers may be pageable or pinned. */
 int tb200_invoke_host(tb200_executable_t* executable, const void* const* host_inputs,
                       void* const* host_outputs);
+/* The same call without the final wait (the deferred command buffer + queue_execute form of
+ * the reference, runtime/driver/torq_device.c:393-442,487-526): uploads go to a second
+ * stream into one of two staging sets, so the upload of call k+1 overlaps the kernels of
+ * call k. Host input memory must stay valid, and host output memory is defined, only after
+ * tb200_wait() returns; pinned host memory is needed for the overlap. */
+int tb200_invoke_host_async(tb200_executable_t* executable, const void* const* host_inputs,
+                            void* const* host_outputs);
 
 /* Per-op device time of one dispatch (CUDA events around each op, averaged over
  * `iters` runs after `warmup`); ms[op_count]. Profiling aid; role of the per-action

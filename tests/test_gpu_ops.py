@@ -247,3 +247,24 @@ def test_pointwise_conv_tensor_core_sweep(device, M, K, N):
     finally:
         del os.environ["TB200_FORCE_SIMT"]
     assert (simt == got).all()
+
+
+def test_pipelined_host_calls(device):
+    """tb200_invoke_host_async: three calls in flight over the two staging sets, one wait at the end."""
+    from torq_b200.runtime import Executable
+    rng = np.random.default_rng(1234)
+    shape = (4, 28, 28, 32)
+    g = Graph()
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, 64) * 40.0 / (np.sqrt(32) * 74 * 74))
+    y = g.conv2d(g.input(shape), rng.integers(-127, 128, (64, 1, 1, 32), dtype=np.int8),
+                 np.round(rng.normal(0, 1000, 64)).astype(np.int32), m, s, input_zp=3, out_zp=-1)
+    g.output(y)
+    xs = [rng.integers(-128, 128, shape, dtype=np.int8) for _ in range(3)]
+    outs = [np.zeros((4, 28, 28, 64), np.int8) for _ in range(3)]
+    ex = Executable(device, g.serialize())
+    for x, o in zip(xs, outs):
+        ex.invoke_host_async([x], [o])
+    device.wait()
+    for x, o in zip(xs, outs):
+        assert (o == run_graph(g, [x])[0]).all()
+    ex.destroy()

@@ -51,6 +51,20 @@ __device__ __forceinline__ int32_t requant_cp(int32_t acc, const ChanParams& cp,
   return max(cmin, min(cmax, r));
 }
 
+// 64-bit value from two 32-bit registers without any instruction (register pairing).
+__device__ __forceinline__ long long make_i64(int32_t hi, int32_t lo) {
+  return __double_as_longlong(__hiloint2double(hi, lo));
+}
+
+// Compact form of the rescale for ops whose shifts are all >= 33: c = {bias, mult, high word
+// of rnd, shift - 32}; rnd_lo and dmul are the same for every channel of the op.
+__device__ __forceinline__ int32_t scale_hi33(int32_t acc, int32_t mult, int32_t rnd_hi, int32_t hshift,
+                                              int32_t rnd_lo, int32_t dmul) {
+  long long t = (long long)acc * (long long)mult + make_i64(rnd_hi, rnd_lo);
+  t += (long long)(int32_t)((uint32_t)acc >> 31) * (long long)dmul;
+  return (int32_t)(t >> 32) >> hshift;
+}
+
 // apply_scale_32 part of requant_cp (no zero point, no clamp).
 template <bool HI>
 __device__ __forceinline__ int32_t scale_cp(int32_t acc, const ChanParams& cp) {

@@ -8,7 +8,9 @@
 //    transposes the 4x4 byte block with PRMT so that a register holds one channel's
 //    horizontal taps, and feeds dp4a with weights packed (w0,w1,w2,0) / (0,w0,w1,w2):
 //    one transposed register serves two adjacent outputs. Rows roll through a 3-row
-//    register window, so every input row is loaded and transposed once per strip.
+//    register window (fully unrolled, so the roll is register renaming); all rows of a strip
+//    are requested up front with cp.async into per-thread shared-memory slots, so every
+//    input row is loaded and transposed once per strip with its latency hidden.
 //    Taps outside the image are staged as izp, i.e. (izp - izp) * w = 0, and
 //    -izp * sum(w) sits folded in ChanParams::bias.
 //  * depthwise_generic_kernel: any window, stride, dilation, channel multiplier and
@@ -31,9 +33,24 @@ __device__ __forceinline__ void transpose4x4(uint32_t p0, uint32_t p1, uint32_t 
   t[3] = __byte_perm(b, d, 0x7632);
 }
 
+// cp.async.wait_group takes an immediate; in the unrolled loops the argument is a constant
+// and the switch folds to a single instruction.
+__device__ __forceinline__ void cp_async_wait(int n) {
+  switch (n) {
+#define TB200_CASE(N) case N: asm volatile("cp.async.wait_group " #N ";" ::: "memory"); break;
+    TB200_CASE(0) TB200_CASE(1) TB200_CASE(2) TB200_CASE(3) TB200_CASE(4) TB200_CASE(5) TB200_CASE(6)
+    TB200_CASE(7) TB200_CASE(8) TB200_CASE(9) TB200_CASE(10) TB200_CASE(11) TB200_CASE(12) TB200_CASE(13)
+    TB200_CASE(14) TB200_CASE(15) TB200_CASE(16)
+#undef TB200_CASE
+    default: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+  }
+}
+
 // HI33: every rescale shift of the op is >= 33 (compact constants, see gemm_tcgen05.cu).
+// All addressing is 32-bit element offsets from the tensor bases (the launcher checks that
+// both tensors are below 2 GiB), so a load costs one add and a predicated LDG.
 template <int STRIDE, bool HI33>
-__global__ void __launch_bounds__(128, 5) dw3x3_kernel(DwArgs a) {
+__global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
   constexpr int TW = STRIDE == 1 ? 2 : 1;    // outputs per thread along W
   constexpr int NCOL = STRIDE == 1 ? 4 : 3;  // input columns per row load
   const int groups = a.C >> 2;
@@ -52,11 +69,13 @@ __global__ void __launch_bounds__(128, 5) dw3x3_kernel(DwArgs a) {
   const int ow0 = j * TW;
   const int iw0 = ow0 * STRIDE - a.pad_l;
   const int oh_begin = rb * kRows;
-  const int oh_end = min(a.OH, oh_begin + kRows);
-  const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.C + c;
+  const int n_rows = min(a.OH - oh_begin, kRows);
   const uint32_t zpw = (uint32_t)(a.input_zp & 0xff) * 0x01010101u;
   const uint32_t lo2 = (uint32_t)(a.clamp_min & 0xffff) * 0x10001u;
   const uint32_t hi2 = (uint32_t)(a.clamp_max & 0xffff) * 0x10001u;
+  const uint32_t* __restrict__ x32 = reinterpret_cast<const uint32_t*>(a.x);
+  uint32_t* __restrict__ o32 = reinterpret_cast<uint32_t*>(a.out);
+  const int Cw = a.C >> 2;  // words per pixel
 
   // weights: [3 rows][TW variants][C] words, this thread's 4 channels
   uint32_t wq[3][TW][4];
@@ -77,78 +96,82 @@ __global__ void __launch_bounds__(128, 5) dw3x3_kernel(DwArgs a) {
     else cp[k] = t;
   }
 
-  // raw pixel words of one input row (izp for anything outside the image)
-  auto fetch_row = [&](int ih, uint32_t (&p)[4]) {
-    const bool row_in = ih >= 0 && ih < a.H;
-    const int8_t* row = xin + (size_t)(row_in ? ih : 0) * a.W * a.C;
+  // column word offsets and validity of the NCOL input columns this strip touches
+  int col_off[4];
+  bool col_ok[4];
 #pragma unroll
-    for (int k = 0; k < 4; k++) {
-      const int iw = iw0 + k;
-      p[k] = (k < NCOL && row_in && iw >= 0 && iw < a.W) ? *reinterpret_cast<const uint32_t*>(row + (size_t)iw * a.C) : zpw;
-    }
-  };
-
-  uint32_t win[3][4];
-  uint32_t pend[2][4];  // rows fetched ahead of their use (1 for stride 1, 2 for stride 2)
-  {
-    uint32_t p[4];
-    if (STRIDE == 1) {
-      fetch_row(oh_begin - a.pad_t, p);
-      transpose4x4(p[0], p[1], p[2], p[3], win[0]);
-      fetch_row(oh_begin - a.pad_t + 1, p);
-      transpose4x4(p[0], p[1], p[2], p[3], win[1]);
-      fetch_row(oh_begin - a.pad_t + 2, pend[0]);
-    } else {
-      fetch_row(oh_begin * 2 - a.pad_t, p);
-      transpose4x4(p[0], p[1], p[2], p[3], win[0]);
-      fetch_row(oh_begin * 2 - a.pad_t + 1, pend[0]);
-      fetch_row(oh_begin * 2 - a.pad_t + 2, pend[1]);
-    }
+  for (int k = 0; k < 4; k++) {
+    const int iw = iw0 + k;
+    col_ok[k] = k < NCOL && iw >= 0 && iw < a.W;
+    col_off[k] = iw * Cw + g;
   }
-  for (int oh = oh_begin; oh < oh_end; oh++) {
-    const int ih0 = oh * STRIDE - a.pad_t;
-    // consume the rows fetched during the previous iteration, then fetch the next ones
-    if (STRIDE == 1) {
-      transpose4x4(pend[0][0], pend[0][1], pend[0][2], pend[0][3], win[2]);
-      if (oh + 1 < oh_end) fetch_row(ih0 + 3, pend[0]);
-    } else {
-      transpose4x4(pend[0][0], pend[0][1], pend[0][2], pend[0][3], win[1]);
-      transpose4x4(pend[1][0], pend[1][1], pend[1][2], pend[1][3], win[2]);
-      if (oh + 1 < oh_end) {
-        fetch_row(ih0 + 3, pend[0]);
-        fetch_row(ih0 + 4, pend[1]);
+  const int img_off = n * a.H * a.W * Cw;  // word offset of image n
+  const int row_words = a.W * Cw;
+
+  // The strip's input rows R[0..NR): output row r reads R[S*r], R[S*r+1], R[S*r+2]. Every row
+  // is requested up front with cp.async into this thread's own shared-memory slots (one
+  // commit group per row), so all of a strip's bytes are in flight at once; the loop over
+  // output rows is fully unrolled and waits for just the rows it needs.
+  constexpr int NR = (kRows - 1) * STRIDE + 3;
+  extern __shared__ uint32_t stage[];  // [NR][4][128]
+  const uint32_t stage_addr = (uint32_t)__cvta_generic_to_shared(stage) + threadIdx.x * 4;
+  const int ih_base = oh_begin * STRIDE - a.pad_t;
+  const int nr_live = (n_rows - 1) * STRIDE + 3;  // rows this strip really needs
+#pragma unroll
+  for (int i = 0; i < NR; i++) {
+    const int ih = ih_base + i;
+    const bool row_in = i < nr_live && ih >= 0 && ih < a.H;
+    const int roff = img_off + ih * row_words;
+#pragma unroll
+    for (int k = 0; k < NCOL; k++) {
+      if (row_in && col_ok[k]) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(stage_addr + (i * 4 + k) * 512),
+                     "l"(x32 + (uint32_t)(roff + col_off[k]))
+                     : "memory");
+      } else {
+        stage[(i * 4 + k) * 128 + threadIdx.x] = zpw;
       }
     }
-    int8_t* orow = a.out + (((size_t)n * a.OH + oh) * a.OW + ow0) * a.C + c;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  auto take_row = [&](int i, uint32_t (&t)[4]) {
+    const uint32_t p0 = stage[(i * 4 + 0) * 128 + threadIdx.x], p1 = stage[(i * 4 + 1) * 128 + threadIdx.x],
+                   p2 = stage[(i * 4 + 2) * 128 + threadIdx.x];
+    const uint32_t p3 = NCOL == 4 ? stage[(i * 4 + 3) * 128 + threadIdx.x] : zpw;
+    transpose4x4(p0, p1, p2, p3, t);
+  };
+  uint32_t win[NR][4];
+  int out_off = ((n * a.OH + oh_begin) * a.OW + ow0) * Cw + g;  // word offset of the first output
+  const int out_row_words = a.OW * Cw;
+  const bool second = TW == 2 && ow0 + 1 < a.OW;
 #pragma unroll
-    for (int v = 0; v < TW; v++) {
-      if (ow0 + v >= a.OW) break;
-      int q[4];
+  for (int r = 0; r < kRows; r++) {
+    if (r < n_rows) {
+      // wait for this output row's newest input row (groups complete in order), then transpose
+      cp_async_wait(NR - 1 - (STRIDE * r + 2));
+      if (r == 0) {
+        take_row(0, win[0]);
+        take_row(1, win[1]);
+        take_row(2, win[2]);
+      } else {
 #pragma unroll
-      for (int k = 0; k < 4; k++) {
-        int acc = HI33 ? cq[k].x : cp[k].bias;
+        for (int i = 0; i < STRIDE; i++) take_row(STRIDE * r + 2 - i, win[STRIDE * r + 2 - i]);
+      }
 #pragma unroll
-        for (int kh = 0; kh < 3; kh++) acc = __dp4a((int)win[kh][k], (int)wq[kh][v][k], acc);
-        if (HI33) {
-          long long tt = (long long)acc * (long long)cq[k].y + (((long long)cq[k].z << 32) | (long long)(uint32_t)a.rnd_lo);
-          tt += (long long)(int32_t)((uint32_t)acc >> 31) * (long long)a.dmul;
-          q[k] = ((int32_t)(tt >> 32) >> cq[k].w) + a.out_zp;
-        } else {
-          q[k] = scale_cp<false>(acc, cp[k]) + a.out_zp;
+      for (int v = 0; v < TW; v++) {
+        int q[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          int acc = HI33 ? cq[k].x : cp[k].bias;
+#pragma unroll
+          for (int kh = 0; kh < 3; kh++) acc = __dp4a((int)win[STRIDE * r + kh][k], (int)wq[kh][v][k], acc);
+          if (HI33) q[k] = scale_hi33(acc, cq[k].y, cq[k].z, cq[k].w, a.rnd_lo, a.dmul) + a.out_zp;
+          else q[k] = scale_cp<false>(acc, cp[k]) + a.out_zp;
         }
+        const uint32_t word = clamp_pack4(q[0], q[1], q[2], q[3], lo2, hi2);
+        if (v == 0 || second) o32[(uint32_t)(out_off + v * Cw)] = word;
       }
-      *reinterpret_cast<uint32_t*>(orow + (size_t)v * a.C) = clamp_pack4(q[0], q[1], q[2], q[3], lo2, hi2);
-    }
-    // roll the window
-    if (STRIDE == 1) {
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        win[0][k] = win[1][k];
-        win[1][k] = win[2][k];
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; k++) win[0][k] = win[2][k];
+      out_off += out_row_words;
     }
   }
 }
@@ -220,6 +243,8 @@ __global__ void __launch_bounds__(256) depthwise_generic_kernel(DwArgs a) {
 }  // namespace
 
 bool depthwise3x3_supported(const DwArgs& a) {
+  const long long in_bytes = (long long)a.N * a.H * a.W * a.C, out_bytes = (long long)a.N * a.OH * a.OW * a.C;
+  if (in_bytes >= (1ll << 31) || out_bytes >= (1ll << 31)) return false;  // 32-bit offsets inside the kernel
   return a.KH == 3 && a.KW == 3 && a.M == 1 && (a.C & 3) == 0 && a.dil_h == 1 && a.dil_w == 1 &&
          a.stride_h == a.stride_w && (a.stride_h == 1 || a.stride_h == 2) && a.weight_zp == 0;
 }
@@ -241,12 +266,13 @@ void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
     const int tw = a.stride_h == 1 ? 2 : 1;
     long long total = (long long)a.N * ((a.OH + kRows - 1) / kRows) * ((a.OW + tw - 1) / tw) * (a.C >> 2);
     unsigned blocks = (unsigned)((total + 127) / 128);
+    const size_t smem1 = (size_t)((kRows - 1) * 1 + 3) * 4 * 128 * 4, smem2 = (size_t)((kRows - 1) * 2 + 3) * 4 * 128 * 4;
     if (a.stride_h == 1) {
-      if (a.hi33) dw3x3_kernel<1, true><<<blocks, 128, 0, stream>>>(a);
-      else dw3x3_kernel<1, false><<<blocks, 128, 0, stream>>>(a);
+      if (a.hi33) dw3x3_kernel<1, true><<<blocks, 128, smem1, stream>>>(a);
+      else dw3x3_kernel<1, false><<<blocks, 128, smem1, stream>>>(a);
     } else {
-      if (a.hi33) dw3x3_kernel<2, true><<<blocks, 128, 0, stream>>>(a);
-      else dw3x3_kernel<2, false><<<blocks, 128, 0, stream>>>(a);
+      if (a.hi33) dw3x3_kernel<2, true><<<blocks, 128, smem2, stream>>>(a);
+      else dw3x3_kernel<2, false><<<blocks, 128, smem2, stream>>>(a);
     }
   } else if (a.M == 1 && (a.C & 3) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C >> 2);

@@ -366,10 +366,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int j = 0; j < 4; j++) {
               if (HI33) {
                 const int4 c = cps[c0 + g * 4 + j];
-                const int acc = (int)v[g * 4 + j] + c.x;
-                long long tt = (long long)acc * (long long)c.y + (((long long)c.z << 32) | (long long)(uint32_t)p.rnd_lo);
-                tt += (long long)(int32_t)((uint32_t)acc >> 31) * (long long)p.dmul;
-                r[j] = ((int32_t)(tt >> 32) >> c.w) + p.out_zp;
+                r[j] = scale_hi33((int)v[g * 4 + j] + c.x, c.y, c.z, c.w, p.rnd_lo, p.dmul) + p.out_zp;
               } else {
                 const ChanParams c = chan_n[c0 + g * 4 + j];
                 r[j] = scale_cp<false>((int)v[g * 4 + j] + c.bias, c) + p.out_zp;

@@ -26,6 +26,7 @@ using namespace tb200;
 struct tb200_device {
   int ordinal = 0;
   cudaStream_t stream = nullptr;
+  cudaStream_t copy_stream = nullptr;  // host-to-device uploads of the pipelined host call
   std::string last_error;
   std::mutex submit_mutex;  // one submission at a time, like the reference's
                             // per-executable mutex (TorqExecutable.cc:1043-1045)
@@ -111,6 +112,11 @@ extern "C" int tb200_device_create(int ordinal, tb200_device_t** out) {
     delete d;
     return TB200_INTERNAL;
   }
+  if (cudaStreamCreateWithFlags(&d->copy_stream, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaStreamDestroy(d->stream);
+    delete d;
+    return TB200_INTERNAL;
+  }
   if (cudaMalloc(&d->status_word, sizeof(int)) != cudaSuccess || cudaMemset(d->status_word, 0, sizeof(int)) != cudaSuccess) {
     cudaStreamDestroy(d->stream);
     delete d;
@@ -124,6 +130,8 @@ extern "C" int tb200_device_destroy(tb200_device_t* d) {
   if (!d) return TB200_INVALID_ARGUMENT;
   cudaSetDevice(d->ordinal);
   cudaStreamSynchronize(d->stream);
+  cudaStreamSynchronize(d->copy_stream);
+  cudaStreamDestroy(d->copy_stream);
   cudaStreamDestroy(d->stream);
   cudaFree(d->status_word);
   if (d->profile_csv) fclose(d->profile_csv);
@@ -246,7 +254,11 @@ struct tb200_executable {
   Plan plan;                       // launch list + arena layout (plan.h)
   void* arena = nullptr;
   void* const_dev = nullptr;       // derived constants (packed weights, channel params)
-  std::vector<tb200_buffer_t*> staging_in, staging_out;  // for tb200_invoke_host
+  // tb200_invoke_host[_async]: two sets of device staging buffers, used alternately, so the
+  // upload of one call overlaps the kernels of the previous one
+  std::vector<tb200_buffer_t*> staging_in[2], staging_out[2];
+  cudaEvent_t ev_uploaded[2] = {nullptr, nullptr}, ev_released[2] = {nullptr, nullptr};
+  uint64_t host_calls = 0;
   // CUDA graphs of the whole launch list, one per distinct set of bound addresses
   // (a dispatch with the same bindings replays its graph: one submission instead of
   // one per kernel). Small LRU; TB200_NO_GRAPH=1 turns it off.
@@ -358,8 +370,13 @@ extern "C" int tb200_executable_destroy(tb200_executable_t* ex) {
   cudaSetDevice(ex->dev->ordinal);
   cudaStreamSynchronize(ex->dev->stream);
   for (auto& g : ex->graphs) cudaGraphExecDestroy(g.exec);
-  for (auto* b : ex->staging_in) tb200_buffer_free(b);
-  for (auto* b : ex->staging_out) tb200_buffer_free(b);
+  cudaStreamSynchronize(ex->dev->copy_stream);
+  for (int s = 0; s < 2; s++) {
+    for (auto* b : ex->staging_in[s]) tb200_buffer_free(b);
+    for (auto* b : ex->staging_out[s]) tb200_buffer_free(b);
+    if (ex->ev_uploaded[s]) cudaEventDestroy(ex->ev_uploaded[s]);
+    if (ex->ev_released[s]) cudaEventDestroy(ex->ev_released[s]);
+  }
   if (ex->arena) cudaFree(ex->arena);
   if (ex->const_dev) cudaFree(ex->const_dev);
   delete ex;
@@ -555,42 +572,63 @@ extern "C" int tb200_wait(tb200_device_t* d, uint64_t timeout_ns) {
   }
 }
 
-extern "C" int tb200_invoke_host(tb200_executable_t* ex, const void* const* host_inputs,
-                                 void* const* host_outputs) {
+extern "C" int tb200_invoke_host_async(tb200_executable_t* ex, const void* const* host_inputs,
+                                       void* const* host_outputs) {
   if (!ex || (!host_inputs && !ex->inputs.empty()) || (!host_outputs && !ex->outputs.empty()))
     return TB200_INVALID_ARGUMENT;
   tb200_device* d = ex->dev;
-  size_t ni = ex->inputs.size(), no = ex->outputs.size();
-  if (ex->staging_in.empty() && ex->staging_out.empty()) {
-    for (size_t i = 0; i < ni; i++) {
-      tb200_buffer_t* b = nullptr;
-      int st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->inputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
-      if (st != TB200_OK) return st;
-      ex->staging_in.push_back(b);
-    }
-    for (size_t i = 0; i < no; i++) {
-      tb200_buffer_t* b = nullptr;
-      int st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->outputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
-      if (st != TB200_OK) return st;
-      ex->staging_out.push_back(b);
+  cudaSetDevice(d->ordinal);
+  const size_t ni = ex->inputs.size(), no = ex->outputs.size();
+  if (!ex->ev_uploaded[0]) {
+    for (int s = 0; s < 2; s++) {
+      for (size_t i = 0; i < ni; i++) {
+        tb200_buffer_t* b = nullptr;
+        int st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->inputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
+        if (st != TB200_OK) return st;
+        ex->staging_in[s].push_back(b);
+      }
+      for (size_t i = 0; i < no; i++) {
+        tb200_buffer_t* b = nullptr;
+        int st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->outputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
+        if (st != TB200_OK) return st;
+        ex->staging_out[s].push_back(b);
+      }
+      CUDA_OK(d, cudaEventCreateWithFlags(&ex->ev_released[s], cudaEventDisableTiming));
+      CUDA_OK(d, cudaEventCreateWithFlags(&ex->ev_uploaded[s], cudaEventDisableTiming));
     }
   }
-  std::vector<tb200_binding_t> bind(ni + no);
-  for (size_t i = 0; i < ni; i++) {
+  for (size_t i = 0; i < ni; i++)
     if (!host_inputs[i]) return fail(d, TB200_INVALID_ARGUMENT, "host input %zu is NULL", i);
-    int st = tb200_buffer_upload(ex->staging_in[i], 0, host_inputs[i], ex->staging_in[i]->bytes);
-    if (st != TB200_OK) return st;
-    bind[i] = {ex->staging_in[i], 0, 0};
-  }
-  for (size_t i = 0; i < no; i++) bind[ni + i] = {ex->staging_out[i], 0, 0};
+  for (size_t i = 0; i < no; i++)
+    if (!host_outputs[i]) return fail(d, TB200_INVALID_ARGUMENT, "host output %zu is NULL", i);
+  const int s = (int)(ex->host_calls & 1);
+  const bool reused = ex->host_calls >= 2;
+  ex->host_calls++;
+  // upload stream: wait until the call two back has released this staging set, then copy in
+  if (reused) CUDA_OK(d, cudaStreamWaitEvent(d->copy_stream, ex->ev_released[s], 0));
+  for (size_t i = 0; i < ni; i++)
+    CUDA_OK(d, cudaMemcpyAsync(ex->staging_in[s][i]->ptr, host_inputs[i], ex->staging_in[s][i]->bytes,
+                               cudaMemcpyHostToDevice, d->copy_stream));
+  CUDA_OK(d, cudaEventRecord(ex->ev_uploaded[s], d->copy_stream));
+  // compute stream: wait for the upload, run, copy the results out, release the set
+  CUDA_OK(d, cudaStreamWaitEvent(d->stream, ex->ev_uploaded[s], 0));
+  std::vector<tb200_binding_t> bind(ni + no);
+  for (size_t i = 0; i < ni; i++) bind[i] = {ex->staging_in[s][i], 0, 0};
+  for (size_t i = 0; i < no; i++) bind[ni + i] = {ex->staging_out[s][i], 0, 0};
   int st = tb200_dispatch(ex, bind.data(), bind.size());
   if (st != TB200_OK) return st;
-  for (size_t i = 0; i < no; i++) {
-    if (!host_outputs[i]) return fail(d, TB200_INVALID_ARGUMENT, "host output %zu is NULL", i);
-    st = tb200_buffer_download(ex->staging_out[i], 0, host_outputs[i], ex->staging_out[i]->bytes);
-    if (st != TB200_OK) return st;
-  }
-  CUDA_OK(d, cudaStreamSynchronize(d->stream));
+  for (size_t i = 0; i < no; i++)
+    CUDA_OK(d, cudaMemcpyAsync(host_outputs[i], ex->staging_out[s][i]->ptr, ex->staging_out[s][i]->bytes,
+                               cudaMemcpyDeviceToHost, d->stream));
+  CUDA_OK(d, cudaEventRecord(ex->ev_released[s], d->stream));
+  return TB200_OK;
+}
+
+extern "C" int tb200_invoke_host(tb200_executable_t* ex, const void* const* host_inputs,
+                                 void* const* host_outputs) {
+  int st = tb200_invoke_host_async(ex, host_inputs, host_outputs);
+  if (st != TB200_OK) return st;
+  CUDA_OK(ex->dev, cudaStreamSynchronize(ex->dev->stream));
   return TB200_OK;
 }
 

@@ -71,6 +71,7 @@ _SIGNATURES = {
     "tb200_dispatch": (C.c_int, [C.c_void_p, C.POINTER(Binding), C.c_size_t]),
     "tb200_wait": (C.c_int, [C.c_void_p, C.c_uint64]),
     "tb200_invoke_host": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "tb200_invoke_host_async": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "tb200_executable_profile_ops": (C.c_int, [C.c_void_p, C.POINTER(Binding), C.c_size_t, C.c_int, C.c_int,
                                                C.POINTER(C.c_float), C.c_uint32]),
 }
@@ -235,6 +236,13 @@ class Executable:
         ins = (C.c_void_p * len(host_inputs))(*[a.ctypes.data for a in host_inputs])
         outs = (C.c_void_p * len(host_outputs))(*[a.ctypes.data for a in host_outputs])
         self.device._check(self.device._lib.tb200_invoke_host(self._h, ins, outs))
+
+    def invoke_host_async(self, host_inputs: Sequence[np.ndarray], host_outputs: Sequence[np.ndarray]):
+        """As invoke_host without the final wait: the upload overlaps the previous call's kernels.
+        Arrays must stay alive (and outputs are defined) only after Device.wait()."""
+        ins = (C.c_void_p * len(host_inputs))(*[a.ctypes.data for a in host_inputs])
+        outs = (C.c_void_p * len(host_outputs))(*[a.ctypes.data for a in host_outputs])
+        self.device._check(self.device._lib.tb200_invoke_host_async(self._h, ins, outs))
 
     def profile_ops(self, inputs: Sequence[Buffer], outputs: Sequence[Buffer], warmup=1, iters=3) -> np.ndarray:
         bufs = list(inputs) + list(outputs)
