@@ -85,6 +85,7 @@ def cpu_oracle_throughput(batch_sample: int, repeats: int):
     from oracle import oracle as oc
     from oracle_exec import run_graph
     from torq_b200.workloads.mobilenet_v2 import build_mobilenet_v2, synthetic_images
+    oc.set_num_threads(len(os.sched_getaffinity(0)))  # torchrun pins OMP_NUM_THREADS=1; use every host core
     g, _ = build_mobilenet_v2(batch_sample)
     x = synthetic_images(batch_sample)
     run_graph(g, [x])  # warm-up
@@ -106,6 +107,7 @@ def run_reference(args, rank, world):
     from oracle import oracle as oc
     from oracle_exec import run_graph
     from torq_b200.workloads.mobilenet_v2 import build_mobilenet_v2, synthetic_images
+    oc.set_num_threads(len(os.sched_getaffinity(0)))  # torchrun pins OMP_NUM_THREADS=1; use every host core
     g, _ = build_mobilenet_v2(sample)
     x = synthetic_images(sample)
     for _ in range(args.warmup):
@@ -221,6 +223,8 @@ def main():
 
     if rank != 0:
         barrier()
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     # ---- roofline of the dominant kernel class (live CUDA-event timing per op) ----
@@ -278,6 +282,8 @@ def main():
     }
     print(json.dumps(line), flush=True)
     barrier()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
