@@ -97,6 +97,60 @@ def cpu_oracle_throughput(batch_sample: int, repeats: int):
     return batch_sample / float(np.median(times)), oc.num_threads(), times
 
 
+def decoder_bench(dev, stream, batch: int, prompt_len: int = 1024, gen_len: int = 128):
+    """Gemma-3-1B-architecture int8-weight greedy decode (second metric of the benchmark set):
+    tokens/s over `gen_len` decode steps after a `prompt_len`-token seeded prompt, one GPU.
+    Every step is one dispatch (CUDA-graph replay); the next token and position move on the device."""
+    import torch
+    from torq_b200.runtime import MEMORY_HOST_PINNED, Executable
+    from torq_b200.workloads import gemma3
+    cfg = gemma3.GemmaConfig()
+    params = gemma3.random_weights(cfg, 1234)
+    g = gemma3.build_decode_step(cfg, batch, params)
+    ex = Executable(dev, g.serialize())
+    del params, g
+    rng = np.random.default_rng(1234)
+    prompt = rng.integers(0, cfg.vocab, (prompt_len, batch)).astype(np.int32)
+    steps = prompt_len + gen_len
+    h_tok = dev.alloc(prompt.nbytes, MEMORY_HOST_PINNED)
+    h_tok.as_numpy(prompt.shape, np.int32)[...] = prompt
+    h_pos = dev.alloc(steps * 4, MEMORY_HOST_PINNED)
+    h_pos.as_numpy((steps,), np.int32)[...] = np.arange(steps, dtype=np.int32)
+    d_tok, d_pos, d_next = dev.alloc(batch * 4), dev.alloc(4), dev.alloc(batch * 4)
+    lib = dev._lib
+    import ctypes as C
+
+    def step(pos, from_prompt):
+        src = h_tok.pointer + pos * batch * 4 if from_prompt else d_next.pointer
+        dev._check(lib.tb200_buffer_upload(d_tok._h, 0, C.c_void_p(src), batch * 4))
+        dev._check(lib.tb200_buffer_upload(d_pos._h, 0, C.c_void_p(h_pos.pointer + pos * 4), 4))
+        ex.dispatch([d_tok, d_pos], [d_next])
+
+    for pos in range(prompt_len):
+        step(pos, True)
+    dev.wait(300.0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for pos in range(prompt_len, steps):
+        step(pos, False)
+    e1.record(stream)
+    dev.wait(300.0)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    last = d_next.download((batch,), np.int32)
+    wbytes = gemma3.weight_bytes_per_token(cfg)
+    kv_bytes = sum(2 * min(steps, cfg.max_seq if cfg.is_global(l) else cfg.window) * cfg.head_dim * 2 for l in range(cfg.layers)) * batch
+    launches = ex.launch_count
+    ex.destroy()
+    for b in (h_tok, h_pos, d_tok, d_pos, d_next):
+        b.free()
+    step_ms = ms / gen_len
+    return {"batch": batch, "tok_per_s": batch * gen_len / (ms * 1e-3), "ms_per_step": step_ms,
+            "weight_bytes_per_step": wbytes, "kv_bytes_per_step": kv_bytes,
+            "hbm_gbs": (wbytes + kv_bytes) / (step_ms * 1e-3) / 1e9, "launches_per_step": launches,
+            "last_tokens": [int(t) for t in last[:4]]}
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's host arithmetic (CPU oracle port; IREE's llvm-cpu
     path cannot be built here) on all host threads, same metric and config."""
@@ -139,6 +193,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layer-table", default=None, help="write per-layer kernel, ms and GB/s to this CSV")
+    ap.add_argument("--decoder", default="1", help="comma list of decode batch sizes for the Gemma-3-1B-shape "
+                    "second metric (rank 0, one GPU); empty string skips it")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -228,6 +284,7 @@ def main():
         return
 
     # ---- roofline of the dominant kernel class (live CUDA-event timing per op) ----
+    cnn_launches = ex.launch_count
     op_ms = ex.profile_ops([ins[0]], [out], warmup=2, iters=5)
     kernels = ex.op_kernels()
     real_layers = [l for l in layers]
@@ -267,6 +324,20 @@ def main():
         cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                         "sample": f"16 images x 5 passes of the same network (median {np.median(times):.3f} s per pass)"}
 
+    decoder = None
+    if args.decoder:
+        decoder = {"metric": "gemma3_1b_w8_decode_tok_per_s", "unit": "tokens/s", "dtype": "bf16 activations, int8 weights",
+                   "workload": "Gemma-3-1B architecture, random-init, 1024-token prompt + 128 greedy tokens, 1 GPU",
+                   "hbm_peak_gbs": peaks["hbm_gbs"], "runs": []}
+        ex.destroy()  # free the CNN arena first
+        for bsz in [int(t) for t in args.decoder.split(",") if t]:
+            try:
+                r = decoder_bench(dev, stream, bsz)
+                r["hbm_frac"] = r["hbm_gbs"] / peaks["hbm_gbs"]
+                decoder["runs"].append(r)
+            except Exception as e:  # the headline line must still print
+                decoder["runs"].append({"batch": bsz, "error": repr(e)[:200]})
+
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -277,8 +348,8 @@ def main():
                          "activations per step exceed L2"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_info.nbytes, "d2h_bytes_per_step": out_info.nbytes,
                 "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
-        "gpu_launches": ex.launch_count * args.steps,
-        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "gpu_launches": cnn_launches * args.steps,
+        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "decoder": decoder,
     }
     print(json.dumps(line), flush=True)
     barrier()

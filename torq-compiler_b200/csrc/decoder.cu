@@ -1,0 +1,413 @@
+// Decoder-side kernels: bf16 activations, int8 per-output-channel weights with bf16
+// scales, fp32 accumulation, bf16 KV cache. They implement the op set the reference
+// reaches for an LLM decode step: weight expansion + matmul
+// (torq_hl.expand_weights + bf16 torq_hl.matmul, compiler/torq/Dialect/TorqHL/TorqHLOps.td:943-957,
+// tests/testdata/torch_ops/matmul_dql_q8_0.mlir; here block = K, zero point 0), the
+// RMSNorm pieces (ReduceMeanPattern.cpp:37-466), tanh-GELU (GeluPattern.cpp:35-46), softmax
+// over the keys (SoftmaxPattern.cpp:23-333) and the KV cache passed through as tied
+// state (tests/testdata/torch_ops/tied_operands_kv_cache.mlir).
+//
+// Every one of them is bandwidth-bound at decode batch sizes: the design goal is bytes in
+// flight (split-K GEMV, split-T attention) and one pass over the weights.
+// Rounding points (bf16, round-to-nearest-even) are stated at each kernel; the torch
+// reference used by the tests rounds at the same points.
+#include <cuda_bf16.h>
+
+#include "kernels.h"
+
+namespace tb200 {
+
+namespace {
+
+__device__ __forceinline__ float bf2f(uint16_t v) { return __uint_as_float((uint32_t)v << 16); }
+__device__ __forceinline__ uint16_t f2bf(float f) {
+  return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+// int8 -> float without the conversion pipe: place the biased byte in the mantissa of 2^23
+__device__ __forceinline__ float s8_to_float(uint32_t word, int j) {
+  const uint32_t b = ((word >> (8 * j)) & 0xffu) ^ 0x80u;
+  return __uint_as_float(0x4B000000u | b) - 8388736.0f;  // 2^23 + 128
+}
+
+// x[b, :] = bf16( bf16(E[tok[b], :] * scale[tok[b]]) * mult )
+__global__ void __launch_bounds__(128) embed_kernel(const int32_t* __restrict__ tok, const int8_t* __restrict__ table,
+                                                    const uint16_t* __restrict__ scale, uint16_t* __restrict__ out,
+                                                    int H, int V, float mult) {
+  const int b = blockIdx.x;
+  int t = tok[b];
+  t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+  const float s = bf2f(scale[t]);
+  const int8_t* row = table + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[(size_t)b * H + i] = f2bf(bf2f(f2bf((float)row[i] * s)) * mult);
+}
+
+// y = [res +] bf16( x * rsqrt(mean(x^2) + eps) * (1 + w) )   (sum of res and the rounded norm is rounded again)
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res,
+                                                      const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
+                                                      int H, float eps) {
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = bf2f(x[base + i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float n = bf2f(f2bf(bf2f(x[base + i]) * inv * (1.0f + bf2f(w[i]))));
+    out[base + i] = res ? f2bf(bf2f(res[base + i]) + n) : f2bf(n);
+  }
+}
+
+// Split-K GEMV / skinny GEMM with int8 weights: one warp per output row n and K slice.
+//   acc[b] = sum_{k in slice} x[b,k] * W[n,k]      (fp32)
+// splits == 1: y[b,n] = bf16(acc * scale[n]); otherwise the partial sums go to scratch
+// [split][b][n] and gemv_finalize_kernel adds them in split order.
+template <int BT>
+__global__ void __launch_bounds__(256) gemv_w8_kernel(const uint16_t* __restrict__ x, const int8_t* __restrict__ W,
+                                                      const uint16_t* __restrict__ scale, void* __restrict__ y,
+                                                      float* __restrict__ partial, int B, int N, int K, int k_slice,
+                                                      int y_f32) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const int split = blockIdx.y, splits = gridDim.y;
+  const int k_begin = split * k_slice;
+  const int k_end = min(K, k_begin + k_slice);
+  float acc[BT];
+#pragma unroll
+  for (int b = 0; b < BT; b++) acc[b] = 0.f;
+  const int8_t* wrow = W + (size_t)n * K;
+  for (int k = k_begin + lane * 16; k < k_end; k += 32 * 16) {
+    const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k);
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    float wf[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) wf[j] = s8_to_float(ww[j >> 2], j & 3);
+#pragma unroll
+    for (int b = 0; b < BT; b++) {
+      if (b < B) {
+        const uint4 x0 = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + k));
+        const uint4 x1 = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + k + 8));
+        const uint32_t xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        float s = acc[b];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          s = fmaf(wf[2 * j], __uint_as_float(xw[j] << 16), s);
+          s = fmaf(wf[2 * j + 1], __uint_as_float(xw[j] & 0xffff0000u), s);
+        }
+        acc[b] = s;
+      }
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < BT; b++) acc[b] = warp_sum(acc[b]);
+  if (lane == 0) {
+    const float s = bf2f(scale[n]);
+#pragma unroll
+    for (int b = 0; b < BT; b++) {
+      if (b < B) {
+        if (splits == 1) {
+          if (y_f32) ((float*)y)[(size_t)b * N + n] = acc[b] * s;
+          else ((uint16_t*)y)[(size_t)b * N + n] = f2bf(acc[b] * s);
+        } else partial[((size_t)split * B + b) * N + n] = acc[b];
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) gemv_finalize_kernel(const float* __restrict__ partial,
+                                                            const uint16_t* __restrict__ scale,
+                                                            void* __restrict__ y, int B, int N, int splits, int y_f32) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)B * N) return;
+  const int n = (int)(i % N);
+  float s = 0.f;
+  for (int sp = 0; sp < splits; sp++) s += partial[(size_t)sp * B * N + i];
+  if (y_f32) ((float*)y)[i] = s * bf2f(scale[n]);
+  else ((uint16_t*)y)[i] = f2bf(s * bf2f(scale[n]));
+}
+
+// Per head: RMSNorm over head_dim (q and k heads; v is copied), rotate-half RoPE at position
+// pos, q heads to q_out, the k/v heads appended to the caches [B, T, kv_heads * D].
+// Rounding: the normalised head is rounded to bf16, the rotated value is rounded once.
+__global__ void __launch_bounds__(128) rope_kv_kernel(const uint16_t* __restrict__ qkv, const int32_t* __restrict__ pos_p,
+                                                      const uint16_t* __restrict__ qw, const uint16_t* __restrict__ kw,
+                                                      uint16_t* __restrict__ q_out, uint16_t* __restrict__ kcache,
+                                                      uint16_t* __restrict__ vcache, int n_q, int n_kv, int D, int T,
+                                                      float theta, float eps) {
+  __shared__ float red[32];
+  __shared__ float hv[512];
+  const int b = blockIdx.x, h = blockIdx.y;  // h: q heads, then k heads, then v heads
+  int pos = pos_p[0];
+  pos = pos < 0 ? 0 : (pos >= T ? T - 1 : pos);
+  const int width = (n_q + 2 * n_kv) * D;
+  const uint16_t* src = qkv + (size_t)b * width + (size_t)h * D;
+  const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
+  if (!is_q && !is_k) {  // v head: plain copy into the cache
+    const int hk = h - n_q - n_kv;
+    uint16_t* dst = vcache + (((size_t)b * T + pos) * n_kv + hk) * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+    return;
+  }
+  const uint16_t* w = is_q ? qw : kw;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float v = bf2f(src[i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)D + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) hv[i] = bf2f(f2bf(bf2f(src[i]) * inv * (1.0f + bf2f(w[i]))));
+  __syncthreads();
+  uint16_t* dst = is_q ? q_out + ((size_t)b * n_q + h) * D
+                       : kcache + (((size_t)b * T + pos) * n_kv + (h - n_q)) * D;
+  const int half = D >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float inv_freq = powf(theta, -(float)i / (float)half);
+    float sn, cs;
+    sincosf((float)pos * inv_freq, &sn, &cs);
+    const float x1 = hv[i], x2 = hv[i + half];
+    dst[i] = f2bf(x1 * cs - x2 * sn);
+    dst[i + half] = f2bf(x2 * cs + x1 * sn);
+  }
+}
+
+// Split-T single-query attention (one KV head shared by n_q query heads, D = 256):
+// block = (batch b, T slice), warp w = query head w. Each warp keeps a running (max, sum,
+// acc[D]) over its slice and writes it to scratch; attn_combine_kernel merges the slices.
+constexpr int kAttnD = 256;
+__global__ void __launch_bounds__(128) attn_partial_kernel(const uint16_t* __restrict__ q, const int32_t* __restrict__ pos_p,
+                                                           const uint16_t* __restrict__ kcache,
+                                                           const uint16_t* __restrict__ vcache, float* __restrict__ part,
+                                                           int n_q, int T, int window, float scale) {
+  const int b = blockIdx.x, sp = blockIdx.y, S = gridDim.y;
+  const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (h >= n_q) return;
+  int pos = pos_p[0];
+  pos = pos < 0 ? 0 : (pos >= T ? T - 1 : pos);
+  const int t_lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int span = pos + 1 - t_lo;
+  const int per = (span + S - 1) / S;
+  const int t0 = t_lo + sp * per, t1 = min(pos + 1, t0 + per);
+  // this lane's 8 dims of the query, pre-scaled
+  float qv[8];
+  {
+    const uint4 qq = *reinterpret_cast<const uint4*>(q + ((size_t)b * n_q + h) * kAttnD + lane * 8);
+    const uint32_t w[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      qv[2 * j] = __uint_as_float(w[j] << 16) * scale;
+      qv[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u) * scale;
+    }
+  }
+  float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) acc[j] = 0.f;
+  for (int t = t0; t < t1; t++) {
+    const size_t off = ((size_t)b * T + t) * kAttnD + lane * 8;
+    const uint4 kk = __ldg(reinterpret_cast<const uint4*>(kcache + off));
+    const uint4 vv = __ldg(reinterpret_cast<const uint4*>(vcache + off));
+    const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      s = fmaf(qv[2 * j], __uint_as_float(kw[j] << 16), s);
+      s = fmaf(qv[2 * j + 1], __uint_as_float(kw[j] & 0xffff0000u), s);
+    }
+    s = warp_sum(s);
+    const float m_new = fmaxf(m, s);
+    const float corr = expf(m - m_new), p = expf(s - m_new);
+    l = l * corr + p;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      acc[2 * j] = acc[2 * j] * corr + p * __uint_as_float(vw[j] << 16);
+      acc[2 * j + 1] = acc[2 * j + 1] * corr + p * __uint_as_float(vw[j] & 0xffff0000u);
+    }
+    m = m_new;
+  }
+  float* dst = part + (((size_t)b * n_q + h) * S + sp) * (kAttnD + 2);
+  if (lane == 0) {
+    dst[0] = m;
+    dst[1] = l;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++) dst[2 + lane * 8 + j] = acc[j];
+}
+
+__global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ part, uint16_t* __restrict__ out,
+                                                           int S) {
+  const int bh = blockIdx.x, d = threadIdx.x;  // one block per (b, head), one thread per dim
+  const float* p = part + (size_t)bh * S * (kAttnD + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < S; s++) m = fmaxf(m, p[(size_t)s * (kAttnD + 2)]);
+  float l = 0.f, o = 0.f;
+  for (int s = 0; s < S; s++) {
+    const float* ps = p + (size_t)s * (kAttnD + 2);
+    if (ps[1] > 0.f) {
+      const float c = expf(ps[0] - m);
+      l += ps[1] * c;
+      o += ps[2 + d] * c;
+    }
+  }
+  out[(size_t)bh * kAttnD + d] = f2bf(o / l);
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * x * (1.0f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+// out[b, i] = bf16( bf16(gelu_tanh(gate)) * up ), gate = gu[b, i], up = gu[b, I + i]
+__global__ void __launch_bounds__(256) geglu_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out, int B,
+                                                    int I) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)B * I) return;
+  const int i = (int)(idx % I);
+  const size_t b = idx / I;
+  const float g = bf2f(gu[b * 2 * I + i]), u = bf2f(gu[b * 2 * I + I + i]);
+  out[idx] = f2bf(bf2f(f2bf(gelu_tanh(g))) * u);
+}
+
+// greedy token: arg max over the vocabulary, lowest index on ties; two stages through scratch
+constexpr int kArgmaxChunks = 64;
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const void* __restrict__ logits, int is_f32,
+                                                             float* __restrict__ pv, int32_t* __restrict__ pi, int V) {
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  const int b = blockIdx.x, ch = blockIdx.y;
+  const int per = (V + kArgmaxChunks - 1) / kArgmaxChunks;
+  const int v0 = ch * per, v1 = min(V, v0 + per);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    const float x = is_f32 ? ((const float*)logits)[(size_t)b * V + v] : bf2f(((const uint16_t*)logits)[(size_t)b * V + v]);
+    if (x > best || (x == best && v < bi)) {
+      best = x;
+      bi = v;
+    }
+  }
+  sv[threadIdx.x] = best;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      const float x = sv[threadIdx.x + o];
+      const int i = si[threadIdx.x + o];
+      if (x > sv[threadIdx.x] || (x == sv[threadIdx.x] && i < si[threadIdx.x])) {
+        sv[threadIdx.x] = x;
+        si[threadIdx.x] = i;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    pv[b * kArgmaxChunks + ch] = sv[0];
+    pi[b * kArgmaxChunks + ch] = si[0];
+  }
+}
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int32_t* __restrict__ pi, int32_t* __restrict__ out) {
+  const int b = blockIdx.x;
+  if (threadIdx.x != 0) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = 0; c < kArgmaxChunks; c++) {
+    const float x = pv[b * kArgmaxChunks + c];
+    const int i = pi[b * kArgmaxChunks + c];
+    if (x > best || (x == best && i < bi)) {
+      best = x;
+      bi = i;
+    }
+  }
+  out[b] = bi;
+}
+
+}  // namespace
+
+void launch_embed(const int32_t* tok, const int8_t* table, const uint16_t* scale, uint16_t* out, int B, int H, int V,
+                  float mult, cudaStream_t stream) {
+  embed_kernel<<<B, 128, 0, stream>>>(tok, table, scale, out, H, V, mult);
+}
+
+void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, uint16_t* out, int rows, int H, float eps,
+                    cudaStream_t stream) {
+  rmsnorm_kernel<<<rows, 256, 0, stream>>>(x, res, w, out, H, eps);
+}
+
+int gemv_w8_splits(int B, int N, int K) {
+  // enough warps to fill the machine: one warp per (row, slice); slices are multiples of 512 bytes
+  const long long warps_wanted = 148LL * 32;
+  int splits = (int)((warps_wanted + N - 1) / N);
+  const int max_splits = K / 512 > 0 ? K / 512 : 1;
+  if (splits > max_splits) splits = max_splits;
+  if (splits > 16) splits = 16;
+  if (splits < 1) splits = 1;
+  (void)B;
+  return splits;
+}
+
+size_t gemv_w8_scratch_bytes(int B, int N, int splits) { return splits > 1 ? (size_t)splits * B * N * sizeof(float) : 0; }
+
+void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, void* y, int y_f32, float* scratch, int B,
+                    int N, int K, int splits, cudaStream_t stream) {
+  const int slice = ((K + splits - 1) / splits + 511) / 512 * 512;
+  const int used = (K + slice - 1) / slice;  // slices that really hold data
+  dim3 grid((N + 7) / 8, used);
+  if (B <= 1) gemv_w8_kernel<1><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  else if (B <= 4) gemv_w8_kernel<4><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  else if (B <= 8) gemv_w8_kernel<8><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  else if (B <= 16) gemv_w8_kernel<16><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  else gemv_w8_kernel<32><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  if (used > 1) {
+    const size_t total = (size_t)B * N;
+    gemv_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, scale, y, B, N, used, y_f32);
+  }
+}
+
+void launch_rope_kv(const uint16_t* qkv, const int32_t* pos, const uint16_t* qw, const uint16_t* kw, uint16_t* q_out,
+                    uint16_t* kcache, uint16_t* vcache, int B, int n_q, int n_kv, int D, int T, float theta, float eps,
+                    cudaStream_t stream) {
+  rope_kv_kernel<<<dim3(B, n_q + 2 * n_kv), 128, 0, stream>>>(qkv, pos, qw, kw, q_out, kcache, vcache, n_q, n_kv, D, T,
+                                                              theta, eps);
+}
+
+int attn_decode_splits(int B) { return B >= 32 ? 4 : B >= 8 ? 8 : 32; }
+size_t attn_decode_scratch_bytes(int B, int n_q, int splits) {
+  return (size_t)B * n_q * splits * (kAttnD + 2) * sizeof(float);
+}
+void launch_attn_decode(const uint16_t* q, const int32_t* pos, const uint16_t* kcache, const uint16_t* vcache,
+                        uint16_t* out, float* scratch, int B, int n_q, int T, int window, float scale, int splits,
+                        cudaStream_t stream) {
+  attn_partial_kernel<<<dim3(B, splits), 128, 0, stream>>>(q, pos, kcache, vcache, scratch, n_q, T, window, scale);
+  attn_combine_kernel<<<B * n_q, kAttnD, 0, stream>>>(scratch, out, splits);
+}
+
+void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t stream) {
+  const size_t total = (size_t)B * I;
+  geglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(gu, out, B, I);
+}
+
+size_t argmax_scratch_bytes(int B) { return (size_t)B * kArgmaxChunks * 8; }
+void launch_argmax(const void* logits, int is_f32, int32_t* out, void* scratch, int B, int V, cudaStream_t stream) {
+  float* pv = (float*)scratch;
+  int32_t* pi = (int32_t*)((char*)scratch + (size_t)B * kArgmaxChunks * 4);
+  argmax_partial_kernel<<<dim3(B, kArgmaxChunks), 256, 0, stream>>>(logits, is_f32, pv, pi, V);
+  argmax_final_kernel<<<B, 32, 0, stream>>>(pv, pi, out);
+}
+
+}  // namespace tb200

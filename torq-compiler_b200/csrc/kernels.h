@@ -109,6 +109,27 @@ void gemm_tc_state_free(GemmTcState* s);
 bool gemm_tc_supported(long long M, int N, int K, long long lda);
 cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t stream);
 
+// ---- decoder kernels (decoder.cu): bf16 tensors are passed as uint16_t bit patterns ----
+void launch_embed(const int32_t* tok, const int8_t* table, const uint16_t* scale, uint16_t* out, int B, int H, int V,
+                  float mult, cudaStream_t stream);
+void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, uint16_t* out, int rows, int H, float eps,
+                    cudaStream_t stream);
+int gemv_w8_splits(int B, int N, int K);
+size_t gemv_w8_scratch_bytes(int B, int N, int splits);
+void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, void* y, int y_f32, float* scratch, int B,
+                    int N, int K, int splits, cudaStream_t stream);  // y bf16, or fp32 when y_f32
+void launch_rope_kv(const uint16_t* qkv, const int32_t* pos, const uint16_t* qw, const uint16_t* kw, uint16_t* q_out,
+                    uint16_t* kcache, uint16_t* vcache, int B, int n_q, int n_kv, int D, int T, float theta, float eps,
+                    cudaStream_t stream);
+int attn_decode_splits(int B);
+size_t attn_decode_scratch_bytes(int B, int n_q, int splits);
+void launch_attn_decode(const uint16_t* q, const int32_t* pos, const uint16_t* kcache, const uint16_t* vcache,
+                        uint16_t* out, float* scratch, int B, int n_q, int T, int window, float scale, int splits,
+                        cudaStream_t stream);
+void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t stream);
+size_t argmax_scratch_bytes(int B);
+void launch_argmax(const void* logits, int is_f32, int32_t* out, void* scratch, int B, int V, cudaStream_t stream);
+
 void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream);
 
 }  // namespace tb200

@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <memory>
 
 #include "../../include/torq_b200.h"
@@ -44,6 +45,25 @@ struct Builder {
     plan.const_image.resize(off + bytes);
     memcpy(plan.const_image.data() + off, data, bytes);
     return off;
+  }
+
+  // Uploads a constant tensor's bytes unchanged, once per tensor id (the tied embedding /
+  // LM-head table is named by two ops).
+  std::map<int, size_t> raw_offsets;
+  bool add_raw_const(int id, size_t min_bytes, const char* what, int op_index, size_t& off) {
+    if (!valid_id(id) || tensors[id].kind != TB200_TENSOR_CONSTANT || tensors[id].const_bytes < min_bytes) {
+      fail(TB200_INVALID_ARGUMENT, "op %d: %s is not a constant of at least %zu bytes", op_index, what, min_bytes);
+      return false;
+    }
+    auto it = raw_offsets.find(id);
+    if (it == raw_offsets.end())
+      it = raw_offsets.emplace(id, add_const(constants.data() + tensors[id].const_offset, tensors[id].const_bytes)).first;
+    off = it->second;
+    return true;
+  }
+
+  bool is_t(int id, uint32_t dtype, uint32_t rank) const {
+    return valid_id(id) && tensors[id].dtype == dtype && tensors[id].rank == rank;
   }
 
   template <typename T>
@@ -251,6 +271,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
       if (root[id] != id) plan.tensor_loc[id] = plan.tensor_loc[root[id]];
   }
 
+  size_t scratch_need = 0;
   // ---- one step per op ----
   for (int i = 0; i < (int)ops.size(); i++) {
     const auto& op = ops[i];
@@ -623,6 +644,144 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         };
         break;
       }
+      case TB200_OP_EMBED: {
+        if (!b.is_t(op.in0, TB200_I32, 1) || !b.is_t(op.out0, TB200_BF16, 2) || !b.valid_id(op.weights) ||
+            tensors[op.weights].rank != 2)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: embed wants i32 [B] tokens, an int8 [V,H] table, bf16 [B,H] out", i);
+        const int B = tensors[op.in0].shape[0], V = tensors[op.weights].shape[0], H = tensors[op.weights].shape[1];
+        if (tensors[op.out0].shape[0] != B || tensors[op.out0].shape[1] != H)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: embed output shape mismatch", i);
+        size_t w_off, s_off;
+        if (!b.add_raw_const(op.weights, (size_t)V * H, "table", i, w_off)) return b.status;
+        if (!b.add_raw_const(op.bias, (size_t)V * 2, "scales", i, s_off)) return b.status;
+        Loc lt = loc(op.in0), lo = loc(op.out0);
+        const float mult = op.f0;
+        step.kernel_name = "embed_w8";
+        step.launch = [=](const ExecContext& c) {
+          launch_embed((const int32_t*)lt.resolve(c), (const int8_t*)(c.consts + w_off),
+                       (const uint16_t*)(c.consts + s_off), (uint16_t*)lo.resolve(c), B, H, V, mult, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_RMSNORM: {
+        if (!b.is_t(op.in0, TB200_BF16, 2) || !b.is_t(op.out0, TB200_BF16, 2) || (op.in1 >= 0 && !b.is_t(op.in1, TB200_BF16, 2)))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: rmsnorm wants bf16 [rows,H] tensors", i);
+        const int rows = tensors[op.in0].shape[0], H = tensors[op.in0].shape[1];
+        if (b.numel(op.out0) != (size_t)rows * H || (op.in1 >= 0 && b.numel(op.in1) != (size_t)rows * H))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: rmsnorm shape mismatch", i);
+        size_t w_off;
+        if (!b.add_raw_const(op.weights, (size_t)H * 2, "norm weight", i, w_off)) return b.status;
+        Loc lx = loc(op.in0), lr = loc(op.in1), lo = loc(op.out0);
+        const float eps = op.f0;
+        const bool has_res = op.in1 >= 0;
+        step.kernel_name = "rmsnorm";
+        step.launch = [=](const ExecContext& c) {
+          launch_rmsnorm((const uint16_t*)lx.resolve(c), has_res ? (const uint16_t*)lr.resolve(c) : nullptr,
+                         (const uint16_t*)(c.consts + w_off), (uint16_t*)lo.resolve(c), rows, H, eps, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_GEMV_W8: {
+        if (!b.is_t(op.in0, TB200_BF16, 2) || (!b.is_t(op.out0, TB200_BF16, 2) && !b.is_t(op.out0, TB200_F32, 2)) ||
+            !b.valid_id(op.weights) || tensors[op.weights].rank != 2 || tensors[op.weights].dtype != TB200_I8)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: gemv_w8 wants bf16 [B,K] x int8 [N,K] -> bf16 or f32 [B,N]", i);
+        const int y_f32 = tensors[op.out0].dtype == TB200_F32;
+        const int B = tensors[op.in0].shape[0], K = tensors[op.in0].shape[1], N = tensors[op.weights].shape[0];
+        if (tensors[op.weights].shape[1] != K || tensors[op.out0].shape[0] != B || tensors[op.out0].shape[1] != N)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: gemv_w8 shape mismatch", i);
+        if (K % 16 != 0 || B > 32) return b.fail(TB200_UNIMPLEMENTED, "op %d: gemv_w8 needs K %% 16 == 0 and batch <= 32", i);
+        size_t w_off, s_off;
+        if (!b.add_raw_const(op.weights, (size_t)N * K, "weights", i, w_off)) return b.status;
+        if (!b.add_raw_const(op.bias, (size_t)N * 2, "scales", i, s_off)) return b.status;
+        const int splits = op.i0 > 0 ? op.i0 : gemv_w8_splits(B, N, K);
+        scratch_need = std::max(scratch_need, gemv_w8_scratch_bytes(B, N, splits));
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = splits > 1 ? "gemv_w8_splitk" : "gemv_w8";
+        step.launches = splits > 1 ? 2 : 1;
+        step.launch = [=](const ExecContext& c) {
+          launch_gemv_w8((const uint16_t*)lx.resolve(c), (const int8_t*)(c.consts + w_off),
+                         (const uint16_t*)(c.consts + s_off), lo.resolve(c), y_f32, (float*)c.scratch, B, N, K, splits,
+                         c.stream);
+        };
+        break;
+      }
+      case TB200_OP_ROPE_KV: {
+        const int n_q = op.i0, n_kv = op.i1, D = op.i2;
+        if (!b.is_t(op.in0, TB200_BF16, 2) || !b.is_t(op.in1, TB200_I32, 1) || !b.is_t(op.out0, TB200_BF16, 2) ||
+            !b.is_t(op.out1, TB200_BF16, 3) || !b.is_t(op.in2, TB200_BF16, 3) || n_q < 1 || n_kv < 1 || D < 2 || D > 512 ||
+            (D & 1))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: rope_kv wants bf16 qkv [B,(q+2kv)*D], i32 pos, bf16 caches [B,T,kv*D]", i);
+        const int B = tensors[op.in0].shape[0], T = tensors[op.out1].shape[1];
+        if (tensors[op.in0].shape[1] != (n_q + 2 * n_kv) * D || tensors[op.out0].shape[0] != B ||
+            tensors[op.out0].shape[1] != n_q * D || tensors[op.out1].shape[0] != B || tensors[op.out1].shape[2] != n_kv * D ||
+            b.numel(op.in2) != b.numel(op.out1) || tensors[op.out1].kind != TB200_TENSOR_STATE ||
+            tensors[op.in2].kind != TB200_TENSOR_STATE)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: rope_kv shape mismatch (caches must be state tensors)", i);
+        size_t qw_off, kw_off;
+        if (!b.add_raw_const(op.weights, (size_t)D * 2, "q_norm weight", i, qw_off)) return b.status;
+        if (!b.add_raw_const(op.bias, (size_t)D * 2, "k_norm weight", i, kw_off)) return b.status;
+        Loc lx = loc(op.in0), lp = loc(op.in1), lq = loc(op.out0), lk = loc(op.out1), lv = loc(op.in2);
+        const float theta = op.f0, eps = op.f1;
+        step.kernel_name = "rope_kv";
+        step.launch = [=](const ExecContext& c) {
+          launch_rope_kv((const uint16_t*)lx.resolve(c), (const int32_t*)lp.resolve(c), (const uint16_t*)(c.consts + qw_off),
+                         (const uint16_t*)(c.consts + kw_off), (uint16_t*)lq.resolve(c), (uint16_t*)lk.resolve(c),
+                         (uint16_t*)lv.resolve(c), B, n_q, n_kv, D, T, theta, eps, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_ATTN_DECODE: {
+        const int n_q = op.i0, n_kv = op.i1, D = op.i2, window = op.i3;
+        // in2 = K cache, weights = V cache (a state tensor id, not a constant)
+        if (!b.is_t(op.in0, TB200_BF16, 2) || !b.is_t(op.in1, TB200_I32, 1) || !b.is_t(op.in2, TB200_BF16, 3) ||
+            !b.is_t(op.weights, TB200_BF16, 3) || !b.is_t(op.out0, TB200_BF16, 2))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: attn_decode wants bf16 q [B,q*D], i32 pos, bf16 K/V caches", i);
+        if (n_kv != 1 || D != 256 || n_q < 1 || n_q > 4)
+          return b.fail(TB200_UNIMPLEMENTED, "op %d: attn_decode supports one KV head of 256 dims and up to 4 query heads", i);
+        const int B = tensors[op.in0].shape[0], T = tensors[op.in2].shape[1];
+        if (tensors[op.in0].shape[1] != n_q * D || b.numel(op.out0) != (size_t)B * n_q * D ||
+            tensors[op.in2].shape[0] != B || tensors[op.in2].shape[2] != D || b.numel(op.weights) != b.numel(op.in2))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: attn_decode shape mismatch", i);
+        const int splits = attn_decode_splits(B);
+        scratch_need = std::max(scratch_need, attn_decode_scratch_bytes(B, n_q, splits));
+        Loc lq = loc(op.in0), lp = loc(op.in1), lk = loc(op.in2), lv = plan.tensor_loc[op.weights], lo = loc(op.out0);
+        const float scale = op.f0;
+        step.kernel_name = "attn_decode_splitT";
+        step.launches = 2;
+        step.launch = [=](const ExecContext& c) {
+          launch_attn_decode((const uint16_t*)lq.resolve(c), (const int32_t*)lp.resolve(c), (const uint16_t*)lk.resolve(c),
+                             (const uint16_t*)lv.resolve(c), (uint16_t*)lo.resolve(c), (float*)c.scratch, B, n_q, T, window,
+                             scale, splits, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_GEGLU: {
+        if (!b.is_t(op.in0, TB200_BF16, 2) || !b.is_t(op.out0, TB200_BF16, 2) ||
+            tensors[op.in0].shape[1] != 2 * tensors[op.out0].shape[1] || tensors[op.in0].shape[0] != tensors[op.out0].shape[0])
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: geglu wants bf16 [B,2I] -> bf16 [B,I]", i);
+        const int B = tensors[op.out0].shape[0], I = tensors[op.out0].shape[1];
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "geglu";
+        step.launch = [=](const ExecContext& c) {
+          launch_geglu((const uint16_t*)lx.resolve(c), (uint16_t*)lo.resolve(c), B, I, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_ARGMAX: {
+        if ((!b.is_t(op.in0, TB200_BF16, 2) && !b.is_t(op.in0, TB200_F32, 2)) || !b.is_t(op.out0, TB200_I32, 1) ||
+            tensors[op.out0].shape[0] != tensors[op.in0].shape[0])
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: argmax wants bf16 or f32 [B,V] -> i32 [B]", i);
+        const int is_f32 = tensors[op.in0].dtype == TB200_F32;
+        const int B = tensors[op.in0].shape[0], V = tensors[op.in0].shape[1];
+        scratch_need = std::max(scratch_need, argmax_scratch_bytes(B));
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "argmax";
+        step.launches = 2;
+        step.launch = [=](const ExecContext& c) {
+          launch_argmax(lx.resolve(c), is_f32, (int32_t*)lo.resolve(c), c.scratch, B, V, c.stream);
+        };
+        break;
+      }
       case TB200_OP_RESHAPE: {
         if (bytes_of(op.in0) != bytes_of(op.out0) || tensors[op.in0].dtype != tensors[op.out0].dtype)
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: reshape changes the byte count", i);
@@ -637,6 +796,10 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
     plan.launch_count += step.launches;
     plan.steps.push_back(std::move(step));
   }
+  // scratch shared by the ops that need one, behind the activations
+  plan.scratch_offset = (plan.arena_bytes + 255) & ~(size_t)255;
+  plan.scratch_bytes = scratch_need;
+  plan.arena_bytes = plan.scratch_offset + scratch_need;
   return TB200_OK;
 }
 

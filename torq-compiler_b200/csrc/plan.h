@@ -21,6 +21,7 @@ struct ExecContext {
   void* const* io;  // inputs then outputs
   cudaStream_t stream;
   int* status;      // device status word (0 = fine)
+  char* scratch;    // per-dispatch scratch shared by the ops that need one (split-K partials, ...)
 };
 
 // Where a tensor lives at dispatch time.
@@ -49,6 +50,8 @@ struct Plan {
   size_t arena_bytes = 0;
   size_t state_bytes = 0;         // prefix of the arena holding persistent state, zeroed at create
   size_t launch_count = 0;
+  size_t scratch_offset = 0;      // scratch sits behind the activations inside the arena allocation
+  size_t scratch_bytes = 0;
   std::vector<Loc> tensor_loc;
 };
 

@@ -452,6 +452,7 @@ int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cud
   ctx.io = io.data();
   ctx.stream = d->stream;
   ctx.status = d->status_word;
+  ctx.scratch = (char*)ex->arena + ex->plan.scratch_offset;
   for (size_t i = 0; i < ex->plan.steps.size(); i++) {
     if (events) cudaEventRecord((*events)[i], d->stream);
     ex->plan.steps[i].launch(ctx);

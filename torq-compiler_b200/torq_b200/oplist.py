@@ -265,6 +265,54 @@ class Graph:
             raise ValueError("reshape changes the element count")
         return self._emit("reshape", [x], shape, x.dtype)
 
+    # ---- decoder ops (bf16 activations, int8 per-output-channel weights) ------
+    def embed(self, tokens, table_i8, scales_bf16, mult: float):
+        """x[b] = bf16(bf16(E[tok[b]] * scale[tok[b]]) * mult). table/scales may be TensorRefs
+        (to share the tied LM-head table) or arrays."""
+        tab = table_i8 if isinstance(table_i8, TensorRef) else self.const(np.asarray(table_i8, np.int8))
+        sc = scales_bf16 if isinstance(scales_bf16, TensorRef) else self.const(np.asarray(scales_bf16, np.uint16), "bf16")
+        return self._emit("embed", [tokens], (tokens.shape[0], tab.shape[1]), "bf16", consts={"weights": tab, "bias": sc},
+                          f0=float(mult))
+
+    def rmsnorm(self, x, weight_bf16, eps: float, residual=None):
+        """y = [residual +] bf16(x * rsqrt(mean(x^2) + eps) * (1 + w))."""
+        w = weight_bf16 if isinstance(weight_bf16, TensorRef) else self.const(np.asarray(weight_bf16, np.uint16), "bf16")
+        ins = [x] + ([residual] if residual is not None else [])
+        return self._emit("rmsnorm", ins, x.shape, "bf16", consts={"weights": w}, f0=float(eps))
+
+    def gemv_w8(self, x, weights_i8, scales_bf16, splits: int = 0, out_dtype: str = "bf16"):
+        """y[b, n] = scale[n] * sum_k x[b, k] * W[n, k], rounded to bf16 or kept in fp32 (out_dtype "f32");
+        W is [N, K] int8."""
+        w = weights_i8 if isinstance(weights_i8, TensorRef) else self.const(np.asarray(weights_i8, np.int8))
+        sc = scales_bf16 if isinstance(scales_bf16, TensorRef) else self.const(np.asarray(scales_bf16, np.uint16), "bf16")
+        if w.shape[1] != x.shape[1]:
+            raise ValueError("weight K mismatch")
+        return self._emit("gemv_w8", [x], (x.shape[0], w.shape[0]), out_dtype, consts={"weights": w, "bias": sc}, i0=splits)
+
+    def rope_kv(self, qkv, pos, q_norm_w, k_norm_w, k_cache, v_cache, *, n_q, n_kv, head_dim, theta, eps):
+        """Per-head RMSNorm + rotary on q and k at position pos; k and v appended to the caches
+        (state tensors [B, T, n_kv * head_dim]). Returns the rotated queries [B, n_q * head_dim]."""
+        qw = self.const(np.asarray(q_norm_w, np.uint16), "bf16")
+        kw = self.const(np.asarray(k_norm_w, np.uint16), "bf16")
+        out = self._tensor((qkv.shape[0], n_q * head_dim), "bf16", ACTIVATION)
+        self.ops.append(Op("rope_kv", [qkv, pos, v_cache], [out, k_cache], {"weights": qw, "bias": kw},
+                           dict(i0=n_q, i1=n_kv, i2=head_dim, f0=float(theta), f1=float(eps))))
+        return out
+
+    def attn_decode(self, q, pos, k_cache, v_cache, *, n_q, n_kv, head_dim, window, scale):
+        """Single-query attention over the cached keys [max(0, pos - window + 1), pos] (window 0 = all)."""
+        out = self._tensor(q.shape, "bf16", ACTIVATION)
+        self.ops.append(Op("attn_decode", [q, pos, k_cache], [out], {"weights": v_cache},
+                           dict(i0=n_q, i1=n_kv, i2=head_dim, i3=window, f0=float(scale))))
+        return out
+
+    def geglu(self, gate_up):
+        """y = bf16(bf16(gelu_tanh(gate)) * up), gate = first half of the columns."""
+        return self._emit("geglu", [gate_up], (gate_up.shape[0], gate_up.shape[1] // 2), "bf16")
+
+    def argmax(self, logits):
+        return self._emit("argmax", [logits], (logits.shape[0],), "i32")
+
     # ---- serialisation ------------------------------------------------------
     def serialize(self) -> bytes:
         const_blob = bytearray()
