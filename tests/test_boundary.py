@@ -87,3 +87,19 @@ def test_graph_builder_rejects_bad_shapes():
               out_zp=0)
     with pytest.raises(ValueError):
         g.table(x, np.zeros(255, np.int8))
+
+
+def test_workload_builders_match_the_benchmark_shapes():
+    from torq_b200.workloads.mobilenet_v2 import build_mobilenet_v2
+    from torq_b200.workloads.yolov8n import build_yolov8n
+    from torq_b200.workloads import gemma3
+    g, layers = build_mobilenet_v2(1)
+    assert sum(l["macs"] for l in layers) == 300774272 and sum(l["weight_bytes"] for l in layers) == 3469760
+    assert sum(1 for l in layers if l["kind"] in ("conv2d", "depthwise")) == 52
+    g, macs = build_yolov8n(1, 640)
+    assert [o.shape for o in g.outputs] == [(1, 80, 80, 64), (1, 80, 80, 80), (1, 40, 40, 64), (1, 40, 40, 80),
+                                            (1, 20, 20, 64), (1, 20, 20, 80)]
+    assert 4.2e9 < macs < 4.6e9
+    assert gemma3.weight_bytes_per_token(gemma3.GemmaConfig()) == 999751680
+    cfg = gemma3.GemmaConfig()
+    assert [cfg.is_global(l) for l in range(7)] == [False] * 5 + [True, False]

@@ -1,0 +1,71 @@
+"""The TOSA-text front end on modules written for this test (same textual forms as the
+reference's fixtures: tosa.const / arith.constant, hex dense blobs, fused rescale chains)."""
+import numpy as np
+import pytest
+
+from oracle_exec import run_graph
+from torq_b200 import tosa_frontend
+
+CONV = '''
+module {
+  func.func @main(%arg0: tensor<1x6x6x4xi8> {some.attr = "x"}) -> (tensor<1x6x6x2xi8> {other = "y"}) {
+    %0 = "tosa.const"() <{values = dense<"0xWEIGHTHEX"> : tensor<2x3x3x4xi8>}> : () -> tensor<2x3x3x4xi8>
+    %1 = "tosa.const"() <{values = dense<[100, -200]> : tensor<2xi32>}> : () -> tensor<2xi32>
+    %cst = arith.constant dense<-3> : tensor<1xi8>
+    %cst_0 = arith.constant dense<0> : tensor<1xi8>
+    %2 = tosa.conv2d %arg0, %0, %1, %cst, %cst_0 {acc_type = i32, dilation = array<i64: 1, 1>, pad = array<i64: 1, 1, 1, 1>, stride = array<i64: 1, 1>} : (tensor<1x6x6x4xi8>, tensor<2x3x3x4xi8>, tensor<2xi32>, tensor<1xi8>, tensor<1xi8>) -> tensor<1x6x6x2xi32>
+    %cst_1 = arith.constant dense<[1500000000, 1300000000]> : tensor<2xi32>
+    %cst_2 = arith.constant dense<40> : tensor<2xi8>
+    %cst_3 = arith.constant dense<0> : tensor<1xi32>
+    %cst_4 = arith.constant dense<5> : tensor<1xi8>
+    %3 = tosa.rescale %2, %cst_1, %cst_2, %cst_3, %cst_4 {input_unsigned = false, output_unsigned = false, per_channel = true, rounding_mode = DOUBLE_ROUND, scale32 = true} : (tensor<1x6x6x2xi32>, tensor<2xi32>, tensor<2xi8>, tensor<1xi32>, tensor<1xi8>) -> tensor<1x6x6x2xi8>
+    %4 = tosa.clamp %3 {max_val = 100 : i8, min_val = 5 : i8} : (tensor<1x6x6x2xi8>) -> tensor<1x6x6x2xi8>
+    return %4 : tensor<1x6x6x2xi8>
+  }
+}
+'''
+
+
+def test_conv_rescale_clamp_chain_becomes_one_op():
+    w = np.random.default_rng(1).integers(-127, 128, (2, 3, 3, 4), dtype=np.int8)
+    text = CONV.replace("WEIGHTHEX", w.tobytes().hex().upper())
+    g = tosa_frontend.build_graph(text)
+    assert [op.kind for op in g.ops] == ["conv2d"]
+    op = g.ops[0]
+    assert (op.consts["weights"].data == w).all() and op.consts["bias"].data.tolist() == [100, -200]
+    a = op.attrs
+    assert (a["in0_zp"], a["out_zp"], a["clamp_min"], a["clamp_max"], a["per_channel"], a["double_round"]) == (-3, 5, 5, 100, 1, 1)
+    assert op.consts["multiplier"].data.tolist() == [1500000000, 1300000000] and op.consts["shift"].data.tolist() == [40, 40]
+    x = np.random.default_rng(2).integers(-40, 40, (1, 6, 6, 4), dtype=np.int8)
+    out = run_graph(g, [x])[0]
+    assert out.shape == (1, 6, 6, 2) and out.min() >= 5 and out.max() <= 100
+
+
+ADD = '''
+module {
+  func.func @main(%arg0: tensor<1x4x4x8xi8>, %arg1: tensor<1x4x4x8xi8>) -> tensor<1x4x4x8xi8> {
+    %c = arith.constant dense<1073741824> : tensor<1xi32>
+    %s = arith.constant dense<11> : tensor<1xi8>
+    %z0 = arith.constant dense<-3> : tensor<1xi8>
+    %z1 = arith.constant dense<7> : tensor<1xi8>
+    %zero = arith.constant dense<0> : tensor<1xi32>
+    %0 = tosa.rescale %arg0, %c, %s, %z0, %zero {input_unsigned = false, output_unsigned = false, per_channel = false, rounding_mode = DOUBLE_ROUND, scale32 = true} : (tensor<1x4x4x8xi8>, tensor<1xi32>, tensor<1xi8>, tensor<1xi8>, tensor<1xi32>) -> tensor<1x4x4x8xi32>
+    %1 = tosa.rescale %arg1, %c, %s, %z1, %zero {input_unsigned = false, output_unsigned = false, per_channel = false, rounding_mode = DOUBLE_ROUND, scale32 = true} : (tensor<1x4x4x8xi8>, tensor<1xi32>, tensor<1xi8>, tensor<1xi8>, tensor<1xi32>) -> tensor<1x4x4x8xi32>
+    %2 = tosa.add %0, %1 : (tensor<1x4x4x8xi32>, tensor<1x4x4x8xi32>) -> tensor<1x4x4x8xi32>
+    %m = arith.constant dense<1200000000> : tensor<1xi32>
+    %sh = arith.constant dense<49> : tensor<1xi8>
+    %oz = arith.constant dense<-2> : tensor<1xi8>
+    %3 = tosa.rescale %2, %m, %sh, %zero, %oz {input_unsigned = false, output_unsigned = false, per_channel = false, rounding_mode = DOUBLE_ROUND, scale32 = true} : (tensor<1x4x4x8xi32>, tensor<1xi32>, tensor<1xi8>, tensor<1xi32>, tensor<1xi8>) -> tensor<1x4x4x8xi8>
+    return %3 : tensor<1x4x4x8xi8>
+  }
+}
+'''
+
+
+def test_add_chain_and_unsupported_ops():
+    g = tosa_frontend.build_graph(ADD)
+    assert [op.kind for op in g.ops] == ["add"]
+    a = g.ops[0].attrs
+    assert (a["in0_zp"], a["in1_zp"], a["in0_shift"], a["out_mult"], a["out_shift"], a["out_zp"]) == (-3, 7, 11, 1200000000, 49, -2)
+    with pytest.raises(NotImplementedError):
+        tosa_frontend.build_graph(ADD.replace("tosa.add", "tosa.bitwise_and"))

@@ -314,6 +314,40 @@ class Graph:
         return self._emit("argmax", [logits], (logits.shape[0],), "i32")
 
     # ---- serialisation ------------------------------------------------------
+    @staticmethod
+    def deserialize(blob: bytes) -> "Graph":
+        """Rebuilds a Graph (tensors, op records with their constants) from a torq-b200-ops blob,
+        e.g. a model file: the inverse of serialize()."""
+        h = Header.from_buffer_copy(blob[:C.sizeof(Header)])
+        if h.magic != MAGIC or h.version != VERSION:
+            raise ValueError("not a torq-b200-ops blob of this version")
+        kinds = {v: k for k, v in OP_KINDS.items()}
+        dnames = {v: k for k, v in DTYPES.items()}
+        g = Graph()
+        for i in range(h.n_tensors):
+            r = TensorRec.from_buffer_copy(blob[h.tensors_offset + i * C.sizeof(TensorRec):][:C.sizeof(TensorRec)])
+            shape = tuple(r.shape[k] for k in range(r.rank))
+            dt = dnames[r.dtype]
+            data = None
+            if r.kind == CONSTANT:
+                raw = blob[h.const_offset + r.const_offset:h.const_offset + r.const_offset + r.const_bytes]
+                data = np.frombuffer(raw, NP_DTYPE[dt]).reshape(shape).copy()
+            g.tensors.append(TensorRef(i, shape, dt, r.kind, data))
+        const_fields = _OP_INT_FIELDS[5:10]
+        for i in range(h.n_ops):
+            r = OpRec.from_buffer_copy(blob[h.ops_offset + i * C.sizeof(OpRec):][:C.sizeof(OpRec)])
+            ins = [g.tensors[t] for t in (r.in0, r.in1, r.in2) if t >= 0]
+            outs = [g.tensors[t] for t in (r.out0, r.out1) if t >= 0]
+            consts = {n: g.tensors[getattr(r, n)] for n in const_fields if getattr(r, n) >= 0}
+            attrs = {n: getattr(r, n) for n in _OP_INT_FIELDS[10:]}
+            attrs.update({f: getattr(r, f) for f in ("f0", "f1", "f2", "f3")})
+            g.ops.append(Op(kinds[r.kind], ins, outs, consts, attrs))
+        ids_in = np.frombuffer(blob[h.inputs_offset:h.inputs_offset + 4 * h.n_inputs], np.int32)
+        ids_out = np.frombuffer(blob[h.outputs_offset:h.outputs_offset + 4 * h.n_outputs], np.int32)
+        g.inputs = [g.tensors[i] for i in ids_in]
+        g.outputs = [g.tensors[i] for i in ids_out]
+        return g
+
     def serialize(self) -> bytes:
         const_blob = bytearray()
         trecs = []
