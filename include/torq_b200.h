@@ -144,6 +144,21 @@ int tb200_executable_profile_ops(tb200_executable_t* executable, const tb200_bin
 /* Name of the kernel the plan picked for op `index` (static string). */
 const char* tb200_executable_op_kernel(tb200_executable_t* executable, uint32_t index);
 
+/* No counterpart in the reference. The split-K int8-weight GEMV (y[b,n] = scale[n] * sum_k
+ * x[b,k] * W[n,k]; x bf16 [B,K], W int8 [N,K], scale bf16 [N], y bf16 or fp32 [B,N]) for
+ * callers that cannot allocate: a host whose own allocator already holds all device memory,
+ * or a latency-critical loop that cannot afford the device-wide synchronisation an
+ * allocation may bring. Its partial sums live in a fixed 4 MiB array inside the library
+ * (held by every GPU that loads the library until the process exits), so
+ * slices * B * N must be <= 1,048,576 or the call returns TB200_OUT_OF_RANGE (and says so on
+ * stderr). All pointers are device pointers on GPU `cuda_ordinal`; `stream` is a
+ * cudaStream_t or NULL; splits <= 0 picks the slice count. The first call on a device
+ * resolves the array's device address and should be made before any stream capture. Calls
+ * share the array: calls that may overlap on the GPU race with each other and must be ordered
+ * by the caller. Nothing is allocated or freed by this call. */
+int tb200_gemv_w8_noalloc(int cuda_ordinal, void* stream, const void* x_bf16, const void* w_i8,
+                          const void* scale_bf16, void* y, int y_is_f32, int B, int N, int K, int splits);
+
 #ifdef __cplusplus
 }
 #endif

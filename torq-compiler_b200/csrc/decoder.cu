@@ -13,6 +13,9 @@
 // reference used by the tests rounds at the same points.
 #include <cuda_bf16.h>
 
+#include <cstdio>
+#include <mutex>
+
 #include "kernels.h"
 
 namespace tb200 {
@@ -410,4 +413,67 @@ void launch_argmax(const void* logits, int is_f32, int32_t* out, void* scratch, 
   argmax_final_kernel<<<B, 32, 0, stream>>>(pv, pi, out);
 }
 
+// ---------------------------------------------------------------------------------------
+// tb200_gemv_w8_noalloc: the split-K int8-weight GEMV for callers that must not allocate.
+//
+// Who that is: a host that has handed all device memory to its own allocator (a HAL
+// allocator that reserved the HBM, a serving engine with a fixed memory plan) has no free
+// memory left for a cudaMalloc made behind its back, and a latency-critical loop cannot take
+// the device-wide synchronisation an allocation may imply. For them the partial sums of
+// the split-K reduction live in the fixed array below instead of a buffer from the arena.
+//
+// The array belongs to the library image: every GPU that loads the library holds its
+// 4 MiB until the process exits. All calls on a device share it and it keeps whatever the
+// last call left there. Nothing in it has to start at zero - each (slice, row, column)
+// partial is written by exactly one warp before the reduction kernel reads it - but two
+// calls whose kernels overlap on the GPU (different streams, or different host threads
+// without ordering) would overwrite each other's partial sums: callers must order them.
+// ---------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kNoAllocScratchFloats = 1u << 20;  // 4 MiB: slices * batch * N must fit
+static __device__ __align__(256) float g_noalloc_gemv_scratch[kNoAllocScratchFloats];
+constexpr int kMaxDevices = 64;
+float* g_noalloc_scratch_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+}  // namespace
+
 }  // namespace tb200
+
+// Status numbers are those of include/torq_b200.h (0 OK, 3 INVALID_ARGUMENT, 11 OUT_OF_RANGE,
+// 13 INTERNAL). All pointers are device pointers on GPU `cuda_ordinal`; `stream` is a
+// cudaStream_t (NULL = the default stream). The first call on a device looks up the device
+// address of the scratch array (cudaGetSymbolAddress with that device current); make that
+// first call before any stream capture begins. No cudaMalloc, cudaFree or allocating
+// library routine is called, on the first call or later.
+extern "C" int tb200_gemv_w8_noalloc(int cuda_ordinal, void* stream, const void* x_bf16, const void* w_i8,
+                                     const void* scale_bf16, void* y, int y_is_f32, int B, int N, int K,
+                                     int splits) {
+  using namespace tb200;
+  if (!x_bf16 || !w_i8 || !scale_bf16 || !y || B < 1 || B > 32 || N < 1 || K < 16 || (K % 16) != 0 ||
+      cuda_ordinal < 0 || cuda_ordinal >= kMaxDevices)
+    return 3;
+  if (splits <= 0) splits = gemv_w8_splits(B, N, K);
+  if ((size_t)splits * (size_t)B * (size_t)N > kNoAllocScratchFloats) {
+    fprintf(stderr,
+            "tb200_gemv_w8_noalloc: %d slices x batch %d x %d columns = %zu partial sums exceed the fixed scratch of "
+            "%zu floats; use fewer slices or the executable path\n",
+            splits, B, N, (size_t)splits * B * N, (size_t)kNoAllocScratchFloats);
+    return 11;
+  }
+  if (cudaSetDevice(cuda_ordinal) != cudaSuccess) return 13;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_scratch_ptr[cuda_ordinal]) {
+      // In host code the array's name is only a handle: the device address has to be asked for,
+      // once per device, with that device current.
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_noalloc_gemv_scratch) != cudaSuccess || !p) return 13;
+      g_noalloc_scratch_ptr[cuda_ordinal] = (float*)p;
+    }
+    scratch = g_noalloc_scratch_ptr[cuda_ordinal];
+  }
+  launch_gemv_w8((const uint16_t*)x_bf16, (const int8_t*)w_i8, (const uint16_t*)scale_bf16, y, y_is_f32 ? 1 : 0, scratch,
+                 B, N, K, splits, (cudaStream_t)stream);
+  return cudaGetLastError() == cudaSuccess ? 0 : 13;
+}

@@ -72,6 +72,8 @@ _SIGNATURES = {
     "tb200_wait": (C.c_int, [C.c_void_p, C.c_uint64]),
     "tb200_invoke_host": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "tb200_invoke_host_async": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "tb200_gemv_w8_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                        C.c_int, C.c_int, C.c_int, C.c_int]),
     "tb200_executable_profile_ops": (C.c_int, [C.c_void_p, C.POINTER(Binding), C.c_size_t, C.c_int, C.c_int,
                                                C.POINTER(C.c_float), C.c_uint32]),
 }
