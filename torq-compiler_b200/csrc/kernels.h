@@ -130,6 +130,40 @@ void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t 
 size_t argmax_scratch_bytes(int B);
 void launch_argmax(const void* logits, int is_f32, int32_t* out, void* scratch, int B, int V, cudaStream_t stream);
 
+// ---- whole decode step as one persistent kernel (decode_step.cu) ----
+// Byte offsets: weights and norm vectors into the constant image, caches into the arena.
+struct DecodeLayerDesc {
+  unsigned long long w_qkv, s_qkv, w_o, s_o, w_gu, s_gu, w_down, s_down;
+  unsigned long long in_norm, post_attn_norm, pre_ffn_norm, post_ffn_norm, q_norm, k_norm;
+  unsigned long long kcache, vcache;
+  float theta;
+  int window;
+  int rope_table;  // which of DecodeStepArgs::theta this layer rotates with
+  int pad_;
+};
+struct DecodeStepArgs {
+  const char* consts;
+  char* arena;
+  char* scratch;
+  const int32_t* tokens;  // [B]
+  const int32_t* pos;     // [1]
+  int32_t* out_ids;       // [B]
+  float* logits;          // [B, V] or null
+  int* status;            // device status word
+  unsigned long long layers_off, embed_w, embed_s, final_norm;  // constant-image offsets
+  unsigned long long counter_off, qkv_off, o_off, act_off, d_off, attn_ml_off, attn_part_off, attn_out_off, amax_off;  // scratch offsets
+  unsigned long long trace_off;  // scratch offset of the stage timestamps, 0 = tracing off
+  int trace_len;
+  int n_layers, B, H, n_q, I, V, T;
+  int attn_slices, nslots, xin_stride, xin_bytes, grid;
+  float eps, attn_scale, embed_mult;
+  float theta[2];  // the (at most two) RoPE bases of the layers
+};
+bool decode_step_supported(int B, int H, int n_q, int n_kv, int D, int I, int V);
+// fills the scratch offsets and the slice count of `offsets`; returns the scratch size
+size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int sm_count, DecodeStepArgs* offsets);
+cudaError_t launch_decode_step(DecodeStepArgs a, cudaStream_t stream);
+
 void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream);
 
 }  // namespace tb200

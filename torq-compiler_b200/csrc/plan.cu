@@ -183,6 +183,170 @@ bool force_simt() {
   return e && *e && *e != '0';
 }
 
+
+bool decode_per_op() {
+  const char* e = getenv("TB200_DECODE_PER_OP");
+  return e && *e && *e != '0';
+}
+
+// Recognises the whole-graph shape of one decode step (embed; per layer rmsnorm, gemv,
+// rope_kv, attn_decode, gemv, rmsnorm+residual, rmsnorm, gemv, geglu, gemv, rmsnorm+residual;
+// final rmsnorm, gemv to fp32 logits, argmax) and replaces its per-op launches by the one
+// persistent kernel of decode_step.cu. Anything that does not fit exactly keeps the per-op plan.
+bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
+  const auto& ops = b.ops;
+  const auto& T = b.tensors;
+  const int n = (int)ops.size();
+  if (decode_per_op() || n < 15 || (n - 4) % 11 != 0) return false;
+  const int L = (n - 4) / 11;
+  static const uint32_t layer_kinds[11] = {TB200_OP_RMSNORM, TB200_OP_GEMV_W8, TB200_OP_ROPE_KV, TB200_OP_ATTN_DECODE,
+                                           TB200_OP_GEMV_W8, TB200_OP_RMSNORM, TB200_OP_RMSNORM, TB200_OP_GEMV_W8,
+                                           TB200_OP_GEGLU,   TB200_OP_GEMV_W8, TB200_OP_RMSNORM};
+  if (ops[0].kind != TB200_OP_EMBED || ops[n - 3].kind != TB200_OP_RMSNORM || ops[n - 2].kind != TB200_OP_GEMV_W8 ||
+      ops[n - 1].kind != TB200_OP_ARGMAX)
+    return false;
+  for (int l = 0; l < L; l++)
+    for (int k = 0; k < 11; k++)
+      if (ops[1 + 11 * l + k].kind != layer_kinds[k]) return false;
+  auto inter = [&](int id) { return id >= 0 && T[id].kind == TB200_TENSOR_ACTIVATION; };
+  const tb200_op_t& emb = ops[0];
+  const int tokens = emb.in0;
+  const int B = T[emb.in0].shape[0], V = T[emb.weights].shape[0], H = T[emb.weights].shape[1];
+  const tb200_op_t& first_rope = ops[3];
+  const int n_q = first_rope.i0, n_kv = first_rope.i1, D = first_rope.i2, pos = first_rope.in1;
+  const int I = T[ops[9].out0].shape[1];
+  const int Tlen = T[first_rope.out1].shape[1];
+  const float eps = ops[1].f0, attn_scale = ops[4].f0;
+  if (!decode_step_supported(B, H, n_q, n_kv, D, I, V)) return false;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return false;
+  // every CTA must own at least one row of every projection (the barrier protocol counts on it)
+  if (sms < 1 || H < sms || I < sms || V < sms || (n_q + 2) * D < sms) return false;
+  if (T[tokens].kind != TB200_TENSOR_INPUT || T[pos].kind != TB200_TENSOR_INPUT) return false;
+
+  std::vector<DecodeLayerDesc> descs(L);
+  float thetas[2] = {0.f, 0.f};
+  size_t off = 0;
+  auto cst = [&](int id, size_t bytes, unsigned long long& dst) {
+    if (!b.add_raw_const(id, bytes, "decode-step constant", 0, off)) return false;
+    dst = off;
+    return true;
+  };
+  auto gemv_ok = [&](const tb200_op_t& g, int in, int N, int K, bool f32) {
+    return g.in0 == in && inter(in) && T[g.weights].rank == 2 && T[g.weights].shape[0] == N && T[g.weights].shape[1] == K &&
+           T[g.out0].dtype == (f32 ? TB200_F32 : TB200_BF16) && T[g.in0].shape[0] == B;
+  };
+  auto norm_ok = [&](const tb200_op_t& r, int in, int res) {
+    return r.in0 == in && r.in1 == res && r.f0 == eps && T[r.in0].shape[1] == H && T[r.in0].shape[0] == B;
+  };
+  int x = emb.out0;
+  if (!inter(x)) return false;
+  for (int l = 0; l < L; l++) {
+    const tb200_op_t* o = &ops[1 + 11 * l];
+    DecodeLayerDesc& d = descs[l];
+    if (!norm_ok(o[0], x, -1) || !gemv_ok(o[1], o[0].out0, (n_q + 2) * D, H, false)) return false;
+    const tb200_op_t& rope = o[2];
+    const tb200_op_t& att = o[3];
+    if (rope.in0 != o[1].out0 || !inter(rope.in0) || rope.in1 != pos || rope.i0 != n_q || rope.i1 != n_kv || rope.i2 != D ||
+        rope.f1 != eps || T[rope.out1].shape[1] != Tlen || !inter(rope.out0))
+      return false;
+    if (att.in0 != rope.out0 || att.in1 != pos || att.in2 != rope.out1 || att.weights != rope.in2 || att.i0 != n_q ||
+        att.i1 != n_kv || att.i2 != D || att.f0 != attn_scale || att.i3 < 0)
+      return false;
+    if (!gemv_ok(o[4], att.out0, H, n_q * D, false) || !norm_ok(o[5], o[4].out0, x) || !inter(o[4].out0)) return false;
+    x = o[5].out0;
+    if (!inter(x) || !norm_ok(o[6], x, -1) || !gemv_ok(o[7], o[6].out0, 2 * I, H, false)) return false;
+    if (o[8].in0 != o[7].out0 || !inter(o[8].in0) || T[o[8].out0].shape[1] != I) return false;
+    if (!gemv_ok(o[9], o[8].out0, H, I, false) || !norm_ok(o[10], o[9].out0, x) || !inter(o[9].out0)) return false;
+    x = o[10].out0;
+    if (!inter(x)) return false;
+    if (!cst(o[0].weights, (size_t)H * 2, d.in_norm) || !cst(o[1].weights, (size_t)(n_q + 2) * D * H, d.w_qkv) ||
+        !cst(o[1].bias, (size_t)(n_q + 2) * D * 2, d.s_qkv) || !cst(rope.weights, (size_t)D * 2, d.q_norm) ||
+        !cst(rope.bias, (size_t)D * 2, d.k_norm) || !cst(o[4].weights, (size_t)H * n_q * D, d.w_o) ||
+        !cst(o[4].bias, (size_t)H * 2, d.s_o) || !cst(o[5].weights, (size_t)H * 2, d.post_attn_norm) ||
+        !cst(o[6].weights, (size_t)H * 2, d.pre_ffn_norm) || !cst(o[7].weights, (size_t)2 * I * H, d.w_gu) ||
+        !cst(o[7].bias, (size_t)2 * I * 2, d.s_gu) || !cst(o[9].weights, (size_t)H * I, d.w_down) ||
+        !cst(o[9].bias, (size_t)H * 2, d.s_down) || !cst(o[10].weights, (size_t)H * 2, d.post_ffn_norm))
+      return false;
+    d.kcache = plan.tensor_loc[rope.out1].offset;
+    d.vcache = plan.tensor_loc[rope.in2].offset;
+    d.theta = rope.f0;
+    d.window = att.i3;
+    // at most two RoPE bases (local and global layers) share the kernel's two tables
+    if (l == 0) thetas[0] = thetas[1] = rope.f0;
+    if (rope.f0 == thetas[0]) d.rope_table = 0;
+    else if (thetas[1] == thetas[0] || rope.f0 == thetas[1]) { thetas[1] = rope.f0; d.rope_table = 1; }
+    else return false;
+    // the fp16 copy of a normed vector is exact only while |1 + w| stays moderate
+    for (int id : {o[0].weights, o[5].weights, o[6].weights, o[10].weights}) {
+      const uint16_t* w = b.const_data<uint16_t>(id, H, "norm weight", 0);
+      if (!w) return false;
+      for (int i = 0; i < H; i++) {
+        const uint32_t bits = (uint32_t)w[i] << 16;
+        float f;
+        memcpy(&f, &bits, 4);
+        if (!(f > -257.0f && f < 255.0f)) return false;
+      }
+    }
+  }
+  const tb200_op_t& nf = ops[n - 3];
+  const tb200_op_t& lm = ops[n - 2];
+  const tb200_op_t& am = ops[n - 1];
+  if (!norm_ok(nf, x, -1) || !gemv_ok(lm, nf.out0, V, H, true) || lm.weights != emb.weights || lm.bias != emb.bias ||
+      am.in0 != lm.out0 || T[am.out0].kind != TB200_TENSOR_OUTPUT || T[am.out0].shape[0] != B)
+    return false;
+  const bool logits_out = T[lm.out0].kind == TB200_TENSOR_OUTPUT;
+  if (!logits_out && !inter(lm.out0)) return false;
+
+  DecodeStepArgs a{};
+  if (!cst(emb.weights, (size_t)V * H, a.embed_w) || !cst(emb.bias, (size_t)V * 2, a.embed_s) ||
+      !cst(nf.weights, (size_t)H * 2, a.final_norm))
+    return false;
+  a.layers_off = b.add_const(descs.data(), descs.size() * sizeof(DecodeLayerDesc));
+  a.n_layers = L; a.B = B; a.H = H; a.n_q = n_q; a.I = I; a.V = V; a.T = Tlen;
+  a.eps = eps; a.attn_scale = attn_scale; a.embed_mult = emb.f0; a.grid = sms;
+  a.theta[0] = thetas[0]; a.theta[1] = thetas[1];
+  scratch_need = std::max(scratch_need, decode_step_scratch_bytes(B, H, n_q, I, L, sms, &a));
+  const Loc ltok = plan.tensor_loc[tokens], lpos = plan.tensor_loc[pos], lids = plan.tensor_loc[am.out0],
+            llog = plan.tensor_loc[lm.out0];
+  for (auto& st : plan.steps) {
+    st.kernel_name = "(in decode_step)";
+    st.launches = 0;
+    st.launch = [](const ExecContext&) {};
+  }
+  plan.steps[0].kernel_name = "decode_step_persistent";
+  plan.steps[0].launches = 1;
+  // TB200_DECODE_TRACE=<file>: after every dispatch, wait for it and append CTA 0's stage
+  // timestamps (ns, one line per dispatch) to the file. For profiling only: it serialises.
+  const char* trace_env = getenv("TB200_DECODE_TRACE");
+  const std::string trace_path = trace_env ? trace_env : "";
+  if (trace_path.empty()) a.trace_off = 0;
+  plan.steps[0].launch = [=](const ExecContext& c) {
+    DecodeStepArgs k = a;
+    k.consts = c.consts; k.arena = c.arena; k.scratch = c.scratch; k.status = c.status;
+    k.tokens = (const int32_t*)ltok.resolve(c);
+    k.pos = (const int32_t*)lpos.resolve(c);
+    k.out_ids = (int32_t*)lids.resolve(c);
+    k.logits = logits_out ? (float*)llog.resolve(c) : nullptr;
+    const cudaError_t e = launch_decode_step(k, c.stream);
+    if (e != cudaSuccess && c.launch_error) *c.launch_error = e;
+    if (e == cudaSuccess && !trace_path.empty() && cudaStreamSynchronize(c.stream) == cudaSuccess) {
+      std::vector<unsigned long long> t(k.trace_len);
+      if (cudaMemcpy(t.data(), c.scratch + k.trace_off, t.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
+        if (FILE* f = fopen(trace_path.c_str(), "a")) {
+          for (size_t i = 0; i < t.size(); i++) fprintf(f, "%llu%c", t[i] - t[0], i + 1 < t.size() ? ',' : '\n');
+          fclose(f);
+        }
+      }
+    }
+  };
+  plan.launch_count = 1;
+  plan.use_graph = false;    // one launch per dispatch: nothing for a graph to save
+  plan.zero_scratch = true;  // the grid-barrier counters start at zero
+  return true;
+}
+
 }  // namespace
 
 int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb200_op_t>& ops,
@@ -796,6 +960,8 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
     plan.launch_count += step.launches;
     plan.steps.push_back(std::move(step));
   }
+  try_fuse_decode_step(b, plan, scratch_need);
+  if (b.status != TB200_OK) return b.status;
   // scratch shared by the ops that need one, behind the activations
   plan.scratch_offset = (plan.arena_bytes + 255) & ~(size_t)255;
   plan.scratch_bytes = scratch_need;

@@ -22,6 +22,7 @@ struct ExecContext {
   cudaStream_t stream;
   int* status;      // device status word (0 = fine)
   char* scratch;    // per-dispatch scratch shared by the ops that need one (split-K partials, ...)
+  cudaError_t* launch_error;  // a step whose launcher refuses (not a CUDA launch failure) records why here
 };
 
 // Where a tensor lives at dispatch time.
@@ -52,6 +53,8 @@ struct Plan {
   size_t launch_count = 0;
   size_t scratch_offset = 0;      // scratch sits behind the activations inside the arena allocation
   size_t scratch_bytes = 0;
+  bool zero_scratch = false;      // the scratch must read as zero before the first dispatch
+  bool use_graph = true;          // replay the launch list as a CUDA graph
   std::vector<Loc> tensor_loc;
 };
 

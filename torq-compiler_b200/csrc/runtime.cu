@@ -353,6 +353,8 @@ extern "C" int tb200_executable_create(tb200_device_t* d, const void* bytes, siz
     // persistent state tensors live at the front of the arena and start at zero
     e = cudaMemsetAsync(ex->arena, 0, ex->plan.state_bytes, d->stream);
   }
+  if (e == cudaSuccess && ex->plan.zero_scratch && ex->plan.scratch_bytes)
+    e = cudaMemsetAsync((char*)ex->arena + ex->plan.scratch_offset, 0, ex->plan.scratch_bytes, d->stream);
   if (e != cudaSuccess) {
     st = fail(d, e == cudaErrorMemoryAllocation ? TB200_RESOURCE_EXHAUSTED : TB200_INTERNAL,
               "executable memory: %s", cudaGetErrorString(e));
@@ -453,11 +455,14 @@ int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cud
   ctx.stream = d->stream;
   ctx.status = d->status_word;
   ctx.scratch = (char*)ex->arena + ex->plan.scratch_offset;
+  cudaError_t launch_error = cudaSuccess;
+  ctx.launch_error = &launch_error;
   for (size_t i = 0; i < ex->plan.steps.size(); i++) {
     if (events) cudaEventRecord((*events)[i], d->stream);
     ex->plan.steps[i].launch(ctx);
   }
   if (events) cudaEventRecord((*events)[ex->plan.steps.size()], d->stream);
+  CUDA_OK(d, launch_error);
   CUDA_OK(d, cudaGetLastError());
   return TB200_OK;
 }
@@ -521,7 +526,7 @@ extern "C" int tb200_dispatch(tb200_executable_t* ex, const tb200_binding_t* bin
   std::vector<void*> io;
   int st = resolve_bindings(ex, bindings, n, io);
   if (st != TB200_OK) return st;
-  if (!d->profile_csv) return use_graphs() ? run_graph(ex, io) : run_plan(ex, io, nullptr);
+  if (!d->profile_csv) return use_graphs() && ex->plan.use_graph ? run_graph(ex, io) : run_plan(ex, io, nullptr);
 
   // profiled dispatch: bracket every op with events and write the reference's CSV schema
   size_t ns = ex->plan.steps.size();
