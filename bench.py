@@ -97,18 +97,24 @@ def cpu_oracle_throughput(batch_sample: int, repeats: int):
     return batch_sample / float(np.median(times)), oc.num_threads(), times
 
 
-def decoder_bench(dev, stream, batch: int, prompt_len: int = 1024, gen_len: int = 128):
+def decoder_bench(dev, stream, batch: int, prompt_len: int = 1024, gen_len: int = 128, tp: int = 1, rank: int = 0):
     """Gemma-3-1B-architecture int8-weight greedy decode (second metric of the benchmark set):
-    tokens/s over `gen_len` decode steps after a `prompt_len`-token seeded prompt, one GPU.
-    Every step is one dispatch (CUDA-graph replay); the next token and position move on the device."""
+    tokens/s over `gen_len` decode steps after a `prompt_len`-token seeded prompt. One GPU, or
+    (tp > 1, every rank of the process group calls this) tensor-parallel over tp GPUs: each rank
+    runs its shard, the shards exchange partial results through peer memory inside the step kernel.
+    Every step is one dispatch; the next token and position move on the device."""
     import torch
     from torq_b200.runtime import MEMORY_HOST_PINNED, Executable
     from torq_b200.workloads import gemma3
     cfg = gemma3.GemmaConfig()
     params = gemma3.random_weights(cfg, 1234)
-    g = gemma3.build_decode_step(cfg, batch, params)
+    if tp > 1:
+        params = gemma3.shard_weights(cfg, params, tp, rank)
+    g = gemma3.build_decode_step(cfg, batch, params, tp=tp, rank=rank)
     ex = Executable(dev, g.serialize())
     del params, g
+    if tp > 1:
+        ex.connect_group()
     rng = np.random.default_rng(1234)
     prompt = rng.integers(0, cfg.vocab, (prompt_len, batch)).astype(np.int32)
     steps = prompt_len + gen_len
@@ -137,6 +143,11 @@ def decoder_bench(dev, stream, batch: int, prompt_len: int = 1024, gen_len: int 
     dev.wait(300.0)
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
+    if tp > 1:  # the slowest rank's time counts
+        import torch.distributed as dist
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     last = d_next.download((batch,), np.int32)
     wbytes = gemma3.weight_bytes_per_token(cfg)
     kv_bytes = sum(2 * min(steps, cfg.max_seq if cfg.is_global(l) else cfg.window) * cfg.head_dim * 2 for l in range(cfg.layers)) * batch
@@ -145,7 +156,7 @@ def decoder_bench(dev, stream, batch: int, prompt_len: int = 1024, gen_len: int 
     for b in (h_tok, h_pos, d_tok, d_pos, d_next):
         b.free()
     step_ms = ms / gen_len
-    return {"batch": batch, "tok_per_s": batch * gen_len / (ms * 1e-3), "ms_per_step": step_ms,
+    return {"batch": batch, "tp": tp, "tok_per_s": batch * gen_len / (ms * 1e-3), "ms_per_step": step_ms,
             "weight_bytes_per_step": wbytes, "kv_bytes_per_step": kv_bytes,
             "hbm_gbs": (wbytes + kv_bytes) / (step_ms * 1e-3) / 1e9, "launches_per_step": launches,
             "last_tokens": [int(t) for t in last[:4]]}
@@ -277,6 +288,19 @@ def main():
     e2e_value = B * world * e2e_steps / (ms_e2e * 1e-3)
     clocks = sampler.stop() if sampler else None
 
+    # ---- tensor-parallel decode over all ranks (the group size must divide the 4 query heads) ----
+    decoder_tp = None
+    if world > 1 and args.decoder and 4 % world == 0:
+        decoder_tp = []
+        for bsz in [int(t) for t in args.decoder.split(",") if t]:
+            if bsz > 8:
+                continue  # the fused step kernel takes up to 8 sequences
+            try:
+                decoder_tp.append(decoder_bench(dev, stream, bsz, tp=world, rank=rank))
+            except Exception as e:
+                decoder_tp.append({"batch": bsz, "tp": world, "error": repr(e)[:200]})
+                break
+
     if rank != 0:
         barrier()
         if world > 1:
@@ -337,6 +361,11 @@ def main():
                 decoder["runs"].append(r)
             except Exception as e:  # the headline line must still print
                 decoder["runs"].append({"batch": bsz, "error": repr(e)[:200]})
+        if decoder_tp:
+            for r in decoder_tp:
+                if "hbm_gbs" in r:  # per-GPU share of the bytes against one GPU's bandwidth
+                    r["hbm_frac_per_gpu"] = r["hbm_gbs"] / r["tp"] / peaks["hbm_gbs"]
+            decoder["tensor_parallel_runs"] = decoder_tp
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

@@ -144,6 +144,21 @@ int tb200_executable_profile_ops(tb200_executable_t* executable, const tb200_bin
 /* Name of the kernel the plan picked for op `index` (static string). */
 const char* tb200_executable_op_kernel(tb200_executable_t* executable, uint32_t index);
 
+/* ---- tensor-parallel groups (LLM decode split over the GPUs of one node) ----
+ * The reference's device offers no collectives (create_channel and the collective commands are
+ * UNIMPLEMENTED, runtime/driver/torq_device.c:235-240): these three calls are what a HAL channel
+ * for this backend would be built on. An executable whose op list holds TB200_OP_ALLREDUCE ops is
+ * one shard of a group (rank and size are read from the ops). One process per GPU: each member
+ * asks for its handle, the handles travel out of band (any host transport), and every member
+ * connects with the full, rank-ordered list before its first dispatch. From then on a dispatch
+ * must be made by every member: the decode-step kernels of the members exchange their partial
+ * results through each other's memory (peer stores) and wait for one another (bounded: a member
+ * that never shows up ends the others' dispatch with TB200_ABORTED from tb200_wait). */
+typedef struct tb200_comm_handle_t { unsigned char bytes[96]; } tb200_comm_handle_t;
+int tb200_executable_comm_info(tb200_executable_t* executable, int32_t* rank, int32_t* group_size);
+int tb200_executable_comm_handle(tb200_executable_t* executable, tb200_comm_handle_t* out);
+int tb200_executable_connect_peers(tb200_executable_t* executable, const tb200_comm_handle_t* handles, size_t n);
+
 /* No counterpart in the reference. The split-K int8-weight GEMV (y[b,n] = scale[n] * sum_k
  * x[b,k] * W[n,k]; x bf16 [B,K], W int8 [N,K], scale bf16 [N], y bf16 or fp32 [B,N]) for
  * callers that cannot allocate: a host whose own allocator already holds all device memory,

@@ -78,7 +78,10 @@ enum tb200_op_kind {
   TB200_OP_ATTN_DECODE = 36,  /* single-query GQA attention over the cache */
   TB200_OP_GEGLU = 37,        /* y = gelu_tanh(gate) * up */
   TB200_OP_ADD_BF16 = 38,     /* residual add */
-  TB200_OP_ARGMAX = 39,       /* greedy token id from logits */
+  TB200_OP_ARGMAX = 39,       /* greedy token id from logits; i1 >= 2: over the shards of a tensor-parallel
+                               * group of i1 GPUs, this shard's ids offset by i0 */
+  TB200_OP_ALLREDUCE = 40,    /* sum of the fp32 partial results of the i0 GPUs of a tensor-parallel group
+                               * (this one is rank i1), rounded to bf16; only inside the fused decode step */
 };
 
 enum tb200_requant_mode {

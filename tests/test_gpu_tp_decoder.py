@@ -1,0 +1,37 @@
+"""Tensor-parallel decode over 2 (and 4) GPUs of one node: one process per GPU, the shards'
+decode-step kernels exchange partial results through peer memory. Needs at least two GPUs
+(skipped otherwise); the check itself runs in tests/tp_decode_worker.py."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(world, size, batch, steps, gain, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "tp_decode_worker.py"), size, str(batch), str(steps), str(gain)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("TP_RESULT ")][-1]
+    return json.loads(line[len("TP_RESULT "):])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_decode_matches_unsharded_reference(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    # peaked logits (embedding gain 0.3): ids must agree, logits within 1e-2 of the unsharded fp32 reference
+    r = _run(world, "small", 2, 40, 0.3, 29500 + world)
+    assert r["worst_rel"] <= 1e-2, r
+    assert r["agree"] == r["total"], r
+    # flat logits: tolerance 3e-2, most ids agree
+    r = _run(world, "small", 1, 40, 0.02, 29510 + world)
+    assert r["worst_rel"] <= 3e-2, r
+    assert r["agree"] >= 0.8 * r["total"], r

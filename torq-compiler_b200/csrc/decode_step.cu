@@ -115,28 +115,57 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
-__device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-// Grid barrier, arrival side: everything this thread (and, through the preceding CTA-level
-// synchronisation, its CTA) wrote is made visible before the count goes up.
-__device__ __forceinline__ void grid_arrive(unsigned int* counter) {
-  __threadfence();
-  atomicAdd(counter, 1u);
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
 }
-// Grid barrier, waiting side (one thread per CTA). Bounded like mbar_wait.
-__device__ __forceinline__ bool grid_wait(const unsigned int* counter, unsigned int target, int* status, bool ok) {
+// Grid barriers. Counters only ever grow (64 bits): a launch starts from the bases its
+// predecessor left behind and adds one count per CTA per barrier. Barriers inside one GPU use
+// the local counter. A barrier that spans the tensor-parallel peers uses one of two counters in
+// alternation (so that a GPU that is one barrier ahead never adds to the counter its peers are
+// still waiting on); every CTA of every GPU adds to that counter on every GPU through peer
+// memory, its own GPU's first.
+// Counter block (byte offsets): local 0, global 8 and 16, their bases 24, 32, 40, exit count 48.
+struct BarrierState {
+  unsigned long long local, global[2];  // expected values
+  int parity;
+};
+// Arrival side: everything this thread (and, through the preceding CTA-level synchronisation,
+// its CTA) wrote is made visible before the count goes up.
+__device__ __forceinline__ void grid_arrive(const DecodeStepArgs& a, bool all_gpus, int parity) {
+  if (all_gpus && a.tp > 1) {
+    __threadfence_system();
+    const unsigned long long off = a.counter_off + 8 + 8 * parity;
+    const unsigned long long old = atomicAdd_system((unsigned long long*)(a.scratch + off), 1ull);
+    // the peers' counters are touched only after this GPU's own count is in (address depends on it)
+    const unsigned long long dep = old & 0x8000000000000000ull;  // always zero
+    for (int r = 0; r < a.tp; r++)
+      if (r != a.rank) atomicAdd_system((unsigned long long*)(a.peer_scratch[r] + off + dep), 1ull);
+  } else {
+    __threadfence();
+    atomicAdd((unsigned long long*)(a.scratch + a.counter_off), 1ull);
+  }
+}
+// Waiting side (one thread per CTA). Bounded like mbar_wait.
+__device__ __forceinline__ bool grid_wait(const DecodeStepArgs& a, bool all_gpus, int parity, unsigned long long target,
+                                          int* status, bool ok) {
   if (!ok) return false;
+  const bool sys = all_gpus && a.tp > 1;
+  const unsigned long long* counter = (const unsigned long long*)(a.scratch + a.counter_off + (sys ? 8 + 8 * parity : 0));
 #pragma unroll 1
   for (int i = 0; i < 4096; i++)
-    if (ld_acquire(counter) >= target) return true;
+    if ((sys ? ld_acquire_sys(counter) : ld_acquire_gpu(counter)) >= target) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; i++)
-      if (ld_acquire(counter) >= target) return true;
+      if ((sys ? ld_acquire_sys(counter) : ld_acquire_gpu(counter)) >= target) return true;
     if (*(volatile int*)status != 0) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       atomicCAS(status, 0, (int)kErrGrid);
@@ -217,7 +246,7 @@ __device__ __forceinline__ Phase make_phase(const DecodeStepArgs& a, const Decod
       p.K = a.H; p.N = a.I; p.kind = kPairs; break;
     case kDown: p.W = (const int8_t*)(a.consts + L->w_down); p.scale = (const uint16_t*)(a.consts + L->s_down);
       p.K = a.I; p.N = a.H; break;
-    default: p.W = (const int8_t*)(a.consts + a.embed_w); p.scale = (const uint16_t*)(a.consts + a.embed_s);
+    default: p.W = (const int8_t*)(a.consts + a.lm_w); p.scale = (const uint16_t*)(a.consts + a.lm_s);
       p.K = a.H; p.N = a.V; p.kind = kLogits; break;
   }
   p.first = a_first[which];
@@ -330,9 +359,21 @@ __device__ __forceinline__ NormWeights load_norm_weights(const uint16_t* w_post,
 //   if src: xs <- bf16(xs + bf16(src * rsqrt(mean(src^2) + eps) * (1 + w_post)))
 //   xin    <- fp16(bf16(xs * rsqrt(mean(xs^2) + eps) * (1 + w_pre)))   (exact: |value| <= sqrt(H) * |1 + w|)
 // src is a [B, H] bf16 tensor in global memory written by other CTAs before the last barrier.
+// With tensor parallelism the projection's output arrives as one fp32 partial result per GPU
+// (inbox [tp][B][H] at byte offset `inbox` of the scratch area); they are added in rank order
+// and rounded to bf16, the same on every GPU.
+__device__ __forceinline__ float load_projection(const DecodeStepArgs& a, const uint16_t* src, unsigned long long inbox, int b,
+                                                 int i) {
+  if (a.tp <= 1) return bf2f(__ldcg(src + (size_t)b * a.H + i));
+  const float* in = (const float*)(a.scratch + inbox);
+  float s = 0.f;
+  for (int r = 0; r < a.tp; r++) s += __ldcg(in + ((size_t)r * a.B + b) * a.H + i);
+  return rbf(s);
+}
 template <int BT>
-__device__ __forceinline__ void residual_norm(const DecodeStepArgs& a, const uint16_t* src, const NormWeights& nw,
-                                              uint16_t* xs, char* xin, int xin_stride, float* red, int tid) {
+__device__ __forceinline__ void residual_norm(const DecodeStepArgs& a, const uint16_t* src, unsigned long long inbox,
+                                              const NormWeights& nw, uint16_t* xs, char* xin, int xin_stride, float* red,
+                                              int tid) {
   const int H = a.H;
   float ss[BT];
   if (src) {
@@ -343,7 +384,7 @@ __device__ __forceinline__ void residual_norm(const DecodeStepArgs& a, const uin
 #pragma unroll
       for (int e = 0; e < kNormElems; e++) {
         const int i = tid + e * kConsumerThreads;
-        sv[b][e] = (b < a.B && i < H) ? bf2f(__ldcg(src + (size_t)b * H + i)) : 0.f;
+        sv[b][e] = (b < a.B && i < H) ? load_projection(a, src, inbox, b, i) : 0.f;
         ss[b] += sv[b][e] * sv[b][e];
       }
     }
@@ -878,7 +919,8 @@ __device__ __forceinline__ TileScales load_tile_scales(const Phase& p, int t, in
   return s;
 }
 __device__ __forceinline__ void reduce_phase(const DecodeStepArgs& a, const Phase& p, const Smem& sm, int nslots,
-                                             RingPos& tile, int* status, bool& ok, int lane, void* out, ArgBest* best) {
+                                             RingPos& tile, int* status, bool& ok, int lane, void* out, unsigned long long inbox,
+                                             ArgBest* best) {
   const int g = lane >> 2, tig = lane & 3;
   const float* xscale = (const float*)(sm.base + sm.off_red + kRedXscale);
   // the scales of the next tiles are requested ahead: their latency must not sit between two tiles
@@ -905,7 +947,20 @@ __device__ __forceinline__ void reduce_phase(const DecodeStepArgs& a, const Phas
     if (lane == 0 && ok) mbar_arrive(sm.bars + 8 * (2 * nslots + 2 + buf));
     c[0] *= xs0; c[1] *= xs1; c[2] *= xs0; c[3] *= xs1;  // exact: powers of two
     const float s_lo = cur.lo, s_hi = cur.hi;
-    if (p.kind == kRows) {
+    if (p.kind == kRows && inbox) {
+      // tensor parallel, K split over the GPUs: fp32 partial result to every GPU's inbox [rank][B][N]
+      for (int r = 0; r < a.tp; r++) {
+        float* y = (float*)(a.peer_scratch[r] + inbox) + (size_t)a.rank * a.B * p.N;
+        if (r_lo >= 0) {
+          if (b0 < a.B) y[(size_t)b0 * p.N + r_lo] = c[0] * s_lo;
+          if (b1 < a.B) y[(size_t)b1 * p.N + r_lo] = c[1] * s_lo;
+        }
+        if (r_hi >= 0) {
+          if (b0 < a.B) y[(size_t)b0 * p.N + r_hi] = c[2] * s_hi;
+          if (b1 < a.B) y[(size_t)b1 * p.N + r_hi] = c[3] * s_hi;
+        }
+      }
+    } else if (p.kind == kRows) {
       uint16_t* y = (uint16_t*)out;
       if (r_lo >= 0) {
         if (b0 < a.B) y[(size_t)b0 * p.N + r_lo] = f2bf(c[0] * s_lo);
@@ -933,7 +988,7 @@ __device__ __forceinline__ void reduce_phase(const DecodeStepArgs& a, const Phas
           if (a.logits) a.logits[(size_t)bb * p.N + rr[q]] = v[q];
           if (v[q] > best->v[q & 1]) {  // rows are visited in rising order: ties keep the lower index
             best->v[q & 1] = v[q];
-            best->i[q & 1] = rr[q];
+            best->i[q & 1] = rr[q] + a.vocab_offset;
           }
         }
       }
@@ -959,7 +1014,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
   sm.bars = sm.ring + sm.off_bars;
   const int xin_stride = a.xin_stride;
   const DecodeLayerDesc* layers = (const DecodeLayerDesc*)(a.consts + a.layers_off);
-  unsigned int* counter = (unsigned int*)(a.scratch + a.counter_off);
+  const unsigned long long* bases = (const unsigned long long*)(a.scratch + a.counter_off + 24);
   int* status = a.status;
   volatile int* gave_up = (volatile int*)(smem_raw + sm.off_bars + 8 * (2 * nslots + 4));
 
@@ -988,6 +1043,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
   const int* row_first = (const int*)(smem_raw + sm.off_red + kRedRows);
   const int* row_count = row_first + 5;
   bool ok = true;
+  BarrierState bs;  // followed by the consumer threads; thread 0 stores it for the next launch
+  bs.local = bases[0];
+  bs.global[0] = bases[1];
+  bs.global[1] = bases[2];
+  bs.parity = 0;
   if (warp == kProducerWarp) {
     // ---------------- producer: stream this CTA's weight rows, in consumption order ----------------
     RingPos pc{0, 0};
@@ -1034,6 +1094,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
   } else if (warp == kReducerWarp) {
     // ---------------- reducer ----------------
     RingPos tiles{0, 0};
+    int gpar = 0;  // which of the two cross-GPU counters the next cross-GPU barrier uses
     ArgBest best;
     best.v[0] = best.v[1] = -INFINITY;
     best.i[0] = best.i[1] = 0x7fffffff;
@@ -1042,15 +1103,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       for (int which = kQkv; which <= kDown; which++) {
         const Phase p = make_phase(a, L, which, row_first, row_count);
         void* out = a.scratch + (which == kQkv ? a.qkv_off : which == kO ? a.o_off : which == kGateUp ? a.act_off : a.d_off);
-        reduce_phase(a, p, sm, nslots, tiles, status, ok, lane, out, &best);
-        __threadfence();
+        // o and down are split along K over the tensor-parallel GPUs: partial results to every inbox
+        const bool split_k = a.tp > 1 && (which == kO || which == kDown);
+        reduce_phase(a, p, sm, nslots, tiles, status, ok, lane, out,
+                     split_k ? (which == kO ? a.inbox_o_off : a.inbox_d_off) : 0ull, &best);
+        if (split_k) __threadfence_system();
+        else __threadfence();
         __syncwarp();
-        if (lane == 0) atomicAdd(counter, 1u);
+        if (lane == 0) grid_arrive(a, split_k, gpar);
+        if (split_k) gpar ^= 1;
       }
     }
     {
       const Phase p = make_phase(a, layers, kLmHead, row_first, row_count);
-      reduce_phase(a, p, sm, nslots, tiles, status, ok, lane, nullptr, &best);
+      reduce_phase(a, p, sm, nslots, tiles, status, ok, lane, nullptr, 0ull, &best);
       // lanes with the same token pair differ in bits 2..4
 #pragma unroll
       for (int q = 0; q < 2; q++) {
@@ -1067,15 +1133,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
         }
         const int bb = 2 * (lane & 3) + q;
         if ((lane >> 2) == 0 && bb < a.B) {
-          float* pv = (float*)(a.scratch + a.amax_off);
-          int* pi = (int*)(pv + (size_t)G * 8);
-          pv[blk * 8 + bb] = v;
-          pi[blk * 8 + bb] = i;
+          // every GPU collects every GPU's candidates: [rank][CTA][8] values, then the same of indices
+          for (int r = 0; r < a.tp; r++) {
+            float* pv = (float*)(a.peer_scratch[r] + a.amax_off);
+            int* pi = (int*)(pv + (size_t)a.tp * G * 8);
+            pv[((size_t)a.rank * G + blk) * 8 + bb] = v;
+            pi[((size_t)a.rank * G + blk) * 8 + bb] = i;
+          }
         }
       }
-      __threadfence();
+      if (a.tp > 1) __threadfence_system();
+      else __threadfence();
       __syncwarp();
-      if (lane == 0) atomicAdd(counter, 1u);
+      if (lane == 0) grid_arrive(a, true, gpar);
     }
   } else {
     // ---------------- consumers ----------------
@@ -1083,13 +1153,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
     char* xin = smem_raw + sm.off_xin;
     float* red = (float*)(smem_raw + sm.off_red);
     RingPos slots{0, 0}, tiles{0, 0};
-    unsigned int barrier_index = 0;
-    auto wait_grid = [&]() {
+    // all_gpus: the barrier follows a stage whose results cross the tensor-parallel GPUs
+    auto wait_grid = [&](bool all_gpus, bool poll = true) {
+      const bool sys = all_gpus && a.tp > 1;
+      unsigned long long target;
+      const int parity = bs.parity;
+      if (sys) {
+        target = (bs.global[parity] += (unsigned long long)G * a.tp);
+        bs.parity ^= 1;
+      } else {
+        target = (bs.local += (unsigned long long)G);
+      }
+      if (!poll) return;  // only the count is advanced
       if (tid == 0) {
-        const bool r = grid_wait(counter, (barrier_index + 1) * (unsigned int)G, status, ok);
+        const bool r = grid_wait(a, sys, parity, target, status, ok);
         if (!r) *gave_up = 1;
       }
-      barrier_index++;
       bar_consumers();
       if (*gave_up) ok = false;
     };
@@ -1106,7 +1185,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
     // embedding: xs[b, i] = bf16(bf16(E[tok, i] * scale[tok]) * mult)
     for (int b = 0; b < a.B; b++) {
       int tk = __ldg(a.tokens + b);
-      tk = tk < 0 ? 0 : (tk >= a.V ? a.V - 1 : tk);
+      tk = tk < 0 ? 0 : (tk >= a.V_embed ? a.V_embed - 1 : tk);
       const float s = bf2f(__ldg((const uint16_t*)(a.consts + a.embed_s) + tk));
       const int8_t* row = (const int8_t*)(a.consts + a.embed_w) + (size_t)tk * a.H;
       for (int i = tid; i < a.H; i += kConsumerThreads) xs[b * a.H + i] = f2bf(rbf((float)row[i] * s) * a.embed_mult);
@@ -1121,9 +1200,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       {
         const NormWeights nw = load_norm_weights(l > 0 ? (const uint16_t*)(a.consts + layers[l - 1].post_ffn_norm) : nullptr,
                                                  (const uint16_t*)(a.consts + L->in_norm), a.H, tid);
-        if (l > 0) wait_grid();
+        if (l > 0) wait_grid(true);  // the down projection's partial results come from every GPU
         trace_mark(a, blk, tid, mark);
-        residual_norm<BT>(a, l > 0 ? (const uint16_t*)(a.scratch + a.d_off) : nullptr, nw, xs, xin, xin_stride, red, tid);
+        residual_norm<BT>(a, l > 0 ? (const uint16_t*)(a.scratch + a.d_off) : nullptr, a.inbox_d_off, nw, xs, xin, xin_stride, red,
+                          tid);
       }
       trace_mark(a, blk, tid, mark);
       consume_phase(make_phase(a, L, kQkv, row_first, row_count), sm, nslots, a.B, xin_stride, slots, tiles, status, ok, warp, lane);
@@ -1131,23 +1211,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       // ---- attention over the cache: slices, barrier, merge ----
       {
         const HeadNormWeights hw = load_head_norm_weights(a, L, warp, lane);
-        wait_grid();
+        wait_grid(false);
         trace_mark(a, blk, tid, mark);
         for (int b = 0; b < a.B; b++) {
           attention_slice(a, L, sm, hw, b, blk, tid);
           bar_consumers();
         }
       }
-      if (tid == 0) grid_arrive(counter);
+      if (tid == 0) grid_arrive(a, false, 0);
       trace_mark(a, blk, tid, mark);
-      wait_grid();
+      wait_grid(false);
       trace_mark(a, blk, tid, mark);
       attention_merge(a, blk, tid);
       bar_consumers();
-      if (tid == 0) grid_arrive(counter);
+      if (tid == 0) grid_arrive(a, false, 0);
       trace_mark(a, blk, tid, mark);
       // ---- o projection ----
-      wait_grid();
+      wait_grid(false);
       trace_mark(a, blk, tid, mark);
       stage_attention<BT>(a, sm, xin_stride, tid);
       trace_mark(a, blk, tid, mark);
@@ -1157,15 +1237,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       {
         const NormWeights nw = load_norm_weights((const uint16_t*)(a.consts + L->post_attn_norm),
                                                  (const uint16_t*)(a.consts + L->pre_ffn_norm), a.H, tid);
-        wait_grid();
+        wait_grid(true);  // the o projection's partial results come from every GPU
         trace_mark(a, blk, tid, mark);
-        residual_norm<BT>(a, (const uint16_t*)(a.scratch + a.o_off), nw, xs, xin, xin_stride, red, tid);
+        residual_norm<BT>(a, (const uint16_t*)(a.scratch + a.o_off), a.inbox_o_off, nw, xs, xin, xin_stride, red, tid);
       }
       trace_mark(a, blk, tid, mark);
       consume_phase(make_phase(a, L, kGateUp, row_first, row_count), sm, nslots, a.B, xin_stride, slots, tiles, status, ok, warp, lane);
       trace_mark(a, blk, tid, mark);
       // ---- down projection ----
-      wait_grid();
+      wait_grid(false);
       trace_mark(a, blk, tid, mark);
       stage_activations<BT>(a, sm, xin_stride, tid);
       trace_mark(a, blk, tid, mark);
@@ -1175,23 +1255,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
     {
       const NormWeights nw = load_norm_weights((const uint16_t*)(a.consts + layers[a.n_layers - 1].post_ffn_norm),
                                                (const uint16_t*)(a.consts + a.final_norm), a.H, tid);
-      wait_grid();
+      wait_grid(true);
       trace_mark(a, blk, tid, mark);
-      residual_norm<BT>(a, (const uint16_t*)(a.scratch + a.d_off), nw, xs, xin, xin_stride, red, tid);
+      residual_norm<BT>(a, (const uint16_t*)(a.scratch + a.d_off), a.inbox_d_off, nw, xs, xin, xin_stride, red, tid);
     }
     trace_mark(a, blk, tid, mark);
     consume_phase(make_phase(a, layers, kLmHead, row_first, row_count), sm, nslots, a.B, xin_stride, slots, tiles, status, ok, warp, lane);
     trace_mark(a, blk, tid, mark);
+    wait_grid(true, blk == 0);  // only CTA 0 needs the other CTAs' candidates
     if (blk == 0) {
-      wait_grid();
       trace_mark(a, blk, tid, mark);
-      // greedy ids: best (value, lowest index) over the CTAs' partial results
+      // greedy ids: best (value, lowest index) over the candidates of every CTA of every GPU
+      const int cand = a.tp * G;
       const float* pv = (const float*)(a.scratch + a.amax_off);
-      const int* pi = (const int*)(pv + (size_t)G * 8);
+      const int* pi = (const int*)(pv + (size_t)cand * 8);
       if (warp < a.B) {
         float v = -INFINITY;
         int i = 0x7fffffff;
-        for (int c = lane; c < G; c += 32) {
+        for (int c = lane; c < cand; c += 32) {
           const float ov = __ldcg(pv + c * 8 + warp);
           const int oi = __ldcg(pi + c * 8 + warp);
           if (ov > v || (ov == v && oi < i)) {
@@ -1213,12 +1294,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
     }
   }
   __syncthreads();
-  // the last CTA to leave puts the barrier counters back to zero for the next launch
+  // the last CTA to leave stores where the counters will stand once this launch's counts are all
+  // in: the bases of the next launch
   if (tid == 0) {
-    const unsigned int old = atomicAdd(counter + 1, 1u);
+    unsigned int* exit_count = (unsigned int*)(a.scratch + a.counter_off + 48);
+    const unsigned int old = atomicAdd(exit_count, 1u);
     if (old == (unsigned int)G - 1) {
-      counter[0] = 0;
-      counter[1] = 0;
+      unsigned long long* next = (unsigned long long*)(a.scratch + a.counter_off + 24);
+      next[0] = bs.local;
+      next[1] = bs.global[0];
+      next[2] = bs.global[1];
+      *exit_count = 0;
       __threadfence();
     }
   }
@@ -1255,7 +1341,7 @@ SmemPlan plan_smem(int B, int H, int n_q, int I, int max_bytes) {
 }
 }  // namespace
 
-size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int sm_count, DecodeStepArgs* offsets) {
+size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int sm_count, int tp, DecodeStepArgs* offsets) {
   // qkv | o | act | d (bf16), attention partials, arg-max partials, barrier counters
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -1272,7 +1358,9 @@ size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int
   offsets->attn_out_off = take((size_t)B * n_q * kD * 2);
   offsets->attn_ml_off = take((size_t)B * n_q * sm_count * 8);
   offsets->attn_part_off = take((size_t)B * n_q * sm_count * kD * 4);
-  offsets->amax_off = take((size_t)sm_count * 8 * 8);
+  offsets->amax_off = take((size_t)tp * sm_count * 8 * 8);
+  offsets->inbox_o_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
+  offsets->inbox_d_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
   offsets->trace_len = 16 * n_layers + 8;
   offsets->trace_off = take((size_t)offsets->trace_len * 8);
   return off;

@@ -150,18 +150,24 @@ struct DecodeStepArgs {
   int32_t* out_ids;       // [B]
   float* logits;          // [B, V] or null
   int* status;            // device status word
-  unsigned long long layers_off, embed_w, embed_s, final_norm;  // constant-image offsets
+  unsigned long long layers_off, embed_w, embed_s, lm_w, lm_s, final_norm;  // constant-image offsets
   unsigned long long counter_off, qkv_off, o_off, act_off, d_off, attn_ml_off, attn_part_off, attn_out_off, amax_off;  // scratch offsets
   unsigned long long trace_off;  // scratch offset of the stage timestamps, 0 = tracing off
   int trace_len;
-  int n_layers, B, H, n_q, I, V, T;
+  int n_layers, B, H, n_q, I, V, V_embed, T;  // V: rows of the LM head (this GPU's shard), V_embed: of the embedding table
   int attn_slices, nslots, xin_stride, xin_bytes, grid;
   float eps, attn_scale, embed_mult;
   float theta[2];  // the (at most two) RoPE bases of the layers
+  // tensor parallelism: this GPU's rank, the group size, every member's scratch area as mapped
+  // into this process (peer_scratch[rank] == scratch), the inboxes of the K-split projections
+  // (scratch offsets, fp32 [tp][B][H]) and the first vocabulary row of this GPU's LM-head shard
+  int tp, rank, vocab_offset, pad_;
+  unsigned long long inbox_o_off, inbox_d_off;
+  char* peer_scratch[8];
 };
 bool decode_step_supported(int B, int H, int n_q, int n_kv, int D, int I, int V);
 // fills the scratch offsets and the slice count of `offsets`; returns the scratch size
-size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int sm_count, DecodeStepArgs* offsets);
+size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int sm_count, int tp, DecodeStepArgs* offsets);
 cudaError_t launch_decode_step(DecodeStepArgs a, cudaStream_t stream);
 
 void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream);

@@ -197,26 +197,45 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
   const auto& ops = b.ops;
   const auto& T = b.tensors;
   const int n = (int)ops.size();
-  if (decode_per_op() || n < 15 || (n - 4) % 11 != 0) return false;
-  const int L = (n - 4) / 11;
+  if (decode_per_op() || n < 15) return false;
+  // Tensor-parallel shards carry an all-reduce after the o and the down projection.
+  const bool tp_graph = ops[6].kind == TB200_OP_ALLREDUCE;
+  const int stride = tp_graph ? 13 : 11;
+  if ((n - 4) % stride != 0) return false;
+  const int L = (n - 4) / stride;
   static const uint32_t layer_kinds[11] = {TB200_OP_RMSNORM, TB200_OP_GEMV_W8, TB200_OP_ROPE_KV, TB200_OP_ATTN_DECODE,
                                            TB200_OP_GEMV_W8, TB200_OP_RMSNORM, TB200_OP_RMSNORM, TB200_OP_GEMV_W8,
                                            TB200_OP_GEGLU,   TB200_OP_GEMV_W8, TB200_OP_RMSNORM};
   if (ops[0].kind != TB200_OP_EMBED || ops[n - 3].kind != TB200_OP_RMSNORM || ops[n - 2].kind != TB200_OP_GEMV_W8 ||
       ops[n - 1].kind != TB200_OP_ARGMAX)
     return false;
-  for (int l = 0; l < L; l++)
-    for (int k = 0; k < 11; k++)
-      if (ops[1 + 11 * l + k].kind != layer_kinds[k]) return false;
+  // per layer: the 11 ops of the single-GPU form, and the two all-reduces when present
+  std::vector<const tb200_op_t*> lo((size_t)L * 11), ar((size_t)L * 2, nullptr);
+  for (int l = 0; l < L; l++) {
+    int k = 0;
+    for (int j = 0; j < stride; j++) {
+      const tb200_op_t* op = &ops[1 + stride * l + j];
+      if (tp_graph && (j == 5 || j == 11)) {
+        if (op->kind != TB200_OP_ALLREDUCE) return false;
+        ar[2 * l + (j == 11)] = op;
+        continue;
+      }
+      if (op->kind != layer_kinds[k]) return false;
+      lo[(size_t)11 * l + k++] = op;
+    }
+  }
+  const int tp = tp_graph ? ar[0]->i0 : 1, rank = tp_graph ? ar[0]->i1 : 0;
+  if (tp < 1 || tp > 8 || rank < 0 || rank >= tp) return false;
   auto inter = [&](int id) { return id >= 0 && T[id].kind == TB200_TENSOR_ACTIVATION; };
   const tb200_op_t& emb = ops[0];
   const int tokens = emb.in0;
-  const int B = T[emb.in0].shape[0], V = T[emb.weights].shape[0], H = T[emb.weights].shape[1];
-  const tb200_op_t& first_rope = ops[3];
+  const int B = T[emb.in0].shape[0], V_embed = T[emb.weights].shape[0], H = T[emb.weights].shape[1];
+  const int V = T[ops[n - 2].weights].shape[0];  // rows of this GPU's LM-head shard
+  const tb200_op_t& first_rope = *lo[2];
   const int n_q = first_rope.i0, n_kv = first_rope.i1, D = first_rope.i2, pos = first_rope.in1;
-  const int I = T[ops[9].out0].shape[1];
+  const int I = T[lo[8]->out0].shape[1];
   const int Tlen = T[first_rope.out1].shape[1];
-  const float eps = ops[1].f0, attn_scale = ops[4].f0;
+  const float eps = lo[0]->f0, attn_scale = lo[3]->f0;
   if (!decode_step_supported(B, H, n_q, n_kv, D, I, V)) return false;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
@@ -243,7 +262,8 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
   int x = emb.out0;
   if (!inter(x)) return false;
   for (int l = 0; l < L; l++) {
-    const tb200_op_t* o = &ops[1 + 11 * l];
+    tb200_op_t o[11];
+    for (int k = 0; k < 11; k++) o[k] = *lo[(size_t)11 * l + k];
     DecodeLayerDesc& d = descs[l];
     if (!norm_ok(o[0], x, -1) || !gemv_ok(o[1], o[0].out0, (n_q + 2) * D, H, false)) return false;
     const tb200_op_t& rope = o[2];
@@ -254,11 +274,21 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
     if (att.in0 != rope.out0 || att.in1 != pos || att.in2 != rope.out1 || att.weights != rope.in2 || att.i0 != n_q ||
         att.i1 != n_kv || att.i2 != D || att.f0 != attn_scale || att.i3 < 0)
       return false;
-    if (!gemv_ok(o[4], att.out0, H, n_q * D, false) || !norm_ok(o[5], o[4].out0, x) || !inter(o[4].out0)) return false;
+    // with tensor parallelism the K-split projections give fp32 partial results, summed by the all-reduce
+    auto reduced = [&](const tb200_op_t& g, const tb200_op_t* red) {
+      if (!tp_graph) return g.out0;
+      if (!red || red->in0 != g.out0 || !inter(g.out0) || red->i0 != tp || red->i1 != rank || T[red->in0].dtype != TB200_F32 ||
+          T[red->out0].dtype != TB200_BF16 || b.numel(red->in0) != b.numel(red->out0))
+        return -1;
+      return red->out0;
+    };
+    const int o_out = reduced(o[4], ar[2 * l]);
+    if (o_out < 0 || !gemv_ok(o[4], att.out0, H, n_q * D, tp_graph) || !norm_ok(o[5], o_out, x) || !inter(o_out)) return false;
     x = o[5].out0;
     if (!inter(x) || !norm_ok(o[6], x, -1) || !gemv_ok(o[7], o[6].out0, 2 * I, H, false)) return false;
     if (o[8].in0 != o[7].out0 || !inter(o[8].in0) || T[o[8].out0].shape[1] != I) return false;
-    if (!gemv_ok(o[9], o[8].out0, H, I, false) || !norm_ok(o[10], o[9].out0, x) || !inter(o[9].out0)) return false;
+    const int d_out = reduced(o[9], ar[2 * l + 1]);
+    if (d_out < 0 || !gemv_ok(o[9], o[8].out0, H, I, tp_graph) || !norm_ok(o[10], d_out, x) || !inter(d_out)) return false;
     x = o[10].out0;
     if (!inter(x)) return false;
     if (!cst(o[0].weights, (size_t)H * 2, d.in_norm) || !cst(o[1].weights, (size_t)(n_q + 2) * D * H, d.w_qkv) ||
@@ -293,21 +323,25 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
   const tb200_op_t& nf = ops[n - 3];
   const tb200_op_t& lm = ops[n - 2];
   const tb200_op_t& am = ops[n - 1];
-  if (!norm_ok(nf, x, -1) || !gemv_ok(lm, nf.out0, V, H, true) || lm.weights != emb.weights || lm.bias != emb.bias ||
-      am.in0 != lm.out0 || T[am.out0].kind != TB200_TENSOR_OUTPUT || T[am.out0].shape[0] != B)
+  if (!norm_ok(nf, x, -1) || !gemv_ok(lm, nf.out0, V, H, true) || am.in0 != lm.out0 ||
+      T[am.out0].kind != TB200_TENSOR_OUTPUT || T[am.out0].shape[0] != B)
     return false;
+  if (!tp_graph && (lm.weights != emb.weights || lm.bias != emb.bias || am.i1 > 1)) return false;
+  if (tp_graph && (am.i1 != tp || am.i0 < 0)) return false;  // arg max over every GPU's shard, ids offset by i0
   const bool logits_out = T[lm.out0].kind == TB200_TENSOR_OUTPUT;
   if (!logits_out && !inter(lm.out0)) return false;
 
   DecodeStepArgs a{};
-  if (!cst(emb.weights, (size_t)V * H, a.embed_w) || !cst(emb.bias, (size_t)V * 2, a.embed_s) ||
+  if (!cst(emb.weights, (size_t)V_embed * H, a.embed_w) || !cst(emb.bias, (size_t)V_embed * 2, a.embed_s) ||
+      !cst(lm.weights, (size_t)V * H, a.lm_w) || !cst(lm.bias, (size_t)V * 2, a.lm_s) ||
       !cst(nf.weights, (size_t)H * 2, a.final_norm))
     return false;
   a.layers_off = b.add_const(descs.data(), descs.size() * sizeof(DecodeLayerDesc));
-  a.n_layers = L; a.B = B; a.H = H; a.n_q = n_q; a.I = I; a.V = V; a.T = Tlen;
+  a.n_layers = L; a.B = B; a.H = H; a.n_q = n_q; a.I = I; a.V = V; a.V_embed = V_embed; a.T = Tlen;
+  a.tp = tp; a.rank = rank; a.vocab_offset = tp_graph ? am.i0 : 0;
   a.eps = eps; a.attn_scale = attn_scale; a.embed_mult = emb.f0; a.grid = sms;
   a.theta[0] = thetas[0]; a.theta[1] = thetas[1];
-  scratch_need = std::max(scratch_need, decode_step_scratch_bytes(B, H, n_q, I, L, sms, &a));
+  scratch_need = std::max(scratch_need, decode_step_scratch_bytes(B, H, n_q, I, L, sms, tp, &a));
   const Loc ltok = plan.tensor_loc[tokens], lpos = plan.tensor_loc[pos], lids = plan.tensor_loc[am.out0],
             llog = plan.tensor_loc[lm.out0];
   for (auto& st : plan.steps) {
@@ -325,6 +359,15 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
   plan.steps[0].launch = [=](const ExecContext& c) {
     DecodeStepArgs k = a;
     k.consts = c.consts; k.arena = c.arena; k.scratch = c.scratch; k.status = c.status;
+    for (int r = 0; r < 8; r++) k.peer_scratch[r] = nullptr;
+    k.peer_scratch[rank] = c.scratch;
+    if (tp > 1) {
+      if (!c.peer_scratch) {
+        if (c.launch_error) *c.launch_error = cudaErrorNotReady;  // the peers have not been connected yet
+        return;
+      }
+      for (int r = 0; r < tp; r++) k.peer_scratch[r] = c.peer_scratch[r];
+    }
     k.tokens = (const int32_t*)ltok.resolve(c);
     k.pos = (const int32_t*)lpos.resolve(c);
     k.out_ids = (int32_t*)lids.resolve(c);
@@ -343,6 +386,8 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
   };
   plan.launch_count = 1;
   plan.use_graph = false;    // one launch per dispatch: nothing for a graph to save
+  plan.tp = tp;
+  plan.rank = rank;
   plan.zero_scratch = true;  // the grid-barrier counters start at zero
   return true;
 }
@@ -436,6 +481,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
   }
 
   size_t scratch_need = 0;
+  bool needs_fusion = false;  // the graph holds ops that exist only inside the fused decode step
   // ---- one step per op ----
   for (int i = 0; i < (int)ops.size(); i++) {
     const auto& op = ops[i];
@@ -937,6 +983,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: argmax wants bf16 or f32 [B,V] -> i32 [B]", i);
         const int is_f32 = tensors[op.in0].dtype == TB200_F32;
         const int B = tensors[op.in0].shape[0], V = tensors[op.in0].shape[1];
+        if (op.i1 > 1) needs_fusion = true;  // arg max over the shards of a tensor-parallel group
         scratch_need = std::max(scratch_need, argmax_scratch_bytes(B));
         Loc lx = loc(op.in0), lo = loc(op.out0);
         step.kernel_name = "argmax";
@@ -944,6 +991,16 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         step.launch = [=](const ExecContext& c) {
           launch_argmax(lx.resolve(c), is_f32, (int32_t*)lo.resolve(c), c.scratch, B, V, c.stream);
         };
+        break;
+      }
+      case TB200_OP_ALLREDUCE: {
+        // Only meaningful inside the fused decode step (the exchange happens in that kernel).
+        if (!b.is_t(op.in0, TB200_F32, 2) || !b.is_t(op.out0, TB200_BF16, 2) || b.numel(op.in0) != b.numel(op.out0) ||
+            op.i0 < 2 || op.i0 > 8 || op.i1 < 0 || op.i1 >= op.i0)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: allreduce wants f32 [B,H] -> bf16 [B,H], group size 2..8, a rank inside it", i);
+        needs_fusion = true;
+        step.kernel_name = "allreduce";
+        step.launch = [](const ExecContext&) {};
         break;
       }
       case TB200_OP_RESHAPE: {
@@ -960,8 +1017,10 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
     plan.launch_count += step.launches;
     plan.steps.push_back(std::move(step));
   }
-  try_fuse_decode_step(b, plan, scratch_need);
+  const bool fused = try_fuse_decode_step(b, plan, scratch_need);
   if (b.status != TB200_OK) return b.status;
+  if (needs_fusion && !fused)
+    return b.fail(TB200_UNIMPLEMENTED, "tensor-parallel ops run only inside the fused decode step, and this graph does not fit it");
   // scratch shared by the ops that need one, behind the activations
   plan.scratch_offset = (plan.arena_bytes + 255) & ~(size_t)255;
   plan.scratch_bytes = scratch_need;

@@ -22,6 +22,7 @@ struct ExecContext {
   cudaStream_t stream;
   int* status;      // device status word (0 = fine)
   char* scratch;    // per-dispatch scratch shared by the ops that need one (split-K partials, ...)
+  char* const* peer_scratch;  // tensor parallelism: every rank's scratch area as mapped here, or null
   cudaError_t* launch_error;  // a step whose launcher refuses (not a CUDA launch failure) records why here
 };
 
@@ -55,6 +56,7 @@ struct Plan {
   size_t scratch_bytes = 0;
   bool zero_scratch = false;      // the scratch must read as zero before the first dispatch
   bool use_graph = true;          // replay the launch list as a CUDA graph
+  int tp = 1, rank = 0;           // tensor-parallel group size and this executable's place in it
   std::vector<Loc> tensor_loc;
 };
 

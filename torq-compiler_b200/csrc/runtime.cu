@@ -269,6 +269,11 @@ struct tb200_executable {
   };
   std::vector<CachedGraph> graphs;
   uint64_t graph_clock = 0;
+  // tensor parallelism: the scratch area of every member of the group as mapped into this
+  // process (own entry = own scratch); mapped[r] = base of a peer's arena opened through IPC
+  char* peer_scratch[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  void* peer_mapped[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  bool peers_connected = false;
 };
 
 extern "C" int tb200_executable_create(tb200_device_t* d, const void* bytes, size_t n_bytes,
@@ -379,9 +384,73 @@ extern "C" int tb200_executable_destroy(tb200_executable_t* ex) {
     if (ex->ev_uploaded[s]) cudaEventDestroy(ex->ev_uploaded[s]);
     if (ex->ev_released[s]) cudaEventDestroy(ex->ev_released[s]);
   }
+  for (void* m : ex->peer_mapped)
+    if (m) cudaIpcCloseMemHandle(m);
   if (ex->arena) cudaFree(ex->arena);
   if (ex->const_dev) cudaFree(ex->const_dev);
   delete ex;
+  return TB200_OK;
+}
+
+// ---- tensor-parallel groups: one process per GPU; the members exchange handles out of band ----
+namespace {
+struct CommHandle {  // the 96 bytes of tb200_comm_handle_t
+  cudaIpcMemHandle_t mem;  // the executable's arena allocation
+  uint64_t scratch_offset;
+  int32_t rank, tp;
+  uint8_t pad[16];
+};
+static_assert(sizeof(CommHandle) == sizeof(tb200_comm_handle_t), "tb200_comm_handle_t size");
+}  // namespace
+
+extern "C" int tb200_executable_comm_info(tb200_executable_t* ex, int32_t* rank, int32_t* group_size) {
+  if (!ex || !rank || !group_size) return TB200_INVALID_ARGUMENT;
+  *rank = ex->plan.rank;
+  *group_size = ex->plan.tp;
+  return TB200_OK;
+}
+
+extern "C" int tb200_executable_comm_handle(tb200_executable_t* ex, tb200_comm_handle_t* out) {
+  if (!ex || !out) return TB200_INVALID_ARGUMENT;
+  tb200_device* d = ex->dev;
+  if (ex->plan.tp < 2) return fail(d, TB200_FAILED_PRECONDITION, "the executable is not a tensor-parallel shard");
+  cudaSetDevice(d->ordinal);
+  CommHandle h{};
+  CUDA_OK(d, cudaIpcGetMemHandle(&h.mem, ex->arena));
+  h.scratch_offset = ex->plan.scratch_offset;
+  h.rank = ex->plan.rank;
+  h.tp = ex->plan.tp;
+  memcpy(out, &h, sizeof(h));
+  return TB200_OK;
+}
+
+extern "C" int tb200_executable_connect_peers(tb200_executable_t* ex, const tb200_comm_handle_t* handles, size_t n) {
+  if (!ex || !handles) return TB200_INVALID_ARGUMENT;
+  tb200_device* d = ex->dev;
+  const int tp = ex->plan.tp, rank = ex->plan.rank;
+  if (tp < 2) return fail(d, TB200_FAILED_PRECONDITION, "the executable is not a tensor-parallel shard");
+  if ((int)n != tp) return fail(d, TB200_INVALID_ARGUMENT, "%zu handles for a group of %d", n, tp);
+  if (ex->peers_connected) return fail(d, TB200_FAILED_PRECONDITION, "the peers are already connected");
+  std::lock_guard<std::mutex> lock(d->submit_mutex);
+  cudaSetDevice(d->ordinal);
+  for (int r = 0; r < tp; r++) {
+    CommHandle h;
+    memcpy(&h, &handles[r], sizeof(h));
+    if (h.rank != r || h.tp != tp || h.scratch_offset != ex->plan.scratch_offset)
+      return fail(d, TB200_INVALID_ARGUMENT, "handle %d describes rank %d of %d with another memory plan", r, h.rank, h.tp);
+    if (r == rank) {
+      ex->peer_scratch[r] = (char*)ex->arena + ex->plan.scratch_offset;
+      continue;
+    }
+    void* base = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&base, h.mem, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess)
+      return fail(d, TB200_UNAVAILABLE, "cannot map rank %d's memory (peer access over NVLink/PCIe needed): %s", r,
+                  cudaGetErrorString(e));
+    ex->peer_mapped[r] = base;
+    ex->peer_scratch[r] = (char*)base + h.scratch_offset;
+  }
+  ex->peers_connected = true;
   return TB200_OK;
 }
 
@@ -457,6 +526,7 @@ int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cud
   ctx.scratch = (char*)ex->arena + ex->plan.scratch_offset;
   cudaError_t launch_error = cudaSuccess;
   ctx.launch_error = &launch_error;
+  ctx.peer_scratch = ex->peers_connected ? ex->peer_scratch : nullptr;
   for (size_t i = 0; i < ex->plan.steps.size(); i++) {
     if (events) cudaEventRecord((*events)[i], d->stream);
     ex->plan.steps[i].launch(ctx);

@@ -28,7 +28,7 @@ OP_KINDS = {
     "conv2d": 1, "depthwise": 2, "fc": 3, "maxpool": 4, "avgpool": 5, "add": 6, "mul": 7, "table": 8,
     "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
     "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
-    "add_bf16": 38, "argmax": 39,
+    "add_bf16": 38, "argmax": 39, "allreduce": 40,
 }
 
 
@@ -310,8 +310,17 @@ class Graph:
         """y = bf16(bf16(gelu_tanh(gate)) * up), gate = first half of the columns."""
         return self._emit("geglu", [gate_up], (gate_up.shape[0], gate_up.shape[1] // 2), "bf16")
 
-    def argmax(self, logits):
-        return self._emit("argmax", [logits], (logits.shape[0],), "i32")
+    def argmax(self, logits, vocab_offset: int = 0, group_size: int = 1):
+        """Greedy ids. group_size >= 2: `logits` is this GPU's vocabulary shard of a tensor-parallel
+        group; the result is the arg max over all shards, this shard's ids offset by vocab_offset."""
+        return self._emit("argmax", [logits], (logits.shape[0],), "i32", i0=int(vocab_offset), i1=int(group_size))
+
+    def allreduce(self, partial_f32, group_size: int, rank: int):
+        """bf16(sum over the group's GPUs of their fp32 partial results), in rank order. Exists only
+        inside the fused decode step of a tensor-parallel shard."""
+        if partial_f32.dtype != "f32" or not 2 <= group_size <= 8 or not 0 <= rank < group_size:
+            raise ValueError("allreduce wants an f32 tensor, a group of 2..8 and a rank inside it")
+        return self._emit("allreduce", [partial_f32], partial_f32.shape, "bf16", i0=int(group_size), i1=int(rank))
 
     # ---- serialisation ------------------------------------------------------
     @staticmethod

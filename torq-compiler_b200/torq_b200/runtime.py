@@ -72,6 +72,9 @@ _SIGNATURES = {
     "tb200_wait": (C.c_int, [C.c_void_p, C.c_uint64]),
     "tb200_invoke_host": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "tb200_invoke_host_async": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "tb200_executable_comm_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "tb200_executable_comm_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "tb200_executable_connect_peers": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "tb200_gemv_w8_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                         C.c_int, C.c_int, C.c_int, C.c_int]),
     "tb200_executable_profile_ops": (C.c_int, [C.c_void_p, C.POINTER(Binding), C.c_size_t, C.c_int, C.c_int,
@@ -218,6 +221,38 @@ class Executable:
     @property
     def launch_count(self) -> int:
         return self.device._lib.tb200_executable_launch_count(self._h)
+
+    @property
+    def comm_info(self) -> tuple[int, int]:
+        """(rank, group size) of a tensor-parallel shard; (0, 1) for an ordinary executable."""
+        r, n = C.c_int32(), C.c_int32()
+        self.device._check(self.device._lib.tb200_executable_comm_info(self._h, C.byref(r), C.byref(n)))
+        return r.value, n.value
+
+    def comm_handle(self) -> bytes:
+        """This shard's 96-byte handle, to be sent to the other members of the group."""
+        buf = C.create_string_buffer(96)
+        self.device._check(self.device._lib.tb200_executable_comm_handle(self._h, buf))
+        return buf.raw
+
+    def connect_peers(self, handles: Sequence[bytes]):
+        """handles: every member's comm_handle(), in rank order (this member's own included)."""
+        blob = b"".join(handles)
+        if len(blob) != 96 * len(handles):
+            raise ValueError("comm handles are 96 bytes each")
+        self.device._check(self.device._lib.tb200_executable_connect_peers(self._h, blob, len(handles)))
+
+    def connect_group(self, group=None):
+        """Exchanges the handles over torch.distributed (any backend) and connects; every member of
+        the group calls it. Ends with a barrier: after it every member may dispatch."""
+        import torch.distributed as dist
+        rank, size = self.comm_info
+        if dist.get_world_size(group) != size or dist.get_rank(group) != rank:
+            raise ValueError("the process group does not match the shard's rank and group size")
+        handles = [None] * size
+        dist.all_gather_object(handles, self.comm_handle(), group=group)
+        self.connect_peers(handles)
+        dist.barrier(group=group)
 
     def op_kernels(self) -> list[str]:
         return [self.device._lib.tb200_executable_op_kernel(self._h, i).decode() for i in range(self.op_count)]

@@ -79,9 +79,40 @@ def random_weights(cfg: GemmaConfig, seed: int = 1234, embed_gain: float = 0.02)
     return P
 
 
-def build_decode_step(cfg: GemmaConfig, batch: int, params: dict, with_logits: bool = False) -> Graph:
+def shard_weights(cfg: GemmaConfig, params: dict, tp: int, rank: int) -> dict:
+    """Megatron-style shard `rank` of `tp` (tensor parallelism over the GPUs of one node):
+    q heads and the gate/up rows are split by output row, the o and down projections by input
+    column (their partial results are summed across the GPUs), the LM head by vocabulary row;
+    the single KV head, the norms and the embedding table are replicated."""
+    if cfg.n_kv != 1 or cfg.n_q % tp or cfg.intermediate % tp or cfg.vocab % tp:
+        raise ValueError("the group size must divide the query heads, the MLP width and the vocabulary")
+    D, I = cfg.head_dim, cfg.intermediate
+    hq, Il, Vl = cfg.n_q // tp, I // tp, cfg.vocab // tp
+    q_rows = np.arange(rank * hq * D, (rank + 1) * hq * D)
+    kv_rows = np.arange(cfg.n_q * D, (cfg.n_q + 2) * D)
+    gu_rows = np.concatenate([np.arange(rank * Il, (rank + 1) * Il), I + np.arange(rank * Il, (rank + 1) * Il)])
+    out = {"embed": params["embed"], "final_norm": params["final_norm"], "layers": [],
+           "lm_head": (np.ascontiguousarray(params["embed"][0][rank * Vl:(rank + 1) * Vl]),
+                       np.ascontiguousarray(params["embed"][1][rank * Vl:(rank + 1) * Vl])),
+           "vocab_offset": rank * Vl}
+    for L in params["layers"]:
+        rows = np.concatenate([q_rows, kv_rows])
+        S = dict(L)
+        S["qkv"] = (np.ascontiguousarray(L["qkv"][0][rows]), np.ascontiguousarray(L["qkv"][1][rows]))
+        S["o"] = (np.ascontiguousarray(L["o"][0][:, rank * hq * D:(rank + 1) * hq * D]), L["o"][1])
+        S["gate_up"] = (np.ascontiguousarray(L["gate_up"][0][gu_rows]), np.ascontiguousarray(L["gate_up"][1][gu_rows]))
+        S["down"] = (np.ascontiguousarray(L["down"][0][:, rank * Il:(rank + 1) * Il]), L["down"][1])
+        out["layers"].append(S)
+    return out
+
+
+def build_decode_step(cfg: GemmaConfig, batch: int, params: dict, with_logits: bool = False, tp: int = 1,
+                      rank: int = 0) -> Graph:
+    """tp > 1: `params` is shard_weights(cfg, full_params, tp, rank); the graph is that GPU's share
+    of the step (logits, when asked for, are the shard's [B, vocab / tp] slice)."""
     g = Graph()
     H, D = cfg.hidden, cfg.head_dim
+    n_q = cfg.n_q // tp
     tokens = g.input((batch,), "i32")
     pos = g.input((1,), "i32")
     table = g.const(params["embed"][0])
@@ -94,20 +125,24 @@ def build_decode_step(cfg: GemmaConfig, batch: int, params: dict, with_logits: b
         vc = g.state((batch, cfg.max_seq, cfg.n_kv * D), "bf16")
         h = g.rmsnorm(x, L["in_norm"], cfg.eps)
         qkv = g.gemv_w8(h, *L["qkv"])
-        q = g.rope_kv(qkv, pos, L["q_norm"], L["k_norm"], kc, vc, n_q=cfg.n_q, n_kv=cfg.n_kv, head_dim=D,
+        q = g.rope_kv(qkv, pos, L["q_norm"], L["k_norm"], kc, vc, n_q=n_q, n_kv=cfg.n_kv, head_dim=D,
                       theta=cfg.theta_global if glob else cfg.theta_local, eps=cfg.eps)
-        a = g.attn_decode(q, pos, kc, vc, n_q=cfg.n_q, n_kv=cfg.n_kv, head_dim=D, window=0 if glob else cfg.window,
+        a = g.attn_decode(q, pos, kc, vc, n_q=n_q, n_kv=cfg.n_kv, head_dim=D, window=0 if glob else cfg.window,
                           scale=D ** -0.5)
-        o = g.gemv_w8(a, *L["o"])
+        o = g.gemv_w8(a, *L["o"]) if tp == 1 else g.allreduce(g.gemv_w8(a, *L["o"], out_dtype="f32"), tp, rank)
         x = g.rmsnorm(o, L["post_attn_norm"], cfg.eps, residual=x)
         h = g.rmsnorm(x, L["pre_ffn_norm"], cfg.eps)
         gu = g.gemv_w8(h, *L["gate_up"])
         act = g.geglu(gu)
-        d = g.gemv_w8(act, *L["down"])
+        d = g.gemv_w8(act, *L["down"]) if tp == 1 else g.allreduce(g.gemv_w8(act, *L["down"], out_dtype="f32"), tp, rank)
         x = g.rmsnorm(d, L["post_ffn_norm"], cfg.eps, residual=x)
     x = g.rmsnorm(x, params["final_norm"], cfg.eps)
-    logits = g.gemv_w8(x, table, table_scale, out_dtype="f32")  # logits stay fp32: greedy ids do not hinge on bf16 ties
-    nxt = g.argmax(logits)
+    if tp == 1:
+        logits = g.gemv_w8(x, table, table_scale, out_dtype="f32")  # logits stay fp32: greedy ids do not hinge on bf16 ties
+        nxt = g.argmax(logits)
+    else:
+        logits = g.gemv_w8(x, *params["lm_head"], out_dtype="f32")
+        nxt = g.argmax(logits, vocab_offset=params["vocab_offset"], group_size=tp)
     g.output(nxt)
     if with_logits:
         g.output(logits)
