@@ -206,6 +206,11 @@ def main():
     ap.add_argument("--layer-table", default=None, help="write per-layer kernel, ms and GB/s to this CSV")
     ap.add_argument("--decoder", default="1", help="comma list of decode batch sizes for the Gemma-3-1B-shape "
                     "second metric (rank 0, one GPU); empty string skips it")
+    ap.add_argument("--decode-prompt", type=int, default=1024, help="prompt length of the decode metric")
+    ap.add_argument("--decode-gen", type=int, default=128, help="generated tokens of the decode metric")
+    ap.add_argument("--only", choices=["all", "cnn", "decoder"], default="all",
+                    help="profiling aid: 'cnn' runs just the timed MobileNetV2 steps, 'decoder' just the decode metric "
+                         "(one GPU); the JSON line then carries only that part")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -232,6 +237,11 @@ def main():
 
     B = args.batch
     dev = Device(local_rank)
+    if args.only == "decoder":
+        stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local_rank))
+        runs = [decoder_bench(dev, stream, int(t), args.decode_prompt, args.decode_gen) for t in args.decoder.split(",") if t]
+        print(json.dumps({"metric": "gemma3_1b_w8_decode_tok_per_s", "unit": "tokens/s", "only": "decoder", "runs": runs}), flush=True)
+        return
     g, layers = build_mobilenet_v2(B)
     ex = Executable(dev, g.serialize())
     in_info, out_info = ex.inputs_info[0], ex.outputs_info[0]
@@ -278,6 +288,16 @@ def main():
     ms_total = timed(lambda i: ex.dispatch([ins[i % n_rot]], [out]), args.steps, args.warmup)
     value = B * world * args.steps / (ms_total * 1e-3)
 
+    if args.only == "cnn":
+        if sampler:
+            sampler.stop()
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "only": "cnn", "steps": args.steps,
+                              "ms_per_step": ms_total / args.steps, "gpu_launches": ex.launch_count * args.steps}), flush=True)
+        barrier()
+        if world > 1:
+            dist.destroy_process_group()
+        return
     # ---- end to end through the host-pointer call (pinned host memory) ----
     hin = [h.as_numpy(in_info.shape, np.int8) for h in host_in]
     hout = host_out.as_numpy(out_info.shape, np.int8)
@@ -296,7 +316,7 @@ def main():
             if bsz > 8:
                 continue  # the fused step kernel takes up to 8 sequences
             try:
-                decoder_tp.append(decoder_bench(dev, stream, bsz, tp=world, rank=rank))
+                decoder_tp.append(decoder_bench(dev, stream, bsz, args.decode_prompt, args.decode_gen, tp=world, rank=rank))
             except Exception as e:
                 decoder_tp.append({"batch": bsz, "tp": world, "error": repr(e)[:200]})
                 break
@@ -336,8 +356,13 @@ def main():
     peaks, peak_kind = measured_peaks()
     d = per_kernel[dom]
     achieved = d["bytes"] / (d["ms"] * 1e-3) / 1e9
+    # DRAM bytes per launch from the ncu launch list of this workload (profiles/mobilenetv2_b256_launch_list.md:
+    # dram__bytes_read.sum + dram__bytes_write.sum over a step, divided by the class's launches), batch 256 only
+    ncu_traffic_per_launch = {"gemm_i8_tcgen05": (1745290752 + 860791808) / 70,
+                              "depthwise3x3_dp4a": (934547456 + 260309248 + 983089408 + 142840064) / 34}
+    traffic = ncu_traffic_per_launch.get(dom) if B == 256 else None
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": f"of {peak_kind}",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "peak_source": f"of {peak_kind}",
                 "launches_per_step": d["launches"], "avg_launch_ms": d["ms"] / d["launches"],
                 "algorithmic_bytes_per_launch": d["bytes"] / d["launches"],
                 "per_kernel_ms": {k: round(v["ms"], 4) for k, v in per_kernel.items()}}
@@ -356,7 +381,7 @@ def main():
         ex.destroy()  # free the CNN arena first
         for bsz in [int(t) for t in args.decoder.split(",") if t]:
             try:
-                r = decoder_bench(dev, stream, bsz)
+                r = decoder_bench(dev, stream, bsz, args.decode_prompt, args.decode_gen)
                 r["hbm_frac"] = r["hbm_gbs"] / peaks["hbm_gbs"]
                 decoder["runs"].append(r)
             except Exception as e:  # the headline line must still print

@@ -138,9 +138,10 @@ struct BarrierState {
 };
 // Arrival side: everything this thread (and, through the preceding CTA-level synchronisation,
 // its CTA) wrote is made visible before the count goes up.
-__device__ __forceinline__ void grid_arrive(const DecodeStepArgs& a, bool all_gpus, int parity) {
+// fence = false: the caller has already fenced (every lane of the reducer warp fences its own stores).
+__device__ __forceinline__ void grid_arrive(const DecodeStepArgs& a, bool all_gpus, int parity, bool fence = true) {
   if (all_gpus && a.tp > 1) {
-    __threadfence_system();
+    if (fence) __threadfence_system();
     const unsigned long long off = a.counter_off + 8 + 8 * parity;
     const unsigned long long old = atomicAdd_system((unsigned long long*)(a.scratch + off), 1ull);
     // the peers' counters are touched only after this GPU's own count is in (address depends on it)
@@ -148,7 +149,7 @@ __device__ __forceinline__ void grid_arrive(const DecodeStepArgs& a, bool all_gp
     for (int r = 0; r < a.tp; r++)
       if (r != a.rank) atomicAdd_system((unsigned long long*)(a.peer_scratch[r] + off + dep), 1ull);
   } else {
-    __threadfence();
+    if (fence) __threadfence();
     atomicAdd((unsigned long long*)(a.scratch + a.counter_off), 1ull);
   }
 }
@@ -1110,7 +1111,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
         if (split_k) __threadfence_system();
         else __threadfence();
         __syncwarp();
-        if (lane == 0) grid_arrive(a, split_k, gpar);
+        if (lane == 0) grid_arrive(a, split_k, gpar, false);
         if (split_k) gpar ^= 1;
       }
     }
@@ -1145,7 +1146,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       if (a.tp > 1) __threadfence_system();
       else __threadfence();
       __syncwarp();
-      if (lane == 0) grid_arrive(a, true, gpar);
+      if (lane == 0) grid_arrive(a, true, gpar, false);
     }
   } else {
     // ---------------- consumers ----------------
