@@ -56,6 +56,42 @@ def test_conv2d(device, case, mode):
     _check(device, g, [x])
 
 
+IGEMM_CASES = [
+    # x shape, OC, kernel, stride, pad(t,b,l,r), izp   (IC % 32 == 0, OC % 16 == 0: tensor-core implicit GEMM)
+    ((1, 56, 56, 64), 64, (3, 3), 1, (1, 1, 1, 1), -3),      # BASELINE's single-conv configuration
+    ((2, 20, 20, 128), 128, (3, 3), 1, (1, 1, 1, 1), 7),     # ragged patches (20 is no multiple of the patch)
+    ((1, 13, 17, 32), 48, (3, 3), 1, (1, 1, 1, 1), -9),      # odd frame, 32-byte rows
+    ((2, 40, 40, 64), 128, (3, 3), 2, (0, 1, 0, 1), 4),      # stride 2, TensorFlow SAME padding
+    ((1, 33, 29, 96), 32, (3, 3), 2, (1, 1, 1, 1), -1),      # stride 2, odd frame, 96 channels = 3 blocks of 32
+    ((1, 24, 24, 256), 272, (3, 3), 1, (1, 1, 1, 1), 5),     # weights too large to stay in shared memory; 3 N tiles
+    ((1, 18, 18, 64), 16, (5, 5), 1, (2, 2, 2, 2), 11),      # 25 taps, 3 x 3 border classes per axis
+    ((3, 16, 16, 32), 64, (3, 3), 1, (0, 0, 0, 0), 6),       # no padding: no border classes
+    ((1, 12, 12, 64), 64, (3, 3), 1, (1, 1, 1, 1), 0),       # zero input zero point: no correction table
+    ((1, 9, 140, 32), 32, (1, 7), 1, (0, 0, 3, 3), -20),     # one-row window, wide frame
+]
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("case", IGEMM_CASES)
+def test_conv2d_implicit_gemm(device, case, mode):
+    from torq_b200.runtime import Executable
+    shape, OC, k, stride, pad, izp = case
+    rng = np.random.default_rng(1234)
+    x = rng.integers(-128, 128, shape, dtype=np.int8)
+    w = rng.integers(-127, 128, (OC,) + k + (shape[3],), dtype=np.int8)
+    bias = np.round(rng.normal(0, 2000, OC)).astype(np.int32)
+    K = k[0] * k[1] * shape[3]
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, OC) * 40.0 / (np.sqrt(K) * 74 * 74))
+    g = Graph()
+    y = g.conv2d(g.input(shape), w, bias, m, s, stride=(stride, stride), pad=pad, input_zp=izp, out_zp=-7, clamp=(-128, 127),
+                 requant_mode=mode)
+    g.output(y)
+    ex = Executable(device, g.serialize())
+    assert ex.op_kernels() == ["conv_igemm_i8_tcgen05"]
+    ex.destroy()
+    _check(device, g, [x])
+
+
 def test_conv2d_per_tensor_scale_and_relu6_clamp(device):
     rng = np.random.default_rng(1234)
     x = rng.integers(-128, 128, (1, 8, 8, 1), dtype=np.int8)

@@ -25,6 +25,16 @@
 //     full lines instead of 16-byte pieces at a row stride;
 //   * single-thread roles carry no divisions: tile coordinates and ring indices advance
 //     incrementally.
+// The same kernel runs KH x KW convolutions as implicit GEMM (CONV = true): an M tile is a
+// TH x TW patch of output pixels of one image (TH * TW = 128); for every tap (kh, kw) and block
+// of input channels the producer loads the patch's input pixels with ONE 4-D TMA box
+// {channels, TW pixels at the conv stride, TH rows at the conv stride, 1 image} whose start is
+// shifted by the tap, and the issuer accumulates all taps into the same TMEM tile (K runs over
+// (kh, kw, ic), the order of OHWI weights). Padding costs nothing: out-of-range pixels are
+// zero-filled by the copy engine. Zero fill means "x = 0", while the op pads with the input zero
+// point, so border pixels get a per-class correction izp * sum of the padded taps' weights,
+// added in the epilogue from a small table (classes = which rows x which columns of the window
+// fall outside). The output tile leaves through a 4-D TMA store, which clips ragged edges.
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the device
 // status word and every role drains to the common exit, where TMEM is freed.
 #include <cuda.h>
@@ -58,6 +68,13 @@ struct GemmTcParams {
   int out_zp, clamp_min, clamp_max;
   int rnd_lo, dmul;     // uniform parts of the rounding constants (HI33 kernels)
   int acc_stride, acc_stages, tmem_cols;
+  // implicit-GEMM convolution (CONV kernels): tile = TH x TW output pixels, TW a power of two
+  int tw_log2, TH, tiles_w, tiles_per_img, OH, OW, cstride, pad_t, pad_l, KW, icb_per_tap;
+  const int32_t* corr;  // [row classes * col classes][n_tiles * BN] border corrections, or null
+  const uint8_t* rcls;  // [OH] row class
+  const uint8_t* ccls;  // [OW] column class
+  const uint8_t* cls_nonzero;  // [classes] 1 when the class has a non-zero correction
+  int ncc;              // column classes
   int tma_store;        // stage the output tile in shared memory and write it with one TMA store
   uint32_t staging_off; // byte offset of the staging buffers inside dynamic shared memory
   int* status;
@@ -119,6 +136,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
       : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(map), "r"(c0),
+               "r"(c1), "r"(c2), "r"(c3), "r"(src)
+               : "memory");
 }
 
 // K-major operand in shared memory, rows of row_bytes (= the swizzle width), 8-row groups
@@ -185,7 +214,7 @@ __device__ __forceinline__ void tmem_ld_wait32(uint32_t (&v)[32]) {
 // HI33: every rescale shift of the op is >= 33, so the rounding constant's low word and the
 // negative-accumulator term are the same for all channels and a channel needs only
 // {bias, mult, high word of rnd, shift - 32}: one 16-byte shared-memory load per output.
-template <bool HI33>
+template <bool HI33, bool CONV>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, GemmTcParams p) {
@@ -245,12 +274,32 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       int n = blockIdx.x / p.m_tiles, m = blockIdx.x - n * p.m_tiles;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        // convolution: where the tile's patch starts in the input, and the tap / channel block of kb
+        int img = 0, ih0 = 0, iw0 = 0, kh = 0, kw = 0, icb = 0;
+        if (CONV) {
+          img = m / p.tiles_per_img;
+          const int r = m - img * p.tiles_per_img;
+          const int ty = r / p.tiles_w, tx = r - ty * p.tiles_w;
+          ih0 = ty * p.TH * p.cstride - p.pad_t;
+          iw0 = (tx << p.tw_log2) * p.cstride - p.pad_l;
+        }
         for (int kb = 0; kb < p.k_blocks; kb++) {
           if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1, p.status, 1))) break;
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_ring + (uint32_t)s * stage_bytes;
           mbar_expect_tx(full, stage_bytes);
-          tma_load_2d(dst, &tmA, kb * p.row_bytes, m * kBM, full);
+          if (CONV) {
+            // zero fill outside the frame; the channel coordinate is a multiple of 32 bytes
+            tma_load_4d(dst, &tmA, icb * p.row_bytes, iw0 + kw, ih0 + kh, img, full);
+            if (++icb == p.icb_per_tap) {
+              icb = 0;
+              if (++kw == p.KW) {
+                kw = 0;
+                kh++;
+              }
+            }
+          } else
+            tma_load_2d(dst, &tmA, kb * p.row_bytes, m * kBM, full);
           if (!p.w_resident) tma_load_2d(dst + a_stage_bytes, &tmB, kb * p.row_bytes, n * p.BN, full);
           if (++s == p.stages) {
             s = 0;
@@ -347,6 +396,21 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (ok) {
         tc_fence_after();
         const int row = m * kBM + row_in_tile;
+        // convolution: this thread's output pixel and its border class
+        int img = 0, oh0 = 0, ow0 = 0;
+        const int32_t* corr_row = nullptr;
+        if (CONV) {
+          img = m / p.tiles_per_img;
+          const int r = m - img * p.tiles_per_img;
+          const int ty = r / p.tiles_w, tx = r - ty * p.tiles_w;
+          oh0 = ty * p.TH;
+          ow0 = tx << p.tw_log2;
+          const int oh = oh0 + (row_in_tile >> p.tw_log2), ow = ow0 + (row_in_tile & ((1 << p.tw_log2) - 1));
+          if (p.corr && oh < p.OH && ow < p.OW) {
+            const int cls = p.rcls[oh] * p.ncc + p.ccls[ow];
+            if (p.cls_nonzero[cls]) corr_row = p.corr + (size_t)cls * p.n_tiles * p.BN + (size_t)n * p.BN;
+          }
+        }
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(group * p.acc_stride);
         int8_t* orow = p.out + (long long)row * p.ldc + (long long)n * p.BN;
         const int ncol0 = n * p.BN;
@@ -364,12 +428,14 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             int r[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
+              int acc = (int)v[g * 4 + j];
+              if (CONV && corr_row) acc += corr_row[c0 + g * 4 + j];
               if (HI33) {
                 const int4 c = cps[c0 + g * 4 + j];
-                r[j] = scale_hi33((int)v[g * 4 + j] + c.x, c.y, c.z, c.w, p.rnd_lo, p.dmul) + p.out_zp;
+                r[j] = scale_hi33(acc + c.x, c.y, c.z, c.w, p.rnd_lo, p.dmul) + p.out_zp;
               } else {
                 const ChanParams c = chan_n[c0 + g * 4 + j];
-                r[j] = scale_cp<false>((int)v[g * 4 + j] + c.bias, c) + p.out_zp;
+                r[j] = scale_cp<false>(acc + c.bias, c) + p.out_zp;
               }
             }
             w4[g] = clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
@@ -406,7 +472,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // staged bytes -> visible to the TMA engine
           group_sync();
           if (e == 0) {
-            tma_store_2d(&tmC, ncol0, m * kBM, smem_u32(stage_tile));
+            if (CONV) tma_store_4d(&tmC, ncol0, ow0, oh0, img, smem_u32(stage_tile));
+            else tma_store_2d(&tmC, ncol0, m * kBM, smem_u32(stage_tile));
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
@@ -478,6 +545,37 @@ bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                                                   : CU_TENSOR_MAP_SWIZZLE_32B;
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Input of a convolution as a 4-D tensor {C, W, H, N}: box = {row_bytes channels, TW pixels at the
+// conv stride, TH rows at the conv stride, 1 image}, which lands in shared memory as 128 rows of
+// row_bytes, the same K-major layout the 2-D loads produce. Out-of-range elements read as zero.
+bool encode_conv_input(CUtensorMap* map, const void* base, int N, int H, int W, int C, int row_bytes, int TW, int TH,
+                       int stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+  cuuint64_t strides[3] = {(cuuint64_t)C, (cuuint64_t)W * C, (cuuint64_t)H * W * C};
+  cuuint32_t box[4] = {(cuuint32_t)row_bytes, (cuuint32_t)(TW * stride), (cuuint32_t)(TH * stride), 1};
+  cuuint32_t estr[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
+  const CUtensorMapSwizzle sw = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                  : CU_TENSOR_MAP_SWIZZLE_32B;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// Output {OC, OW, OH, N}: box = {BN, TW, TH, 1}, dense in shared memory; the store clips ragged edges.
+bool encode_conv_output(CUtensorMap* map, const void* base, int N, int OH, int OW, int OC, int BN, int TW, int TH) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)OC, (cuuint64_t)OW, (cuuint64_t)OH, (cuuint64_t)N};
+  cuuint64_t strides[3] = {(cuuint64_t)OC, (cuuint64_t)OW * OC, (cuuint64_t)OH * OW * OC};
+  cuuint32_t box[4] = {(cuuint32_t)BN, (cuuint32_t)TW, (cuuint32_t)TH, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -586,16 +684,123 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   const size_t smem = 1024 + p.staging_off + staging_bytes;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  if (a.hi33) gemm_i8_tc_kernel<true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  else gemm_i8_tc_kernel<false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  if (a.hi33) gemm_i8_tc_kernel<true, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  else gemm_i8_tc_kernel<false, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  return cudaGetLastError();
+}
+
+// ---- convolution as implicit GEMM ----
+ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW) {
+  ConvTcGeometry g{};
+  g.row_bytes = IC % 128 == 0 ? 128 : IC % 64 == 0 ? 64 : 32;
+  g.icb_per_tap = IC / g.row_bytes;
+  g.k_blocks = KH * KW * g.icb_per_tap;
+  g.Kpad = KH * KW * IC;
+  const GemmTcGeometry n = gemm_tc_geometry(OC, g.Kpad);
+  g.BN = n.BN;
+  g.n_tiles = n.n_tiles;
+  // patch shape: TW * TH = 128 with the least padded area (ties: the wider patch, longer contiguous runs)
+  long long best = -1;
+  for (int tw = 128; tw >= 4; tw >>= 1) {
+    const int th = 128 / tw;
+    const long long area = (long long)((OW + tw - 1) / tw) * tw * ((OH + th - 1) / th) * th;
+    if (best < 0 || area < best) {
+      best = area;
+      g.TW = tw;
+      g.TH = th;
+    }
+  }
+  g.tiles_w = (OW + g.TW - 1) / g.TW;
+  g.tiles_h = (OH + g.TH - 1) / g.TH;
+  return g;
+}
+
+bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w,
+                       int OH, int OW) {
+  if (IC % 32 != 0 || OC % 16 != 0 || stride_h != stride_w || stride_h < 1 || stride_h > 2 || dil_h != 1 || dil_w != 1 ||
+      KH < 1 || KW < 1 || KH * KW > 49 || KH * KW == 1)
+    return false;
+  const ConvTcGeometry g = conv_tc_geometry(OH, OW, IC, OC, KH, KW);
+  if (g.TW * stride_w > 256 || g.TH * stride_h > 256) return false;  // TMA box extents
+  if ((long long)N * g.tiles_w * g.tiles_h >= (1ll << 30)) return false;
+  return H >= 1 && W >= 1;
+}
+
+cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t stream) {
+  const ConvTcGeometry g = conv_tc_geometry(a.OH, a.OW, a.IC, a.OC, a.KH, a.KW);
+  if (st->a != a.x) {
+    if (!encode_conv_input(&st->tmA, a.x, a.N, a.H, a.W, a.IC, g.row_bytes, g.TW, g.TH, a.stride)) return cudaErrorInvalidValue;
+    st->a = a.x;
+  }
+  if (st->w != a.w) {
+    if (!encode_2d(&st->tmB, a.w, (uint64_t)g.n_tiles * g.BN, (uint64_t)g.Kpad, (uint64_t)g.Kpad, (uint32_t)g.BN, g.row_bytes))
+      return cudaErrorInvalidValue;
+    st->w = a.w;
+  }
+  if (((uintptr_t)a.out % 16) != 0) return cudaErrorInvalidValue;
+  if (st->c != a.out) {
+    if (!encode_conv_output(&st->tmC, a.out, a.N, a.OH, a.OW, a.OC, g.BN, g.TW, g.TH)) return cudaErrorInvalidValue;
+    st->c = a.out;
+  }
+  GemmTcParams p{};
+  p.tma_store = 1;
+  p.chan = a.chan;
+  p.out = a.out;
+  p.ldc = a.OC;
+  p.N = a.OC;
+  p.BN = g.BN;
+  p.n_tiles = g.n_tiles;
+  p.tiles_w = g.tiles_w;
+  p.tiles_per_img = g.tiles_w * g.tiles_h;
+  p.m_tiles = a.N * p.tiles_per_img;
+  p.M = p.m_tiles * kBM;
+  p.k_blocks = g.k_blocks;
+  p.k_last_steps = g.row_bytes / 32;
+  p.row_bytes = g.row_bytes;
+  p.TH = g.TH;
+  p.tw_log2 = 0;
+  while ((1 << p.tw_log2) < g.TW) p.tw_log2++;
+  p.OH = a.OH; p.OW = a.OW; p.cstride = a.stride; p.pad_t = a.pad_t; p.pad_l = a.pad_l; p.KW = a.KW;
+  p.icb_per_tap = g.icb_per_tap;
+  p.corr = a.corr; p.rcls = a.rcls; p.ccls = a.ccls; p.cls_nonzero = a.cls_nonzero; p.ncc = a.ncc;
+  const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
+  p.w_resident = w_bytes <= (size_t)kResidentWeightBytes;
+  const size_t stage_bytes = (size_t)kBM * g.row_bytes + (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes);
+  const size_t staging_bytes = (size_t)kEpiGroups * kBM * g.BN;
+  const size_t ring_budget = (size_t)kSmemBudget - 1024 - (p.w_resident ? w_bytes : 0) - staging_bytes;
+  int stages = (int)(ring_budget / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return cudaErrorInvalidConfiguration;
+  p.stages = stages;
+  p.out_zp = a.out_zp; p.clamp_min = a.clamp_min; p.clamp_max = a.clamp_max; p.rnd_lo = a.rnd_lo; p.dmul = a.dmul;
+  int stride = 32;
+  while (stride < g.BN) stride <<= 1;
+  p.acc_stride = stride;
+  p.acc_stages = kEpiGroups;
+  p.tmem_cols = p.acc_stages * stride;
+  p.status = a.status;
+  p.staging_off = (uint32_t)((p.w_resident ? w_bytes : 0) + (size_t)stages * stage_bytes);
+  const size_t smem = 1024 + p.staging_off + staging_bytes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  if (a.hi33) gemm_i8_tc_kernel<true, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  else gemm_i8_tc_kernel<false, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   return cudaGetLastError();
 }
 

@@ -109,6 +109,34 @@ void gemm_tc_state_free(GemmTcState* s);
 bool gemm_tc_supported(long long M, int N, int K, long long lda);
 cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t stream);
 
+// KH x KW convolution (stride 1 or 2, no dilation, symmetric weights, IC % 32 == 0, OC % 16 == 0)
+// as implicit GEMM on the same kernel: see gemm_tcgen05.cu.
+struct ConvTcGeometry {
+  int row_bytes, icb_per_tap, k_blocks, Kpad;  // K = (kh, kw, ic): the OHWI row of a filter
+  int BN, n_tiles;
+  int TW, TH, tiles_w, tiles_h;                // output patch of a tile (TW * TH = 128)
+};
+ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW);
+bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w,
+                       int OH, int OW);
+struct ConvTcArgs {
+  const int8_t* x;        // [N, H, W, IC]
+  const int8_t* w;        // [n_tiles * BN][KH * KW * IC], rows beyond OC zero
+  const ChanParams* chan; // [n_tiles * BN], bias already holds bias - izp * sum of all taps
+  int8_t* out;            // [N, OH, OW, OC]
+  int N, H, W, IC, OC, KH, KW, OH, OW, stride, pad_t, pad_l;
+  int out_zp, clamp_min, clamp_max, hi33, rnd_lo, dmul;
+  // border classes: pixel (oh, ow) has class rcls[oh] * ncc + ccls[ow]; corr[class][n_tiles * BN] =
+  // izp * (sum of the weights of the taps that fall outside the frame for that class)
+  const int32_t* corr;
+  const uint8_t* rcls;
+  const uint8_t* ccls;
+  const uint8_t* cls_nonzero;
+  int ncc;
+  int* status;
+};
+cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t stream);
+
 // ---- decoder kernels (decoder.cu): bf16 tensors are passed as uint16_t bit patterns ----
 void launch_embed(const int32_t* tok, const int8_t* table, const uint16_t* scale, uint16_t* out, int B, int H, int V,
                   float mult, cudaStream_t stream);

@@ -596,6 +596,101 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           break;
         }
 
+        // KH x KW convolution with symmetric weights: implicit GEMM on the tensor cores (one TMA box per
+        // tap and channel block, taps accumulated in TMEM; see gemm_tcgen05.cu)
+        if (!fc && !pointwise && op.weight_zp == 0 && !force_simt() &&
+            conv_tc_supported(N, H, W, IC, OC, KH, KW, op.stride_h, op.stride_w, op.dil_h, op.dil_w, OH, OW)) {
+          const ConvTcGeometry geo = conv_tc_geometry(OH, OW, IC, OC, KH, KW);
+          ConvTcArgs ca{};
+          ca.N = N; ca.H = H; ca.W = W; ca.IC = IC; ca.OC = OC; ca.KH = KH; ca.KW = KW; ca.OH = OH; ca.OW = OW;
+          ca.stride = op.stride_h; ca.pad_t = op.pad_t; ca.pad_l = op.pad_l;
+          ca.out_zp = op.out_zp; ca.clamp_min = op.clamp_min; ca.clamp_max = op.clamp_max;
+          ca.hi33 = b.last_min_shift >= 33;
+          if (ca.hi33 && b.last_max_shift <= 55) {
+            for (auto& c : cp) c.rnd += (long long)op.out_zp << c.shift;
+            ca.out_zp = 0;
+          }
+          ca.rnd_lo = (int)(cp[0].rnd & 0xffffffffll); ca.dmul = cp[0].dmul;
+          const int rows = geo.n_tiles * geo.BN;
+          std::vector<int8_t> wp((size_t)rows * geo.Kpad, 0);
+          memcpy(wp.data(), w, (size_t)OC * K);  // OHWI rows are already in (kh, kw, ic) order
+          { ChanParams z{}; z.shift = 34; z.hshift = 2; z.rnd = 1ll << 33; cp.resize(rows, z); }
+          // Border classes. The copy engine fills taps outside the frame with 0 where the op means the
+          // input zero point; cp's bias assumed izp for every tap, so a pixel gets back
+          // izp * (weights of its outside taps).
+          std::vector<uint8_t> rcls(OH), ccls(OW), nonzero;
+          std::vector<uint32_t> rmasks, cmasks;
+          auto classify = [](int out_dim, int in_dim, int k, int stride, int pad, std::vector<uint8_t>& cls,
+                             std::vector<uint32_t>& masks) {
+            for (int o = 0; o < out_dim; o++) {
+              uint32_t m = 0;
+              for (int t = 0; t < k; t++) {
+                const int i = o * stride + t - pad;
+                if (i < 0 || i >= in_dim) m |= 1u << t;
+              }
+              size_t id = 0;
+              while (id < masks.size() && masks[id] != m) id++;
+              if (id == masks.size()) masks.push_back(m);
+              cls[o] = (uint8_t)id;
+            }
+          };
+          classify(OH, H, KH, op.stride_h, op.pad_t, rcls, rmasks);
+          classify(OW, W, KW, op.stride_w, op.pad_l, ccls, cmasks);
+          std::vector<int32_t> corr;
+          const bool need_corr = op.in0_zp != 0 && (rmasks.size() > 1 || cmasks.size() > 1 || rmasks[0] || cmasks[0]);
+          if (need_corr) {
+            if (rmasks.size() * cmasks.size() > 255) return b.fail(TB200_UNIMPLEMENTED, "op %d: too many border classes", i);
+            corr.assign(rmasks.size() * cmasks.size() * (size_t)rows, 0);
+            nonzero.assign(rmasks.size() * cmasks.size(), 0);
+            for (size_t rc = 0; rc < rmasks.size(); rc++)
+              for (size_t cc = 0; cc < cmasks.size(); cc++) {
+                const size_t cls = rc * cmasks.size() + cc;
+                for (int oc = 0; oc < OC; oc++) {
+                  int32_t sum = 0;
+                  for (int kh = 0; kh < KH; kh++)
+                    for (int kw = 0; kw < KW; kw++)
+                      if ((rmasks[rc] >> kh & 1) || (cmasks[cc] >> kw & 1)) {
+                        const int8_t* tap = w + ((size_t)oc * KH * KW + (size_t)kh * KW + kw) * IC;
+                        for (int ic = 0; ic < IC; ic++) sum += tap[ic];
+                      }
+                  const int32_t v = (int32_t)((uint32_t)op.in0_zp * (uint32_t)sum);
+                  corr[cls * rows + oc] = v;
+                  if (v) nonzero[cls] = 1;
+                }
+              }
+          }
+          const size_t w_off = b.add_const(wp.data(), wp.size());
+          const size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+          size_t corr_off = 0, rcls_off = 0, ccls_off = 0, nz_off = 0;
+          if (need_corr) {
+            corr_off = b.add_const(corr.data(), corr.size() * 4);
+            rcls_off = b.add_const(rcls.data(), rcls.size());
+            ccls_off = b.add_const(ccls.data(), ccls.size());
+            nz_off = b.add_const(nonzero.data(), nonzero.size());
+            ca.ncc = (int)cmasks.size();
+          }
+          Loc lx = loc(op.in0), lo = loc(op.out0);
+          std::shared_ptr<GemmTcState> st(gemm_tc_state_new(), gemm_tc_state_free);
+          step.kernel_name = "conv_igemm_i8_tcgen05";
+          step.launch = [=](const ExecContext& c) {
+            ConvTcArgs k = ca;
+            k.x = (const int8_t*)lx.resolve(c);
+            k.out = (int8_t*)lo.resolve(c);
+            k.w = (const int8_t*)(c.consts + w_off);
+            k.chan = (const ChanParams*)(c.consts + c_off);
+            if (need_corr) {
+              k.corr = (const int32_t*)(c.consts + corr_off);
+              k.rcls = (const uint8_t*)(c.consts + rcls_off);
+              k.ccls = (const uint8_t*)(c.consts + ccls_off);
+              k.cls_nonzero = (const uint8_t*)(c.consts + nz_off);
+            }
+            k.status = c.status;
+            const cudaError_t e = launch_conv_i8_tc(k, st.get(), c.stream);
+            if (e != cudaSuccess && c.launch_error) *c.launch_error = e;
+          };
+          break;
+        }
+
         const int Kpad = (int)((K + 31) / 32 * 32);
         std::vector<int8_t> packed((size_t)OC * Kpad, 0);
         for (int oc = 0; oc < OC; oc++) memcpy(packed.data() + (size_t)oc * Kpad, w + (size_t)oc * K, (size_t)K);
