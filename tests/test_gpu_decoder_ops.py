@@ -50,7 +50,11 @@ def test_embed_and_rmsnorm(device):
 
 
 @pytest.mark.parametrize("B,K,N,splits", [(1, 1152, 1536, 0), (1, 6912, 1152, 0), (3, 512, 200, 1), (3, 1024, 77, 2),
-                                          (8, 2048, 64, 4), (32, 1152, 256, 0), (1, 1152, 4096, 1)])
+                                          (8, 2048, 64, 4), (32, 1152, 256, 0), (1, 1152, 4096, 1),
+                                          # batches above 8: the tensor-core kernel (K % 64 == 0), ragged N, K splits
+                                          (9, 1152, 1536, 0), (32, 6912, 1152, 0), (17, 256, 200, 0), (32, 1152, 4100, 1),
+                                          (12, 1024, 77, 2), (24, 2048, 130, 5),
+                                          (16, 1040, 64, 0)])  # K % 64 != 0: stays on the CUDA-core kernel
 def test_gemv_w8(device, B, K, N, splits):
     rng = np.random.default_rng(1234 + K + N)
     x = to_bf16(rng.normal(0, 1, (B, K)).astype(np.float32))

@@ -135,6 +135,103 @@ __global__ void __launch_bounds__(256) gemv_w8_kernel(const uint16_t* __restrict
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same product for batches above 8 on the tensor cores (mma.sync m16n8k16, bf16 operands,
+// fp32 accumulation): with 9..32 tokens the CUDA-core kernel above spends 32 FMAs per weight
+// byte and is FMA-bound at a few percent of the HBM rate. Block = 128 weight rows (8 warps x 16
+// rows) x one K slice; the slice of x for all tokens is staged in shared memory once per block
+// (bf16, token rows 16 bytes apart modulo 128 so that the fragment loads do not conflict);
+// every warp streams its 16 rows straight from global memory, 64 bytes of K at a time, turns
+// the int8 weights into bf16 fragments (exact) and issues one MMA per group of 8 tokens.
+// The weights are the 16-row operand, the tokens the 8-column operand, as in decode_step.cu.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;  // bytes biased by 128
+  const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.0f;  // 2^23 + 128
+  const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.0f;
+  const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.0f;
+  const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.0f;
+  lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);  // high halves = the bf16 values
+  hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT>  // groups of 8 tokens
+__global__ void __launch_bounds__(256) gemv_w8_mma_kernel(const uint16_t* __restrict__ x, const int8_t* __restrict__ W,
+                                                          const uint16_t* __restrict__ scale, void* __restrict__ y,
+                                                          float* __restrict__ partial, int B, int N, int K, int k_slice,
+                                                          int y_f32) {
+  extern __shared__ __align__(16) unsigned char xs_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  const int split = blockIdx.y, splits = gridDim.y;
+  const int k_begin = split * k_slice;
+  const int k_len = min(k_slice, K - k_begin);  // a multiple of 64
+  const int xstride = ((k_slice * 2 + 127) / 128) * 128 + 16;  // bytes per token row in shared memory
+  // stage x[:, k_begin : k_begin + k_len]; tokens beyond B read as zero
+  for (int i = threadIdx.x; i < NT * 8 * (k_len / 8); i += blockDim.x) {
+    const int b = i / (k_len / 8), c = i % (k_len / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (b < B) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + k_begin) + c);
+    *reinterpret_cast<uint4*>(xs_raw + (size_t)b * xstride + 16 * c) = v;
+  }
+  __syncthreads();
+  const int row0 = blockIdx.x * 128 + warp * 16;
+  if (row0 >= N) return;
+  const int r_lo = row0 + g, r_hi = row0 + g + 8;
+  const int8_t* w_lo = W + (size_t)min(r_lo, N - 1) * K + k_begin + tig * 16;
+  const int8_t* w_hi = W + (size_t)min(r_hi, N - 1) * K + k_begin + tig * 16;
+  float c[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; t++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) c[t][j] = 0.f;
+  const unsigned char* xrow = xs_raw + (size_t)g * xstride + tig * 32;
+  const int kbs = k_len >> 6;
+#pragma unroll 2
+  for (int kb = 0; kb < kbs; kb++) {
+    const uint4 wa = __ldg(reinterpret_cast<const uint4*>(w_lo + kb * 64));
+    const uint4 wb = __ldg(reinterpret_cast<const uint4*>(w_hi + kb * 64));
+    uint32_t a[4][4];  // [mma within the block of 64][a0..a3]
+    s8x4_to_bf16x4(wa.x, a[0][0], a[0][2]); s8x4_to_bf16x4(wb.x, a[0][1], a[0][3]);
+    s8x4_to_bf16x4(wa.y, a[1][0], a[1][2]); s8x4_to_bf16x4(wb.y, a[1][1], a[1][3]);
+    s8x4_to_bf16x4(wa.z, a[2][0], a[2][2]); s8x4_to_bf16x4(wb.z, a[2][1], a[2][3]);
+    s8x4_to_bf16x4(wa.w, a[3][0], a[3][2]); s8x4_to_bf16x4(wb.w, a[3][1], a[3][3]);
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+      const uint4 x0 = *reinterpret_cast<const uint4*>(xrow + (size_t)t * 8 * xstride + kb * 128);
+      const uint4 x1 = *reinterpret_cast<const uint4*>(xrow + (size_t)t * 8 * xstride + kb * 128 + 16);
+      mma_bf16(c[t], a[0][0], a[0][1], a[0][2], a[0][3], x0.x, x0.y);
+      mma_bf16(c[t], a[1][0], a[1][1], a[1][2], a[1][3], x0.z, x0.w);
+      mma_bf16(c[t], a[2][0], a[2][1], a[2][2], a[2][3], x1.x, x1.y);
+      mma_bf16(c[t], a[3][0], a[3][1], a[3][2], a[3][3], x1.z, x1.w);
+    }
+  }
+  // c[t][0], c[t][1]: row r_lo, tokens 8t + 2tig, + 1; c[t][2], c[t][3]: row r_hi
+  const float s_lo = r_lo < N ? bf2f(__ldg(scale + r_lo)) : 0.f, s_hi = r_hi < N ? bf2f(__ldg(scale + r_hi)) : 0.f;
+#pragma unroll
+  for (int t = 0; t < NT; t++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int b = 8 * t + 2 * tig + (j & 1), r = (j & 2) ? r_hi : r_lo;
+      if (b < B && r < N) {
+        if (splits == 1) {
+          const float v = c[t][j] * ((j & 2) ? s_hi : s_lo);
+          if (y_f32) ((float*)y)[(size_t)b * N + r] = v;
+          else ((uint16_t*)y)[(size_t)b * N + r] = f2bf(v);
+        } else
+          partial[((size_t)split * B + b) * N + r] = c[t][j];
+      }
+    }
+}
+
 __global__ void __launch_bounds__(256) gemv_finalize_kernel(const float* __restrict__ partial,
                                                             const uint16_t* __restrict__ scale,
                                                             void* __restrict__ y, int B, int N, int splits, int y_f32) {
@@ -352,7 +449,27 @@ void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, u
   rmsnorm_kernel<<<rows, 256, 0, stream>>>(x, res, w, out, H, eps);
 }
 
+// Batches above 8 with K a multiple of 64 take the tensor-core kernel: K slices of a multiple of 64.
+static bool gemv_use_mma(int B, int K) { return B > 8 && (K % 64) == 0; }
+static int gemv_mma_slice(int N, int K, int splits) {
+  int slice = ((K + splits - 1) / splits + 63) / 64 * 64;
+  (void)N;
+  return slice;
+}
+
 int gemv_w8_splits(int B, int N, int K) {
+  if (gemv_use_mma(B, K)) {
+    // blocks of 128 rows: split K until about two blocks per SM exist, slices >= 128 bytes, <= 16 slices;
+    // a slice of x for 32 tokens must fit in shared memory (K = 1152 unsplit: 74 KB)
+    const long long row_blocks = (N + 127) / 128;
+    int splits = (int)((2 * 148 + row_blocks - 1) / row_blocks);
+    const int max_splits = K / 128 > 0 ? K / 128 : 1;
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+    while (gemv_mma_slice(N, K, splits) > 2048) splits++;  // shared-memory bound on the x slice
+    return splits;
+  }
   // enough warps to fill the machine: one warp per (row, slice); slices are multiples of 512 bytes
   const long long warps_wanted = 148LL * 32;
   int splits = (int)((warps_wanted + N - 1) / N);
@@ -368,6 +485,30 @@ size_t gemv_w8_scratch_bytes(int B, int N, int splits) { return splits > 1 ? (si
 
 void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, void* y, int y_f32, float* scratch, int B,
                     int N, int K, int splits, cudaStream_t stream) {
+  if (gemv_use_mma(B, K)) {
+    const int slice = gemv_mma_slice(N, K, splits);
+    const int used = (K + slice - 1) / slice;
+    const int nt = (B + 7) / 8;
+    const int xstride = ((slice * 2 + 127) / 128) * 128 + 16;
+    const size_t smem = (size_t)nt * 8 * xstride;
+    dim3 grid((N + 127) / 128, used);
+    auto run = [&](auto kernel) {
+      static bool attr_done[5] = {false, false, false, false, false};
+      if (!attr_done[nt]) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        attr_done[nt] = true;
+      }
+      kernel<<<grid, 256, smem, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
+    };
+    if (nt == 2) run(gemv_w8_mma_kernel<2>);
+    else if (nt == 3) run(gemv_w8_mma_kernel<3>);
+    else run(gemv_w8_mma_kernel<4>);
+    if (used > 1) {
+      const size_t total = (size_t)B * N;
+      gemv_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, scale, y, B, N, used, y_f32);
+    }
+    return;
+  }
   const int slice = ((K + splits - 1) / splits + 511) / 512 * 512;
   const int used = (K + slice - 1) / slice;  // slices that really hold data
   dim3 grid((N + 7) / 8, used);
@@ -389,7 +530,7 @@ void launch_rope_kv(const uint16_t* qkv, const int32_t* pos, const uint16_t* qw,
                                                               theta, eps);
 }
 
-int attn_decode_splits(int B) { return B >= 32 ? 4 : B >= 8 ? 8 : 32; }
+int attn_decode_splits(int B) { return B >= 16 ? 16 : 32; }
 size_t attn_decode_scratch_bytes(int B, int n_q, int splits) {
   return (size_t)B * n_q * splits * (kAttnD + 2) * sizeof(float);
 }
