@@ -80,6 +80,14 @@ enum tb200_op_kind {
   TB200_OP_ADD_BF16 = 38,     /* residual add */
   TB200_OP_ARGMAX = 39,       /* greedy token id from logits; i1 >= 2: over the shards of a tensor-parallel
                                * group of i1 GPUs, this shard's ids offset by i0 */
+  TB200_OP_ACT_BF16 = 41,     /* elementwise bf16 activation, i0: 0 sigmoid, 1 tanh-GELU, 2 exp, 3 tanh, 4 SiLU
+                               * (SigmoidPattern.cpp:25-232, GeluPattern.cpp:25-283, ExpOpPattern, TrigOpPattern);
+                               * computed in fp32 and rounded once, like the reference's host path */
+  TB200_OP_GEMV_Q8B = 42,     /* y = x . bf16((W - zp) * scale) with block-wise scales and zero points along K
+                               * (ONNX DequantizeLinear(axis=0, block_size=i0) + MatMul, the reference's Gemma form:
+                               * tests/testdata/torch_ops/matmul_dql_q8_0.mlir, ExpandWeightsPattern.cpp:350-376);
+                               * weights int8 [K, N], bias slot = scales bf16 [K/i0, N], multiplier slot = zero
+                               * points int8 [K/i0, N] or -1 */
   TB200_OP_ALLREDUCE = 40,    /* sum of the fp32 partial results of the i0 GPUs of a tensor-parallel group
                                * (this one is rank i1), rounded to bf16; only inside the fused decode step */
 };

@@ -127,3 +127,41 @@ def test_geglu_and_argmax(device):
     got = run_graph_gpu(device, g, [logits])[0]
     want = from_bf16(logits).argmax(-1)
     assert (got == want).all() and got[1] == 17
+
+
+@pytest.mark.parametrize("fn", ["sigmoid", "gelu_tanh", "exp", "tanh", "silu"])
+def test_act_bf16(device, fn):
+    """bf16 activations (the reference's Sigmoid/Gelu/Exp/Trig patterns, host semantics: fp32 math, one
+    rounding). Tolerance: one bf16 ulp (2^-8 relative) against torch's fp32 functions."""
+    rng = np.random.default_rng(99)
+    x = to_bf16(np.concatenate([rng.normal(0, 3, 5000), np.linspace(-12, 12, 3001), [0.0, -0.0, 30.0, -30.0]]).astype(np.float32))
+    g = Graph()
+    g.output(g.act_bf16(g.input(x.shape, "bf16"), fn))
+    got = from_bf16(run_graph_gpu(device, g, [x])[0])
+    t = torch.from_numpy(from_bf16(x))
+    want = {"sigmoid": torch.sigmoid, "gelu_tanh": lambda v: torch.nn.functional.gelu(v, approximate="tanh"), "exp": torch.exp,
+            "tanh": torch.tanh, "silu": torch.nn.functional.silu}[fn](t).numpy()
+    err = np.abs(got - want)
+    # 1 + tanh(.) cancels for negative arguments: tanh-GELU's tiny outputs carry fp32's absolute error (~|x| * 2^-24)
+    floor = 2e-6 if fn == "gelu_tanh" else 1e-30
+    assert (err <= np.abs(want) * 2.0 ** -7 + floor).all(), float((err / (np.abs(want) + floor)).max())
+    assert len(np.unique(got)) > 100
+
+
+@pytest.mark.parametrize("B,K,N,with_zp", [(1, 640, 256, True), (3, 1152, 200, True), (8, 2048, 96, False)])
+def test_gemv_block_quantised(device, B, K, N, with_zp):
+    """The reference's Gemma weight form (tests/testdata/torch_ops/matmul_dql_q8_0.mlir: x 1x640 bf16, W 640x256
+    si8, scales and zero points 20x256, block 32): dequantised weights are rounded to bf16, the product
+    accumulates in fp32. First case = that fixture's shapes."""
+    rng = np.random.default_rng(640 + K)
+    x = to_bf16(rng.normal(0, 1, (B, K)).astype(np.float32))
+    w = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    sc = to_bf16((rng.uniform(0.5, 1.5, (K // 32, N)) / (73.0 * np.sqrt(K))).astype(np.float32))
+    zp = rng.integers(-8, 9, (K // 32, N), dtype=np.int8) if with_zp else None
+    g = Graph()
+    g.output(g.gemv_q8b(g.input((B, K), "bf16"), w, sc, zp, 32))
+    got = run_graph_gpu(device, g, [x])[0]
+    wz = torch.from_numpy(w.astype(np.float32)) - (torch.from_numpy(np.repeat(zp, 32, 0).astype(np.float32)) if with_zp else 0.0)
+    wd = _bf(wz * torch.from_numpy(np.repeat(from_bf16(sc), 32, 0)))
+    want = _bf(torch.from_numpy(from_bf16(x)) @ wd)
+    _close(got, want, floor=0.05)

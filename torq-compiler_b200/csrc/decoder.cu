@@ -384,6 +384,75 @@ __global__ void __launch_bounds__(256) geglu_kernel(const uint16_t* __restrict__
   out[idx] = f2bf(bf2f(f2bf(gelu_tanh(g))) * u);
 }
 
+// Block-quantised weights (the reference's Gemma form): y[b, n] = bf16( sum_k x[b, k] * wd[k, n] ),
+// wd = bf16((W - zp) * scale), scale and zp per (block of `bs` consecutive k, n). The planner has
+// transposed W to [N, K] and the per-block tables to [N, K / bs], so a warp streams one output row.
+template <int BT>
+__global__ void __launch_bounds__(256) gemv_q8b_kernel(const uint16_t* __restrict__ x, const int8_t* __restrict__ W,
+                                                       const uint16_t* __restrict__ scale, const int8_t* __restrict__ zp,
+                                                       uint16_t* __restrict__ y, int B, int N, int K, int bs) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const int nblk = K / bs;
+  float acc[BT];
+#pragma unroll
+  for (int b = 0; b < BT; b++) acc[b] = 0.f;
+  const int8_t* wrow = W + (size_t)n * K;
+  for (int k = lane * 16; k < K; k += 32 * 16) {
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + k));
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    const int blk = k / bs;  // bs is a multiple of 16: the 16 weights share a block
+    const float s = bf2f(__ldg(scale + (size_t)n * nblk + blk));
+    const int z = zp ? (int)__ldg(zp + (size_t)n * nblk + blk) : 0;
+    float wd[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int w8 = (int)(int8_t)(ww[j >> 2] >> (8 * (j & 3)));
+      wd[j] = bf2f(f2bf((float)(w8 - z) * s));
+    }
+#pragma unroll
+    for (int b = 0; b < BT; b++)
+      if (b < B) {
+        const uint4 x0 = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + k));
+        const uint4 x1 = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + k + 8));
+        const uint32_t xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        float a = acc[b];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          a = fmaf(wd[2 * j], __uint_as_float(xw[j] << 16), a);
+          a = fmaf(wd[2 * j + 1], __uint_as_float(xw[j] & 0xffff0000u), a);
+        }
+        acc[b] = a;
+      }
+  }
+#pragma unroll
+  for (int b = 0; b < BT; b++) acc[b] = warp_sum(acc[b]);
+  if (lane == 0)
+#pragma unroll
+    for (int b = 0; b < BT; b++)
+      if (b < B) y[(size_t)b * N + n] = f2bf(acc[b]);
+}
+
+// y = bf16(f(x)), f evaluated in fp32: the host semantics of the reference's bf16 activation
+// patterns (python/torq/testing/numpy.py:13-27 is the fp32 form its tests compare with; the NPU's
+// piecewise-linear tables, scripts/bf16luts.py, approximate the same functions).
+__global__ void __launch_bounds__(256) act_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out,
+                                                       long long n, int fn) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = bf2f(x[i]);
+    float r;
+    switch (fn) {
+      case 0: r = 1.0f / (1.0f + expf(-v)); break;
+      case 1: r = gelu_tanh(v); break;
+      case 2: r = expf(v); break;
+      case 3: r = tanhf(v); break;
+      default: r = v / (1.0f + expf(-v)); break;
+    }
+    out[i] = f2bf(r);
+  }
+}
+
 // greedy token: arg max over the vocabulary, lowest index on ties; two stages through scratch
 constexpr int kArgmaxChunks = 64;
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const void* __restrict__ logits, int is_f32,
@@ -544,6 +613,20 @@ void launch_attn_decode(const uint16_t* q, const int32_t* pos, const uint16_t* k
 void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t stream) {
   const size_t total = (size_t)B * I;
   geglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(gu, out, B, I);
+}
+
+void launch_gemv_q8b(const uint16_t* x, const int8_t* W, const uint16_t* scale, const int8_t* zp, uint16_t* y, int B, int N,
+                     int K, int bs, cudaStream_t stream) {
+  const dim3 grid((N + 7) / 8);
+  if (B <= 1) gemv_q8b_kernel<1><<<grid, 256, 0, stream>>>(x, W, scale, zp, y, B, N, K, bs);
+  else if (B <= 4) gemv_q8b_kernel<4><<<grid, 256, 0, stream>>>(x, W, scale, zp, y, B, N, K, bs);
+  else gemv_q8b_kernel<8><<<grid, 256, 0, stream>>>(x, W, scale, zp, y, B, N, K, bs);
+}
+
+void launch_act_bf16(const uint16_t* x, uint16_t* out, long long n, int fn, cudaStream_t stream) {
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  act_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, out, n, fn);
 }
 
 size_t argmax_scratch_bytes(int B) { return (size_t)B * kArgmaxChunks * 8; }

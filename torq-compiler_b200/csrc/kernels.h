@@ -155,6 +155,10 @@ void launch_attn_decode(const uint16_t* q, const int32_t* pos, const uint16_t* k
                         uint16_t* out, float* scratch, int B, int n_q, int T, int window, float scale, int splits,
                         cudaStream_t stream);
 void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t stream);
+// block-quantised GEMV: W [N, K] int8, scale bf16 and zp int8 (or null) [N, K / bs], bs a multiple of 16, batch <= 8
+void launch_gemv_q8b(const uint16_t* x, const int8_t* W, const uint16_t* scale, const int8_t* zp, uint16_t* y, int B, int N,
+                     int K, int bs, cudaStream_t stream);
+void launch_act_bf16(const uint16_t* x, uint16_t* out, long long n, int fn, cudaStream_t stream);  // fn: see TB200_OP_ACT_BF16
 size_t argmax_scratch_bytes(int B);
 void launch_argmax(const void* logits, int is_f32, int32_t* out, void* scratch, int B, int V, cudaStream_t stream);
 

@@ -1088,6 +1088,57 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         };
         break;
       }
+      case TB200_OP_GEMV_Q8B: {
+        if (!b.is_t(op.in0, TB200_BF16, 2) || !b.is_t(op.out0, TB200_BF16, 2) || !b.valid_id(op.weights) ||
+            tensors[op.weights].rank != 2 || tensors[op.weights].dtype != TB200_I8)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: gemv_q8b wants bf16 [B,K] x int8 [K,N] -> bf16 [B,N]", i);
+        const int B = tensors[op.in0].shape[0], K = tensors[op.in0].shape[1], N = tensors[op.weights].shape[1], bs = op.i0;
+        if (tensors[op.weights].shape[0] != K || tensors[op.out0].shape[0] != B || tensors[op.out0].shape[1] != N)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: gemv_q8b shape mismatch", i);
+        if (bs < 16 || bs % 16 != 0 || K % bs != 0 || K % 16 != 0 || B > 8)
+          return b.fail(TB200_UNIMPLEMENTED, "op %d: gemv_q8b needs a block size that is a multiple of 16 and divides K, batch <= 8", i);
+        const int nblk = K / bs;
+        const int8_t* w = b.const_data<int8_t>(op.weights, (size_t)K * N, "weights", i);
+        const uint16_t* sc = b.const_data<uint16_t>(op.bias, (size_t)nblk * N, "block scales", i);
+        if (!w || !sc) return b.status;
+        const int8_t* zp = nullptr;
+        if (op.multiplier >= 0 && !(zp = b.const_data<int8_t>(op.multiplier, (size_t)nblk * N, "block zero points", i)))
+          return b.status;
+        // row-major per output: W^T [N, K], tables [N, K / bs]
+        std::vector<int8_t> wt((size_t)N * K), zt(zp ? (size_t)N * nblk : 0);
+        std::vector<uint16_t> st((size_t)N * nblk);
+        for (int k = 0; k < K; k++)
+          for (int nn = 0; nn < N; nn++) wt[(size_t)nn * K + k] = w[(size_t)k * N + nn];
+        for (int q = 0; q < nblk; q++)
+          for (int nn = 0; nn < N; nn++) {
+            st[(size_t)nn * nblk + q] = sc[(size_t)q * N + nn];
+            if (zp) zt[(size_t)nn * nblk + q] = zp[(size_t)q * N + nn];
+          }
+        const size_t w_off = b.add_const(wt.data(), wt.size());
+        const size_t s_off = b.add_const(st.data(), st.size() * 2);
+        const size_t z_off = zp ? b.add_const(zt.data(), zt.size()) : 0;
+        const bool has_zp = zp != nullptr;
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "gemv_q8b";
+        step.launch = [=](const ExecContext& c) {
+          launch_gemv_q8b((const uint16_t*)lx.resolve(c), (const int8_t*)(c.consts + w_off), (const uint16_t*)(c.consts + s_off),
+                          has_zp ? (const int8_t*)(c.consts + z_off) : nullptr, (uint16_t*)lo.resolve(c), B, N, K, bs, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_ACT_BF16: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || tensors[op.in0].dtype != TB200_BF16 ||
+            tensors[op.out0].dtype != TB200_BF16 || b.numel(op.in0) != b.numel(op.out0) || op.i0 < 0 || op.i0 > 4)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: act_bf16 wants bf16 tensors of equal size and a function id 0..4", i);
+        const long long n = (long long)b.numel(op.in0);
+        const int fn = op.i0;
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "act_bf16";
+        step.launch = [=](const ExecContext& c) {
+          launch_act_bf16((const uint16_t*)lx.resolve(c), (uint16_t*)lo.resolve(c), n, fn, c.stream);
+        };
+        break;
+      }
       case TB200_OP_ALLREDUCE: {
         // Only meaningful inside the fused decode step (the exchange happens in that kernel).
         if (!b.is_t(op.in0, TB200_F32, 2) || !b.is_t(op.out0, TB200_BF16, 2) || b.numel(op.in0) != b.numel(op.out0) ||

@@ -28,7 +28,7 @@ OP_KINDS = {
     "conv2d": 1, "depthwise": 2, "fc": 3, "maxpool": 4, "avgpool": 5, "add": 6, "mul": 7, "table": 8,
     "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
     "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
-    "add_bf16": 38, "argmax": 39, "allreduce": 40,
+    "add_bf16": 38, "argmax": 39, "allreduce": 40, "act_bf16": 41, "gemv_q8b": 42,
 }
 
 
@@ -309,6 +309,25 @@ class Graph:
     def geglu(self, gate_up):
         """y = bf16(bf16(gelu_tanh(gate)) * up), gate = first half of the columns."""
         return self._emit("geglu", [gate_up], (gate_up.shape[0], gate_up.shape[1] // 2), "bf16")
+
+    def gemv_q8b(self, x, weights_kn_i8, block_scales_bf16, block_zero_points_i8=None, block_size: int = 32):
+        """y = bf16(x . bf16((W - zp) * scale)): W int8 [K, N], scales bf16 and zero points int8 [K / block, N]
+        (ONNX DequantizeLinear(axis=0, block_size) + MatMul)."""
+        w = self.const(np.asarray(weights_kn_i8, np.int8))
+        consts = {"weights": w, "bias": self.const(np.asarray(block_scales_bf16, np.uint16), "bf16")}
+        if block_zero_points_i8 is not None:
+            consts["multiplier"] = self.const(np.asarray(block_zero_points_i8, np.int8))
+        if w.shape[0] != x.shape[1]:
+            raise ValueError("weight K mismatch")
+        return self._emit("gemv_q8b", [x], (x.shape[0], w.shape[1]), "bf16", consts=consts, i0=int(block_size))
+
+    ACT_FUNCTIONS = {"sigmoid": 0, "gelu_tanh": 1, "exp": 2, "tanh": 3, "silu": 4}
+
+    def act_bf16(self, x, function: str):
+        """y = bf16(f(x)) with f evaluated in fp32: sigmoid, gelu_tanh, exp, tanh or silu."""
+        if x.dtype != "bf16":
+            raise ValueError("act_bf16 wants a bf16 tensor")
+        return self._emit("act_bf16", [x], x.shape, "bf16", i0=self.ACT_FUNCTIONS[function])
 
     def argmax(self, logits, vocab_offset: int = 0, group_size: int = 1):
         """Greedy ids. group_size >= 2: `logits` is this GPU's vocabulary shard of a tensor-parallel
