@@ -97,6 +97,50 @@ def cpu_oracle_throughput(batch_sample: int, repeats: int):
     return batch_sample / float(np.median(times)), oc.num_threads(), times
 
 
+_DECODER_PARAMS = {}
+
+
+def _decoder_params(cfg, tp, rank):
+    """Random-init weights of the 1B shape (generated once per process: 1 GB of seeded integers)."""
+    from torq_b200.workloads import gemma3
+    if "full" not in _DECODER_PARAMS:
+        _DECODER_PARAMS["full"] = gemma3.random_weights(cfg, 1234)
+    if tp == 1:
+        return _DECODER_PARAMS["full"]
+    return gemma3.shard_weights(cfg, _DECODER_PARAMS["full"], tp, rank)
+
+
+def yolo_bench(dev, stream, batch: int = 64, steps: int = 5):
+    """YOLOv8n-style int8 detector at 640x640 (BASELINE's detector configuration): images/s, inputs resident."""
+    import torch
+    from torq_b200.runtime import Executable
+    from torq_b200.workloads.yolov8n import build_yolov8n, synthetic_images
+    g, macs = build_yolov8n(batch, 640)
+    ex = Executable(dev, g.serialize())
+    x = synthetic_images(batch, 640)
+    d_in = dev.alloc(x.nbytes)
+    d_in.upload(x)
+    outs = [dev.alloc(o.nbytes) for o in ex.outputs_info]
+    for _ in range(3):
+        ex.dispatch([d_in], outs)
+    dev.wait(120.0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        ex.dispatch([d_in], outs)
+    e1.record(stream)
+    dev.wait(120.0)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    kernels = sorted(set(ex.op_kernels()))
+    launches = ex.launch_count
+    ex.destroy()
+    for b in [d_in] + outs:
+        b.free()
+    return {"workload": f"YOLOv8n-style int8 detector 640x640, batch {batch}", "images_per_s": batch / (ms * 1e-3),
+            "ms_per_step": ms, "gmac_per_image": macs / 1e9, "launches_per_step": launches, "kernels": kernels}
+
+
 def decoder_bench(dev, stream, batch: int, prompt_len: int = 1024, gen_len: int = 128, tp: int = 1, rank: int = 0):
     """Gemma-3-1B-architecture int8-weight greedy decode (second metric of the benchmark set):
     tokens/s over `gen_len` decode steps after a `prompt_len`-token seeded prompt. One GPU, or
@@ -107,9 +151,7 @@ def decoder_bench(dev, stream, batch: int, prompt_len: int = 1024, gen_len: int 
     from torq_b200.runtime import MEMORY_HOST_PINNED, Executable
     from torq_b200.workloads import gemma3
     cfg = gemma3.GemmaConfig()
-    params = gemma3.random_weights(cfg, 1234)
-    if tp > 1:
-        params = gemma3.shard_weights(cfg, params, tp, rank)
+    params = _decoder_params(cfg, tp, rank)
     g = gemma3.build_decode_step(cfg, batch, params, tp=tp, rank=rank)
     ex = Executable(dev, g.serialize())
     del params, g
@@ -204,8 +246,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layer-table", default=None, help="write per-layer kernel, ms and GB/s to this CSV")
-    ap.add_argument("--decoder", default="1", help="comma list of decode batch sizes for the Gemma-3-1B-shape "
-                    "second metric (rank 0, one GPU); empty string skips it")
+    ap.add_argument("--decoder", default="1,32", help="comma list of decode batch sizes for the Gemma-3-1B-shape "
+                    "second metric (rank 0 on one GPU; with several ranks also tensor-parallel, batches <= 8); "
+                    "empty string skips it")
+    ap.add_argument("--no-yolo", action="store_true", help="skip the YOLOv8n-style detector timing")
     ap.add_argument("--decode-prompt", type=int, default=1024, help="prompt length of the decode metric")
     ap.add_argument("--decode-gen", type=int, default=128, help="generated tokens of the decode metric")
     ap.add_argument("--only", choices=["all", "cnn", "decoder"], default="all",
@@ -392,6 +436,13 @@ def main():
                     r["hbm_frac_per_gpu"] = r["hbm_gbs"] / r["tp"] / peaks["hbm_gbs"]
             decoder["tensor_parallel_runs"] = decoder_tp
 
+    yolo = None
+    if not args.no_yolo:
+        try:
+            yolo = yolo_bench(dev, stream)
+        except Exception as e:
+            yolo = {"error": repr(e)[:200]}
+
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -403,7 +454,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_info.nbytes, "d2h_bytes_per_step": out_info.nbytes,
                 "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
         "gpu_launches": cnn_launches * args.steps,
-        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "decoder": decoder,
+        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "decoder": decoder, "yolo": yolo,
     }
     print(json.dumps(line), flush=True)
     barrier()
