@@ -36,6 +36,9 @@ CONV_CASES = [
     ((2, 14, 14, 96), 576, (1, 1), (1, 1), (1, 1), (0, 0, 0, 0), 9, 0),
     ((1, 224, 224, 3), 32, (3, 3), (2, 2), (1, 1), (0, 1, 0, 1), -4, 0),    # MobileNetV2 stem
     ((1, 7, 7, 100), 130, (1, 1), (1, 1), (1, 1), (0, 0, 0, 0), 2, -1),
+    ((2, 20, 22, 16), 32, (3, 3), (1, 1), (1, 1), (1, 1, 1, 1), -5, 0),     # 16 input channels: direct dp4a kernel
+    ((1, 21, 21, 16), 24, (3, 3), (2, 2), (1, 1), (0, 1, 0, 1), 3, 0),
+    ((1, 12, 12, 16), 7, (5, 5), (1, 1), (1, 1), (2, 2, 2, 2), 9, 0),
 ]
 
 
@@ -57,7 +60,7 @@ def test_conv2d(device, case, mode):
 
 
 IGEMM_CASES = [
-    # x shape, OC, kernel, stride, pad(t,b,l,r), izp   (IC % 32 == 0, OC % 16 == 0: tensor-core implicit GEMM)
+    # x shape, OC, kernel, stride, pad(t,b,l,r), izp   (IC % 16 == 0, OC % 16 == 0: tensor-core implicit GEMM)
     ((1, 56, 56, 64), 64, (3, 3), 1, (1, 1, 1, 1), -3),      # BASELINE's single-conv configuration
     ((2, 20, 20, 128), 128, (3, 3), 1, (1, 1, 1, 1), 7),     # ragged patches (20 is no multiple of the patch)
     ((1, 13, 17, 32), 48, (3, 3), 1, (1, 1, 1, 1), -9),      # odd frame, 32-byte rows
@@ -68,6 +71,9 @@ IGEMM_CASES = [
     ((3, 16, 16, 32), 64, (3, 3), 1, (0, 0, 0, 0), 6),       # no padding: no border classes
     ((1, 12, 12, 64), 64, (3, 3), 1, (1, 1, 1, 1), 0),       # zero input zero point: no correction table
     ((1, 9, 140, 32), 32, (1, 7), 1, (0, 0, 3, 3), -20),     # one-row window, wide frame
+    ((2, 20, 20, 80), 80, (3, 3), 1, (1, 1, 1, 1), 3),       # 80 channels: the last 32-byte block is half zero fill
+    ((1, 30, 34, 16), 32, (3, 3), 2, (0, 1, 0, 1), -6),      # 16 channels in a 32-byte block
+    ((1, 11, 11, 48), 16, (3, 3), 1, (1, 1, 1, 1), 8),       # 48 channels in one 64-byte block
 ]
 
 
@@ -277,7 +283,7 @@ def test_pointwise_conv_tensor_core_sweep(device, M, K, N):
     os.environ["TB200_FORCE_SIMT"] = "1"
     try:
         ex = Executable(device, g.serialize())
-        assert ex.op_kernels() == ["conv2d_simt"]
+        assert ex.op_kernels()[0] in ("conv2d_simt", "conv2d_c16_dp4a")  # CUDA-core kernels
         ex.destroy()
         simt = run_graph_gpu(device, g, [a])[0]
     finally:
@@ -304,3 +310,25 @@ def test_pipelined_host_calls(device):
     for x, o in zip(xs, outs):
         assert (o == run_graph(g, [x])[0]).all()
     ex.destroy()
+
+
+def test_chained_concats_are_written_in_place(device):
+    """concat(concat(a, b), c) with a pass-through rescale on the inner result: the planner writes the inner
+    result straight into the outer one (one launch less); a non-identity rescale keeps the copy."""
+    from torq_b200.runtime import Executable
+    rng = np.random.default_rng(1234)
+    shape = (2, 9, 7, 16)
+    xs = [rng.integers(-128, 128, shape, dtype=np.int8) for _ in range(4)]
+    ident = ((1 << 30), 30)
+    for passthrough, want_launches in ((True, 4), (False, 6)):
+        g = Graph()
+        ins = [g.input(shape) for _ in range(4)]
+        acc = g.concat(ins[0], ins[1], a_zp=3, a_ms=quantize_multiplier(0.7), b_zp=-2, b_ms=quantize_multiplier(1.3), out_zp=4)
+        mid = ident if passthrough else quantize_multiplier(0.9)
+        acc = g.concat(acc, ins[2], a_zp=4, a_ms=mid, b_zp=0, b_ms=quantize_multiplier(0.5), out_zp=4)
+        acc = g.concat(acc, ins[3], a_zp=4, a_ms=mid, b_zp=7, b_ms=quantize_multiplier(1.1), out_zp=4)
+        g.output(g.table(acc, np.arange(-128, 128, dtype=np.int8)[::-1].copy()))  # a consumer of the final result
+        ex = Executable(device, g.serialize())
+        assert ex.launch_count == want_launches + 1
+        ex.destroy()
+        _check(device, g, xs)

@@ -270,6 +270,67 @@ __global__ void __launch_bounds__(128) conv2d_smallic_kernel(ConvArgs a) {
   }
 }
 
+// Convolutions over exactly 16 input channels (the first stages of detector backbones: large
+// frames, few channels). A tap of one pixel is one 16-byte load; a thread gathers the TAPS taps
+// of its output pixel once (input zero point for taps outside the frame) and runs them against
+// every output channel's weights, broadcast from shared memory: 4 dp4a per tap and channel.
+// Weight rows are Kpad bytes apart (K = TAPS * 16 is a multiple of 16, Kpad of 32).
+template <int TAPS>
+__global__ void __launch_bounds__(128) conv2d_c16_kernel(ConvArgs a) {
+  extern __shared__ uint4 w16[];  // [OC][TAPS]
+  for (int i = threadIdx.x; i < a.OC * TAPS; i += blockDim.x) {
+    const int oc = i / TAPS, t = i - oc * TAPS;
+    w16[i] = *reinterpret_cast<const uint4*>(a.w + (size_t)oc * a.Kpad + t * 16);
+  }
+  __syncthreads();
+  const long long P = (long long)a.N * a.OH * a.OW;
+  const long long p = (long long)blockIdx.x * 128 + threadIdx.x;
+  if (p >= P) return;
+  const int ow = (int)(p % a.OW);
+  const long long t0 = p / a.OW;
+  const int oh = (int)(t0 % a.OH), n = (int)(t0 / a.OH);
+  const int ih0 = oh * a.stride_h - a.pad_t, iw0 = ow * a.stride_w - a.pad_l;
+  const int8_t* xin = a.x + (size_t)n * a.H * a.W * 16;
+  const uint32_t zw = (uint32_t)(a.input_zp & 0xff) * 0x01010101u;
+  uint4 tap[TAPS];
+#pragma unroll
+  for (int t = 0; t < TAPS; t++) {
+    const int kh = t / a.KW, kw = t - kh * a.KW;
+    const int ih = ih0 + kh * a.dil_h, iw = iw0 + kw * a.dil_w;
+    tap[t] = (ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
+                 ? __ldg(reinterpret_cast<const uint4*>(xin + ((size_t)ih * a.W + iw) * 16))
+                 : make_uint4(zw, zw, zw, zw);
+  }
+  const bool hi = a.hi_shift != 0;
+  int8_t* o = a.out + (size_t)p * a.OC;
+  for (int oc0 = 0; oc0 < a.OC; oc0 += 4) {
+    int q[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int oc = min(oc0 + j, a.OC - 1);
+      int acc = 0;
+#pragma unroll
+      for (int t = 0; t < TAPS; t++) {
+        const uint4 w = w16[oc * TAPS + t];
+        acc = __dp4a((int)tap[t].x, (int)w.x, acc);
+        acc = __dp4a((int)tap[t].y, (int)w.y, acc);
+        acc = __dp4a((int)tap[t].z, (int)w.z, acc);
+        acc = __dp4a((int)tap[t].w, (int)w.w, acc);
+      }
+      const ChanParams cp = a.chan[oc];
+      q[j] = hi ? requant_cp<true>(acc + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max)
+                : requant_cp<false>(acc + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max);
+    }
+    if ((a.OC & 3) == 0) {
+      *reinterpret_cast<uint32_t*>(o + oc0) = pack4(q[0], q[1], q[2], q[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (oc0 + j < a.OC) o[oc0 + j] = (int8_t)q[j];
+    }
+  }
+}
+
 // raw torq_hl.matmul, int32 result (tests/testdata/tosa_ops/matmul-in-int8-out-int32.mlir).
 __global__ void __launch_bounds__(256) matmul_i32_kernel(const int8_t* __restrict__ a,
                                                          const int8_t* __restrict__ b,
@@ -286,12 +347,36 @@ __global__ void __launch_bounds__(256) matmul_i32_kernel(const int8_t* __restric
 
 }  // namespace
 
+static bool conv_c16_applies(const ConvArgs& a) {
+  const int taps = a.KH * a.KW;
+  return a.IC == 16 && a.weight_zp == 0 && a.OC <= 256 && (taps == 9 || taps == 1 || taps == 25);
+}
+
 const char* conv2d_simt_kernel_name(const ConvArgs& a) {
+  if (conv_c16_applies(a)) return "conv2d_c16_dp4a";
   return (a.IC <= 4 && a.K <= 64 && a.OC <= 256 && a.weight_zp == 0) ? "conv2d_smallic_dp4a" : "conv2d_simt";
 }
 
 void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
   long long P = (long long)a.N * a.OH * a.OW;
+  if (conv_c16_applies(a)) {
+    const unsigned blocks = (unsigned)((P + 127) / 128);
+    const int taps = a.KH * a.KW;
+    const size_t smem = (size_t)a.OC * taps * 16;
+    if (taps == 9) {
+      conv2d_c16_kernel<9><<<blocks, 128, smem, stream>>>(a);
+    } else if (taps == 1) {
+      conv2d_c16_kernel<1><<<blocks, 128, smem, stream>>>(a);
+    } else {
+      static bool attr = false;
+      if (!attr) {
+        cudaFuncSetAttribute(conv2d_c16_kernel<25>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 25 * 16);
+        attr = true;
+      }
+      conv2d_c16_kernel<25><<<blocks, 128, smem, stream>>>(a);
+    }
+    return;
+  }
   if (a.IC <= 4 && a.K <= 64 && a.OC <= 256 && a.weight_zp == 0) {
     const unsigned blocks = (unsigned)((P + 128 * kPix - 1) / (128 * kPix));
     const int kwords = (a.K + 3) / 4;

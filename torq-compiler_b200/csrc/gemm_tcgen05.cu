@@ -700,10 +700,20 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
 // ---- convolution as implicit GEMM ----
 ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW) {
   ConvTcGeometry g{};
-  g.row_bytes = IC % 128 == 0 ? 128 : IC % 64 == 0 ? 64 : 32;
-  g.icb_per_tap = IC / g.row_bytes;
+  // channel block = swizzle width: the widest of 128 / 64 / 32 bytes with the least padding of IC. A last
+  // block that reaches beyond IC is fine: the copy engine fills the missing channels with zeros and the
+  // packed weights hold zeros there.
+  int best_pad = 1 << 30;
+  for (int rb = 128; rb >= 32; rb >>= 1) {
+    const int padded = (IC + rb - 1) / rb * rb;
+    if (padded < best_pad) {
+      best_pad = padded;
+      g.row_bytes = rb;
+    }
+  }
+  g.icb_per_tap = (IC + g.row_bytes - 1) / g.row_bytes;
   g.k_blocks = KH * KW * g.icb_per_tap;
-  g.Kpad = KH * KW * IC;
+  g.Kpad = g.k_blocks * g.row_bytes;
   const GemmTcGeometry n = gemm_tc_geometry(OC, g.Kpad);
   g.BN = n.BN;
   g.n_tiles = n.n_tiles;
@@ -725,7 +735,7 @@ ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW) 
 
 bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w,
                        int OH, int OW) {
-  if (IC % 32 != 0 || OC % 16 != 0 || stride_h != stride_w || stride_h < 1 || stride_h > 2 || dil_h != 1 || dil_w != 1 ||
+  if (IC % 16 != 0 || OC % 16 != 0 || stride_h != stride_w || stride_h < 1 || stride_h > 2 || dil_h != 1 || dil_w != 1 ||
       KH < 1 || KW < 1 || KH * KW > 49 || KH * KW == 1)
     return false;
   const ConvTcGeometry g = conv_tc_geometry(OH, OW, IC, OC, KH, KW);

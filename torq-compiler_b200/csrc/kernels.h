@@ -109,7 +109,7 @@ void gemm_tc_state_free(GemmTcState* s);
 bool gemm_tc_supported(long long M, int N, int K, long long lda);
 cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t stream);
 
-// KH x KW convolution (stride 1 or 2, no dilation, symmetric weights, IC % 32 == 0, OC % 16 == 0)
+// KH x KW convolution (stride 1 or 2, no dilation, symmetric weights, IC % 16 == 0, OC % 16 == 0)
 // as implicit GEMM on the same kernel: see gemm_tcgen05.cu.
 struct ConvTcGeometry {
   int row_bytes, icb_per_tap, k_blocks, Kpad;  // K = (kh, kw, ic): the OHWI row of a filter
@@ -121,7 +121,7 @@ bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int 
                        int OH, int OW);
 struct ConvTcArgs {
   const int8_t* x;        // [N, H, W, IC]
-  const int8_t* w;        // [n_tiles * BN][KH * KW * IC], rows beyond OC zero
+  const int8_t* w;        // [n_tiles * BN][Kpad]: per tap IC weights padded to whole channel blocks; rows beyond OC zero
   const ChanParams* chan; // [n_tiles * BN], bias already holds bias - izp * sum of all taps
   int8_t* out;            // [N, OH, OW, OC]
   int N, H, W, IC, OC, KH, KW, OH, OW, stride, pad_t, pad_l;

@@ -403,6 +403,30 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
   plan.tensor_loc.assign(nt, Loc{});
   std::vector<int> first_def(nt, -1), last_use(nt, -1), root(nt);
   for (int id = 0; id < nt; id++) root[id] = id;
+  // Chained concats: concat(concat(p, q), r) where the inner result is used nowhere else and the
+  // outer op passes it through unchanged (multiplier 2^30, shift 30, equal zero points) is written in
+  // place: the inner result becomes the leading columns of the outer one (same storage, the outer
+  // row stride) and the outer op only adds its second operand.
+  std::vector<int> concat_into(nt, -1);  // inner result tensor -> outer result tensor
+  {
+    std::vector<int> uses(nt, 0), producer(nt, -1);
+    for (int i = 0; i < (int)ops.size(); i++) {
+      for (int id : {ops[i].in0, ops[i].in1, ops[i].in2, ops[i].weights})
+        if (id >= 0 && id < nt) uses[id]++;
+      for (int id : {ops[i].out0, ops[i].out1})
+        if (id >= 0 && id < nt) producer[id] = i;
+    }
+    for (int i = 0; i < (int)ops.size(); i++) {
+      const auto& op = ops[i];
+      if (op.kind != TB200_OP_CONCAT || op.in0 < 0 || op.in0 >= nt || op.out0 < 0 || op.out0 >= nt) continue;
+      const int a = op.in0, pa = producer[a];
+      if (pa < 0 || ops[pa].kind != TB200_OP_CONCAT || uses[a] != 1 || tensors[a].kind != TB200_TENSOR_ACTIVATION ||
+          tensors[op.out0].kind != TB200_TENSOR_ACTIVATION)
+        continue;
+      if (op.in0_mult == (1 << 30) && op.in0_shift == 30 && op.in0_zp == op.out_zp && tensors[a].dtype == TB200_I8)
+        concat_into[a] = op.out0;
+    }
+  }
   for (int i = 0; i < (int)ops.size(); i++) {
     const auto& op = ops[i];
     int ins[3] = {op.in0, op.in1, op.in2};
@@ -420,6 +444,14 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         if (first_def[id] < 0) first_def[id] = i;
         last_use[id] = std::max(last_use[id], i);
       }
+    if (op.kind == TB200_OP_CONCAT && op.out0 >= 0 && concat_into[op.out0] >= 0) {
+      // written in place into the outer concat's result: that tensor's storage starts living here
+      int fin = op.out0;
+      while (concat_into[fin] >= 0) fin = concat_into[fin];
+      root[op.out0] = fin;
+      if (first_def[fin] < 0 || first_def[fin] > i) first_def[fin] = i;
+      last_use[fin] = std::max(last_use[fin], i);
+    }
     if (op.kind == TB200_OP_RESHAPE) {
       // a view: shares the storage (and the lifetime) of what it reshapes
       if (op.in0 < 0 || op.out0 < 0 || tensors[op.out0].kind != TB200_TENSOR_ACTIVATION ||
@@ -451,7 +483,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
     const size_t base = cursor;
     for (int i = 0; i < (int)ops.size(); i++) {
       int outs[2] = {ops[i].out0, ops[i].out1};
-      for (int id : outs) {
+      for (int out_id : outs) {
+        // a result written in place into a later tensor (concat chains) allocates that tensor now
+        const int id = out_id >= 0 && ops[i].kind == TB200_OP_CONCAT ? root[out_id] : out_id;
         if (id < 0 || tensors[id].kind != TB200_TENSOR_ACTIVATION || first_def[id] != i) continue;
         if (plan.tensor_loc[id].kind != Loc::NONE || root[id] != id) continue;
         size_t need = (bytes_of(id) + 255) & ~(size_t)255;
@@ -613,7 +647,13 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           ca.rnd_lo = (int)(cp[0].rnd & 0xffffffffll); ca.dmul = cp[0].dmul;
           const int rows = geo.n_tiles * geo.BN;
           std::vector<int8_t> wp((size_t)rows * geo.Kpad, 0);
-          memcpy(wp.data(), w, (size_t)OC * K);  // OHWI rows are already in (kh, kw, ic) order
+          // OHWI rows are already in (kh, kw, ic) order; every tap is padded to whole channel blocks
+          {
+            const size_t tap_pad = (size_t)geo.icb_per_tap * geo.row_bytes;
+            for (int oc = 0; oc < OC; oc++)
+              for (int t = 0; t < KH * KW; t++)
+                memcpy(wp.data() + (size_t)oc * geo.Kpad + t * tap_pad, w + ((size_t)oc * KH * KW + t) * IC, (size_t)IC);
+          }
           { ChanParams z{}; z.shift = 34; z.hshift = 2; z.rnd = 1ll << 33; cp.resize(rows, z); }
           // Border classes. The copy engine fills taps outside the frame with 0 where the op means the
           // input zero point; cp's bias assumed izp for every tap, so a pixel gets back
@@ -919,18 +959,24 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         a0.out_zp = a1.out_zp = op.out_zp;
         a0.clamp_min = a1.clamp_min = -128; a0.clamp_max = a1.clamp_max = 127;
         a0.double_round = a1.double_round = op.double_round;
-        a0.out_row_stride = a1.out_row_stride = CO;
+        // chained concats are written in place (see concat_into): rows are as wide as the last result of
+        // the chain, and an operand that is already in place is not copied
+        int fin = op.out0;
+        while (concat_into[fin] >= 0) fin = concat_into[fin];
+        const int row_stride = tensors[fin].shape[tensors[fin].rank - 1];
+        const bool in0_in_place = concat_into[op.in0] == op.out0;
+        a0.out_row_stride = a1.out_row_stride = row_stride;
         a0.out_col_offset = 0; a1.out_col_offset = C0;
         Loc l0 = loc(op.in0), l1 = loc(op.in1), lo = loc(op.out0);
         step.kernel_name = "concat_rescale";
-        step.launches = 2;
+        step.launches = in0_in_place ? 1 : 2;
         step.launch = [=](const ExecContext& c) {
           RescaleArgs k0 = a0, k1 = a1;
           k0.x = (const int8_t*)l0.resolve(c); k1.x = (const int8_t*)l1.resolve(c);
           k0.out = k1.out = (int8_t*)lo.resolve(c);
           k0.chan = (const ChanParams*)(c.consts + c0_off);
           k1.chan = (const ChanParams*)(c.consts + c1_off);
-          launch_rescale(k0, c.stream);
+          if (!in0_in_place) launch_rescale(k0, c.stream);
           launch_rescale(k1, c.stream);
         };
         break;
