@@ -72,7 +72,7 @@ IGEMM_CASES = [
     ((1, 12, 12, 64), 64, (3, 3), 1, (1, 1, 1, 1), 0),       # zero input zero point: no correction table
     ((1, 9, 140, 32), 32, (1, 7), 1, (0, 0, 3, 3), -20),     # one-row window, wide frame
     ((2, 20, 20, 80), 80, (3, 3), 1, (1, 1, 1, 1), 3),       # 80 channels: the last 32-byte block is half zero fill
-    ((1, 30, 34, 16), 32, (3, 3), 2, (0, 1, 0, 1), -6),      # 16 channels in a 32-byte block
+    ((1, 30, 34, 16), 32, (3, 3), 2, (0, 1, 0, 1), -6),      # 16 channels (dp4a kernel)
     ((1, 11, 11, 48), 16, (3, 3), 1, (1, 1, 1, 1), 8),       # 48 channels in one 64-byte block
 ]
 
@@ -93,7 +93,8 @@ def test_conv2d_implicit_gemm(device, case, mode):
                  requant_mode=mode)
     g.output(y)
     ex = Executable(device, g.serialize())
-    assert ex.op_kernels() == ["conv_igemm_i8_tcgen05"]
+    # 16 input channels make 16-byte operand rows: the direct dp4a kernel is faster and takes those
+    assert ex.op_kernels() == ["conv2d_c16_dp4a" if shape[3] == 16 else "conv_igemm_i8_tcgen05"]
     ex.destroy()
     _check(device, g, [x])
 
@@ -332,3 +333,37 @@ def test_chained_concats_are_written_in_place(device):
         assert ex.launch_count == want_launches + 1
         ex.destroy()
         _check(device, g, xs)
+
+
+@pytest.mark.parametrize("shape,OC,k,dil", [((1, 12, 12, 64), 32, 1, 1),    # 1x1: tensor-core GEMM
+                                            ((2, 14, 14, 32), 48, 3, 1),    # 3x3: tensor-core implicit GEMM
+                                            ((1, 18, 18, 16), 20, 3, 1),    # 16 channels: direct dp4a kernel
+                                            ((1, 20, 20, 3), 16, 3, 1),     # stem kernel
+                                            ((1, 11, 11, 24), 10, 3, 2)])   # dilation: generic CUDA-core kernel
+def test_table_fused_into_conv_epilogue(device, shape, OC, k, dil):
+    """conv -> table (SiLU as a 256-entry table follows every convolution of the detector): when the table is
+    the convolution's only reader it runs in the convolution's epilogue; same bytes as the two-kernel form."""
+    import os
+    from torq_b200.runtime import Executable
+    rng = np.random.default_rng(1234)
+    x = rng.integers(-128, 128, shape, dtype=np.int8)
+    w = rng.integers(-127, 128, (OC, k, k, shape[3]), dtype=np.int8)
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, OC) * 40.0 / (np.sqrt(k * k * shape[3]) * 74 * 74))
+    table = rng.integers(-128, 128, 256, dtype=np.int8)
+    p = dil * (k - 1) // 2
+    g = Graph()
+    y = g.conv2d(g.input(shape), w, np.round(rng.normal(0, 2000, OC)).astype(np.int32), m, s, dilation=(dil, dil),
+                 pad=(p, p, p, p), input_zp=-4, out_zp=3)
+    g.output(g.table(y, table))
+    ex = Executable(device, g.serialize())
+    assert ex.launch_count == 1, ex.op_kernels()
+    ex.destroy()
+    fused = _check(device, g, [x])[0]
+    os.environ["TB200_NO_TABLE_FUSION"] = "1"
+    try:
+        ex = Executable(device, g.serialize())
+        assert ex.launch_count == 2
+        ex.destroy()
+        assert (run_graph_gpu(device, g, [x])[0] == fused).all()
+    finally:
+        del os.environ["TB200_NO_TABLE_FUSION"]

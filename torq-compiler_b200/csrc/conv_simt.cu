@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(256) conv2d_simt_kernel(ConvArgs a) {
       int v = acc[i][j] - a.weight_zp * xsum[i] + cp[j].bias;
       q[j] = hi ? requant_cp<true>(v, cp[j], a.out_zp, a.clamp_min, a.clamp_max)
                 : requant_cp<false>(v, cp[j], a.out_zp, a.clamp_min, a.clamp_max);
+      if (a.lut) q[j] = __ldg(a.lut + q[j] + 128);
     }
     int8_t* o = a.out + (size_t)p * a.OC + oc0;
     if (vec_ok) {
@@ -251,8 +252,11 @@ __global__ void __launch_bounds__(128) conv2d_smallic_kernel(ConvArgs a) {
       const ChanParams cp = a.chan[oc];
 #pragma unroll
       for (int px = 0; px < kPix; px++)
+      {
         q[px][j] = hi ? requant_cp<true>(acc[px] + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max)
                       : requant_cp<false>(acc[px] + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max);
+        if (a.lut) q[px][j] = __ldg(a.lut + q[px][j] + 128);
+      }
     }
 #pragma unroll
     for (int px = 0; px < kPix; px++) {
@@ -320,6 +324,7 @@ __global__ void __launch_bounds__(128) conv2d_c16_kernel(ConvArgs a) {
       const ChanParams cp = a.chan[oc];
       q[j] = hi ? requant_cp<true>(acc + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max)
                 : requant_cp<false>(acc + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max);
+      if (a.lut) q[j] = __ldg(a.lut + q[j] + 128);
     }
     if ((a.OC & 3) == 0) {
       *reinterpret_cast<uint32_t*>(o + oc0) = pack4(q[0], q[1], q[2], q[3]);

@@ -191,7 +191,54 @@ __global__ void __launch_bounds__(kThreads) rescale_kernel(RescaleArgs a) {
   }
 }
 
+// 16 channels per thread when the rows allow 16-byte accesses; IDENT: the rescale is a pass-through
+// (multiplier 2^30, shift 30, equal zero points, full clamp range), i.e. a strided copy
+template <bool IDENT>
+__global__ void __launch_bounds__(kThreads) rescale_vec16_kernel(RescaleArgs a) {
+  const int cv = a.C >> 4;
+  const long long total = a.rows * cv;
+  const bool dr = a.double_round != 0;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int c16 = (int)(idx % cv);
+    const long long r = idx / cv;
+    uint4 v = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)r * a.C) + c16);
+    if (!IDENT) {
+      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        int o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const ChanParams cp = a.chan[a.per_channel ? c16 * 16 + q * 4 + j : 0];
+          o[j] = requant(sx8(w[q], j) - a.input_zp, cp.mult, cp.shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
+        }
+        w[q] = pack4(o[0], o[1], o[2], o[3]);
+      }
+      v = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    *reinterpret_cast<uint4*>(a.out + (size_t)r * a.out_row_stride + a.out_col_offset + c16 * 16) = v;
+  }
+}
+
 // ---- nearest 2x (PatternUtils.cpp:489-491): out[y,x] = in[y/2, x/2] ----
+__global__ void __launch_bounds__(kThreads) resize_nn2x_vec16_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ out,
+                                                                     int N, int H, int W, int C) {
+  const int cv = C >> 4;
+  const long long total = (long long)N * 2 * H * 2 * W * cv;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int c16 = (int)(idx % cv);
+    long long p = idx / cv;
+    const int ow = (int)(p % (2 * W));
+    long long t = p / (2 * W);
+    const int oh = (int)(t % (2 * H));
+    const int n = (int)(t / (2 * H));
+    reinterpret_cast<uint4*>(out)[idx] =
+        __ldg(reinterpret_cast<const uint4*>(x + (((size_t)n * H + (oh >> 1)) * W + (ow >> 1)) * C) + c16);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) resize_nn2x_kernel(const int8_t* __restrict__ x,
                                                                int8_t* __restrict__ out, int N, int H,
                                                                int W, int C) {
@@ -239,10 +286,18 @@ void launch_table(const int8_t* x, const int8_t* table, int8_t* out, long long n
 }
 
 void launch_rescale(const RescaleArgs& a, cudaStream_t stream) {
-  rescale_kernel<<<grid_for(a.rows * a.C), kThreads, 0, stream>>>(a);
+  const bool vec = (a.C & 15) == 0 && (a.out_row_stride & 15) == 0 && (a.out_col_offset & 15) == 0 &&
+                   ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0;
+  if (vec && a.identity) rescale_vec16_kernel<true><<<grid_for(a.rows * (a.C >> 4)), kThreads, 0, stream>>>(a);
+  else if (vec) rescale_vec16_kernel<false><<<grid_for(a.rows * (a.C >> 4)), kThreads, 0, stream>>>(a);
+  else rescale_kernel<<<grid_for(a.rows * a.C), kThreads, 0, stream>>>(a);
 }
 
 void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream) {
+  if ((C & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    resize_nn2x_vec16_kernel<<<grid_for((long long)N * 4 * H * W * (C >> 4)), kThreads, 0, stream>>>(x, out, N, H, W, C);
+    return;
+  }
   resize_nn2x_kernel<<<grid_for((long long)N * 4 * H * W * C), kThreads, 0, stream>>>(x, out, N, H, W, C);
 }
 

@@ -75,6 +75,7 @@ struct GemmTcParams {
   const uint8_t* ccls;  // [OW] column class
   const uint8_t* cls_nonzero;  // [classes] 1 when the class has a non-zero correction
   int ncc;              // column classes
+  const int8_t* lut;    // 256-entry table applied to the int8 result (a fused tosa.table), or null
   int tma_store;        // stage the output tile in shared memory and write it with one TMA store
   uint32_t staging_off; // byte offset of the staging buffers inside dynamic shared memory
   int* status;
@@ -223,6 +224,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bar_w;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(16) int4 cp_s[kEpiGroups][128];  // per epilogue group: {bias, mult, rnd_hi, shift - 32}
+  __shared__ __align__(16) uint8_t lut_s[256];           // fused table, indexed by value + 128
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -247,6 +249,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  if (p.lut && threadIdx.x >= 64 && threadIdx.x < 64 + 256) lut_s[threadIdx.x - 64] = (uint8_t)p.lut[threadIdx.x - 64];
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                  "r"((uint32_t)p.tmem_cols)
@@ -439,6 +442,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               }
             }
             w4[g] = clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
+            if (p.lut) {  // out = table[value + 128], byte by byte
+              const uint32_t x = w4[g] ^ 0x80808080u;
+              w4[g] = (uint32_t)lut_s[x & 0xff] | ((uint32_t)lut_s[(x >> 8) & 0xff] << 8) |
+                      ((uint32_t)lut_s[(x >> 16) & 0xff] << 16) | ((uint32_t)lut_s[x >> 24] << 24);
+            }
           }
           if (p.tma_store) {
             *reinterpret_cast<uint4*>(srow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
@@ -680,6 +688,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   p.acc_stages = kEpiGroups;  // BN <= 128, so 4 stages fit the 512 TMEM columns
   p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
+  p.lut = a.lut;
   p.staging_off = (uint32_t)((p.w_resident ? w_bytes : 0) + (size_t)stages * stage_bytes);
   const size_t smem = 1024 + p.staging_off + staging_bytes;
   static bool attr_set = false;
@@ -797,6 +806,7 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   p.acc_stages = kEpiGroups;
   p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
+  p.lut = a.lut;
   p.staging_off = (uint32_t)((p.w_resident ? w_bytes : 0) + (size_t)stages * stage_bytes);
   const size_t smem = 1024 + p.staging_off + staging_bytes;
   static bool attr_set = false;

@@ -19,6 +19,7 @@ struct ConvArgs {
   int input_zp, weight_zp, out_zp, clamp_min, clamp_max;
   int double_round;
   int hi_shift;           // every rescale shift of the op is >= 32
+  const int8_t* lut;      // 256-entry table applied to the int8 result (out = lut[q + 128]), or null
 };
 void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream);
 const char* conv2d_simt_kernel_name(const ConvArgs& a);  // which CUDA-core kernel the launcher picks
@@ -77,6 +78,7 @@ struct RescaleArgs {
   long long rows;
   int C, per_channel, input_zp, out_zp, clamp_min, clamp_max, double_round;
   int out_row_stride, out_col_offset;  // lets a concat write into a wider row
+  int identity;  // the rescale passes values through unchanged (set by the planner): a strided copy
 };
 void launch_rescale(const RescaleArgs& a, cudaStream_t stream);
 
@@ -102,6 +104,7 @@ struct GemmTcArgs {
   int hi33;               // every rescale shift >= 33: the 16-byte-constant epilogue applies
   int rnd_lo, dmul;       // with hi33: low word of the rounding constant, negative-accumulator term
   int* status;            // device status word: a kernel whose bounded wait expires writes a code here
+  const int8_t* lut;      // 256-entry table applied to the int8 result, or null
 };
 struct GemmTcState;       // cached tensor maps of one GEMM step
 GemmTcState* gemm_tc_state_new();
@@ -134,6 +137,7 @@ struct ConvTcArgs {
   const uint8_t* cls_nonzero;
   int ncc;
   int* status;
+  const int8_t* lut;      // 256-entry table applied to the int8 result, or null
 };
 cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t stream);
 

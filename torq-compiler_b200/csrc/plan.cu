@@ -408,6 +408,10 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
   // place: the inner result becomes the leading columns of the outer one (same storage, the outer
   // row stride) and the outer op only adds its second operand.
   std::vector<int> concat_into(nt, -1);  // inner result tensor -> outer result tensor
+  // A 256-entry table that is the only reader of a convolution's result (the reference fuses the same
+  // pair: OptimizeSwishActivationPattern.cpp:100-190) is applied in the convolution's epilogue.
+  std::vector<int> table_after(ops.size(), -1);  // conv op -> index of its fused table op
+  std::vector<char> fused_away(ops.size(), 0);
   {
     std::vector<int> uses(nt, 0), producer(nt, -1);
     for (int i = 0; i < (int)ops.size(); i++) {
@@ -426,11 +430,22 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
       if (op.in0_mult == (1 << 30) && op.in0_shift == 30 && op.in0_zp == op.out_zp && tensors[a].dtype == TB200_I8)
         concat_into[a] = op.out0;
     }
+    const char* no_fuse = getenv("TB200_NO_TABLE_FUSION");
+    for (int i = 0; i < (int)ops.size() && !(no_fuse && *no_fuse && *no_fuse != '0'); i++) {
+      const auto& op = ops[i];
+      if (op.kind != TB200_OP_TABLE || op.in0 < 0 || op.in0 >= nt || op.out0 < 0 || op.out0 >= nt) continue;
+      const int src = op.in0, pc = producer[src];
+      if (pc < 0 || pc >= i || ops[pc].kind != TB200_OP_CONV2D || uses[src] != 1 || table_after[pc] >= 0 ||
+          tensors[src].kind != TB200_TENSOR_ACTIVATION || tensors[src].dtype != TB200_I8 || tensors[op.out0].dtype != TB200_I8)
+        continue;
+      table_after[pc] = i;
+      fused_away[i] = 1;
+    }
   }
   for (int i = 0; i < (int)ops.size(); i++) {
     const auto& op = ops[i];
     int ins[3] = {op.in0, op.in1, op.in2};
-    int outs[2] = {op.out0, op.out1};
+    int outs[3] = {op.out0, op.out1, table_after[i] >= 0 ? ops[table_after[i]].out0 : -1};
     for (int id : ins)
       if (id >= 0) {
         if (!b.valid_id(id)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input tensor id %d out of range", i, id);
@@ -482,7 +497,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
     size_t high = cursor;
     const size_t base = cursor;
     for (int i = 0; i < (int)ops.size(); i++) {
-      int outs[2] = {ops[i].out0, ops[i].out1};
+      int outs[3] = {ops[i].out0, ops[i].out1, table_after[i] >= 0 ? ops[table_after[i]].out0 : -1};
       for (int out_id : outs) {
         // a result written in place into a later tensor (concat chains) allocates that tensor now
         const int id = out_id >= 0 && ops[i].kind == TB200_OP_CONCAT ? root[out_id] : out_id;
@@ -525,10 +540,29 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
       if (id >= 0 && tensors[id].kind != TB200_TENSOR_CONSTANT && plan.tensor_loc[id].kind == Loc::NONE)
         return b.fail(TB200_INVALID_ARGUMENT, "op %d reads tensor %d before anything wrote it", i, id);
 
+    if (fused_away[i]) {
+      step.kernel_name = "(table in the convolution's epilogue)";
+      step.launches = 0;
+      step.launch = [](const ExecContext&) {};
+      plan.steps.push_back(std::move(step));
+      continue;
+    }
     switch (op.kind) {
       case TB200_OP_CONV2D:
       case TB200_OP_FC: {
         const bool fc = op.kind == TB200_OP_FC;
+        // a table fused into the epilogue: the result goes to the table op's output
+        const int fused_table = table_after[i];
+        const int result_id = fused_table >= 0 ? ops[fused_table].out0 : op.out0;
+        size_t lut_off = 0;
+        if (fused_table >= 0) {
+          const int8_t* tbl = b.const_data<int8_t>(ops[fused_table].table, 256, "table", fused_table);
+          if (!tbl) return b.status;
+          if (b.numel(ops[fused_table].out0) != b.numel(op.out0))
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: table wants int8 input/output of equal size", fused_table);
+          lut_off = b.add_const(tbl, 256);
+        }
+        const bool has_lut = fused_table >= 0;
         int N, H, W, IC, OC, KH, KW, OH, OW;
         if (fc) {
           if (!b.act_i8(op.in0, 2) || !b.act_i8(op.out0, 2) || !b.valid_id(op.weights) || tensors[op.weights].rank != 2)
@@ -615,7 +649,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           { ChanParams z{}; z.shift = 34; z.hshift = 2; z.rnd = 1ll << 33; cp.resize(rows, z); }
           size_t w_off = b.add_const(wp.data(), wp.size());
           size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
-          Loc lx = loc(op.in0), lo = loc(op.out0);
+          Loc lx = loc(op.in0), lo = loc(result_id);
           std::shared_ptr<GemmTcState> st(gemm_tc_state_new(), gemm_tc_state_free);
           step.kernel_name = "gemm_i8_tcgen05";
           step.launch = [=](const ExecContext& c) {
@@ -625,6 +659,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             k.w = (const int8_t*)(c.consts + w_off);
             k.chan = (const ChanParams*)(c.consts + c_off);
             k.status = c.status;
+            k.lut = has_lut ? (const int8_t*)(c.consts + lut_off) : nullptr;
             launch_gemm_i8_tc(k, st.get(), c.stream);
           };
           break;
@@ -632,7 +667,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
 
         // KH x KW convolution with symmetric weights: implicit GEMM on the tensor cores (one TMA box per
         // tap and channel block, taps accumulated in TMEM; see gemm_tcgen05.cu)
-        if (!fc && !pointwise && op.weight_zp == 0 && !force_simt() &&
+        // (16 input channels: the copy engine's per-row cost makes 16-byte rows a poor tensor-core operand;
+        // the direct dp4a kernel is faster there)
+        if (!fc && !pointwise && op.weight_zp == 0 && !force_simt() && IC != 16 &&
             conv_tc_supported(N, H, W, IC, OC, KH, KW, op.stride_h, op.stride_w, op.dil_h, op.dil_w, OH, OW)) {
           const ConvTcGeometry geo = conv_tc_geometry(OH, OW, IC, OC, KH, KW);
           ConvTcArgs ca{};
@@ -709,7 +746,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             nz_off = b.add_const(nonzero.data(), nonzero.size());
             ca.ncc = (int)cmasks.size();
           }
-          Loc lx = loc(op.in0), lo = loc(op.out0);
+          Loc lx = loc(op.in0), lo = loc(result_id);
           std::shared_ptr<GemmTcState> st(gemm_tc_state_new(), gemm_tc_state_free);
           step.kernel_name = "conv_igemm_i8_tcgen05";
           step.launch = [=](const ExecContext& c) {
@@ -725,6 +762,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
               k.cls_nonzero = (const uint8_t*)(c.consts + nz_off);
             }
             k.status = c.status;
+            k.lut = has_lut ? (const int8_t*)(c.consts + lut_off) : nullptr;
             const cudaError_t e = launch_conv_i8_tc(k, st.get(), c.stream);
             if (e != cudaSuccess && c.launch_error) *c.launch_error = e;
           };
@@ -744,7 +782,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max; a.double_round = dr; a.hi_shift = b.last_hi_shift;
         size_t w_off = b.add_const(packed.data(), packed.size());
         size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
-        Loc lx = loc(op.in0), lo = loc(op.out0);
+        Loc lx = loc(op.in0), lo = loc(result_id);
         step.kernel_name = conv2d_simt_kernel_name(a);
         step.launch = [=](const ExecContext& c) {
           ConvArgs k = a;
@@ -752,6 +790,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           k.out = (int8_t*)lo.resolve(c);
           k.w = (const int8_t*)(c.consts + w_off);
           k.chan = (const ChanParams*)(c.consts + c_off);
+          k.lut = has_lut ? (const int8_t*)(c.consts + lut_off) : nullptr;
           launch_conv2d_simt(k, c.stream);
         };
         break;
@@ -967,6 +1006,8 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         const bool in0_in_place = concat_into[op.in0] == op.out0;
         a0.out_row_stride = a1.out_row_stride = row_stride;
         a0.out_col_offset = 0; a1.out_col_offset = C0;
+        a0.identity = op.in0_mult == (1 << 30) && op.in0_shift == 30 && op.in0_zp == op.out_zp;
+        a1.identity = op.in1_mult == (1 << 30) && op.in1_shift == 30 && op.in1_zp == op.out_zp;
         Loc l0 = loc(op.in0), l1 = loc(op.in1), lo = loc(op.out0);
         step.kernel_name = "concat_rescale";
         step.launches = in0_in_place ? 1 : 2;
