@@ -144,7 +144,9 @@ def test_depthwise(device, case, mode):
 
 
 @pytest.mark.parametrize("M,K,N,azp", [(1, 512, 512, 0), (64, 512, 512, -7), (512, 1024, 1024, 0), (5, 40, 9, -7),
-                                       (33, 100, 130, 3), (256, 1280, 1000, -2)])
+                                       (33, 100, 130, 3), (256, 1280, 1000, -2),
+                                       # the large corners of the FC sweep (M up to 4096, K = N up to 8192)
+                                       (64, 4096, 4096, -7), (1, 8192, 8192, 0), (512, 8192, 8192, -7), (4096, 4096, 4096, 0)])
 def test_fully_connected(device, M, K, N, azp):
     rng = np.random.default_rng(1234)
     a = rng.integers(-128, 128, (M, K), dtype=np.int8)

@@ -621,7 +621,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             rgroup *= 2;
         }
         if (pointwise && op.weight_zp == 0 && !force_simt() && rgroup <= 8 && M % rgroup == 0 &&
-            (long long)OC * rgroup <= 4096 && gemm_tc_supported(M / rgroup, OC * rgroup, (int)K * rgroup, K * rgroup)) {
+            (long long)OC * rgroup <= 65536 && gemm_tc_supported(M / rgroup, OC * rgroup, (int)K * rgroup, K * rgroup)) {
           GemmTcArgs ga{};
           const int Ng = OC * rgroup, Kg = (int)K * rgroup;
           const GemmTcGeometry geo = gemm_tc_geometry(Ng, Kg);
