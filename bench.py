@@ -252,9 +252,9 @@ def main():
     ap.add_argument("--no-yolo", action="store_true", help="skip the YOLOv8n-style detector timing")
     ap.add_argument("--decode-prompt", type=int, default=1024, help="prompt length of the decode metric")
     ap.add_argument("--decode-gen", type=int, default=128, help="generated tokens of the decode metric")
-    ap.add_argument("--only", choices=["all", "cnn", "decoder"], default="all",
+    ap.add_argument("--only", choices=["all", "cnn", "decoder", "yolo"], default="all",
                     help="profiling aid: 'cnn' runs just the timed MobileNetV2 steps, 'decoder' just the decode metric "
-                         "(one GPU); the JSON line then carries only that part")
+                         "(one GPU), 'yolo' just the detector timing; the JSON line then carries only that part")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -281,6 +281,10 @@ def main():
 
     B = args.batch
     dev = Device(local_rank)
+    if args.only == "yolo":
+        stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local_rank))
+        print(json.dumps({"only": "yolo", **yolo_bench(dev, stream, steps=args.steps)}), flush=True)
+        return
     if args.only == "decoder":
         stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local_rank))
         runs = [decoder_bench(dev, stream, int(t), args.decode_prompt, args.decode_gen) for t in args.decoder.split(",") if t]
