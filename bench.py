@@ -356,9 +356,9 @@ def main():
     e2e_value = B * world * e2e_steps / (ms_e2e * 1e-3)
     clocks = sampler.stop() if sampler else None
 
-    # ---- tensor-parallel decode over all ranks (the group size must divide the 4 query heads) ----
+    # ---- tensor-parallel decode over all ranks ----
     decoder_tp = None
-    if world > 1 and args.decoder and 4 % world == 0:
+    if world in (2, 4, 8) and args.decoder:
         decoder_tp = []
         for bsz in [int(t) for t in args.decoder.split(",") if t]:
             if bsz > 8:

@@ -11,10 +11,10 @@ import pytest
 from torq_b200.bf16 import from_bf16
 from torq_b200.workloads import gemma3
 
-CFG = gemma3.GemmaConfig(layers=2, hidden=128, intermediate=256, vocab=512, window=8, local_per_global=1, max_seq=32)
+CFG = gemma3.GemmaConfig(layers=2, hidden=128, intermediate=64 * 11, vocab=512, window=8, local_per_global=1, max_seq=32)
 
 
-@pytest.mark.parametrize("tp", [2, 4])
+@pytest.mark.parametrize("tp", [2, 4, 8])
 def test_shards_add_up_to_the_full_projections(tp):
     P = gemma3.random_weights(CFG, 5)
     shards = [gemma3.shard_weights(CFG, P, tp, r) for r in range(tp)]
@@ -22,25 +22,33 @@ def test_shards_add_up_to_the_full_projections(tp):
     D, nq, I = CFG.head_dim, CFG.n_q, CFG.intermediate
     L = P["layers"][0]
     # q rows split by head, the KV head replicated
-    q_rows = np.concatenate([s["layers"][0]["qkv"][0][:nq // tp * D] for s in shards])
-    assert (q_rows == L["qkv"][0][:nq * D]).all()
     for s in shards:
-        assert (s["layers"][0]["qkv"][0][nq // tp * D:] == L["qkv"][0][nq * D:]).all()
+        lay = s["layout"]
+        hq, h0 = lay["heads"], lay["head0"]
+        assert (s["layers"][0]["qkv"][0][:hq * D] == L["qkv"][0][h0 * D:(h0 + hq) * D]).all()
+        assert (s["layers"][0]["qkv"][0][hq * D:] == L["qkv"][0][nq * D:]).all()
+        # the o slice starts o_k_offset columns into the local attention output (the GPU's heads)
+        assert lay["o_cols"][0] == h0 * D + lay["o_k_offset"] and 0 <= lay["o_k_offset"] < hq * D
+    # every query head is computed by someone, the o columns tile [0, n_q * D)
+    assert sorted({h for s in shards for h in range(s["layout"]["head0"], s["layout"]["head0"] + s["layout"]["heads"])}) == list(range(nq))
+    assert [s["layout"]["o_cols"] for s in shards] == [(r * nq * D // tp, (r + 1) * nq * D // tp) for r in range(tp)]
     # o and down: the sum over the ranks of the K-split products is the full product (exact in integers)
     a = rng.integers(-50, 50, nq * D).astype(np.int64)
     full = L["o"][0].astype(np.int64) @ a
-    parts = sum(s["layers"][0]["o"][0].astype(np.int64) @ a[r * nq // tp * D:(r + 1) * nq // tp * D] for r, s in enumerate(shards))
+    parts = sum(s["layers"][0]["o"][0].astype(np.int64) @ a[s["layout"]["o_cols"][0]:s["layout"]["o_cols"][1]] for s in shards)
     assert (full == parts).all()
     act = rng.integers(-50, 50, I).astype(np.int64)
     full = L["down"][0].astype(np.int64) @ act
-    parts = sum(s["layers"][0]["down"][0].astype(np.int64) @ act[r * I // tp:(r + 1) * I // tp] for r, s in enumerate(shards))
+    parts = sum(s["layers"][0]["down"][0].astype(np.int64) @ act[s["layout"]["mlp"][0]:s["layout"]["mlp"][1]] for s in shards)
     assert (full == parts).all()
-    # gate/up: shard r holds gate rows and the matching up rows of its slice, with their scales
-    for r, s in enumerate(shards):
+    assert shards[0]["layout"]["mlp"][0] == 0 and shards[-1]["layout"]["mlp"][1] == I
+    # gate/up: a shard holds the gate rows and the matching up rows of its slice, with their scales
+    for s in shards:
         w, sc = s["layers"][0]["gate_up"]
-        Il = I // tp
-        assert (w[:Il] == L["gate_up"][0][r * Il:(r + 1) * Il]).all() and (w[Il:] == L["gate_up"][0][I + r * Il:I + (r + 1) * Il]).all()
-        assert (from_bf16(sc[Il:]) == from_bf16(L["gate_up"][1][I + r * Il:I + (r + 1) * Il])).all()
+        i0, i1 = s["layout"]["mlp"]
+        Il = i1 - i0
+        assert Il % 64 == 0 and (w[:Il] == L["gate_up"][0][i0:i1]).all() and (w[Il:] == L["gate_up"][0][I + i0:I + i1]).all()
+        assert (from_bf16(sc[Il:]) == from_bf16(L["gate_up"][1][I + i0:I + i1])).all()
     # LM head: vocabulary rows in rank order
     assert (np.concatenate([s["lm_head"][0] for s in shards]) == P["embed"][0]).all()
     assert [s["vocab_offset"] for s in shards] == [r * CFG.vocab // tp for r in range(tp)]

@@ -27,6 +27,9 @@ def main():
     dist.init_process_group("gloo")  # host transport for the handles only
     cfg = {"small": gemma3.GemmaConfig(layers=3, hidden=256, intermediate=1024, vocab=4096, window=24, local_per_global=2,
                                        max_seq=96),
+           # 8 GPUs: every GPU needs at least as many rows of each projection as it has SMs
+           "small8": gemma3.GemmaConfig(layers=3, hidden=256, intermediate=64 * 27, vocab=4096, window=24, local_per_global=2,
+                                        max_seq=96),
            "full": gemma3.GemmaConfig()}[size_name]
     params = gemma3.random_weights(cfg, 1234, gain)
     dev = Device(local)
@@ -38,7 +41,7 @@ def main():
     vl = cfg.vocab // world
     d_tok, d_pos = dev.alloc(batch * 4), dev.alloc(4)
     d_next, d_logits = dev.alloc(batch * 4), dev.alloc(batch * vl * 4)
-    ref = RefDecoder(cfg, params, batch, device="cpu" if size_name == "small" else None) if rank == 0 else None
+    ref = RefDecoder(cfg, params, batch, device="cpu" if size_name.startswith("small") else None) if rank == 0 else None
     rng = np.random.default_rng(7)
     toks = rng.integers(0, cfg.vocab, (steps, batch)).astype(np.int32)
     worst, agree, total = 0.0, 0, 0

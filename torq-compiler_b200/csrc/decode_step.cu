@@ -242,7 +242,7 @@ __device__ __forceinline__ Phase make_phase(const DecodeStepArgs& a, const Decod
     case kQkv: p.W = (const int8_t*)(a.consts + L->w_qkv); p.scale = (const uint16_t*)(a.consts + L->s_qkv);
       p.K = a.H; p.N = (a.n_q + 2) * kD; break;
     case kO: p.W = (const int8_t*)(a.consts + L->w_o); p.scale = (const uint16_t*)(a.consts + L->s_o);
-      p.K = a.n_q * kD; p.N = a.H; break;
+      p.K = a.o_k; p.N = a.H; break;  // a.o_k < n_q * 256 when a head is shared by two tensor-parallel GPUs
     case kGateUp: p.W = (const int8_t*)(a.consts + L->w_gu); p.scale = (const uint16_t*)(a.consts + L->s_gu);
       p.K = a.H; p.N = a.I; p.kind = kPairs; break;
     case kDown: p.W = (const int8_t*)(a.consts + L->w_down); p.scale = (const uint16_t*)(a.consts + L->s_down);
@@ -816,7 +816,8 @@ __device__ __forceinline__ void stage_attention(const DecodeStepArgs& a, const S
   char* xin = sm.base + sm.off_xin;
   float* red = (float*)(sm.base + sm.off_red);
   float* xscale = (float*)(sm.base + sm.off_red + kRedXscale);
-  const int width = a.n_q * kD, vec = width / 8;  // <= 128 vectors of 8 values per batch row
+  // this GPU's K slice of the o projection: columns [o_k_offset, o_k_offset + o_k) of the local attention output
+  const int width = a.n_q * kD, vec = a.o_k / 8;  // <= 128 vectors of 8 values per batch row
   uint4 v[BT];
   float amax[BT];
 #pragma unroll
@@ -824,7 +825,7 @@ __device__ __forceinline__ void stage_attention(const DecodeStepArgs& a, const S
     amax[b] = 0.f;
     v[b] = make_uint4(0, 0, 0, 0);
     if (b < a.B && tid < vec) {
-      v[b] = __ldcg((const uint4*)(src + (size_t)b * width) + tid);
+      v[b] = __ldcg((const uint4*)(src + (size_t)b * width + a.o_k_offset) + tid);
       const uint32_t w[4] = {v[b].x, v[b].y, v[b].z, v[b].w};
 #pragma unroll
       for (int j = 0; j < 4; j++)

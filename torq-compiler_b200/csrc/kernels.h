@@ -197,7 +197,8 @@ struct DecodeStepArgs {
   // tensor parallelism: this GPU's rank, the group size, every member's scratch area as mapped
   // into this process (peer_scratch[rank] == scratch), the inboxes of the K-split projections
   // (scratch offsets, fp32 [tp][B][H]) and the first vocabulary row of this GPU's LM-head shard
-  int tp, rank, vocab_offset, pad_;
+  int tp, rank, vocab_offset;
+  int o_k, o_k_offset;  // K of the o projection and where its slice starts in the local attention output
   unsigned long long inbox_o_off, inbox_d_off;
   char* peer_scratch[8];
 };

@@ -254,8 +254,13 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
   };
   auto gemv_ok = [&](const tb200_op_t& g, int in, int N, int K, bool f32) {
     return g.in0 == in && inter(in) && T[g.weights].rank == 2 && T[g.weights].shape[0] == N && T[g.weights].shape[1] == K &&
-           T[g.out0].dtype == (f32 ? TB200_F32 : TB200_BF16) && T[g.in0].shape[0] == B;
+           T[g.out0].dtype == (f32 ? TB200_F32 : TB200_BF16) && T[g.in0].shape[0] == B && g.i1 == 0 &&
+           T[g.in0].shape[1] == K;
   };
+  // the o projection may take a K slice of the attention output (a head shared by two GPUs)
+  const int o_k = T[lo[4]->weights].shape[1], o_k_offset = lo[4]->i1;
+  if (o_k < 64 || o_k % 64 != 0 || o_k_offset < 0 || o_k_offset % 8 != 0 || o_k_offset + o_k > n_q * D) return false;
+  if (!tp_graph && (o_k != n_q * D || o_k_offset != 0)) return false;
   auto norm_ok = [&](const tb200_op_t& r, int in, int res) {
     return r.in0 == in && r.in1 == res && r.f0 == eps && T[r.in0].shape[1] == H && T[r.in0].shape[0] == B;
   };
@@ -283,7 +288,13 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
       return red->out0;
     };
     const int o_out = reduced(o[4], ar[2 * l]);
-    if (o_out < 0 || !gemv_ok(o[4], att.out0, H, n_q * D, tp_graph) || !norm_ok(o[5], o_out, x) || !inter(o_out)) return false;
+    {
+      const tb200_op_t& og = o[4];  // like gemv_ok, with the K slice
+      if (og.in0 != att.out0 || !inter(og.in0) || T[og.weights].rank != 2 || T[og.weights].shape[0] != H ||
+          T[og.weights].shape[1] != o_k || og.i1 != o_k_offset || T[og.out0].dtype != (tp_graph ? TB200_F32 : TB200_BF16))
+        return false;
+    }
+    if (o_out < 0 || !norm_ok(o[5], o_out, x) || !inter(o_out)) return false;
     x = o[5].out0;
     if (!inter(x) || !norm_ok(o[6], x, -1) || !gemv_ok(o[7], o[6].out0, 2 * I, H, false)) return false;
     if (o[8].in0 != o[7].out0 || !inter(o[8].in0) || T[o[8].out0].shape[1] != I) return false;
@@ -293,7 +304,7 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
     if (!inter(x)) return false;
     if (!cst(o[0].weights, (size_t)H * 2, d.in_norm) || !cst(o[1].weights, (size_t)(n_q + 2) * D * H, d.w_qkv) ||
         !cst(o[1].bias, (size_t)(n_q + 2) * D * 2, d.s_qkv) || !cst(rope.weights, (size_t)D * 2, d.q_norm) ||
-        !cst(rope.bias, (size_t)D * 2, d.k_norm) || !cst(o[4].weights, (size_t)H * n_q * D, d.w_o) ||
+        !cst(rope.bias, (size_t)D * 2, d.k_norm) || !cst(o[4].weights, (size_t)H * o_k, d.w_o) ||
         !cst(o[4].bias, (size_t)H * 2, d.s_o) || !cst(o[5].weights, (size_t)H * 2, d.post_attn_norm) ||
         !cst(o[6].weights, (size_t)H * 2, d.pre_ffn_norm) || !cst(o[7].weights, (size_t)2 * I * H, d.w_gu) ||
         !cst(o[7].bias, (size_t)2 * I * 2, d.s_gu) || !cst(o[9].weights, (size_t)H * I, d.w_down) ||
@@ -339,6 +350,7 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
   a.layers_off = b.add_const(descs.data(), descs.size() * sizeof(DecodeLayerDesc));
   a.n_layers = L; a.B = B; a.H = H; a.n_q = n_q; a.I = I; a.V = V; a.V_embed = V_embed; a.T = Tlen;
   a.tp = tp; a.rank = rank; a.vocab_offset = tp_graph ? am.i0 : 0;
+  a.o_k = o_k; a.o_k_offset = o_k_offset;
   a.eps = eps; a.attn_scale = attn_scale; a.embed_mult = emb.f0; a.grid = sms;
   a.theta[0] = thetas[0]; a.theta[1] = thetas[1];
   scratch_need = std::max(scratch_need, decode_step_scratch_bytes(B, H, n_q, I, L, sms, tp, &a));
@@ -1078,9 +1090,13 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             !b.valid_id(op.weights) || tensors[op.weights].rank != 2 || tensors[op.weights].dtype != TB200_I8)
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: gemv_w8 wants bf16 [B,K] x int8 [N,K] -> bf16 or f32 [B,N]", i);
         const int y_f32 = tensors[op.out0].dtype == TB200_F32;
-        const int B = tensors[op.in0].shape[0], K = tensors[op.in0].shape[1], N = tensors[op.weights].shape[0];
-        if (tensors[op.weights].shape[1] != K || tensors[op.out0].shape[0] != B || tensors[op.out0].shape[1] != N)
+        const int B = tensors[op.in0].shape[0], N = tensors[op.weights].shape[0];
+        // i1 > 0 or a narrower weight matrix: the product takes columns [i1, i1 + K) of the input (a tensor-
+        // parallel shard whose K slice is part of a head); only the fused decode step implements that
+        const int K = tensors[op.weights].shape[1];
+        if (op.i1 < 0 || op.i1 + K > tensors[op.in0].shape[1] || tensors[op.out0].shape[0] != B || tensors[op.out0].shape[1] != N)
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: gemv_w8 shape mismatch", i);
+        if (op.i1 != 0 || K != tensors[op.in0].shape[1]) needs_fusion = true;
         if (K % 16 != 0 || B > 32) return b.fail(TB200_UNIMPLEMENTED, "op %d: gemv_w8 needs K %% 16 == 0 and batch <= 32", i);
         size_t w_off, s_off;
         if (!b.add_raw_const(op.weights, (size_t)N * K, "weights", i, w_off)) return b.status;

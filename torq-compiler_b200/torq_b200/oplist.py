@@ -280,14 +280,16 @@ class Graph:
         ins = [x] + ([residual] if residual is not None else [])
         return self._emit("rmsnorm", ins, x.shape, "bf16", consts={"weights": w}, f0=float(eps))
 
-    def gemv_w8(self, x, weights_i8, scales_bf16, splits: int = 0, out_dtype: str = "bf16"):
-        """y[b, n] = scale[n] * sum_k x[b, k] * W[n, k], rounded to bf16 or kept in fp32 (out_dtype "f32");
-        W is [N, K] int8."""
+    def gemv_w8(self, x, weights_i8, scales_bf16, splits: int = 0, out_dtype: str = "bf16", in_offset: int = 0):
+        """y[b, n] = scale[n] * sum_k x[b, in_offset + k] * W[n, k], rounded to bf16 or kept in fp32 (out_dtype
+        "f32"); W is [N, K] int8. A W narrower than x (with in_offset) takes a column slice of x; that form
+        exists only inside the fused decode step (tensor-parallel shards)."""
         w = weights_i8 if isinstance(weights_i8, TensorRef) else self.const(np.asarray(weights_i8, np.int8))
         sc = scales_bf16 if isinstance(scales_bf16, TensorRef) else self.const(np.asarray(scales_bf16, np.uint16), "bf16")
-        if w.shape[1] != x.shape[1]:
+        if in_offset < 0 or in_offset + w.shape[1] > x.shape[1] or (in_offset == 0 and w.shape[1] != x.shape[1] and out_dtype != "f32"):
             raise ValueError("weight K mismatch")
-        return self._emit("gemv_w8", [x], (x.shape[0], w.shape[0]), out_dtype, consts={"weights": w, "bias": sc}, i0=splits)
+        return self._emit("gemv_w8", [x], (x.shape[0], w.shape[0]), out_dtype, consts={"weights": w, "bias": sc}, i0=splits,
+                          i1=int(in_offset))
 
     def rope_kv(self, qkv, pos, q_norm_w, k_norm_w, k_cache, v_cache, *, n_q, n_kv, head_dim, theta, eps):
         """Per-head RMSNorm + rotary on q and k at position pos; k and v appended to the caches

@@ -79,29 +79,46 @@ def random_weights(cfg: GemmaConfig, seed: int = 1234, embed_gain: float = 0.02)
     return P
 
 
+def shard_layout(cfg: GemmaConfig, tp: int, rank: int) -> dict:
+    """Which rows and columns rank `rank` of `tp` owns. Up to n_q GPUs each take whole query heads; beyond
+    that (tp a multiple of n_q) a head is computed by tp / n_q GPUs, each of which takes a column slice of
+    that head for the o projection. The MLP width is split in blocks of 64 (unevenly when it must be)."""
+    D, I, nq = cfg.head_dim, cfg.intermediate, cfg.n_q
+    if cfg.n_kv != 1 or I % 64 or cfg.vocab % tp or not (nq % tp == 0 or tp % nq == 0) or (nq * D // tp) % 64:
+        raise ValueError("unsupported tensor-parallel group size for this shape")
+    share = max(1, tp // nq)            # GPUs per head
+    hq = max(1, nq // tp)               # heads per GPU
+    head0 = rank // share if tp > nq else rank * hq
+    o_k = nq * D // tp
+    nb, base, extra = I // 64, (I // 64) // tp, (I // 64) % tp
+    i0 = 64 * (rank * base + min(rank, extra))
+    i1 = i0 + 64 * (base + (1 if rank < extra else 0))
+    return dict(heads=hq, head0=head0, o_cols=(rank * o_k, (rank + 1) * o_k), o_k_offset=rank * o_k - head0 * D,
+                mlp=(i0, i1), vocab=(rank * cfg.vocab // tp, (rank + 1) * cfg.vocab // tp))
+
+
 def shard_weights(cfg: GemmaConfig, params: dict, tp: int, rank: int) -> dict:
     """Megatron-style shard `rank` of `tp` (tensor parallelism over the GPUs of one node):
     q heads and the gate/up rows are split by output row, the o and down projections by input
     column (their partial results are summed across the GPUs), the LM head by vocabulary row;
     the single KV head, the norms and the embedding table are replicated."""
-    if cfg.n_kv != 1 or cfg.n_q % tp or cfg.intermediate % tp or cfg.vocab % tp:
-        raise ValueError("the group size must divide the query heads, the MLP width and the vocabulary")
+    lay = shard_layout(cfg, tp, rank)
     D, I = cfg.head_dim, cfg.intermediate
-    hq, Il, Vl = cfg.n_q // tp, I // tp, cfg.vocab // tp
-    q_rows = np.arange(rank * hq * D, (rank + 1) * hq * D)
+    q_rows = np.arange(lay["head0"] * D, (lay["head0"] + lay["heads"]) * D)
     kv_rows = np.arange(cfg.n_q * D, (cfg.n_q + 2) * D)
-    gu_rows = np.concatenate([np.arange(rank * Il, (rank + 1) * Il), I + np.arange(rank * Il, (rank + 1) * Il)])
+    i0, i1 = lay["mlp"]
+    gu_rows = np.concatenate([np.arange(i0, i1), I + np.arange(i0, i1)])
+    v0, v1 = lay["vocab"]
     out = {"embed": params["embed"], "final_norm": params["final_norm"], "layers": [],
-           "lm_head": (np.ascontiguousarray(params["embed"][0][rank * Vl:(rank + 1) * Vl]),
-                       np.ascontiguousarray(params["embed"][1][rank * Vl:(rank + 1) * Vl])),
-           "vocab_offset": rank * Vl}
+           "lm_head": (np.ascontiguousarray(params["embed"][0][v0:v1]), np.ascontiguousarray(params["embed"][1][v0:v1])),
+           "vocab_offset": v0, "layout": lay}
     for L in params["layers"]:
         rows = np.concatenate([q_rows, kv_rows])
         S = dict(L)
         S["qkv"] = (np.ascontiguousarray(L["qkv"][0][rows]), np.ascontiguousarray(L["qkv"][1][rows]))
-        S["o"] = (np.ascontiguousarray(L["o"][0][:, rank * hq * D:(rank + 1) * hq * D]), L["o"][1])
+        S["o"] = (np.ascontiguousarray(L["o"][0][:, lay["o_cols"][0]:lay["o_cols"][1]]), L["o"][1])
         S["gate_up"] = (np.ascontiguousarray(L["gate_up"][0][gu_rows]), np.ascontiguousarray(L["gate_up"][1][gu_rows]))
-        S["down"] = (np.ascontiguousarray(L["down"][0][:, rank * Il:(rank + 1) * Il]), L["down"][1])
+        S["down"] = (np.ascontiguousarray(L["down"][0][:, i0:i1]), L["down"][1])
         out["layers"].append(S)
     return out
 
@@ -112,7 +129,8 @@ def build_decode_step(cfg: GemmaConfig, batch: int, params: dict, with_logits: b
     of the step (logits, when asked for, are the shard's [B, vocab / tp] slice)."""
     g = Graph()
     H, D = cfg.hidden, cfg.head_dim
-    n_q = cfg.n_q // tp
+    n_q = params["layout"]["heads"] if tp > 1 else cfg.n_q
+    o_k_offset = params["layout"]["o_k_offset"] if tp > 1 else 0
     tokens = g.input((batch,), "i32")
     pos = g.input((1,), "i32")
     table = g.const(params["embed"][0])
@@ -129,7 +147,7 @@ def build_decode_step(cfg: GemmaConfig, batch: int, params: dict, with_logits: b
                       theta=cfg.theta_global if glob else cfg.theta_local, eps=cfg.eps)
         a = g.attn_decode(q, pos, kc, vc, n_q=n_q, n_kv=cfg.n_kv, head_dim=D, window=0 if glob else cfg.window,
                           scale=D ** -0.5)
-        o = g.gemv_w8(a, *L["o"]) if tp == 1 else g.allreduce(g.gemv_w8(a, *L["o"], out_dtype="f32"), tp, rank)
+        o = g.gemv_w8(a, *L["o"]) if tp == 1 else g.allreduce(g.gemv_w8(a, *L["o"], out_dtype="f32", in_offset=o_k_offset), tp, rank)
         x = g.rmsnorm(o, L["post_attn_norm"], cfg.eps, residual=x)
         h = g.rmsnorm(x, L["pre_ffn_norm"], cfg.eps)
         gu = g.gemv_w8(h, *L["gate_up"])
