@@ -30,6 +30,10 @@ def main():
            # 8 GPUs: every GPU needs at least as many rows of each projection as it has SMs
            "small8": gemma3.GemmaConfig(layers=3, hidden=256, intermediate=64 * 27, vocab=4096, window=24, local_per_global=2,
                                         max_seq=96),
+           # one query head over two GPUs: the shared-head path (o-projection column slices) and an uneven
+           # MLP split (7 blocks of 64) at a group size of 2
+           "shared": gemma3.GemmaConfig(layers=3, hidden=256, n_q=1, intermediate=64 * 7, vocab=4096, window=24,
+                                        local_per_global=2, max_seq=96),
            "full": gemma3.GemmaConfig()}[size_name]
     params = gemma3.random_weights(cfg, 1234, gain)
     dev = Device(local)
@@ -41,7 +45,7 @@ def main():
     vl = cfg.vocab // world
     d_tok, d_pos = dev.alloc(batch * 4), dev.alloc(4)
     d_next, d_logits = dev.alloc(batch * 4), dev.alloc(batch * vl * 4)
-    ref = RefDecoder(cfg, params, batch, device="cpu" if size_name.startswith("small") else None) if rank == 0 else None
+    ref = RefDecoder(cfg, params, batch, device="cpu" if size_name != "full" else None) if rank == 0 else None
     rng = np.random.default_rng(7)
     toks = rng.integers(0, cfg.vocab, (steps, batch)).astype(np.int32)
     worst, agree, total = 0.0, 0, 0

@@ -1351,7 +1351,12 @@ size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int
     off += (bytes + 255) & ~(size_t)255;
     return at;
   };
+  // Regions that other GPUs write come first: their offsets depend only on B, H, the group size and the
+  // SM count, which are the same on every member (a shard's MLP width may differ from its peers').
   offsets->counter_off = take(256);
+  offsets->amax_off = take((size_t)tp * sm_count * 8 * 8);
+  offsets->inbox_o_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
+  offsets->inbox_d_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
   offsets->qkv_off = take((size_t)B * (n_q + 2) * kD * 2);
   offsets->o_off = take((size_t)B * H * 2);
   offsets->act_off = take((size_t)B * I * 2);
@@ -1360,9 +1365,6 @@ size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int
   offsets->attn_out_off = take((size_t)B * n_q * kD * 2);
   offsets->attn_ml_off = take((size_t)B * n_q * sm_count * 8);
   offsets->attn_part_off = take((size_t)B * n_q * sm_count * kD * 4);
-  offsets->amax_off = take((size_t)tp * sm_count * 8 * 8);
-  offsets->inbox_o_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
-  offsets->inbox_d_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
   offsets->trace_len = 16 * n_layers + 8;
   offsets->trace_off = take((size_t)offsets->trace_len * 8);
   return off;

@@ -436,8 +436,8 @@ extern "C" int tb200_executable_connect_peers(tb200_executable_t* ex, const tb20
   for (int r = 0; r < tp; r++) {
     CommHandle h;
     memcpy(&h, &handles[r], sizeof(h));
-    if (h.rank != r || h.tp != tp || h.scratch_offset != ex->plan.scratch_offset)
-      return fail(d, TB200_INVALID_ARGUMENT, "handle %d describes rank %d of %d with another memory plan", r, h.rank, h.tp);
+    if (h.rank != r || h.tp != tp)
+      return fail(d, TB200_INVALID_ARGUMENT, "handle %d describes rank %d of a group of %d", r, h.rank, h.tp);
     if (r == rank) {
       ex->peer_scratch[r] = (char*)ex->arena + ex->plan.scratch_offset;
       continue;
