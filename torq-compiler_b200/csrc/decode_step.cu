@@ -17,9 +17,14 @@
 //     magnitude would not fit). A slot holds 16 weight rows x 1152 bytes of K; the
 //     warps split its K range, a 17th warp adds their partial tiles in a fixed order and
 //     applies the stage's epilogue (bf16 scale, GeGLU, logits + running arg max);
-//   * stages are separated by a grid-wide barrier (one counter in global memory, cooperative
-//     launch, every wait bounded); each CTA keeps the residual stream in shared memory and
-//     recomputes the small norms itself, so only the projections' outputs cross the barrier.
+//   * stages hand their results over in one of two ways. A projection's output (a few KB) travels
+//     as 32-bit words {epoch tag, bf16 value}: the reader spins on the words it needs until they
+//     carry the stage's tag, so the data IS the signal: one L2 round trip, no fence, no counter.
+//     Where a stage's result is large or crosses GPUs (attention partial sums, the K-split
+//     projections of tensor parallelism, the arg max) a grid-wide barrier is used (one counter in
+//     global memory, cooperative launch). Every wait is bounded. Each CTA keeps the residual
+//     stream in shared memory and recomputes the small norms itself, so only the projections'
+//     outputs cross between CTAs.
 // The tensor work is HBM-bound (1.25 instructions per weight byte to build the fragments is
 // the on-chip cost), which is why the operands go through mma.sync registers and not through
 // a shared-memory staging pass for tcgen05.
@@ -125,13 +130,65 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+// Tagged hand-over of a projection's output: element = (tag << 16) | bf16 bits, one 32-bit store.
+// The tag is the low 16 bits of an epoch that grows by one per (launch, layer, projection); a buffer is
+// rewritten every layer, so a stale word always carries an older tag than the one waited for.
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_v4(const uint32_t* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// Spins until the word carries `tag`; returns its bf16 payload as a float. Bounded like every wait.
+__device__ __forceinline__ float wait_tagged(const uint32_t* p, uint32_t tag, int* status, bool& ok) {
+  uint32_t w = ld_relaxed_u32(p);
+  if ((w >> 16) == tag || !ok) return __uint_as_float(w << 16);
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; i++) {
+      w = ld_relaxed_u32(p);
+      if ((w >> 16) == tag) return __uint_as_float(w << 16);
+    }
+    if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
+      atomicCAS(status, 0, (int)kErrGrid);
+      ok = false;
+      return 0.f;
+    }
+  }
+}
+// The same for four consecutive words (16-byte aligned).
+__device__ __forceinline__ uint4 wait_tagged4(const uint32_t* p, uint32_t tag, int* status, bool& ok) {
+  uint4 w = ld_relaxed_v4(p);
+  auto good = [&](const uint4& v) { return (v.x >> 16) == tag && (v.y >> 16) == tag && (v.z >> 16) == tag && (v.w >> 16) == tag; };
+  if (good(w) || !ok) return w;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; i++) {
+      w = ld_relaxed_v4(p);
+      if (good(w)) return w;
+    }
+    if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
+      atomicCAS(status, 0, (int)kErrGrid);
+      ok = false;
+      return make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
 // Grid barriers. Counters only ever grow (64 bits): a launch starts from the bases its
 // predecessor left behind and adds one count per CTA per barrier. Barriers inside one GPU use
 // the local counter. A barrier that spans the tensor-parallel peers uses one of two counters in
 // alternation (so that a GPU that is one barrier ahead never adds to the counter its peers are
 // still waiting on); every CTA of every GPU adds to that counter on every GPU through peer
 // memory, its own GPU's first.
-// Counter block (byte offsets): local 0, global 8 and 16, their bases 24, 32, 40, exit count 48.
+// Counter block (byte offsets): local 0, global 8 and 16, their bases 24, 32, 40, exit count 48, epoch of
+// the tagged hand-overs 56.
 struct BarrierState {
   unsigned long long local, global[2];  // expected values
   int parity;
@@ -356,6 +413,20 @@ __device__ __forceinline__ NormWeights load_norm_weights(const uint16_t* w_post,
   return nw;
 }
 
+// The norm vectors of a layer (six short constants, read once per step, so always an HBM miss) are pulled
+// into L2 a layer ahead: the loads in front of each norm then cost an L2 round trip, not a DRAM one.
+__device__ __forceinline__ void prefetch_layer_constants(const DecodeStepArgs& a, const DecodeLayerDesc* L, int tid) {
+  const int lines = (a.H * 2 + 127) / 128;
+  if (tid < 4 * lines) {
+    const int which = tid / lines, line = tid - which * lines;
+    const unsigned long long off = which == 0 ? L->in_norm : which == 1 ? L->post_attn_norm : which == 2 ? L->pre_ffn_norm : L->post_ffn_norm;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.consts + off + (size_t)line * 128));
+  } else if (tid < 4 * lines + 8) {
+    const int j = tid - 4 * lines;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.consts + (j < 4 ? L->q_norm : L->k_norm) + (size_t)(j & 3) * 128));
+  }
+}
+
 // Residual update and the norm that feeds the next projection:
 //   if src: xs <- bf16(xs + bf16(src * rsqrt(mean(src^2) + eps) * (1 + w_post)))
 //   xin    <- fp16(bf16(xs * rsqrt(mean(xs^2) + eps) * (1 + w_pre)))   (exact: |value| <= sqrt(H) * |1 + w|)
@@ -363,18 +434,18 @@ __device__ __forceinline__ NormWeights load_norm_weights(const uint16_t* w_post,
 // With tensor parallelism the projection's output arrives as one fp32 partial result per GPU
 // (inbox [tp][B][H] at byte offset `inbox` of the scratch area); they are added in rank order
 // and rounded to bf16, the same on every GPU.
-__device__ __forceinline__ float load_projection(const DecodeStepArgs& a, const uint16_t* src, unsigned long long inbox, int b,
-                                                 int i) {
-  if (a.tp <= 1) return bf2f(__ldcg(src + (size_t)b * a.H + i));
+__device__ __forceinline__ float load_projection(const DecodeStepArgs& a, const uint32_t* src, uint32_t tag,
+                                                 unsigned long long inbox, int b, int i, int* status, bool& ok) {
+  if (a.tp <= 1) return wait_tagged(src + (size_t)b * a.H + i, tag, status, ok);
   const float* in = (const float*)(a.scratch + inbox);
   float s = 0.f;
   for (int r = 0; r < a.tp; r++) s += __ldcg(in + ((size_t)r * a.B + b) * a.H + i);
   return rbf(s);
 }
 template <int BT>
-__device__ __forceinline__ void residual_norm(const DecodeStepArgs& a, const uint16_t* src, unsigned long long inbox,
-                                              const NormWeights& nw, uint16_t* xs, char* xin, int xin_stride, float* red,
-                                              int tid) {
+__device__ __forceinline__ void residual_norm(const DecodeStepArgs& a, const uint32_t* src, uint32_t tag,
+                                              unsigned long long inbox, const NormWeights& nw, uint16_t* xs, char* xin,
+                                              int xin_stride, float* red, int tid, int* status, bool& ok) {
   const int H = a.H;
   float ss[BT];
   if (src) {
@@ -385,7 +456,7 @@ __device__ __forceinline__ void residual_norm(const DecodeStepArgs& a, const uin
 #pragma unroll
       for (int e = 0; e < kNormElems; e++) {
         const int i = tid + e * kConsumerThreads;
-        sv[b][e] = (b < a.B && i < H) ? load_projection(a, src, inbox, b, i) : 0.f;
+        sv[b][e] = (b < a.B && i < H) ? load_projection(a, src, tag, inbox, b, i, status, ok) : 0.f;
         ss[b] += sv[b][e] * sv[b][e];
       }
     }
@@ -573,7 +644,7 @@ __device__ __forceinline__ HeadNormWeights load_head_norm_weights(const DecodeSt
 // CTA 0 writes the cache); the keys of the CTA's slice; the 8 token lanes merged per head; the
 // CTA's partial per head published.
 __device__ void attention_slice(const DecodeStepArgs& a, const DecodeLayerDesc* L, const Smem& sm, const HeadNormWeights& nw,
-                                int b, int blk, int tid) {
+                                int b, int blk, int tid, uint32_t tag, int* status, bool& ok) {
   const int warp = tid >> 5, lane = tid & 31;
   const int G = a.grid;
   char* scratch = sm.base + sm.off_xin;
@@ -585,7 +656,7 @@ __device__ void attention_slice(const DecodeStepArgs& a, const DecodeLayerDesc* 
   const int hp = warp & 1, tl = warp >> 1;
   const KeyRange kr = key_range(a, L, blk, tl);
   const int pos = kr.pos;
-  const uint16_t* qkv = (const uint16_t*)(a.scratch + a.qkv_off) + (size_t)b * (a.n_q + 2) * kD;
+  const uint32_t* qkv = (const uint32_t*)(a.scratch + a.qkv_off) + (size_t)b * (a.n_q + 2) * kD;
   uint16_t* kcache = (uint16_t*)(a.arena + L->kcache) + (size_t)b * a.T * kD;
   uint16_t* vcache = (uint16_t*)(a.arena + L->vcache) + (size_t)b * a.T * kD;
   // this warp's first keys and values: issued before anything else so that the cache latency
@@ -604,8 +675,11 @@ __device__ void attention_slice(const DecodeStepArgs& a, const DecodeLayerDesc* 
   if (warp < a.n_q + 2) {
     const int hh = warp;
     // this lane's elements: [4*lane, 4*lane+4) of each half of the head
-    const uint2 lo2 = __ldcg((const uint2*)(qkv + hh * kD + 4 * lane));
-    const uint2 hi2 = __ldcg((const uint2*)(qkv + hh * kD + 128 + 4 * lane));
+    // tagged words written by the qkv projection's reducers: the wait for them is the stage's barrier
+    const uint4 t_lo = wait_tagged4(qkv + hh * kD + 4 * lane, tag, status, ok);
+    const uint4 t_hi = wait_tagged4(qkv + hh * kD + 128 + 4 * lane, tag, status, ok);
+    const uint2 lo2 = make_uint2((t_lo.x & 0xffffu) | (t_lo.y << 16), (t_lo.z & 0xffffu) | (t_lo.w << 16));
+    const uint2 hi2 = make_uint2((t_hi.x & 0xffffu) | (t_hi.y << 16), (t_hi.z & 0xffffu) | (t_hi.w << 16));
     const uint32_t raw[4] = {lo2.x, lo2.y, hi2.x, hi2.y};
     float v[8];
 #pragma unroll
@@ -922,7 +996,7 @@ __device__ __forceinline__ TileScales load_tile_scales(const Phase& p, int t, in
 }
 __device__ __forceinline__ void reduce_phase(const DecodeStepArgs& a, const Phase& p, const Smem& sm, int nslots,
                                              RingPos& tile, int* status, bool& ok, int lane, void* out, unsigned long long inbox,
-                                             ArgBest* best) {
+                                             uint32_t tag, ArgBest* best) {
   const int g = lane >> 2, tig = lane & 3;
   const float* xscale = (const float*)(sm.base + sm.off_red + kRedXscale);
   // the scales of the next tiles are requested ahead: their latency must not sit between two tiles
@@ -963,17 +1037,20 @@ __device__ __forceinline__ void reduce_phase(const DecodeStepArgs& a, const Phas
         }
       }
     } else if (p.kind == kRows) {
-      uint16_t* y = (uint16_t*)out;
+      uint32_t* y = (uint32_t*)out;  // tagged words: the store is the signal
+      const uint32_t th = tag << 16;
       if (r_lo >= 0) {
-        if (b0 < a.B) y[(size_t)b0 * p.N + r_lo] = f2bf(c[0] * s_lo);
-        if (b1 < a.B) y[(size_t)b1 * p.N + r_lo] = f2bf(c[1] * s_lo);
+        if (b0 < a.B) y[(size_t)b0 * p.N + r_lo] = th | f2bf(c[0] * s_lo);
+        if (b1 < a.B) y[(size_t)b1 * p.N + r_lo] = th | f2bf(c[1] * s_lo);
       }
       if (r_hi >= 0) {
-        if (b0 < a.B) y[(size_t)b0 * p.N + r_hi] = f2bf(c[2] * s_hi);
-        if (b1 < a.B) y[(size_t)b1 * p.N + r_hi] = f2bf(c[3] * s_hi);
+        if (b0 < a.B) y[(size_t)b0 * p.N + r_hi] = th | f2bf(c[2] * s_hi);
+        if (b1 < a.B) y[(size_t)b1 * p.N + r_hi] = th | f2bf(c[3] * s_hi);
       }
     } else if (p.kind == kPairs) {
-      // rows g hold gate, rows g+8 the matching up row: act = bf16(bf16(gelu(gate)) * up)
+      // rows g hold gate, rows g+8 the matching up row: act = bf16(bf16(gelu(gate)) * up). This vector is
+      // 6 times longer than the others: plain bf16 and a grid barrier (tagged words would double what every
+      // CTA has to read through its load/store unit).
       uint16_t* y = (uint16_t*)out;
       if (r_lo >= 0) {
         const int col = r_lo;  // index inside the intermediate vector
@@ -1017,6 +1094,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
   const int xin_stride = a.xin_stride;
   const DecodeLayerDesc* layers = (const DecodeLayerDesc*)(a.consts + a.layers_off);
   const unsigned long long* bases = (const unsigned long long*)(a.scratch + a.counter_off + 24);
+  // epoch of the tagged hand-overs: one per (launch, layer, projection); the tag is its low 16 bits
+  const uint32_t epoch_base = *(const uint32_t*)(a.scratch + a.counter_off + 56);
+  auto tag_of = [&](int layer, int which) { return (epoch_base + 4u * (uint32_t)layer + (uint32_t)which + 1u) & 0xffffu; };
   int* status = a.status;
   volatile int* gave_up = (volatile int*)(smem_raw + sm.off_bars + 8 * (2 * nslots + 4));
 
@@ -1108,17 +1188,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
         // o and down are split along K over the tensor-parallel GPUs: partial results to every inbox
         const bool split_k = a.tp > 1 && (which == kO || which == kDown);
         reduce_phase(a, p, sm, nslots, tiles, status, ok, lane, out,
-                     split_k ? (which == kO ? a.inbox_o_off : a.inbox_d_off) : 0ull, &best);
-        if (split_k) __threadfence_system();
-        else __threadfence();
-        __syncwarp();
-        if (lane == 0) grid_arrive(a, split_k, gpar, false);
-        if (split_k) gpar ^= 1;
+                     split_k ? (which == kO ? a.inbox_o_off : a.inbox_d_off) : 0ull, tag_of(l, which), &best);
+        if (split_k) {  // partial results in the peers' inboxes: cross-GPU barrier
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) grid_arrive(a, true, gpar, false);
+          gpar ^= 1;
+        } else if (which == kGateUp) {  // the long activation vector: grid barrier
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) grid_arrive(a, false, 0, false);
+        }  // otherwise the tagged words are the signal
       }
     }
     {
       const Phase p = make_phase(a, layers, kLmHead, row_first, row_count);
-      reduce_phase(a, p, sm, nslots, tiles, status, ok, lane, nullptr, 0ull, &best);
+      reduce_phase(a, p, sm, nslots, tiles, status, ok, lane, nullptr, 0ull, 0u, &best);
       // lanes with the same token pair differ in bits 2..4
 #pragma unroll
       for (int q = 0; q < 2; q++) {
@@ -1192,20 +1277,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       const int8_t* row = (const int8_t*)(a.consts + a.embed_w) + (size_t)tk * a.H;
       for (int i = tid; i < a.H; i += kConsumerThreads) xs[b * a.H + i] = f2bf(rbf((float)row[i] * s) * a.embed_mult);
     }
+    prefetch_layer_constants(a, layers, tid);
     bar_consumers();
     int mark = 0;
     trace_mark(a, blk, tid, mark);
     for (int l = 0; l < a.n_layers; l++) {
       const DecodeLayerDesc* L = layers + l;
       prefetch_keys(a, L, blk, warp, lane);  // well ahead of the attention stage
+      if (l + 1 < a.n_layers) prefetch_layer_constants(a, layers + l + 1, tid);
       // ---- qkv projection (input: norm of the residual stream, updated with the previous layer's MLP output) ----
       {
         const NormWeights nw = load_norm_weights(l > 0 ? (const uint16_t*)(a.consts + layers[l - 1].post_ffn_norm) : nullptr,
                                                  (const uint16_t*)(a.consts + L->in_norm), a.H, tid);
-        if (l > 0) wait_grid(true);  // the down projection's partial results come from every GPU
+        if (l > 0 && a.tp > 1) wait_grid(true);  // the down projection's partial results come from every GPU
         trace_mark(a, blk, tid, mark);
-        residual_norm<BT>(a, l > 0 ? (const uint16_t*)(a.scratch + a.d_off) : nullptr, a.inbox_d_off, nw, xs, xin, xin_stride, red,
-                          tid);
+        residual_norm<BT>(a, l > 0 ? (const uint32_t*)(a.scratch + a.d_off) : nullptr, tag_of(l - 1, kDown), a.inbox_d_off, nw, xs,
+                          xin, xin_stride, red, tid, status, ok);
       }
       trace_mark(a, blk, tid, mark);
       consume_phase(make_phase(a, L, kQkv, row_first, row_count), sm, nslots, a.B, xin_stride, slots, tiles, status, ok, warp, lane);
@@ -1213,10 +1300,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       // ---- attention over the cache: slices, barrier, merge ----
       {
         const HeadNormWeights hw = load_head_norm_weights(a, L, warp, lane);
-        wait_grid(false);
+        bar_consumers();  // every warp is done with the staged activations: their space becomes attention scratch
         trace_mark(a, blk, tid, mark);
         for (int b = 0; b < a.B; b++) {
-          attention_slice(a, L, sm, hw, b, blk, tid);
+          attention_slice(a, L, sm, hw, b, blk, tid, tag_of(l, kQkv), status, ok);
           bar_consumers();
         }
       }
@@ -1239,9 +1326,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       {
         const NormWeights nw = load_norm_weights((const uint16_t*)(a.consts + L->post_attn_norm),
                                                  (const uint16_t*)(a.consts + L->pre_ffn_norm), a.H, tid);
-        wait_grid(true);  // the o projection's partial results come from every GPU
+        if (a.tp > 1) wait_grid(true);  // the o projection's partial results come from every GPU
         trace_mark(a, blk, tid, mark);
-        residual_norm<BT>(a, (const uint16_t*)(a.scratch + a.o_off), a.inbox_o_off, nw, xs, xin, xin_stride, red, tid);
+        residual_norm<BT>(a, (const uint32_t*)(a.scratch + a.o_off), tag_of(l, kO), a.inbox_o_off, nw, xs, xin, xin_stride, red, tid,
+                          status, ok);
       }
       trace_mark(a, blk, tid, mark);
       consume_phase(make_phase(a, L, kGateUp, row_first, row_count), sm, nslots, a.B, xin_stride, slots, tiles, status, ok, warp, lane);
@@ -1257,9 +1345,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
     {
       const NormWeights nw = load_norm_weights((const uint16_t*)(a.consts + layers[a.n_layers - 1].post_ffn_norm),
                                                (const uint16_t*)(a.consts + a.final_norm), a.H, tid);
-      wait_grid(true);
+      if (a.tp > 1) wait_grid(true);
       trace_mark(a, blk, tid, mark);
-      residual_norm<BT>(a, (const uint16_t*)(a.scratch + a.d_off), a.inbox_d_off, nw, xs, xin, xin_stride, red, tid);
+      residual_norm<BT>(a, (const uint32_t*)(a.scratch + a.d_off), tag_of(a.n_layers - 1, kDown), a.inbox_d_off, nw, xs, xin,
+                        xin_stride, red, tid, status, ok);
     }
     trace_mark(a, blk, tid, mark);
     consume_phase(make_phase(a, layers, kLmHead, row_first, row_count), sm, nslots, a.B, xin_stride, slots, tiles, status, ok, warp, lane);
@@ -1306,6 +1395,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       next[0] = bs.local;
       next[1] = bs.global[0];
       next[2] = bs.global[1];
+      *(uint32_t*)(a.scratch + a.counter_off + 56) = epoch_base + 4u * (uint32_t)a.n_layers;
       *exit_count = 0;
       __threadfence();
     }
@@ -1357,10 +1447,11 @@ size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int
   offsets->amax_off = take((size_t)tp * sm_count * 8 * 8);
   offsets->inbox_o_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
   offsets->inbox_d_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
-  offsets->qkv_off = take((size_t)B * (n_q + 2) * kD * 2);
-  offsets->o_off = take((size_t)B * H * 2);
-  offsets->act_off = take((size_t)B * I * 2);
-  offsets->d_off = take((size_t)B * H * 2);
+  // projection outputs as tagged 32-bit words
+  offsets->qkv_off = take((size_t)B * (n_q + 2) * kD * 4);
+  offsets->o_off = take((size_t)B * H * 4);
+  offsets->act_off = take((size_t)B * I * 2);  // plain bf16
+  offsets->d_off = take((size_t)B * H * 4);
   offsets->attn_slices = sm_count;
   offsets->attn_out_off = take((size_t)B * n_q * kD * 2);
   offsets->attn_ml_off = take((size_t)B * n_q * sm_count * 8);
