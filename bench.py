@@ -111,7 +111,7 @@ def _decoder_params(cfg, tp, rank):
 
 
 def yolo_bench(dev, stream, batch: int = 64, steps: int = 5):
-    """YOLOv8n-style int8 detector at 640x640 (BASELINE's detector configuration): images/s, inputs resident."""
+    """YOLOv8n-style int8 detector at 640x640 (the detector configuration of the benchmark set): images/s, inputs resident."""
     import torch
     from torq_b200.runtime import Executable
     from torq_b200.workloads.yolov8n import build_yolov8n, synthetic_images

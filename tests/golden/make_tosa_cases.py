@@ -1,6 +1,6 @@
 """Generates tests/golden/tosa_*.b200ops / tosa_*.npz from the reference's own TOSA fixtures.
 
-Run here (where the reference tree is mounted):  python tests/golden/make_tosa_cases.py /root/reference
+Run where the reference tree is available:  python tests/golden/make_tosa_cases.py <path of the reference tree>
 
 For each chosen fixture the TOSA text is read by torq_b200.tosa_frontend (so the constants -
 weights, multipliers, shifts, zero points, pad values - are the reference's own), serialized
@@ -86,4 +86,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_tosa_cases.py <path of the reference tree>")
+    main(sys.argv[1])

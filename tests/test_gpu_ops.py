@@ -61,7 +61,7 @@ def test_conv2d(device, case, mode):
 
 IGEMM_CASES = [
     # x shape, OC, kernel, stride, pad(t,b,l,r), izp   (IC % 16 == 0, OC % 16 == 0: tensor-core implicit GEMM)
-    ((1, 56, 56, 64), 64, (3, 3), 1, (1, 1, 1, 1), -3),      # BASELINE's single-conv configuration
+    ((1, 56, 56, 64), 64, (3, 3), 1, (1, 1, 1, 1), -3),      # the benchmark set's single-conv configuration
     ((2, 20, 20, 128), 128, (3, 3), 1, (1, 1, 1, 1), 7),     # ragged patches (20 is no multiple of the patch)
     ((1, 13, 17, 32), 48, (3, 3), 1, (1, 1, 1, 1), -9),      # odd frame, 32-byte rows
     ((2, 40, 40, 64), 128, (3, 3), 2, (0, 1, 0, 1), 4),      # stride 2, TensorFlow SAME padding

@@ -14,6 +14,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.h"
@@ -519,7 +520,11 @@ void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, u
 }
 
 // Batches above 8 with K a multiple of 64 take the tensor-core kernel: K slices of a multiple of 64.
-static bool gemv_use_mma(int B, int K) { return B > 8 && (K % 64) == 0; }
+static bool gemv_use_mma(int B, int K) {
+  static int min_b = -1;
+  if (min_b < 0) { const char* e = getenv("TB200_GEMV_MMA_MIN_B"); min_b = e ? atoi(e) : 9; }
+  return B >= min_b && (K % 64) == 0;
+}
 static int gemv_mma_slice(int N, int K, int splits) {
   int slice = ((K + splits - 1) / splits + 63) / 64 * 64;
   (void)N;
@@ -569,7 +574,8 @@ void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, v
       }
       kernel<<<grid, 256, smem, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
     };
-    if (nt == 2) run(gemv_w8_mma_kernel<2>);
+    if (nt == 1) run(gemv_w8_mma_kernel<1>);
+    else if (nt == 2) run(gemv_w8_mma_kernel<2>);
     else if (nt == 3) run(gemv_w8_mma_kernel<3>);
     else run(gemv_w8_mma_kernel<4>);
     if (used > 1) {
