@@ -117,7 +117,11 @@ uint32_t tb200_executable_launch_count(tb200_executable_t* executable);
  * TorqExecutable.cc:512-531). Asynchronous: work is queued on the device stream. */
 int tb200_dispatch(tb200_executable_t* executable, const tb200_binding_t* bindings, size_t n_bindings);
 /* Host wait with a deadline (TorqHw::wait, runtime/torq_hw/src/TorqHw.cpp:155-213):
- * DEADLINE_EXCEEDED when the stream has not drained in time. */
+ * DEADLINE_EXCEEDED when the stream has not drained in time. ABORTED when a kernel gave up one of
+ * its bounded internal waits (the message names which): the device stays usable, the results of
+ * the dispatches since the last successful wait are undefined, and an executable that runs as one
+ * persistent kernel (a decode step) must be destroyed and created again, since its barrier
+ * counters no longer match. */
 int tb200_wait(tb200_device_t* device, uint64_t timeout_ns);
 
 /* The reference's synchronous host-pointer dispatch (the command buffer maps every

@@ -137,8 +137,8 @@ __global__ void __launch_bounds__(256) gemv_w8_kernel(const uint16_t* __restrict
 }
 
 // ---------------------------------------------------------------------------------------
-// The same product for batches above 8 on the tensor cores (mma.sync m16n8k16, bf16 operands,
-// fp32 accumulation): with 9..32 tokens the CUDA-core kernel above spends 32 FMAs per weight
+// The same product for larger batches on the tensor cores (mma.sync m16n8k16, bf16 operands,
+// fp32 accumulation): with many tokens the CUDA-core kernel above spends one FMA per token and weight
 // byte and is FMA-bound at a few percent of the HBM rate. Block = 128 weight rows (8 warps x 16
 // rows) x one K slice; the slice of x for all tokens is staged in shared memory once per block
 // (bf16, token rows 16 bytes apart modulo 128 so that the fragment loads do not conflict);
@@ -519,10 +519,11 @@ void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, u
   rmsnorm_kernel<<<rows, 256, 0, stream>>>(x, res, w, out, H, eps);
 }
 
-// Batches above 8 with K a multiple of 64 take the tensor-core kernel: K slices of a multiple of 64.
+// Batches of 5 and more with K a multiple of 64 take the tensor-core kernel (measured crossover with the
+// CUDA-core kernel and with the fused step; TB200_GEMV_MMA_MIN_B moves it): K slices of a multiple of 64.
 static bool gemv_use_mma(int B, int K) {
   static int min_b = -1;
-  if (min_b < 0) { const char* e = getenv("TB200_GEMV_MMA_MIN_B"); min_b = e ? atoi(e) : 9; }
+  if (min_b < 0) { const char* e = getenv("TB200_GEMV_MMA_MIN_B"); min_b = e ? atoi(e) : 5; }
   return B >= min_b && (K % 64) == 0;
 }
 static int gemv_mma_slice(int N, int K, int splits) {
