@@ -11,6 +11,8 @@ a trained model's are. Both cases are tested with their tolerance stated:
   * peaked logits (embedding gain 0.3): LOGIT_REL_TOL = 1e-2, ids identical;
   * flat logits   (embedding gain 0.02): FLAT_LOGIT_REL_TOL = 3e-2, ids identical unless the
     reference's top two are within 1e-3 relative."""
+import os
+
 import numpy as np
 import pytest
 
@@ -92,3 +94,48 @@ def test_full_size_decoder_matches_reference(device):
     worst, exact, near_tie, wrong, _ = _run(device, cfg, 1, prompt_len=8, gen_len=8, embed_gain=6.0)  # 52 branch additions: a larger gain keeps the logits peaked
     assert worst <= LOGIT_REL_TOL, worst
     assert wrong == 0 and near_tie == 0, (exact, near_tie, wrong)
+
+
+MID = gemma3.GemmaConfig(layers=2, hidden=1024, intermediate=2048, vocab=4096, window=16, local_per_global=1, max_seq=64)
+
+
+@pytest.mark.parametrize("cfg,batch", [(gemma3.SMALL, 8), (gemma3.SMALL, 32), (MID, 3), (MID, 16)])
+def test_op_by_op_launch_fusions_change_no_bit(device, cfg, batch):
+    """Run op by op, the planner lets the reader of a split-K product finalize the partial sums and runs
+    two norms in a row as one launch. The arithmetic and its order are the same: logits and ids must be
+    bit-identical with the fusions switched off (TB200_NO_DECODER_FUSION=1 when the plan is built)."""
+    params = gemma3.random_weights(cfg, 77, 0.3)
+    blob = gemma3.build_decode_step(cfg, batch, params, with_logits=True).serialize()
+    os.environ["TB200_DECODE_PER_OP"] = "1"
+    try:
+        fused = Executable(device, blob)
+        os.environ["TB200_NO_DECODER_FUSION"] = "1"
+        plain = Executable(device, blob)
+    finally:
+        os.environ.pop("TB200_NO_DECODER_FUSION", None)
+        os.environ.pop("TB200_DECODE_PER_OP", None)
+    names_f, names_p = fused.op_kernels(), plain.op_kernels()
+    assert any(n.startswith("rmsnorm_pair") for n in names_f) and "rope_kv_from_partials" in names_f
+    assert "geglu_from_partials" in names_f and fused.launch_count < plain.launch_count
+    assert not any("partials" in n or "pair" in n for n in names_p)
+    rng = np.random.default_rng(5)
+    d_tok, d_pos = device.alloc(batch * 4), device.alloc(4)
+    outs = [(device.alloc(batch * 4), device.alloc(batch * cfg.vocab * 4)) for _ in range(2)]
+    tok = rng.integers(0, cfg.vocab, batch).astype(np.int32)
+    for pos in range(30):
+        d_tok.upload(tok)
+        d_pos.upload(np.array([pos], np.int32))
+        got = []
+        for ex, (d_next, d_logits) in zip((fused, plain), outs):
+            ex.dispatch([d_tok, d_pos], [d_next, d_logits])
+            got.append((d_next.download((batch,), np.int32), d_logits.download((batch, cfg.vocab), np.float32)))
+        assert np.array_equal(got[0][0], got[1][0]), pos
+        assert np.array_equal(got[0][1].view(np.uint32), got[1][1].view(np.uint32)), pos
+        tok = got[0][0].copy()
+    for a, c in outs:
+        a.free()
+        c.free()
+    d_tok.free()
+    d_pos.free()
+    fused.destroy()
+    plain.destroy()

@@ -41,6 +41,14 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   float t = lane < nw ? red[lane] : 0.f;
   return warp_sum(t);
 }
+// One launch helper for every kernel of this file. (Launching them as programmatic dependents of one
+// another - blocks resident early, griddepcontrol.wait before the first memory access - was measured on
+// B200 inside the captured graph of a decode step: 4-6 % slower at batches 8 and 32, so it is not used.)
+template <typename... KArgs, typename... Args>
+void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  kernel<<<grid, block, smem, stream>>>(KArgs(args)...);
+}
+
 // int8 -> float without the conversion pipe: place the biased byte in the mantissa of 2^23
 __device__ __forceinline__ float s8_to_float(uint32_t word, int j) {
   const uint32_t b = ((word >> (8 * j)) & 0xffu) ^ 0x80u;
@@ -61,7 +69,7 @@ __global__ void __launch_bounds__(128) embed_kernel(const int32_t* __restrict__ 
 }
 
 // y = [res +] bf16( x * rsqrt(mean(x^2) + eps) * (1 + w) )   (sum of res and the rounded norm is rounded again)
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res,
+__global__ void __launch_bounds__(512) rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res,
                                                       const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
                                                       int H, float eps) {
   __shared__ float red[32];
@@ -77,6 +85,52 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict
     const float n = bf2f(f2bf(bf2f(x[base + i]) * inv * (1.0f + bf2f(w[i]))));
     out[base + i] = res ? f2bf(bf2f(res[base + i]) + n) : f2bf(n);
   }
+}
+
+// One element of a bf16 [B, N] operand: the tensor itself, or the finalized sum of split-K partials.
+__device__ __forceinline__ float operand_at(const uint16_t* __restrict__ x, const GemvPartials& gp, size_t bn, size_t idx,
+                                            int n) {
+  if (gp.splits == 0) return bf2f(x[idx]);
+  float s = 0.f;
+#pragma unroll 4
+  for (int sp = 0; sp < gp.splits; sp++) s += __ldg(gp.partial + (size_t)sp * bn + idx);
+  return bf2f(f2bf(s * bf2f(__ldg(gp.scale + n))));
+}
+
+// rmsnorm_kernel, its input optionally split-K partials, and optionally a second norm (no residual) of the
+// result in the same launch: out2 = bf16( out * rsqrt(mean(out^2) + eps2) * (1 + w2) ). One block per row,
+// the row kept in shared memory as fp32.
+__global__ void __launch_bounds__(512) rmsnorm_fused_kernel(const uint16_t* __restrict__ x, GemvPartials gp,
+                                                            const uint16_t* __restrict__ res,
+                                                            const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
+                                                            const uint16_t* __restrict__ w2, uint16_t* __restrict__ out2,
+                                                            int rows, int H, float eps, float eps2) {
+  extern __shared__ float row_s[];
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  const size_t bn = (size_t)rows * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = operand_at(x, gp, bn, base + i, i);
+    row_s[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float n = bf2f(f2bf(row_s[i] * inv * (1.0f + bf2f(w[i]))));
+    const uint16_t o = res ? f2bf(bf2f(res[base + i]) + n) : f2bf(n);
+    out[base + i] = o;
+    const float ov = bf2f(o);
+    row_s[i] = ov;
+    ss2 += ov * ov;
+  }
+  if (!w2) return;
+  __syncthreads();  // red is reused
+  ss2 = block_sum(ss2, red);
+  const float inv2 = rsqrtf(ss2 / (float)H + eps2);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out2[base + i] = f2bf(row_s[i] * inv2 * (1.0f + bf2f(w2[i])));
 }
 
 // Split-K GEMV / skinny GEMM with int8 weights: one warp per output row n and K slice.
@@ -252,30 +306,32 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const uint16_t* __restrict
                                                       const uint16_t* __restrict__ qw, const uint16_t* __restrict__ kw,
                                                       uint16_t* __restrict__ q_out, uint16_t* __restrict__ kcache,
                                                       uint16_t* __restrict__ vcache, int n_q, int n_kv, int D, int T,
-                                                      float theta, float eps) {
+                                                      float theta, float eps, GemvPartials gp) {
   __shared__ float red[32];
   __shared__ float hv[512];
   const int b = blockIdx.x, h = blockIdx.y;  // h: q heads, then k heads, then v heads
   int pos = pos_p[0];
   pos = pos < 0 ? 0 : (pos >= T ? T - 1 : pos);
   const int width = (n_q + 2 * n_kv) * D;
-  const uint16_t* src = qkv + (size_t)b * width + (size_t)h * D;
+  const size_t src = (size_t)b * width + (size_t)h * D;  // element offset of this head in qkv
+  const size_t bn = (size_t)gridDim.x * width;
   const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
   if (!is_q && !is_k) {  // v head: plain copy into the cache
     const int hk = h - n_q - n_kv;
     uint16_t* dst = vcache + (((size_t)b * T + pos) * n_kv + hk) * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = f2bf(operand_at(qkv, gp, bn, src + i, h * D + i));
     return;
   }
   const uint16_t* w = is_q ? qw : kw;
   float ss = 0.f;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    const float v = bf2f(src[i]);
+    const float v = operand_at(qkv, gp, bn, src + i, h * D + i);
+    hv[i] = v;
     ss += v * v;
   }
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)D + eps);
-  for (int i = threadIdx.x; i < D; i += blockDim.x) hv[i] = bf2f(f2bf(bf2f(src[i]) * inv * (1.0f + bf2f(w[i]))));
+  for (int i = threadIdx.x; i < D; i += blockDim.x) hv[i] = bf2f(f2bf(hv[i] * inv * (1.0f + bf2f(w[i]))));
   __syncthreads();
   uint16_t* dst = is_q ? q_out + ((size_t)b * n_q + h) * D
                        : kcache + (((size_t)b * T + pos) * n_kv + (h - n_q)) * D;
@@ -376,12 +432,13 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 }
 // out[b, i] = bf16( bf16(gelu_tanh(gate)) * up ), gate = gu[b, i], up = gu[b, I + i]
 __global__ void __launch_bounds__(256) geglu_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out, int B,
-                                                    int I) {
+                                                    int I, GemvPartials gp) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)B * I) return;
   const int i = (int)(idx % I);
   const size_t b = idx / I;
-  const float g = bf2f(gu[b * 2 * I + i]), u = bf2f(gu[b * 2 * I + I + i]);
+  const size_t bn = (size_t)B * 2 * I;
+  const float g = operand_at(gu, gp, bn, b * 2 * I + i, i), u = operand_at(gu, gp, bn, b * 2 * I + I + i, I + i);
   out[idx] = f2bf(bf2f(f2bf(gelu_tanh(g))) * u);
 }
 
@@ -511,12 +568,12 @@ __global__ void argmax_final_kernel(const float* __restrict__ pv, const int32_t*
 
 void launch_embed(const int32_t* tok, const int8_t* table, const uint16_t* scale, uint16_t* out, int B, int H, int V,
                   float mult, cudaStream_t stream) {
-  embed_kernel<<<B, 128, 0, stream>>>(tok, table, scale, out, H, V, mult);
+  launch_k(embed_kernel, dim3(B), dim3(128), 0, stream, tok, table, scale, out, H, V, mult);
 }
 
 void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, uint16_t* out, int rows, int H, float eps,
                     cudaStream_t stream) {
-  rmsnorm_kernel<<<rows, 256, 0, stream>>>(x, res, w, out, H, eps);
+  launch_k(rmsnorm_kernel, dim3(rows), dim3(512), 0, stream, x, res, w, out, H, eps);
 }
 
 // Batches of 5 and more with K a multiple of 64 take the tensor-core kernel (measured crossover with the
@@ -558,8 +615,19 @@ int gemv_w8_splits(int B, int N, int K) {
 
 size_t gemv_w8_scratch_bytes(int B, int N, int splits) { return splits > 1 ? (size_t)splits * B * N * sizeof(float) : 0; }
 
+int gemv_w8_used_splits(int B, int N, int K, int splits) {
+  const int slice = gemv_use_mma(B, K) ? gemv_mma_slice(N, K, splits) : ((K + splits - 1) / splits + 511) / 512 * 512;
+  return (K + slice - 1) / slice;
+}
+
+void launch_rmsnorm_fused(const uint16_t* x, GemvPartials gp, const uint16_t* res, const uint16_t* w, uint16_t* out,
+                          const uint16_t* w2, uint16_t* out2, int rows, int H, float eps, float eps2,
+                          cudaStream_t stream) {
+  launch_k(rmsnorm_fused_kernel, dim3(rows), dim3(512), (size_t)H * sizeof(float), stream, x, gp, res, w, out, w2, out2, rows, H, eps, eps2);
+}
+
 void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, void* y, int y_f32, float* scratch, int B,
-                    int N, int K, int splits, cudaStream_t stream) {
+                    int N, int K, int splits, cudaStream_t stream, bool finalize) {
   if (gemv_use_mma(B, K)) {
     const int slice = gemv_mma_slice(N, K, splits);
     const int used = (K + slice - 1) / slice;
@@ -573,37 +641,37 @@ void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, v
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         attr_done[nt] = true;
       }
-      kernel<<<grid, 256, smem, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
+      launch_k(kernel, dim3(grid), dim3(256), smem, stream, x, W, scale, y, scratch, B, N, K, slice, y_f32);
     };
     if (nt == 1) run(gemv_w8_mma_kernel<1>);
     else if (nt == 2) run(gemv_w8_mma_kernel<2>);
     else if (nt == 3) run(gemv_w8_mma_kernel<3>);
     else run(gemv_w8_mma_kernel<4>);
-    if (used > 1) {
+    if (used > 1 && finalize) {
       const size_t total = (size_t)B * N;
-      gemv_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, scale, y, B, N, used, y_f32);
+      launch_k(gemv_finalize_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, scratch, scale, y, B, N, used, y_f32);
     }
     return;
   }
   const int slice = ((K + splits - 1) / splits + 511) / 512 * 512;
   const int used = (K + slice - 1) / slice;  // slices that really hold data
   dim3 grid((N + 7) / 8, used);
-  if (B <= 1) gemv_w8_kernel<1><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
-  else if (B <= 4) gemv_w8_kernel<4><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
-  else if (B <= 8) gemv_w8_kernel<8><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
-  else if (B <= 16) gemv_w8_kernel<16><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
-  else gemv_w8_kernel<32><<<grid, 256, 0, stream>>>(x, W, scale, y, scratch, B, N, K, slice, y_f32);
-  if (used > 1) {
+  if (B <= 1) launch_k(gemv_w8_kernel<1>, dim3(grid), dim3(256), 0, stream, x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  else if (B <= 4) launch_k(gemv_w8_kernel<4>, dim3(grid), dim3(256), 0, stream, x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  else if (B <= 8) launch_k(gemv_w8_kernel<8>, dim3(grid), dim3(256), 0, stream, x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  else if (B <= 16) launch_k(gemv_w8_kernel<16>, dim3(grid), dim3(256), 0, stream, x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  else launch_k(gemv_w8_kernel<32>, dim3(grid), dim3(256), 0, stream, x, W, scale, y, scratch, B, N, K, slice, y_f32);
+  if (used > 1 && finalize) {
     const size_t total = (size_t)B * N;
-    gemv_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, scale, y, B, N, used, y_f32);
+    launch_k(gemv_finalize_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, scratch, scale, y, B, N, used, y_f32);
   }
 }
 
 void launch_rope_kv(const uint16_t* qkv, const int32_t* pos, const uint16_t* qw, const uint16_t* kw, uint16_t* q_out,
                     uint16_t* kcache, uint16_t* vcache, int B, int n_q, int n_kv, int D, int T, float theta, float eps,
-                    cudaStream_t stream) {
-  rope_kv_kernel<<<dim3(B, n_q + 2 * n_kv), 128, 0, stream>>>(qkv, pos, qw, kw, q_out, kcache, vcache, n_q, n_kv, D, T,
-                                                              theta, eps);
+                    cudaStream_t stream, GemvPartials gp) {
+  launch_k(rope_kv_kernel, dim3(dim3(B, n_q + 2 * n_kv)), dim3(128), 0, stream, qkv, pos, qw, kw, q_out, kcache, vcache, n_q, n_kv, D, T,
+                                                              theta, eps, gp);
 }
 
 int attn_decode_splits(int B) { return B >= 16 ? 16 : 32; }
@@ -613,35 +681,35 @@ size_t attn_decode_scratch_bytes(int B, int n_q, int splits) {
 void launch_attn_decode(const uint16_t* q, const int32_t* pos, const uint16_t* kcache, const uint16_t* vcache,
                         uint16_t* out, float* scratch, int B, int n_q, int T, int window, float scale, int splits,
                         cudaStream_t stream) {
-  attn_partial_kernel<<<dim3(B, splits), 128, 0, stream>>>(q, pos, kcache, vcache, scratch, n_q, T, window, scale);
-  attn_combine_kernel<<<B * n_q, kAttnD, 0, stream>>>(scratch, out, splits);
+  launch_k(attn_partial_kernel, dim3(dim3(B, splits)), dim3(128), 0, stream, q, pos, kcache, vcache, scratch, n_q, T, window, scale);
+  launch_k(attn_combine_kernel, dim3(B * n_q), dim3(kAttnD), 0, stream, scratch, out, splits);
 }
 
-void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t stream) {
+void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t stream, GemvPartials gp) {
   const size_t total = (size_t)B * I;
-  geglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(gu, out, B, I);
+  launch_k(geglu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, gu, out, B, I, gp);
 }
 
 void launch_gemv_q8b(const uint16_t* x, const int8_t* W, const uint16_t* scale, const int8_t* zp, uint16_t* y, int B, int N,
                      int K, int bs, cudaStream_t stream) {
   const dim3 grid((N + 7) / 8);
-  if (B <= 1) gemv_q8b_kernel<1><<<grid, 256, 0, stream>>>(x, W, scale, zp, y, B, N, K, bs);
-  else if (B <= 4) gemv_q8b_kernel<4><<<grid, 256, 0, stream>>>(x, W, scale, zp, y, B, N, K, bs);
-  else gemv_q8b_kernel<8><<<grid, 256, 0, stream>>>(x, W, scale, zp, y, B, N, K, bs);
+  if (B <= 1) launch_k(gemv_q8b_kernel<1>, dim3(grid), dim3(256), 0, stream, x, W, scale, zp, y, B, N, K, bs);
+  else if (B <= 4) launch_k(gemv_q8b_kernel<4>, dim3(grid), dim3(256), 0, stream, x, W, scale, zp, y, B, N, K, bs);
+  else launch_k(gemv_q8b_kernel<8>, dim3(grid), dim3(256), 0, stream, x, W, scale, zp, y, B, N, K, bs);
 }
 
 void launch_act_bf16(const uint16_t* x, uint16_t* out, long long n, int fn, cudaStream_t stream) {
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  act_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, out, n, fn);
+  launch_k(act_bf16_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, out, n, fn);
 }
 
 size_t argmax_scratch_bytes(int B) { return (size_t)B * kArgmaxChunks * 8; }
 void launch_argmax(const void* logits, int is_f32, int32_t* out, void* scratch, int B, int V, cudaStream_t stream) {
   float* pv = (float*)scratch;
   int32_t* pi = (int32_t*)((char*)scratch + (size_t)B * kArgmaxChunks * 4);
-  argmax_partial_kernel<<<dim3(B, kArgmaxChunks), 256, 0, stream>>>(logits, is_f32, pv, pi, V);
-  argmax_final_kernel<<<B, 32, 0, stream>>>(pv, pi, out);
+  launch_k(argmax_partial_kernel, dim3(dim3(B, kArgmaxChunks)), dim3(256), 0, stream, logits, is_f32, pv, pi, V);
+  launch_k(argmax_final_kernel, dim3(B), dim3(32), 0, stream, pv, pi, out);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -148,17 +148,34 @@ void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, u
                     cudaStream_t stream);
 int gemv_w8_splits(int B, int N, int K);
 size_t gemv_w8_scratch_bytes(int B, int N, int splits);
+// y bf16, or fp32 when y_f32. finalize == false with more than one K slice in use leaves the per-slice
+// sums in scratch ([slice][B][N] fp32) for a consumer kernel that takes a GemvPartials.
 void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, void* y, int y_f32, float* scratch, int B,
-                    int N, int K, int splits, cudaStream_t stream);  // y bf16, or fp32 when y_f32
+                    int N, int K, int splits, cudaStream_t stream, bool finalize = true);
+int gemv_w8_used_splits(int B, int N, int K, int splits);  // K slices that launch_gemv_w8 really launches
+// A bf16 [B, N] operand that is still the per-slice partial sums of a split-K product: the consumer adds
+// the slices in order, applies the row scale and rounds to bf16, exactly as the finalize kernel would.
+// splits == 0: the operand is an ordinary bf16 tensor.
+struct GemvPartials {
+  const float* partial;
+  const uint16_t* scale;
+  int splits;
+};
+// First norm as launch_rmsnorm (x may be partial sums); with w2 a second norm without residual of the
+// first result goes to out2 in the same launch. H * 4 bytes of shared memory: H <= 8192.
+void launch_rmsnorm_fused(const uint16_t* x, GemvPartials gp, const uint16_t* res, const uint16_t* w, uint16_t* out,
+                          const uint16_t* w2, uint16_t* out2, int rows, int H, float eps, float eps2,
+                          cudaStream_t stream);
 void launch_rope_kv(const uint16_t* qkv, const int32_t* pos, const uint16_t* qw, const uint16_t* kw, uint16_t* q_out,
                     uint16_t* kcache, uint16_t* vcache, int B, int n_q, int n_kv, int D, int T, float theta, float eps,
-                    cudaStream_t stream);
+                    cudaStream_t stream, GemvPartials gp = GemvPartials{nullptr, nullptr, 0});
 int attn_decode_splits(int B);
 size_t attn_decode_scratch_bytes(int B, int n_q, int splits);
 void launch_attn_decode(const uint16_t* q, const int32_t* pos, const uint16_t* kcache, const uint16_t* vcache,
                         uint16_t* out, float* scratch, int B, int n_q, int T, int window, float scale, int splits,
                         cudaStream_t stream);
-void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t stream);
+void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t stream,
+                  GemvPartials gp = GemvPartials{nullptr, nullptr, 0});
 // block-quantised GEMV: W [N, K] int8, scale bf16 and zp int8 (or null) [N, K / bs], bs a multiple of 16, batch <= 8
 void launch_gemv_q8b(const uint16_t* x, const int8_t* W, const uint16_t* scale, const int8_t* zp, uint16_t* y, int B, int N,
                      int K, int bs, cudaStream_t stream);

@@ -432,6 +432,13 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
   // pair: OptimizeSwishActivationPattern.cpp:100-190) is applied in the convolution's epilogue.
   std::vector<int> table_after(ops.size(), -1);  // conv op -> index of its fused table op
   std::vector<char> fused_away(ops.size(), 0);
+  // Decoder graphs run op by op: (1) a split-K gemv_w8 whose only reader is the next op (rmsnorm, rope_kv or
+  // geglu) leaves its per-slice sums in scratch and the reader finalizes them as it loads; (2) an rmsnorm
+  // directly followed by an rmsnorm of its result runs as one launch. Same arithmetic, fewer launches.
+  std::vector<int> partials_from(ops.size(), -1);  // reader op -> the gemv_w8 op whose partial sums it takes
+  std::vector<char> defer_finalize(ops.size(), 0);
+  std::vector<int> norm_second(ops.size(), -1);    // rmsnorm op -> the rmsnorm op fused into it
+  std::vector<int> extra_out(ops.size(), -1);      // tensor an op writes on behalf of the op fused into it
   {
     std::vector<int> uses(nt, 0), producer(nt, -1);
     for (int i = 0; i < (int)ops.size(); i++) {
@@ -460,12 +467,43 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         continue;
       table_after[pc] = i;
       fused_away[i] = 1;
+      extra_out[pc] = op.out0;
+    }
+    const char* no_dec = getenv("TB200_NO_DECODER_FUSION");
+    for (int i = 0; i + 1 < (int)ops.size() && !(no_dec && *no_dec && *no_dec != '0'); i++) {
+      const auto& op = ops[i];
+      const auto& nx = ops[i + 1];
+      auto ok2d = [&](int id, int dtype) {
+        return id >= 0 && id < nt && tensors[id].rank == 2 && tensors[id].dtype == dtype;
+      };
+      if (op.kind == TB200_OP_GEMV_W8 && ok2d(op.in0, TB200_BF16) && ok2d(op.out0, TB200_BF16) && ok2d(op.weights, TB200_I8) &&
+          tensors[op.out0].kind == TB200_TENSOR_ACTIVATION && uses[op.out0] == 1 && nx.in0 == op.out0 && op.i1 == 0 &&
+          (nx.kind == TB200_OP_RMSNORM || nx.kind == TB200_OP_ROPE_KV || nx.kind == TB200_OP_GEGLU)) {
+        const int B = tensors[op.in0].shape[0], N = tensors[op.weights].shape[0], K = tensors[op.weights].shape[1];
+        const bool plain = K == tensors[op.in0].shape[1] && K > 0 && K % 16 == 0 && B >= 1 && B <= 32 && N >= 1;
+        if (plain && !(nx.kind == TB200_OP_RMSNORM && N > 8192)) {
+          const int splits = op.i0 > 0 ? op.i0 : gemv_w8_splits(B, N, K);
+          if (gemv_w8_used_splits(B, N, K, splits) > 1) {
+            defer_finalize[i] = 1;
+            partials_from[i + 1] = i;
+          }
+        }
+      }
+      if (op.kind == TB200_OP_RMSNORM && nx.kind == TB200_OP_RMSNORM && !fused_away[i] && nx.in0 == op.out0 && nx.in1 < 0 &&
+          ok2d(op.in0, TB200_BF16) && ok2d(op.out0, TB200_BF16) && ok2d(nx.out0, TB200_BF16) && nx.out0 != op.out0 &&
+          tensors[op.in0].shape[1] <= 8192 && tensors[nx.out0].shape[0] == tensors[op.out0].shape[0] &&
+          tensors[nx.out0].shape[1] == tensors[op.out0].shape[1] && tensors[op.out0].shape[1] == tensors[op.in0].shape[1] &&
+          tensors[op.out0].shape[0] == tensors[op.in0].shape[0]) {
+        norm_second[i] = i + 1;
+        fused_away[i + 1] = 1;
+        extra_out[i] = nx.out0;
+      }
     }
   }
   for (int i = 0; i < (int)ops.size(); i++) {
     const auto& op = ops[i];
     int ins[3] = {op.in0, op.in1, op.in2};
-    int outs[3] = {op.out0, op.out1, table_after[i] >= 0 ? ops[table_after[i]].out0 : -1};
+    int outs[3] = {op.out0, op.out1, extra_out[i]};
     for (int id : ins)
       if (id >= 0) {
         if (!b.valid_id(id)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input tensor id %d out of range", i, id);
@@ -517,7 +555,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
     size_t high = cursor;
     const size_t base = cursor;
     for (int i = 0; i < (int)ops.size(); i++) {
-      int outs[3] = {ops[i].out0, ops[i].out1, table_after[i] >= 0 ? ops[table_after[i]].out0 : -1};
+      int outs[3] = {ops[i].out0, ops[i].out1, extra_out[i]};
       for (int out_id : outs) {
         // a result written in place into a later tensor (concat chains) allocates that tensor now
         const int id = out_id >= 0 && ops[i].kind == TB200_OP_CONCAT ? root[out_id] : out_id;
@@ -550,6 +588,13 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
   }
 
   size_t scratch_need = 0;
+  struct DeferredGemv { size_t scale_off; int splits; };
+  std::vector<DeferredGemv> deferred(ops.size(), DeferredGemv{0, 0});
+  // the operand a reader of deferred partial sums passes to its kernel
+  auto partials_of = [&](int reader) {
+    const int src = partials_from[reader];
+    return src >= 0 ? deferred[src] : DeferredGemv{0, 0};
+  };
   bool needs_fusion = false;  // the graph holds ops that exist only inside the fused decode step
   // ---- one step per op ----
   for (int i = 0; i < (int)ops.size(); i++) {
@@ -561,7 +606,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         return b.fail(TB200_INVALID_ARGUMENT, "op %d reads tensor %d before anything wrote it", i, id);
 
     if (fused_away[i]) {
-      step.kernel_name = "(table in the convolution's epilogue)";
+      step.kernel_name = op.kind == TB200_OP_RMSNORM ? "(norm fused into the previous norm)" : "(table in the convolution's epilogue)";
       step.launches = 0;
       step.launch = [](const ExecContext&) {};
       plan.steps.push_back(std::move(step));
@@ -1086,6 +1131,29 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         Loc lx = loc(op.in0), lr = loc(op.in1), lo = loc(op.out0);
         const float eps = op.f0;
         const bool has_res = op.in1 >= 0;
+        const DeferredGemv dg = partials_of(i);
+        const int second = norm_second[i];
+        if (dg.splits > 0 || second >= 0) {
+          size_t w2_off = 0;
+          Loc lo2{};
+          float eps2 = 0.f;
+          if (second >= 0) {
+            if (!b.add_raw_const(ops[second].weights, (size_t)H * 2, "norm weight", second, w2_off)) return b.status;
+            lo2 = loc(ops[second].out0);
+            eps2 = ops[second].f0;
+          }
+          step.kernel_name = second >= 0 ? (dg.splits > 0 ? "rmsnorm_pair_from_partials" : "rmsnorm_pair")
+                                         : "rmsnorm_from_partials";
+          step.launch = [=](const ExecContext& c) {
+            const GemvPartials gp{dg.splits > 0 ? (const float*)c.scratch : nullptr,
+                                  dg.splits > 0 ? (const uint16_t*)(c.consts + dg.scale_off) : nullptr, dg.splits};
+            launch_rmsnorm_fused((const uint16_t*)lx.resolve(c), gp, has_res ? (const uint16_t*)lr.resolve(c) : nullptr,
+                                 (const uint16_t*)(c.consts + w_off), (uint16_t*)lo.resolve(c),
+                                 second >= 0 ? (const uint16_t*)(c.consts + w2_off) : nullptr,
+                                 second >= 0 ? (uint16_t*)lo2.resolve(c) : nullptr, rows, H, eps, eps2, c.stream);
+          };
+          break;
+        }
         step.kernel_name = "rmsnorm";
         step.launch = [=](const ExecContext& c) {
           launch_rmsnorm((const uint16_t*)lx.resolve(c), has_res ? (const uint16_t*)lr.resolve(c) : nullptr,
@@ -1112,12 +1180,14 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         const int splits = op.i0 > 0 ? op.i0 : gemv_w8_splits(B, N, K);
         scratch_need = std::max(scratch_need, gemv_w8_scratch_bytes(B, N, splits));
         Loc lx = loc(op.in0), lo = loc(op.out0);
-        step.kernel_name = splits > 1 ? "gemv_w8_splitk" : "gemv_w8";
-        step.launches = splits > 1 ? 2 : 1;
+        const bool finalize = !defer_finalize[i];
+        if (!finalize) deferred[i] = DeferredGemv{s_off, gemv_w8_used_splits(B, N, K, splits)};
+        step.kernel_name = !finalize ? "gemv_w8_splitk_partials" : splits > 1 ? "gemv_w8_splitk" : "gemv_w8";
+        step.launches = splits > 1 && finalize ? 2 : 1;
         step.launch = [=](const ExecContext& c) {
           launch_gemv_w8((const uint16_t*)lx.resolve(c), (const int8_t*)(c.consts + w_off),
                          (const uint16_t*)(c.consts + s_off), lo.resolve(c), y_f32, (float*)c.scratch, B, N, K, splits,
-                         c.stream);
+                         c.stream, finalize);
         };
         break;
       }
@@ -1138,11 +1208,14 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         if (!b.add_raw_const(op.bias, (size_t)D * 2, "k_norm weight", i, kw_off)) return b.status;
         Loc lx = loc(op.in0), lp = loc(op.in1), lq = loc(op.out0), lk = loc(op.out1), lv = loc(op.in2);
         const float theta = op.f0, eps = op.f1;
-        step.kernel_name = "rope_kv";
+        const DeferredGemv dg = partials_of(i);
+        step.kernel_name = dg.splits > 0 ? "rope_kv_from_partials" : "rope_kv";
         step.launch = [=](const ExecContext& c) {
+          const GemvPartials gp{dg.splits > 0 ? (const float*)c.scratch : nullptr,
+                                dg.splits > 0 ? (const uint16_t*)(c.consts + dg.scale_off) : nullptr, dg.splits};
           launch_rope_kv((const uint16_t*)lx.resolve(c), (const int32_t*)lp.resolve(c), (const uint16_t*)(c.consts + qw_off),
                          (const uint16_t*)(c.consts + kw_off), (uint16_t*)lq.resolve(c), (uint16_t*)lk.resolve(c),
-                         (uint16_t*)lv.resolve(c), B, n_q, n_kv, D, T, theta, eps, c.stream);
+                         (uint16_t*)lv.resolve(c), B, n_q, n_kv, D, T, theta, eps, c.stream, gp);
         };
         break;
       }
@@ -1177,9 +1250,12 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: geglu wants bf16 [B,2I] -> bf16 [B,I]", i);
         const int B = tensors[op.out0].shape[0], I = tensors[op.out0].shape[1];
         Loc lx = loc(op.in0), lo = loc(op.out0);
-        step.kernel_name = "geglu";
+        const DeferredGemv dg = partials_of(i);
+        step.kernel_name = dg.splits > 0 ? "geglu_from_partials" : "geglu";
         step.launch = [=](const ExecContext& c) {
-          launch_geglu((const uint16_t*)lx.resolve(c), (uint16_t*)lo.resolve(c), B, I, c.stream);
+          const GemvPartials gp{dg.splits > 0 ? (const float*)c.scratch : nullptr,
+                                dg.splits > 0 ? (const uint16_t*)(c.consts + dg.scale_off) : nullptr, dg.splits};
+          launch_geglu((const uint16_t*)lx.resolve(c), (uint16_t*)lo.resolve(c), B, I, c.stream, gp);
         };
         break;
       }
