@@ -110,10 +110,32 @@ __global__ void __launch_bounds__(512) rmsnorm_fused_kernel(const uint16_t* __re
   const size_t base = (size_t)blockIdx.x * H;
   const size_t bn = (size_t)rows * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = operand_at(x, gp, bn, base + i, i);
-    row_s[i] = v;
-    ss += v * v;
+  if (gp.splits > 0 && H <= 4 * (int)blockDim.x) {
+    // up to four elements per thread: slices outermost, so that 4 x 8 loads are in flight together;
+    // every element still adds its slices in order
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* p0 = gp.partial + base + threadIdx.x;
+#pragma unroll 8
+    for (int sp = 0; sp < gp.splits; sp++) {
+#pragma unroll
+      for (int e = 0; e < 4; e++)
+        if ((int)threadIdx.x + e * (int)blockDim.x < H) a[e] += __ldg(p0 + (size_t)sp * bn + e * blockDim.x);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const int i = threadIdx.x + e * blockDim.x;
+      if (i < H) {
+        const float v = bf2f(f2bf(a[e] * bf2f(__ldg(gp.scale + i))));
+        row_s[i] = v;
+        ss += v * v;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float v = operand_at(x, gp, bn, base + i, i);
+      row_s[i] = v;
+      ss += v * v;
+    }
   }
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)H + eps);
@@ -230,6 +252,23 @@ __global__ void __launch_bounds__(256) gemv_w8_mma_kernel(const uint16_t* __rest
   const int k_begin = split * k_slice;
   const int k_len = min(k_slice, K - k_begin);  // a multiple of 64
   const int xstride = ((k_slice * 2 + 127) / 128) * 128 + 16;  // bytes per token row in shared memory
+  const int row0 = blockIdx.x * 128 + warp * 16;
+  const bool active = row0 < N;
+  const int r_lo = row0 + g, r_hi = row0 + g + 8;
+  const int8_t* w_lo = W + (size_t)min(r_lo, N - 1) * K + k_begin + tig * 16;
+  const int8_t* w_hi = W + (size_t)min(r_hi, N - 1) * K + k_begin + tig * 16;
+  const int kbs = k_len >> 6;
+  // the first two 64-byte blocks of this lane's weight rows are requested before x is staged, so that
+  // their latency overlaps the staging
+  uint4 pa[2], pb[2];
+#pragma unroll
+  for (int p = 0; p < 2; p++) {
+    pa[p] = pb[p] = make_uint4(0, 0, 0, 0);
+    if (active && p < kbs) {
+      pa[p] = __ldg(reinterpret_cast<const uint4*>(w_lo + p * 64));
+      pb[p] = __ldg(reinterpret_cast<const uint4*>(w_hi + p * 64));
+    }
+  }
   // stage x[:, k_begin : k_begin + k_len]; tokens beyond B read as zero
   for (int i = threadIdx.x; i < NT * 8 * (k_len / 8); i += blockDim.x) {
     const int b = i / (k_len / 8), c = i % (k_len / 8);
@@ -238,22 +277,14 @@ __global__ void __launch_bounds__(256) gemv_w8_mma_kernel(const uint16_t* __rest
     *reinterpret_cast<uint4*>(xs_raw + (size_t)b * xstride + 16 * c) = v;
   }
   __syncthreads();
-  const int row0 = blockIdx.x * 128 + warp * 16;
-  if (row0 >= N) return;
-  const int r_lo = row0 + g, r_hi = row0 + g + 8;
-  const int8_t* w_lo = W + (size_t)min(r_lo, N - 1) * K + k_begin + tig * 16;
-  const int8_t* w_hi = W + (size_t)min(r_hi, N - 1) * K + k_begin + tig * 16;
+  if (!active) return;
   float c[NT][4];
 #pragma unroll
   for (int t = 0; t < NT; t++)
 #pragma unroll
     for (int j = 0; j < 4; j++) c[t][j] = 0.f;
   const unsigned char* xrow = xs_raw + (size_t)g * xstride + tig * 32;
-  const int kbs = k_len >> 6;
-#pragma unroll 2
-  for (int kb = 0; kb < kbs; kb++) {
-    const uint4 wa = __ldg(reinterpret_cast<const uint4*>(w_lo + kb * 64));
-    const uint4 wb = __ldg(reinterpret_cast<const uint4*>(w_hi + kb * 64));
+  auto block64 = [&](int kb, const uint4& wa, const uint4& wb) {
     uint32_t a[4][4];  // [mma within the block of 64][a0..a3]
     s8x4_to_bf16x4(wa.x, a[0][0], a[0][2]); s8x4_to_bf16x4(wb.x, a[0][1], a[0][3]);
     s8x4_to_bf16x4(wa.y, a[1][0], a[1][2]); s8x4_to_bf16x4(wb.y, a[1][1], a[1][3]);
@@ -268,6 +299,14 @@ __global__ void __launch_bounds__(256) gemv_w8_mma_kernel(const uint16_t* __rest
       mma_bf16(c[t], a[2][0], a[2][1], a[2][2], a[2][3], x1.x, x1.y);
       mma_bf16(c[t], a[3][0], a[3][1], a[3][2], a[3][3], x1.z, x1.w);
     }
+  };
+  if (kbs > 0) block64(0, pa[0], pb[0]);
+  if (kbs > 1) block64(1, pa[1], pb[1]);
+#pragma unroll 2
+  for (int kb = 2; kb < kbs; kb++) {
+    const uint4 wa = __ldg(reinterpret_cast<const uint4*>(w_lo + kb * 64));
+    const uint4 wb = __ldg(reinterpret_cast<const uint4*>(w_hi + kb * 64));
+    block64(kb, wa, wb);
   }
   // c[t][0], c[t][1]: row r_lo, tokens 8t + 2tig, + 1; c[t][2], c[t][3]: row r_hi
   const float s_lo = r_lo < N ? bf2f(__ldg(scale + r_lo)) : 0.f, s_hi = r_hi < N ? bf2f(__ldg(scale + r_hi)) : 0.f;
@@ -377,27 +416,62 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const uint16_t* __res
   float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
   for (int j = 0; j < 8; j++) acc[j] = 0.f;
-  for (int t = t0; t < t1; t++) {
-    const size_t off = ((size_t)b * T + t) * kAttnD + lane * 8;
-    const uint4 kk = __ldg(reinterpret_cast<const uint4*>(kcache + off));
-    const uint4 vv = __ldg(reinterpret_cast<const uint4*>(vcache + off));
-    const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
-    float s = 0.f;
+  // four keys per round: their score reductions interleave and one rescale serves all four
+  // and the next round's rows are loaded before this round's arithmetic (registers as the second buffer)
+  uint4 kk[4], vv[4], nk[4], nv[4];
+  auto load_round = [&](int t, uint4 (&kd)[4], uint4 (&vd)[4]) {
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      s = fmaf(qv[2 * j], __uint_as_float(kw[j] << 16), s);
-      s = fmaf(qv[2 * j + 1], __uint_as_float(kw[j] & 0xffff0000u), s);
+    for (int u = 0; u < 4; u++) {
+      const size_t off = ((size_t)b * T + min(t + u, t1 - 1)) * kAttnD + lane * 8;
+      kd[u] = __ldg(reinterpret_cast<const uint4*>(kcache + off));
+      vd[u] = __ldg(reinterpret_cast<const uint4*>(vcache + off));
     }
-    s = warp_sum(s);
-    const float m_new = fmaxf(m, s);
-    const float corr = expf(m - m_new), p = expf(s - m_new);
-    l = l * corr + p;
+  };
+  if (t0 < t1) load_round(t0, kk, vv);
+  for (int t = t0; t < t1; t += 4) {
+    if (t + 4 < t1) load_round(t + 4, nk, nv);
+    float s[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      acc[2 * j] = acc[2 * j] * corr + p * __uint_as_float(vw[j] << 16);
-      acc[2 * j + 1] = acc[2 * j + 1] * corr + p * __uint_as_float(vw[j] & 0xffff0000u);
+    for (int u = 0; u < 4; u++) {
+      const uint32_t kw[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
+      float d = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        d = fmaf(qv[2 * j], __uint_as_float(kw[j] << 16), d);
+        d = fmaf(qv[2 * j + 1], __uint_as_float(kw[j] & 0xffff0000u), d);
+      }
+      s[u] = d;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int u = 0; u < 4; u++) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+#pragma unroll
+    for (int u = 1; u < 4; u++)
+      if (t + u >= t1) s[u] = -INFINITY;  // past the slice: weight 0
+    const float m_new = fmaxf(fmaxf(m, s[0]), fmaxf(fmaxf(s[1], s[2]), s[3]));
+    const float corr = expf(m - m_new);
+    float p[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) p[u] = expf(s[u] - m_new);
+    l = l * corr + ((p[0] + p[1]) + (p[2] + p[3]));
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] *= corr;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const uint32_t vw[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        acc[2 * j] = fmaf(p[u], __uint_as_float(vw[j] << 16), acc[2 * j]);
+        acc[2 * j + 1] = fmaf(p[u], __uint_as_float(vw[j] & 0xffff0000u), acc[2 * j + 1]);
+      }
     }
     m = m_new;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      kk[u] = nk[u];
+      vv[u] = nv[u];
+    }
   }
   float* dst = part + (((size_t)b * n_q + h) * S + sp) * (kAttnD + 2);
   if (lane == 0) {
