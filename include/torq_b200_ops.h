@@ -145,7 +145,8 @@ typedef struct tb200_op {
   int32_t in1_mult, in1_shift;
   int32_t out_mult, out_shift; /* output rescale of elementwise ops (scalar) */
   int32_t pad_value;      /* MAXPOOL: constant of the folded tosa.pad */
-  int32_t i0, i1, i2, i3; /* op-specific (decoder: heads, kv heads, head_dim, window) */
+  int32_t i0, i1, i2, i3; /* op-specific (decoder: heads, kv heads, head_dim, window; ADD/SUB/MUL: i0, i1 =
+                             left shift of (in0 - zp), (in1 - zp) before the input-side rescale, 0..22) */
   float f0, f1, f2, f3;   /* op-specific (eps, rope theta, scale) */
 } tb200_op_t;
 

@@ -192,13 +192,13 @@ _KIND = {"add": 0, "sub": 1, "mul": 2}
 
 
 def binary(kind, a, b, a_zp, a_mult, a_shift, b_zp, b_mult, b_shift, out_mult, out_shift, out_zp,
-           double_round=True, clamp_min=-128, clamp_max=127):
+           double_round=True, clamp_min=-128, clamp_max=127, a_lshift=0, b_lshift=0):
     a, b = _i8(a), _i8(b)
     assert a.shape == b.shape
     out = np.empty(a.shape, np.int8)
-    lib().tq_binary(_KIND[kind], _p8(a), _p8(b), C.c_int64(a.size), int(a_zp), int(a_mult), int(a_shift),
-                    int(b_zp), int(b_mult), int(b_shift), int(out_mult), int(out_shift), int(out_zp),
-                    int(double_round), int(clamp_min), int(clamp_max), _p8(out))
+    lib().tq_binary_pre(_KIND[kind], _p8(a), _p8(b), C.c_int64(a.size), int(a_zp), int(a_lshift), int(a_mult),
+                        int(a_shift), int(b_zp), int(b_lshift), int(b_mult), int(b_shift), int(out_mult),
+                        int(out_shift), int(out_zp), int(double_round), int(clamp_min), int(clamp_max), _p8(out))
     return out
 
 

@@ -172,9 +172,10 @@ def avgpool(x, kernel, stride, pad=(0, 0, 0, 0), input_zp=0, output_zp=0):
 
 
 def binary(kind, a, b, a_zp, a_mult, a_shift, b_zp, b_mult, b_shift, out_mult, out_shift, out_zp,
-           double_round=True, clamp_min=-128, clamp_max=127):
-    ra = apply_scale_32(np.asarray(a, np.int64) - a_zp, a_mult, a_shift, double_round)
-    rb = apply_scale_32(np.asarray(b, np.int64) - b_zp, b_mult, b_shift, double_round)
+           double_round=True, clamp_min=-128, clamp_max=127, a_lshift=0, b_lshift=0):
+    # x_lshift: the exact left shift that the first stage of a two-stage input rescale amounts to
+    ra = apply_scale_32((np.asarray(a, np.int64) - a_zp) << a_lshift, a_mult, a_shift, double_round)
+    rb = apply_scale_32((np.asarray(b, np.int64) - b_zp) << b_lshift, b_mult, b_shift, double_round)
     v = wrap32({"add": ra + rb, "sub": ra - rb, "mul": ra * rb}[kind])
     r = wrap32(apply_scale_32(v, out_mult, out_shift, double_round) + out_zp)
     return np.clip(r, clamp_min, clamp_max).astype(np.int8)

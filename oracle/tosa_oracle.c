@@ -322,10 +322,21 @@ void tq_avgpool(const int8_t* x, int N, int H, int W, int C, int KH, int KW, int
 void tq_binary(int kind, const int8_t* a, const int8_t* b, int64_t n, int a_zp, int a_mult, int a_shift,
                int b_zp, int b_mult, int b_shift, int out_mult, int out_shift, int out_zp,
                int double_round, int clamp_min, int clamp_max, int8_t* out) {
+  tq_binary_pre(kind, a, b, n, a_zp, 0, a_mult, a_shift, b_zp, 0, b_mult, b_shift, out_mult, out_shift, out_zp,
+                double_round, clamp_min, clamp_max, out);
+}
+
+/* The same with the two-stage input rescale of the TFLite-derived fixtures
+ * (tests/testdata/tosa_ops/add-56x56x256.mlir, sub-56x56x256xi8.mlir): the first tosa.rescale
+ * (multiplier 2^30, shift s <= 30, i8 -> i32) is an exact left shift by 30 - s, the second
+ * (i32 -> i32) is the real scaling. x_lshift is that left shift (0: single-stage form). */
+void tq_binary_pre(int kind, const int8_t* a, const int8_t* b, int64_t n, int a_zp, int a_lshift, int a_mult, int a_shift,
+                   int b_zp, int b_lshift, int b_mult, int b_shift, int out_mult, int out_shift, int out_zp,
+                   int double_round, int clamp_min, int clamp_max, int8_t* out) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; i++) {
-    int32_t ra = tq_apply_scale_32((int32_t)a[i] - a_zp, a_mult, a_shift, double_round);
-    int32_t rb = tq_apply_scale_32((int32_t)b[i] - b_zp, b_mult, b_shift, double_round);
+    int32_t ra = tq_apply_scale_32(((int32_t)a[i] - a_zp) * (1 << a_lshift), a_mult, a_shift, double_round);
+    int32_t rb = tq_apply_scale_32(((int32_t)b[i] - b_zp) * (1 << b_lshift), b_mult, b_shift, double_round);
     int32_t v = kind == 0 ? wadd(ra, rb) : kind == 1 ? wsub(ra, rb) : wmul(ra, rb);
     int32_t r = tq_apply_scale_32(v, out_mult, out_shift, double_round);
     r = wadd(r, out_zp);

@@ -66,6 +66,9 @@ void tq_avgpool(const int8_t* x, int N, int H, int W, int C, int KH, int KW, int
 void tq_binary(int kind, const int8_t* a, const int8_t* b, int64_t n, int a_zp, int a_mult, int a_shift,
                int b_zp, int b_mult, int b_shift, int out_mult, int out_shift, int out_zp,
                int double_round, int clamp_min, int clamp_max, int8_t* out);
+void tq_binary_pre(int kind, const int8_t* a, const int8_t* b, int64_t n, int a_zp, int a_lshift, int a_mult, int a_shift,
+                   int b_zp, int b_lshift, int b_mult, int b_shift, int out_mult, int out_shift, int out_zp,
+                   int double_round, int clamp_min, int clamp_max, int8_t* out);
 void tq_table(const int8_t* x, int64_t n, const int8_t* table, int8_t* out);
 void tq_rescale(const int8_t* x, int64_t rows, int C, int input_zp, const tq_requant_t* rq, int8_t* out);
 void tq_resize_nn2x(const int8_t* x, int N, int H, int W, int C, int8_t* out);

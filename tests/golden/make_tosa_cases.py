@@ -23,13 +23,28 @@ from oracle import oracle_np as onp  # noqa: E402
 from oracle_exec import run_graph  # noqa: E402
 from torq_b200 import tosa_frontend  # noqa: E402
 
+# every fixture of tests/testdata/{tosa_ops,gen_ops} that the front end reads, with int8 tensors and at most
+# 1.3 M input + output elements (the larger and the int16 ones are left out)
 CASES = [
-    "gen_ops/conv2d_8x8", "gen_ops/conv2d_64x64", "gen_ops/maxpool2d_8x8", "tosa_ops/dw_peeling", "tosa_ops/dw_4x4_stride2",
-    "tosa_ops/dw_21x21_odd_frame_stride2", "tosa_ops/conv_5x5_odd_frame_stride2", "tosa_ops/avgpool2d",
-    "tosa_ops/add-single-rescale", "tosa_ops/disable-sub", "tosa_ops/yolov8_block_mul_rescale",
-    "tosa_ops/efficientnet-sigmoid-rescale-mul", "tosa_ops/maxpool2d-stride2-k3x3-pad-112x112x64",
-    "tosa_ops/maxpool2d-stride2-k3x3-top-left-pad", "tosa_ops/maxpool_f5_s2_top_left_pad_10x10x4",
-    "tosa_ops/maxpool_f7_8x8x4", "tosa_ops/resize-8x8x32xi8", "tosa_ops/resize-31x31x33xi8",
+    "tosa_ops/add-rank2", "tosa_ops/add-single-rescale", "tosa_ops/add", "tosa_ops/add_dense_8x8x24xi8",
+    "tosa_ops/add_strided_7x7x24xi8", "tosa_ops/avgpool2d", "tosa_ops/conv_5x5_odd_frame_stride2",
+    "tosa_ops/disable-avgpool", "tosa_ops/disable-resize-nearest-neighbor-10x10x512xi8",
+    "tosa_ops/disable-resize-nearest-neighbor-20x20x256xi8", "tosa_ops/disable-sub",
+    "tosa_ops/dw_21x21_odd_frame_stride2", "tosa_ops/dw_4x4_stride2", "tosa_ops/dw_peeling",
+    "tosa_ops/efficientnet-sigmoid-rescale-mul", "tosa_ops/maxpool-seg-tile-1", "tosa_ops/maxpool-seg-tile",
+    "tosa_ops/maxpool1d_i8_stride4_k4x1_256x16x32", "tosa_ops/maxpool2d-stride1-k3x3-32x32x4",
+    "tosa_ops/maxpool2d-stride2-k2x2-32x32x4", "tosa_ops/maxpool2d-stride2-k2x2-8x8x1",
+    "tosa_ops/maxpool2d-stride2-k2x2-8x8x32", "tosa_ops/maxpool2d-stride2-k2x2-8x8x4",
+    "tosa_ops/maxpool2d-stride2-k3x3-32x32x4", "tosa_ops/maxpool2d-stride2-k3x3-8x8x4",
+    "tosa_ops/maxpool2d-stride2-k3x3-bottom-right-pad", "tosa_ops/maxpool2d-stride2-k3x3-pad-112x112x64",
+    "tosa_ops/maxpool2d-stride2-k3x3-pad-32x32x64", "tosa_ops/maxpool2d-stride2-k3x3-top-left-pad",
+    "tosa_ops/maxpool2d_int8_batch1_2x2_stride2x2_32x16x4", "tosa_ops/maxpool_f5_15x20x384", "tosa_ops/maxpool_f5_8x8x4",
+    "tosa_ops/maxpool_f5_s2_10x10x4", "tosa_ops/maxpool_f5_s2_top_left_pad_10x10x4", "tosa_ops/maxpool_f7_8x8x4",
+    "tosa_ops/maxpool_f7_s2_10x10x4", "tosa_ops/maxpool_f7_s2_top_left_pad_10x10x4",
+    "tosa_ops/maxpool_int8_batch1_3x3_stride1x1_16x4", "tosa_ops/reshape", "tosa_ops/resize-31x31x33xi8",
+    "tosa_ops/resize-4x4x32xi8", "tosa_ops/resize-8x8x32xi8", "tosa_ops/sub-1input-56x56x24xi8",
+    "tosa_ops/sub-1input-strided-7x7x24xi8", "tosa_ops/yolov8_block_mul_rescale", "gen_ops/add_8x8", "gen_ops/add_8x8_i8",
+    "gen_ops/conv2d_64x64", "gen_ops/conv2d_8x8", "gen_ops/maxpool2d_8x8",
 ]
 
 
@@ -54,7 +69,7 @@ def numpy_replay(g, inputs):
         elif k in ("add", "sub", "mul"):
             y = onp.binary(k, x, vals[op.inputs[1].id], a["in0_zp"], a["in0_mult"], a["in0_shift"], a["in1_zp"], a["in1_mult"],
                            a["in1_shift"], a["out_mult"], a["out_shift"], a["out_zp"], bool(a["double_round"]), a["clamp_min"],
-                           a["clamp_max"])
+                           a["clamp_max"], a_lshift=a["i0"], b_lshift=a["i1"])
         elif k == "table":
             y = onp.table(x, op.consts["table"].data)
         elif k == "resize_nn2x":

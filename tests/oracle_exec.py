@@ -44,7 +44,7 @@ def run_graph(graph, inputs, keep_all=False):
         elif k in ("add", "sub", "mul"):
             y = oc.binary(k, x, vals[op.inputs[1].id], a["in0_zp"], a["in0_mult"], a["in0_shift"], a["in1_zp"],
                           a["in1_mult"], a["in1_shift"], a["out_mult"], a["out_shift"], a["out_zp"],
-                          bool(a["double_round"]), a["clamp_min"], a["clamp_max"])
+                          bool(a["double_round"]), a["clamp_min"], a["clamp_max"], a_lshift=a["i0"], b_lshift=a["i1"])
         elif k == "table":
             y = oc.table(x, op.consts["table"].data)
         elif k == "rescale":

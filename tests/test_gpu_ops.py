@@ -197,6 +197,13 @@ def test_add_sub_mul(device, shape):
         g.output(fn(g.input(shape), g.input(shape), a_zp=-3, a_ms=(1 << 30, 11), b_zp=5, b_ms=(1 << 30, 11),
                     out_ms=(1093202297, 49), out_zp=-2))
         _check(device, g, [a, b])
+        # two-stage input rescale (left shift 20, then a 32-bit multiplier with shift 32: the double-round branch
+        # on the input side), the form of tests/testdata/tosa_ops/add-56x56x256.mlir with other constants
+        g = Graph()
+        fn = getattr(g, kind)
+        g.output(fn(g.input(shape), g.input(shape), a_zp=-60, a_ms=(1400000001, 32), a_lshift=20, b_zp=9, b_ms=(1 << 30, 11),
+                    out_ms=(1090000000, 48), out_zp=-128))
+        _check(device, g, [a, b])
     g = Graph()
     g.output(g.mul(g.input(shape), g.input(shape), a_zp=3, a_ms=(1 << 30, 30), b_zp=-4, b_ms=(1 << 30, 30),
                    out_ms=quantize_multiplier(1.0 / 150), out_zp=1, clamp=(-100, 100)))

@@ -69,3 +69,49 @@ def test_add_chain_and_unsupported_ops():
     assert (a["in0_zp"], a["in1_zp"], a["in0_shift"], a["out_mult"], a["out_shift"], a["out_zp"]) == (-3, 7, 11, 1200000000, 49, -2)
     with pytest.raises(NotImplementedError):
         tosa_frontend.build_graph(ADD.replace("tosa.add", "tosa.bitwise_and"))
+
+
+TWO_STAGE = '''
+module {
+  func.func @main(%arg0: tensor<1x3x5x16xi8>, %arg1: tensor<1x3x5x16xi8>) -> tensor<1x3x5x16xi8> {
+    %one = arith.constant dense<1073741824> : tensor<1xi32>
+    %s9 = arith.constant dense<9> : tensor<1xi8>
+    %z0 = arith.constant dense<-21> : tensor<1xi8>
+    %zero = arith.constant dense<0> : tensor<1xi32>
+    %0 = tosa.rescale %arg0, %one, %s9, %z0, %zero {input_unsigned = false, output_unsigned = false, per_channel = false, rounding_mode = DOUBLE_ROUND, scale32 = true} : (tensor<1x3x5x16xi8>, tensor<1xi32>, tensor<1xi8>, tensor<1xi8>, tensor<1xi32>) -> tensor<1x3x5x16xi32>
+    %m0 = arith.constant dense<1711111111> : tensor<1xi32>
+    %s32 = arith.constant dense<32> : tensor<1xi8>
+    %1 = tosa.rescale %0, %m0, %s32, %zero, %zero {input_unsigned = false, output_unsigned = false, per_channel = false, rounding_mode = DOUBLE_ROUND, scale32 = true} : (tensor<1x3x5x16xi32>, tensor<1xi32>, tensor<1xi8>, tensor<1xi32>, tensor<1xi32>) -> tensor<1x3x5x16xi32>
+    %s10 = arith.constant dense<10> : tensor<1xi8>
+    %z1 = arith.constant dense<4> : tensor<1xi8>
+    %2 = tosa.rescale %arg1, %one, %s10, %z1, %zero {input_unsigned = false, output_unsigned = false, per_channel = false, rounding_mode = DOUBLE_ROUND, scale32 = true} : (tensor<1x3x5x16xi8>, tensor<1xi32>, tensor<1xi8>, tensor<1xi8>, tensor<1xi32>) -> tensor<1x3x5x16xi32>
+    %3 = tosa.OPNAME %1, %2 : (tensor<1x3x5x16xi32>, tensor<1x3x5x16xi32>) -> tensor<1x3x5x16xi32>
+    %m = arith.constant dense<1100000000> : tensor<1xi32>
+    %sh = arith.constant dense<50> : tensor<1xi8>
+    %oz = arith.constant dense<-100> : tensor<1xi8>
+    %4 = tosa.rescale %3, %m, %sh, %zero, %oz {input_unsigned = false, output_unsigned = false, per_channel = false, rounding_mode = DOUBLE_ROUND, scale32 = true} : (tensor<1x3x5x16xi32>, tensor<1xi32>, tensor<1xi8>, tensor<1xi32>, tensor<1xi8>) -> tensor<1x3x5x16xi8>
+    return %4 : tensor<1x3x5x16xi8>
+  }
+}
+'''
+
+
+@pytest.mark.parametrize("name", ["add", "sub"])
+def test_two_stage_input_rescale_becomes_a_left_shift(name):
+    """i8 -> i32 with multiplier 2^30 and shift s (an exact left shift by 30 - s) followed by an i32 -> i32
+    rescale: one op whose operand is shifted before its rescale. Checked against the staged arithmetic
+    written out with the numpy restatement of apply_scale_32."""
+    from oracle import oracle_np as onp
+    g = tosa_frontend.build_graph(TWO_STAGE.replace("OPNAME", name))
+    assert [op.kind for op in g.ops] == [name]
+    a = g.ops[0].attrs
+    assert (a["i0"], a["i1"], a["in0_zp"], a["in1_zp"]) == (21, 0, -21, 4)  # the single-stage operand keeps its rescale
+    assert (a["in0_mult"], a["in0_shift"], a["in1_mult"], a["in1_shift"]) == (1711111111, 32, 1 << 30, 10)
+    rng = np.random.default_rng(3)
+    x, y = (rng.integers(-128, 128, (1, 3, 5, 16), dtype=np.int8) for _ in range(2))
+    got = run_graph(g, [x, y])[0]
+    r0 = onp.apply_scale_32(onp.apply_scale_32(x.astype(np.int64) + 21, 1 << 30, 9, True), 1711111111, 32, True)
+    r1 = onp.apply_scale_32(y.astype(np.int64) - 4, 1 << 30, 10, True)
+    v = r0 + r1 if name == "add" else r0 - r1
+    want = np.clip(onp.apply_scale_32(v, 1100000000, 50, True) - 100, -128, 127).astype(np.int8)
+    assert (got == want).all() and len(np.unique(got)) > 20

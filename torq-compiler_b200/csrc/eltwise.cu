@@ -121,8 +121,8 @@ __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
 // ---- add / sub / mul in TOSA form (ElementWiseBinaryPattern.cpp:385-570, MulPattern.cpp:229-238) ----
 __device__ __forceinline__ int binary_one(const BinaryArgs& a, int av, int bv) {
   const bool dr = a.double_round != 0;
-  int ra = apply_scale_32(av - a.a_zp, a.a_mult, a.a_shift, dr);
-  int rb = apply_scale_32(bv - a.b_zp, a.b_mult, a.b_shift, dr);
+  int ra = apply_scale_32((av - a.a_zp) * (1 << a.a_lshift), a.a_mult, a.a_shift, dr);
+  int rb = apply_scale_32((bv - a.b_zp) * (1 << a.b_lshift), a.b_mult, a.b_shift, dr);
   int v = a.kind == 0 ? ra + rb : a.kind == 1 ? ra - rb : ra * rb;
   return requant(v, a.out_mult, a.out_shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
 }

@@ -66,6 +66,7 @@ struct BinaryArgs {
   int kind;  // 0 add, 1 sub, 2 mul
   int a_zp, a_mult, a_shift, b_zp, b_mult, b_shift, out_mult, out_shift, out_zp;
   int double_round, clamp_min, clamp_max;
+  int a_lshift, b_lshift;  // (x - zp) << lshift before the input rescale (two-stage input rescale), 0..22
 };
 void launch_binary(const BinaryArgs& a, cudaStream_t stream);
 

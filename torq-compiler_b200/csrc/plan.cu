@@ -987,6 +987,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         a.b_zp = op.in1_zp; a.b_mult = op.in1_mult; a.b_shift = op.in1_shift;
         a.out_mult = op.out_mult; a.out_shift = op.out_shift; a.out_zp = op.out_zp;
         a.double_round = op.double_round; a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
+        if (op.i0 < 0 || op.i0 > 22 || op.i1 < 0 || op.i1 > 22)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: input left shift outside [0,22]", i);
+        a.a_lshift = op.i0; a.b_lshift = op.i1;
         Loc la = loc(op.in0), lb = loc(op.in1), lo = loc(op.out0);
         step.kernel_name = "binary_rescale";
         step.launch = [=](const ExecContext& c) {

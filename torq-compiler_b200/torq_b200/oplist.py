@@ -217,22 +217,29 @@ class Graph:
                           stride_w=stride[1], pad_t=pad[0], pad_b=pad[1], pad_l=pad[2], pad_r=pad[3],
                           in0_zp=input_zp, out_zp=output_zp)
 
-    def _binary(self, kind, a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round):
+    def _binary(self, kind, a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round, a_lshift=0, b_lshift=0):
         if a.shape != b.shape:
             raise ValueError("elementwise operands must have equal shapes")
+        if not (0 <= a_lshift <= 22 and 0 <= b_lshift <= 22):
+            raise ValueError("input left shift outside [0, 22]")
         return self._emit(kind, [a, b], a.shape, in0_zp=a_zp, in0_mult=a_ms[0], in0_shift=a_ms[1], in1_zp=b_zp,
                           in1_mult=b_ms[0], in1_shift=b_ms[1], out_mult=out_ms[0], out_shift=out_ms[1],
-                          out_zp=out_zp, clamp_min=clamp[0], clamp_max=clamp[1], double_round=int(double_round))
+                          out_zp=out_zp, clamp_min=clamp[0], clamp_max=clamp[1], double_round=int(double_round),
+                          i0=a_lshift, i1=b_lshift)
 
-    def add(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True):
-        """torq_hl.add in TOSA form; *_ms = (multiplier, shift)."""
-        return self._binary("add", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round)
+    def add(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True, a_lshift=0,
+            b_lshift=0):
+        """torq_hl.add in TOSA form; *_ms = (multiplier, shift). x_lshift: (x - zp) is shifted left by this
+        before its rescale (the first stage of the two-stage input rescale TFLite-derived graphs carry)."""
+        return self._binary("add", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round, a_lshift, b_lshift)
 
-    def sub(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True):
-        return self._binary("sub", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round)
+    def sub(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True, a_lshift=0,
+            b_lshift=0):
+        return self._binary("sub", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round, a_lshift, b_lshift)
 
-    def mul(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True):
-        return self._binary("mul", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round)
+    def mul(self, a, b, *, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp=(-128, 127), double_round=True, a_lshift=0,
+            b_lshift=0):
+        return self._binary("mul", a, b, a_zp, a_ms, b_zp, b_ms, out_ms, out_zp, clamp, double_round, a_lshift, b_lshift)
 
     def table(self, x, table):
         t = np.asarray(table, np.int8)

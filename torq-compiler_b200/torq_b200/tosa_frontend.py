@@ -195,9 +195,17 @@ def build_graph(text: str) -> Graph:
             src = op.operands[0]
             if src.dtype == "i8" and op.result.dtype == "i32":
                 users = list({id(u): u for u in op.users}.values())  # x + x uses the rescale twice
+                if len(users) == 1 and users[0].name == "rescale" and users[0].result.dtype == "i32":
+                    users = list({id(u): u for u in users[0].users}.values())  # first of two input stages
                 if len(users) != 1 or users[0].name not in ("add", "sub", "mul"):
                     raise NotImplementedError("i8->i32 rescale that does not feed add/sub/mul")
                 continue  # consumed when the binary op is reached
+            if src.dtype == "i32" and op.result.dtype == "i32" and src.op is not None and src.op.name == "rescale" and \
+                    src.op.operands[0].dtype == "i8":
+                users = list({id(u): u for u in op.users}.values())
+                if len(users) != 1 or users[0].name not in ("add", "sub", "mul"):
+                    raise NotImplementedError("i32->i32 rescale that does not feed add/sub/mul")
+                continue  # second input stage, consumed when the binary op is reached
             if src.dtype == "i8" and op.result.dtype == "i8":
                 last, lo, hi = fold_clamp(op)
                 mult, shift = (p["mult"], p["shift"]) if p["per_channel"] else (p["mult"][:1], p["shift"][:1])
@@ -213,16 +221,35 @@ def build_graph(text: str) -> Graph:
             if rs is None:
                 raise NotImplementedError(f"{n} without an output rescale")
             done.add(id(rs))
-            pa, pb, po = rescale_params(a.op), rescale_params(b.op), rescale_params(rs)
+            po = rescale_params(rs)
             if po["izp"] != 0:
                 raise NotImplementedError("output rescale of a binary op with a non-zero input zero point")
+
+            def input_side(v):
+                """(source i8 value, zero point, left shift, multiplier, shift) of one operand. Two forms:
+                one rescale i8->i32, or the TFLite-derived pair: i8->i32 with multiplier 2^30 and shift
+                s <= 30 (an exact left shift by 30 - s), then i32->i32 with the real multiplier."""
+                p2 = rescale_params(v.op)
+                if p2["ozp"] != 0 or p2["per_channel"] or p2["double_round"] != po["double_round"]:
+                    raise NotImplementedError("input rescale with an output zero point, per channel, or another rounding mode")
+                src = p2["x"]
+                if src.dtype == "i8":
+                    return src, p2["izp"], 0, int(p2["mult"][0]), int(p2["shift"][0])
+                if src.dtype == "i32" and src.op is not None and src.op.name == "rescale" and src.op.operands[0].dtype == "i8":
+                    p1 = rescale_params(src.op)
+                    s1 = int(p1["shift"][0])
+                    if int(p1["mult"][0]) != 1 << 30 or not 8 <= s1 <= 30 or p1["ozp"] != 0 or p2["izp"] != 0 or p1["per_channel"]:
+                        raise NotImplementedError("first input stage that is not an exact left shift")
+                    return p1["x"], p1["izp"], 30 - s1, int(p2["mult"][0]), int(p2["shift"][0])
+                raise NotImplementedError(f"{n} whose operands are not i8->i32 rescales")
+
+            xa, za, la, ma, sa = input_side(a)
+            xb, zb, lb, mb, sb = input_side(b)
             last, lo, hi = fold_clamp(rs)
             fn = getattr(g, n)
-            env[last.result.name] = fn(env[pa["x"].name], env[pb["x"].name], a_zp=pa["izp"],
-                                       a_ms=(int(pa["mult"][0]), int(pa["shift"][0])), b_zp=pb["izp"],
-                                       b_ms=(int(pb["mult"][0]), int(pb["shift"][0])),
+            env[last.result.name] = fn(env[xa.name], env[xb.name], a_zp=za, a_ms=(ma, sa), b_zp=zb, b_ms=(mb, sb),
                                        out_ms=(int(po["mult"][0]), int(po["shift"][0])), out_zp=po["ozp"], clamp=(lo, hi),
-                                       double_round=po["double_round"])
+                                       double_round=po["double_round"], a_lshift=la, b_lshift=lb)
         elif n == "table":
             env[op.result.name] = g.table(env[op.operands[0].name], op.operands[1].const.reshape(-1))
         elif n == "pad":
