@@ -26,12 +26,15 @@ from torq_b200 import tosa_frontend  # noqa: E402
 # every fixture of tests/testdata/{tosa_ops,gen_ops} that the front end reads, with int8 tensors and at most
 # 1.3 M input + output elements (the larger and the int16 ones are left out)
 CASES = [
-    "tosa_ops/add-rank2", "tosa_ops/add-single-rescale", "tosa_ops/add", "tosa_ops/add_dense_8x8x24xi8",
-    "tosa_ops/add_strided_7x7x24xi8", "tosa_ops/avgpool2d", "tosa_ops/conv_5x5_odd_frame_stride2",
+    "tosa_ops/add", "tosa_ops/add-rank2", "tosa_ops/add-single-rescale", "tosa_ops/add_dense_8x8x24xi8",
+    "tosa_ops/add_strided_7x7x24xi8", "tosa_ops/avgpool2d", "tosa_ops/clamp-int8", "tosa_ops/conv_5x5_odd_frame_stride2",
     "tosa_ops/disable-avgpool", "tosa_ops/disable-resize-nearest-neighbor-10x10x512xi8",
     "tosa_ops/disable-resize-nearest-neighbor-20x20x256xi8", "tosa_ops/disable-sub",
     "tosa_ops/dw_21x21_odd_frame_stride2", "tosa_ops/dw_4x4_stride2", "tosa_ops/dw_peeling",
-    "tosa_ops/efficientnet-sigmoid-rescale-mul", "tosa_ops/maxpool-seg-tile-1", "tosa_ops/maxpool-seg-tile",
+    "tosa_ops/efficientnet-sigmoid-rescale-mul", "tosa_ops/identity-4x16x16", "tosa_ops/identity-56-i8",
+    "tosa_ops/identity-64-i8", "tosa_ops/matmul-in-int8-out-int32", "tosa_ops/matmul-in-int8-out-int32-1",
+    "tosa_ops/matmul-in-int8-out-int32-2", "tosa_ops/matmul-in-int8-out-int32-3",
+    "tosa_ops/matmul-in-int8-out-int32-noalign", "tosa_ops/maxpool-seg-tile", "tosa_ops/maxpool-seg-tile-1",
     "tosa_ops/maxpool1d_i8_stride4_k4x1_256x16x32", "tosa_ops/maxpool2d-stride1-k3x3-32x32x4",
     "tosa_ops/maxpool2d-stride2-k2x2-32x32x4", "tosa_ops/maxpool2d-stride2-k2x2-8x8x1",
     "tosa_ops/maxpool2d-stride2-k2x2-8x8x32", "tosa_ops/maxpool2d-stride2-k2x2-8x8x4",
@@ -72,6 +75,11 @@ def numpy_replay(g, inputs):
                            a["clamp_max"], a_lshift=a["i0"], b_lshift=a["i1"])
         elif k == "table":
             y = onp.table(x, op.consts["table"].data)
+        elif k == "rescale":
+            y = onp.rescale(x, op.consts["multiplier"].data, op.consts["shift"].data, a["in0_zp"], a["out_zp"], a["clamp_min"],
+                            a["clamp_max"], bool(a["double_round"]), a["requant_mode"])
+        elif k == "matmul_i32":
+            y = onp.matmul_i32(x, vals[op.inputs[1].id], a["in0_zp"], a["weight_zp"])
         elif k == "resize_nn2x":
             y = onp.resize_nn2x(x)
         elif k == "reshape":

@@ -34,7 +34,8 @@ def run_graph(graph, inputs, keep_all=False):
             y = oc.fully_connected(x, op.consts["weights"].data, op.consts["bias"].data, _rq(op),
                                    input_zp=a["in0_zp"], weight_zp=a["weight_zp"])
         elif k == "matmul_i32":
-            y = oc.matmul_i32(x, op.consts["weights"].data, a["in0_zp"], a["weight_zp"])
+            rhs = op.consts["weights"].data if "weights" in op.consts else vals[op.inputs[1].id]
+            y = oc.matmul_i32(x, rhs, a["in0_zp"], a["weight_zp"])
         elif k == "maxpool":
             y = oc.maxpool(x, (a["kh"], a["kw"]), (a["stride_h"], a["stride_w"]),
                            (a["pad_t"], a["pad_b"], a["pad_l"], a["pad_r"]), a["pad_value"])

@@ -527,10 +527,11 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
     }
     if (op.kind == TB200_OP_RESHAPE) {
       // a view: shares the storage (and the lifetime) of what it reshapes
-      if (op.in0 < 0 || op.out0 < 0 || tensors[op.out0].kind != TB200_TENSOR_ACTIVATION ||
-          tensors[op.in0].kind == TB200_TENSOR_CONSTANT)
-        return b.fail(TB200_INVALID_ARGUMENT, "op %d: reshape wants a non-constant input and an intermediate result", i);
-      root[op.out0] = root[op.in0];
+      if (op.in0 < 0 || op.out0 < 0 || tensors[op.in0].kind == TB200_TENSOR_CONSTANT ||
+          (tensors[op.out0].kind != TB200_TENSOR_ACTIVATION && tensors[op.out0].kind != TB200_TENSOR_OUTPUT))
+        return b.fail(TB200_INVALID_ARGUMENT, "op %d: reshape wants a non-constant input and a writable result", i);
+      // a reshape that produces a graph output cannot alias (the output has its own binding): it copies
+      if (tensors[op.out0].kind == TB200_TENSOR_ACTIVATION) root[op.out0] = root[op.in0];
     }
   }
   auto bytes_of = [&](int id) {
@@ -922,6 +923,23 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         break;
       }
       case TB200_OP_MATMUL_I32: {
+        if (op.weights < 0 && op.in1 >= 0) {
+          // both operands are runtime tensors (the form of the reference's tosa.matmul fixtures)
+          if (!b.act_i8(op.in0, 2) || !b.act_i8(op.in1, 2) || !b.valid_id(op.out0) || tensors[op.out0].dtype != TB200_I32 ||
+              tensors[op.out0].rank != 2)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul wants int8 [M,K] x int8 [K,N] -> int32 [M,N]", i);
+          const int M = tensors[op.in0].shape[0], K = tensors[op.in0].shape[1], N = tensors[op.in1].shape[1];
+          if (tensors[op.in1].shape[0] != K || tensors[op.out0].shape[0] != M || tensors[op.out0].shape[1] != N)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul shape mismatch", i);
+          Loc lx = loc(op.in0), lw = loc(op.in1), lo = loc(op.out0);
+          const int azp = op.in0_zp, bzp = op.weight_zp;
+          step.kernel_name = "matmul_i32";
+          step.launch = [=](const ExecContext& c) {
+            launch_matmul_i32((const int8_t*)lx.resolve(c), (const int8_t*)lw.resolve(c), (int32_t*)lo.resolve(c), M, K, N,
+                              azp, bzp, c.stream);
+          };
+          break;
+        }
         if (!b.act_i8(op.in0, 2) || !b.valid_id(op.weights) || tensors[op.weights].rank != 2 || !b.valid_id(op.out0) ||
             tensors[op.out0].dtype != TB200_I32 || tensors[op.out0].rank != 2)
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul wants int8 [M,K] x const int8 [K,N] -> int32 [M,N]", i);
@@ -1342,6 +1360,16 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
       case TB200_OP_RESHAPE: {
         if (bytes_of(op.in0) != bytes_of(op.out0) || tensors[op.in0].dtype != tensors[op.out0].dtype)
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: reshape changes the byte count", i);
+        if (tensors[op.out0].kind == TB200_TENSOR_OUTPUT) {
+          const size_t nbytes = bytes_of(op.in0);
+          Loc lx = loc(op.in0), lo = loc(op.out0);
+          step.kernel_name = "copy (reshape into an output)";
+          step.launch = [=](const ExecContext& c) {
+            const cudaError_t e = cudaMemcpyAsync(lo.resolve(c), lx.resolve(c), nbytes, cudaMemcpyDeviceToDevice, c.stream);
+            if (e != cudaSuccess && c.launch_error) *c.launch_error = e;
+          };
+          break;
+        }
         step.kernel_name = "view";
         step.launches = 0;
         step.launch = [](const ExecContext&) {};

@@ -196,7 +196,12 @@ class Graph:
                           requant_mode=requant_mode)
 
     def matmul_i32(self, a, b, *, a_zp=0, b_zp=0):
-        """raw torq_hl.matmul: a [M, K] int8, constant b [K, N] int8 -> int32."""
+        """raw torq_hl.matmul: a [M, K] int8 x b [K, N] int8 -> int32; b a constant array or, as in the
+        reference's tosa.matmul fixtures, a second runtime tensor."""
+        if isinstance(b, TensorRef):
+            if len(a.shape) != 2 or len(b.shape) != 2 or a.shape[1] != b.shape[0]:
+                raise ValueError("matmul wants [M, K] x [K, N]")
+            return self._emit("matmul_i32", [a, b], (a.shape[0], b.shape[1]), "i32", in0_zp=a_zp, weight_zp=b_zp)
         bw = np.asarray(b, np.int8)
         return self._emit("matmul_i32", [a], (a.shape[0], bw.shape[1]), "i32", consts={"weights": self.const(bw)},
                           in0_zp=a_zp, weight_zp=b_zp)

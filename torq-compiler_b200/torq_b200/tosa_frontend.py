@@ -285,8 +285,24 @@ def build_graph(text: str) -> Graph:
                 raise NotImplementedError("concat along a non-channel axis")
             one = (1 << 30, 30)
             env[op.result.name] = g.concat(env[a.name], env[b.name], a_zp=0, a_ms=one, b_zp=0, b_ms=one, out_zp=0)
+        elif n == "matmul":
+            a, b, azp, bzp = op.operands
+            if a.dtype != "i8" or b.dtype != "i8" or op.result.dtype != "i32" or len(a.shape) != 3 or a.shape[0] != 1:
+                raise NotImplementedError("tosa.matmul other than one batch of i8 x i8 -> i32")
+            y = g.matmul_i32(g.reshape(env[a.name], a.shape[1:]), g.reshape(env[b.name], b.shape[1:]), a_zp=_scalar(azp),
+                             b_zp=_scalar(bzp))
+            env[op.result.name] = g.reshape(y, op.result.shape)
         elif n == "clamp":
-            raise NotImplementedError("clamp that does not follow a rescale")
+            x = op.operands[0]
+            if x.dtype != "i8":
+                raise NotImplementedError("clamp that does not follow a rescale")
+            # on its own: the identity rescale (multiplier 2^30, shift 30 is exact) with the clamp range
+            env[op.result.name] = g.rescale(env[x.name], np.array([1 << 30], np.int32), np.array([30], np.int8), input_zp=0,
+                                            out_zp=0, clamp=(max(-128, int(op.attrs["min_val"])), min(127, int(op.attrs["max_val"]))),
+                                            double_round=False)
+        elif n == "identity":
+            x = op.operands[0]
+            env[op.result.name] = g.reshape(env[x.name], x.shape)
         else:
             raise NotImplementedError(f"tosa.{n}")
     for v in returned:
