@@ -167,6 +167,17 @@ def matmul_i32(a, b, a_zp=0, b_zp=0):
 
 
 def maxpool(x, kernel, stride, pad=(0, 0, 0, 0), pad_value=-128):
+    """int8, or int16 when x is an int16 array."""
+    if np.asarray(x).dtype == np.int16:
+        x = np.ascontiguousarray(x)
+        N, H, W, Cc = x.shape
+        OH = out_dim(H, kernel[0], stride[0], 1, pad[0], pad[1])
+        OW = out_dim(W, kernel[1], stride[1], 1, pad[2], pad[3])
+        out = np.empty((N, OH, OW, Cc), np.int16)
+        p16 = C.POINTER(C.c_int16)
+        lib().tq_maxpool_i16(x.ctypes.data_as(p16), N, H, W, Cc, kernel[0], kernel[1], stride[0], stride[1], pad[0],
+                             pad[2], int(pad_value), out.ctypes.data_as(p16), OH, OW)
+        return out
     x = _i8(x)
     N, H, W, Cc = x.shape
     OH = out_dim(H, kernel[0], stride[0], 1, pad[0], pad[1])

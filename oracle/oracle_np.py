@@ -145,11 +145,12 @@ def _windows(x, kernel, stride, pad, fill):
 
 
 def maxpool(x, kernel, stride, pad=(0, 0, 0, 0), pad_value=-128):
+    out_dtype = np.int16 if np.asarray(x).dtype == np.int16 else np.int8
     x = np.asarray(x, np.int64)
     out = None
     for win in _windows(x, kernel, stride, pad, pad_value):
         out = win.copy() if out is None else np.maximum(out, win)
-    return out.astype(np.int8)
+    return out.astype(out_dtype)
 
 
 def avgpool(x, kernel, stride, pad=(0, 0, 0, 0), input_zp=0, output_zp=0):

@@ -275,6 +275,34 @@ void tq_maxpool(const int8_t* x, int N, int H, int W, int C, int KH, int KW, int
   }
 }
 
+/* The same on int16 tensors (tests/testdata/tosa_ops/maxpool2d_i16_s2_k3x3_32x32x4.mlir,
+ * doc/user-manual/ops.md: MaxPool2D i16 -> i16). */
+void tq_maxpool_i16(const int16_t* x, int N, int H, int W, int C, int KH, int KW, int stride_h, int stride_w,
+                    int pad_t, int pad_l, int pad_value, int16_t* out, int OH, int OW) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int n = 0; n < N; n++) {
+    for (int oh = 0; oh < OH; oh++) {
+      for (int ow = 0; ow < OW; ow++) {
+        int16_t* o = out + (((size_t)n * OH + oh) * OW + ow) * C;
+        for (int c = 0; c < C; c++) {
+          int32_t best = -32768;
+          for (int kh = 0; kh < KH; kh++) {
+            int ih = oh * stride_h - pad_t + kh;
+            for (int kw = 0; kw < KW; kw++) {
+              int iw = ow * stride_w - pad_l + kw;
+              int32_t v = (ih < 0 || ih >= H || iw < 0 || iw >= W)
+                              ? pad_value
+                              : (int32_t)x[(((size_t)n * H + ih) * W + iw) * C + c];
+              if (v > best) best = v;
+            }
+          }
+          o[c] = (int16_t)best;
+        }
+      }
+    }
+  }
+}
+
 /* tosa.avg_pool2d {acc_type = i32} (tests/testdata/tosa_ops/avgpool2d.mlir);
  * count excludes padding, scale = reciprocal_scale(count), single rounding
  * (compiler/torq/Conversions/LinalgToTorqHL/PoolingPattern.cpp:263-355 for the

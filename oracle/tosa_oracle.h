@@ -58,6 +58,8 @@ void tq_matmul_i32(const int8_t* a, int M, int K, const int8_t* b, int N, int a_
 void tq_maxpool(const int8_t* x, int N, int H, int W, int C, int KH, int KW, int stride_h,
                 int stride_w, int pad_t, int pad_b, int pad_l, int pad_r, int pad_value, int8_t* out,
                 int OH, int OW);
+void tq_maxpool_i16(const int16_t* x, int N, int H, int W, int C, int KH, int KW, int stride_h, int stride_w,
+                    int pad_t, int pad_l, int pad_value, int16_t* out, int OH, int OW);
 void tq_avgpool(const int8_t* x, int N, int H, int W, int C, int KH, int KW, int stride_h,
                 int stride_w, int pad_t, int pad_b, int pad_l, int pad_r, int input_zp, int output_zp,
                 int8_t* out, int OH, int OW);

@@ -22,9 +22,10 @@ for p in (ROOT, os.path.join(ROOT, "torq-compiler_b200"), os.path.join(ROOT, "te
 from oracle import oracle_np as onp  # noqa: E402
 from oracle_exec import run_graph  # noqa: E402
 from torq_b200 import tosa_frontend  # noqa: E402
+from torq_b200.oplist import NP_DTYPE  # noqa: E402
 
-# every fixture of tests/testdata/{tosa_ops,gen_ops} that the front end reads, with int8 tensors and at most
-# 1.3 M input + output elements (the larger and the int16 ones are left out)
+# every fixture of tests/testdata/{tosa_ops,gen_ops} that the front end reads and every engine here runs, with at
+# most 1.3 M input + output elements (the larger ones are left out)
 CASES = [
     "tosa_ops/add", "tosa_ops/add-rank2", "tosa_ops/add-single-rescale", "tosa_ops/add_dense_8x8x24xi8",
     "tosa_ops/add_strided_7x7x24xi8", "tosa_ops/avgpool2d", "tosa_ops/clamp-int8", "tosa_ops/conv_5x5_odd_frame_stride2",
@@ -35,19 +36,21 @@ CASES = [
     "tosa_ops/identity-64-i8", "tosa_ops/matmul-in-int8-out-int32", "tosa_ops/matmul-in-int8-out-int32-1",
     "tosa_ops/matmul-in-int8-out-int32-2", "tosa_ops/matmul-in-int8-out-int32-3",
     "tosa_ops/matmul-in-int8-out-int32-noalign", "tosa_ops/maxpool-seg-tile", "tosa_ops/maxpool-seg-tile-1",
-    "tosa_ops/maxpool1d_i8_stride4_k4x1_256x16x32", "tosa_ops/maxpool2d-stride1-k3x3-32x32x4",
+    "tosa_ops/maxpool1d_i16_stride4_k4x1_256x16x32", "tosa_ops/maxpool1d_i8_stride4_k4x1_256x16x32",
+    "tosa_ops/maxpool2d-stride1-k3x3-32x32x4", "tosa_ops/maxpool2d-stride1-k3x3-32x32x4-i16",
     "tosa_ops/maxpool2d-stride2-k2x2-32x32x4", "tosa_ops/maxpool2d-stride2-k2x2-8x8x1",
     "tosa_ops/maxpool2d-stride2-k2x2-8x8x32", "tosa_ops/maxpool2d-stride2-k2x2-8x8x4",
     "tosa_ops/maxpool2d-stride2-k3x3-32x32x4", "tosa_ops/maxpool2d-stride2-k3x3-8x8x4",
     "tosa_ops/maxpool2d-stride2-k3x3-bottom-right-pad", "tosa_ops/maxpool2d-stride2-k3x3-pad-112x112x64",
     "tosa_ops/maxpool2d-stride2-k3x3-pad-32x32x64", "tosa_ops/maxpool2d-stride2-k3x3-top-left-pad",
+    "tosa_ops/maxpool2d_i16_s2_k3x3_32x32x4", "tosa_ops/maxpool2d_i16_s2_k7x7_10x10x4",
     "tosa_ops/maxpool2d_int8_batch1_2x2_stride2x2_32x16x4", "tosa_ops/maxpool_f5_15x20x384", "tosa_ops/maxpool_f5_8x8x4",
     "tosa_ops/maxpool_f5_s2_10x10x4", "tosa_ops/maxpool_f5_s2_top_left_pad_10x10x4", "tosa_ops/maxpool_f7_8x8x4",
     "tosa_ops/maxpool_f7_s2_10x10x4", "tosa_ops/maxpool_f7_s2_top_left_pad_10x10x4",
-    "tosa_ops/maxpool_int8_batch1_3x3_stride1x1_16x4", "tosa_ops/reshape", "tosa_ops/resize-31x31x33xi8",
-    "tosa_ops/resize-4x4x32xi8", "tosa_ops/resize-8x8x32xi8", "tosa_ops/sub-1input-56x56x24xi8",
-    "tosa_ops/sub-1input-strided-7x7x24xi8", "tosa_ops/yolov8_block_mul_rescale", "gen_ops/add_8x8", "gen_ops/add_8x8_i8",
-    "gen_ops/conv2d_64x64", "gen_ops/conv2d_8x8", "gen_ops/maxpool2d_8x8",
+    "tosa_ops/maxpool_int16_batch1_3x3_stride1x1_16x4", "tosa_ops/maxpool_int8_batch1_3x3_stride1x1_16x4",
+    "tosa_ops/reshape", "tosa_ops/resize-31x31x33xi8", "tosa_ops/resize-4x4x32xi8", "tosa_ops/resize-8x8x32xi8",
+    "tosa_ops/sub-1input-56x56x24xi8", "tosa_ops/sub-1input-strided-7x7x24xi8", "tosa_ops/yolov8_block_mul_rescale",
+    "gen_ops/add_8x8", "gen_ops/add_8x8_i8", "gen_ops/conv2d_64x64", "gen_ops/conv2d_8x8", "gen_ops/maxpool2d_8x8",
 ]
 
 
@@ -95,7 +98,7 @@ def main(ref_root):
     for case in CASES:
         g = tosa_frontend.build_graph_from_file(os.path.join(ref_root, "tests", "testdata", case + ".mlir"))
         rng = np.random.default_rng(1234)
-        inputs = [rng.integers(-40, 40, t.shape).astype(np.int8) for t in g.inputs]
+        inputs = [rng.integers(-40, 40, t.shape, dtype=NP_DTYPE[t.dtype]) for t in g.inputs]
         want_c = run_graph(g, inputs)
         want_np = numpy_replay(g, inputs)
         for a, b in zip(want_c, want_np):

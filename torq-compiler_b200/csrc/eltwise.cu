@@ -65,6 +65,54 @@ __global__ void __launch_bounds__(kThreads) maxpool_kernel(PoolArgs a) {
   }
 }
 
+// The same on int16 tensors (the reference's MaxPool2D i16 -> i16): 8 channels per thread, or 1.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) maxpool_i16_kernel(PoolArgs a) {
+  const int16_t* x = reinterpret_cast<const int16_t*>(a.x);
+  int16_t* out = reinterpret_cast<int16_t*>(a.out);
+  const int groups = a.C / VEC;
+  const long long total = (long long)a.N * a.OH * a.OW * groups;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int g = (int)(idx % groups);
+    const long long p = idx / groups;
+    const int ow = (int)(p % a.OW);
+    const long long t = p / a.OW;
+    const int oh = (int)(t % a.OH);
+    const int n = (int)(t / a.OH);
+    const int16_t* xin = x + (size_t)n * a.H * a.W * a.C + g * VEC;
+    if (VEC == 8) {
+      uint32_t best[4] = {0x80008000u, 0x80008000u, 0x80008000u, 0x80008000u};
+      const uint32_t padw = (uint32_t)(a.pad_value & 0xffff) * 0x00010001u;
+      for (int kh = 0; kh < a.KH; kh++) {
+        const int ih = oh * a.stride_h - a.pad_t + kh;
+        for (int kw = 0; kw < a.KW; kw++) {
+          const int iw = ow * a.stride_w - a.pad_l + kw;
+          uint4 v;
+          if (ih < 0 || ih >= a.H || iw < 0 || iw >= a.W) v = make_uint4(padw, padw, padw, padw);
+          else v = *reinterpret_cast<const uint4*>(xin + ((size_t)ih * a.W + iw) * a.C);
+          best[0] = __vmaxs2(best[0], v.x);
+          best[1] = __vmaxs2(best[1], v.y);
+          best[2] = __vmaxs2(best[2], v.z);
+          best[3] = __vmaxs2(best[3], v.w);
+        }
+      }
+      *reinterpret_cast<uint4*>(out + (size_t)p * a.C + g * 8) = make_uint4(best[0], best[1], best[2], best[3]);
+    } else {
+      int best = -32768;
+      for (int kh = 0; kh < a.KH; kh++) {
+        const int ih = oh * a.stride_h - a.pad_t + kh;
+        for (int kw = 0; kw < a.KW; kw++) {
+          const int iw = ow * a.stride_w - a.pad_l + kw;
+          const int v = (ih < 0 || ih >= a.H || iw < 0 || iw >= a.W) ? a.pad_value : (int)xin[((size_t)ih * a.W + iw) * a.C];
+          best = max(best, v);
+        }
+      }
+      out[(size_t)p * a.C + g] = (int16_t)best;
+    }
+  }
+}
+
 // reciprocal_scale of the TOSA spec (compiler/torq/Conversions/TosaToTorqHL/Patterns.cpp:796-805)
 __device__ __forceinline__ void reciprocal_scale(uint32_t count, int32_t& mult, int32_t& shift) {
   int k = 32 - __clz((int)(count - 1));
@@ -258,6 +306,11 @@ __global__ void __launch_bounds__(kThreads) resize_nn2x_kernel(const int8_t* __r
 }  // namespace
 
 void launch_maxpool(const PoolArgs& a, cudaStream_t stream) {
+  if (a.elem16) {
+    if ((a.C & 7) == 0) maxpool_i16_kernel<8><<<grid_for((long long)a.N * a.OH * a.OW * (a.C / 8)), kThreads, 0, stream>>>(a);
+    else maxpool_i16_kernel<1><<<grid_for((long long)a.N * a.OH * a.OW * a.C), kThreads, 0, stream>>>(a);
+    return;
+  }
   if ((a.C & 15) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C / 16);
     maxpool_kernel<16><<<grid_for(total), kThreads, 0, stream>>>(a);

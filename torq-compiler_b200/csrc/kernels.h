@@ -54,6 +54,7 @@ struct PoolArgs {
   int N, H, W, C, KH, KW, OH, OW, stride_h, stride_w, pad_t, pad_l;
   int pad_value;            // max pool
   int input_zp, output_zp;  // avg pool
+  int elem16;               // max pool on int16 tensors (x and out then point to int16 data)
 };
 void launch_maxpool(const PoolArgs& a, cudaStream_t stream);
 void launch_avgpool(const PoolArgs& a, cudaStream_t stream);

@@ -960,10 +960,16 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
       }
       case TB200_OP_MAXPOOL:
       case TB200_OP_AVGPOOL: {
-        if (!b.act_i8(op.in0, 4) || !b.act_i8(op.out0, 4))
-          return b.fail(TB200_INVALID_ARGUMENT, "op %d: pooling wants int8 NHWC input/output", i);
+        // max pool also takes int16 tensors (the reference's MaxPool2D i16 -> i16)
+        const bool pool16 = op.kind == TB200_OP_MAXPOOL && b.valid_id(op.in0) && b.valid_id(op.out0) &&
+                            tensors[op.in0].dtype == TB200_I16 && tensors[op.out0].dtype == TB200_I16 &&
+                            tensors[op.in0].rank == 4 && tensors[op.out0].rank == 4 &&
+                            tensors[op.in0].kind != TB200_TENSOR_CONSTANT;
+        if (!pool16 && (!b.act_i8(op.in0, 4) || !b.act_i8(op.out0, 4)))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: pooling wants int8 NHWC input/output (max pool: or int16)", i);
         const auto& x = tensors[op.in0]; const auto& o = tensors[op.out0];
         PoolArgs a{};
+        a.elem16 = pool16 ? 1 : 0;
         a.N = x.shape[0]; a.H = x.shape[1]; a.W = x.shape[2]; a.C = x.shape[3];
         a.KH = op.kh; a.KW = op.kw; a.stride_h = op.stride_h; a.stride_w = op.stride_w;
         a.pad_t = op.pad_t; a.pad_l = op.pad_l;

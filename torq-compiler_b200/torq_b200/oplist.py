@@ -210,7 +210,7 @@ class Graph:
         N, H, W, Cc = x.shape
         OH = _out_dim(H, kernel[0], stride[0], 1, pad[0], pad[1])
         OW = _out_dim(W, kernel[1], stride[1], 1, pad[2], pad[3])
-        return self._emit("maxpool", [x], (N, OH, OW, Cc), kh=kernel[0], kw=kernel[1], stride_h=stride[0],
+        return self._emit("maxpool", [x], (N, OH, OW, Cc), x.dtype if x.dtype == "i16" else "i8", kh=kernel[0], kw=kernel[1], stride_h=stride[0],
                           stride_w=stride[1], pad_t=pad[0], pad_b=pad[1], pad_l=pad[2], pad_r=pad[3],
                           pad_value=pad_value)
 

@@ -260,7 +260,7 @@ def build_graph(text: str) -> Graph:
         elif n == "max_pool2d":
             src = op.operands[0]
             pad = list(op.attrs["pad"])
-            pad_value = -128
+            pad_value = -32768 if src.dtype == "i16" else -128  # the type's lowest value: padding never wins
             if src.op is not None and src.op.name == "pad":
                 amounts = src.op.operands[1].const.reshape(-1)  # [n0,n1,h0,h1,w0,w1,c0,c1]
                 pad = [pad[0] + int(amounts[2]), pad[1] + int(amounts[3]), pad[2] + int(amounts[4]), pad[3] + int(amounts[5])]
