@@ -167,15 +167,24 @@ __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
 }
 
 // ---- add / sub / mul in TOSA form (ElementWiseBinaryPattern.cpp:385-570, MulPattern.cpp:229-238) ----
-__device__ __forceinline__ int binary_one(const BinaryArgs& a, int av, int bv) {
-  const bool dr = a.double_round != 0;
-  int ra = apply_scale_32((av - a.a_zp) * (1 << a.a_lshift), a.a_mult, a.a_shift, dr);
-  int rb = apply_scale_32((bv - a.b_zp) * (1 << a.b_lshift), a.b_mult, a.b_shift, dr);
-  int v = a.kind == 0 ? ra + rb : a.kind == 1 ? ra - rb : ra * rb;
-  return requant(v, a.out_mult, a.out_shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
-}
-
+// An int8 operand takes 256 values, so its input-side rescale is a 256-entry table (filled here by the
+// same apply_scale_32, one entry per thread): per element two shared-memory loads replace two 64-bit
+// multiply-shift sequences; the output rescale stays arithmetic.
 __global__ void __launch_bounds__(kThreads) binary_kernel(BinaryArgs a) {
+  __shared__ int ta[256], tb[256];  // indexed by the raw byte
+  {
+    const bool dr = a.double_round != 0;
+    const int v = (int)(int8_t)threadIdx.x;
+    ta[threadIdx.x] = apply_scale_32((v - a.a_zp) * (1 << a.a_lshift), a.a_mult, a.a_shift, dr);
+    tb[threadIdx.x] = apply_scale_32((v - a.b_zp) * (1 << a.b_lshift), a.b_mult, a.b_shift, dr);
+  }
+  __syncthreads();
+  const bool dr = a.double_round != 0;
+  auto one = [&](uint32_t xa, uint32_t xb) {
+    const int ra = ta[xa], rb = tb[xb];
+    const int v = a.kind == 0 ? ra + rb : a.kind == 1 ? ra - rb : ra * rb;
+    return requant(v, a.out_mult, a.out_shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
+  };
   const long long nvec = a.n >> 4;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -189,13 +198,13 @@ __global__ void __launch_bounds__(kThreads) binary_kernel(BinaryArgs a) {
     for (int w = 0; w < 4; w++) {
       int q[4];
 #pragma unroll
-      for (int j = 0; j < 4; j++) q[j] = binary_one(a, sx8(wa[w], j), sx8(wb[w], j));
+      for (int j = 0; j < 4; j++) q[j] = one((wa[w] >> (8 * j)) & 0xff, (wb[w] >> (8 * j)) & 0xff);
       wo[w] = pack4(q[0], q[1], q[2], q[3]);
     }
     reinterpret_cast<uint4*>(a.out)[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
   }
   for (long long i = (nvec << 4) + tid; i < a.n; i += stride)
-    a.out[i] = (int8_t)binary_one(a, a.a[i], a.b[i]);
+    a.out[i] = (int8_t)one((uint8_t)a.a[i], (uint8_t)a.b[i]);
 }
 
 // ---- table: out = table[x + 128] (ExtractPattern.cpp:97-135) ----
@@ -266,6 +275,36 @@ __global__ void __launch_bounds__(kThreads) rescale_vec16_kernel(RescaleArgs a) 
       v = make_uint4(w[0], w[1], w[2], w[3]);
     }
     *reinterpret_cast<uint4*>(a.out + (size_t)r * a.out_row_stride + a.out_col_offset + c16 * 16) = v;
+  }
+}
+
+// Per-tensor constants: the rescale is a function of the input byte alone, so it runs as a 256-entry table
+// in shared memory (one entry per thread, filled by the same requant), 16 channels per thread.
+__global__ void __launch_bounds__(kThreads) rescale_lut_vec16_kernel(RescaleArgs a) {
+  __shared__ uint8_t lut[256];  // indexed by the raw byte
+  {
+    const ChanParams cp = a.chan[0];
+    lut[threadIdx.x] = (uint8_t)requant((int)(int8_t)threadIdx.x - a.input_zp, cp.mult, cp.shift, a.double_round != 0,
+                                        a.out_zp, a.clamp_min, a.clamp_max);
+  }
+  __syncthreads();
+  const int cv = a.C >> 4;
+  const long long total = a.rows * cv;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int c16 = (int)(idx % cv);
+    const long long r = idx / cv;
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)r * a.C) + c16);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      uint32_t o = 0;
+#pragma unroll
+      for (int j = 0; j < 4; j++) o |= (uint32_t)lut[(w[k] >> (8 * j)) & 0xff] << (8 * j);
+      w[k] = o;
+    }
+    *reinterpret_cast<uint4*>(a.out + (size_t)r * a.out_row_stride + a.out_col_offset + c16 * 16) =
+        make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -342,6 +381,7 @@ void launch_rescale(const RescaleArgs& a, cudaStream_t stream) {
   const bool vec = (a.C & 15) == 0 && (a.out_row_stride & 15) == 0 && (a.out_col_offset & 15) == 0 &&
                    ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0;
   if (vec && a.identity) rescale_vec16_kernel<true><<<grid_for(a.rows * (a.C >> 4)), kThreads, 0, stream>>>(a);
+  else if (vec && !a.per_channel) rescale_lut_vec16_kernel<<<grid_for(a.rows * (a.C >> 4)), kThreads, 0, stream>>>(a);
   else if (vec) rescale_vec16_kernel<false><<<grid_for(a.rows * (a.C >> 4)), kThreads, 0, stream>>>(a);
   else rescale_kernel<<<grid_for(a.rows * a.C), kThreads, 0, stream>>>(a);
 }
