@@ -176,6 +176,131 @@ __global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
   }
 }
 
+// The same arithmetic with the block's input tile loaded cooperatively (C % 16 == 0): a block is
+// CG channel groups (4 channels each, CG*4 a multiple of 16) x SW column strips = 128 threads and owns
+// kRows output rows x SW*TW output columns x CG*4 channels. Its input tile [NR rows][IWT columns][CG*4
+// bytes] is fetched with 16-byte cp.async by whichever thread the piece falls to (about one piece per
+// thread and row instead of four 4-byte copies per thread and row, and no 64-bit index arithmetic per
+// thread); pieces outside the image are stored as the input zero point. After one barrier every thread
+// reads its own 4 channels of its 3 or 4 columns from the tile and proceeds exactly as dw3x3_kernel.
+template <int STRIDE, bool HI33>
+__global__ void __launch_bounds__(128, 4) dw3x3_tile_kernel(DwArgs a, int cg_log2, int cchunks) {
+  constexpr int TW = STRIDE == 1 ? 2 : 1;
+  constexpr int NCOL = STRIDE == 1 ? 4 : 3;
+  constexpr int NR = (kRows - 1) * STRIDE + 3;
+  extern __shared__ __align__(16) uint32_t tile[];  // [NR][IWT][CG] words
+  const int CG = 1 << cg_log2, SW = 128 >> cg_log2;
+  const int IWT = (SW * TW - 1) * STRIDE + 3;  // input columns of the tile
+  const int gl = threadIdx.x & (CG - 1), strip = threadIdx.x >> cg_log2;
+  const int wt = blockIdx.x / cchunks, cc = blockIdx.x - wt * cchunks;
+  const int rb = blockIdx.y, n = blockIdx.z;
+  const int c0 = cc << (cg_log2 + 2);        // first channel of the block
+  const int ow_tile = wt * SW * TW;          // first output column of the block
+  const int iw_tile = ow_tile * STRIDE - a.pad_l;
+  const int oh_begin = rb * kRows;
+  const int n_rows = min(a.OH - oh_begin, kRows);
+  const int nr_live = (n_rows - 1) * STRIDE + 3;
+  const int ih_base = oh_begin * STRIDE - a.pad_t;
+  const uint32_t zpw = (uint32_t)(a.input_zp & 0xff) * 0x01010101u;
+
+  // ---- cooperative tile load: pieces of 16 bytes, index q = column * (CG/4) + piece ----
+  {
+    const int p16_log2 = cg_log2 - 2;  // 16-byte pieces per column
+    const int per_row = IWT << p16_log2;
+    const uint32_t tile_addr = (uint32_t)__cvta_generic_to_shared(tile);
+    const int8_t* img = a.x + (size_t)n * a.H * a.W * a.C + c0;
+    for (int q = threadIdx.x; q < per_row; q += 128) {
+      const int col = q >> p16_log2, piece = q & ((1 << p16_log2) - 1);
+      const int iw = iw_tile + col;
+      const bool col_in = iw >= 0 && iw < a.W;
+      const int8_t* src = img + (size_t)iw * a.C + piece * 16;
+#pragma unroll
+      for (int i = 0; i < NR; i++) {
+        const int ih = ih_base + i;
+        const uint32_t dst = tile_addr + (uint32_t)((i * per_row + q) * 16);
+        if (i < nr_live) {
+          if (col_in && ih >= 0 && ih < a.H) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + (size_t)ih * a.W * a.C) : "memory");
+          } else {
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(zpw) : "memory");
+          }
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  const int c = c0 + gl * 4;
+  const int ow0 = ow_tile + strip * TW;
+  const bool live = ow0 < a.OW;
+  // weights and per-channel constants of this thread's 4 channels (requested before the wait)
+  uint32_t wq[3][TW][4];
+#pragma unroll
+  for (int kh = 0; kh < 3; kh++)
+#pragma unroll
+    for (int v = 0; v < TW; v++) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(a.wq + ((size_t)(kh * TW + v) * a.C + c)));
+      wq[kh][v][0] = w.x; wq[kh][v][1] = w.y; wq[kh][v][2] = w.z; wq[kh][v][3] = w.w;
+    }
+  int4 cq[4];
+  ChanParams cp[HI33 ? 1 : 4];
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const ChanParams t = a.chan[c + k];
+    if (HI33) cq[k] = make_int4(t.bias, t.mult, (int)(t.rnd >> 32), t.hshift);
+    else cp[k] = t;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  if (!live) return;
+
+  const uint32_t lo2 = (uint32_t)(a.clamp_min & 0xffff) * 0x10001u;
+  const uint32_t hi2 = (uint32_t)(a.clamp_max & 0xffff) * 0x10001u;
+  const int col_words = CG;                       // words per tile column
+  const int row_words_t = IWT << cg_log2;         // words per tile row
+  const uint32_t* mine = tile + strip * TW * STRIDE * col_words + gl;
+  auto take_row = [&](int i, uint32_t (&t)[4]) {
+    const uint32_t* r = mine + i * row_words_t;
+    const uint32_t p0 = r[0], p1 = r[col_words], p2 = r[2 * col_words];
+    const uint32_t p3 = NCOL == 4 ? r[3 * col_words] : zpw;
+    transpose4x4(p0, p1, p2, p3, t);
+  };
+  uint32_t* __restrict__ o32 = reinterpret_cast<uint32_t*>(a.out);
+  const int Cw = a.C >> 2;
+  uint32_t win[NR][4];
+  int out_off = ((n * a.OH + oh_begin) * a.OW + ow0) * Cw + (c >> 2);
+  const int out_row_words = a.OW * Cw;
+  const bool second = TW == 2 && ow0 + 1 < a.OW;
+#pragma unroll
+  for (int r = 0; r < kRows; r++) {
+    if (r < n_rows) {
+      if (r == 0) {
+        take_row(0, win[0]);
+        take_row(1, win[1]);
+        take_row(2, win[2]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < STRIDE; i++) take_row(STRIDE * r + 2 - i, win[STRIDE * r + 2 - i]);
+      }
+#pragma unroll
+      for (int v = 0; v < TW; v++) {
+        int q[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          int acc = HI33 ? cq[k].x : cp[k].bias;
+#pragma unroll
+          for (int kh = 0; kh < 3; kh++) acc = __dp4a((int)win[STRIDE * r + kh][k], (int)wq[kh][v][k], acc);
+          if (HI33) q[k] = scale_hi33(acc, cq[k].y, cq[k].z, cq[k].w, a.rnd_lo, a.dmul) + a.out_zp;
+          else q[k] = scale_cp<false>(acc, cp[k]) + a.out_zp;
+        }
+        const uint32_t word = clamp_pack4(q[0], q[1], q[2], q[3], lo2, hi2);
+        if (v == 0 || second) o32[(uint32_t)(out_off + v * Cw)] = word;
+      }
+      out_off += out_row_words;
+    }
+  }
+}
+
 // One thread per (output pixel, VEC consecutive channels); taps outside the image are skipped.
 template <int VEC>
 __global__ void __launch_bounds__(256) depthwise_generic_kernel(DwArgs a) {
@@ -261,8 +386,42 @@ size_t depthwise3x3_pack(const int8_t* w, int C, int stride, uint32_t* out) {
   return (size_t)3 * variants * C;
 }
 
+// Block shape of dw3x3_tile_kernel: the widest channel chunk (16..128 channels) that divides C among those
+// that waste the fewest threads on the columns beyond OW.
+static bool dw_tile_shape(const DwArgs& a, int& cg_log2, int& tiles, int& cchunks) {
+  if ((a.C & 15) != 0 || a.N > 65535 || getenv("TB200_DW_NO_TILE")) return false;
+  const int tw = a.stride_h == 1 ? 2 : 1;
+  const int owt = (a.OW + tw - 1) / tw;
+  int best = -1, best_threads = 0;
+  for (int l = 2; l <= 5; l++) {
+    const int ch = 4 << l;
+    if (a.C % ch) continue;
+    const int sw = 128 >> l;
+    const int threads = ((owt + sw - 1) / sw) * sw;
+    if (best < 0 || threads <= best_threads) { best = l; best_threads = threads; }
+  }
+  if (best < 0) return false;
+  cg_log2 = best;
+  tiles = best_threads / (128 >> best);
+  cchunks = a.C / (4 << best);
+  return true;
+}
+
 void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
-  if (a.wq && depthwise3x3_supported(a)) {
+  int cg_log2 = 0, tiles = 0, cchunks = 0;
+  if (a.wq && depthwise3x3_supported(a) && dw_tile_shape(a, cg_log2, tiles, cchunks)) {
+    const int S = a.stride_h, tw = S == 1 ? 2 : 1, sw = 128 >> cg_log2;
+    const int nr = (kRows - 1) * S + 3, iwt = (sw * tw - 1) * S + 3;
+    const size_t smem = (size_t)nr * iwt * (4 << cg_log2);
+    const dim3 grid((unsigned)(tiles * cchunks), (unsigned)((a.OH + kRows - 1) / kRows), (unsigned)a.N);
+    if (S == 1) {
+      if (a.hi33) dw3x3_tile_kernel<1, true><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      else dw3x3_tile_kernel<1, false><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+    } else {
+      if (a.hi33) dw3x3_tile_kernel<2, true><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      else dw3x3_tile_kernel<2, false><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+    }
+  } else if (a.wq && depthwise3x3_supported(a)) {
     const int tw = a.stride_h == 1 ? 2 : 1;
     long long total = (long long)a.N * ((a.OH + kRows - 1) / kRows) * ((a.OW + tw - 1) / tw) * (a.C >> 2);
     unsigned blocks = (unsigned)((total + 127) / 128);
