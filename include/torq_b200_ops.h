@@ -59,7 +59,7 @@ enum tb200_op_kind {
   TB200_OP_CONV2D = 1,        /* torq_hl.conv2d            */
   TB200_OP_DEPTHWISE = 2,     /* torq_hl.depthwise_conv2d  */
   TB200_OP_FC = 3,            /* torq_hl.fully_connected / torq_hl.matmul with constant B */
-  TB200_OP_MAXPOOL = 4,       /* torq_hl.maxpool2d         */
+  TB200_OP_MAXPOOL = 4,       /* torq_hl.maxpool2d: int8, or int16 in and out (doc/user-manual/ops.md MaxPool2D i16) */
   TB200_OP_AVGPOOL = 5,       /* torq_hl.avg_pool2d (any window; whole-frame = global) */
   TB200_OP_ADD = 6,           /* torq_hl.add : rescale,rescale -> add -> rescale */
   TB200_OP_MUL = 7,           /* torq_hl.mul : rescale,rescale -> mul -> rescale */
@@ -68,8 +68,9 @@ enum tb200_op_kind {
   TB200_OP_RESIZE_NN2X = 10,  /* torq_hl.resize_nearest_neighbor, 2x replicate */
   TB200_OP_CONCAT = 11,       /* channel concat of in0,in1 with per-input rescale */
   TB200_OP_SUB = 12,          /* as ADD with in1 negated after its rescale */
-  TB200_OP_MATMUL_I32 = 13,   /* raw torq_hl.matmul: int8 x int8 -> int32, no rescale */
-  TB200_OP_RESHAPE = 14,      /* tosa.reshape: out0 is a view of in0's bytes, no launch */
+  TB200_OP_MATMUL_I32 = 13,   /* raw torq_hl.matmul: int8 [M,K] x int8 [K,N] -> int32, no rescale; B is the constant
+                               * `weights`, or (weights = -1) the runtime tensor in1 as in tosa.matmul */
+  TB200_OP_RESHAPE = 14,      /* tosa.reshape / tosa.identity: out0 is a view of in0 (no launch); a device copy when out0 is a graph output */
   /* decoder (bf16 activations, int8 per-output-channel weights) */
   TB200_OP_EMBED = 32,        /* gather rows of an int8 table, dequant, * f0 */
   TB200_OP_RMSNORM = 33,      /* y = x * rsqrt(mean(x^2) + f0) * (1 + w)  (bf16) */
