@@ -123,6 +123,15 @@ DW_CASES = [
     ((1, 23, 23, 16), (21, 21), 1, (2, 2), (10, 10, 10, 10), 6),  # dw_21x21_odd_frame_stride2 class
     ((2, 28, 28, 192), (3, 3), 1, (1, 1), (1, 1, 1, 1), -7),
     ((2, 28, 28, 144), (3, 3), 1, (2, 2), (0, 1, 0, 1), 10),
+    # C % 16 == 0: the cooperative-tile 3x3 kernel in each of its block shapes (16..128 channels per block),
+    # widths below, at and beyond a tile, odd frames, stride 2 with either padding style
+    ((3, 14, 14, 64), (3, 3), 1, (1, 1), (1, 1, 1, 1), 5),
+    ((2, 7, 7, 960), (3, 3), 1, (1, 1), (1, 1, 1, 1), -3),
+    ((1, 15, 17, 48), (3, 3), 1, (2, 2), (0, 1, 0, 1), 9),
+    ((2, 112, 112, 32), (3, 3), 1, (1, 1), (1, 1, 1, 1), -128),
+    ((1, 33, 130, 16), (3, 3), 1, (1, 1), (1, 1, 1, 1), 127),
+    ((1, 33, 131, 128), (3, 3), 1, (2, 2), (1, 1, 1, 1), 0),
+    ((1, 10, 300, 32), (3, 3), 1, (2, 2), (0, 1, 0, 1), -20),
 ]
 
 

@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
 // thread); pieces outside the image are stored as the input zero point. After one barrier every thread
 // reads its own 4 channels of its 3 or 4 columns from the tile and proceeds exactly as dw3x3_kernel.
 template <int STRIDE, bool HI33>
-__global__ void __launch_bounds__(128, 4) dw3x3_tile_kernel(DwArgs a, int cg_log2, int cchunks) {
+__global__ void __launch_bounds__(128, STRIDE == 1 ? 6 : 8) dw3x3_tile_kernel(DwArgs a, int cg_log2, int cchunks) {
   constexpr int TW = STRIDE == 1 ? 2 : 1;
   constexpr int NCOL = STRIDE == 1 ? 4 : 3;
   constexpr int NR = (kRows - 1) * STRIDE + 3;
@@ -274,6 +274,9 @@ __global__ void __launch_bounds__(128, 4) dw3x3_tile_kernel(DwArgs a, int cg_log
 #pragma unroll
   for (int r = 0; r < kRows; r++) {
     if (r < n_rows) {
+      // keep the tile reads of later rows behind this row's arithmetic: hoisted to the top they cost
+      // 30-40 registers and two resident blocks per SM
+      asm volatile("" ::: "memory");
       if (r == 0) {
         take_row(0, win[0]);
         take_row(1, win[1]);
