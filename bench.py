@@ -406,8 +406,8 @@ def main():
     achieved = d["bytes"] / (d["ms"] * 1e-3) / 1e9
     # DRAM bytes per launch from the ncu launch list of this workload (profiles/mobilenetv2_b256_launch_list.md:
     # dram__bytes_read.sum + dram__bytes_write.sum over a step, divided by the class's launches), batch 256 only
-    ncu_traffic_per_launch = {"gemm_i8_tcgen05": (1745290752 + 860791808) / 70,
-                              "depthwise3x3_dp4a": (934547456 + 260309248 + 983089408 + 142840064) / 34}
+    ncu_traffic_per_launch = {"gemm_i8_tcgen05": (1743967232 + 855919360) / 70,
+                              "depthwise3x3_dp4a": (934375936 + 271396864 + 982956032 + 149633024) / 34}
     traffic = ncu_traffic_per_launch.get(dom) if B == 256 else None
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "peak_source": f"of {peak_kind}",
