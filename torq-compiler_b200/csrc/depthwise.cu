@@ -15,6 +15,8 @@
 //    -izp * sum(w) sits folded in ChanParams::bias.
 //  * depthwise_generic_kernel: any window, stride, dilation, channel multiplier and
 //    weight zero point; taps outside the image are skipped.
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace tb200 {
@@ -392,7 +394,8 @@ size_t depthwise3x3_pack(const int8_t* w, int C, int stride, uint32_t* out) {
 // Block shape of dw3x3_tile_kernel: the widest channel chunk (16..128 channels) that divides C among those
 // that waste the fewest threads on the columns beyond OW.
 static bool dw_tile_shape(const DwArgs& a, int& cg_log2, int& tiles, int& cchunks) {
-  if ((a.C & 15) != 0 || a.N > 65535 || getenv("TB200_DW_NO_TILE")) return false;
+  static const bool no_tile = getenv("TB200_DW_NO_TILE") != nullptr;  // A/B switch: the per-thread-copy kernel
+  if ((a.C & 15) != 0 || a.N > 65535 || no_tile) return false;
   const int tw = a.stride_h == 1 ? 2 : 1;
   const int owt = (a.OW + tw - 1) / tw;
   int best = -1, best_threads = 0;
