@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(128) embed_kernel(const int32_t* __restrict__ 
 }
 
 // y = [res +] bf16( x * rsqrt(mean(x^2) + eps) * (1 + w) )   (sum of res and the rounded norm is rounded again)
-__global__ void __launch_bounds__(512) rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res,
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res,
                                                       const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
                                                       int H, float eps) {
   __shared__ float red[32];
@@ -100,7 +100,7 @@ __device__ __forceinline__ float operand_at(const uint16_t* __restrict__ x, cons
 // rmsnorm_kernel, its input optionally split-K partials, and optionally a second norm (no residual) of the
 // result in the same launch: out2 = bf16( out * rsqrt(mean(out^2) + eps2) * (1 + w2) ). One block per row,
 // the row kept in shared memory as fp32.
-__global__ void __launch_bounds__(512) rmsnorm_fused_kernel(const uint16_t* __restrict__ x, GemvPartials gp,
+__global__ void __launch_bounds__(1024) rmsnorm_fused_kernel(const uint16_t* __restrict__ x, GemvPartials gp,
                                                             const uint16_t* __restrict__ res,
                                                             const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
                                                             const uint16_t* __restrict__ w2, uint16_t* __restrict__ out2,
@@ -647,7 +647,7 @@ void launch_embed(const int32_t* tok, const int8_t* table, const uint16_t* scale
 
 void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, uint16_t* out, int rows, int H, float eps,
                     cudaStream_t stream) {
-  launch_k(rmsnorm_kernel, dim3(rows), dim3(512), 0, stream, x, res, w, out, H, eps);
+  launch_k(rmsnorm_kernel, dim3(rows), dim3(1024), 0, stream, x, res, w, out, H, eps);
 }
 
 // Batches of 5 and more with K a multiple of 64 take the tensor-core kernel (measured crossover with the
@@ -697,7 +697,7 @@ int gemv_w8_used_splits(int B, int N, int K, int splits) {
 void launch_rmsnorm_fused(const uint16_t* x, GemvPartials gp, const uint16_t* res, const uint16_t* w, uint16_t* out,
                           const uint16_t* w2, uint16_t* out2, int rows, int H, float eps, float eps2,
                           cudaStream_t stream) {
-  launch_k(rmsnorm_fused_kernel, dim3(rows), dim3(512), (size_t)H * sizeof(float), stream, x, gp, res, w, out, w2, out2, rows, H, eps, eps2);
+  launch_k(rmsnorm_fused_kernel, dim3(rows), dim3(1024), (size_t)H * sizeof(float), stream, x, gp, res, w, out, w2, out2, rows, H, eps, eps2);
 }
 
 void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, void* y, int y_f32, float* scratch, int B,
