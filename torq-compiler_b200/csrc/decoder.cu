@@ -671,7 +671,9 @@ int gemv_w8_splits(int B, int N, int K) {
     int splits = (int)((2 * 148 + row_blocks - 1) / row_blocks);
     const int max_splits = K / 128 > 0 ? K / 128 : 1;
     if (splits > max_splits) splits = max_splits;
-    if (splits > 16) splits = 16;
+    static int cap = -1;  // TB200_GEMV_MAX_SPLITS: upper bound on the K slices of the tensor-core kernel
+    if (cap < 0) { const char* e = getenv("TB200_GEMV_MAX_SPLITS"); cap = e && atoi(e) > 0 ? atoi(e) : 16; }
+    if (splits > cap) splits = cap;
     if (splits < 1) splits = 1;
     while (gemv_mma_slice(N, K, splits) > 2048) splits++;  // shared-memory bound on the x slice
     return splits;
