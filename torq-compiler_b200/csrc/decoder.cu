@@ -750,7 +750,12 @@ void launch_rope_kv(const uint16_t* qkv, const int32_t* pos, const uint16_t* qw,
                                                               theta, eps, gp);
 }
 
-int attn_decode_splits(int B) { return B >= 16 ? 16 : 32; }
+int attn_decode_splits(int B) {
+  static int forced = -1;  // TB200_ATTN_SPLITS: T slices of the split-T attention (1..64), else by batch
+  if (forced < 0) { const char* e = getenv("TB200_ATTN_SPLITS"); forced = e && atoi(e) > 0 && atoi(e) <= 64 ? atoi(e) : 0; }
+  if (forced) return forced;
+  return B >= 16 ? 16 : 32;
+}
 size_t attn_decode_scratch_bytes(int B, int n_q, int splits) {
   return (size_t)B * n_q * splits * (kAttnD + 2) * sizeof(float);
 }
