@@ -650,11 +650,11 @@ void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, u
   launch_k(rmsnorm_kernel, dim3(rows), dim3(1024), 0, stream, x, res, w, out, H, eps);
 }
 
-// Batches of 5 and more with K a multiple of 64 take the tensor-core kernel (measured crossover with the
+// Batches of 3 and more with K a multiple of 64 take the tensor-core kernel (measured crossover with the
 // CUDA-core kernel and with the fused step; TB200_GEMV_MMA_MIN_B moves it): K slices of a multiple of 64.
 static bool gemv_use_mma(int B, int K) {
   static int min_b = -1;
-  if (min_b < 0) { const char* e = getenv("TB200_GEMV_MMA_MIN_B"); min_b = e ? atoi(e) : 5; }
+  if (min_b < 0) { const char* e = getenv("TB200_GEMV_MMA_MIN_B"); min_b = e ? atoi(e) : 3; }
   return B >= min_b && (K % 64) == 0;
 }
 static int gemv_mma_slice(int N, int K, int splits) {

@@ -237,12 +237,13 @@ bool try_fuse_decode_step(Builder& b, Plan& plan, size_t& scratch_need) {
   const int Tlen = T[first_rope.out1].shape[1];
   const float eps = lo[0]->f0, attn_scale = lo[3]->f0;
   if (!decode_step_supported(B, H, n_q, n_kv, D, I, V)) return false;
-  // Measured on the 1B shape: the fused step wins up to 4 sequences (1.70 ms against 1.88 ms at 4); from 5 on
-  // the per-op path with the tensor-core GEMV is faster (1.90 ms against 2.83 ms at 8). Tensor-parallel
-  // shards exist only in fused form. TB200_DECODE_FUSED_MAX_B moves the threshold.
+  // Measured on the 1B shape: the fused step wins at 1 and 2 sequences (1.17 ms against 1.43 ms at 2); from 3 on
+  // the per-op path with the tensor-core GEMV is faster (1.44 ms against 1.57 ms at 3, 1.44 against 1.70 at 4,
+  // 1.47 against 2.83 at 8). Tensor-parallel shards exist only in fused form. TB200_DECODE_FUSED_MAX_B moves
+  // the threshold.
   {
     const char* e = getenv("TB200_DECODE_FUSED_MAX_B");
-    const int max_b = e ? atoi(e) : 4;
+    const int max_b = e ? atoi(e) : 2;
     if (!tp_graph && B > max_b) return false;
   }
   int dev = 0, sms = 0;
