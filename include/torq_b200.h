@@ -170,13 +170,30 @@ int tb200_executable_connect_peers(tb200_executable_t* executable, const tb200_c
  * allocation may bring. Its partial sums live in a fixed 4 MiB array inside the library
  * (held by every GPU that loads the library until the process exits), so
  * slices * B * N must be <= 1,048,576 or the call returns TB200_OUT_OF_RANGE (and says so on
- * stderr). All pointers are device pointers on GPU `cuda_ordinal`; `stream` is a
+ * stderr); so does a slice count that leaves K slices longer than 2048 values at B >= 3. x and W
+ * must be 16-byte aligned, y and scale aligned to their element (else TB200_INVALID_ARGUMENT).
+ * The calling thread's current device is left as it was. All pointers are device pointers on GPU `cuda_ordinal`; `stream` is a
  * cudaStream_t or NULL; splits <= 0 picks the slice count. The first call on a device
  * resolves the array's device address and should be made before any stream capture. Calls
  * share the array: calls that may overlap on the GPU race with each other and must be ordered
  * by the caller. Nothing is allocated or freed by this call. */
 int tb200_gemv_w8_noalloc(int cuda_ordinal, void* stream, const void* x_bf16, const void* w_i8,
                           const void* scale_bf16, void* y, int y_is_f32, int B, int N, int K, int splits);
+
+/* Self-test of the bounded-wait contract (the reference bounds its wait for the NPU by polling with a
+ * timeout, runtime/torq_hw/src/TorqHw.cpp:172-186; here every wait INSIDE a kernel is bounded). Queues a
+ * one-block kernel that waits, with the kernels' own wait helper and a limit of `limit_ms` (1..1000), on a
+ * barrier that nothing completes. The kernel gives up, records code 99 and returns; the next tb200_wait()
+ * therefore answers TB200_ABORTED once, and the device stays usable. */
+int tb200_device_probe_bounded_wait(tb200_device_t* device, uint32_t limit_ms);
+
+/* No counterpart in the reference (a measurement aid). Runs, on every SM of GPU `cuda_ordinal`,
+ * `rounds` batches of 128 back-to-back tcgen05.mma kind::i8 instructions (M 128, N 256, K 32) on
+ * operands resident in shared memory with TMEM accumulators - no memory traffic - and returns the
+ * rate in tera-ops per second (1 multiply-accumulate = 2 ops) and the launch time. This is the
+ * measured ceiling of the int8 tensor pipe that the contraction kernels' fractions are quoted
+ * against. Synchronous; allocates a status word and a stream for its own use and frees them. */
+int tb200_measure_i8_mma_peak(int cuda_ordinal, int rounds, double* tera_ops_per_s, double* ms);
 
 #ifdef __cplusplus
 }

@@ -54,18 +54,25 @@ def test_embed_and_rmsnorm(device):
                                           # batches above 8: the tensor-core kernel (K % 64 == 0), ragged N, K splits
                                           (9, 1152, 1536, 0), (32, 6912, 1152, 0), (17, 256, 200, 0), (32, 1152, 4100, 1),
                                           (12, 1024, 77, 2), (24, 2048, 130, 5),
-                                          (16, 1040, 64, 0)])  # K % 64 != 0: stays on the CUDA-core kernel
-def test_gemv_w8(device, B, K, N, splits):
+                                          (16, 1040, 64, 0),   # K % 64 != 0: stays on the CUDA-core kernel
+                                          (4, 2048, 320, 4)])  # the shape the allocation-free entry point is checked on
+@pytest.mark.parametrize("f32", [False, True])
+def test_gemv_w8(device, B, K, N, splits, f32):
     rng = np.random.default_rng(1234 + K + N)
     x = to_bf16(rng.normal(0, 1, (B, K)).astype(np.float32))
     w = rng.integers(-127, 128, (N, K), dtype=np.int8)
     s = to_bf16(rng.uniform(0.5, 1.5, N).astype(np.float32) / (73.0 * np.sqrt(K)))
     g = Graph()
-    y = g.gemv_w8(g.input((B, K), "bf16"), w, s, splits=splits)
+    y = g.gemv_w8(g.input((B, K), "bf16"), w, s, splits=splits, out_dtype="f32" if f32 else "bf16")
     g.output(y)
     got = run_graph_gpu(device, g, [x])[0]
-    want = _bf((torch.from_numpy(from_bf16(x)) @ torch.from_numpy(w.astype(np.float32)).T) * torch.from_numpy(from_bf16(s)))
-    _close(got, want, floor=0.05)
+    want = (torch.from_numpy(from_bf16(x)) @ torch.from_numpy(w.astype(np.float32)).T) * torch.from_numpy(from_bf16(s))
+    if f32:  # fp32 results: relative to the largest magnitude, the summation order differs from torch's
+        assert got.dtype == np.float32
+        err = np.abs(got - want.numpy()).max() / np.abs(want.numpy()).max()
+        assert err <= 1e-5, err
+        return
+    _close(got, _bf(want), floor=0.05)
 
 
 def test_rope_kv_and_attention(device):

@@ -53,4 +53,43 @@ def test_noalloc_gemv_rejects_what_does_not_fit(device):
     assert lib.tb200_gemv_w8_noalloc(device.ordinal, None, p, p, p, p, 0, 32, 4096, 8192, 16) == 11  # OUT_OF_RANGE
     assert lib.tb200_gemv_w8_noalloc(device.ordinal, None, p, p, p, p, 0, 1, 64, 24, 1) == 3           # K % 16 != 0
     assert lib.tb200_gemv_w8_noalloc(device.ordinal, None, None, p, p, p, 0, 1, 64, 32, 1) == 3        # NULL input
+    # pointers the kernels' 16-byte loads cannot take are refused on the host, nothing is launched
+    off = C.c_void_p(d.pointer + 8)
+    assert lib.tb200_gemv_w8_noalloc(device.ordinal, None, off, p, p, p, 0, 1, 64, 32, 1) == 3         # x misaligned
+    assert lib.tb200_gemv_w8_noalloc(device.ordinal, None, p, off, p, p, 0, 1, 64, 32, 1) == 3         # W misaligned
+    assert lib.tb200_gemv_w8_noalloc(device.ordinal, None, p, p, C.c_void_p(d.pointer + 1), p, 0, 1, 64, 32, 1) == 3
+    assert lib.tb200_gemv_w8_noalloc(device.ordinal, None, p, p, p, C.c_void_p(d.pointer + 2), 1, 1, 64, 32, 1) == 3  # fp32 y
+    # one slice of K = 4096 at batch 32 is more than the tensor-core kernel can stage in shared memory
+    assert lib.tb200_gemv_w8_noalloc(device.ordinal, None, p, p, p, p, 0, 32, 8, 4096, 1) == 11
     d.free()
+
+
+def test_noalloc_gemv_on_a_second_device_and_current_device_kept():
+    """The scratch array's address and the kernels' attributes are per device; the caller's current device
+    is left as it was."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from torq_b200.runtime import Device
+    B, K, N = 32, 1152, 256   # batch 32: the tensor-core kernel with more than 48 KB of shared memory
+    rng = np.random.default_rng(7)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    scale = to_bf16((rng.uniform(0.5, 1.5, N) / (73.0 * np.sqrt(K))).astype(np.float32))
+    x = to_bf16(rng.normal(0, 1, (B, K)).astype(np.float32))
+    results = []
+    for ordinal in (0, 1):
+        dev = Device(ordinal)
+        torch.cuda.set_device(0)
+        d_x, d_w, d_s, d_y = dev.alloc(x.nbytes), dev.alloc(w.nbytes), dev.alloc(scale.nbytes), dev.alloc(B * N * 2)
+        d_x.upload(x), d_w.upload(w), d_s.upload(scale)
+        dev.wait()
+        torch.cuda.set_device(0)
+        st = dev._lib.tb200_gemv_w8_noalloc(ordinal, C.c_void_p(dev.stream), C.c_void_p(d_x.pointer), C.c_void_p(d_w.pointer),
+                                            C.c_void_p(d_s.pointer), C.c_void_p(d_y.pointer), 0, B, N, K, 0)
+        assert st == 0
+        assert torch.cuda.current_device() == 0
+        results.append(d_y.download((B, N), np.uint16))
+        for b in (d_x, d_w, d_s, d_y):
+            b.free()
+        dev.close()
+    assert (results[0] == results[1]).all() and len(np.unique(results[0])) > 8

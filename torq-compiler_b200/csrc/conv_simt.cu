@@ -373,10 +373,10 @@ void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
     } else if (taps == 1) {
       conv2d_c16_kernel<1><<<blocks, 128, smem, stream>>>(a);
     } else {
-      static bool attr = false;
-      if (!attr) {
+      static std::atomic<unsigned long long> attr{0};  // function attributes are per device
+      if (first_use_on_device(attr)) {
         cudaFuncSetAttribute(conv2d_c16_kernel<25>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 25 * 16);
-        attr = true;
+        mark_used_on_device(attr);
       }
       conv2d_c16_kernel<25><<<blocks, 128, smem, stream>>>(a);
     }

@@ -54,7 +54,9 @@ constexpr int kLongSeg = 2304;                // long rows: bytes of K per slot 
 constexpr int kLongStride = 2368;             // ... at this row distance (= 64 mod 128), 8 rows per slot
 constexpr int kPartFloats = kConsumerWarps * 128;
 constexpr int kD = 256;                       // head dim
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+// limit of every bounded wait of the kernel in ns, copied from the launch arguments by thread 0 before the
+// first block-wide barrier
+__shared__ unsigned long long s_wait_limit_ns;
 
 // status codes written to the device status word when a bounded wait gives up
 enum { kErrFull = 16, kErrEmpty = 17, kErrGrid = 18, kErrPartFull = 19, kErrPartEmpty = 20 };
@@ -109,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     for (int i = 0; i < 256; i++)
       if (mbar_try_wait(bar, parity)) return true;
     if (*(volatile int*)status != 0) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (globaltimer_ns() - t0 > s_wait_limit_ns) {
       atomicCAS(status, 0, code);
       return false;
     }
@@ -154,7 +156,7 @@ __device__ __forceinline__ float wait_tagged(const uint32_t* p, uint32_t tag, in
       w = ld_relaxed_u32(p);
       if ((w >> 16) == tag) return __uint_as_float(w << 16);
     }
-    if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > s_wait_limit_ns) {
       atomicCAS(status, 0, (int)kErrGrid);
       ok = false;
       return 0.f;
@@ -173,7 +175,7 @@ __device__ __forceinline__ uint4 wait_tagged4(const uint32_t* p, uint32_t tag, i
       w = ld_relaxed_v4(p);
       if (good(w)) return w;
     }
-    if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > s_wait_limit_ns) {
       atomicCAS(status, 0, (int)kErrGrid);
       ok = false;
       return make_uint4(0, 0, 0, 0);
@@ -225,7 +227,7 @@ __device__ __forceinline__ bool grid_wait(const DecodeStepArgs& a, bool all_gpus
     for (int i = 0; i < 256; i++)
       if ((sys ? ld_acquire_sys(counter) : ld_acquire_gpu(counter)) >= target) return true;
     if (*(volatile int*)status != 0) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (globaltimer_ns() - t0 > s_wait_limit_ns) {
       atomicCAS(status, 0, (int)kErrGrid);
       return false;
     }
@@ -1110,6 +1112,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       mbar_init(sm.bars + 8 * (2 * nslots + 2 + i), 1);           // partial tile read
     }
     *gave_up = 0;
+    s_wait_limit_ns = a.wait_ns;
     // rows of each projection owned by this CTA (the same in every layer)
     int* rf = (int*)(smem_raw + sm.off_red + kRedRows);
     const int rows_of[5] = {(a.n_q + 2) * kD, a.H, a.I, a.H, a.V};
@@ -1474,6 +1477,7 @@ cudaError_t launch_decode_step(DecodeStepArgs a, cudaStream_t stream) {
   a.nslots = sp.nslots;
   a.xin_stride = sp.xin_stride;
   a.xin_bytes = sp.xin_bytes;
+  a.wait_ns = wait_limit_ns();
   void (*kernel)(const DecodeStepArgs) = a.B <= 1 ? decode_step_kernel<1>
                                          : a.B <= 2 ? decode_step_kernel<2>
                                          : a.B <= 4 ? decode_step_kernel<4>

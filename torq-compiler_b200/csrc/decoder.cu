@@ -689,6 +689,10 @@ int gemv_w8_splits(int B, int N, int K) {
   return splits;
 }
 
+bool gemv_w8_splits_fit(int B, int N, int K, int splits) {
+  return splits >= 1 && (!gemv_use_mma(B, K) || gemv_mma_slice(N, K, splits) <= 2048);
+}
+
 size_t gemv_w8_scratch_bytes(int B, int N, int splits) { return splits > 1 ? (size_t)splits * B * N * sizeof(float) : 0; }
 
 int gemv_w8_used_splits(int B, int N, int K, int splits) {
@@ -712,10 +716,11 @@ void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, v
     const size_t smem = (size_t)nt * 8 * xstride;
     dim3 grid((N + 127) / 128, used);
     auto run = [&](auto kernel) {
-      static bool attr_done[5] = {false, false, false, false, false};
-      if (!attr_done[nt]) {
+      // one flag per instantiation of this lambda (= per kernel); function attributes are per device
+      static std::atomic<unsigned long long> attr_done{0};
+      if (first_use_on_device(attr_done)) {
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        attr_done[nt] = true;
+        mark_used_on_device(attr_done);
       }
       launch_k(kernel, dim3(grid), dim3(256), smem, stream, x, W, scale, y, scratch, B, N, K, slice, y_f32);
     };
@@ -832,7 +837,18 @@ extern "C" int tb200_gemv_w8_noalloc(int cuda_ordinal, void* stream, const void*
   if (!x_bf16 || !w_i8 || !scale_bf16 || !y || B < 1 || B > 32 || N < 1 || K < 16 || (K % 16) != 0 ||
       cuda_ordinal < 0 || cuda_ordinal >= kMaxDevices)
     return 3;
+  // the kernels read x and W with 16-byte vector loads; the scales and y are accessed element by element
+  if (((uintptr_t)x_bf16 & 15) || ((uintptr_t)w_i8 & 15) || ((uintptr_t)y & (y_is_f32 ? 3 : 1)) || ((uintptr_t)scale_bf16 & 1)) {
+    fprintf(stderr, "tb200_gemv_w8_noalloc: x and W must be 16-byte aligned, y and the scales aligned to their element\n");
+    return 3;
+  }
   if (splits <= 0) splits = gemv_w8_splits(B, N, K);
+  if (!gemv_w8_splits_fit(B, N, K, splits)) {
+    fprintf(stderr,
+            "tb200_gemv_w8_noalloc: %d slices of K = %d leave a slice of the input too long for the tensor-core kernel's "
+            "shared memory (at most 2048 values per slice at batch >= 3); use more slices\n", splits, K);
+    return 11;
+  }
   if ((size_t)splits * (size_t)B * (size_t)N > kNoAllocScratchFloats) {
     fprintf(stderr,
             "tb200_gemv_w8_noalloc: %d slices x batch %d x %d columns = %zu partial sums exceed the fixed scratch of "
@@ -840,7 +856,14 @@ extern "C" int tb200_gemv_w8_noalloc(int cuda_ordinal, void* stream, const void*
             splits, B, N, (size_t)splits * B * N, (size_t)kNoAllocScratchFloats);
     return 11;
   }
-  if (cudaSetDevice(cuda_ordinal) != cudaSuccess) return 13;
+  // the caller's current device is put back before returning
+  int caller_device = -1;
+  if (cudaGetDevice(&caller_device) != cudaSuccess) return 13;
+  struct RestoreDevice {
+    int dev;
+    ~RestoreDevice() { if (dev >= 0) cudaSetDevice(dev); }
+  } restore{caller_device == cuda_ordinal ? -1 : caller_device};
+  if (caller_device != cuda_ordinal && cudaSetDevice(cuda_ordinal) != cudaSuccess) return 13;
   float* scratch = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_noalloc_mutex);
@@ -853,6 +876,7 @@ extern "C" int tb200_gemv_w8_noalloc(int cuda_ordinal, void* stream, const void*
     }
     scratch = g_noalloc_scratch_ptr[cuda_ordinal];
   }
+  (void)cudaGetLastError();  // an earlier, unrelated error of the host must not be reported as this call's
   launch_gemv_w8((const uint16_t*)x_bf16, (const int8_t*)w_i8, (const uint16_t*)scale_bf16, y, y_is_f32 ? 1 : 0, scratch,
                  B, N, K, splits, (cudaStream_t)stream);
   return cudaGetLastError() == cudaSuccess ? 0 : 13;

@@ -43,6 +43,7 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "tcgen05_ptx.cuh"
 
 namespace tb200 {
 
@@ -55,7 +56,6 @@ constexpr int kEpiWarps = 4 * kEpiGroups;
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kSmemBudget = 196 * 1024;          // dynamic shared memory the kernel may use
 constexpr int kResidentWeightBytes = 64 * 1024;  // weights up to this size stay in shared memory
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 struct GemmTcParams {
   const ChanParams* chan;
@@ -79,138 +79,9 @@ struct GemmTcParams {
   int tma_store;        // stage the output tile in shared memory and write it with one TMA store
   uint32_t staging_off; // byte offset of the staging buffers inside dynamic shared memory
   int* status;
+  unsigned long long wait_ns;  // limit of every mbarrier wait
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false (and a code in the status word) if the phase does not complete in time.
-// The clock is only consulted after a few thousand polls, so the common case costs one poll.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-#pragma unroll 1
-  for (int i = 0; i < 4096; i++)
-    if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 256; i++)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      if (*(volatile int*)status == 0) *(volatile int*)status = code;
-      return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0),
-               "r"(c1), "r"(src)
-               : "memory");
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(map), "r"(c0),
-               "r"(c1), "r"(c2), "r"(c3), "r"(src)
-               : "memory");
-}
-
-// K-major operand in shared memory, rows of row_bytes (= the swizzle width), 8-row groups
-// 8 * row_bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int row_bytes) {
-  const uint64_t layout = row_bytes == 128 ? 2 : row_bytes == 64 ? 4 : 6;  // SWIZZLE_128B / 64B / 32B
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;                          // leading byte offset (unused for these layouts)
-  d |= (uint64_t)((8 * row_bytes) >> 4) << 32;     // stride byte offset
-  d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
-  d |= layout << 61;
-  return d;
-}
-
-__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-// Issue a 32-column load without waiting; tmem_ld_wait32 completes it. The wait names the
-// destination registers as operands so that no use of them can be scheduled ahead of it.
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
-      "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait32(uint32_t (&v)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
-                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
-                 "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]),
-                 "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]),
-                 "+r"(v[30]), "+r"(v[31])
-               :
-               : "memory");
-}
 
 // HI33: every rescale shift of the op is >= 33, so the rounding constant's low word and the
 // negative-accumulator term are the same for all channels and a channel needs only
@@ -287,7 +158,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           iw0 = (tx << p.tw_log2) * p.cstride - p.pad_l;
         }
         for (int kb = 0; kb < p.k_blocks; kb++) {
-          if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1, p.status, 1))) break;
+          if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1, p.status, 1, p.wait_ns))) break;
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_ring + (uint32_t)s * stage_bytes;
           mbar_expect_tx(full, stage_bytes);
@@ -324,7 +195,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      if (p.w_resident) ok = mbar_wait(smem_u32(&bar_w), 0, p.status, 5);
+      if (p.w_resident) ok = mbar_wait(smem_u32(&bar_w), 0, p.status, 5, p.wait_ns);
       int n = blockIdx.x / p.m_tiles, m = blockIdx.x - n * p.m_tiles;
       int as = 0;
       uint32_t acc_phase = 0;
@@ -332,11 +203,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint64_t desc0_w = make_smem_desc(p.w_resident ? smem_w : smem_ring + a_stage_bytes, p.row_bytes);
       const uint32_t stage_units = stage_bytes >> 4, w_tile_units = w_tile_bytes >> 4;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        if (!(ok = mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2))) break;
+        if (!(ok = mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2, p.wait_ns))) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(as * p.acc_stride);
         for (int kb = 0; kb < p.k_blocks; kb++) {
-          if (!(ok = mbar_wait(smem_u32(&bar_full[s]), phase, p.status, 3))) break;
+          if (!(ok = mbar_wait(smem_u32(&bar_full[s]), phase, p.status, 3, p.wait_ns))) break;
           tc_fence_after();
           const int steps = (kb == p.k_blocks - 1) ? p.k_last_steps : steps_full;
           const uint64_t da = desc0_ring + (uint64_t)((uint32_t)s * stage_units);
@@ -395,7 +266,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         group_sync();
         loaded_n = n;
       }
-      if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[group]), acc_phase, p.status, 4);
+      if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[group]), acc_phase, p.status, 4, p.wait_ns);
       if (ok) {
         tc_fence_after();
         const int row = m * kBM + row_in_tile;
@@ -587,17 +458,6 @@ bool encode_conv_output(CUtensorMap* map, const void* base, int N, int OH, int O
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
 }  // namespace
 
 GemmTcGeometry gemm_tc_geometry(int N, int K) {
@@ -688,19 +548,20 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   p.acc_stages = kEpiGroups;  // BN <= 128, so 4 stages fit the 512 TMEM columns
   p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
+  p.wait_ns = wait_limit_ns();
   p.lut = a.lut;
   p.staging_off = (uint32_t)((p.w_resident ? w_bytes : 0) + (size_t)stages * stage_bytes);
   const size_t smem = 1024 + p.staging_off + staging_bytes;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static std::atomic<unsigned long long> attr_set{0};
+  if (first_use_on_device(attr_set)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return e;
-    attr_set = true;
+    mark_used_on_device(attr_set);
   }
   const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
   if (a.hi33) gemm_i8_tc_kernel<true, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   else gemm_i8_tc_kernel<false, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   return cudaGetLastError();
@@ -806,19 +667,20 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   p.acc_stages = kEpiGroups;
   p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
+  p.wait_ns = wait_limit_ns();
   p.lut = a.lut;
   p.staging_off = (uint32_t)((p.w_resident ? w_bytes : 0) + (size_t)stages * stage_bytes);
   const size_t smem = 1024 + p.staging_off + staging_bytes;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static std::atomic<unsigned long long> attr_set{0};
+  if (first_use_on_device(attr_set)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return e;
-    attr_set = true;
+    mark_used_on_device(attr_set);
   }
   const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
   if (a.hi33) gemm_i8_tc_kernel<true, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   else gemm_i8_tc_kernel<false, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   return cudaGetLastError();

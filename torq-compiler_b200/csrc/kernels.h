@@ -4,9 +4,21 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace tb200 {
+
+// ---- per-device facts (device_util.cu) ----
+int current_device();
+int current_sm_count();  // SMs of the current device
+// One-time set-up that is per device (function attributes): first_use_on_device is true until
+// mark_used_on_device has been called with the same flag while the same device was current.
+bool first_use_on_device(std::atomic<unsigned long long>& done);
+void mark_used_on_device(std::atomic<unsigned long long>& done);
+// Limit of every bounded wait inside the kernels, from TB200_WAIT_LIMIT_MS (default 2000 ms).
+unsigned long long wait_limit_ns();
 
 struct ConvArgs {
   const int8_t* x;        // NHWC
@@ -150,6 +162,8 @@ void launch_rmsnorm(const uint16_t* x, const uint16_t* res, const uint16_t* w, u
                     cudaStream_t stream);
 int gemv_w8_splits(int B, int N, int K);
 size_t gemv_w8_scratch_bytes(int B, int N, int splits);
+// false when a caller-chosen slice count leaves K slices the tensor-core kernel cannot stage in shared memory
+bool gemv_w8_splits_fit(int B, int N, int K, int splits);
 // y bf16, or fp32 when y_f32. finalize == false with more than one K slice in use leaves the per-slice
 // sums in scratch ([slice][B][N] fp32) for a consumer kernel that takes a GemvPartials.
 void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, void* y, int y_f32, float* scratch, int B,
@@ -220,6 +234,7 @@ struct DecodeStepArgs {
   int o_k, o_k_offset;  // K of the o projection and where its slice starts in the local attention output
   unsigned long long inbox_o_off, inbox_d_off;
   char* peer_scratch[8];
+  unsigned long long wait_ns;  // limit of every bounded wait inside the kernel (filled by the launcher)
 };
 bool decode_step_supported(int B, int H, int n_q, int n_kv, int D, int I, int V);
 // fills the scratch offsets and the slice count of `offsets`; returns the scratch size

@@ -1206,6 +1206,8 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         if (!b.add_raw_const(op.weights, (size_t)N * K, "weights", i, w_off)) return b.status;
         if (!b.add_raw_const(op.bias, (size_t)N * 2, "scales", i, s_off)) return b.status;
         const int splits = op.i0 > 0 ? op.i0 : gemv_w8_splits(B, N, K);
+        if (!gemv_w8_splits_fit(B, N, K, splits))
+          return b.fail(TB200_OUT_OF_RANGE, "op %d: %d K slices leave a slice longer than the tensor-core gemv_w8 can stage", i, splits);
         scratch_need = std::max(scratch_need, gemv_w8_scratch_bytes(B, N, splits));
         Loc lx = loc(op.in0), lo = loc(op.out0);
         const bool finalize = !defer_finalize[i];

@@ -6,6 +6,7 @@
 // every failure surfaces as a status.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
@@ -20,6 +21,7 @@
 #include "../../include/torq_b200_ops.h"
 #include "kernels.h"
 #include "plan.h"
+#include "tcgen05_ptx.cuh"
 
 using namespace tb200;
 
@@ -33,6 +35,7 @@ struct tb200_device {
   FILE* profile_csv = nullptr;
   uint64_t invocation_id = 0;
   int* status_word = nullptr;  // device word a kernel writes when one of its bounded waits expires
+  int* status_host = nullptr;  // pinned host copy of it, refreshed by a stream-ordered copy at the end of every dispatch
   std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
 };
 
@@ -117,11 +120,15 @@ extern "C" int tb200_device_create(int ordinal, tb200_device_t** out) {
     delete d;
     return TB200_INTERNAL;
   }
-  if (cudaMalloc(&d->status_word, sizeof(int)) != cudaSuccess || cudaMemset(d->status_word, 0, sizeof(int)) != cudaSuccess) {
+  if (cudaMalloc(&d->status_word, sizeof(int)) != cudaSuccess || cudaMemset(d->status_word, 0, sizeof(int)) != cudaSuccess ||
+      cudaHostAlloc((void**)&d->status_host, sizeof(int), cudaHostAllocDefault) != cudaSuccess) {
+    if (d->status_word) cudaFree(d->status_word);
+    cudaStreamDestroy(d->copy_stream);
     cudaStreamDestroy(d->stream);
     delete d;
     return TB200_RESOURCE_EXHAUSTED;
   }
+  *d->status_host = 0;
   *out = d;
   return TB200_OK;
 }
@@ -134,6 +141,7 @@ extern "C" int tb200_device_destroy(tb200_device_t* d) {
   cudaStreamDestroy(d->copy_stream);
   cudaStreamDestroy(d->stream);
   cudaFree(d->status_word);
+  cudaFreeHost(d->status_host);
   if (d->profile_csv) fclose(d->profile_csv);
   delete d;
   return TB200_OK;
@@ -176,6 +184,22 @@ extern "C" int tb200_device_set_profile_csv(tb200_device_t* d, const char* path)
 }
 
 // ------------------------------------------------------------------ buffers
+
+namespace {
+// With the host profiling log open, an explicit transfer is logged as a HOST_COPY event (the reference's
+// name for host-side copies, runtime/torq_hw/inc/TorqEventLog.h:42) outside any dispatch: the first call
+// (begin_us < 0) writes the _BEGIN row and returns its time, the second writes the _END row. The times are
+// those of the enqueue: the copy itself is asynchronous.
+long long profile_host_copy(tb200_device* d, long long begin_us) {
+  if (!d->profile_csv) return 0;
+  std::lock_guard<std::mutex> lock(d->submit_mutex);
+  if (!d->profile_csv) return 0;
+  const long long t = (long long)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - d->t0).count();
+  fprintf(d->profile_csv, "__HAL,%llu,-1,%lld,HOST_COPY_%s\n", (unsigned long long)d->invocation_id, begin_us < 0 ? t : std::max(t, begin_us),
+          begin_us < 0 ? "BEGIN" : "END");
+  return t;
+}
+}  // namespace
 
 extern "C" int tb200_buffer_alloc(tb200_device_t* d, uint64_t bytes, int memory_type, tb200_buffer_t** out) {
   if (!d || !out) return TB200_INVALID_ARGUMENT;
@@ -226,17 +250,21 @@ extern "C" int tb200_buffer_free(tb200_buffer_t* b) {
 
 extern "C" int tb200_buffer_upload(tb200_buffer_t* b, uint64_t offset, const void* host, uint64_t bytes) {
   if (!b || (!host && bytes)) return TB200_INVALID_ARGUMENT;
-  if (offset + bytes > b->bytes) return fail(b->dev, TB200_OUT_OF_RANGE, "upload beyond end of buffer");
+  if (offset > b->bytes || bytes > b->bytes - offset) return fail(b->dev, TB200_OUT_OF_RANGE, "upload beyond end of buffer");
   cudaSetDevice(b->dev->ordinal);
+  const long long t0 = profile_host_copy(b->dev, -1);
   CUDA_OK(b->dev, cudaMemcpyAsync((char*)b->ptr + offset, host, bytes, cudaMemcpyDefault, b->dev->stream));
+  profile_host_copy(b->dev, t0);
   return TB200_OK;
 }
 
 extern "C" int tb200_buffer_download(tb200_buffer_t* b, uint64_t offset, void* host, uint64_t bytes) {
   if (!b || (!host && bytes)) return TB200_INVALID_ARGUMENT;
-  if (offset + bytes > b->bytes) return fail(b->dev, TB200_OUT_OF_RANGE, "download beyond end of buffer");
+  if (offset > b->bytes || bytes > b->bytes - offset) return fail(b->dev, TB200_OUT_OF_RANGE, "download beyond end of buffer");
   cudaSetDevice(b->dev->ordinal);
+  const long long t0 = profile_host_copy(b->dev, -1);
   CUDA_OK(b->dev, cudaMemcpyAsync(host, (const char*)b->ptr + offset, bytes, cudaMemcpyDefault, b->dev->stream));
+  profile_host_copy(b->dev, t0);
   return TB200_OK;
 }
 
@@ -283,8 +311,11 @@ extern "C" int tb200_executable_create(tb200_device_t* d, const void* bytes, siz
   if (n_bytes < sizeof(tb200_ops_header_t)) return fail(d, TB200_INVALID_ARGUMENT, "blob shorter than its header");
   tb200_ops_header_t h;
   memcpy(&h, bytes, sizeof(h));
+  // a blob of another format: NOT_FOUND, as the reference's executable cache answers for a format it has
+  // no implementation for (runtime/driver/nop_executable_cache.cc:97-105)
   if (h.magic != TB200_OPS_MAGIC)
-    return fail(d, TB200_INVALID_ARGUMENT, "not a %s executable (bad magic)", TB200_OPS_FORMAT_STRING);
+    return fail(d, TB200_NOT_FOUND, "no executable implementation for this format: not a %s blob (bad magic)",
+                TB200_OPS_FORMAT_STRING);
   if (h.version != TB200_OPS_VERSION)
     return fail(d, TB200_UNAVAILABLE, "executable version %u is not compatible with runtime version %u",
                 h.version, TB200_OPS_VERSION);
@@ -495,7 +526,9 @@ int resolve_bindings(tb200_executable* ex, const tb200_binding_t* bindings, size
   io.resize(n);
   for (size_t i = 0; i < n; i++) {
     const auto& b = bindings[i];
-    if (!b.buffer || !b.buffer->ptr) return fail(d, TB200_INVALID_ARGUMENT, "binding %zu is NULL", i);
+    // runtime/driver/torq_command_buffer.c:488-495: a NULL binding is FAILED_PRECONDITION
+    if (!b.buffer || !b.buffer->ptr)
+      return fail(d, TB200_FAILED_PRECONDITION, "required binding %zu is NULL; all bindings must have a valid pointer", i);
     int32_t tid = i < ex->inputs.size() ? ex->inputs[i] : ex->outputs[i - ex->inputs.size()];
     uint64_t need = tensor_bytes(ex->tensors[tid]);
     if (b.offset > b.buffer->bytes) return fail(d, TB200_OUT_OF_RANGE, "binding %zu offset beyond buffer", i);
@@ -503,7 +536,9 @@ int resolve_bindings(tb200_executable* ex, const tb200_binding_t* bindings, size
     if (len > b.buffer->bytes - b.offset || len < need)
       return fail(d, TB200_OUT_OF_RANGE, "binding %zu: %llu bytes bound, tensor needs %llu", i,
                   (unsigned long long)len, (unsigned long long)need);
-    if (b.offset & 15) return fail(d, TB200_INVALID_ARGUMENT, "binding %zu offset must be 16-byte aligned", i);
+    // the kernels use 16-byte vector accesses and TMA on bound tensors: the bound ADDRESS must be aligned
+    if (((uintptr_t)b.buffer->ptr + b.offset) & 15)
+      return fail(d, TB200_INVALID_ARGUMENT, "binding %zu: address (buffer + offset) must be 16-byte aligned", i);
     if (b.buffer->memory_type != TB200_MEMORY_DEVICE_LOCAL)
       return fail(d, TB200_FAILED_PRECONDITION, "binding %zu is not device-local memory", i);
     io[i] = (char*)b.buffer->ptr + b.offset;
@@ -511,8 +546,17 @@ int resolve_bindings(tb200_executable* ex, const tb200_binding_t* bindings, size
   return TB200_OK;
 }
 
-double now_us(tb200_device* d) {
-  return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - d->t0).count();
+long long now_us(tb200_device* d) {
+  return (long long)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - d->t0).count();
+}
+
+// One row of the host profiling log. Columns, event names and the _BEGIN/_END suffixes are the
+// reference's (runtime/torq_hw/src/TorqEventLog.cpp:49,95-100; names runtime/torq_hw/inc/TorqEventLog.h:19-49);
+// timestamps are whole microseconds like its, so its readers (python/torq/debug_info.py:84) parse the file.
+void csv_row(tb200_device* d, const char* name, uint64_t invocation, long long action, long long t_us, const char* event,
+             bool begin) {
+  fprintf(d->profile_csv, "%s,%llu,%lld,%lld,%s_%s\n", name, (unsigned long long)invocation, action, t_us, event,
+          begin ? "BEGIN" : "END");
 }
 
 int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cudaEvent_t>* events) {
@@ -532,6 +576,8 @@ int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cud
     ex->plan.steps[i].launch(ctx);
   }
   if (events) cudaEventRecord((*events)[ex->plan.steps.size()], d->stream);
+  // the status word follows the kernels to pinned host memory, so the host wait reads it without a copy of its own
+  cudaMemcpyAsync(d->status_host, d->status_word, sizeof(int), cudaMemcpyDeviceToHost, d->stream);
   CUDA_OK(d, launch_error);
   CUDA_OK(d, cudaGetLastError());
   return TB200_OK;
@@ -586,6 +632,72 @@ int run_graph(tb200_executable* ex, const std::vector<void*>& io) {
   return TB200_OK;
 }
 
+// Host-side copies that bracket a profiled dispatch (tb200_invoke_host): run inside the
+// DISPATCH_SYNC_BINDINGS_IN / _OUT events, like the reference's binding syncs
+// (runtime/driver/TorqExecutable.cc:1071-1073,1088-1090).
+struct HostSync {
+  std::function<int()> copy_in, copy_out;
+};
+
+// The dispatch proper; the caller holds submit_mutex and has made the device current.
+int dispatch_locked(tb200_executable* ex, const std::vector<void*>& io, const HostSync* host) {
+  tb200_device* d = ex->dev;
+  if (!d->profile_csv) {
+    int st = TB200_OK;
+    if (host && host->copy_in && (st = host->copy_in()) != TB200_OK) return st;
+    st = use_graphs() && ex->plan.use_graph ? run_graph(ex, io) : run_plan(ex, io, nullptr);
+    if (st == TB200_OK && host && host->copy_out) st = host->copy_out();
+    return st;
+  }
+  // Profiled dispatch: synchronous, every op bracketed by CUDA events. An op's kernel plays the part of an
+  // NSS job of the reference: its NSS_START_BEGIN / NSS_START_END rows bracket the device execution.
+  const size_t ns = ex->plan.steps.size();
+  std::vector<cudaEvent_t> ev(ns + 1);
+  for (auto& e : ev) cudaEventCreate(&e);
+  const uint64_t inv = d->invocation_id++;
+  const char* name = "dispatch";
+  int st = TB200_OK;
+  csv_row(d, name, inv, -1, now_us(d), "DISPATCH", true);
+  csv_row(d, name, inv, -1, now_us(d), "DISPATCH_SYNC_BINDINGS_IN", true);
+  if (host && host->copy_in) st = host->copy_in();
+  if (st == TB200_OK && cudaStreamSynchronize(d->stream) != cudaSuccess) st = fail(d, TB200_INTERNAL, "stream failed before the dispatch");
+  csv_row(d, name, inv, -1, now_us(d), "DISPATCH_SYNC_BINDINGS_IN", false);
+  if (st == TB200_OK) {
+    const long long t_begin = now_us(d);
+    csv_row(d, name, inv, -1, t_begin, "DISPATCH_EXECUTE_ACTIONS", true);
+    st = run_plan(ex, io, &ev);
+    if (st == TB200_OK && cudaStreamSynchronize(d->stream) != cudaSuccess) st = fail(d, TB200_INTERNAL, "stream failed in the dispatch");
+    long long t_last = t_begin;
+    if (st == TB200_OK) {
+      // device times of the ops, placed after the host time at which the launches began
+      double acc_us = 0.0;
+      for (size_t i = 0; i < ns; i++) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+        const long long b = t_begin + (long long)(acc_us + 0.5);
+        acc_us += (double)ms * 1e3;
+        const long long e = t_begin + (long long)(acc_us + 0.5);
+        if (ex->plan.steps[i].launches == 0) continue;  // views and ops fused into a neighbour launch nothing
+        csv_row(d, ex->plan.steps[i].kernel_name, inv, (long long)i, b, "NSS_START", true);
+        csv_row(d, ex->plan.steps[i].kernel_name, inv, (long long)i, e, "NSS_START", false);
+        t_last = e;
+      }
+    }
+    const long long t_end = std::max(now_us(d), t_last);
+    csv_row(d, name, inv, -1, t_end, "DISPATCH_EXECUTE_ACTIONS", false);
+    csv_row(d, name, inv, -1, t_end, "DISPATCH_SYNC_BINDINGS_OUT", true);
+    if (st == TB200_OK && host && host->copy_out) {
+      st = host->copy_out();
+      if (st == TB200_OK && cudaStreamSynchronize(d->stream) != cudaSuccess) st = fail(d, TB200_INTERNAL, "stream failed after the dispatch");
+    }
+    csv_row(d, name, inv, -1, std::max(now_us(d), t_end), "DISPATCH_SYNC_BINDINGS_OUT", false);
+  }
+  csv_row(d, name, inv, -1, std::max(now_us(d), (long long)0), "DISPATCH", false);
+  fflush(d->profile_csv);
+  for (auto& e : ev) cudaEventDestroy(e);
+  return st;
+}
+
 }  // namespace
 
 extern "C" int tb200_dispatch(tb200_executable_t* ex, const tb200_binding_t* bindings, size_t n) {
@@ -596,33 +708,7 @@ extern "C" int tb200_dispatch(tb200_executable_t* ex, const tb200_binding_t* bin
   std::vector<void*> io;
   int st = resolve_bindings(ex, bindings, n, io);
   if (st != TB200_OK) return st;
-  if (!d->profile_csv) return use_graphs() && ex->plan.use_graph ? run_graph(ex, io) : run_plan(ex, io, nullptr);
-
-  // profiled dispatch: bracket every op with events and write the reference's CSV schema
-  size_t ns = ex->plan.steps.size();
-  std::vector<cudaEvent_t> ev(ns + 1);
-  for (auto& e : ev) cudaEventCreate(&e);
-  uint64_t inv = d->invocation_id++;
-  double t_begin = now_us(d);
-  fprintf(d->profile_csv, "dispatch,%llu,-1,%.3f,DISPATCH_BEGIN\n", (unsigned long long)inv, t_begin);
-  st = run_plan(ex, io, &ev);
-  if (st == TB200_OK) {
-    cudaStreamSynchronize(d->stream);
-    float acc_ms = 0.f;
-    for (size_t i = 0; i < ns; i++) {
-      float ms = 0.f;
-      cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
-      fprintf(d->profile_csv, "%s,%llu,%zu,%.3f,OP_BEGIN\n", ex->plan.steps[i].kernel_name,
-              (unsigned long long)inv, i, t_begin + acc_ms * 1e3);
-      acc_ms += ms;
-      fprintf(d->profile_csv, "%s,%llu,%zu,%.3f,OP_END\n", ex->plan.steps[i].kernel_name,
-              (unsigned long long)inv, i, t_begin + acc_ms * 1e3);
-    }
-    fprintf(d->profile_csv, "dispatch,%llu,-1,%.3f,DISPATCH_END\n", (unsigned long long)inv, now_us(d));
-    fflush(d->profile_csv);
-  }
-  for (auto& e : ev) cudaEventDestroy(e);
-  return st;
+  return dispatch_locked(ex, io, nullptr);
 }
 
 extern "C" int tb200_wait(tb200_device_t* d, uint64_t timeout_ns) {
@@ -632,12 +718,12 @@ extern "C" int tb200_wait(tb200_device_t* d, uint64_t timeout_ns) {
   for (;;) {
     cudaError_t e = cudaStreamQuery(d->stream);
     if (e == cudaSuccess) {
-      // the stream drained: did a kernel give up on one of its bounded waits?
-      int code = 0;
-      if (cudaMemcpy(&code, d->status_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
-        return fail(d, TB200_INTERNAL, "cannot read the device status word");
+      // The stream drained: did a kernel give up on one of its bounded waits? Every dispatch ends with a
+      // stream-ordered copy of the device status word to pinned host memory, so this is a plain read.
+      const int code = *(volatile int*)d->status_host;
       if (code != 0) {
-        cudaMemset(d->status_word, 0, sizeof(int));
+        *(volatile int*)d->status_host = 0;
+        cudaMemsetAsync(d->status_word, 0, sizeof(int), d->stream);
         return fail(d, TB200_ABORTED, "a kernel's bounded wait expired (code %d); results of this dispatch are invalid", code);
       }
       return TB200_OK;
@@ -648,55 +734,105 @@ extern "C" int tb200_wait(tb200_device_t* d, uint64_t timeout_ns) {
   }
 }
 
+namespace {
+// Frees whatever a failed set-up of the host-call staging left behind, so the next call starts over.
+void drop_staging(tb200_executable* ex) {
+  for (int s = 0; s < 2; s++) {
+    for (auto* b : ex->staging_in[s]) tb200_buffer_free(b);
+    for (auto* b : ex->staging_out[s]) tb200_buffer_free(b);
+    ex->staging_in[s].clear();
+    ex->staging_out[s].clear();
+    if (ex->ev_uploaded[s]) cudaEventDestroy(ex->ev_uploaded[s]);
+    if (ex->ev_released[s]) cudaEventDestroy(ex->ev_released[s]);
+    ex->ev_uploaded[s] = ex->ev_released[s] = nullptr;
+  }
+}
+}  // namespace
+
 extern "C" int tb200_invoke_host_async(tb200_executable_t* ex, const void* const* host_inputs,
                                        void* const* host_outputs) {
   if (!ex || (!host_inputs && !ex->inputs.empty()) || (!host_outputs && !ex->outputs.empty()))
     return TB200_INVALID_ARGUMENT;
   tb200_device* d = ex->dev;
+  std::lock_guard<std::mutex> lock(d->submit_mutex);
   cudaSetDevice(d->ordinal);
   const size_t ni = ex->inputs.size(), no = ex->outputs.size();
-  if (!ex->ev_uploaded[0]) {
-    for (int s = 0; s < 2; s++) {
-      for (size_t i = 0; i < ni; i++) {
+  for (size_t i = 0; i < ni; i++)
+    if (!host_inputs[i]) return fail(d, TB200_FAILED_PRECONDITION, "host input %zu is NULL; all bindings must have a valid pointer", i);
+  for (size_t i = 0; i < no; i++)
+    if (!host_outputs[i]) return fail(d, TB200_FAILED_PRECONDITION, "host output %zu is NULL; all bindings must have a valid pointer", i);
+  if (!ex->ev_uploaded[1]) {
+    drop_staging(ex);  // nothing, or the remains of a set-up that failed half way
+    int st = TB200_OK;
+    for (int s = 0; s < 2 && st == TB200_OK; s++) {
+      for (size_t i = 0; i < ni && st == TB200_OK; i++) {
         tb200_buffer_t* b = nullptr;
-        int st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->inputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
-        if (st != TB200_OK) return st;
-        ex->staging_in[s].push_back(b);
+        st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->inputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
+        if (st == TB200_OK) ex->staging_in[s].push_back(b);
       }
-      for (size_t i = 0; i < no; i++) {
+      for (size_t i = 0; i < no && st == TB200_OK; i++) {
         tb200_buffer_t* b = nullptr;
-        int st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->outputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
-        if (st != TB200_OK) return st;
-        ex->staging_out[s].push_back(b);
+        st = tb200_buffer_alloc(d, tensor_bytes(ex->tensors[ex->outputs[i]]), TB200_MEMORY_DEVICE_LOCAL, &b);
+        if (st == TB200_OK) ex->staging_out[s].push_back(b);
       }
-      CUDA_OK(d, cudaEventCreateWithFlags(&ex->ev_released[s], cudaEventDisableTiming));
-      CUDA_OK(d, cudaEventCreateWithFlags(&ex->ev_uploaded[s], cudaEventDisableTiming));
+      if (st == TB200_OK && cudaEventCreateWithFlags(&ex->ev_released[s], cudaEventDisableTiming) != cudaSuccess)
+        st = fail(d, TB200_INTERNAL, "cannot create an event");
+      if (st == TB200_OK && cudaEventCreateWithFlags(&ex->ev_uploaded[s], cudaEventDisableTiming) != cudaSuccess)
+        st = fail(d, TB200_INTERNAL, "cannot create an event");
+    }
+    if (st != TB200_OK) {
+      drop_staging(ex);
+      return st;
     }
   }
-  for (size_t i = 0; i < ni; i++)
-    if (!host_inputs[i]) return fail(d, TB200_INVALID_ARGUMENT, "host input %zu is NULL", i);
-  for (size_t i = 0; i < no; i++)
-    if (!host_outputs[i]) return fail(d, TB200_INVALID_ARGUMENT, "host output %zu is NULL", i);
   const int s = (int)(ex->host_calls & 1);
   const bool reused = ex->host_calls >= 2;
   ex->host_calls++;
-  // upload stream: wait until the call two back has released this staging set, then copy in
-  if (reused) CUDA_OK(d, cudaStreamWaitEvent(d->copy_stream, ex->ev_released[s], 0));
-  for (size_t i = 0; i < ni; i++)
-    CUDA_OK(d, cudaMemcpyAsync(ex->staging_in[s][i]->ptr, host_inputs[i], ex->staging_in[s][i]->bytes,
-                               cudaMemcpyHostToDevice, d->copy_stream));
-  CUDA_OK(d, cudaEventRecord(ex->ev_uploaded[s], d->copy_stream));
-  // compute stream: wait for the upload, run, copy the results out, release the set
-  CUDA_OK(d, cudaStreamWaitEvent(d->stream, ex->ev_uploaded[s], 0));
-  std::vector<tb200_binding_t> bind(ni + no);
-  for (size_t i = 0; i < ni; i++) bind[i] = {ex->staging_in[s][i], 0, 0};
-  for (size_t i = 0; i < no; i++) bind[ni + i] = {ex->staging_out[s][i], 0, 0};
-  int st = tb200_dispatch(ex, bind.data(), bind.size());
-  if (st != TB200_OK) return st;
-  for (size_t i = 0; i < no; i++)
-    CUDA_OK(d, cudaMemcpyAsync(host_outputs[i], ex->staging_out[s][i]->ptr, ex->staging_out[s][i]->bytes,
-                               cudaMemcpyDeviceToHost, d->stream));
-  CUDA_OK(d, cudaEventRecord(ex->ev_released[s], d->stream));
+  std::vector<void*> io(ni + no);
+  for (size_t i = 0; i < ni; i++) io[i] = ex->staging_in[s][i]->ptr;
+  for (size_t i = 0; i < no; i++) io[ni + i] = ex->staging_out[s][i]->ptr;
+  HostSync host;
+  host.copy_in = [&]() -> int {
+    // upload stream: wait until the call two back has released this staging set, then copy in
+    if (reused) CUDA_OK(d, cudaStreamWaitEvent(d->copy_stream, ex->ev_released[s], 0));
+    for (size_t i = 0; i < ni; i++)
+      CUDA_OK(d, cudaMemcpyAsync(ex->staging_in[s][i]->ptr, host_inputs[i], ex->staging_in[s][i]->bytes,
+                                 cudaMemcpyHostToDevice, d->copy_stream));
+    CUDA_OK(d, cudaEventRecord(ex->ev_uploaded[s], d->copy_stream));
+    // compute stream: wait for the upload
+    CUDA_OK(d, cudaStreamWaitEvent(d->stream, ex->ev_uploaded[s], 0));
+    return TB200_OK;
+  };
+  host.copy_out = [&]() -> int {
+    for (size_t i = 0; i < no; i++)
+      CUDA_OK(d, cudaMemcpyAsync(host_outputs[i], ex->staging_out[s][i]->ptr, ex->staging_out[s][i]->bytes,
+                                 cudaMemcpyDeviceToHost, d->stream));
+    CUDA_OK(d, cudaEventRecord(ex->ev_released[s], d->stream));
+    return TB200_OK;
+  };
+  return dispatch_locked(ex, io, &host);
+}
+
+namespace {
+// A wait that nothing ever completes, bounded like every wait of the real kernels (same helper).
+__global__ void wait_probe_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    tb200::mbar_init(tb200::smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) tb200::mbar_wait(tb200::smem_u32(&bar), 0, status, 99, limit_ns);
+}
+}  // namespace
+
+extern "C" int tb200_device_probe_bounded_wait(tb200_device_t* d, uint32_t limit_ms) {
+  if (!d || limit_ms < 1 || limit_ms > 1000) return TB200_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(d->submit_mutex);
+  cudaSetDevice(d->ordinal);
+  wait_probe_kernel<<<1, 32, 0, d->stream>>>(d->status_word, (unsigned long long)limit_ms * 1000000ull);
+  CUDA_OK(d, cudaGetLastError());
+  CUDA_OK(d, cudaMemcpyAsync(d->status_host, d->status_word, sizeof(int), cudaMemcpyDeviceToHost, d->stream));
   return TB200_OK;
 }
 

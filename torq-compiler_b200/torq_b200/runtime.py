@@ -77,6 +77,8 @@ _SIGNATURES = {
     "tb200_executable_connect_peers": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "tb200_gemv_w8_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                         C.c_int, C.c_int, C.c_int, C.c_int]),
+    "tb200_device_probe_bounded_wait": (C.c_int, [C.c_void_p, C.c_uint32]),
+    "tb200_measure_i8_mma_peak": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "tb200_executable_profile_ops": (C.c_int, [C.c_void_p, C.POINTER(Binding), C.c_size_t, C.c_int, C.c_int,
                                                C.POINTER(C.c_float), C.c_uint32]),
 }
@@ -142,6 +144,10 @@ class Device:
 
     def wait(self, timeout_s: float = 60.0):
         self._check(self._lib.tb200_wait(self._h, int(timeout_s * 1e9)))
+
+    def probe_bounded_wait(self, limit_ms: int = 20):
+        """Queues a kernel whose (bounded) wait nothing completes: the next wait() raises ABORTED once."""
+        self._check(self._lib.tb200_device_probe_bounded_wait(self._h, limit_ms))
 
     def close(self):
         if self._h:
@@ -347,6 +353,16 @@ class InferenceRunner:
         self.executable.destroy()
         if self._own_device:
             self.device.close()
+
+
+def measure_i8_mma_peak(ordinal: int = 0, rounds: int = 2000) -> tuple[float, float]:
+    """(tera-ops/s, ms) of the resident-operand tcgen05 kind::i8 loop on every SM of GPU `ordinal`."""
+    lib = load_library()
+    tops, ms = C.c_double(), C.c_double()
+    st = lib.tb200_measure_i8_mma_peak(ordinal, rounds, C.byref(tops), C.byref(ms))
+    if st != OK:
+        raise TorqB200Error(st, "int8 tensor-pipe peak measurement failed")
+    return tops.value, ms.value
 
 
 def run_model(model, inputs: Sequence[np.ndarray], **kw):
