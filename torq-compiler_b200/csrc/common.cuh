@@ -56,13 +56,24 @@ __device__ __forceinline__ long long make_i64(int32_t hi, int32_t lo) {
   return __double_as_longlong(__hiloint2double(hi, lo));
 }
 
-// Compact form of the rescale for ops whose shifts are all >= 33: c = {bias, mult, high word
-// of rnd, shift - 32}; rnd_lo and dmul are the same for every channel of the op.
-__device__ __forceinline__ int32_t scale_hi33(int32_t acc, int32_t mult, int32_t rnd_hi, int32_t hshift,
-                                              int32_t rnd_lo, int32_t dmul) {
-  long long t = (long long)acc * (long long)mult + make_i64(rnd_hi, rnd_lo);
-  t += (long long)(int32_t)((uint32_t)acc >> 31) * (long long)dmul;
-  return (int32_t)(t >> 32) >> hshift;
+// Compact form of the rescale ("Q4"), one 16-byte record {4 * bias, mult, rh, shift - 30} per channel and no
+// 64-bit arithmetic. With v = acc + bias:
+//   (v * M + R) >> S  ==  (4v * M + 4R) >> (S + 2),
+// and for S >= 32 the rounding constant 4R = 2^(S+1) (+- 2^32 with DOUBLE_ROUND) has a zero low word, so the
+// low word of the product never carries into the result:
+//   r = (mulhi(4v, M) + rh [+- 1 by the sign of v]) >> (S - 30),   rh = 2^(S-31) + (out_zp << (S - 30)).
+// The output zero point rides in rh. The planner uses this form only when it has shown, from the weights and
+// the bias, that |4v| stays below 2^31 and that every shift of the op lies in [32, 52].
+// Double rounding: rh additionally holds the +1 of a non-negative v, and a negative v takes 2 back.
+__device__ __forceinline__ int32_t scale_q4_sign(int32_t acc, const int4& c) {
+  const int32_t v4 = acc * 4 + c.x;
+  const int32_t neg = v4 >> 31;  // -1 for a negative accumulator
+  return (__mulhi(v4, c.y) + c.z + neg + neg) >> c.w;
+}
+// Without the sign term: single rounding, or a clamp whose lower end is at or above the output zero point
+// (ReLU-like): every negative v then lands on that lower end whichever way it is rounded.
+__device__ __forceinline__ int32_t scale_q4(int32_t acc, const int4& c) {
+  return (__mulhi(acc * 4 + c.x, c.y) + c.z) >> c.w;
 }
 
 // apply_scale_32 part of requant_cp (no zero point, no clamp).
@@ -85,6 +96,14 @@ __device__ __forceinline__ uint32_t clamp_pack4(int32_t r0, int32_t r1, int32_t 
   asm("min.s16x2 %0, %0, %1;" : "+r"(a) : "r"(hi2));
   asm("min.s16x2 %0, %0, %1;" : "+r"(b) : "r"(hi2));
   return __byte_perm(a, b, 0x6420);
+}
+
+// The same for the full int8 range: two saturating packs.
+__device__ __forceinline__ uint32_t sat_pack4(int32_t r0, int32_t r1, int32_t r2, int32_t r3) {
+  uint32_t a, b;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(a) : "r"(r3), "r"(r2));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(b) : "r"(r1), "r"(r0), "r"(a));
+  return b;
 }
 
 __device__ __forceinline__ int32_t sx8(uint32_t word, int j) {

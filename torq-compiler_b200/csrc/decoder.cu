@@ -716,11 +716,11 @@ void launch_gemv_w8(const uint16_t* x, const int8_t* W, const uint16_t* scale, v
     const size_t smem = (size_t)nt * 8 * xstride;
     dim3 grid((N + 127) / 128, used);
     auto run = [&](auto kernel) {
-      // one flag per instantiation of this lambda (= per kernel); function attributes are per device
-      static std::atomic<unsigned long long> attr_done{0};
-      if (first_use_on_device(attr_done)) {
+      // one flag per kernel (the four instantiations share the lambda's type); function attributes are per device
+      static std::atomic<unsigned long long> attr_done[5];
+      if (first_use_on_device(attr_done[nt])) {
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        mark_used_on_device(attr_done);
+        mark_used_on_device(attr_done[nt]);
       }
       launch_k(kernel, dim3(grid), dim3(256), smem, stream, x, W, scale, y, scratch, B, N, K, slice, y_f32);
     };

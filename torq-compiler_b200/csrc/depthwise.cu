@@ -48,10 +48,11 @@ __device__ __forceinline__ void cp_async_wait(int n) {
   }
 }
 
-// HI33: every rescale shift of the op is >= 33 (compact constants, see gemm_tcgen05.cu).
+// EPI: 0 = rescale from the full ChanParams record; 1 / 2 = compact Q4 records with / without the sign term
+// (common.cuh), four of them held in registers per thread.
 // All addressing is 32-bit element offsets from the tensor bases (the launcher checks that
 // both tensors are below 2 GiB), so a load costs one add and a predicated LDG.
-template <int STRIDE, bool HI33>
+template <int STRIDE, int EPI>
 __global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
   constexpr int TW = STRIDE == 1 ? 2 : 1;    // outputs per thread along W
   constexpr int NCOL = STRIDE == 1 ? 4 : 3;  // input columns per row load
@@ -88,14 +89,13 @@ __global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
       uint4 w = *reinterpret_cast<const uint4*>(a.wq + ((size_t)(kh * TW + v) * a.C + c));
       wq[kh][v][0] = w.x; wq[kh][v][1] = w.y; wq[kh][v][2] = w.z; wq[kh][v][3] = w.w;
     }
-  // per-channel constants: {bias, mult, high word of rnd, shift - 32} (HI33) or the full record
+  // per-channel constants: the Q4 record or the full record
   int4 cq[4];
-  ChanParams cp[HI33 ? 1 : 4];
+  ChanParams cp[EPI != 0 ? 1 : 4];
 #pragma unroll
   for (int k = 0; k < 4; k++) {
-    const ChanParams t = a.chan[c + k];
-    if (HI33) cq[k] = make_int4(t.bias, t.mult, (int)(t.rnd >> 32), t.hshift);
-    else cp[k] = t;
+    if (EPI != 0) cq[k] = __ldg(a.q4 + c + k);
+    else cp[k] = a.chan[c + k];
   }
 
   // column word offsets and validity of the NCOL input columns this strip touches
@@ -164,10 +164,11 @@ __global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
         int q[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-          int acc = HI33 ? cq[k].x : cp[k].bias;
+          int acc = EPI != 0 ? 0 : cp[k].bias;
 #pragma unroll
           for (int kh = 0; kh < 3; kh++) acc = __dp4a((int)win[STRIDE * r + kh][k], (int)wq[kh][v][k], acc);
-          if (HI33) q[k] = scale_hi33(acc, cq[k].y, cq[k].z, cq[k].w, a.rnd_lo, a.dmul) + a.out_zp;
+          if (EPI == 1) q[k] = scale_q4_sign(acc, cq[k]);
+          else if (EPI == 2) q[k] = scale_q4(acc, cq[k]);
           else q[k] = scale_cp<false>(acc, cp[k]) + a.out_zp;
         }
         const uint32_t word = clamp_pack4(q[0], q[1], q[2], q[3], lo2, hi2);
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
 // thread and row instead of four 4-byte copies per thread and row, and no 64-bit index arithmetic per
 // thread); pieces outside the image are stored as the input zero point. After one barrier every thread
 // reads its own 4 channels of its 3 or 4 columns from the tile and proceeds exactly as dw3x3_kernel.
-template <int STRIDE, bool HI33>
+template <int STRIDE, int EPI>
 __global__ void __launch_bounds__(128, STRIDE == 1 ? 6 : 8) dw3x3_tile_kernel(DwArgs a, int cg_log2, int cchunks) {
   constexpr int TW = STRIDE == 1 ? 2 : 1;
   constexpr int NCOL = STRIDE == 1 ? 4 : 3;
@@ -245,12 +246,11 @@ __global__ void __launch_bounds__(128, STRIDE == 1 ? 6 : 8) dw3x3_tile_kernel(Dw
       wq[kh][v][0] = w.x; wq[kh][v][1] = w.y; wq[kh][v][2] = w.z; wq[kh][v][3] = w.w;
     }
   int4 cq[4];
-  ChanParams cp[HI33 ? 1 : 4];
+  ChanParams cp[EPI != 0 ? 1 : 4];
 #pragma unroll
   for (int k = 0; k < 4; k++) {
-    const ChanParams t = a.chan[c + k];
-    if (HI33) cq[k] = make_int4(t.bias, t.mult, (int)(t.rnd >> 32), t.hshift);
-    else cp[k] = t;
+    if (EPI != 0) cq[k] = __ldg(a.q4 + c + k);
+    else cp[k] = a.chan[c + k];
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
@@ -292,10 +292,11 @@ __global__ void __launch_bounds__(128, STRIDE == 1 ? 6 : 8) dw3x3_tile_kernel(Dw
         int q[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-          int acc = HI33 ? cq[k].x : cp[k].bias;
+          int acc = EPI != 0 ? 0 : cp[k].bias;
 #pragma unroll
           for (int kh = 0; kh < 3; kh++) acc = __dp4a((int)win[STRIDE * r + kh][k], (int)wq[kh][v][k], acc);
-          if (HI33) q[k] = scale_hi33(acc, cq[k].y, cq[k].z, cq[k].w, a.rnd_lo, a.dmul) + a.out_zp;
+          if (EPI == 1) q[k] = scale_q4_sign(acc, cq[k]);
+          else if (EPI == 2) q[k] = scale_q4(acc, cq[k]);
           else q[k] = scale_cp<false>(acc, cp[k]) + a.out_zp;
         }
         const uint32_t word = clamp_pack4(q[0], q[1], q[2], q[3], lo2, hi2);
@@ -421,11 +422,13 @@ void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
     const size_t smem = (size_t)nr * iwt * (4 << cg_log2);
     const dim3 grid((unsigned)(tiles * cchunks), (unsigned)((a.OH + kRows - 1) / kRows), (unsigned)a.N);
     if (S == 1) {
-      if (a.hi33) dw3x3_tile_kernel<1, true><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
-      else dw3x3_tile_kernel<1, false><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      if (a.epi == 1) dw3x3_tile_kernel<1, 1><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      else if (a.epi == 2) dw3x3_tile_kernel<1, 2><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      else dw3x3_tile_kernel<1, 0><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
     } else {
-      if (a.hi33) dw3x3_tile_kernel<2, true><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
-      else dw3x3_tile_kernel<2, false><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      if (a.epi == 1) dw3x3_tile_kernel<2, 1><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      else if (a.epi == 2) dw3x3_tile_kernel<2, 2><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      else dw3x3_tile_kernel<2, 0><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
     }
   } else if (a.wq && depthwise3x3_supported(a)) {
     const int tw = a.stride_h == 1 ? 2 : 1;
@@ -433,11 +436,13 @@ void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
     unsigned blocks = (unsigned)((total + 127) / 128);
     const size_t smem1 = (size_t)((kRows - 1) * 1 + 3) * 4 * 128 * 4, smem2 = (size_t)((kRows - 1) * 2 + 3) * 4 * 128 * 4;
     if (a.stride_h == 1) {
-      if (a.hi33) dw3x3_kernel<1, true><<<blocks, 128, smem1, stream>>>(a);
-      else dw3x3_kernel<1, false><<<blocks, 128, smem1, stream>>>(a);
+      if (a.epi == 1) dw3x3_kernel<1, 1><<<blocks, 128, smem1, stream>>>(a);
+      else if (a.epi == 2) dw3x3_kernel<1, 2><<<blocks, 128, smem1, stream>>>(a);
+      else dw3x3_kernel<1, 0><<<blocks, 128, smem1, stream>>>(a);
     } else {
-      if (a.hi33) dw3x3_kernel<2, true><<<blocks, 128, smem2, stream>>>(a);
-      else dw3x3_kernel<2, false><<<blocks, 128, smem2, stream>>>(a);
+      if (a.epi == 1) dw3x3_kernel<2, 1><<<blocks, 128, smem2, stream>>>(a);
+      else if (a.epi == 2) dw3x3_kernel<2, 2><<<blocks, 128, smem2, stream>>>(a);
+      else dw3x3_kernel<2, 0><<<blocks, 128, smem2, stream>>>(a);
     }
   } else if (a.M == 1 && (a.C & 3) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C >> 2);

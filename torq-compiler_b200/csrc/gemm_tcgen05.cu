@@ -66,7 +66,7 @@ struct GemmTcParams {
   int stages;           // A (or A+W) ring depth
   int w_resident;       // weights loaded once
   int out_zp, clamp_min, clamp_max;
-  int rnd_lo, dmul;     // uniform parts of the rounding constants (HI33 kernels)
+  const int4* q4;       // compact per-channel records of the EPI 1 / 2 kernels
   int acc_stride, acc_stages, tmem_cols;
   // implicit-GEMM convolution (CONV kernels): tile = TH x TW output pixels, TW a power of two
   int tw_log2, TH, tiles_w, tiles_per_img, OH, OW, cstride, pad_t, pad_l, KW, icb_per_tap;
@@ -83,10 +83,10 @@ struct GemmTcParams {
 };
 
 
-// HI33: every rescale shift of the op is >= 33, so the rounding constant's low word and the
-// negative-accumulator term are the same for all channels and a channel needs only
-// {bias, mult, high word of rnd, shift - 32}: one 16-byte shared-memory load per output.
-template <bool HI33, bool CONV>
+// EPI: 0 = the general rescale from the 32-byte ChanParams (any shift, 64-bit arithmetic); 1 / 2 = the compact
+// Q4 records (common.cuh: one 16-byte shared-memory load, one 32-bit multiply-high per output) with / without
+// the sign term of DOUBLE_ROUND.
+template <int EPI, bool CONV>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, GemmTcParams p) {
@@ -94,7 +94,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_empty[kMaxStages], bar_acc_full[4], bar_acc_empty[4],
       bar_w;
   __shared__ uint32_t tmem_slot;
-  __shared__ __align__(16) int4 cp_s[kEpiGroups][128];  // per epilogue group: {bias, mult, rnd_hi, shift - 32}
+  __shared__ __align__(16) int4 cp_s[kEpiGroups][128];  // per epilogue group: the Q4 records of its current n tile
   __shared__ __align__(16) uint8_t lut_s[256];           // fused table, indexed by value + 128
 
   const int warp = threadIdx.x >> 5;
@@ -242,6 +242,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t lo2 = (uint32_t)(p.clamp_min & 0xffff) * 0x10001u;
     const uint32_t hi2 = (uint32_t)(p.clamp_max & 0xffff) * 0x10001u;
     const bool vec_ok = (p.ldc & 15) == 0;
+    const bool full_range = p.clamp_min <= -128 && p.clamp_max >= 127;
     const int nfull = p.BN >> 5;
     const uint32_t tile_bytes = (uint32_t)kBM * p.BN;
     // one staging tile per group for the TMA store of the output
@@ -257,12 +258,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int n = t_first / p.m_tiles, m = t_first - n * p.m_tiles;
     for (int t = t_first; t < total_tiles; t += kEpiGroups * gridDim.x) {
       const ChanParams* chan_n = p.chan + (size_t)n * p.BN;
-      if (HI33 && n != loaded_n) {
+      if (EPI != 0 && n != loaded_n) {
         group_sync();
-        if (e < p.BN) {
-          const ChanParams c = chan_n[e];
-          cps[e] = make_int4(c.bias, c.mult, (int)(c.rnd >> 32), c.hshift);
-        }
+        if (e < p.BN) cps[e] = p.q4[(size_t)n * p.BN + e];
         group_sync();
         loaded_n = n;
       }
@@ -304,15 +302,16 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int j = 0; j < 4; j++) {
               int acc = (int)v[g * 4 + j];
               if (CONV && corr_row) acc += corr_row[c0 + g * 4 + j];
-              if (HI33) {
-                const int4 c = cps[c0 + g * 4 + j];
-                r[j] = scale_hi33(acc + c.x, c.y, c.z, c.w, p.rnd_lo, p.dmul) + p.out_zp;
+              if (EPI == 1) {
+                r[j] = scale_q4_sign(acc, cps[c0 + g * 4 + j]);
+              } else if (EPI == 2) {
+                r[j] = scale_q4(acc, cps[c0 + g * 4 + j]);
               } else {
                 const ChanParams c = chan_n[c0 + g * 4 + j];
                 r[j] = scale_cp<false>(acc + c.bias, c) + p.out_zp;
               }
             }
-            w4[g] = clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
+            w4[g] = (EPI == 1 && full_range) ? sat_pack4(r[0], r[1], r[2], r[3]) : clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
             if (p.lut) {  // out = table[value + 128], byte by byte
               const uint32_t x = w4[g] ^ 0x80808080u;
               w4[g] = (uint32_t)lut_s[x & 0xff] | ((uint32_t)lut_s[(x >> 8) & 0xff] << 8) |
@@ -540,8 +539,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   p.out_zp = a.out_zp;
   p.clamp_min = a.clamp_min;
   p.clamp_max = a.clamp_max;
-  p.rnd_lo = a.rnd_lo;
-  p.dmul = a.dmul;
+  p.q4 = a.q4;
   int stride = 32;
   while (stride < g.BN) stride <<= 1;
   p.acc_stride = stride;
@@ -554,16 +552,19 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   const size_t smem = 1024 + p.staging_off + staging_bytes;
   static std::atomic<unsigned long long> attr_set{0};
   if (first_use_on_device(attr_set)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return e;
     mark_used_on_device(attr_set);
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
-  if (a.hi33) gemm_i8_tc_kernel<true, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  else gemm_i8_tc_kernel<false, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  if (a.epi == 1) gemm_i8_tc_kernel<1, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  else if (a.epi == 2) gemm_i8_tc_kernel<2, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  else gemm_i8_tc_kernel<0, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   return cudaGetLastError();
 }
 
@@ -660,7 +661,7 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   p.stages = stages;
-  p.out_zp = a.out_zp; p.clamp_min = a.clamp_min; p.clamp_max = a.clamp_max; p.rnd_lo = a.rnd_lo; p.dmul = a.dmul;
+  p.out_zp = a.out_zp; p.clamp_min = a.clamp_min; p.clamp_max = a.clamp_max; p.q4 = a.q4;
   int stride = 32;
   while (stride < g.BN) stride <<= 1;
   p.acc_stride = stride;
@@ -673,16 +674,19 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   const size_t smem = 1024 + p.staging_off + staging_bytes;
   static std::atomic<unsigned long long> attr_set{0};
   if (first_use_on_device(attr_set)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return e;
     mark_used_on_device(attr_set);
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
-  if (a.hi33) gemm_i8_tc_kernel<true, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  else gemm_i8_tc_kernel<false, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  if (a.epi == 1) gemm_i8_tc_kernel<1, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  else if (a.epi == 2) gemm_i8_tc_kernel<2, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  else gemm_i8_tc_kernel<0, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   return cudaGetLastError();
 }
 

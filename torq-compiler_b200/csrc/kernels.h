@@ -46,7 +46,8 @@ struct DwArgs {
   int input_zp, weight_zp, out_zp, clamp_min, clamp_max;
   int double_round;
   int hi_shift;           // every rescale shift of the op is >= 32
-  int hi33, rnd_lo, dmul; // every shift >= 33: compact constants; uniform rounding parts (3x3 fast path)
+  int epi;                // 3x3 fast path: 0 = ChanParams arithmetic, 1 / 2 = compact Q4 records with / without the sign term
+  const int4* q4;         // [C] Q4 records (epi != 0); the output zero point rides in them
   const uint32_t* wq;     // 3x3 fast path: weights packed per row for dp4a (see depthwise.cu), else null
 };
 void launch_depthwise(const DwArgs& a, cudaStream_t stream);
@@ -115,8 +116,8 @@ struct GemmTcArgs {
   long long M;
   int N, K;
   int out_zp, clamp_min, clamp_max;
-  int hi33;               // every rescale shift >= 33: the 16-byte-constant epilogue applies
-  int rnd_lo, dmul;       // with hi33: low word of the rounding constant, negative-accumulator term
+  int epi;                // 0 = ChanParams arithmetic (any shift), 1 / 2 = compact Q4 records with / without the sign term
+  const int4* q4;         // [n_tiles * BN] Q4 records when epi != 0 (common.cuh); the output zero point rides in them
   int* status;            // device status word: a kernel whose bounded wait expires writes a code here
   const int8_t* lut;      // 256-entry table applied to the int8 result, or null
 };
@@ -142,7 +143,9 @@ struct ConvTcArgs {
   const ChanParams* chan; // [n_tiles * BN], bias already holds bias - izp * sum of all taps
   int8_t* out;            // [N, OH, OW, OC]
   int N, H, W, IC, OC, KH, KW, OH, OW, stride, pad_t, pad_l;
-  int out_zp, clamp_min, clamp_max, hi33, rnd_lo, dmul;
+  int out_zp, clamp_min, clamp_max;
+  int epi;                // as GemmTcArgs::epi
+  const int4* q4;
   // border classes: pixel (oh, ow) has class rcls[oh] * ncc + ccls[ow]; corr[class][n_tiles * BN] =
   // izp * (sum of the weights of the taps that fall outside the frame for that class)
   const int32_t* corr;

@@ -168,6 +168,31 @@ struct Builder {
   int last_min_shift = 64;  // smallest effective shift of the op
   int last_max_shift = 0;   // largest
 
+  // The compact "Q4" epilogue records {4 * bias, mult, rh, shift - 30} (common.cuh) for the channels in cp,
+  // when the op qualifies: every shift in [32, 52], multipliers non-negative, and |4 * (acc + bias)| provably
+  // below 2^31, where |acc| <= acc_bound[c] (from the weights: 128 * sum |w|, doubled when the kernel adds a
+  // border correction). mode: 1 = with the sign term of DOUBLE_ROUND, 2 = without (single rounding, or the
+  // clamp's lower end is at or above the output zero point so that every negative value lands on it anyway).
+  // Returns 0 when the op does not qualify.
+  static int q4_params(const std::vector<ChanParams>& cp, const std::vector<long long>& acc_bound, bool double_round,
+                       int out_zp, int clamp_min, std::vector<int4>& out) {
+    out.resize(cp.size());
+    bool any_double = false;
+    for (size_t c = 0; c < cp.size(); c++) {
+      const ChanParams& p = cp[c];
+      if (p.shift < 32 || p.shift > 52 || p.mult < 0) return 0;
+      const long long b = p.bias;
+      if ((acc_bound[c] + (b < 0 ? -b : b)) >= (1ll << 29)) return 0;
+      const bool second = double_round && p.shift > 31;
+      any_double |= second;
+      const long long rh = (1ll << (p.shift - 31)) + ((long long)out_zp << (p.shift - 30)) + (second ? 1 : 0);
+      // |mulhi(4v, M)| < 2^28 for |4v| < 2^31 and M < 2^31
+      if (rh >= (1ll << 30) || rh <= -(1ll << 30)) return 0;
+      out[c] = make_int4((int)(4 * b), p.mult, (int)rh, p.shift - 30);
+    }
+    return any_double && clamp_min < out_zp ? 1 : 2;
+  }
+
   static void fill_rounding(ChanParams& p, bool double_round) {
     const bool second = double_round && p.shift > 31;
     p.rnd = (1ll << (p.shift - 1)) + (second ? (1ll << 30) : 0ll);
@@ -658,10 +683,17 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         if (!w) return b.status;
         if (op.in0_zp < -128 || op.in0_zp > 127) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input_zp outside int8", i);
         std::vector<int32_t> wsum(OC, 0);
+        std::vector<long long> acc_bound(OC, 0);  // |sum x * w| <= 128 * sum |w|
         for (int oc = 0; oc < OC; oc++) {
           int32_t s = 0;
-          for (long long k = 0; k < K; k++) s += w[(size_t)oc * K + k];
+          long long sabs = 0;
+          for (long long k = 0; k < K; k++) {
+            const int v = w[(size_t)oc * K + k];
+            s += v;
+            sabs += v < 0 ? -v : v;
+          }
           wsum[oc] = s;
+          acc_bound[oc] = 128 * sabs;
         }
         std::vector<ChanParams> cp;
         int dr = 0;
@@ -695,13 +727,8 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           ga.M = M / rgroup; ga.N = Ng; ga.K = Kg;
           ga.lda = Kg; ga.ldc = Ng;
           ga.out_zp = op.out_zp; ga.clamp_min = op.clamp_min; ga.clamp_max = op.clamp_max;
-          ga.hi33 = b.last_min_shift >= 33;
-          if (ga.hi33 && b.last_max_shift <= 55) {
-            // (t + (zp << S)) >> S == (t >> S) + zp: the output zero point rides in the rounding constant
-            for (auto& c : cp) c.rnd += (long long)op.out_zp << c.shift;
-            ga.out_zp = 0;
-          }
-          ga.rnd_lo = (int)(cp[0].rnd & 0xffffffffll); ga.dmul = cp[0].dmul;
+          std::vector<int4> q4;
+          ga.epi = Builder::q4_params(cp, acc_bound, dr != 0, op.out_zp, op.clamp_min, q4);
           const int rows = geo.n_tiles * geo.BN;
           std::vector<int8_t> wp((size_t)rows * geo.Kpad, 0);
           for (int j = 0; j < rgroup; j++)
@@ -716,6 +743,14 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           { ChanParams z{}; z.shift = 34; z.hshift = 2; z.rnd = 1ll << 33; cp.resize(rows, z); }
           size_t w_off = b.add_const(wp.data(), wp.size());
           size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+          size_t q_off = 0;
+          if (ga.epi) {
+            std::vector<int4> rep((size_t)rows, make_int4(0, 0, 0, 1));
+            for (int j = 0; j < rgroup; j++)
+              for (int oc = 0; oc < OC; oc++) rep[(size_t)j * OC + oc] = q4[oc];
+            q_off = b.add_const(rep.data(), rep.size() * sizeof(int4));
+          }
+          const bool has_q4 = ga.epi != 0;
           Loc lx = loc(op.in0), lo = loc(result_id);
           std::shared_ptr<GemmTcState> st(gemm_tc_state_new(), gemm_tc_state_free);
           step.kernel_name = "gemm_i8_tcgen05";
@@ -725,6 +760,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             k.out = (int8_t*)lo.resolve(c);
             k.w = (const int8_t*)(c.consts + w_off);
             k.chan = (const ChanParams*)(c.consts + c_off);
+            k.q4 = has_q4 ? (const int4*)(c.consts + q_off) : nullptr;
             k.status = c.status;
             k.lut = has_lut ? (const int8_t*)(c.consts + lut_off) : nullptr;
             launch_gemm_i8_tc(k, st.get(), c.stream);
@@ -743,12 +779,13 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           ca.N = N; ca.H = H; ca.W = W; ca.IC = IC; ca.OC = OC; ca.KH = KH; ca.KW = KW; ca.OH = OH; ca.OW = OW;
           ca.stride = op.stride_h; ca.pad_t = op.pad_t; ca.pad_l = op.pad_l;
           ca.out_zp = op.out_zp; ca.clamp_min = op.clamp_min; ca.clamp_max = op.clamp_max;
-          ca.hi33 = b.last_min_shift >= 33;
-          if (ca.hi33 && b.last_max_shift <= 55) {
-            for (auto& c : cp) c.rnd += (long long)op.out_zp << c.shift;
-            ca.out_zp = 0;
+          std::vector<int4> q4;
+          {
+            // the kernel adds a border correction of at most |izp| * sum |w| to the accumulator
+            std::vector<long long> bound(acc_bound);
+            for (auto& v : bound) v *= 2;
+            ca.epi = Builder::q4_params(cp, bound, dr != 0, op.out_zp, op.clamp_min, q4);
           }
-          ca.rnd_lo = (int)(cp[0].rnd & 0xffffffffll); ca.dmul = cp[0].dmul;
           const int rows = geo.n_tiles * geo.BN;
           std::vector<int8_t> wp((size_t)rows * geo.Kpad, 0);
           // OHWI rows are already in (kh, kw, ic) order; every tap is padded to whole channel blocks
@@ -805,6 +842,12 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           }
           const size_t w_off = b.add_const(wp.data(), wp.size());
           const size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+          size_t q_off = 0;
+          if (ca.epi) {
+            q4.resize(rows, make_int4(0, 0, 0, 1));
+            q_off = b.add_const(q4.data(), q4.size() * sizeof(int4));
+          }
+          const bool has_q4 = ca.epi != 0;
           size_t corr_off = 0, rcls_off = 0, ccls_off = 0, nz_off = 0;
           if (need_corr) {
             corr_off = b.add_const(corr.data(), corr.size() * 4);
@@ -822,6 +865,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             k.out = (int8_t*)lo.resolve(c);
             k.w = (const int8_t*)(c.consts + w_off);
             k.chan = (const ChanParams*)(c.consts + c_off);
+            k.q4 = has_q4 ? (const int4*)(c.consts + q_off) : nullptr;
             if (need_corr) {
               k.corr = (const int32_t*)(c.consts + corr_off);
               k.rcls = (const uint8_t*)(c.consts + rcls_off);
@@ -897,19 +941,24 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         int dr = 0;
         if (!b.chan_params(op, i, OC, fast ? wsum.data() : nullptr, 9, fast, cp, dr)) return b.status;
         a.double_round = dr; a.hi_shift = b.last_hi_shift;
-        a.hi33 = b.last_min_shift >= 33; a.rnd_lo = (int)(cp[0].rnd & 0xffffffffll); a.dmul = cp[0].dmul;
-        if (fast && a.hi33 && b.last_max_shift <= 55) {
-          for (auto& cc : cp) cc.rnd += (long long)op.out_zp << cc.shift;  // zero point rides in the rounding constant
-          a.out_zp = 0;
+        std::vector<int4> q4;
+        if (fast) {
+          // nine taps: |acc| <= 128 * sum |w| (taps outside the image are staged as the zero point and add nothing)
+          std::vector<long long> bound(OC, 0);
+          for (int t = 0; t < 9; t++)
+            for (int ch = 0; ch < OC; ch++) bound[ch] += 128 * (long long)std::abs((int)wd[(size_t)t * OC + ch]);
+          a.epi = Builder::q4_params(cp, bound, dr != 0, op.out_zp, op.clamp_min, q4);
         }
         size_t w_off = b.add_const(wd, (size_t)a.KH * a.KW * OC);
         size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
-        size_t q_off = 0;
+        size_t q_off = 0, q4_off = 0;
         if (fast) {
           std::vector<uint32_t> wq((size_t)3 * 2 * OC);
           size_t nw = depthwise3x3_pack(wd, OC, op.stride_h, wq.data());
           q_off = b.add_const(wq.data(), nw * sizeof(uint32_t));
+          if (a.epi) q4_off = b.add_const(q4.data(), q4.size() * sizeof(int4));
         }
+        const bool has_q4 = a.epi != 0;
         Loc lx = loc(op.in0), lo = loc(op.out0);
         step.kernel_name = fast ? "depthwise3x3_dp4a" : "depthwise";
         step.launch = [=](const ExecContext& c) {
@@ -919,6 +968,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           k.w = (const int8_t*)(c.consts + w_off);
           k.chan = (const ChanParams*)(c.consts + c_off);
           k.wq = fast ? (const uint32_t*)(c.consts + q_off) : nullptr;
+          k.q4 = has_q4 ? (const int4*)(c.consts + q4_off) : nullptr;
           launch_depthwise(k, c.stream);
         };
         break;
