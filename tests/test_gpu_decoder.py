@@ -96,6 +96,24 @@ def test_full_size_decoder_matches_reference(device):
     assert wrong == 0 and near_tie == 0, (exact, near_tie, wrong)
 
 
+def test_benchmark_decode_workload_matches_reference(device):
+    """The decode workload the benchmark times: the 1B-parameter shape, batch 1, a 1024-token seeded prompt and
+    128 greedy tokens, with the peaked logits of the benchmark's weights (embedding gain 6.0). Logits within 1e-2
+    (relative max-abs) of the fp32 reference at every one of the 1151 steps, greedy ids identical over all 128."""
+    cfg = gemma3.GemmaConfig()
+    worst, exact, near_tie, wrong, got = _run(device, cfg, 1, prompt_len=1024, gen_len=128, embed_gain=6.0)
+    assert worst <= LOGIT_REL_TOL, worst
+    assert wrong == 0 and near_tie == 0 and exact == 128, (exact, near_tie, wrong)
+
+
+def test_benchmark_decode_workload_batch_32(device):
+    """Batch 32 of the same shape (the op-by-op path with the tensor-core GEMV): 16 prompt + 16 greedy steps."""
+    cfg = gemma3.GemmaConfig()
+    worst, exact, near_tie, wrong, got = _run(device, cfg, 32, prompt_len=16, gen_len=16, embed_gain=6.0)
+    assert worst <= LOGIT_REL_TOL, worst
+    assert wrong == 0 and near_tie == 0 and exact == 32 * 16, (exact, near_tie, wrong)
+
+
 MID = gemma3.GemmaConfig(layers=2, hidden=1024, intermediate=2048, vocab=4096, window=16, local_per_global=1, max_seq=64)
 
 
