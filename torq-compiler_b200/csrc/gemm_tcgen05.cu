@@ -40,6 +40,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.h"
@@ -54,7 +55,7 @@ constexpr int kMaxStages = 16;
 constexpr int kEpiGroups = 4;                    // each group = 4 warps = the 128 TMEM lanes of one accumulator
 constexpr int kEpiWarps = 4 * kEpiGroups;
 constexpr int kThreads = 64 + 32 * kEpiWarps;
-constexpr int kSmemBudget = 196 * 1024;          // dynamic shared memory the kernel may use
+constexpr int kSmemBudget = 216 * 1024;          // dynamic shared memory the kernel may use (227 KB less the static part)
 constexpr int kResidentWeightBytes = 64 * 1024;  // weights up to this size stay in shared memory
 
 struct GemmTcParams {
@@ -68,6 +69,7 @@ struct GemmTcParams {
   int out_zp, clamp_min, clamp_max;
   const int4* q4;       // compact per-channel records of the EPI 1 / 2 kernels
   int acc_stride, acc_stages, tmem_cols;
+  int gpt, BNh;         // epilogue groups per accumulator (1 or 2) and the columns each of them drains (BN / gpt)
   // implicit-GEMM convolution (CONV kernels): tile = TH x TW output pixels, TW a power of two
   int tw_log2, TH, tiles_w, tiles_per_img, OH, OW, cstride, pad_t, pad_l, KW, icb_per_tap;
   const int32_t* corr;  // [row classes * col classes][n_tiles * BN] border corrections, or null
@@ -114,7 +116,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     for (int s = 0; s < 4; s++) {
       mbar_init(smem_u32(&bar_acc_full[s]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[s]), 4);
+      mbar_init(smem_u32(&bar_acc_empty[s]), 4 * p.gpt);  // one arrival per epilogue warp that drains the stage
     }
     mbar_init(smem_u32(&bar_w), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -237,34 +239,38 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // stage g and takes this CTA's tiles g, g + 4, g + 8, ...
     const int q = warp & 3;                // TMEM lane quarter this warp may read
     const int group = (warp - 2) >> 2;
+    // gpt == 1: group g drains accumulator stage g alone. gpt == 2 (tiles wider than 128 columns, two
+    // stages): groups 2s and 2s + 1 drain stage s together, each its half of the columns.
+    const int astage = p.gpt == 2 ? group >> 1 : group;
+    const int col_half = p.gpt == 2 ? (group & 1) * p.BNh : 0;
     const int e = (threadIdx.x - 64) & 127;
     int4* cps = cp_s[group];
     const uint32_t lo2 = (uint32_t)(p.clamp_min & 0xffff) * 0x10001u;
     const uint32_t hi2 = (uint32_t)(p.clamp_max & 0xffff) * 0x10001u;
     const bool vec_ok = (p.ldc & 15) == 0;
     const bool full_range = p.clamp_min <= -128 && p.clamp_max >= 127;
-    const int nfull = p.BN >> 5;
-    const uint32_t tile_bytes = (uint32_t)kBM * p.BN;
+    const int nfull = p.BNh >> 5;
+    const uint32_t tile_bytes = (uint32_t)kBM * p.BNh;
     // one staging tile per group for the TMA store of the output
     uint8_t* const stage_tile = smem_raw + (smem_base - smem_u32(smem_raw)) + p.staging_off + (size_t)group * tile_bytes;
     const int row_in_tile = q * 32 + lane;
-    uint8_t* const srow = stage_tile + (size_t)row_in_tile * p.BN;
+    uint8_t* const srow = stage_tile + (size_t)row_in_tile * p.BNh;
     const int bar_id = 1 + group;
     auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory"); };
     int loaded_n = -1;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const int t_first = blockIdx.x + group * gridDim.x;
+    const int t_first = blockIdx.x + astage * gridDim.x;
     int n = t_first / p.m_tiles, m = t_first - n * p.m_tiles;
-    for (int t = t_first; t < total_tiles; t += kEpiGroups * gridDim.x) {
-      const ChanParams* chan_n = p.chan + (size_t)n * p.BN;
+    for (int t = t_first; t < total_tiles; t += p.acc_stages * gridDim.x) {
+      const ChanParams* chan_n = p.chan + (size_t)n * p.BN + col_half;
       if (EPI != 0 && n != loaded_n) {
         group_sync();
-        if (e < p.BN) cps[e] = p.q4[(size_t)n * p.BN + e];
+        if (e < p.BNh) cps[e] = p.q4[(size_t)n * p.BN + col_half + e];
         group_sync();
         loaded_n = n;
       }
-      if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[group]), acc_phase, p.status, 4, p.wait_ns);
+      if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[astage]), acc_phase, p.status, 4, p.wait_ns);
       if (ok) {
         tc_fence_after();
         const int row = m * kBM + row_in_tile;
@@ -280,12 +286,12 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const int oh = oh0 + (row_in_tile >> p.tw_log2), ow = ow0 + (row_in_tile & ((1 << p.tw_log2) - 1));
           if (p.corr && oh < p.OH && ow < p.OW) {
             const int cls = p.rcls[oh] * p.ncc + p.ccls[ow];
-            if (p.cls_nonzero[cls]) corr_row = p.corr + (size_t)cls * p.n_tiles * p.BN + (size_t)n * p.BN;
+            if (p.cls_nonzero[cls]) corr_row = p.corr + (size_t)cls * p.n_tiles * p.BN + (size_t)n * p.BN + col_half;
           }
         }
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(group * p.acc_stride);
-        int8_t* orow = p.out + (long long)row * p.ldc + (long long)n * p.BN;
-        const int ncol0 = n * p.BN;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(astage * p.acc_stride + col_half);
+        int8_t* orow = p.out + (long long)row * p.ldc + (long long)n * p.BN + col_half;
+        const int ncol0 = n * p.BN + col_half;
         if (p.tma_store) {
           // this group's previous store must have read the staging tile before it is overwritten
           if (e == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -338,14 +344,14 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           emit16(v, c * 32);
           emit16(v + 16, c * 32 + 16);
         }
-        if (p.BN & 16) {
+        if (p.BNh & 16) {
           uint32_t vt[16];
           tmem_ld16(taddr + nfull * 32, vt);
           emit16(vt, nfull * 32);
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[group]));  // TMEM stage drained
+        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[astage]));  // this warp's share of the TMEM stage is drained
         if (p.tma_store) {
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // staged bytes -> visible to the TMA engine
           group_sync();
@@ -357,7 +363,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
       }
       acc_phase ^= 1;
-      m += kEpiGroups * gridDim.x;
+      m += p.acc_stages * gridDim.x;
       while (m >= p.m_tiles) {
         m -= p.m_tiles;
         n++;
@@ -464,8 +470,8 @@ GemmTcGeometry gemm_tc_geometry(int N, int K) {
   g.row_bytes = K <= 32 ? 32 : K <= 64 ? 64 : 128;
   g.k_blocks = (K + g.row_bytes - 1) / g.row_bytes;
   g.Kpad = g.k_blocks * g.row_bytes;
-  // N tiles of at most 128 columns (4 accumulator stages fit TMEM); least padding wins
   const int npad = (N + 15) / 16 * 16;
+  // narrow tiles: at most 128 columns, four accumulator stages, one epilogue group per tile; least padding wins
   int best_tiles = 0, best_bn = 0, best_total = 1 << 30;
   const int t0 = (npad + 127) / 128;
   for (int tiles = t0; tiles <= t0 + 2; tiles++) {
@@ -478,6 +484,30 @@ GemmTcGeometry gemm_tc_geometry(int N, int K) {
   }
   g.BN = best_bn;
   g.n_tiles = best_tiles;
+  g.gpt = 1;
+  // wide tiles: 160..256 columns (a multiple of 32), two accumulator stages, two epilogue groups per tile.
+  // Each A tile then meets twice as many weight columns per load and the MMA reads less shared memory per
+  // multiply-accumulate. Taken when it pads no more than 1/16 beyond the narrow choice.
+  static int max_bn = -1;  // TB200_GEMM_MAX_BN=128 keeps the narrow tiles (A/B aid)
+  if (max_bn < 0) { const char* e = getenv("TB200_GEMM_MAX_BN"); max_bn = e && atoi(e) >= 16 ? atoi(e) : 256; }
+  if (npad > 128 && max_bn > 128) {
+    int wt = 0, wbn = 0, wtotal = 1 << 30;
+    const int w0 = (npad + 255) / 256;
+    for (int tiles = w0; tiles <= w0 + 2; tiles++) {
+      const int bn = ((npad + tiles - 1) / tiles + 31) / 32 * 32;
+      if (bn <= 128 || bn > 256) continue;
+      if (bn * tiles < wtotal) {
+        wtotal = bn * tiles;
+        wt = tiles;
+        wbn = bn;
+      }
+    }
+    if (wt > 0 && wtotal <= best_total + best_total / 16) {
+      g.BN = wbn;
+      g.n_tiles = wt;
+      g.gpt = 2;
+    }
+  }
   return g;
 }
 
@@ -508,9 +538,11 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
       return cudaErrorInvalidValue;
     st->w = a.w;
   }
-  const bool tma_store = (a.ldc % 16) == 0 && ((uintptr_t)a.out % 16) == 0;
+  // Long K with wide tiles: the epilogue is a small share of the tile's time and the ring needs the shared memory
+  // more than the output staging does, so the result leaves with 16-byte stores from registers.
+  const bool tma_store = (a.ldc % 16) == 0 && ((uintptr_t)a.out % 16) == 0 && !(g.gpt == 2 && g.k_blocks >= 16);
   if (tma_store && st->c != a.out) {
-    if (!encode_2d_plain(&st->tmC, a.out, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldc, kBM, (uint32_t)g.BN))
+    if (!encode_2d_plain(&st->tmC, a.out, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldc, kBM, (uint32_t)(g.BN / g.gpt)))
       return cudaErrorInvalidValue;
     st->c = a.out;
   }
@@ -530,7 +562,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
   p.w_resident = w_bytes <= (size_t)kResidentWeightBytes;
   const size_t stage_bytes = (size_t)kBM * g.row_bytes + (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes);
-  const size_t staging_bytes = tma_store ? (size_t)kEpiGroups * kBM * g.BN : 0;  // one tile per group
+  const size_t staging_bytes = tma_store ? (size_t)kEpiGroups * kBM * (g.BN / g.gpt) : 0;  // one (half) tile per group
   const size_t ring_budget = (size_t)kSmemBudget - 1024 - (p.w_resident ? w_bytes : 0) - staging_bytes;
   int stages = (int)(ring_budget / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
@@ -543,7 +575,9 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   int stride = 32;
   while (stride < g.BN) stride <<= 1;
   p.acc_stride = stride;
-  p.acc_stages = kEpiGroups;  // BN <= 128, so 4 stages fit the 512 TMEM columns
+  p.gpt = g.gpt;
+  p.BNh = g.BN / g.gpt;
+  p.acc_stages = kEpiGroups / g.gpt;  // 4 stages of <= 128 columns or 2 of <= 256 fill the 512 TMEM columns
   p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
   p.wait_ns = wait_limit_ns();
@@ -588,6 +622,7 @@ ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW) 
   const GemmTcGeometry n = gemm_tc_geometry(OC, g.Kpad);
   g.BN = n.BN;
   g.n_tiles = n.n_tiles;
+  g.gpt = n.gpt;
   // patch shape: TW * TH = 128 with the least padded area (ties: the wider patch, longer contiguous runs)
   long long best = -1;
   for (int tw = 128; tw >= 4; tw >>= 1) {
@@ -628,7 +663,7 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   }
   if (((uintptr_t)a.out % 16) != 0) return cudaErrorInvalidValue;
   if (st->c != a.out) {
-    if (!encode_conv_output(&st->tmC, a.out, a.N, a.OH, a.OW, a.OC, g.BN, g.TW, g.TH)) return cudaErrorInvalidValue;
+    if (!encode_conv_output(&st->tmC, a.out, a.N, a.OH, a.OW, a.OC, g.BN / g.gpt, g.TW, g.TH)) return cudaErrorInvalidValue;
     st->c = a.out;
   }
   GemmTcParams p{};
@@ -655,7 +690,7 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
   p.w_resident = w_bytes <= (size_t)kResidentWeightBytes;
   const size_t stage_bytes = (size_t)kBM * g.row_bytes + (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes);
-  const size_t staging_bytes = (size_t)kEpiGroups * kBM * g.BN;
+  const size_t staging_bytes = (size_t)kEpiGroups * kBM * (g.BN / g.gpt);
   const size_t ring_budget = (size_t)kSmemBudget - 1024 - (p.w_resident ? w_bytes : 0) - staging_bytes;
   int stages = (int)(ring_budget / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
@@ -665,7 +700,9 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   int stride = 32;
   while (stride < g.BN) stride <<= 1;
   p.acc_stride = stride;
-  p.acc_stages = kEpiGroups;
+  p.gpt = g.gpt;
+  p.BNh = g.BN / g.gpt;
+  p.acc_stages = kEpiGroups / g.gpt;
   p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
   p.wait_ns = wait_limit_ns();

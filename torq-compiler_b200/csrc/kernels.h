@@ -102,8 +102,9 @@ struct GemmTcGeometry {
   int row_bytes;  // bytes of K per shared-memory row: 32, 64 or 128
   int k_blocks;   // K blocks of row_bytes
   int Kpad;       // k_blocks * row_bytes: row length of the packed weights
-  int BN;         // columns per N tile (multiple of 16, <= 128)
+  int BN;         // columns per N tile: a multiple of 16 up to 128, or a multiple of 32 up to 256 (gpt == 2)
   int n_tiles;
+  int gpt;        // epilogue groups that share one accumulator tile (1, or 2 for the wide tiles)
 };
 GemmTcGeometry gemm_tc_geometry(int N, int K);
 struct GemmTcArgs {
@@ -131,7 +132,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
 // as implicit GEMM on the same kernel: see gemm_tcgen05.cu.
 struct ConvTcGeometry {
   int row_bytes, icb_per_tap, k_blocks, Kpad;  // K = (kh, kw, ic): the OHWI row of a filter
-  int BN, n_tiles;
+  int BN, n_tiles, gpt;
   int TW, TH, tiles_w, tiles_h;                // output patch of a tile (TW * TH = 128)
 };
 ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW);
