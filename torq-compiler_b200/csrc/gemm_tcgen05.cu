@@ -87,8 +87,10 @@ struct GemmTcParams {
 
 // EPI: 0 = the general rescale from the 32-byte ChanParams (any shift, 64-bit arithmetic); 1 / 2 = the compact
 // Q4 records (common.cuh: one 16-byte shared-memory load, one 32-bit multiply-high per output) with / without
-// the sign term of DOUBLE_ROUND.
-template <int EPI, bool CONV>
+// the sign term of DOUBLE_ROUND; 3 = as 1 with the clamp being the whole int8 range (two saturating packs).
+// LUT: a 256-entry table is applied to the result. Integer instructions issue at half rate on this machine,
+// so whatever the epilogue does per output is a template choice, not a branch.
+template <int EPI, bool CONV, bool LUT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, GemmTcParams p) {
@@ -122,7 +124,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (p.lut && threadIdx.x >= 64 && threadIdx.x < 64 + 256) lut_s[threadIdx.x - 64] = (uint8_t)p.lut[threadIdx.x - 64];
+  if (LUT && threadIdx.x >= 64 && threadIdx.x < 64 + 256) lut_s[threadIdx.x - 64] = (uint8_t)p.lut[threadIdx.x - 64];
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                  "r"((uint32_t)p.tmem_cols)
@@ -248,7 +250,6 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t lo2 = (uint32_t)(p.clamp_min & 0xffff) * 0x10001u;
     const uint32_t hi2 = (uint32_t)(p.clamp_max & 0xffff) * 0x10001u;
     const bool vec_ok = (p.ldc & 15) == 0;
-    const bool full_range = p.clamp_min <= -128 && p.clamp_max >= 127;
     const int nfull = p.BNh >> 5;
     const uint32_t tile_bytes = (uint32_t)kBM * p.BNh;
     // one staging tile per group for the TMA store of the output
@@ -308,7 +309,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int j = 0; j < 4; j++) {
               int acc = (int)v[g * 4 + j];
               if (CONV && corr_row) acc += corr_row[c0 + g * 4 + j];
-              if (EPI == 1) {
+              if (EPI == 1 || EPI == 3) {
                 r[j] = scale_q4_sign(acc, cps[c0 + g * 4 + j]);
               } else if (EPI == 2) {
                 r[j] = scale_q4(acc, cps[c0 + g * 4 + j]);
@@ -317,8 +318,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 r[j] = scale_cp<false>(acc + c.bias, c) + p.out_zp;
               }
             }
-            w4[g] = (EPI == 1 && full_range) ? sat_pack4(r[0], r[1], r[2], r[3]) : clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
-            if (p.lut) {  // out = table[value + 128], byte by byte
+            w4[g] = EPI == 3 ? sat_pack4(r[0], r[1], r[2], r[3]) : clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
+            if (LUT) {  // out = table[value + 128], byte by byte
               const uint32_t x = w4[g] ^ 0x80808080u;
               w4[g] = (uint32_t)lut_s[x & 0xff] | ((uint32_t)lut_s[(x >> 8) & 0xff] << 8) |
                       ((uint32_t)lut_s[(x >> 16) & 0xff] << 16) | ((uint32_t)lut_s[x >> 24] << 24);
@@ -465,7 +466,39 @@ bool encode_conv_output(CUtensorMap* map, const void* base, int N, int OH, int O
 
 }  // namespace
 
-GemmTcGeometry gemm_tc_geometry(int N, int K) {
+
+namespace {
+typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, GemmTcParams);
+// [EPI][LUT] for the plain GEMM and for the implicit-GEMM convolution
+GemmKernelFn gemm_kernel_for(bool conv, int epi, bool lut) {
+  static const GemmKernelFn plain[4][2] = {
+      {gemm_i8_tc_kernel<0, false, false>, gemm_i8_tc_kernel<0, false, true>},
+      {gemm_i8_tc_kernel<1, false, false>, gemm_i8_tc_kernel<1, false, true>},
+      {gemm_i8_tc_kernel<2, false, false>, gemm_i8_tc_kernel<2, false, true>},
+      {gemm_i8_tc_kernel<3, false, false>, gemm_i8_tc_kernel<3, false, true>},
+  };
+  static const GemmKernelFn convk[4][2] = {
+      {gemm_i8_tc_kernel<0, true, false>, gemm_i8_tc_kernel<0, true, true>},
+      {gemm_i8_tc_kernel<1, true, false>, gemm_i8_tc_kernel<1, true, true>},
+      {gemm_i8_tc_kernel<2, true, false>, gemm_i8_tc_kernel<2, true, true>},
+      {gemm_i8_tc_kernel<3, true, false>, gemm_i8_tc_kernel<3, true, true>},
+  };
+  return conv ? convk[epi][lut ? 1 : 0] : plain[epi][lut ? 1 : 0];
+}
+// Every kernel needs its dynamic shared-memory limit raised once per device.
+cudaError_t gemm_kernels_set_smem(bool conv) {
+  for (int e = 0; e < 4; e++)
+    for (int l = 0; l < 2; l++) {
+      const cudaError_t err = cudaFuncSetAttribute(gemm_kernel_for(conv, e, l != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+      if (err != cudaSuccess) return err;
+    }
+  return cudaSuccess;
+}
+// EPI 1 with a clamp that is the whole int8 range packs with two saturating conversions (EPI 3)
+int gemm_epi_variant(int epi, int clamp_min, int clamp_max) { return epi == 1 && clamp_min <= -128 && clamp_max >= 127 ? 3 : epi; }
+}  // namespace
+
+GemmTcGeometry gemm_tc_geometry(int N, int K, long long M) {
   GemmTcGeometry g{};
   g.row_bytes = K <= 32 ? 32 : K <= 64 ? 64 : 128;
   g.k_blocks = (K + g.row_bytes - 1) / g.row_bytes;
@@ -502,7 +535,9 @@ GemmTcGeometry gemm_tc_geometry(int N, int K) {
         wbn = bn;
       }
     }
-    if (wt > 0 && wtotal <= best_total + best_total / 16) {
+    // wide tiles only when they still give every SM a tile: few rows want many small tiles
+    const long long m_tiles = (M + kBM - 1) / kBM;
+    if (wt > 0 && wtotal <= best_total + best_total / 16 && m_tiles * wt >= 148) {
       g.BN = wbn;
       g.n_tiles = wt;
       g.gpt = 2;
@@ -526,7 +561,7 @@ GemmTcState* gemm_tc_state_new() { return new GemmTcState(); }
 void gemm_tc_state_free(GemmTcState* s) { delete s; }
 
 cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t stream) {
-  const GemmTcGeometry g = gemm_tc_geometry(a.N, a.K);
+  const GemmTcGeometry g = gemm_tc_geometry(a.N, a.K, a.M);
   if (st->a != a.a) {
     if (!encode_2d(&st->tmA, a.a, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)a.lda, kBM, g.row_bytes))
       return cudaErrorInvalidValue;
@@ -586,24 +621,18 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   const size_t smem = 1024 + p.staging_off + staging_bytes;
   static std::atomic<unsigned long long> attr_set{0};
   if (first_use_on_device(attr_set)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    const cudaError_t e = gemm_kernels_set_smem(false);
     if (e != cudaSuccess) return e;
     mark_used_on_device(attr_set);
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
-  if (a.epi == 1) gemm_i8_tc_kernel<1, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  else if (a.epi == 2) gemm_i8_tc_kernel<2, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  else gemm_i8_tc_kernel<0, false><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  gemm_kernel_for(false, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr)<<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   return cudaGetLastError();
 }
 
 // ---- convolution as implicit GEMM ----
-ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW) {
+ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, int KW) {
   ConvTcGeometry g{};
   // channel block = swizzle width: the widest of 128 / 64 / 32 bytes with the least padding of IC. A last
   // block that reaches beyond IC is fine: the copy engine fills the missing channels with zeros and the
@@ -619,10 +648,6 @@ ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW) 
   g.icb_per_tap = (IC + g.row_bytes - 1) / g.row_bytes;
   g.k_blocks = KH * KW * g.icb_per_tap;
   g.Kpad = g.k_blocks * g.row_bytes;
-  const GemmTcGeometry n = gemm_tc_geometry(OC, g.Kpad);
-  g.BN = n.BN;
-  g.n_tiles = n.n_tiles;
-  g.gpt = n.gpt;
   // patch shape: TW * TH = 128 with the least padded area (ties: the wider patch, longer contiguous runs)
   long long best = -1;
   for (int tw = 128; tw >= 4; tw >>= 1) {
@@ -636,6 +661,10 @@ ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW) 
   }
   g.tiles_w = (OW + g.TW - 1) / g.TW;
   g.tiles_h = (OH + g.TH - 1) / g.TH;
+  const GemmTcGeometry n = gemm_tc_geometry(OC, g.Kpad, (long long)N * g.tiles_w * g.tiles_h * kBM);
+  g.BN = n.BN;
+  g.n_tiles = n.n_tiles;
+  g.gpt = n.gpt;
   return g;
 }
 
@@ -644,14 +673,14 @@ bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int 
   if (IC % 16 != 0 || OC % 16 != 0 || stride_h != stride_w || stride_h < 1 || stride_h > 2 || dil_h != 1 || dil_w != 1 ||
       KH < 1 || KW < 1 || KH * KW > 49 || KH * KW == 1)
     return false;
-  const ConvTcGeometry g = conv_tc_geometry(OH, OW, IC, OC, KH, KW);
+  const ConvTcGeometry g = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW);
   if (g.TW * stride_w > 256 || g.TH * stride_h > 256) return false;  // TMA box extents
   if ((long long)N * g.tiles_w * g.tiles_h >= (1ll << 30)) return false;
   return H >= 1 && W >= 1;
 }
 
 cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t stream) {
-  const ConvTcGeometry g = conv_tc_geometry(a.OH, a.OW, a.IC, a.OC, a.KH, a.KW);
+  const ConvTcGeometry g = conv_tc_geometry(a.N, a.OH, a.OW, a.IC, a.OC, a.KH, a.KW);
   if (st->a != a.x) {
     if (!encode_conv_input(&st->tmA, a.x, a.N, a.H, a.W, a.IC, g.row_bytes, g.TW, g.TH, a.stride)) return cudaErrorInvalidValue;
     st->a = a.x;
@@ -711,19 +740,13 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   const size_t smem = 1024 + p.staging_off + staging_bytes;
   static std::atomic<unsigned long long> attr_set{0};
   if (first_use_on_device(attr_set)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_i8_tc_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    const cudaError_t e = gemm_kernels_set_smem(true);
     if (e != cudaSuccess) return e;
     mark_used_on_device(attr_set);
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
-  if (a.epi == 1) gemm_i8_tc_kernel<1, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  else if (a.epi == 2) gemm_i8_tc_kernel<2, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  else gemm_i8_tc_kernel<0, true><<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
+  gemm_kernel_for(true, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr)<<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
   return cudaGetLastError();
 }
 

@@ -106,11 +106,11 @@ struct GemmTcGeometry {
   int n_tiles;
   int gpt;        // epilogue groups that share one accumulator tile (1, or 2 for the wide tiles)
 };
-GemmTcGeometry gemm_tc_geometry(int N, int K);
+GemmTcGeometry gemm_tc_geometry(int N, int K, long long M);  // M rows: few rows keep the narrow tiles
 struct GemmTcArgs {
   const int8_t* a;        // [M, K] int8, row pitch lda bytes (multiple of 16)
   long long lda;
-  const int8_t* w;        // packed [n_tiles * BN][Kpad] per gemm_tc_geometry(N, K), zero padded
+  const int8_t* w;        // packed [n_tiles * BN][Kpad] per gemm_tc_geometry(N, K, M), zero padded
   const ChanParams* chan; // [n_tiles * BN]
   int8_t* out;            // [M, N] int8, row pitch ldc bytes
   long long ldc;
@@ -135,7 +135,7 @@ struct ConvTcGeometry {
   int BN, n_tiles, gpt;
   int TW, TH, tiles_w, tiles_h;                // output patch of a tile (TW * TH = 128)
 };
-ConvTcGeometry conv_tc_geometry(int OH, int OW, int IC, int OC, int KH, int KW);
+ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, int KW);
 bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w,
                        int OH, int OW);
 struct ConvTcArgs {

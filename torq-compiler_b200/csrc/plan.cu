@@ -723,7 +723,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             (long long)OC * rgroup <= 65536 && gemm_tc_supported(M / rgroup, OC * rgroup, (int)K * rgroup, K * rgroup)) {
           GemmTcArgs ga{};
           const int Ng = OC * rgroup, Kg = (int)K * rgroup;
-          const GemmTcGeometry geo = gemm_tc_geometry(Ng, Kg);
+          const GemmTcGeometry geo = gemm_tc_geometry(Ng, Kg, M / rgroup);
           ga.M = M / rgroup; ga.N = Ng; ga.K = Kg;
           ga.lda = Kg; ga.ldc = Ng;
           ga.out_zp = op.out_zp; ga.clamp_min = op.clamp_min; ga.clamp_max = op.clamp_max;
@@ -774,7 +774,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         // the direct dp4a kernel is faster there)
         if (!fc && !pointwise && op.weight_zp == 0 && !force_simt() && IC != 16 &&
             conv_tc_supported(N, H, W, IC, OC, KH, KW, op.stride_h, op.stride_w, op.dil_h, op.dil_w, OH, OW)) {
-          const ConvTcGeometry geo = conv_tc_geometry(OH, OW, IC, OC, KH, KW);
+          const ConvTcGeometry geo = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW);
           ConvTcArgs ca{};
           ca.N = N; ca.H = H; ca.W = W; ca.IC = IC; ca.OC = OC; ca.KH = KH; ca.KW = KW; ca.OH = OH; ca.OW = OW;
           ca.stride = op.stride_h; ca.pad_t = op.pad_t; ca.pad_l = op.pad_l;
