@@ -64,7 +64,8 @@ enum tb200_op_kind {
   TB200_OP_ADD = 6,           /* torq_hl.add : rescale,rescale -> add -> rescale */
   TB200_OP_MUL = 7,           /* torq_hl.mul : rescale,rescale -> mul -> rescale */
   TB200_OP_TABLE = 8,         /* torq_hl.table : out = table[x + 128] */
-  TB200_OP_RESCALE = 9,       /* standalone tosa.rescale i8->i8 (torq_hl.fma form) */
+  TB200_OP_RESCALE = 9,       /* standalone tosa.rescale (torq_hl.fma form): i8 -> i8 on the layer path; any of i8 / i16 / i32 in and
+                               * out (TosaToTorqHL/Patterns.cpp:1735-1947) on the generic one, clamped to the result type's range */
   TB200_OP_RESIZE_NN2X = 10,  /* torq_hl.resize_nearest_neighbor, 2x replicate */
   TB200_OP_CONCAT = 11,       /* channel concat of in0,in1 with per-input rescale */
   TB200_OP_SUB = 12,          /* as ADD with in1 negated after its rescale */
@@ -89,9 +90,42 @@ enum tb200_op_kind {
                                * tests/testdata/torch_ops/matmul_dql_q8_0.mlir, ExpandWeightsPattern.cpp:350-376);
                                * weights int8 [K, N], bias slot = scales bf16 [K/i0, N], multiplier slot = zero
                                * points int8 [K/i0, N] or -1 */
+  /* tensor ops outside the layer set: what the reference's fixtures exercise around the layers
+   * (tests/testdata/tosa_ops: cast-*, Elementwise_*, rescale-*, transpose-*, pad_*, identity-stride-offset-*,
+   * reduce-*, argmax-*). Dense row-major tensors of rank <= 4, element types i8 / i16 / i32 / f32 / bf16;
+   * a boolean (i1) tensor is an i8 tensor holding 0 or 1. */
+  TB200_OP_EW = 48,           /* elementwise, i0 = enum tb200_ew_fn, i1 = its argument (tosa.mul shift, tosa.arithmetic_right_shift
+                               * round). Unary (in1 = -1) or binary; both operands and the result have the same rank and an
+                               * extent-1 dimension of an operand is broadcast. Integers are computed in int32 (wrapping) and
+                               * truncated to the result type, floats in fp32 and rounded once (nearest even). NEGATE uses
+                               * in0_zp / out_zp, CLAMP uses clamp_min / clamp_max (integers) or f0 / f1 (floats). */
+  TB200_OP_TRANSPOSE = 49,    /* tosa.transpose: out dimension d is in dimension i<d> (i0..i3) */
+  TB200_OP_SLICE = 50,        /* tosa.slice / tensor.extract_slice with unit strides: i0..i3 = first index per dimension */
+  TB200_OP_PAD = 51,          /* tosa.pad: i0..i3 = leading padding per dimension, pad_value = the constant */
+  TB200_OP_CONCAT_AXIS = 52,  /* tosa.concat of in0, in1 along axis i0 (plain copy, any element type) */
+  TB200_OP_REDUCE = 53,       /* tosa.reduce_sum / reduce_max / reduce_min / argmax along axis i1: i0 = 0 sum, 1 max, 2 min,
+                               * 3 argmax. The result's shape is whatever the op record's output tensor says (the axis kept
+                               * with extent 1, or dropped): only its element count matters. Integer sums wrap in int32;
+                               * argmax gives the first index of the maximum as i32 */
   TB200_OP_ALLREDUCE = 40,    /* sum of the fp32 partial results of the i0 GPUs of a tensor-parallel group
                                * (this one is rank i1), rounded to bf16; only inside the fused decode step */
 };
+
+enum tb200_ew_fn {
+  /* unary */
+  TB200_EW_CAST = 0, TB200_EW_ABS = 1, TB200_EW_NEGATE = 2, TB200_EW_BITWISE_NOT = 3, TB200_EW_LOGICAL_NOT = 4,
+  TB200_EW_CLZ = 5, TB200_EW_CLAMP = 6, TB200_EW_CEIL = 7, TB200_EW_FLOOR = 8,
+  /* binary */
+  TB200_EW_ADD = 16, TB200_EW_SUB = 17, TB200_EW_MUL = 18, TB200_EW_MAX = 19, TB200_EW_MIN = 20,
+  TB200_EW_AND = 21, TB200_EW_OR = 22, TB200_EW_XOR = 23, TB200_EW_LSL = 24, TB200_EW_ASR = 25,
+  TB200_EW_EQ = 26, TB200_EW_GT = 27, TB200_EW_GE = 28, TB200_EW_LOGICAL_AND = 29, TB200_EW_LOGICAL_OR = 30,
+  TB200_EW_LOGICAL_XOR = 31,
+};
+
+/* tb200_op_t::flags of TB200_OP_RESCALE and TB200_OP_EW (CAST) */
+#define TB200_FLAG_INPUT_UNSIGNED 1u  /* tosa.rescale input_unsigned: the input bytes are uint8 / uint16 */
+#define TB200_FLAG_OUTPUT_UNSIGNED 2u /* tosa.rescale output_unsigned */
+#define TB200_FLAG_BOOL_RESULT 4u     /* the result is a boolean (0 / 1 in an i8 tensor): CAST writes x != 0 */
 
 enum tb200_requant_mode {
   TB200_REQUANT_TOSA = 0, /* (A) TOSA apply_scale_32, the host/llvm-cpu arithmetic */

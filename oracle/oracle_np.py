@@ -199,3 +199,144 @@ def concat2(a, b, a_zp, a_mult, a_shift, b_zp, b_mult, b_shift, out_zp, double_r
     ra = rescale(a, a_mult, a_shift, a_zp, out_zp, double_round=double_round)
     rb = rescale(b, b_mult, b_shift, b_zp, out_zp, double_round=double_round)
     return np.concatenate([ra, rb], axis=-1)
+
+
+# ---- tensor ops outside the layer set: a second, element-by-element statement with Python integers -------------------
+# (the vectorised one is oracle/generic_ops.py; the golden generator wants the two to agree bit for bit)
+
+def _wrap_py(v: int, bits: int) -> int:
+    v &= (1 << bits) - 1
+    return v - (1 << bits) if v >> (bits - 1) else v
+
+
+def _bf16_round_py(f: float) -> int:
+    import struct
+    u = struct.unpack("<I", struct.pack("<f", f))[0]
+    if f != f:
+        return 0x7FC0
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF
+
+
+def _f32(v: float) -> float:
+    return float(np.float32(v))
+
+
+def ew_elementwise(fn_name, a, a_dtype, b, b_dtype, out_dtype, out_shape, *, arg=0, in_zp=0, out_zp=0, clamp=(0, 0),
+                   fclamp=(0.0, 0.0), bool_result=False):
+    """Same contract as generic_ops.ew, one element at a time."""
+    import math
+    bits = {"i8": 8, "i16": 16, "i32": 32}
+
+    def elems(x, dt):
+        x = np.broadcast_to(x, out_shape).reshape(-1)
+        if dt == "bf16":
+            return [float(v) for v in (x.astype(np.uint32) << 16).view(np.float32)], True
+        if dt == "f32":
+            return [float(v) for v in x], True
+        return [int(v) for v in x], False
+
+    xs, xf = elems(a, a_dtype)
+    ys, yf = elems(b, b_dtype) if b is not None else ([0] * len(xs), False)
+    flt = xf or yf
+    out = []
+    for x, y in zip(xs, ys):
+        if flt:
+            x, y = _f32(x), _f32(y)
+            r = {"cast": lambda: x, "abs": lambda: abs(x), "negate": lambda: -x, "ceil": lambda: math.copysign(float(math.ceil(x)), x) if math.ceil(x) == 0 else float(math.ceil(x)),
+                 "floor": lambda: math.copysign(float(math.floor(x)), x) if math.floor(x) == 0 else float(math.floor(x)), "clamp": lambda: min(max(x, _f32(fclamp[0])), _f32(fclamp[1])),
+                 "add": lambda: _f32(x + y), "sub": lambda: _f32(x - y), "mul": lambda: _f32(x * y), "maximum": lambda: max(x, y),
+                 "minimum": lambda: min(x, y), "equal": lambda: int(x == y), "greater": lambda: int(x > y),
+                 "greater_equal": lambda: int(x >= y)}[fn_name]()
+            if fn_name in ("equal", "greater", "greater_equal"):
+                out.append(r)
+            elif fn_name == "cast" and bool_result:
+                out.append(int(x != 0.0))
+            elif out_dtype in bits:
+                lo, hi = -(1 << (bits[out_dtype] - 1)), (1 << (bits[out_dtype] - 1)) - 1
+                if r != r:
+                    q = 0
+                else:
+                    fl = math.floor(r)
+                    d = r - fl
+                    q = fl + (1 if d > 0.5 or (d == 0.5 and fl % 2 != 0) else 0)  # nearest, ties to even
+                out.append(min(max(q, lo), hi))
+            elif out_dtype == "bf16":
+                out.append(_bf16_round_py(_f32(r)))
+            else:
+                out.append(_f32(r))
+            continue
+        x, y = _wrap_py(x, 32), _wrap_py(y, 32)
+        if fn_name == "cast":
+            r = int(x != 0) if bool_result else x
+            if out_dtype in ("f32", "bf16"):
+                out.append(_bf16_round_py(_f32(float(x))) if out_dtype == "bf16" else _f32(float(x)))
+                continue
+        elif fn_name == "abs":
+            r = abs(x)
+        elif fn_name == "negate":
+            r = out_zp - (x - in_zp)
+        elif fn_name == "bitwise_not":
+            r = ~x
+        elif fn_name == "logical_not":
+            r = int(x == 0)
+        elif fn_name == "clz":
+            r = 32 - (x & 0xFFFFFFFF).bit_length()
+        elif fn_name == "clamp":
+            r = min(max(x, clamp[0]), clamp[1])
+        elif fn_name == "add":
+            r = x + y
+        elif fn_name == "sub":
+            r = x - y
+        elif fn_name == "mul":
+            r = (x * y + (1 << (arg - 1))) >> arg if arg > 0 else x * y
+        elif fn_name == "maximum":
+            r = max(x, y)
+        elif fn_name == "minimum":
+            r = min(x, y)
+        elif fn_name == "bitwise_and":
+            r = x & y
+        elif fn_name == "bitwise_or":
+            r = x | y
+        elif fn_name == "bitwise_xor":
+            r = x ^ y
+        elif fn_name == "logical_left_shift":
+            r = x << (y & 31)
+        elif fn_name == "arithmetic_right_shift":
+            sft = y & 31
+            r = (x >> sft) + (((x >> (sft - 1)) & 1) if arg and sft > 0 else 0)
+        elif fn_name == "equal":
+            r = int(x == y)
+        elif fn_name == "greater":
+            r = int(x > y)
+        elif fn_name == "greater_equal":
+            r = int(x >= y)
+        elif fn_name == "logical_and":
+            r = int(x != 0 and y != 0)
+        elif fn_name == "logical_or":
+            r = int(x != 0 or y != 0)
+        elif fn_name == "logical_xor":
+            r = int((x != 0) != (y != 0))
+        else:
+            raise NotImplementedError(fn_name)
+        out.append(_wrap_py(r, bits.get(out_dtype, 32)))
+    np_t = {"i8": np.int8, "i16": np.int16, "i32": np.int32, "f32": np.float32, "bf16": np.uint16}[out_dtype]
+    return np.array(out, dtype=np_t).reshape(out_shape)
+
+
+def rescale_elementwise(x, in_dtype, out_dtype, mult, shift, in_zp, out_zp, clamp, *, per_channel, double_round,
+                        input_unsigned=False):
+    bits = {"i8": 8, "i16": 16, "i32": 32}
+    flat = x.reshape(-1)
+    C = x.shape[-1]
+    out = []
+    for i, v in enumerate(int(t) for t in flat):
+        if input_unsigned:
+            v &= (1 << bits[in_dtype]) - 1
+        v = _wrap_py(v - in_zp, 32)
+        m, s = (int(mult[i % C]), int(shift[i % C])) if per_channel else (int(mult[0]), int(shift[0]))
+        rnd = 1 << (s - 1)
+        if double_round and s > 31:
+            rnd += (1 << 30) if v >= 0 else -(1 << 30)
+        r = _wrap_py((v * m + rnd) >> s, 32) + out_zp
+        out.append(_wrap_py(min(max(r, clamp[0]), clamp[1]), bits[out_dtype]))
+    return np.array(out, dtype={"i8": np.int8, "i16": np.int16, "i32": np.int32}[out_dtype]).reshape(x.shape)

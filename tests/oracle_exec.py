@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import numpy as np
 
+from oracle import generic_ops as gops
 from oracle import oracle as oc
 
 
@@ -15,7 +16,8 @@ def _rq(op, mode=None):
 
 def run_graph(graph, inputs, keep_all=False):
     """inputs: list of numpy arrays in graph.inputs order. Returns outputs (and all tensors if keep_all)."""
-    vals = {t.id: np.ascontiguousarray(a) for t, a in zip(graph.inputs, inputs)}
+    vals = {t.id: t.data for t in graph.tensors if t.kind == 3 and t.data is not None}  # constants used as operands
+    vals.update({t.id: np.ascontiguousarray(a) for t, a in zip(graph.inputs, inputs)})
     for op in graph.ops:
         a = op.attrs
         x = vals[op.inputs[0].id]
@@ -48,8 +50,32 @@ def run_graph(graph, inputs, keep_all=False):
                           bool(a["double_round"]), a["clamp_min"], a["clamp_max"], a_lshift=a["i0"], b_lshift=a["i1"])
         elif k == "table":
             y = oc.table(x, op.consts["table"].data)
+        elif k == "rescale" and (op.inputs[0].dtype, op.outputs[0].dtype, a.get("flags", 0)) != ("i8", "i8", 0):
+            y = gops.rescale(x, op.inputs[0].dtype, op.outputs[0].dtype, op.consts["multiplier"].data, op.consts["shift"].data,
+                             a["in0_zp"], a["out_zp"], (a["clamp_min"], a["clamp_max"]), per_channel=bool(a["per_channel"]),
+                             double_round=bool(a["double_round"]), input_unsigned=bool(a.get("flags", 0) & 1),
+                             output_unsigned=bool(a.get("flags", 0) & 2))
         elif k == "rescale":
             y = oc.rescale(x, _rq(op), a["in0_zp"])
+        elif k == "ew":
+            second = vals[op.inputs[1].id] if len(op.inputs) > 1 else None
+            y = gops.ew(a["i0"], x, op.inputs[0].dtype, second, op.inputs[1].dtype if second is not None else None,
+                        op.outputs[0].dtype, arg=a["i1"], in_zp=a["in0_zp"], out_zp=a["out_zp"],
+                        clamp=(a["clamp_min"], a["clamp_max"]), fclamp=(a["f0"], a["f1"]), bool_result=bool(a.get("flags", 0) & 4))
+            y = np.broadcast_to(y, op.outputs[0].shape) if y.shape != tuple(op.outputs[0].shape) else y
+        elif k == "transpose":
+            y = np.transpose(x, [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim])
+        elif k == "slice":
+            start = [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim]
+            y = x[tuple(slice(s, s + n) for s, n in zip(start, op.outputs[0].shape))]
+        elif k == "pad":
+            before = [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim]
+            widths = [(b, o - b - d) for b, o, d in zip(before, op.outputs[0].shape, x.shape)]
+            y = np.pad(x, widths, constant_values=np.array(a["pad_value"]).astype(x.dtype))
+        elif k == "concat_axis":
+            y = np.concatenate([x, vals[op.inputs[1].id]], axis=a["i0"])
+        elif k == "reduce":
+            y = gops.reduce(a["i0"], x, op.inputs[0].dtype, a["i1"], op.outputs[0].shape, op.outputs[0].dtype)
         elif k == "resize_nn2x":
             y = oc.resize_nn2x(x)
         elif k == "concat":
@@ -60,6 +86,6 @@ def run_graph(graph, inputs, keep_all=False):
         else:
             raise NotImplementedError(k)
         assert tuple(y.shape) == tuple(op.outputs[0].shape), (k, y.shape, op.outputs[0].shape)
-        vals[op.outputs[0].id] = y
+        vals[op.outputs[0].id] = np.ascontiguousarray(y)
     outs = [vals[t.id] for t in graph.outputs]
     return (outs, vals) if keep_all else outs

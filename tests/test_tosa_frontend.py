@@ -67,8 +67,12 @@ def test_add_chain_and_unsupported_ops():
     assert [op.kind for op in g.ops] == ["add"]
     a = g.ops[0].attrs
     assert (a["in0_zp"], a["in1_zp"], a["in0_shift"], a["out_mult"], a["out_shift"], a["out_zp"]) == (-3, 7, 11, 1200000000, 49, -2)
+    # another op in the place of the add is not the fused form: the chain is read op by op (generic rescales + elementwise op)
+    g2 = tosa_frontend.build_graph(ADD.replace("tosa.add", "tosa.bitwise_and"))
+    assert [op.kind for op in g2.ops] == ["rescale", "rescale", "ew", "rescale"]
+    assert g2.ops[0].outputs[0].dtype == "i32" and g2.ops[3].outputs[0].dtype == "i8"
     with pytest.raises(NotImplementedError):
-        tosa_frontend.build_graph(ADD.replace("tosa.add", "tosa.bitwise_and"))
+        tosa_frontend.build_graph(ADD.replace("tosa.add", "tosa.scatter"))
 
 
 TWO_STAGE = '''

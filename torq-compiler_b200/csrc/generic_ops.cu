@@ -1,0 +1,233 @@
+// Tensor ops outside the layer set (TB200_OP_EW, the generic tosa.rescale, TRANSPOSE / SLICE / PAD /
+// CONCAT_AXIS, REDUCE): what the reference's op fixtures exercise around the layers
+// (tests/testdata/tosa_ops: cast-*, Elementwise_*, rescale-*, transpose-*, pad_*, reduce-*, argmax-*).
+// All are bandwidth-bound index arithmetic on dense row-major tensors of rank <= 4 with element types
+// i8 / i16 / i32 / f32 / bf16. Integers are computed in int32 with wrap-around and truncated to the result
+// type; floats in fp32, rounded once to nearest even; float -> int casts round to nearest even and saturate.
+#include <cuda_bf16.h>
+
+#include "../../include/torq_b200_ops.h"
+#include "kernels.h"
+
+namespace tb200 {
+
+namespace {
+
+__device__ __forceinline__ bool is_float_dtype(int d) { return d == TB200_F32 || d == TB200_BF16; }
+
+__device__ __forceinline__ int load_int(const void* p, int dtype, long long i) {
+  switch (dtype) {
+    case TB200_I8: return ((const int8_t*)p)[i];
+    case TB200_I16: return ((const int16_t*)p)[i];
+    default: return ((const int32_t*)p)[i];
+  }
+}
+__device__ __forceinline__ float load_float(const void* p, int dtype, long long i) {
+  switch (dtype) {
+    case TB200_F32: return ((const float*)p)[i];
+    case TB200_BF16: return __uint_as_float((uint32_t)((const uint16_t*)p)[i] << 16);
+    default: return (float)load_int(p, dtype, i);
+  }
+}
+__device__ __forceinline__ void store_int(void* p, int dtype, long long i, int v) {
+  switch (dtype) {
+    case TB200_I8: ((int8_t*)p)[i] = (int8_t)v; break;
+    case TB200_I16: ((int16_t*)p)[i] = (int16_t)v; break;
+    case TB200_I32: ((int32_t*)p)[i] = v; break;
+    case TB200_F32: ((float*)p)[i] = (float)v; break;
+    default: ((uint16_t*)p)[i] = __bfloat16_as_ushort(__float2bfloat16_rn((float)v)); break;
+  }
+}
+__device__ __forceinline__ void store_float(void* p, int dtype, long long i, float v) {
+  switch (dtype) {
+    case TB200_F32: ((float*)p)[i] = v; break;
+    case TB200_BF16: ((uint16_t*)p)[i] = __bfloat16_as_ushort(__float2bfloat16_rn(v)); break;
+    default: {  // float -> int: nearest even, saturating, NaN -> 0
+      const int bits = dtype == TB200_I8 ? 8 : dtype == TB200_I16 ? 16 : 32;
+      const float lo = -ldexpf(1.0f, bits - 1), hi = ldexpf(1.0f, bits - 1);
+      int r;
+      if (v != v) r = 0;
+      else if (v <= lo) r = bits == 32 ? INT32_MIN : -(1 << (bits - 1));
+      else if (v >= hi) r = bits == 32 ? INT32_MAX : (1 << (bits - 1)) - 1;
+      else r = __float2int_rn(v);
+      if (bits < 32) r = max(-(1 << (bits - 1)), min((1 << (bits - 1)) - 1, r));
+      store_int(p, dtype, i, r);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) ew_kernel(EwArgs a) {
+  const bool flt = is_float_dtype(a.a_dtype) || (a.b && is_float_dtype(a.b_dtype));
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+    long long ia = i, ib = i;
+    if (!a.contiguous) {  // broadcast: operand offsets from the output coordinates
+      long long r = i;
+      ia = ib = 0;
+#pragma unroll
+      for (int d = 3; d >= 0; d--) {
+        const int c = (int)(r % a.dims[d]);
+        r /= a.dims[d];
+        ia += (long long)c * a.a_str[d];
+        ib += (long long)c * a.b_str[d];
+      }
+    }
+    if (flt) {
+      const float x = load_float(a.a, a.a_dtype, ia);
+      const float y = a.b ? load_float(a.b, a.b_dtype, ib) : 0.f;
+      float r = 0.f;
+      int cmp = -1;
+      switch (a.fn) {
+        case TB200_EW_CAST: r = x; if (a.bool_result) cmp = x != 0.f; break;
+        case TB200_EW_ABS: r = fabsf(x); break;
+        case TB200_EW_NEGATE: r = -x; break;
+        case TB200_EW_CLAMP: r = fminf(fmaxf(x, a.fmin), a.fmax); break;
+        case TB200_EW_CEIL: r = ceilf(x); break;
+        case TB200_EW_FLOOR: r = floorf(x); break;
+        case TB200_EW_ADD: r = x + y; break;
+        case TB200_EW_SUB: r = x - y; break;
+        case TB200_EW_MUL: r = x * y; break;
+        case TB200_EW_MAX: r = fmaxf(x, y); break;
+        case TB200_EW_MIN: r = fminf(x, y); break;
+        case TB200_EW_EQ: cmp = x == y; break;
+        case TB200_EW_GT: cmp = x > y; break;
+        case TB200_EW_GE: cmp = x >= y; break;
+        default: break;
+      }
+      if (cmp >= 0) store_int(a.out, a.out_dtype, i, cmp);
+      else store_float(a.out, a.out_dtype, i, r);
+    } else {
+      const int x = load_int(a.a, a.a_dtype, ia);
+      const int y = a.b ? load_int(a.b, a.b_dtype, ib) : 0;
+      int r = 0;
+      switch (a.fn) {
+        case TB200_EW_CAST: r = a.bool_result ? (x != 0) : x; break;
+        case TB200_EW_ABS: r = x < 0 ? (int)(0u - (uint32_t)x) : x; break;
+        case TB200_EW_NEGATE: r = (int)((uint32_t)a.out_zp - ((uint32_t)x - (uint32_t)a.in_zp)); break;
+        case TB200_EW_BITWISE_NOT: r = ~x; break;
+        case TB200_EW_LOGICAL_NOT: r = x == 0; break;
+        case TB200_EW_CLZ: r = __clz(x); break;
+        case TB200_EW_CLAMP: r = max(a.clamp_min, min(a.clamp_max, x)); break;
+        case TB200_EW_ADD: r = (int)((uint32_t)x + (uint32_t)y); break;
+        case TB200_EW_SUB: r = (int)((uint32_t)x - (uint32_t)y); break;
+        case TB200_EW_MUL:
+          if (a.arg > 0) r = (int)(((long long)x * y + (1ll << (a.arg - 1))) >> a.arg);
+          else r = (int)((uint32_t)x * (uint32_t)y);
+          break;
+        case TB200_EW_MAX: r = max(x, y); break;
+        case TB200_EW_MIN: r = min(x, y); break;
+        case TB200_EW_AND: r = x & y; break;
+        case TB200_EW_OR: r = x | y; break;
+        case TB200_EW_XOR: r = x ^ y; break;
+        case TB200_EW_LSL: r = (int)((uint32_t)x << (y & 31)); break;
+        case TB200_EW_ASR: {
+          const int s = y & 31;
+          r = x >> s;
+          if (a.arg && s > 0) r += (x >> (s - 1)) & 1;
+          break;
+        }
+        case TB200_EW_EQ: r = x == y; break;
+        case TB200_EW_GT: r = x > y; break;
+        case TB200_EW_GE: r = x >= y; break;
+        case TB200_EW_LOGICAL_AND: r = (x != 0) && (y != 0); break;
+        case TB200_EW_LOGICAL_OR: r = (x != 0) || (y != 0); break;
+        case TB200_EW_LOGICAL_XOR: r = (x != 0) != (y != 0); break;
+        default: break;
+      }
+      store_int(a.out, a.out_dtype, i, r);
+    }
+  }
+}
+
+// tosa.rescale between integer types (scale32): v = in - in_zp (int32, wrapping), apply_scale_32, + out_zp, clamp.
+__global__ void __launch_bounds__(256) rescale_generic_kernel(RescaleGenericArgs a) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+    int x = load_int(a.x, a.in_dtype, i);
+    if (a.input_unsigned) x &= a.in_dtype == TB200_I8 ? 0xff : a.in_dtype == TB200_I16 ? 0xffff : -1;
+    const int v = (int)((uint32_t)x - (uint32_t)a.in_zp);
+    const int c = a.per_channel ? (int)(i % a.C) : 0;
+    const int m = a.mult[c], s = a.shift[c];
+    long long rnd = 1ll << (s - 1);
+    if (a.double_round && s > 31) rnd += v >= 0 ? (1ll << 30) : -(1ll << 30);
+    const int r = (int)(((long long)v * m + rnd) >> s);
+    const long long q = (long long)r + a.out_zp;
+    const long long clamped = q < a.clamp_min ? a.clamp_min : q > a.clamp_max ? a.clamp_max : q;
+    store_int(a.out, a.out_dtype, i, (int)clamped);
+  }
+}
+
+// out[o] = in[in_offset + sum (o_d - lo_d) * in_str_d] when every (o_d - lo_d) lies in [0, in_dims_d), else the pad
+// value; the output element sits at out_offset + sum o_d * out_str_d. One kernel for transpose, slice, pad and concat.
+template <typename T>
+__global__ void __launch_bounds__(256) strided_copy_kernel(StridedCopyArgs a) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const T* src = (const T*)a.in;
+  T* dst = (T*)a.out;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+    long long r = i, si = a.in_offset, di = a.out_offset;
+    bool inside = true;
+#pragma unroll
+    for (int d = 3; d >= 0; d--) {
+      const int c = (int)(r % a.dims[d]);
+      r /= a.dims[d];
+      const int ci = c - a.lo[d];
+      inside = inside && ci >= 0 && ci < a.in_dims[d];
+      si += (long long)ci * a.in_str[d];
+      di += (long long)c * a.out_str[d];
+    }
+    dst[di] = inside ? src[si] : (T)a.pad_value;
+  }
+}
+
+// x viewed as [outer, axis, inner]; one thread per (outer, inner).
+__global__ void __launch_bounds__(256) reduce_kernel(ReduceArgs a) {
+  const long long total = (long long)a.outer * a.inner;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long o = i / a.inner, in = i - o * a.inner;
+  const long long base = o * a.axis * a.inner + in;
+  if (is_float_dtype(a.in_dtype)) {
+    float best = load_float(a.x, a.in_dtype, base);
+    int arg = 0;
+    for (int k = 1; k < a.axis; k++) {
+      const float v = load_float(a.x, a.in_dtype, base + (long long)k * a.inner);
+      if (a.fn == 2 ? v < best : v > best) { best = v; arg = k; }
+    }
+    if (a.fn == 3) store_int(a.out, a.out_dtype, i, arg);
+    else store_float(a.out, a.out_dtype, i, best);
+  } else {
+    int best = load_int(a.x, a.in_dtype, base), arg = 0;
+    uint32_t sum = (uint32_t)best;
+    for (int k = 1; k < a.axis; k++) {
+      const int v = load_int(a.x, a.in_dtype, base + (long long)k * a.inner);
+      sum += (uint32_t)v;
+      if (a.fn == 2 ? v < best : v > best) { best = v; arg = k; }
+    }
+    store_int(a.out, a.out_dtype, i, a.fn == 0 ? (int)sum : a.fn == 3 ? arg : best);
+  }
+}
+
+unsigned grid_for(long long n) {
+  const long long blocks = (n + 255) / 256;
+  const long long cap = (long long)current_sm_count() * 16;
+  return (unsigned)(blocks < 1 ? 1 : blocks < cap ? blocks : cap);
+}
+
+}  // namespace
+
+void launch_ew(const EwArgs& a, cudaStream_t stream) { ew_kernel<<<grid_for(a.n), 256, 0, stream>>>(a); }
+void launch_rescale_generic(const RescaleGenericArgs& a, cudaStream_t stream) {
+  rescale_generic_kernel<<<grid_for(a.n), 256, 0, stream>>>(a);
+}
+void launch_strided_copy(const StridedCopyArgs& a, cudaStream_t stream) {
+  if (a.elem_bytes == 1) strided_copy_kernel<uint8_t><<<grid_for(a.n), 256, 0, stream>>>(a);
+  else if (a.elem_bytes == 2) strided_copy_kernel<uint16_t><<<grid_for(a.n), 256, 0, stream>>>(a);
+  else strided_copy_kernel<uint32_t><<<grid_for(a.n), 256, 0, stream>>>(a);
+}
+void launch_reduce(const ReduceArgs& a, cudaStream_t stream) {
+  const long long total = (long long)a.outer * a.inner;
+  reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
+}
+
+}  // namespace tb200

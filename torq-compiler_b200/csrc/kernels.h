@@ -245,6 +245,53 @@ bool decode_step_supported(int B, int H, int n_q, int n_kv, int D, int I, int V)
 size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int sm_count, int tp, DecodeStepArgs* offsets);
 cudaError_t launch_decode_step(DecodeStepArgs a, cudaStream_t stream);
 
+// ---- tensor ops outside the layer set (generic_ops.cu); dtypes are enum tb200_dtype values ----
+struct EwArgs {
+  const void* a;
+  const void* b;   // null for a unary function
+  void* out;
+  long long n;     // output elements
+  int fn, arg;     // enum tb200_ew_fn and its argument
+  int a_dtype, b_dtype, out_dtype;
+  int in_zp, out_zp, clamp_min, clamp_max;
+  float fmin, fmax;
+  int bool_result;
+  int contiguous;  // both operands have the output's shape: element i of each meets element i of the result
+  int dims[4];     // output extents (leading dimensions padded with 1)
+  int a_str[4], b_str[4];  // element strides of the operands per output dimension, 0 where they broadcast
+};
+void launch_ew(const EwArgs& a, cudaStream_t stream);
+struct RescaleGenericArgs {
+  const void* x;
+  void* out;
+  const int32_t* mult;
+  const int8_t* shift;
+  long long n;
+  int C, per_channel, in_dtype, out_dtype, input_unsigned;
+  int in_zp, out_zp, double_round;
+  long long clamp_min, clamp_max;
+};
+void launch_rescale_generic(const RescaleGenericArgs& a, cudaStream_t stream);
+struct StridedCopyArgs {
+  const void* in;
+  void* out;
+  long long n;            // elements visited = product of dims
+  int elem_bytes;         // 1, 2 or 4
+  int dims[4];            // extents of the index space (of the output region written)
+  int lo[4], in_dims[4];  // input coordinate = index - lo, valid inside [0, in_dims)
+  long long in_str[4], out_str[4], in_offset, out_offset;  // in elements
+  int pad_value;
+};
+void launch_strided_copy(const StridedCopyArgs& a, cudaStream_t stream);
+struct ReduceArgs {
+  const void* x;
+  void* out;
+  int outer, axis, inner;  // x viewed as [outer, axis, inner]
+  int fn;                  // 0 sum, 1 max, 2 min, 3 argmax
+  int in_dtype, out_dtype;
+};
+void launch_reduce(const ReduceArgs& a, cudaStream_t stream);
+
 void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream);
 
 }  // namespace tb200

@@ -627,7 +627,15 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
   for (int i = 0; i < (int)ops.size(); i++) {
     const auto& op = ops[i];
     Step step;
-    auto loc = [&](int id) { return id >= 0 ? plan.tensor_loc[id] : Loc{}; };
+    // a constant tensor used as a runtime operand (the generic tensor ops) is uploaded as it is
+    auto loc = [&](int id) {
+      if (id < 0) return Loc{};
+      if (tensors[id].kind == TB200_TENSOR_CONSTANT && plan.tensor_loc[id].kind == Loc::NONE) {
+        size_t off = 0;
+        if (b.add_raw_const(id, 0, "operand", i, off)) plan.tensor_loc[id] = Loc{Loc::CONST, off};
+      }
+      return plan.tensor_loc[id];
+    };
     for (int id : {op.in0, op.in1, op.in2})
       if (id >= 0 && tensors[id].kind != TB200_TENSOR_CONSTANT && plan.tensor_loc[id].kind == Loc::NONE)
         return b.fail(TB200_INVALID_ARGUMENT, "op %d reads tensor %d before anything wrote it", i, id);
@@ -1093,9 +1101,39 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         break;
       }
       case TB200_OP_RESCALE: {
-        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || tensors[op.in0].dtype != TB200_I8 ||
-            tensors[op.out0].dtype != TB200_I8 || b.numel(op.in0) != b.numel(op.out0))
-          return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale wants int8 input/output of equal size", i);
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || b.numel(op.in0) != b.numel(op.out0))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale wants input/output of equal size", i);
+        if (tensors[op.in0].dtype != TB200_I8 || tensors[op.out0].dtype != TB200_I8 || op.flags != 0) {
+          // generic form: any of i8 / i16 / i32 in and out, unsigned storage by flag
+          auto int_t = [](uint32_t d) { return d == TB200_I8 || d == TB200_I16 || d == TB200_I32; };
+          if (!int_t(tensors[op.in0].dtype) || !int_t(tensors[op.out0].dtype))
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale wants integer tensors", i);
+          const auto& x = tensors[op.in0];
+          const int C = x.shape[x.rank - 1];
+          const int nscale = op.per_channel ? C : 1;
+          const int32_t* mult = b.const_data<int32_t>(op.multiplier, nscale, "multiplier", i);
+          const int8_t* shift = b.const_data<int8_t>(op.shift, nscale, "shift", i);
+          if (!mult || !shift) return b.status;
+          for (int c = 0; c < nscale; c++)
+            if (shift[c] < 2 || shift[c] > 62) return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale shift %d outside [2,62]", i, (int)shift[c]);
+          RescaleGenericArgs a{};
+          a.n = (long long)b.numel(op.in0); a.C = C; a.per_channel = op.per_channel;
+          a.in_dtype = x.dtype; a.out_dtype = tensors[op.out0].dtype;
+          a.input_unsigned = (op.flags & TB200_FLAG_INPUT_UNSIGNED) ? 1 : 0;
+          a.in_zp = op.in0_zp; a.out_zp = op.out_zp; a.double_round = op.double_round;
+          a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
+          if (op.flags & TB200_FLAG_OUTPUT_UNSIGNED) a.clamp_max = (long long)(uint32_t)op.clamp_max;
+          const size_t m_off = b.add_const(mult, (size_t)nscale * 4), s_off = b.add_const(shift, (size_t)nscale);
+          Loc lx = loc(op.in0), lo = loc(op.out0);
+          step.kernel_name = "rescale_generic";
+          step.launch = [=](const ExecContext& c) {
+            RescaleGenericArgs k = a;
+            k.x = lx.resolve(c); k.out = lo.resolve(c);
+            k.mult = (const int32_t*)(c.consts + m_off); k.shift = (const int8_t*)(c.consts + s_off);
+            launch_rescale_generic(k, c.stream);
+          };
+          break;
+        }
         const auto& x = tensors[op.in0];
         int C = x.shape[x.rank - 1];
         std::vector<ChanParams> cp;
@@ -1414,6 +1452,152 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         needs_fusion = true;
         step.kernel_name = "allreduce";
         step.launch = [](const ExecContext&) {};
+        break;
+      }
+      case TB200_OP_EW: {
+        const bool binary = op.in1 >= 0;
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || (binary && !b.valid_id(op.in1)))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad tensor id", i);
+        const auto& ta = tensors[op.in0]; const auto& to = tensors[op.out0];
+        const tb200_tensor_t* tb = binary ? &tensors[op.in1] : nullptr;
+        if (ta.dtype == TB200_I64 || to.dtype == TB200_I64 || (tb && tb->dtype == TB200_I64) || ta.rank != to.rank ||
+            (tb && tb->rank != to.rank))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: elementwise op wants i8/i16/i32/f32/bf16 tensors of equal rank", i);
+        EwArgs a{};
+        a.n = (long long)b.numel(op.out0); a.fn = op.i0; a.arg = op.i1;
+        a.a_dtype = ta.dtype; a.b_dtype = tb ? tb->dtype : ta.dtype; a.out_dtype = to.dtype;
+        a.in_zp = op.in0_zp; a.out_zp = op.out_zp; a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
+        a.fmin = op.f0; a.fmax = op.f1; a.bool_result = (op.flags & TB200_FLAG_BOOL_RESULT) ? 1 : 0;
+        a.contiguous = 1;
+        const int r = (int)to.rank;
+        for (int d = 0; d < 4; d++) { a.dims[d] = 1; a.a_str[d] = a.b_str[d] = 0; }
+        long long sa = 1, sb = 1;
+        for (int d = r - 1; d >= 0; d--) {
+          const int od = to.shape[d], ad = ta.shape[d], bd = tb ? tb->shape[d] : od;
+          if ((ad != od && ad != 1) || (bd != od && bd != 1))
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: operand shapes do not broadcast to the result", i);
+          a.dims[4 - r + d] = od;
+          a.a_str[4 - r + d] = ad == 1 && od != 1 ? 0 : (int)sa;
+          a.b_str[4 - r + d] = bd == 1 && od != 1 ? 0 : (int)sb;
+          if ((ad == 1 && od != 1) || (bd == 1 && od != 1)) a.contiguous = 0;
+          sa *= ad; sb *= bd;
+        }
+        Loc la = loc(op.in0), lb = binary ? loc(op.in1) : Loc{}, lo = loc(op.out0);
+        step.kernel_name = "ew";
+        step.launch = [=](const ExecContext& c) {
+          EwArgs k = a;
+          k.a = la.resolve(c); k.b = binary ? lb.resolve(c) : nullptr; k.out = lo.resolve(c);
+          launch_ew(k, c.stream);
+        };
+        break;
+      }
+      case TB200_OP_TRANSPOSE:
+      case TB200_OP_SLICE:
+      case TB200_OP_PAD:
+      case TB200_OP_CONCAT_AXIS: {
+        const bool concat = op.kind == TB200_OP_CONCAT_AXIS;
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || (concat && !b.valid_id(op.in1)))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad tensor id", i);
+        const auto& ti = tensors[op.in0]; const auto& to = tensors[op.out0];
+        const int esz = (int)bytes_of(op.in0) / (int)std::max<size_t>(1, b.numel(op.in0));
+        if (ti.dtype != to.dtype || ti.rank != to.rank || (esz != 1 && esz != 2 && esz != 4))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: wants tensors of one element type (1, 2 or 4 bytes) and equal rank", i);
+        const int r = (int)ti.rank;
+        const int arg[4] = {op.i0, op.i1, op.i2, op.i3};
+        // strides (elements) of a dense tensor, dimensions right-aligned in 4 slots
+        auto dense = [&](const tb200_tensor_t& t, long long (&str)[4], int (&dims)[4]) {
+          for (int d = 0; d < 4; d++) { str[d] = 0; dims[d] = 1; }
+          long long s2 = 1;
+          for (int d = (int)t.rank - 1; d >= 0; d--) { str[4 - t.rank + d] = s2; dims[4 - t.rank + d] = t.shape[d]; s2 *= t.shape[d]; }
+        };
+        std::vector<StridedCopyArgs> parts;
+        StridedCopyArgs a{};
+        a.elem_bytes = esz; a.pad_value = op.pad_value;
+        long long istr[4], ostr[4];
+        int idims[4], odims[4];
+        dense(ti, istr, idims);
+        dense(to, ostr, odims);
+        for (int d = 0; d < 4; d++) { a.lo[d] = 0; a.in_dims[d] = 1 << 30; a.out_str[d] = ostr[d]; a.dims[d] = odims[d]; a.in_str[d] = 0; }
+        const int o = 4 - r;  // first used slot
+        if (op.kind == TB200_OP_TRANSPOSE) {
+          bool seen[4] = {false, false, false, false};
+          for (int d = 0; d < r; d++) {
+            if (arg[d] < 0 || arg[d] >= r || seen[arg[d]] || to.shape[d] != ti.shape[arg[d]])
+              return b.fail(TB200_INVALID_ARGUMENT, "op %d: transpose permutation does not match the shapes", i);
+            seen[arg[d]] = true;
+            a.in_str[o + d] = istr[o + arg[d]];
+          }
+          parts.push_back(a);
+        } else if (op.kind == TB200_OP_SLICE) {
+          for (int d = 0; d < r; d++) {
+            if (arg[d] < 0 || arg[d] + to.shape[d] > ti.shape[d])
+              return b.fail(TB200_INVALID_ARGUMENT, "op %d: slice outside the tensor", i);
+            a.in_str[o + d] = istr[o + d];
+            a.in_offset += (long long)arg[d] * istr[o + d];
+          }
+          parts.push_back(a);
+        } else if (op.kind == TB200_OP_PAD) {
+          for (int d = 0; d < r; d++) {
+            if (arg[d] < 0 || arg[d] + ti.shape[d] > to.shape[d])
+              return b.fail(TB200_INVALID_ARGUMENT, "op %d: pad amounts do not match the shapes", i);
+            a.in_str[o + d] = istr[o + d];
+            a.lo[o + d] = arg[d];
+            a.in_dims[o + d] = ti.shape[d];
+          }
+          parts.push_back(a);
+        } else {
+          const auto& t1 = tensors[op.in1];
+          const int axis = op.i0;
+          if (axis < 0 || axis >= r || t1.dtype != ti.dtype || t1.rank != ti.rank || ti.shape[axis] + t1.shape[axis] != to.shape[axis])
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: concat shapes do not match", i);
+          for (int which = 0; which < 2; which++) {
+            const auto& t = which ? t1 : ti;
+            StridedCopyArgs c2 = a;
+            long long s1[4];
+            int d1[4];
+            dense(t, s1, d1);
+            for (int d = 0; d < 4; d++) { c2.in_str[d] = s1[d]; c2.dims[d] = d1[d]; }
+            c2.out_offset = which ? (long long)ti.shape[axis] * ostr[o + axis] : 0;
+            parts.push_back(c2);
+          }
+        }
+        for (auto& pt : parts) { pt.n = 1; for (int d = 0; d < 4; d++) pt.n *= pt.dims[d]; }
+        Loc l0 = loc(op.in0), l1 = concat ? loc(op.in1) : Loc{}, lo = loc(op.out0);
+        step.kernel_name = op.kind == TB200_OP_TRANSPOSE ? "transpose" : op.kind == TB200_OP_SLICE ? "slice"
+                           : op.kind == TB200_OP_PAD ? "pad" : "concat_axis";
+        step.launches = (int)parts.size();
+        step.launch = [=](const ExecContext& c) {
+          for (size_t q = 0; q < parts.size(); q++) {
+            StridedCopyArgs k = parts[q];
+            k.in = (q == 1 ? l1 : l0).resolve(c);
+            k.out = lo.resolve(c);
+            launch_strided_copy(k, c.stream);
+          }
+        };
+        break;
+      }
+      case TB200_OP_REDUCE: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad tensor id", i);
+        const auto& ti = tensors[op.in0];
+        const int axis = op.i1;
+        if (axis < 0 || axis >= (int)ti.rank || op.i0 < 0 || op.i0 > 3 || ti.dtype == TB200_I64)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad reduction axis, function or element type", i);
+        if (op.i0 == 0 && (ti.dtype == TB200_F32 || ti.dtype == TB200_BF16))
+          return b.fail(TB200_UNIMPLEMENTED, "op %d: floating-point reduce_sum is not an exact op and is not offered", i);
+        ReduceArgs a{};
+        a.outer = a.inner = 1;
+        for (int d = 0; d < axis; d++) a.outer *= ti.shape[d];
+        for (int d = axis + 1; d < (int)ti.rank; d++) a.inner *= ti.shape[d];
+        a.axis = ti.shape[axis]; a.fn = op.i0; a.in_dtype = ti.dtype; a.out_dtype = tensors[op.out0].dtype;
+        if (b.numel(op.out0) != (size_t)a.outer * a.inner)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: reduction result has the wrong element count", i);
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "reduce";
+        step.launch = [=](const ExecContext& c) {
+          ReduceArgs k = a;
+          k.x = lx.resolve(c); k.out = lo.resolve(c);
+          launch_reduce(k, c.stream);
+        };
         break;
       }
       case TB200_OP_RESHAPE: {

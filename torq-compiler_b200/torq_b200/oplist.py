@@ -29,7 +29,15 @@ OP_KINDS = {
     "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
     "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
     "add_bf16": 38, "argmax": 39, "allreduce": 40, "act_bf16": 41, "gemv_q8b": 42,
+    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53,
 }
+
+EW_FN = {"cast": 0, "abs": 1, "negate": 2, "bitwise_not": 3, "logical_not": 4, "clz": 5, "clamp": 6, "ceil": 7, "floor": 8,
+         "add": 16, "sub": 17, "mul": 18, "maximum": 19, "minimum": 20, "bitwise_and": 21, "bitwise_or": 22,
+         "bitwise_xor": 23, "logical_left_shift": 24, "arithmetic_right_shift": 25, "equal": 26, "greater": 27,
+         "greater_equal": 28, "logical_and": 29, "logical_or": 30, "logical_xor": 31}
+FLAG_INPUT_UNSIGNED, FLAG_OUTPUT_UNSIGNED, FLAG_BOOL_RESULT = 1, 2, 4
+REDUCE_FN = {"sum": 0, "max": 1, "min": 2, "argmax": 3}
 
 
 class Header(C.Structure):
@@ -252,12 +260,63 @@ class Graph:
             raise ValueError("table must have 256 entries")
         return self._emit("table", [x], x.shape, consts={"table": self.const(t)})
 
-    def rescale(self, x, multiplier, shift, *, input_zp=0, out_zp=0, clamp=(-128, 127), double_round=True,
-                requant_mode=0):
+    def rescale(self, x, multiplier, shift, *, input_zp=0, out_zp=0, clamp=None, double_round=True,
+                requant_mode=0, out_dtype="i8", input_unsigned=False, output_unsigned=False):
+        """tosa.rescale. i8 -> i8 is the layer-path op; other integer types (i8 / i16 / i32 in and out, unsigned
+        8/16-bit storage by flag) take the generic kernel. The clamp defaults to the result type's range."""
         mt, st, pc = self._requant_consts(multiplier, shift, x.shape[-1])
-        return self._emit("rescale", [x], x.shape, consts={"multiplier": mt, "shift": st}, in0_zp=input_zp,
-                          out_zp=out_zp, clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc,
-                          double_round=int(double_round), requant_mode=requant_mode)
+        if clamp is None:
+            bits = {"i8": 8, "i16": 16, "i32": 32}[out_dtype]
+            clamp = (0, (1 << bits) - 1) if output_unsigned else (-(1 << (bits - 1)), (1 << (bits - 1)) - 1)
+        flags = (FLAG_INPUT_UNSIGNED if input_unsigned else 0) | (FLAG_OUTPUT_UNSIGNED if output_unsigned else 0)
+        return self._emit("rescale", [x], x.shape, out_dtype, consts={"multiplier": mt, "shift": st}, in0_zp=input_zp,
+                          out_zp=out_zp, clamp_min=clamp[0], clamp_max=min(clamp[1], (1 << 31) - 1), per_channel=pc,
+                          double_round=int(double_round), requant_mode=requant_mode, flags=flags)
+
+    # ---- tensor ops outside the layer set ---------------------------------------
+    def ew(self, fn: str, a, b=None, *, out_dtype=None, arg: int = 0, in_zp: int = 0, out_zp: int = 0, clamp=(0, 0),
+           fclamp=(0.0, 0.0), bool_result: bool = False):
+        """Elementwise op `fn` (a key of EW_FN) on one or two tensors of equal rank; extent-1 dimensions broadcast."""
+        if b is not None:
+            if len(a.shape) != len(b.shape) or any(x != y and 1 not in (x, y) for x, y in zip(a.shape, b.shape)):
+                raise ValueError("elementwise operands must have equal rank and broadcastable shapes")
+            shape = tuple(max(x, y) for x, y in zip(a.shape, b.shape))
+        else:
+            shape = a.shape
+        return self._emit("ew", [a] if b is None else [a, b], shape, out_dtype or a.dtype, i0=EW_FN[fn], i1=int(arg),
+                          in0_zp=int(in_zp), out_zp=int(out_zp), clamp_min=int(clamp[0]), clamp_max=int(clamp[1]),
+                          f0=float(fclamp[0]), f1=float(fclamp[1]), flags=FLAG_BOOL_RESULT if bool_result else 0)
+
+    def transpose(self, x, perm):
+        perm = [int(p) for p in perm]
+        if sorted(perm) != list(range(len(x.shape))):
+            raise ValueError("perm must be a permutation of the dimensions")
+        p4 = perm + list(range(len(perm), 4))
+        return self._emit("transpose", [x], tuple(x.shape[p] for p in perm), x.dtype, i0=p4[0], i1=p4[1], i2=p4[2], i3=p4[3])
+
+    def slice(self, x, start, size):
+        if any(s < 0 or s + n > d for s, n, d in zip(start, size, x.shape)):
+            raise ValueError("slice outside the tensor")
+        s4 = [int(v) for v in start] + [0] * (4 - len(start))
+        return self._emit("slice", [x], tuple(int(n) for n in size), x.dtype, i0=s4[0], i1=s4[1], i2=s4[2], i3=s4[3])
+
+    def pad(self, x, before, after, value: int = 0):
+        b4 = [int(v) for v in before] + [0] * (4 - len(before))
+        shape = tuple(d + int(lo) + int(hi) for d, lo, hi in zip(x.shape, before, after))
+        return self._emit("pad", [x], shape, x.dtype, i0=b4[0], i1=b4[1], i2=b4[2], i3=b4[3], pad_value=int(value))
+
+    def concat_axis(self, a, b, axis: int):
+        if a.dtype != b.dtype or len(a.shape) != len(b.shape) or any(
+                x != y for i, (x, y) in enumerate(zip(a.shape, b.shape)) if i != axis):
+            raise ValueError("concat operands differ outside the axis")
+        shape = tuple(d + (b.shape[i] if i == axis else 0) for i, d in enumerate(a.shape))
+        return self._emit("concat_axis", [a, b], shape, a.dtype, i0=int(axis))
+
+    def reduce(self, fn: str, x, axis: int, *, keep_axis: bool = True, out_dtype=None):
+        shape = tuple(1 if i == axis else d for i, d in enumerate(x.shape)) if keep_axis else \
+            tuple(d for i, d in enumerate(x.shape) if i != axis) or (1,)
+        return self._emit("reduce", [x], shape, out_dtype or ("i32" if fn == "argmax" else x.dtype), i0=REDUCE_FN[fn],
+                          i1=int(axis))
 
     def resize_nearest_2x(self, x):
         N, H, W, Cc = x.shape
@@ -382,6 +441,7 @@ class Graph:
             outs = [g.tensors[t] for t in (r.out0, r.out1) if t >= 0]
             consts = {n: g.tensors[getattr(r, n)] for n in const_fields if getattr(r, n) >= 0}
             attrs = {n: getattr(r, n) for n in _OP_INT_FIELDS[10:]}
+            attrs["flags"] = r.flags
             attrs.update({f: getattr(r, f) for f in ("f0", "f1", "f2", "f3")})
             g.ops.append(Op(kinds[r.kind], ins, outs, consts, attrs))
         ids_in = np.frombuffer(blob[h.inputs_offset:h.inputs_offset + 4 * h.n_inputs], np.int32)

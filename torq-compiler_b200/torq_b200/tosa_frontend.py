@@ -22,7 +22,20 @@ import numpy as np
 
 from .oplist import Graph, TensorRef
 
-_NP = {"i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64, "index": np.int64, "f32": np.float32}
+_NP = {"i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64, "index": np.int64, "f32": np.float32,
+       "i1": np.int8, "ui8": np.uint8, "ui16": np.uint16, "bf16": np.uint16, "i48": np.int64}
+# element type of the op-list tensor that holds a TOSA value: booleans are 0 / 1 bytes, unsigned types keep their
+# bits in the signed type of the same width (tosa.rescale's input_unsigned / output_unsigned say how to read them)
+_GRAPH_DTYPE = {"i1": "i8", "ui8": "i8", "ui16": "i16"}
+
+
+def graph_dtype(dtype: str) -> str:
+    return _GRAPH_DTYPE.get(dtype, dtype)
+
+
+def _to_bf16_bits(values) -> np.ndarray:
+    u = np.asarray(values, np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
 
 
 @dataclass
@@ -64,18 +77,24 @@ def _parse_dense(body: str, shape, dtype):
     if body.startswith('"0x'):
         raw = bytes.fromhex(body[3:-1])
         return np.frombuffer(raw, dtype=np_t)[:n].reshape(shape).copy()
+    is_float = dtype in ("f32", "bf16")
     if body.startswith("["):
-        vals = [int(v) if dtype != "f32" else float(v) for v in re.findall(r"-?\d+(?:\.\d+)?(?:[eE][-+]?\d+)?", body)]
-        return np.array(vals, dtype=np_t).reshape(shape)
+        toks = re.findall(r"true|false|-?\d+(?:\.\d*)?(?:[eE][-+]?\d+)?", body)
+        vals = [{"true": 1, "false": 0}[t] if t in ("true", "false") else (float(t) if is_float else int(t)) for t in toks]
+        if dtype == "bf16":
+            return _to_bf16_bits(vals).reshape(shape)
+        return np.array(vals).astype(np_t).reshape(shape)
     v = {"true": 1, "false": 0}.get(body, None)
     if v is None:
-        v = float(body) if dtype == "f32" else int(body)
-    return np.full(shape, v, dtype=np_t)
+        v = float(body) if is_float else int(body)
+    if dtype == "bf16":
+        return np.full(shape, _to_bf16_bits([v])[0], dtype=np.uint16)
+    return np.full(shape, np.array(v).astype(np_t), dtype=np_t)
 
 
 def _parse_attrs(text: str) -> dict:
     out = {}
-    for k, v in re.findall(r"(\w+)\s*=\s*(array<i64:[^>]*>|\"[^\"]*\"|[-\w\.]+(?:\s*:\s*\w+)?)", text):
+    for k, v in re.findall(r"(\w+)\s*=\s*(array<i\d+:[^>]*>|\"[^\"]*\"|[-+\w\.]+(?:\s*:\s*\w+)?)", text):
         if v.startswith("array<"):
             out[k] = [int(x) for x in re.findall(r"-?\d+", v.split(":", 1)[1])]
         elif v.startswith('"'):
@@ -87,7 +106,10 @@ def _parse_attrs(text: str) -> dict:
                 try:
                     out[k] = int(tok)
                 except ValueError:
-                    out[k] = tok
+                    try:
+                        out[k] = float(tok)
+                    except ValueError:
+                        out[k] = tok
     return out
 
 
@@ -134,6 +156,19 @@ def parse_module(text: str):
                     v.op.users.append(op)
             ops.append(op)
             continue
+        e = re.match(r"(%\w+)\s*=\s*tensor\.extract_slice\s+(%\w+)\[([^\]]*)\]\s*\[([^\]]*)\]\s*\[([^\]]*)\]\s*:\s*(tensor<[^>]*>)\s+to\s+(tensor<[^>]*>)", line)
+        if e:
+            ints = lambda t: [int(x) for x in re.findall(r"-?\d+", t)]
+            if any(st != 1 for st in ints(e.group(5))):
+                raise NotImplementedError("tensor.extract_slice with a stride")
+            shape, dt = _parse_type(e.group(7))
+            op = _Op("extract_slice", [vals[e.group(2)]], {"start": ints(e.group(3)), "size": ints(e.group(4))})
+            op.result = _Val(e.group(1), shape, dt, op=op)
+            vals[e.group(1)] = op.result
+            if vals[e.group(2)].op is not None:
+                vals[e.group(2)].op.users.append(op)
+            ops.append(op)
+            continue
         if line.startswith("module") or line.startswith("func.func") or line.startswith("{-#") or line.startswith("#"):
             continue
         raise NotImplementedError(f"cannot read line: {line[:120]}")
@@ -146,13 +181,122 @@ def _scalar(v: _Val) -> int:
     return int(v.const.reshape(-1)[0])
 
 
+def _collapse(shape) -> tuple:
+    """Tensors of the op list have at most four dimensions: the leading dimensions of a longer shape are merged
+    (valid for the elementwise ops, the only ones the front end lets through with such shapes)."""
+    shape = tuple(int(d) for d in shape)
+    if len(shape) <= 4:
+        return shape
+    return (int(np.prod(shape[:-3])),) + shape[-3:]
+
+
 def build_graph(text: str) -> Graph:
     inputs, ops, returned = parse_module(text)
     g = Graph()
     env: dict[str, TensorRef] = {}
     for v in inputs:
-        env[v.name] = g.input(v.shape, v.dtype)
+        env[v.name] = g.input(_collapse(v.shape), graph_dtype(v.dtype))
     done: set[int] = set()
+    deferred: dict[str, _Op] = {}  # i8->i32 rescales waiting for the add/sub/mul that absorbs them
+
+    def get(v: _Val) -> TensorRef:
+        """The op-list tensor of a TOSA value: an input or op result, a constant, or a rescale that was left
+        for a fused consumer that did not come."""
+        if v.name in env:
+            return env[v.name]
+        if v.const is not None:
+            env[v.name] = g.const(np.ascontiguousarray(v.const).reshape(_collapse(v.shape) or (1,)).astype(_NP[v.dtype]).view(
+                {"ui8": np.int8, "ui16": np.int16}.get(v.dtype, _NP[v.dtype])), graph_dtype(v.dtype))
+            return env[v.name]
+        if v.name in deferred:
+            generic(deferred.pop(v.name))
+            return env[v.name]
+        raise NotImplementedError(f"value {v.name} has no producer the front end reads")
+
+    def generic(op: _Op):
+        """One op-list record per TOSA op, no fusion: the tensor ops outside the layer set."""
+        n, res = op.name, op.result
+        oshape, odt = _collapse(res.shape), graph_dtype(res.dtype)
+        if n == "rescale":
+            p = rescale_params(op)
+            x = get(op.operands[0])
+            mult, shift = (p["mult"], p["shift"]) if p["per_channel"] else (p["mult"][:1], p["shift"][:1])
+            if not op.attrs.get("scale32", True):
+                raise NotImplementedError("rescale with scale32 = false")
+            izp, ozp = p["izp"], p["ozp"]
+            if op.attrs.get("input_unsigned", False):
+                izp &= (1 << (8 * np.dtype(_NP[op.operands[0].dtype]).itemsize)) - 1
+            if op.attrs.get("output_unsigned", False):
+                ozp &= (1 << (8 * np.dtype(_NP[res.dtype]).itemsize)) - 1
+            env[res.name] = g.rescale(x, mult, shift, input_zp=izp, out_zp=ozp, double_round=p["double_round"], out_dtype=odt,
+                                      input_unsigned=bool(op.attrs.get("input_unsigned", False)),
+                                      output_unsigned=bool(op.attrs.get("output_unsigned", False)))
+        elif n in ("abs", "bitwise_not", "logical_not", "clz", "ceil", "floor", "cast"):
+            env[res.name] = g.ew(n, get(op.operands[0]), out_dtype=odt, bool_result=res.dtype == "i1" and n == "cast")
+        elif n == "negate":
+            izp = _scalar(op.operands[1]) if len(op.operands) > 1 else 0
+            ozp = _scalar(op.operands[2]) if len(op.operands) > 2 else 0
+            env[res.name] = g.ew("negate", get(op.operands[0]), out_dtype=odt, in_zp=izp, out_zp=ozp)
+        elif n == "clamp":
+            lo, hi = op.attrs["min_val"], op.attrs["max_val"]
+            if res.dtype in ("f32", "bf16"):
+                env[res.name] = g.ew("clamp", get(op.operands[0]), out_dtype=odt, fclamp=(float(lo), float(hi)))
+            else:
+                env[res.name] = g.ew("clamp", get(op.operands[0]), out_dtype=odt, clamp=(int(lo), int(hi)))
+        elif n in ("add", "sub", "mul", "maximum", "minimum", "bitwise_and", "bitwise_or", "bitwise_xor", "logical_left_shift",
+                   "arithmetic_right_shift", "equal", "greater", "greater_equal", "logical_and", "logical_or", "logical_xor"):
+            a, b = get(op.operands[0]), get(op.operands[1])
+            arg = 0
+            if n == "mul" and len(op.operands) > 2:
+                arg = _scalar(op.operands[2])
+            if n == "arithmetic_right_shift":
+                arg = 1 if op.attrs.get("round", False) else 0
+            r = max(len(a.shape), len(b.shape))
+            a = g.reshape(a, (1,) * (r - len(a.shape)) + a.shape) if len(a.shape) < r else a
+            b = g.reshape(b, (1,) * (r - len(b.shape)) + b.shape) if len(b.shape) < r else b
+            env[res.name] = g.ew(n, a, b, out_dtype=odt, arg=arg)
+        elif n == "transpose":
+            x = op.operands[0]
+            perm = [int(v) for v in op.attrs["perms"]]
+            if len(x.shape) > 4:
+                raise NotImplementedError(f"rank {len(x.shape)} transpose")
+            env[res.name] = g.transpose(get(x), perm)
+        elif n in ("slice", "extract_slice"):
+            x = op.operands[0]
+            if len(x.shape) > 4:
+                raise NotImplementedError(f"rank {len(x.shape)} slice")
+            start = op.attrs["start"] if n == "extract_slice" else [int(v) for v in op.operands[1].const.reshape(-1)]
+            size = op.attrs["size"] if n == "extract_slice" else [int(v) for v in op.operands[2].const.reshape(-1)]
+            env[res.name] = g.slice(get(x), start, size)
+        elif n == "pad":
+            x = op.operands[0]
+            if len(x.shape) > 4:
+                raise NotImplementedError(f"rank {len(x.shape)} pad")
+            amounts = [int(v) for v in op.operands[1].const.reshape(-1)]
+            value = int(np.asarray(op.operands[2].const).reshape(-1).view(_NP[op.operands[2].dtype])[0]) if len(op.operands) > 2 else 0
+            env[res.name] = g.pad(get(x), amounts[0::2], amounts[1::2], value)
+        elif n == "concat":
+            vals_ = [get(v) for v in op.operands]
+            axis = int(op.attrs.get("axis", 0))
+            if any(len(v.shape) > 4 for v in op.operands):
+                raise NotImplementedError("rank > 4 concat")
+            acc = vals_[0]
+            for nxt in vals_[1:]:
+                acc = g.concat_axis(acc, nxt, axis)
+            env[res.name] = acc
+        elif n in ("reduce_sum", "reduce_max", "reduce_min", "argmax"):
+            x = op.operands[0]
+            if len(x.shape) > 4:
+                raise NotImplementedError(f"rank {len(x.shape)} reduction")
+            fn = {"reduce_sum": "sum", "reduce_max": "max", "reduce_min": "min", "argmax": "argmax"}[n]
+            t = g.reduce(fn, get(x), int(op.attrs["axis"]), keep_axis=n != "argmax", out_dtype=odt)
+            env[res.name] = t if t.shape == oshape else g.reshape(t, oshape)
+        elif n == "identity":
+            env[res.name] = g.reshape(get(op.operands[0]), oshape)
+        elif n == "reshape":
+            env[res.name] = g.reshape(get(op.operands[0]), oshape)
+        else:
+            raise NotImplementedError(f"tosa.{n}")
 
     def rescale_params(op):
         x, mult, shift, izp, ozp = op.operands
@@ -172,21 +316,22 @@ def build_graph(text: str) -> Graph:
             return c, max(lo, int(c.attrs["min_val"])), min(hi, int(c.attrs["max_val"]))
         return op, lo, hi
 
-    for op in ops:
-        if id(op) in done:
-            continue
+    def fused(op: _Op):
+        """The layer-path forms (one record per fused chain); raises NotImplementedError when the op is not one."""
         n = op.name
         if n in ("conv2d", "depthwise_conv2d"):
             x, w, bias, izp, wzp = op.operands
             rs = only_user(op, "rescale")
             if rs is None or w.const is None:
                 raise NotImplementedError(f"{n} without a constant weight and a following rescale")
+            if x.dtype != "i8" or w.dtype != "i8" or rs.result.dtype != "i8":
+                raise NotImplementedError(f"{n} on {x.dtype} activations")
             done.add(id(rs))
             p = rescale_params(rs)
             last, lo, hi = fold_clamp(rs)
             fn = g.conv2d if n == "conv2d" else g.depthwise_conv2d
             mult, shift = (p["mult"], p["shift"]) if p["per_channel"] else (p["mult"][:1], p["shift"][:1])
-            y = fn(env[x.name], w.const, bias.const.reshape(-1), mult, shift, stride=tuple(op.attrs["stride"]),
+            y = fn(get(x), w.const, bias.const.reshape(-1), mult, shift, stride=tuple(op.attrs["stride"]),
                    dilation=tuple(op.attrs["dilation"]), pad=tuple(op.attrs["pad"]), input_zp=_scalar(izp),
                    weight_zp=_scalar(wzp), out_zp=p["ozp"], clamp=(lo, hi), double_round=p["double_round"])
             env[last.result.name] = y
@@ -199,17 +344,19 @@ def build_graph(text: str) -> Graph:
                     users = list({id(u): u for u in users[0].users}.values())  # first of two input stages
                 if len(users) != 1 or users[0].name not in ("add", "sub", "mul"):
                     raise NotImplementedError("i8->i32 rescale that does not feed add/sub/mul")
-                continue  # consumed when the binary op is reached
+                deferred[op.result.name] = op
+                return  # consumed when the binary op is reached
             if src.dtype == "i32" and op.result.dtype == "i32" and src.op is not None and src.op.name == "rescale" and \
                     src.op.operands[0].dtype == "i8":
                 users = list({id(u): u for u in op.users}.values())
                 if len(users) != 1 or users[0].name not in ("add", "sub", "mul"):
                     raise NotImplementedError("i32->i32 rescale that does not feed add/sub/mul")
-                continue  # second input stage, consumed when the binary op is reached
+                deferred[op.result.name] = op
+                return  # second input stage, consumed when the binary op is reached
             if src.dtype == "i8" and op.result.dtype == "i8":
                 last, lo, hi = fold_clamp(op)
                 mult, shift = (p["mult"], p["shift"]) if p["per_channel"] else (p["mult"][:1], p["shift"][:1])
-                env[last.result.name] = g.rescale(env[src.name], mult, shift, input_zp=p["izp"], out_zp=p["ozp"],
+                env[last.result.name] = g.rescale(get(src), mult, shift, input_zp=p["izp"], out_zp=p["ozp"],
                                                   clamp=(lo, hi), double_round=p["double_round"])
             else:
                 raise NotImplementedError(f"rescale {src.dtype}->{op.result.dtype} outside a fused chain")
@@ -247,16 +394,16 @@ def build_graph(text: str) -> Graph:
             xb, zb, lb, mb, sb = input_side(b)
             last, lo, hi = fold_clamp(rs)
             fn = getattr(g, n)
-            env[last.result.name] = fn(env[xa.name], env[xb.name], a_zp=za, a_ms=(ma, sa), b_zp=zb, b_ms=(mb, sb),
+            env[last.result.name] = fn(get(xa), get(xb), a_zp=za, a_ms=(ma, sa), b_zp=zb, b_ms=(mb, sb),
                                        out_ms=(int(po["mult"][0]), int(po["shift"][0])), out_zp=po["ozp"], clamp=(lo, hi),
                                        double_round=po["double_round"], a_lshift=la, b_lshift=lb)
         elif n == "table":
-            env[op.result.name] = g.table(env[op.operands[0].name], op.operands[1].const.reshape(-1))
+            env[op.result.name] = g.table(get(op.operands[0]), op.operands[1].const.reshape(-1))
         elif n == "pad":
             mp = only_user(op, "max_pool2d")
             if mp is None:
                 raise NotImplementedError("tosa.pad that does not feed max_pool2d")
-            continue
+            return
         elif n == "max_pool2d":
             src = op.operands[0]
             pad = list(op.attrs["pad"])
@@ -266,30 +413,30 @@ def build_graph(text: str) -> Graph:
                 pad = [pad[0] + int(amounts[2]), pad[1] + int(amounts[3]), pad[2] + int(amounts[4]), pad[3] + int(amounts[5])]
                 pad_value = _scalar(src.op.operands[2])
                 src = src.op.operands[0]
-            env[op.result.name] = g.maxpool2d(env[src.name], tuple(op.attrs["kernel"]), tuple(op.attrs["stride"]),
+            env[op.result.name] = g.maxpool2d(get(src), tuple(op.attrs["kernel"]), tuple(op.attrs["stride"]),
                                               tuple(pad), pad_value)
         elif n == "avg_pool2d":
             x, izp, ozp = op.operands
-            env[op.result.name] = g.avg_pool2d(env[x.name], tuple(op.attrs["kernel"]), tuple(op.attrs["stride"]),
+            env[op.result.name] = g.avg_pool2d(get(x), tuple(op.attrs["kernel"]), tuple(op.attrs["stride"]),
                                                tuple(op.attrs["pad"]), _scalar(izp), _scalar(ozp))
         elif n == "reshape":
-            env[op.result.name] = g.reshape(env[op.operands[0].name], op.result.shape)
+            env[op.result.name] = g.reshape(get(op.operands[0]), op.result.shape)
         elif n == "resize":
             x = op.operands[0]
             if op.attrs.get("mode") != "NEAREST_NEIGHBOR" or op.result.shape[1] != 2 * x.shape[1] or op.result.shape[2] != 2 * x.shape[2]:
                 raise NotImplementedError("only 2x nearest-neighbour resize")
-            env[op.result.name] = g.resize_nearest_2x(env[x.name])
+            env[op.result.name] = g.resize_nearest_2x(get(x))
         elif n == "concat":
             a, b = op.operands
             if int(op.attrs.get("axis", -1)) != len(a.shape) - 1:
                 raise NotImplementedError("concat along a non-channel axis")
             one = (1 << 30, 30)
-            env[op.result.name] = g.concat(env[a.name], env[b.name], a_zp=0, a_ms=one, b_zp=0, b_ms=one, out_zp=0)
+            env[op.result.name] = g.concat(get(a), get(b), a_zp=0, a_ms=one, b_zp=0, b_ms=one, out_zp=0)
         elif n == "matmul":
             a, b, azp, bzp = op.operands
             if a.dtype != "i8" or b.dtype != "i8" or op.result.dtype != "i32" or len(a.shape) != 3 or a.shape[0] != 1:
                 raise NotImplementedError("tosa.matmul other than one batch of i8 x i8 -> i32")
-            y = g.matmul_i32(g.reshape(env[a.name], a.shape[1:]), g.reshape(env[b.name], b.shape[1:]), a_zp=_scalar(azp),
+            y = g.matmul_i32(g.reshape(get(a), a.shape[1:]), g.reshape(get(b), b.shape[1:]), a_zp=_scalar(azp),
                              b_zp=_scalar(bzp))
             env[op.result.name] = g.reshape(y, op.result.shape)
         elif n == "clamp":
@@ -297,16 +444,28 @@ def build_graph(text: str) -> Graph:
             if x.dtype != "i8":
                 raise NotImplementedError("clamp that does not follow a rescale")
             # on its own: the identity rescale (multiplier 2^30, shift 30 is exact) with the clamp range
-            env[op.result.name] = g.rescale(env[x.name], np.array([1 << 30], np.int32), np.array([30], np.int8), input_zp=0,
+            env[op.result.name] = g.rescale(get(x), np.array([1 << 30], np.int32), np.array([30], np.int8), input_zp=0,
                                             out_zp=0, clamp=(max(-128, int(op.attrs["min_val"])), min(127, int(op.attrs["max_val"]))),
                                             double_round=False)
         elif n == "identity":
             x = op.operands[0]
-            env[op.result.name] = g.reshape(env[x.name], x.shape)
+            env[op.result.name] = g.reshape(get(x), x.shape)
         else:
             raise NotImplementedError(f"tosa.{n}")
+
+    for op in ops:
+        if id(op) in done:
+            continue
+        saved = set(done)
+        try:
+            fused(op)
+        except NotImplementedError:
+            done.clear()
+            done.update(saved)
+            deferred.pop(op.result.name, None)
+            generic(op)
     for v in returned:
-        g.output(env[v.name])
+        g.output(get(v))
     return g
 
 
