@@ -104,9 +104,13 @@ enum tb200_op_kind {
   TB200_OP_PAD = 51,          /* tosa.pad: i0..i3 = leading padding per dimension, pad_value = the constant */
   TB200_OP_CONCAT_AXIS = 52,  /* tosa.concat of in0, in1 along axis i0 (plain copy, any element type) */
   TB200_OP_REDUCE = 53,       /* tosa.reduce_sum / reduce_max / reduce_min / argmax along axis i1: i0 = 0 sum, 1 max, 2 min,
-                               * 3 argmax. The result's shape is whatever the op record's output tensor says (the axis kept
-                               * with extent 1, or dropped): only its element count matters. Integer sums wrap in int32;
+                               * 3 argmax, 4 mean (floats). The result's shape is whatever the op record's output tensor says (the axis kept
+                               * with extent 1, or dropped): only its element count matters. Integer sums wrap in int32; float sums and means (ReduceMeanPattern.cpp:37-466) add in fp32 in index order;
                                * argmax gives the first index of the maximum as i32 */
+  TB200_OP_TABLE16 = 54,      /* tosa.table on int16: 513-entry int16 table, linear interpolation over the low 7 bits, int32 result
+                               * (base << 7) + (next - base) * fraction; the reference's i16 table op is ExtractPattern.cpp:439-545 */
+  TB200_OP_SOFTMAX = 55,      /* softmax over the last axis of a bf16 / f32 tensor: subtract the row maximum, exp, sum, multiply by the
+                               * reciprocal (the order of SoftmaxPattern.cpp:23-333); fp32 inside, one rounding to the result type */
   TB200_OP_ALLREDUCE = 40,    /* sum of the fp32 partial results of the i0 GPUs of a tensor-parallel group
                                * (this one is rank i1), rounded to bf16; only inside the fused decode step */
 };

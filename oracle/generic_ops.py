@@ -181,8 +181,12 @@ def rescale(x: np.ndarray, in_dtype: str, out_dtype: str, mult, shift, in_zp: in
 
 def reduce(fn: int, x: np.ndarray, dtype: str, axis: int, out_shape, out_dtype: str) -> np.ndarray:
     v, flt = _load(x, dtype)
-    if fn == 0:
-        r = v.sum(axis=axis, dtype=np.float32 if flt else np.int64)
+    if fn in (0, 4) and flt:  # fp32 accumulation in index order (cumsum adds one element at a time)
+        r = np.take(np.cumsum(v.astype(np.float32), axis=axis, dtype=np.float32), -1, axis=axis)
+        if fn == 4:
+            r = (r / np.float32(v.shape[axis])).astype(np.float32)
+    elif fn == 0:
+        r = v.sum(axis=axis, dtype=np.int64)
     elif fn == 1:
         r = v.max(axis=axis)
     elif fn == 2:
@@ -190,3 +194,21 @@ def reduce(fn: int, x: np.ndarray, dtype: str, axis: int, out_shape, out_dtype: 
     else:
         return v.argmax(axis=axis).astype(np.int32).reshape(out_shape)
     return _store(r, flt, out_dtype).reshape(out_shape)
+
+
+def table16(x: np.ndarray, table: np.ndarray) -> np.ndarray:
+    """tosa.table, int16 in, 513-entry int16 table, int32 out: linear interpolation over the low 7 bits."""
+    v = x.astype(np.int64)
+    t = table.astype(np.int64).reshape(-1)
+    index = (v + 32768) >> 7
+    frac = v & 0x7F
+    base, nxt = t[index], t[index + 1]
+    return ((base << 7) + (nxt - base) * frac).astype(np.int32)
+
+
+def softmax(x: np.ndarray, dtype: str) -> np.ndarray:
+    """softmax over the last axis, fp32 inside (tolerance class: the device's exp and summation order differ)."""
+    v, _ = _load(x, dtype)
+    v = v.astype(np.float32)
+    e = np.exp(v - v.max(axis=-1, keepdims=True))
+    return _store(e / e.sum(axis=-1, keepdims=True), True, dtype)

@@ -340,3 +340,12 @@ def rescale_elementwise(x, in_dtype, out_dtype, mult, shift, in_zp, out_zp, clam
         r = _wrap_py((v * m + rnd) >> s, 32) + out_zp
         out.append(_wrap_py(min(max(r, clamp[0]), clamp[1]), bits[out_dtype]))
     return np.array(out, dtype={"i8": np.int8, "i16": np.int16, "i32": np.int32}[out_dtype]).reshape(x.shape)
+
+
+def table16_elementwise(x, table):
+    t = [int(v) for v in table.reshape(-1)]
+    out = []
+    for v in (int(q) for q in x.reshape(-1)):
+        i, f = (v + 32768) >> 7, v & 0x7F
+        out.append(t[i] * 128 + (t[i + 1] - t[i]) * f)
+    return np.array(out, np.int32).reshape(x.shape)

@@ -57,6 +57,7 @@ CASES = [
 # the tensor ops outside the layer set (casts, elementwise integer / float ops, rescales between integer types,
 # transposes, slices, pads, reductions): every further fixture the front end reads with at most 150 k elements
 GENERIC_CASES = [
+    "tosa_ops/mbv2-softmax-i8",  # the decomposed int8 softmax: 42 integer ops incl. four interpolated int16 tables
     "tosa_ops/Elementwise_add-i32", "tosa_ops/Elementwise_bitwise_and-i16-scalar",
     "tosa_ops/Elementwise_bitwise_and-i16", "tosa_ops/Elementwise_bitwise_and-i32",
     "tosa_ops/Elementwise_bitwise_and-i8", "tosa_ops/Elementwise_bitwise_not-i16",
@@ -161,6 +162,8 @@ def numpy_replay(g, inputs):
             before = [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim]
             y = np.full(op.outputs[0].shape, np.array(a["pad_value"]).astype(x.dtype), x.dtype)
             y[tuple(slice(b0, b0 + d) for b0, d in zip(before, x.shape))] = x
+        elif k == "table16":
+            y = onp.table16_elementwise(x, op.consts["table"].data)
         elif k == "concat_axis":
             y = np.concatenate([x, vals[op.inputs[1].id]], axis=a["i0"])
         elif k == "reduce":
@@ -194,8 +197,9 @@ def numpy_replay(g, inputs):
 
 def main(ref_root):
     out_dir = os.path.dirname(os.path.abspath(__file__))
-    only = os.environ.get("TOSA_CASES_ONLY")  # "generic": regenerate only the second list
-    for case in (GENERIC_CASES if only == "generic" else CASES + GENERIC_CASES):
+    only = os.environ.get("TOSA_CASES_ONLY")  # "generic": only the second list; or a comma list of case names
+    todo = GENERIC_CASES if only == "generic" else only.split(",") if only else CASES + GENERIC_CASES
+    for case in todo:
         path = os.path.join(ref_root, "tests", "testdata", case + ".mlir")
         g = tosa_frontend.build_graph_from_file(path)
         rng = np.random.default_rng(1234)

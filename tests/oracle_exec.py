@@ -74,6 +74,10 @@ def run_graph(graph, inputs, keep_all=False):
             y = np.pad(x, widths, constant_values=np.array(a["pad_value"]).astype(x.dtype))
         elif k == "concat_axis":
             y = np.concatenate([x, vals[op.inputs[1].id]], axis=a["i0"])
+        elif k == "softmax":
+            y = gops.softmax(x, op.inputs[0].dtype)
+        elif k == "table16":
+            y = gops.table16(x, op.consts["table"].data)
         elif k == "reduce":
             y = gops.reduce(a["i0"], x, op.inputs[0].dtype, a["i1"], op.outputs[0].shape, op.outputs[0].dtype)
         elif k == "resize_nn2x":

@@ -1,0 +1,199 @@
+"""The tensor ops outside the layer set on the GPU against the oracle (bit-exact for integers and for the exact
+float ops) and, for softmax and float means, against torch fp32 within the bf16 tolerance of the decoder ops.
+Shapes of the float cases are the reference's fixtures (tests/testdata/torch_ops/softmax-1x8x1x207xbf16.mlir,
+reducemean.mlir: rows of 207 and 288 values)."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_exec import run_graph_gpu
+from oracle_exec import run_graph
+from torq_b200.bf16 import from_bf16, to_bf16
+from torq_b200.oplist import EW_FN, Graph
+
+pytestmark = pytest.mark.gpu
+NP = {"i8": np.int8, "i16": np.int16, "i32": np.int32}
+
+
+def _same(device, g, inputs):
+    want = run_graph(g, inputs)
+    got = run_graph_gpu(device, g, inputs)
+    for w, o in zip(want, got):
+        assert w.shape == o.shape and w.dtype == o.dtype
+        assert (w.view(np.uint8) == o.view(np.uint8)).all(), f"{(w != o).sum()} of {w.size} differ"
+    return got
+
+
+@pytest.mark.parametrize("fn", [f for f, code in EW_FN.items() if code >= 16])
+@pytest.mark.parametrize("dtype", ["i8", "i16", "i32"])
+def test_binary_integer_ops_with_broadcast(device, fn, dtype):
+    if fn.startswith("logical_") and fn not in ("logical_left_shift",) and dtype != "i8":
+        pytest.skip("boolean ops live on i8 tensors")
+    rng = np.random.default_rng(EW_FN[fn] * 7 + len(dtype))
+    lim = {"i8": 128, "i16": 30000, "i32": 2 ** 31 - 1}[dtype]
+    a = rng.integers(-lim, lim, (3, 5, 7, 33)).astype(NP[dtype])
+    b = rng.integers(-lim, lim, (1, 5, 1, 33)).astype(NP[dtype])
+    arg = 0
+    if fn in ("logical_left_shift", "arithmetic_right_shift"):
+        b = rng.integers(0, 31, b.shape).astype(NP[dtype])
+        arg = 1
+    if fn == "mul" and dtype == "i32":
+        arg = 31
+    if fn.startswith("logical_") and fn != "logical_left_shift":
+        a, b = (a > 0).astype(np.int8), (b > 0).astype(np.int8)
+    if fn in ("equal", "greater_equal"):
+        a[:, :, ::2, :] = b[:, :, :, :]  # ties on half of the rows
+    out_dtype = "i8" if fn in ("equal", "greater", "greater_equal") or (fn.startswith("logical_") and fn != "logical_left_shift") else \
+        ("i32" if fn == "mul" else dtype)
+    g = Graph()
+    g.output(g.ew(fn, g.input(a.shape, dtype), g.input(b.shape, dtype), out_dtype=out_dtype, arg=arg))
+    got = _same(device, g, [a, b])
+    assert len(np.unique(got[0])) > 1
+
+
+@pytest.mark.parametrize("fn", ["abs", "negate", "bitwise_not", "clz", "clamp", "logical_not"])
+def test_unary_integer_ops(device, fn):
+    rng = np.random.default_rng(11)
+    x = rng.integers(-2 ** 31, 2 ** 31 - 1, (4, 1001)).astype(np.int32)
+    x[0, :4] = [0, -1, -2 ** 31, 2 ** 31 - 1]
+    g = Graph()
+    g.output(g.ew(fn, g.input(x.shape, "i32"), in_zp=3, out_zp=-5, clamp=(-1000, 77777)))
+    _same(device, g, [x])
+
+
+@pytest.mark.parametrize("src,dst", [("i32", "i8"), ("i32", "i16"), ("i8", "i32"), ("i16", "i8"), ("f32", "i8"), ("f32", "i32"),
+                                     ("bf16", "i16"), ("i32", "bf16"), ("i8", "f32"), ("bf16", "f32"), ("f32", "bf16")])
+def test_casts(device, src, dst):
+    rng = np.random.default_rng(5)
+    if src in ("f32", "bf16"):
+        v = rng.uniform(-70000, 70000, (7, 301)).astype(np.float32)
+        v[0, :6] = [0.5, 1.5, 2.5, -0.5, -1.5, 3e9]
+        x = to_bf16(v) if src == "bf16" else v
+    else:
+        x = rng.integers(-2 ** 31, 2 ** 31 - 1, (7, 301)).astype(NP[src])
+    g = Graph()
+    g.output(g.ew("cast", g.input(x.shape, src), out_dtype=dst))
+    _same(device, g, [x])
+
+
+@pytest.mark.parametrize("fn", ["add", "sub", "mul", "maximum", "minimum", "equal", "greater", "greater_equal"])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_float_elementwise_is_exact(device, fn, dtype):
+    rng = np.random.default_rng(9)
+    a = rng.uniform(-40, 40, (2, 9, 129)).astype(np.float32)
+    b = rng.uniform(-40, 40, (2, 1, 129)).astype(np.float32)
+    if dtype == "bf16":
+        a, b = to_bf16(a), to_bf16(b)
+    out_dtype = "i8" if fn in ("equal", "greater", "greater_equal") else dtype
+    g = Graph()
+    g.output(g.ew(fn, g.input(a.shape, dtype), g.input(b.shape, dtype), out_dtype=out_dtype))
+    _same(device, g, [a, b])
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype,unsigned", [("i32", "i8", (False, False)), ("i16", "i32", (False, False)),
+                                                         ("i8", "i16", (False, False)), ("i32", "i32", (False, False)),
+                                                         ("i8", "i8", (True, False)), ("i8", "i8", (False, True)),
+                                                         ("i32", "i16", (False, False))])
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_generic_rescale(device, in_dtype, out_dtype, unsigned, per_channel):
+    rng = np.random.default_rng(21)
+    C = 19
+    lim = {"i8": 128, "i16": 20000, "i32": 3000000}[in_dtype]
+    x = rng.integers(-lim, lim, (2, 6, 5, C)).astype(NP[in_dtype])
+    n = C if per_channel else 1
+    mult = rng.integers(1 << 30, (1 << 31) - 1, n).astype(np.int32)
+    lo, hi = {"i8": (28, 34), "i16": (36, 42), "i32": (44, 48)}[in_dtype]
+    shift = rng.integers(lo, hi, n).astype(np.int8)
+    g = Graph()
+    g.output(g.rescale(g.input(x.shape, in_dtype), mult, shift, input_zp=-3 if not unsigned[0] else 128, out_zp=7,
+                       out_dtype=out_dtype, input_unsigned=unsigned[0], output_unsigned=unsigned[1]))
+    got = _same(device, g, [x])
+    assert len(np.unique(got[0])) > 2
+
+
+def test_layout_ops(device):
+    rng = np.random.default_rng(3)
+    x = rng.integers(-128, 128, (3, 10, 7, 24)).astype(np.int8)
+    h = rng.integers(-30000, 30000, (5, 33, 17)).astype(np.int16)
+    w = rng.integers(-2 ** 31, 2 ** 31 - 1, (64, 96)).astype(np.int32)
+    g = Graph()
+    xi, hi, wi = g.input(x.shape), g.input(h.shape, "i16"), g.input(w.shape, "i32")
+    g.output(g.transpose(xi, [0, 3, 1, 2]))
+    g.output(g.transpose(hi, [2, 0, 1]))
+    g.output(g.transpose(wi, [1, 0]))
+    g.output(g.slice(xi, [1, 2, 3, 4], [2, 5, 3, 16]))
+    g.output(g.pad(xi, [0, 1, 2, 0], [0, 3, 0, 5], value=-77))
+    g.output(g.concat_axis(xi, g.slice(xi, [0, 0, 0, 0], [3, 4, 7, 24]), 1))
+    g.output(g.concat_axis(hi, hi, 2))
+    _same(device, g, [x, h, w])
+
+
+def test_layout_ops_in_16_byte_pieces(device):
+    """Extents, offsets and strides that let the copy move 16 (8, 4) bytes per index; padding repeats the element."""
+    rng = np.random.default_rng(13)
+    x = rng.integers(-128, 128, (2, 9, 6, 64)).astype(np.int8)
+    h = rng.integers(-30000, 30000, (4, 10, 24)).astype(np.int16)
+    w = rng.integers(-2 ** 31, 2 ** 31 - 1, (6, 5, 12)).astype(np.int32)
+    g = Graph()
+    xi, hi, wi = g.input(x.shape), g.input(h.shape, "i16"), g.input(w.shape, "i32")
+    g.output(g.slice(xi, [0, 2, 1, 16], [2, 5, 4, 32]))
+    g.output(g.pad(xi, [0, 1, 1, 16], [0, 2, 0, 48], value=-9))
+    g.output(g.concat_axis(xi, xi, 3))
+    g.output(g.concat_axis(xi, g.slice(xi, [0, 0, 0, 0], [2, 4, 6, 64]), 1))
+    g.output(g.slice(hi, [1, 3, 8], [2, 6, 16]))
+    g.output(g.pad(hi, [0, 0, 4], [1, 0, 4], value=-12345))     # 8-byte pieces
+    g.output(g.pad(wi, [1, 0, 4], [0, 2, 8], value=-2 ** 31))
+    g.output(g.transpose(xi, [0, 2, 1, 3]))                     # the channel axis stays innermost
+    _same(device, g, [x, h, w])
+
+
+@pytest.mark.parametrize("fn", ["sum", "max", "min", "argmax"])
+@pytest.mark.parametrize("axis", [0, 1, 2])
+def test_integer_reductions(device, fn, axis):
+    rng = np.random.default_rng(17)
+    x = rng.integers(-2 ** 30, 2 ** 30, (6, 37, 50)).astype(np.int32)
+    g = Graph()
+    g.output(g.reduce(fn, g.input(x.shape, "i32"), axis, keep_axis=fn != "argmax"))
+    _same(device, g, [x])
+
+
+def test_table16(device):
+    rng = np.random.default_rng(8)
+    x = rng.integers(-32768, 32768, (3, 4001)).astype(np.int16)
+    x[0, :4] = [-32768, 32767, 0, -1]
+    table = np.sort(rng.integers(-32768, 32767, 513)).astype(np.int16)
+    g = Graph()
+    g.output(g.table16(g.input(x.shape, "i16"), table))
+    _same(device, g, [x])
+
+
+@pytest.mark.parametrize("shape", [(1, 8, 1, 207), (1, 1000), (64, 1152)])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_softmax_against_torch(device, shape, dtype):
+    rng = np.random.default_rng(2)
+    v = rng.normal(0, 3, shape).astype(np.float32)
+    x = to_bf16(v) if dtype == "bf16" else v
+    g = Graph()
+    g.output(g.softmax(g.input(shape, dtype)))
+    got = run_graph_gpu(device, g, [x])[0]
+    ref = torch.softmax(torch.from_numpy(from_bf16(x) if dtype == "bf16" else x), -1).numpy()
+    got_f = from_bf16(got) if dtype == "bf16" else got
+    # tolerance of the floating-point class: 2 bf16 ulp of the value (bf16), 1e-5 relative (f32), rows sum to one
+    tol = 2.0 ** -7 if dtype == "bf16" else 1e-5
+    assert np.all(np.abs(got_f - ref) <= tol * np.maximum(ref, 1e-3))
+    assert np.allclose(got_f.sum(-1), 1.0, atol=2e-2 if dtype == "bf16" else 1e-5)
+
+
+@pytest.mark.parametrize("fn", ["mean", "sum", "max"])
+def test_float_reductions(device, fn):
+    """Sums and means add in fp32 in index order on both sides, so they are bit-exact against the oracle; against
+    torch (pairwise sums) they agree to fp32 rounding."""
+    rng = np.random.default_rng(4)
+    v = rng.normal(0, 1, (1, 207, 288)).astype(np.float32)
+    x = to_bf16(v)
+    g = Graph()
+    g.output(g.reduce(fn, g.input(x.shape, "bf16"), 2))
+    got = _same(device, g, [x])[0]
+    t = torch.from_numpy(from_bf16(x))
+    ref = {"mean": t.mean(-1, keepdim=True), "sum": t.sum(-1, keepdim=True), "max": t.max(-1, keepdim=True).values}[fn].numpy()
+    assert np.all(np.abs(from_bf16(got) - ref) <= 2.0 ** -7 * np.maximum(np.abs(ref), 1e-2))

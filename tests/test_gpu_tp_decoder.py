@@ -46,3 +46,23 @@ def test_tp_shared_head_and_uneven_mlp_on_two_gpus():
     r = _run(2, "shared", 2, 40, 0.3, 29531)
     assert r["worst_rel"] <= 1e-2, r
     assert r["agree"] == r["total"], r
+
+
+def test_member_that_misses_a_step_aborts_the_others_wait_and_the_group_recovers():
+    """Rank 1 launches nothing for one step: rank 0's kernel gives up at its wait limit (250 ms here), the host
+    wait answers ABORTED, the device still runs a single-GPU case, and after destroy / create / connect the
+    group's first steps are bit-identical to the first run (tests/tp_abort_worker.py)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29541", os.path.join(HERE, "tp_abort_worker.py")]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TB200_WAIT_LIMIT_MS="250")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("TP_ABORT ")][-1]
+    r = json.loads(line[len("TP_ABORT "):])
+    assert r["rank0_aborted"] and not r["rank1_aborted"], r
+    assert "bounded wait expired" in r["message"], r
+    assert 0.2 <= r["waited_s"] < 5.0, r
+    assert r["single_gpu_ok"] == [True, True], r
+    assert r["bit_identical_after_recreate"] == [True, True], r

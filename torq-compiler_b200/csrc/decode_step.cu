@@ -37,6 +37,7 @@
 #include <cstdio>
 
 #include "kernels.h"
+#include "status_word.cuh"
 
 namespace tb200 {
 
@@ -112,7 +113,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
       if (mbar_try_wait(bar, parity)) return true;
     if (*(volatile int*)status != 0) return false;
     if (globaltimer_ns() - t0 > s_wait_limit_ns) {
-      atomicCAS(status, 0, code);
+      report_expired_wait(status, code);
       return false;
     }
   }
@@ -157,7 +158,7 @@ __device__ __forceinline__ float wait_tagged(const uint32_t* p, uint32_t tag, in
       if ((w >> 16) == tag) return __uint_as_float(w << 16);
     }
     if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > s_wait_limit_ns) {
-      atomicCAS(status, 0, (int)kErrGrid);
+      report_expired_wait(status, (int)kErrGrid);
       ok = false;
       return 0.f;
     }
@@ -176,7 +177,7 @@ __device__ __forceinline__ uint4 wait_tagged4(const uint32_t* p, uint32_t tag, i
       if (good(w)) return w;
     }
     if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > s_wait_limit_ns) {
-      atomicCAS(status, 0, (int)kErrGrid);
+      report_expired_wait(status, (int)kErrGrid);
       ok = false;
       return make_uint4(0, 0, 0, 0);
     }
@@ -184,13 +185,16 @@ __device__ __forceinline__ uint4 wait_tagged4(const uint32_t* p, uint32_t tag, i
 }
 
 // Grid barriers. Counters only ever grow (64 bits): a launch starts from the bases its
-// predecessor left behind and adds one count per CTA per barrier. Barriers inside one GPU use
-// the local counter. A barrier that spans the tensor-parallel peers uses one of two counters in
-// alternation (so that a GPU that is one barrier ahead never adds to the counter its peers are
-// still waiting on); every CTA of every GPU adds to that counter on every GPU through peer
-// memory, its own GPU's first.
-// Counter block (byte offsets): local 0, global 8 and 16, their bases 24, 32, 40, exit count 48, epoch of
-// the tagged hand-overs 56.
+// predecessor left behind. Barriers inside one GPU use the local counter, one count per CTA.
+// A barrier that spans the tensor-parallel peers is hierarchical: every CTA adds to a gathering
+// counter of its own GPU, and only the CTA whose count completes the GPU's G arrivals adds one to the
+// barrier counter on every GPU through peer memory (tp - 1 NVLink atomics per GPU and barrier, not
+// G * (tp - 1)); the waiters' target therefore grows by tp per barrier. Two (gathering, barrier)
+// counter pairs alternate, so that a GPU that is one barrier ahead never adds to the counter its peers
+// are still waiting on; which pair comes next is carried from launch to launch with the bases (a launch
+// has an odd number of cross-GPU barriers).
+// Counter block (byte offsets): local 0, barrier 8 and 16, their bases 24, 32, 40, exit count 48, epoch of
+// the tagged hand-overs 56, next pair 60, gathering 64 and 72.
 struct BarrierState {
   unsigned long long local, global[2];  // expected values
   int parity;
@@ -201,12 +205,16 @@ struct BarrierState {
 __device__ __forceinline__ void grid_arrive(const DecodeStepArgs& a, bool all_gpus, int parity, bool fence = true) {
   if (all_gpus && a.tp > 1) {
     if (fence) __threadfence_system();
-    const unsigned long long off = a.counter_off + 8 + 8 * parity;
-    const unsigned long long old = atomicAdd_system((unsigned long long*)(a.scratch + off), 1ull);
-    // the peers' counters are touched only after this GPU's own count is in (address depends on it)
-    const unsigned long long dep = old & 0x8000000000000000ull;  // always zero
-    for (int r = 0; r < a.tp; r++)
-      if (r != a.rank) atomicAdd_system((unsigned long long*)(a.peer_scratch[r] + off + dep), 1ull);
+    unsigned long long* gather = (unsigned long long*)(a.scratch + a.counter_off + 64 + 8 * parity);
+    const unsigned long long old = atomicAdd(gather, 1ull);
+    if ((old + 1ull) % (unsigned long long)a.grid == 0ull) {
+      // every CTA of this GPU has arrived (each after its own system-scope fence): tell every GPU, this one first
+      __threadfence_system();
+      const unsigned long long off = a.counter_off + 8 + 8 * parity;
+      atomicAdd_system((unsigned long long*)(a.scratch + off), 1ull);
+      for (int r = 0; r < a.tp; r++)
+        if (r != a.rank) atomicAdd_system((unsigned long long*)(a.peer_scratch[r] + off), 1ull);
+    }
   } else {
     if (fence) __threadfence();
     atomicAdd((unsigned long long*)(a.scratch + a.counter_off), 1ull);
@@ -228,7 +236,7 @@ __device__ __forceinline__ bool grid_wait(const DecodeStepArgs& a, bool all_gpus
       if ((sys ? ld_acquire_sys(counter) : ld_acquire_gpu(counter)) >= target) return true;
     if (*(volatile int*)status != 0) return false;
     if (globaltimer_ns() - t0 > s_wait_limit_ns) {
-      atomicCAS(status, 0, (int)kErrGrid);
+      report_expired_wait(status, (int)kErrGrid);
       return false;
     }
   }
@@ -1132,7 +1140,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
   bs.local = bases[0];
   bs.global[0] = bases[1];
   bs.global[1] = bases[2];
-  bs.parity = 0;
+  bs.parity = *(const int*)(a.scratch + a.counter_off + 60);
   if (warp == kProducerWarp) {
     // ---------------- producer: stream this CTA's weight rows, in consumption order ----------------
     RingPos pc{0, 0};
@@ -1179,7 +1187,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
   } else if (warp == kReducerWarp) {
     // ---------------- reducer ----------------
     RingPos tiles{0, 0};
-    int gpar = 0;  // which of the two cross-GPU counters the next cross-GPU barrier uses
+    int gpar = bs.parity;  // which of the two cross-GPU counter pairs the next cross-GPU barrier uses
     ArgBest best;
     best.v[0] = best.v[1] = -INFINITY;
     best.i[0] = best.i[1] = 0x7fffffff;
@@ -1249,7 +1257,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       unsigned long long target;
       const int parity = bs.parity;
       if (sys) {
-        target = (bs.global[parity] += (unsigned long long)G * a.tp);
+        target = (bs.global[parity] += (unsigned long long)a.tp);
         bs.parity ^= 1;
       } else {
         target = (bs.local += (unsigned long long)G);
@@ -1398,6 +1406,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       next[0] = bs.local;
       next[1] = bs.global[0];
       next[2] = bs.global[1];
+      *(int*)(a.scratch + a.counter_off + 60) = bs.parity;
       *(uint32_t*)(a.scratch + a.counter_off + 56) = epoch_base + 4u * (uint32_t)a.n_layers;
       *exit_count = 0;
       __threadfence();

@@ -157,6 +157,26 @@ __global__ void __launch_bounds__(256) rescale_generic_kernel(RescaleGenericArgs
   }
 }
 
+// one piece of padding: the element's value repeated over the piece
+template <typename T>
+__device__ __forceinline__ T pad_piece(int value, int elem_bytes);
+template <> __device__ __forceinline__ uint8_t pad_piece<uint8_t>(int value, int) { return (uint8_t)value; }
+template <> __device__ __forceinline__ uint16_t pad_piece<uint16_t>(int value, int) { return (uint16_t)value; }
+__device__ __forceinline__ uint32_t pad_word(int value, int elem_bytes) {
+  return elem_bytes == 1 ? (uint32_t)(value & 0xff) * 0x01010101u
+         : elem_bytes == 2 ? (uint32_t)(value & 0xffff) * 0x00010001u
+                           : (uint32_t)value;
+}
+template <> __device__ __forceinline__ uint32_t pad_piece<uint32_t>(int value, int eb) { return pad_word(value, eb); }
+template <> __device__ __forceinline__ uint2 pad_piece<uint2>(int value, int eb) {
+  const uint32_t w = pad_word(value, eb);
+  return make_uint2(w, w);
+}
+template <> __device__ __forceinline__ uint4 pad_piece<uint4>(int value, int eb) {
+  const uint32_t w = pad_word(value, eb);
+  return make_uint4(w, w, w, w);
+}
+
 // out[o] = in[in_offset + sum (o_d - lo_d) * in_str_d] when every (o_d - lo_d) lies in [0, in_dims_d), else the pad
 // value; the output element sits at out_offset + sum o_d * out_str_d. One kernel for transpose, slice, pad and concat.
 template <typename T>
@@ -176,7 +196,7 @@ __global__ void __launch_bounds__(256) strided_copy_kernel(StridedCopyArgs a) {
       si += (long long)ci * a.in_str[d];
       di += (long long)c * a.out_str[d];
     }
-    dst[di] = inside ? src[si] : (T)a.pad_value;
+    dst[di] = inside ? src[si] : pad_piece<T>(a.pad_value, a.pad_elem_bytes);
   }
 }
 
@@ -194,7 +214,11 @@ __global__ void __launch_bounds__(256) reduce_kernel(ReduceArgs a) {
       const float v = load_float(a.x, a.in_dtype, base + (long long)k * a.inner);
       if (a.fn == 2 ? v < best : v > best) { best = v; arg = k; }
     }
-    if (a.fn == 3) store_int(a.out, a.out_dtype, i, arg);
+    if (a.fn == 0 || a.fn == 4) {  // fp32 sum in index order; mean = sum / count
+      float sum = 0.f;
+      for (int k = 0; k < a.axis; k++) sum = sum + load_float(a.x, a.in_dtype, base + (long long)k * a.inner);
+      store_float(a.out, a.out_dtype, i, a.fn == 4 ? sum / (float)a.axis : sum);
+    } else if (a.fn == 3) store_int(a.out, a.out_dtype, i, arg);
     else store_float(a.out, a.out_dtype, i, best);
   } else {
     int best = load_int(a.x, a.in_dtype, base), arg = 0;
@@ -206,6 +230,37 @@ __global__ void __launch_bounds__(256) reduce_kernel(ReduceArgs a) {
     }
     store_int(a.out, a.out_dtype, i, a.fn == 0 ? (int)sum : a.fn == 3 ? arg : best);
   }
+}
+
+__global__ void __launch_bounds__(256) table16_kernel(const int16_t* __restrict__ x, const int16_t* __restrict__ table,
+                                                      int32_t* __restrict__ out, long long n) {
+  __shared__ int16_t t[513];
+  for (int i = threadIdx.x; i < 513; i += blockDim.x) t[i] = table[i];
+  __syncthreads();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int v = x[i];
+    const int index = (v + 32768) >> 7, frac = v & 0x7f;
+    const int base = t[index], next = t[index + 1];
+    out[i] = base * 128 + (next - base) * frac;
+  }
+}
+
+// One warp per row: maximum, exp and sum in fp32, then one multiplication by the reciprocal of the sum.
+__global__ void __launch_bounds__(256) softmax_kernel(const void* __restrict__ x, void* __restrict__ out, long long rows, int cols,
+                                                      int dtype) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const long long base = row * cols;
+  float m = -INFINITY;
+  for (int c = lane; c < cols; c += 32) m = fmaxf(m, load_float(x, dtype, base + c));
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float sum = 0.f;
+  for (int c = lane; c < cols; c += 32) sum += expf(load_float(x, dtype, base + c) - m);
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.0f / sum;
+  for (int c = lane; c < cols; c += 32) store_float(out, dtype, base + c, expf(load_float(x, dtype, base + c) - m) * inv);
 }
 
 unsigned grid_for(long long n) {
@@ -223,7 +278,37 @@ void launch_rescale_generic(const RescaleGenericArgs& a, cudaStream_t stream) {
 void launch_strided_copy(const StridedCopyArgs& a, cudaStream_t stream) {
   if (a.elem_bytes == 1) strided_copy_kernel<uint8_t><<<grid_for(a.n), 256, 0, stream>>>(a);
   else if (a.elem_bytes == 2) strided_copy_kernel<uint16_t><<<grid_for(a.n), 256, 0, stream>>>(a);
-  else strided_copy_kernel<uint32_t><<<grid_for(a.n), 256, 0, stream>>>(a);
+  else if (a.elem_bytes == 4) strided_copy_kernel<uint32_t><<<grid_for(a.n), 256, 0, stream>>>(a);
+  else if (a.elem_bytes == 8) strided_copy_kernel<uint2><<<grid_for(a.n), 256, 0, stream>>>(a);
+  else strided_copy_kernel<uint4><<<grid_for(a.n), 256, 0, stream>>>(a);
+}
+void widen_strided_copy(StridedCopyArgs& a) {
+  if (a.in_str[3] != 1 || a.out_str[3] != 1) return;
+  for (int bytes = 16; bytes > a.elem_bytes; bytes >>= 1) {
+    const int v = bytes / a.elem_bytes;
+    bool fits = a.dims[3] % v == 0 && a.lo[3] % v == 0 && (a.in_dims[3] == (1 << 30) || a.in_dims[3] % v == 0) &&
+                a.in_offset % v == 0 && a.out_offset % v == 0;
+    for (int d = 0; d < 3 && fits; d++) fits = a.in_str[d] % v == 0 && a.out_str[d] % v == 0;
+    if (!fits) continue;
+    a.dims[3] /= v;
+    a.lo[3] /= v;
+    if (a.in_dims[3] != (1 << 30)) a.in_dims[3] /= v;
+    for (int d = 0; d < 3; d++) {
+      a.in_str[d] /= v;
+      a.out_str[d] /= v;
+    }
+    a.in_offset /= v;
+    a.out_offset /= v;
+    a.n /= v;
+    a.elem_bytes = bytes;
+    return;
+  }
+}
+void launch_softmax(const void* x, void* out, long long rows, int cols, int dtype, cudaStream_t stream) {
+  softmax_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(x, out, rows, cols, dtype);
+}
+void launch_table16(const int16_t* x, const int16_t* table, int32_t* out, long long n, cudaStream_t stream) {
+  table16_kernel<<<grid_for(n), 256, 0, stream>>>(x, table, out, n);
 }
 void launch_reduce(const ReduceArgs& a, cudaStream_t stream) {
   const long long total = (long long)a.outer * a.inner;

@@ -276,21 +276,27 @@ struct StridedCopyArgs {
   const void* in;
   void* out;
   long long n;            // elements visited = product of dims
-  int elem_bytes;         // 1, 2 or 4
+  int elem_bytes;         // bytes moved per index: 1, 2 or 4 (the element), or 8 / 16 after widen_strided_copy
+  int pad_elem_bytes;     // the tensor's element size (pad_value is one such element)
   int dims[4];            // extents of the index space (of the output region written)
   int lo[4], in_dims[4];  // input coordinate = index - lo, valid inside [0, in_dims)
   long long in_str[4], out_str[4], in_offset, out_offset;  // in elements
   int pad_value;
 };
 void launch_strided_copy(const StridedCopyArgs& a, cudaStream_t stream);
+// Regroups the innermost dimension into 16-, 8- or 4-byte pieces when it is dense on both sides and every
+// extent, offset and stride allows it (host side, plan time).
+void widen_strided_copy(StridedCopyArgs& a);
 struct ReduceArgs {
   const void* x;
   void* out;
   int outer, axis, inner;  // x viewed as [outer, axis, inner]
-  int fn;                  // 0 sum, 1 max, 2 min, 3 argmax
+  int fn;                  // 0 sum, 1 max, 2 min, 3 argmax, 4 mean (floats)
   int in_dtype, out_dtype;
 };
 void launch_reduce(const ReduceArgs& a, cudaStream_t stream);
+void launch_softmax(const void* x, void* out, long long rows, int cols, int dtype, cudaStream_t stream);
+void launch_table16(const int16_t* x, const int16_t* table, int32_t* out, long long n, cudaStream_t stream);
 
 void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream);
 

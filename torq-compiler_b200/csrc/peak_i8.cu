@@ -101,8 +101,8 @@ extern "C" int tb200_measure_i8_mma_peak(int cuda_ordinal, int rounds, double* t
   float ms = 0.f;
   int code = 0;
   const int sms = current_sm_count();
-  if (cudaMalloc(&status, sizeof(int)) != cudaSuccess) return TB200_RESOURCE_EXHAUSTED;
-  if (cudaMemset(status, 0, sizeof(int)) == cudaSuccess && cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) == cudaSuccess &&
+  if (cudaMalloc(&status, kStatusBlockBytes) != cudaSuccess) return TB200_RESOURCE_EXHAUSTED;
+  if (cudaMemset(status, 0, kStatusBlockBytes) == cudaSuccess && cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) == cudaSuccess &&
       cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess) {
     peak_i8_kernel<<<sms, 128, smem, stream>>>(rounds, status, wait_limit_ns());  // warm-up (clocks, instruction cache)
     cudaEventRecord(e0, stream);

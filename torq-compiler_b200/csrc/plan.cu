@@ -1512,7 +1512,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         };
         std::vector<StridedCopyArgs> parts;
         StridedCopyArgs a{};
-        a.elem_bytes = esz; a.pad_value = op.pad_value;
+        a.elem_bytes = esz; a.pad_elem_bytes = esz; a.pad_value = op.pad_value;
         long long istr[4], ostr[4];
         int idims[4], odims[4];
         dense(ti, istr, idims);
@@ -1561,7 +1561,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             parts.push_back(c2);
           }
         }
-        for (auto& pt : parts) { pt.n = 1; for (int d = 0; d < 4; d++) pt.n *= pt.dims[d]; }
+        for (auto& pt : parts) { pt.n = 1; for (int d = 0; d < 4; d++) pt.n *= pt.dims[d]; widen_strided_copy(pt); }
         Loc l0 = loc(op.in0), l1 = concat ? loc(op.in1) : Loc{}, lo = loc(op.out0);
         step.kernel_name = op.kind == TB200_OP_TRANSPOSE ? "transpose" : op.kind == TB200_OP_SLICE ? "slice"
                            : op.kind == TB200_OP_PAD ? "pad" : "concat_axis";
@@ -1576,14 +1576,40 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         };
         break;
       }
+      case TB200_OP_SOFTMAX: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || tensors[op.in0].dtype != tensors[op.out0].dtype ||
+            (tensors[op.in0].dtype != TB200_BF16 && tensors[op.in0].dtype != TB200_F32) || b.numel(op.in0) != b.numel(op.out0))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: softmax wants bf16 or f32 tensors of equal size", i);
+        const auto& x = tensors[op.in0];
+        const int cols = x.shape[x.rank - 1], dt = (int)x.dtype;
+        const long long rows = (long long)(b.numel(op.in0) / cols);
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "softmax";
+        step.launch = [=](const ExecContext& c) { launch_softmax(lx.resolve(c), lo.resolve(c), rows, cols, dt, c.stream); };
+        break;
+      }
+      case TB200_OP_TABLE16: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || tensors[op.in0].dtype != TB200_I16 ||
+            tensors[op.out0].dtype != TB200_I32 || b.numel(op.in0) != b.numel(op.out0))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: table16 wants an int16 input and an int32 output of equal size", i);
+        const int16_t* tbl = b.const_data<int16_t>(op.table, 513, "table", i);
+        if (!tbl) return b.status;
+        const size_t t_off = b.add_const(tbl, 513 * 2);
+        const long long n = (long long)b.numel(op.in0);
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "table16";
+        step.launch = [=](const ExecContext& c) {
+          launch_table16((const int16_t*)lx.resolve(c), (const int16_t*)(c.consts + t_off), (int32_t*)lo.resolve(c), n, c.stream);
+        };
+        break;
+      }
       case TB200_OP_REDUCE: {
         if (!b.valid_id(op.in0) || !b.valid_id(op.out0)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad tensor id", i);
         const auto& ti = tensors[op.in0];
         const int axis = op.i1;
-        if (axis < 0 || axis >= (int)ti.rank || op.i0 < 0 || op.i0 > 3 || ti.dtype == TB200_I64)
+        const bool in_float = ti.dtype == TB200_F32 || ti.dtype == TB200_BF16;
+        if (axis < 0 || axis >= (int)ti.rank || op.i0 < 0 || op.i0 > 4 || ti.dtype == TB200_I64 || (op.i0 == 4 && !in_float))
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad reduction axis, function or element type", i);
-        if (op.i0 == 0 && (ti.dtype == TB200_F32 || ti.dtype == TB200_BF16))
-          return b.fail(TB200_UNIMPLEMENTED, "op %d: floating-point reduce_sum is not an exact op and is not offered", i);
         ReduceArgs a{};
         a.outer = a.inner = 1;
         for (int d = 0; d < axis; d++) a.outer *= ti.shape[d];

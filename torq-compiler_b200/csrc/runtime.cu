@@ -35,7 +35,7 @@ struct tb200_device {
   FILE* profile_csv = nullptr;
   uint64_t invocation_id = 0;
   int* status_word = nullptr;  // device word a kernel writes when one of its bounded waits expires
-  int* status_host = nullptr;  // pinned host copy of it, refreshed by a stream-ordered copy at the end of every dispatch
+  int* status_host = nullptr;  // mapped pinned host word: the kernel that gives up stores its code here too (status_word.cuh)
   std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
 };
 
@@ -120,9 +120,15 @@ extern "C" int tb200_device_create(int ordinal, tb200_device_t** out) {
     delete d;
     return TB200_INTERNAL;
   }
-  if (cudaMalloc(&d->status_word, sizeof(int)) != cudaSuccess || cudaMemset(d->status_word, 0, sizeof(int)) != cudaSuccess ||
-      cudaHostAlloc((void**)&d->status_host, sizeof(int), cudaHostAllocDefault) != cudaSuccess) {
+  int* mirror_dev = nullptr;
+  if (cudaMalloc(&d->status_word, tb200::kStatusBlockBytes) != cudaSuccess ||
+      cudaMemset(d->status_word, 0, tb200::kStatusBlockBytes) != cudaSuccess ||
+      cudaHostAlloc((void**)&d->status_host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess ||
+      cudaHostGetDevicePointer((void**)&mirror_dev, d->status_host, 0) != cudaSuccess ||
+      cudaMemcpy(reinterpret_cast<char*>(d->status_word) + 8, &mirror_dev, sizeof(mirror_dev), cudaMemcpyHostToDevice) !=
+          cudaSuccess) {
     if (d->status_word) cudaFree(d->status_word);
+    if (d->status_host) cudaFreeHost(d->status_host);
     cudaStreamDestroy(d->copy_stream);
     cudaStreamDestroy(d->stream);
     delete d;
@@ -576,8 +582,6 @@ int run_plan(tb200_executable* ex, const std::vector<void*>& io, std::vector<cud
     ex->plan.steps[i].launch(ctx);
   }
   if (events) cudaEventRecord((*events)[ex->plan.steps.size()], d->stream);
-  // the status word follows the kernels to pinned host memory, so the host wait reads it without a copy of its own
-  cudaMemcpyAsync(d->status_host, d->status_word, sizeof(int), cudaMemcpyDeviceToHost, d->stream);
   CUDA_OK(d, launch_error);
   CUDA_OK(d, cudaGetLastError());
   return TB200_OK;
@@ -718,8 +722,8 @@ extern "C" int tb200_wait(tb200_device_t* d, uint64_t timeout_ns) {
   for (;;) {
     cudaError_t e = cudaStreamQuery(d->stream);
     if (e == cudaSuccess) {
-      // The stream drained: did a kernel give up on one of its bounded waits? Every dispatch ends with a
-      // stream-ordered copy of the device status word to pinned host memory, so this is a plain read.
+      // The stream drained: did a kernel give up on one of its bounded waits? The kernel that gives up stores
+      // its code in this mapped host word as well as in the device word, so this is a plain read.
       const int code = *(volatile int*)d->status_host;
       if (code != 0) {
         *(volatile int*)d->status_host = 0;
@@ -832,7 +836,6 @@ extern "C" int tb200_device_probe_bounded_wait(tb200_device_t* d, uint32_t limit
   cudaSetDevice(d->ordinal);
   wait_probe_kernel<<<1, 32, 0, d->stream>>>(d->status_word, (unsigned long long)limit_ms * 1000000ull);
   CUDA_OK(d, cudaGetLastError());
-  CUDA_OK(d, cudaMemcpyAsync(d->status_host, d->status_word, sizeof(int), cudaMemcpyDeviceToHost, d->stream));
   return TB200_OK;
 }
 

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "status_word.cuh"
+
 namespace tb200 {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -47,7 +49,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     for (int i = 0; i < 256; i++)
       if (mbar_try_wait(bar, parity)) return true;
     if (globaltimer_ns() - t0 > limit_ns) {
-      if (*(volatile int*)status == 0) *(volatile int*)status = code;
+      report_expired_wait(status, code);
       return false;
     }
   }

@@ -29,7 +29,7 @@ OP_KINDS = {
     "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
     "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
     "add_bf16": 38, "argmax": 39, "allreduce": 40, "act_bf16": 41, "gemv_q8b": 42,
-    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53,
+    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55,
 }
 
 EW_FN = {"cast": 0, "abs": 1, "negate": 2, "bitwise_not": 3, "logical_not": 4, "clz": 5, "clamp": 6, "ceil": 7, "floor": 8,
@@ -37,7 +37,7 @@ EW_FN = {"cast": 0, "abs": 1, "negate": 2, "bitwise_not": 3, "logical_not": 4, "
          "bitwise_xor": 23, "logical_left_shift": 24, "arithmetic_right_shift": 25, "equal": 26, "greater": 27,
          "greater_equal": 28, "logical_and": 29, "logical_or": 30, "logical_xor": 31}
 FLAG_INPUT_UNSIGNED, FLAG_OUTPUT_UNSIGNED, FLAG_BOOL_RESULT = 1, 2, 4
-REDUCE_FN = {"sum": 0, "max": 1, "min": 2, "argmax": 3}
+REDUCE_FN = {"sum": 0, "max": 1, "min": 2, "argmax": 3, "mean": 4}
 
 
 class Header(C.Structure):
@@ -286,6 +286,19 @@ class Graph:
         return self._emit("ew", [a] if b is None else [a, b], shape, out_dtype or a.dtype, i0=EW_FN[fn], i1=int(arg),
                           in0_zp=int(in_zp), out_zp=int(out_zp), clamp_min=int(clamp[0]), clamp_max=int(clamp[1]),
                           f0=float(fclamp[0]), f1=float(fclamp[1]), flags=FLAG_BOOL_RESULT if bool_result else 0)
+
+    def softmax(self, x):
+        """softmax over the last axis of a bf16 / f32 tensor."""
+        if x.dtype not in ("bf16", "f32"):
+            raise ValueError("softmax wants a bf16 or f32 tensor")
+        return self._emit("softmax", [x], x.shape, x.dtype)
+
+    def table16(self, x, table):
+        """tosa.table on an int16 tensor: 513 int16 entries, interpolated; int32 result."""
+        t = np.asarray(table, np.int16)
+        if t.size != 513 or x.dtype != "i16":
+            raise ValueError("table16 wants an i16 tensor and 513 entries")
+        return self._emit("table16", [x], x.shape, "i32", consts={"table": self.const(t)})
 
     def transpose(self, x, perm):
         perm = [int(p) for p in perm]

@@ -398,6 +398,9 @@ def build_graph(text: str) -> Graph:
                                        out_ms=(int(po["mult"][0]), int(po["shift"][0])), out_zp=po["ozp"], clamp=(lo, hi),
                                        double_round=po["double_round"], a_lshift=la, b_lshift=lb)
         elif n == "table":
+            if op.operands[0].dtype == "i16":
+                env[op.result.name] = g.table16(get(op.operands[0]), op.operands[1].const.reshape(-1))
+                return
             env[op.result.name] = g.table(get(op.operands[0]), op.operands[1].const.reshape(-1))
         elif n == "pad":
             mp = only_user(op, "max_pool2d")
