@@ -111,6 +111,11 @@ enum tb200_op_kind {
                                * (base << 7) + (next - base) * fraction; the reference's i16 table op is ExtractPattern.cpp:439-545 */
   TB200_OP_SOFTMAX = 55,      /* softmax over the last axis of a bf16 / f32 tensor: subtract the row maximum, exp, sum, multiply by the
                                * reciprocal (the order of SoftmaxPattern.cpp:23-333); fp32 inside, one rounding to the result type */
+  TB200_OP_CONV2D_I16 = 56,   /* Conv2D on int16 activations with int8 weights (doc/user-manual/ops.md: "Conv2D i16 i8 -> i32, TOSA specifies
+                               * i48 output"; fixture tests/testdata/gen_ops/conv2d_64x64_i16.mlir) fused with the tosa.rescale
+                               * {scale32 = false} that follows it: 64-bit accumulator + bias (i64[OC] or i64[1]), TOSA apply_scale_16
+                               * (acc * multiplier + 2^(shift-1)) >> shift with a 16-bit multiplier, single rounding, + out_zp, clamp,
+                               * int16 result. Attributes as CONV2D. */
   TB200_OP_ALLREDUCE = 40,    /* sum of the fp32 partial results of the i0 GPUs of a tensor-parallel group
                                * (this one is rank i1), rounded to bf16; only inside the fused decode step */
 };

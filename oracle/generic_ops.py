@@ -196,6 +196,44 @@ def reduce(fn: int, x: np.ndarray, dtype: str, axis: int, out_shape, out_dtype: 
     return _store(r, flt, out_dtype).reshape(out_shape)
 
 
+def matmul_int(a: np.ndarray, b: np.ndarray, a_zp: int, b_zp: int, out_dtype: str) -> np.ndarray:
+    """tosa.matmul on int8 or int16 operands as the reference lowers it (doc/user-manual/ops.md: MatMul i16 x i16 -> i32,
+    "TOSA specifies i48 output"): products added one k at a time into an int32 that wraps, stored as int32 or
+    truncated to int16."""
+    x = a.astype(np.int64) - a_zp
+    y = b.astype(np.int64) - b_zp
+    acc = np.zeros((x.shape[0], y.shape[1]), np.int64)
+    for k in range(x.shape[1]):
+        acc = wrap(acc + wrap(x[:, k, None] * y[None, k, :], 32), 32)
+    return wrap(acc, INT_BITS[out_dtype]).astype({"i16": np.int16, "i32": np.int32}[out_dtype])
+
+
+def conv2d_i16(x: np.ndarray, w: np.ndarray, bias: np.ndarray, mult, shift, *, stride, dilation, pad, input_zp: int, weight_zp: int,
+               out_zp: int, clamp) -> np.ndarray:
+    """tosa.conv2d on int16 activations / int8 weights with acc_type i48, then tosa.rescale {scale32 = false, SINGLE_ROUND}
+    (TOSA 1.0 apply_scale_16: (value * multiplier + 2^(shift-1)) >> shift with a 16-bit multiplier), + out_zp, clamp, int16.
+    x NHWC, w OHWI, pad = (top, bottom, left, right); padded positions contribute (input_zp - input_zp) = 0."""
+    N, H, W, IC = x.shape
+    OC, KH, KW, _ = w.shape
+    OH = (H + pad[0] + pad[1] - (KH - 1) * dilation[0] - 1) // stride[0] + 1
+    OW = (W + pad[2] + pad[3] - (KW - 1) * dilation[1] - 1) // stride[1] + 1
+    xp = np.zeros((N, H + pad[0] + pad[1], W + pad[2] + pad[3], IC), np.int64)
+    xp[:, pad[0]:pad[0] + H, pad[2]:pad[2] + W, :] = x.astype(np.int64) - input_zp
+    wz = w.astype(np.int64) - weight_zp
+    acc = np.zeros((N, OH, OW, OC), np.int64)
+    for kh in range(KH):
+        for kw in range(KW):
+            h0, w0 = kh * dilation[0], kw * dilation[1]
+            win = xp[:, h0:h0 + (OH - 1) * stride[0] + 1:stride[0], w0:w0 + (OW - 1) * stride[1] + 1:stride[1], :]
+            acc += np.einsum("nhwc,oc->nhwo", win, wz[:, kh, kw, :])
+    b = np.asarray(bias, np.int64).reshape(-1)
+    acc = acc + (b if b.size == OC else b[:1])
+    m = np.asarray(mult, np.int64).reshape(-1)
+    s = np.asarray(shift, np.int64).reshape(-1)
+    r = (acc * m + (np.int64(1) << (s - 1))) >> s
+    return np.clip(r + out_zp, clamp[0], clamp[1]).astype(np.int16)
+
+
 def table16(x: np.ndarray, table: np.ndarray) -> np.ndarray:
     """tosa.table, int16 in, 513-entry int16 table, int32 out: linear interpolation over the low 7 bits."""
     v = x.astype(np.int64)

@@ -349,3 +349,36 @@ def table16_elementwise(x, table):
         i, f = (v + 32768) >> 7, v & 0x7F
         out.append(t[i] * 128 + (t[i + 1] - t[i]) * f)
     return np.array(out, np.int32).reshape(x.shape)
+
+
+def conv2d_i16_elementwise(x, w, bias, mult, shift, stride, dilation, pad, input_zp, weight_zp, out_zp, clamp_min, clamp_max):
+    """Element-by-element statement with Python integers of the int16 convolution + 16-bit rescale (small cases only)."""
+    N, H, W, IC = x.shape
+    OC, KH, KW, _ = w.shape
+    OH = (H + pad[0] + pad[1] - (KH - 1) * dilation[0] - 1) // stride[0] + 1
+    OW = (W + pad[2] + pad[3] - (KW - 1) * dilation[1] - 1) // stride[1] + 1
+    xl, wl = x.tolist(), w.tolist()
+    bl = [int(v) for v in np.asarray(bias).reshape(-1)]
+    ml = [int(v) for v in np.asarray(mult).reshape(-1)]
+    sl = [int(v) for v in np.asarray(shift).reshape(-1)]
+    out = np.empty((N, OH, OW, OC), np.int16)
+    for n in range(N):
+        for oh in range(OH):
+            for ow in range(OW):
+                for oc in range(OC):
+                    acc = bl[oc if len(bl) > 1 else 0]
+                    for kh in range(KH):
+                        ih = oh * stride[0] - pad[0] + kh * dilation[0]
+                        if not 0 <= ih < H:
+                            continue
+                        for kw in range(KW):
+                            iw = ow * stride[1] - pad[2] + kw * dilation[1]
+                            if not 0 <= iw < W:
+                                continue
+                            px, wt = xl[n][ih][iw], wl[oc][kh][kw]
+                            for c in range(IC):
+                                acc += (px[c] - input_zp) * (wt[c] - weight_zp)
+                    m, sh = ml[oc if len(ml) > 1 else 0], sl[oc if len(sl) > 1 else 0]
+                    r = ((acc * m + (1 << (sh - 1))) >> sh) + out_zp
+                    out[n, oh, ow, oc] = min(max(r, clamp_min), clamp_max)
+    return out

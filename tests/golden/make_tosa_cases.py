@@ -89,6 +89,8 @@ GENERIC_CASES = [
     "tosa_ops/identity-64-i16", "tosa_ops/identity-64-i32", "tosa_ops/identity-stride-offset-123x120xi8",
     "tosa_ops/identity-stride-offset-6x15x5xi8", "tosa_ops/identity-stride-offset-6x15x70xi8",
     "tosa_ops/identity-stride-offset-6x6xi8", "tosa_ops/matmul-in-int8-out-int16",
+    "tosa_ops/matmul-in-int16-out-int16", "tosa_ops/matmul-in-int16-out-int32",
+    "tosa_ops/matmul-in-int8-out-int16-64x128x2048", "gen_ops/conv2d_64x64_i16",
     "tosa_ops/mul-1hw1-in-int8-out-int32", "tosa_ops/mul-1hwc-in-int16-out-int32",
     "tosa_ops/mul-1hwc-in-int8-out-int32-1", "tosa_ops/mul-1hwc-in-int8-out-int32-2dim",
     "tosa_ops/mul-1hwc-in-int8-out-int32-3dim", "tosa_ops/mul-1hwc-in-int8-out-int32", "tosa_ops/mul-bf16",
@@ -183,8 +185,13 @@ def numpy_replay(g, inputs):
         elif k == "rescale":
             y = onp.rescale(x, op.consts["multiplier"].data, op.consts["shift"].data, a["in0_zp"], a["out_zp"], a["clamp_min"],
                             a["clamp_max"], bool(a["double_round"]), a["requant_mode"])
+        elif k == "conv2d_i16":
+            y = onp.conv2d_i16_elementwise(x, op.consts["weights"].data, op.consts["bias"].data, op.consts["multiplier"].data,
+                                           op.consts["shift"].data, (a["stride_h"], a["stride_w"]), (a["dil_h"], a["dil_w"]),
+                                           (a["pad_t"], a["pad_b"], a["pad_l"], a["pad_r"]), a["in0_zp"], a["weight_zp"],
+                                           a["out_zp"], a["clamp_min"], a["clamp_max"])
         elif k == "matmul_i32":
-            y = onp.matmul_i32(x, vals[op.inputs[1].id], a["in0_zp"], a["weight_zp"])
+            y = onp.matmul_i32(x, vals[op.inputs[1].id], a["in0_zp"], a["weight_zp"]).astype(NP_DTYPE[op.outputs[0].dtype])
         elif k == "resize_nn2x":
             y = onp.resize_nn2x(x)
         elif k == "reshape":

@@ -27,6 +27,11 @@ def run_graph(graph, inputs, keep_all=False):
                           stride=(a["stride_h"], a["stride_w"]), dilation=(a["dil_h"], a["dil_w"]),
                           pad=(a["pad_t"], a["pad_b"], a["pad_l"], a["pad_r"]), input_zp=a["in0_zp"],
                           weight_zp=a["weight_zp"])
+        elif k == "conv2d_i16":
+            y = gops.conv2d_i16(x, op.consts["weights"].data, op.consts["bias"].data, op.consts["multiplier"].data,
+                                op.consts["shift"].data, stride=(a["stride_h"], a["stride_w"]), dilation=(a["dil_h"], a["dil_w"]),
+                                pad=(a["pad_t"], a["pad_b"], a["pad_l"], a["pad_r"]), input_zp=a["in0_zp"],
+                                weight_zp=a["weight_zp"], out_zp=a["out_zp"], clamp=(a["clamp_min"], a["clamp_max"]))
         elif k == "depthwise":
             y = oc.depthwise(x, op.consts["weights"].data, op.consts["bias"].data, _rq(op),
                              stride=(a["stride_h"], a["stride_w"]), dilation=(a["dil_h"], a["dil_w"]),
@@ -37,7 +42,10 @@ def run_graph(graph, inputs, keep_all=False):
                                    input_zp=a["in0_zp"], weight_zp=a["weight_zp"])
         elif k == "matmul_i32":
             rhs = op.consts["weights"].data if "weights" in op.consts else vals[op.inputs[1].id]
-            y = oc.matmul_i32(x, rhs, a["in0_zp"], a["weight_zp"])
+            if op.inputs[0].dtype == "i16" or op.outputs[0].dtype == "i16":
+                y = gops.matmul_int(x, rhs, a["in0_zp"], a["weight_zp"], op.outputs[0].dtype)
+            else:
+                y = oc.matmul_i32(x, rhs, a["in0_zp"], a["weight_zp"])
         elif k == "maxpool":
             y = oc.maxpool(x, (a["kh"], a["kw"]), (a["stride_h"], a["stride_w"]),
                            (a["pad_t"], a["pad_b"], a["pad_l"], a["pad_r"]), a["pad_value"])

@@ -155,7 +155,10 @@ def test_act_bf16(device, fn):
     assert len(np.unique(got)) > 100
 
 
-@pytest.mark.parametrize("B,K,N,with_zp", [(1, 640, 256, True), (3, 1152, 200, True), (8, 2048, 96, False)])
+@pytest.mark.parametrize("B,K,N,with_zp", [(1, 640, 256, True), (3, 1152, 200, True), (8, 2048, 96, False),
+                                           # above 8 tokens: the tensor-core kernel (K in chunks of 1024, ragged N and B)
+                                           (9, 640, 256, True), (16, 1152, 200, True), (32, 2048, 1000, True),
+                                           (27, 6912, 136, False)])
 def test_gemv_block_quantised(device, B, K, N, with_zp):
     """The reference's Gemma weight form (tests/testdata/torch_ops/matmul_dql_q8_0.mlir: x 1x640 bf16, W 640x256
     si8, scales and zero points 20x256, block 32): dequantised weights are rounded to bf16, the product

@@ -197,3 +197,23 @@ def test_float_reductions(device, fn):
     t = torch.from_numpy(from_bf16(x))
     ref = {"mean": t.mean(-1, keepdim=True), "sum": t.sum(-1, keepdim=True), "max": t.max(-1, keepdim=True).values}[fn].numpy()
     assert np.all(np.abs(from_bf16(got) - ref) <= 2.0 ** -7 * np.maximum(np.abs(ref), 1e-2))
+
+
+@pytest.mark.parametrize("shape,oc,k,stride,dil,pad", [((1, 64, 64, 1), 1, 3, 2, 1, (0, 1, 0, 1)), ((2, 17, 13, 5), 7, 3, 1, 1, (1, 1, 1, 1)),
+                                                        ((1, 20, 20, 70), 4, 5, 2, 2, (3, 2, 2, 3)), ((3, 9, 9, 16), 33, 1, 1, 1, (0, 0, 0, 0))])
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_conv2d_int16_activations(device, shape, oc, k, stride, dil, pad, per_channel):
+    """Conv2D i16 x i8 with the 16-bit rescale (first case: the shape of the reference's gen_ops/conv2d_64x64_i16.mlir)."""
+    rng = np.random.default_rng(oc * 31 + k)
+    x = rng.integers(-32768, 32768, shape).astype(np.int16)
+    w = rng.integers(-128, 128, (oc, k, k, shape[3])).astype(np.int8)
+    bias = rng.integers(-2 ** 33, 2 ** 33, oc).astype(np.int64)   # beyond 32 bits: the accumulator is 64 bits wide
+    n = oc if per_channel else 1
+    mult = rng.integers(1 << 14, 1 << 15, n)
+    base = int(np.ceil(np.log2(2 ** 33 * 23000 / 12000)))          # results spread over the int16 range, some saturate
+    shift = rng.integers(base, base + 2, n)
+    g = Graph()
+    g.output(g.conv2d_i16(g.input(shape, "i16"), w, bias if per_channel else bias[:1], mult, shift, stride=(stride, stride),
+                          dilation=(dil, dil), pad=pad, input_zp=0, weight_zp=0, out_zp=-11))
+    got = _same(device, g, [x])
+    assert len(np.unique(got[0])) > 16

@@ -336,18 +336,92 @@ __global__ void __launch_bounds__(128) conv2d_c16_kernel(ConvArgs a) {
   }
 }
 
-// raw torq_hl.matmul, int32 result (tests/testdata/tosa_ops/matmul-in-int8-out-int32.mlir).
-__global__ void __launch_bounds__(256) matmul_i32_kernel(const int8_t* __restrict__ a,
-                                                         const int8_t* __restrict__ b,
-                                                         int32_t* __restrict__ out, int M, int K, int N,
-                                                         int a_zp, int b_zp) {
-  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (long long)M * N) return;
-  int n = (int)(idx % N);
-  int m = (int)(idx / N);
-  int acc = 0;
-  for (int k = 0; k < K; k++) acc += ((int)a[(size_t)m * K + k] - a_zp) * ((int)b[(size_t)k * N + n] - b_zp);
-  out[idx] = acc;
+// raw torq_hl.matmul (tests/testdata/tosa_ops/matmul-in-int8-out-int32.mlir, matmul-in-int16-out-int32.mlir,
+// matmul-in-int16-out-int16.mlir): int8 x int8 or int16 x int16, accumulated in int32 with wrap-around, stored as
+// int32 or truncated to int16. A block computes a 64 x 64 tile of the result from 64 x 16 / 16 x 64 tiles of the
+// operands in shared memory; a thread owns a 4 x 4 patch.
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256) matmul_int_kernel(const TIn* __restrict__ a, const TIn* __restrict__ b,
+                                                         TOut* __restrict__ out, int M, int K, int N, int a_zp, int b_zp) {
+  __shared__ int sa[16][64 + 1];  // [k][m]
+  __shared__ int sb[16][64];      // [k][n]
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  int acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int am = i >> 4, ak = i & 15;  // a: consecutive threads along k
+      sa[ak][am] = (m0 + am < M && k0 + ak < K) ? (int)a[(size_t)(m0 + am) * K + k0 + ak] - a_zp : 0;
+      const int bk = i >> 6, bn = i & 63;  // b: consecutive threads along n
+      sb[bk][bn] = (k0 + bk < K && n0 + bn < N) ? (int)b[(size_t)(k0 + bk) * N + n0 + bn] - b_zp : 0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; k++) {
+      int av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) av[i] = sa[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) bv[j] = sb[k][tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] += av[i] * bv[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int m = m0 + ty * 4 + i, n = n0 + tx + 16 * j;
+      if (m < M && n < N) out[(size_t)m * N + n] = (TOut)acc[i][j];
+    }
+}
+
+// Conv2D i16 x i8 (TB200_OP_CONV2D_I16): one thread per output; consecutive threads take consecutive output channels
+// of a pixel, so the pixel's input window is read by the whole group and the weights stream per thread. 64-bit
+// accumulation (TOSA's 48-bit accumulator never leaves it), then apply_scale_16:
+// (acc * multiplier + 2^(shift-1)) >> shift, + out_zp, clamp, int16.
+__global__ void __launch_bounds__(256) conv2d_i16_kernel(ConvI16Args a) {
+  const long long total = (long long)a.N * a.OH * a.OW * a.OC;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int oc = (int)(idx % a.OC);
+  long long p = idx / a.OC;
+  const int ow = (int)(p % a.OW);
+  p /= a.OW;
+  const int oh = (int)(p % a.OH);
+  const int n = (int)(p / a.OH);
+  long long acc = a.bias[oc];
+  const int8_t* wrow = a.w + (size_t)oc * a.KH * a.KW * a.IC;
+  for (int kh = 0; kh < a.KH; kh++) {
+    const int ih = oh * a.stride_h - a.pad_t + kh * a.dil_h;
+    if (ih < 0 || ih >= a.H) continue;
+    for (int kw = 0; kw < a.KW; kw++) {
+      const int iw = ow * a.stride_w - a.pad_l + kw * a.dil_w;
+      if (iw < 0 || iw >= a.W) continue;
+      const int16_t* px = a.x + (((size_t)n * a.H + ih) * a.W + iw) * a.IC;
+      const int8_t* wt = wrow + ((size_t)kh * a.KW + kw) * a.IC;
+      int part = 0;  // |(x - zp) * (w - wzp)| < 2^16 * 2^8: 64 terms fit in 31 bits
+      for (int c = 0; c < a.IC; c++) {
+        part += ((int)px[c] - a.input_zp) * ((int)wt[c] - a.weight_zp);
+        if ((c & 63) == 63) {
+          acc += part;
+          part = 0;
+        }
+      }
+      acc += part;
+    }
+  }
+  const int sh = a.shift[oc];
+  long long r = ((acc * (long long)a.mult[oc] + (1ll << (sh - 1))) >> sh) + a.out_zp;
+  r = r < a.clamp_min ? a.clamp_min : (r > a.clamp_max ? a.clamp_max : r);
+  a.out[idx] = (int16_t)r;
 }
 
 }  // namespace
@@ -400,10 +474,22 @@ void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
     conv2d_simt_kernel<false><<<grid, 256, 0, stream>>>(a);
 }
 
-void launch_matmul_i32(const int8_t* a, const int8_t* b, int32_t* out, int M, int K, int N, int a_zp,
+void launch_conv2d_i16(const ConvI16Args& a, cudaStream_t stream) {
+  const long long total = (long long)a.N * a.OH * a.OW * a.OC;
+  conv2d_i16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
+}
+
+void launch_matmul_int(const void* a, const void* b, void* out, bool in_i16, bool out_i16, int M, int K, int N, int a_zp,
                        int b_zp, cudaStream_t stream) {
-  long long total = (long long)M * N;
-  matmul_i32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a, b, out, M, K, N, a_zp, b_zp);
+  const dim3 grid((N + 63) / 64, (M + 63) / 64);
+  if (!in_i16 && !out_i16)
+    matmul_int_kernel<int8_t, int32_t><<<grid, 256, 0, stream>>>((const int8_t*)a, (const int8_t*)b, (int32_t*)out, M, K, N, a_zp, b_zp);
+  else if (!in_i16)
+    matmul_int_kernel<int8_t, int16_t><<<grid, 256, 0, stream>>>((const int8_t*)a, (const int8_t*)b, (int16_t*)out, M, K, N, a_zp, b_zp);
+  else if (!out_i16)
+    matmul_int_kernel<int16_t, int32_t><<<grid, 256, 0, stream>>>((const int16_t*)a, (const int16_t*)b, (int32_t*)out, M, K, N, a_zp, b_zp);
+  else
+    matmul_int_kernel<int16_t, int16_t><<<grid, 256, 0, stream>>>((const int16_t*)a, (const int16_t*)b, (int16_t*)out, M, K, N, a_zp, b_zp);
 }
 
 }  // namespace tb200

@@ -566,6 +566,85 @@ __global__ void __launch_bounds__(256) gemv_q8b_kernel(const uint16_t* __restric
       if (b < B) y[(size_t)b * N + n] = f2bf(acc[b]);
 }
 
+// four signed bytes -> (byte - zp) * scale, each rounded to bf16: two bf16x2 words (k, k+1) and (k+2, k+3)
+__device__ __forceinline__ void s8x4_dequant_bf16x4(uint32_t w, int z, float s, uint32_t& lo, uint32_t& hi) {
+  const float f0 = (float)((int)(int8_t)w - z) * s, f1 = (float)((int)(int8_t)(w >> 8) - z) * s;
+  const float f2 = (float)((int)(int8_t)(w >> 16) - z) * s, f3 = (float)(((int)w >> 24) - z) * s;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(f1), "f"(f0));
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(f3), "f"(f2));
+}
+
+// The same product for batches above 8 on the tensor cores: blocks of 128 output rows, the activations of all
+// tokens staged in shared memory one K chunk at a time, the weights dequantised to bf16 in registers exactly as
+// above ((W - zp) * scale, one rounding) and fed to mma.sync m16n8k16 with fp32 accumulation. K % 64 == 0 and a
+// block size that is a multiple of 16 (the 16 consecutive weights a lane holds share a block).
+template <int NT>  // groups of 8 tokens
+__global__ void __launch_bounds__(256) gemv_q8b_mma_kernel(const uint16_t* __restrict__ x, const int8_t* __restrict__ W,
+                                                           const uint16_t* __restrict__ scale,
+                                                           const int8_t* __restrict__ zp, uint16_t* __restrict__ y, int B,
+                                                           int N, int K, int bs, int k_chunk) {
+  extern __shared__ __align__(16) unsigned char xs_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  const int xstride = ((k_chunk * 2 + 127) / 128) * 128 + 16;  // bytes per token row in shared memory
+  const int row0 = blockIdx.x * 128 + warp * 16;
+  const bool active = row0 < N;
+  const int r_lo = min(row0 + g, N - 1), r_hi = min(row0 + g + 8, N - 1);
+  const int nblk = K / bs;
+  const int8_t* w_lo = W + (size_t)r_lo * K + tig * 16;
+  const int8_t* w_hi = W + (size_t)r_hi * K + tig * 16;
+  float c[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; t++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) c[t][j] = 0.f;
+  const unsigned char* xrow = xs_raw + (size_t)g * xstride + tig * 32;
+  for (int k0 = 0; k0 < K; k0 += k_chunk) {
+    const int k_len = min(k_chunk, K - k0);  // a multiple of 64
+    if (k0 > 0) __syncthreads();
+    for (int i = threadIdx.x; i < NT * 8 * (k_len / 8); i += blockDim.x) {
+      const int b = i / (k_len / 8), cc = i % (k_len / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (b < B) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + k0) + cc);
+      *reinterpret_cast<uint4*>(xs_raw + (size_t)b * xstride + 16 * cc) = v;
+    }
+    __syncthreads();
+    if (!active) continue;
+#pragma unroll 2
+    for (int kb = 0; kb < (k_len >> 6); kb++) {
+      const int k = k0 + kb * 64;
+      const uint4 wa = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
+      const uint4 wb = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
+      const int blk = (k + tig * 16) / bs;
+      const float s_lo = bf2f(__ldg(scale + (size_t)r_lo * nblk + blk)), s_hi = bf2f(__ldg(scale + (size_t)r_hi * nblk + blk));
+      const int z_lo = zp ? (int)__ldg(zp + (size_t)r_lo * nblk + blk) : 0, z_hi = zp ? (int)__ldg(zp + (size_t)r_hi * nblk + blk) : 0;
+      uint32_t a[4][4];
+      s8x4_dequant_bf16x4(wa.x, z_lo, s_lo, a[0][0], a[0][2]); s8x4_dequant_bf16x4(wb.x, z_hi, s_hi, a[0][1], a[0][3]);
+      s8x4_dequant_bf16x4(wa.y, z_lo, s_lo, a[1][0], a[1][2]); s8x4_dequant_bf16x4(wb.y, z_hi, s_hi, a[1][1], a[1][3]);
+      s8x4_dequant_bf16x4(wa.z, z_lo, s_lo, a[2][0], a[2][2]); s8x4_dequant_bf16x4(wb.z, z_hi, s_hi, a[2][1], a[2][3]);
+      s8x4_dequant_bf16x4(wa.w, z_lo, s_lo, a[3][0], a[3][2]); s8x4_dequant_bf16x4(wb.w, z_hi, s_hi, a[3][1], a[3][3]);
+#pragma unroll
+      for (int t = 0; t < NT; t++) {
+        const uint4 x0 = *reinterpret_cast<const uint4*>(xrow + (size_t)t * 8 * xstride + kb * 128);
+        const uint4 x1 = *reinterpret_cast<const uint4*>(xrow + (size_t)t * 8 * xstride + kb * 128 + 16);
+        mma_bf16(c[t], a[0][0], a[0][1], a[0][2], a[0][3], x0.x, x0.y);
+        mma_bf16(c[t], a[1][0], a[1][1], a[1][2], a[1][3], x0.z, x0.w);
+        mma_bf16(c[t], a[2][0], a[2][1], a[2][2], a[2][3], x1.x, x1.y);
+        mma_bf16(c[t], a[3][0], a[3][1], a[3][2], a[3][3], x1.z, x1.w);
+      }
+    }
+  }
+  if (!active) return;
+  // c[t][0], c[t][1]: row g, tokens 8t + 2tig, + 1; c[t][2], c[t][3]: row g + 8
+#pragma unroll
+  for (int t = 0; t < NT; t++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int b = 8 * t + 2 * tig + (j & 1), r = row0 + g + ((j & 2) ? 8 : 0);
+      if (b < B && r < N) y[(size_t)b * N + r] = f2bf(c[t][j]);
+    }
+}
+
 // y = bf16(f(x)), f evaluated in fp32: the host semantics of the reference's bf16 activation
 // patterns (python/torq/testing/numpy.py:13-27 is the fp32 form its tests compare with; the NPU's
 // piecewise-linear tables, scripts/bf16luts.py, approximate the same functions).
@@ -778,6 +857,24 @@ void launch_geglu(const uint16_t* gu, uint16_t* out, int B, int I, cudaStream_t 
 
 void launch_gemv_q8b(const uint16_t* x, const int8_t* W, const uint16_t* scale, const int8_t* zp, uint16_t* y, int B, int N,
                      int K, int bs, cudaStream_t stream) {
+  if (B > 8) {  // tensor cores; the planner has checked K % 64 == 0 and B <= 32
+    const int nt = (B + 7) / 8;
+    const int k_chunk = K < 1024 ? K : 1024;
+    const int xstride = ((k_chunk * 2 + 127) / 128) * 128 + 16;
+    const size_t smem = (size_t)nt * 8 * xstride;
+    auto run = [&](auto kernel) {
+      static std::atomic<unsigned long long> attr_done[5];  // per instantiation (index nt) and device
+      if (first_use_on_device(attr_done[nt])) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        mark_used_on_device(attr_done[nt]);
+      }
+      launch_k(kernel, dim3((N + 127) / 128), dim3(256), smem, stream, x, W, scale, zp, y, B, N, K, bs, k_chunk);
+    };
+    if (nt == 2) run(gemv_q8b_mma_kernel<2>);
+    else if (nt == 3) run(gemv_q8b_mma_kernel<3>);
+    else run(gemv_q8b_mma_kernel<4>);
+    return;
+  }
   const dim3 grid((N + 7) / 8);
   if (B <= 1) launch_k(gemv_q8b_kernel<1>, dim3(grid), dim3(256), 0, stream, x, W, scale, zp, y, B, N, K, bs);
   else if (B <= 4) launch_k(gemv_q8b_kernel<4>, dim3(grid), dim3(256), 0, stream, x, W, scale, zp, y, B, N, K, bs);

@@ -34,6 +34,20 @@ struct ConvArgs {
   const int8_t* lut;      // 256-entry table applied to the int8 result (out = lut[q + 128]), or null
 };
 void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream);
+
+// Conv2D on int16 activations with int8 weights and the 16-bit rescale that follows it (TB200_OP_CONV2D_I16).
+struct ConvI16Args {
+  const int16_t* x;         // NHWC
+  const int8_t* w;          // OHWI
+  const long long* bias;    // [OC] (already broadcast)
+  const int32_t* mult;      // [OC] 16-bit multipliers
+  const int32_t* shift;     // [OC]
+  int16_t* out;             // NHWC
+  int N, H, W, IC, OC, KH, KW, OH, OW;
+  int stride_h, stride_w, dil_h, dil_w, pad_t, pad_l;
+  int input_zp, weight_zp, out_zp, clamp_min, clamp_max;
+};
+void launch_conv2d_i16(const ConvI16Args& a, cudaStream_t stream);
 const char* conv2d_simt_kernel_name(const ConvArgs& a);  // which CUDA-core kernel the launcher picks
 
 struct DwArgs {
@@ -58,7 +72,7 @@ bool depthwise3x3_supported(const DwArgs& a);
 size_t depthwise3x3_pack(const int8_t* w, int C, int stride, uint32_t* out);
 
 // raw int8 x int8 -> int32 matmul, b is [K][N]
-void launch_matmul_i32(const int8_t* a, const int8_t* b, int32_t* out, int M, int K, int N, int a_zp,
+void launch_matmul_int(const void* a, const void* b, void* out, bool in_i16, bool out_i16, int M, int K, int N, int a_zp,
                        int b_zp, cudaStream_t stream);
 
 struct PoolArgs {

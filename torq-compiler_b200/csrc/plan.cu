@@ -648,6 +648,62 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
       continue;
     }
     switch (op.kind) {
+      case TB200_OP_CONV2D_I16: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || !b.valid_id(op.weights) || tensors[op.in0].dtype != TB200_I16 ||
+            tensors[op.out0].dtype != TB200_I16 || tensors[op.in0].rank != 4 || tensors[op.out0].rank != 4 ||
+            tensors[op.weights].rank != 4)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: conv2d_i16 wants int16 NHWC input/output and OHWI int8 weights", i);
+        const auto& x = tensors[op.in0]; const auto& w = tensors[op.weights]; const auto& o = tensors[op.out0];
+        ConvI16Args a{};
+        a.N = x.shape[0]; a.H = x.shape[1]; a.W = x.shape[2]; a.IC = x.shape[3];
+        a.OC = w.shape[0]; a.KH = w.shape[1]; a.KW = w.shape[2];
+        if (w.shape[3] != a.IC) return b.fail(TB200_INVALID_ARGUMENT, "op %d: weight IC %d != input IC %d", i, w.shape[3], a.IC);
+        if (op.stride_h < 1 || op.stride_w < 1 || op.dil_h < 1 || op.dil_w < 1 || op.pad_t < 0 || op.pad_b < 0 || op.pad_l < 0 ||
+            op.pad_r < 0)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad stride/dilation/pad", i);
+        a.OH = conv_out_dim(a.H, a.KH, op.stride_h, op.dil_h, op.pad_t, op.pad_b);
+        a.OW = conv_out_dim(a.W, a.KW, op.stride_w, op.dil_w, op.pad_l, op.pad_r);
+        if (o.shape[0] != a.N || o.shape[1] != a.OH || o.shape[2] != a.OW || o.shape[3] != a.OC)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: conv2d_i16 output shape is not %dx%dx%dx%d", i, a.N, a.OH, a.OW, a.OC);
+        const size_t wn = (size_t)a.OC * a.KH * a.KW * a.IC;
+        const int8_t* wd = b.const_data<int8_t>(op.weights, wn, "weights", i);
+        if (!wd) return b.status;
+        const int n_bias = b.valid_id(op.bias) ? (int)b.numel(op.bias) : 0, n_q = op.per_channel ? a.OC : 1;
+        if (n_bias != 1 && n_bias != a.OC) return b.fail(TB200_INVALID_ARGUMENT, "op %d: bias wants 1 or OC int64 entries", i);
+        const long long* bias = b.const_data<long long>(op.bias, (size_t)n_bias, "bias", i);
+        const int32_t* mult = b.const_data<int32_t>(op.multiplier, (size_t)n_q, "multiplier", i);
+        const int8_t* shift = b.const_data<int8_t>(op.shift, (size_t)n_q, "shift", i);
+        if (!bias || !mult || !shift) return b.status;
+        std::vector<long long> bias_v(a.OC);
+        std::vector<int32_t> mult_v(a.OC), shift_v(a.OC);
+        for (int oc = 0; oc < a.OC; oc++) {
+          bias_v[oc] = bias[n_bias == 1 ? 0 : oc];
+          mult_v[oc] = mult[op.per_channel ? oc : 0];
+          shift_v[oc] = shift[op.per_channel ? oc : 0];
+          if (mult_v[oc] < 0 || mult_v[oc] > 32767 || shift_v[oc] < 2 || shift_v[oc] > 62)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: 16-bit rescale wants 0 <= multiplier < 2^15 and 2 <= shift <= 62", i);
+        }
+        const size_t w_off = b.add_const(wd, wn), b_off = b.add_const(bias_v.data(), bias_v.size() * 8),
+                     m_off = b.add_const(mult_v.data(), mult_v.size() * 4), s_off = b.add_const(shift_v.data(), shift_v.size() * 4);
+        a.stride_h = op.stride_h; a.stride_w = op.stride_w; a.dil_h = op.dil_h; a.dil_w = op.dil_w;
+        a.pad_t = op.pad_t; a.pad_l = op.pad_l;
+        a.input_zp = op.in0_zp; a.weight_zp = op.weight_zp; a.out_zp = op.out_zp;
+        a.clamp_min = op.clamp_min < -32768 ? -32768 : op.clamp_min;
+        a.clamp_max = op.clamp_max > 32767 ? 32767 : op.clamp_max;
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "conv2d_i16";
+        step.launch = [=](const ExecContext& c) {
+          ConvI16Args k = a;
+          k.x = (const int16_t*)lx.resolve(c);
+          k.out = (int16_t*)lo.resolve(c);
+          k.w = (const int8_t*)(c.consts + w_off);
+          k.bias = (const long long*)(c.consts + b_off);
+          k.mult = (const int32_t*)(c.consts + m_off);
+          k.shift = (const int32_t*)(c.consts + s_off);
+          launch_conv2d_i16(k, c.stream);
+        };
+        break;
+      }
       case TB200_OP_CONV2D:
       case TB200_OP_FC: {
         const bool fc = op.kind == TB200_OP_FC;
@@ -983,19 +1039,23 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
       }
       case TB200_OP_MATMUL_I32: {
         if (op.weights < 0 && op.in1 >= 0) {
-          // both operands are runtime tensors (the form of the reference's tosa.matmul fixtures)
-          if (!b.act_i8(op.in0, 2) || !b.act_i8(op.in1, 2) || !b.valid_id(op.out0) || tensors[op.out0].dtype != TB200_I32 ||
-              tensors[op.out0].rank != 2)
-            return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul wants int8 [M,K] x int8 [K,N] -> int32 [M,N]", i);
-          const int M = tensors[op.in0].shape[0], K = tensors[op.in0].shape[1], N = tensors[op.in1].shape[1];
-          if (tensors[op.in1].shape[0] != K || tensors[op.out0].shape[0] != M || tensors[op.out0].shape[1] != N)
+          // both operands are runtime tensors (the form of the reference's tosa.matmul fixtures): int8 x int8 or
+          // int16 x int16, int32 or int16 result
+          if (!b.valid_id(op.in0) || !b.valid_id(op.in1) || !b.valid_id(op.out0))
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad tensor id", i);
+          const auto& ta = tensors[op.in0]; const auto& tb = tensors[op.in1]; const auto& to = tensors[op.out0];
+          const bool in16 = ta.dtype == TB200_I16, out16 = to.dtype == TB200_I16;
+          if ((ta.dtype != TB200_I8 && !in16) || tb.dtype != ta.dtype || (to.dtype != TB200_I32 && !out16) || ta.rank != 2 ||
+              tb.rank != 2 || to.rank != 2)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul wants [M,K] x [K,N] of int8 or int16 -> int32 or int16 [M,N]", i);
+          const int M = ta.shape[0], K = ta.shape[1], N = tb.shape[1];
+          if (tb.shape[0] != K || to.shape[0] != M || to.shape[1] != N)
             return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul shape mismatch", i);
           Loc lx = loc(op.in0), lw = loc(op.in1), lo = loc(op.out0);
           const int azp = op.in0_zp, bzp = op.weight_zp;
-          step.kernel_name = "matmul_i32";
+          step.kernel_name = "matmul_int";
           step.launch = [=](const ExecContext& c) {
-            launch_matmul_i32((const int8_t*)lx.resolve(c), (const int8_t*)lw.resolve(c), (int32_t*)lo.resolve(c), M, K, N,
-                              azp, bzp, c.stream);
+            launch_matmul_int(lx.resolve(c), lw.resolve(c), lo.resolve(c), in16, out16, M, K, N, azp, bzp, c.stream);
           };
           break;
         }
@@ -1010,10 +1070,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         size_t w_off = b.add_const(wd, (size_t)K * N);
         Loc lx = loc(op.in0), lo = loc(op.out0);
         int azp = op.in0_zp, bzp = op.weight_zp;
-        step.kernel_name = "matmul_i32";
+        step.kernel_name = "matmul_int";
         step.launch = [=](const ExecContext& c) {
-          launch_matmul_i32((const int8_t*)lx.resolve(c), (const int8_t*)(c.consts + w_off), (int32_t*)lo.resolve(c),
-                            M, K, N, azp, bzp, c.stream);
+          launch_matmul_int(lx.resolve(c), c.consts + w_off, lo.resolve(c), false, false, M, K, N, azp, bzp, c.stream);
         };
         break;
       }
@@ -1400,8 +1459,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         const int B = tensors[op.in0].shape[0], K = tensors[op.in0].shape[1], N = tensors[op.weights].shape[1], bs = op.i0;
         if (tensors[op.weights].shape[0] != K || tensors[op.out0].shape[0] != B || tensors[op.out0].shape[1] != N)
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: gemv_q8b shape mismatch", i);
-        if (bs < 16 || bs % 16 != 0 || K % bs != 0 || K % 16 != 0 || B > 8)
-          return b.fail(TB200_UNIMPLEMENTED, "op %d: gemv_q8b needs a block size that is a multiple of 16 and divides K, batch <= 8", i);
+        if (bs < 16 || bs % 16 != 0 || K % bs != 0 || K % 16 != 0 || B > 32 || (B > 8 && K % 64 != 0))
+          return b.fail(TB200_UNIMPLEMENTED,
+                        "op %d: gemv_q8b needs a block size that is a multiple of 16 and divides K, batch <= 8 (<= 32 when K is a multiple of 64)", i);
         const int nblk = K / bs;
         const int8_t* w = b.const_data<int8_t>(op.weights, (size_t)K * N, "weights", i);
         const uint16_t* sc = b.const_data<uint16_t>(op.bias, (size_t)nblk * N, "block scales", i);

@@ -29,7 +29,7 @@ OP_KINDS = {
     "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
     "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
     "add_bf16": 38, "argmax": 39, "allreduce": 40, "act_bf16": 41, "gemv_q8b": 42,
-    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55,
+    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55, "conv2d_i16": 56,
 }
 
 EW_FN = {"cast": 0, "abs": 1, "negate": 2, "bitwise_not": 3, "logical_not": 4, "clz": 5, "clamp": 6, "ceil": 7, "floor": 8,
@@ -168,6 +168,25 @@ class Graph:
                           clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc, double_round=int(double_round),
                           requant_mode=requant_mode)
 
+    def conv2d_i16(self, x, weights, bias, multiplier, shift, *, stride=(1, 1), dilation=(1, 1), pad=(0, 0, 0, 0),
+                   input_zp=0, weight_zp=0, out_zp=0, clamp=(-32768, 32767)):
+        """Conv2D on int16 activations (NHWC) with int8 weights (OHWI) and the 16-bit rescale that follows it:
+        64-bit accumulation, (acc * multiplier + 2^(shift-1)) >> shift, + out_zp, clamp, int16."""
+        w = np.asarray(weights, np.int8)
+        N, H, W, IC = x.shape
+        OC, KH, KW, IC2 = w.shape
+        if IC != IC2 or x.dtype != "i16":
+            raise ValueError("conv2d_i16 wants an int16 NHWC tensor and OHWI weights of the same channel count")
+        OH = _out_dim(H, KH, stride[0], dilation[0], pad[0], pad[1])
+        OW = _out_dim(W, KW, stride[1], dilation[1], pad[2], pad[3])
+        mt, st, pc = self._requant_consts(multiplier, shift, OC)
+        consts = {"weights": self.const(w), "bias": self.const(np.atleast_1d(bias).astype(np.int64)),
+                  "multiplier": mt, "shift": st}
+        return self._emit("conv2d_i16", [x], (N, OH, OW, OC), "i16", consts=consts, kh=KH, kw=KW, stride_h=stride[0],
+                          stride_w=stride[1], dil_h=dilation[0], dil_w=dilation[1], pad_t=pad[0], pad_b=pad[1],
+                          pad_l=pad[2], pad_r=pad[3], in0_zp=input_zp, weight_zp=weight_zp, out_zp=out_zp,
+                          clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc, double_round=0)
+
     def depthwise_conv2d(self, x, weights, bias, multiplier, shift, *, stride=(1, 1), dilation=(1, 1),
                          pad=(0, 0, 0, 0), input_zp=0, weight_zp=0, out_zp=0, clamp=(-128, 127),
                          double_round=True, requant_mode=0):
@@ -203,13 +222,16 @@ class Graph:
                           clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc, double_round=int(double_round),
                           requant_mode=requant_mode)
 
-    def matmul_i32(self, a, b, *, a_zp=0, b_zp=0):
-        """raw torq_hl.matmul: a [M, K] int8 x b [K, N] int8 -> int32; b a constant array or, as in the
-        reference's tosa.matmul fixtures, a second runtime tensor."""
+    def matmul_i32(self, a, b, *, a_zp=0, b_zp=0, out_dtype="i32"):
+        """raw torq_hl.matmul: a [M, K] x b [K, N], int32 accumulation with wrap-around. b is a constant int8 array
+        or, as in the reference's tosa.matmul fixtures, a second runtime tensor; two runtime tensors may both be
+        int16, and the result may be stored truncated to int16."""
         if isinstance(b, TensorRef):
             if len(a.shape) != 2 or len(b.shape) != 2 or a.shape[1] != b.shape[0]:
                 raise ValueError("matmul wants [M, K] x [K, N]")
-            return self._emit("matmul_i32", [a, b], (a.shape[0], b.shape[1]), "i32", in0_zp=a_zp, weight_zp=b_zp)
+            if a.dtype not in ("i8", "i16") or b.dtype != a.dtype or out_dtype not in ("i32", "i16"):
+                raise ValueError("matmul wants int8 x int8 or int16 x int16 -> int32 or int16")
+            return self._emit("matmul_i32", [a, b], (a.shape[0], b.shape[1]), out_dtype, in0_zp=a_zp, weight_zp=b_zp)
         bw = np.asarray(b, np.int8)
         return self._emit("matmul_i32", [a], (a.shape[0], bw.shape[1]), "i32", consts={"weights": self.const(bw)},
                           in0_zp=a_zp, weight_zp=b_zp)

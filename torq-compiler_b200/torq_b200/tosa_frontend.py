@@ -324,6 +324,19 @@ def build_graph(text: str) -> Graph:
             rs = only_user(op, "rescale")
             if rs is None or w.const is None:
                 raise NotImplementedError(f"{n} without a constant weight and a following rescale")
+            if n == "conv2d" and x.dtype == "i16" and w.dtype == "i8" and rs.result.dtype == "i16" and \
+                    not rs.attrs.get("scale32", True) and "DOUBLE" not in str(rs.attrs.get("rounding_mode", "")):
+                done.add(id(rs))
+                p = rescale_params(rs)
+                last, lo, hi = fold_clamp(rs, -32768, 32767)
+                if p["izp"] != 0:
+                    raise NotImplementedError("16-bit rescale of a convolution with an input zero point")
+                mult, shift = (p["mult"], p["shift"]) if p["per_channel"] else (p["mult"][:1], p["shift"][:1])
+                env[last.result.name] = g.conv2d_i16(get(x), w.const, bias.const.reshape(-1), mult, shift,
+                                                     stride=tuple(op.attrs["stride"]), dilation=tuple(op.attrs["dilation"]),
+                                                     pad=tuple(op.attrs["pad"]), input_zp=_scalar(izp), weight_zp=_scalar(wzp),
+                                                     out_zp=p["ozp"], clamp=(lo, hi))
+                return
             if x.dtype != "i8" or w.dtype != "i8" or rs.result.dtype != "i8":
                 raise NotImplementedError(f"{n} on {x.dtype} activations")
             done.add(id(rs))
@@ -437,10 +450,11 @@ def build_graph(text: str) -> Graph:
             env[op.result.name] = g.concat(get(a), get(b), a_zp=0, a_ms=one, b_zp=0, b_ms=one, out_zp=0)
         elif n == "matmul":
             a, b, azp, bzp = op.operands
-            if a.dtype != "i8" or b.dtype != "i8" or op.result.dtype != "i32" or len(a.shape) != 3 or a.shape[0] != 1:
-                raise NotImplementedError("tosa.matmul other than one batch of i8 x i8 -> i32")
+            if a.dtype not in ("i8", "i16") or b.dtype != a.dtype or op.result.dtype not in ("i32", "i16") or \
+                    len(a.shape) != 3 or a.shape[0] != 1:
+                raise NotImplementedError("tosa.matmul other than one batch of i8 x i8 or i16 x i16 -> i32 or i16")
             y = g.matmul_i32(g.reshape(get(a), a.shape[1:]), g.reshape(get(b), b.shape[1:]), a_zp=_scalar(azp),
-                             b_zp=_scalar(bzp))
+                             b_zp=_scalar(bzp), out_dtype=op.result.dtype)
             env[op.result.name] = g.reshape(y, op.result.shape)
         elif n == "clamp":
             x = op.operands[0]
