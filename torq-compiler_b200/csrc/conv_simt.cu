@@ -383,6 +383,112 @@ __global__ void __launch_bounds__(256) matmul_int_kernel(const TIn* __restrict__
     }
 }
 
+// The 3x3 window over 3 channels (the stem of an image network) with the compact 32-bit epilogue records. A thread
+// owns kStemPix output pixels (adjacent threads adjacent pixels). A kernel row of a pixel is 9 consecutive bytes of
+// the input: three aligned words and two funnel shifts bring them in (pixels whose window leaves the image, or whose
+// words would reach past the tensor, gather byte by byte with the input zero point outside). The 27 bytes are packed
+// into 7 dp4a operands once and run against every output channel's 7 weight words (two 16-byte shared-memory loads
+// per channel, shared by the thread's pixels): 7 dp4a + about 7 instructions of rescale per output.
+constexpr int kStemPix = 4;
+template <int EPI>
+__global__ void __launch_bounds__(128) conv2d_stem333_kernel(ConvArgs a) {
+  extern __shared__ __align__(16) uint32_t stem_s[];  // [OC][8] weight words (word 7 zero), then [OC] Q4 records
+  uint4* w_s = reinterpret_cast<uint4*>(stem_s);
+  int4* q_s = reinterpret_cast<int4*>(stem_s + (size_t)a.OC * 8);
+  for (int i = threadIdx.x; i < a.OC * 8; i += blockDim.x) {
+    const int oc = i >> 3, kw = i & 7;
+    stem_s[i] = kw < 7 ? *reinterpret_cast<const uint32_t*>(a.w + (size_t)oc * a.Kpad + kw * 4) : 0u;
+  }
+  for (int i = threadIdx.x; i < a.OC; i += blockDim.x) q_s[i] = a.q4[i];
+  __syncthreads();
+  const long long P = (long long)a.N * a.OH * a.OW;
+  const long long p_base = (long long)blockIdx.x * (128 * kStemPix) + threadIdx.x;
+  const uint32_t zp_byte = (uint32_t)(a.input_zp & 0xff);
+  uint32_t patch[kStemPix][7];
+#pragma unroll
+  for (int px = 0; px < kStemPix; px++) {
+    const long long p = p_base + px * 128;
+    const long long pp = p < P ? p : 0;
+    const int ow = (int)(pp % a.OW);
+    const long long t = pp / a.OW;
+    const int oh = (int)(t % a.OH);
+    const int n = (int)(t / a.OH);
+    const int ih0 = oh * a.stride_h - a.pad_t, iw0 = ow * a.stride_w - a.pad_l;
+    uint32_t row[3][3];  // per kernel row: bytes 0-3, 4-7, 8 (upper bytes of the third word are not used)
+    const long long off0 = (((long long)n * a.H + ih0) * a.W + iw0) * 3;
+    const bool inside = ih0 >= 0 && ih0 + 2 < a.H && iw0 >= 0 && iw0 + 2 < a.W &&
+                        ((off0 + 2ll * a.W * 3) & ~3ll) + 12 <= a.x_bytes;
+    if (inside) {
+#pragma unroll
+      for (int kh = 0; kh < 3; kh++) {
+        const long long off = off0 + (long long)kh * a.W * 3;
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(a.x + (off & ~3ll));
+        const uint32_t w0 = __ldg(wp), w1 = __ldg(wp + 1), w2 = __ldg(wp + 2);
+        const uint32_t sh = (uint32_t)(off & 3) * 8;
+        row[kh][0] = __funnelshift_r(w0, w1, sh);
+        row[kh][1] = __funnelshift_r(w1, w2, sh);
+        row[kh][2] = w2 >> sh;
+      }
+    } else {
+      const int8_t* xin = a.x + (size_t)n * a.H * a.W * 3;
+#pragma unroll
+      for (int kh = 0; kh < 3; kh++) {
+        const int ih = ih0 + kh;
+        uint32_t b[12];
+#pragma unroll
+        for (int j = 0; j < 9; j++) {
+          const int iw = iw0 + j / 3;
+          b[j] = (ih >= 0 && ih < a.H && iw >= 0 && iw < a.W) ? (uint32_t)(uint8_t)xin[((size_t)ih * a.W + iw) * 3 + j % 3] : zp_byte;
+        }
+        row[kh][0] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+        row[kh][1] = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+        row[kh][2] = b[8];
+      }
+    }
+    // K order (kh, kw, ic): bytes 0-8 row 0, 9-17 row 1, 18-26 row 2, byte 27 meets a zero weight
+    patch[px][0] = row[0][0];
+    patch[px][1] = row[0][1];
+    patch[px][2] = (row[0][2] & 0xffu) | (row[1][0] << 8);
+    patch[px][3] = __funnelshift_r(row[1][0], row[1][1], 24);
+    patch[px][4] = (row[1][1] >> 24) | ((row[1][2] & 0xffu) << 8) | (row[2][0] << 16);
+    patch[px][5] = __funnelshift_r(row[2][0], row[2][1], 16);
+    patch[px][6] = (row[2][1] >> 16) | ((row[2][2] & 0xffu) << 16);
+  }
+  for (int oc0 = 0; oc0 < a.OC; oc0 += 16) {
+    uint32_t packed[kStemPix][4];
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+      int q[kStemPix][4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int oc = min(oc0 + 4 * g + j, a.OC - 1);
+        const uint4 wa = w_s[oc * 2], wb = w_s[oc * 2 + 1];
+        const int4 c = q_s[oc];
+#pragma unroll
+        for (int px = 0; px < kStemPix; px++) {
+          int acc = __dp4a((int)patch[px][0], (int)wa.x, 0);
+          acc = __dp4a((int)patch[px][1], (int)wa.y, acc);
+          acc = __dp4a((int)patch[px][2], (int)wa.z, acc);
+          acc = __dp4a((int)patch[px][3], (int)wa.w, acc);
+          acc = __dp4a((int)patch[px][4], (int)wb.x, acc);
+          acc = __dp4a((int)patch[px][5], (int)wb.y, acc);
+          acc = __dp4a((int)patch[px][6], (int)wb.z, acc);
+          const int r = EPI == 1 ? scale_q4_sign(acc, c) : scale_q4(acc, c);
+          q[px][j] = max(a.clamp_min, min(a.clamp_max, r));
+        }
+      }
+#pragma unroll
+      for (int px = 0; px < kStemPix; px++) packed[px][g] = pack4(q[px][0], q[px][1], q[px][2], q[px][3]);
+    }
+#pragma unroll
+    for (int px = 0; px < kStemPix; px++) {
+      const long long p = p_base + px * 128;
+      if (p >= P) continue;
+      *reinterpret_cast<uint4*>(a.out + (size_t)p * a.OC + oc0) = make_uint4(packed[px][0], packed[px][1], packed[px][2], packed[px][3]);
+    }
+  }
+}
+
 // Conv2D i16 x i8 (TB200_OP_CONV2D_I16): one thread per output; consecutive threads take consecutive output channels
 // of a pixel, so the pixel's input window is read by the whole group and the weights stream per thread. 64-bit
 // accumulation (TOSA's 48-bit accumulator never leaves it), then apply_scale_16:
@@ -431,8 +537,19 @@ static bool conv_c16_applies(const ConvArgs& a) {
   return a.IC == 16 && a.weight_zp == 0 && a.OC <= 256 && (taps == 9 || taps == 1 || taps == 25);
 }
 
+// the 3x3x3 stem with 32-bit epilogue records (the planner leaves epi at 0 when a table is fused), output channels in
+// whole 16-byte groups
+static bool conv_stem333_shape(const ConvArgs& a) {
+  return a.IC == 3 && a.KH == 3 && a.KW == 3 && a.dil_h == 1 && a.dil_w == 1 && a.weight_zp == 0 && a.epi != 0 &&
+         (a.OC & 15) == 0 && a.OC <= 256;
+}
+static bool conv_stem333_applies(const ConvArgs& a) {
+  return conv_stem333_shape(a) && a.q4 && !a.lut && ((uintptr_t)a.x & 3) == 0 && ((uintptr_t)a.out & 15) == 0;
+}
+
 const char* conv2d_simt_kernel_name(const ConvArgs& a) {
   if (conv_c16_applies(a)) return "conv2d_c16_dp4a";
+  if (conv_stem333_shape(a)) return "conv2d_stem333_dp4a";
   return (a.IC <= 4 && a.K <= 64 && a.OC <= 256 && a.weight_zp == 0) ? "conv2d_smallic_dp4a" : "conv2d_simt";
 }
 
@@ -454,6 +571,13 @@ void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
       }
       conv2d_c16_kernel<25><<<blocks, 128, smem, stream>>>(a);
     }
+    return;
+  }
+  if (conv_stem333_applies(a)) {
+    const unsigned blocks = (unsigned)((P + 128 * kStemPix - 1) / (128 * kStemPix));
+    const size_t smem = (size_t)a.OC * (32 + 16);
+    if (a.epi == 1) conv2d_stem333_kernel<1><<<blocks, 128, smem, stream>>>(a);
+    else conv2d_stem333_kernel<2><<<blocks, 128, smem, stream>>>(a);
     return;
   }
   if (a.IC <= 4 && a.K <= 64 && a.OC <= 256 && a.weight_zp == 0) {

@@ -20,9 +20,10 @@
 //   * stages hand their results over in one of two ways. A projection's output (a few KB) travels
 //     as 32-bit words {epoch tag, bf16 value}: the reader spins on the words it needs until they
 //     carry the stage's tag, so the data IS the signal: one L2 round trip, no fence, no counter.
-//     Where a stage's result is large or crosses GPUs (attention partial sums, the K-split
-//     projections of tensor parallelism, the arg max) a grid-wide barrier is used (one counter in
-//     global memory, cooperative launch). Every wait is bounded. Each CTA keeps the residual
+//     The K-split projections of tensor parallelism travel the same way through peer memory, as 64-bit words
+//     {tag, fp32 partial result}, one per GPU and element. Where a stage's result is large (attention partial
+//     sums, the GeGLU vector) or needs every GPU's candidates (the arg max) a grid-wide barrier is used (one
+//     counter in global memory, cooperative launch). Every wait is bounded. Each CTA keeps the residual
 //     stream in shared memory and recomputes the small norms itself, so only the projections'
 //     outputs cross between CTAs.
 // The tensor work is HBM-bound (1.25 instructions per weight byte to build the fragments is
@@ -164,6 +165,30 @@ __device__ __forceinline__ float wait_tagged(const uint32_t* p, uint32_t tag, in
     }
   }
 }
+// Across GPUs the hand-over word is 64 bits {tag, fp32 partial result}: one store through peer memory carries the
+// value and its signal (no fence, no barrier; one NVLink crossing), and the reader polls its own GPU's memory.
+__device__ __forceinline__ void st_tagged_sys(float* inbox_word, float value, uint32_t tag) {
+  const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(value);
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(inbox_word), "l"(w) : "memory");
+}
+__device__ __forceinline__ float wait_tagged_sys(const float* inbox_word, uint32_t tag, int* status, bool& ok) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(inbox_word) : "memory");
+  if ((uint32_t)(w >> 32) == tag || !ok) return __uint_as_float((uint32_t)w);
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; i++) {
+      asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(inbox_word) : "memory");
+      if ((uint32_t)(w >> 32) == tag) return __uint_as_float((uint32_t)w);
+    }
+    if (*(volatile int*)status != 0 || globaltimer_ns() - t0 > s_wait_limit_ns) {
+      report_expired_wait(status, (int)kErrGrid);
+      ok = false;
+      return 0.f;
+    }
+  }
+}
 // The same for four consecutive words (16-byte aligned).
 __device__ __forceinline__ uint4 wait_tagged4(const uint32_t* p, uint32_t tag, int* status, bool& ok) {
   uint4 w = ld_relaxed_v4(p);
@@ -192,7 +217,7 @@ __device__ __forceinline__ uint4 wait_tagged4(const uint32_t* p, uint32_t tag, i
 // G * (tp - 1)); the waiters' target therefore grows by tp per barrier. Two (gathering, barrier)
 // counter pairs alternate, so that a GPU that is one barrier ahead never adds to the counter its peers
 // are still waiting on; which pair comes next is carried from launch to launch with the bases (a launch
-// has an odd number of cross-GPU barriers).
+// has one cross-GPU barrier, the arg max's).
 // Counter block (byte offsets): local 0, barrier 8 and 16, their bases 24, 32, 40, exit count 48, epoch of
 // the tagged hand-overs 56, next pair 60, gathering 64 and 72.
 struct BarrierState {
@@ -442,14 +467,17 @@ __device__ __forceinline__ void prefetch_layer_constants(const DecodeStepArgs& a
 //   xin    <- fp16(bf16(xs * rsqrt(mean(xs^2) + eps) * (1 + w_pre)))   (exact: |value| <= sqrt(H) * |1 + w|)
 // src is a [B, H] bf16 tensor in global memory written by other CTAs before the last barrier.
 // With tensor parallelism the projection's output arrives as one fp32 partial result per GPU
-// (inbox [tp][B][H] at byte offset `inbox` of the scratch area); they are added in rank order
-// and rounded to bf16, the same on every GPU.
+// (inbox [tp][B][H] of tagged 64-bit words at byte offset `inbox` of the scratch area, written by the
+// peers' reducer warps); each is awaited by its tag, they are added in rank order and rounded to bf16,
+// the same on every GPU. An inbox word is rewritten only after every CTA of this GPU has read it: a peer's
+// next partial result for it depends, through the projection in between, on rows that every CTA here
+// produces after this read.
 __device__ __forceinline__ float load_projection(const DecodeStepArgs& a, const uint32_t* src, uint32_t tag,
                                                  unsigned long long inbox, int b, int i, int* status, bool& ok) {
   if (a.tp <= 1) return wait_tagged(src + (size_t)b * a.H + i, tag, status, ok);
-  const float* in = (const float*)(a.scratch + inbox);
+  const float* in = (const float*)(a.scratch + inbox);  // 64-bit words {tag, value}: two floats per element
   float s = 0.f;
-  for (int r = 0; r < a.tp; r++) s += __ldcg(in + ((size_t)r * a.B + b) * a.H + i);
+  for (int r = 0; r < a.tp; r++) s += wait_tagged_sys(in + 2 * (((size_t)r * a.B + b) * a.H + i), tag, status, ok);
   return rbf(s);
 }
 template <int BT>
@@ -1034,16 +1062,16 @@ __device__ __forceinline__ void reduce_phase(const DecodeStepArgs& a, const Phas
     c[0] *= xs0; c[1] *= xs1; c[2] *= xs0; c[3] *= xs1;  // exact: powers of two
     const float s_lo = cur.lo, s_hi = cur.hi;
     if (p.kind == kRows && inbox) {
-      // tensor parallel, K split over the GPUs: fp32 partial result to every GPU's inbox [rank][B][N]
+      // tensor parallel, K split over the GPUs: fp32 partial result, tagged, to every GPU's inbox [rank][B][N]
       for (int r = 0; r < a.tp; r++) {
-        float* y = (float*)(a.peer_scratch[r] + inbox) + (size_t)a.rank * a.B * p.N;
+        float* y = (float*)(a.peer_scratch[r] + inbox) + 2 * (size_t)a.rank * a.B * p.N;
         if (r_lo >= 0) {
-          if (b0 < a.B) y[(size_t)b0 * p.N + r_lo] = c[0] * s_lo;
-          if (b1 < a.B) y[(size_t)b1 * p.N + r_lo] = c[1] * s_lo;
+          if (b0 < a.B) st_tagged_sys(y + 2 * ((size_t)b0 * p.N + r_lo), c[0] * s_lo, tag);
+          if (b1 < a.B) st_tagged_sys(y + 2 * ((size_t)b1 * p.N + r_lo), c[1] * s_lo, tag);
         }
         if (r_hi >= 0) {
-          if (b0 < a.B) y[(size_t)b0 * p.N + r_hi] = c[2] * s_hi;
-          if (b1 < a.B) y[(size_t)b1 * p.N + r_hi] = c[3] * s_hi;
+          if (b0 < a.B) st_tagged_sys(y + 2 * ((size_t)b0 * p.N + r_hi), c[2] * s_hi, tag);
+          if (b1 < a.B) st_tagged_sys(y + 2 * ((size_t)b1 * p.N + r_hi), c[3] * s_hi, tag);
         }
       }
     } else if (p.kind == kRows) {
@@ -1200,12 +1228,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
         const bool split_k = a.tp > 1 && (which == kO || which == kDown);
         reduce_phase(a, p, sm, nslots, tiles, status, ok, lane, out,
                      split_k ? (which == kO ? a.inbox_o_off : a.inbox_d_off) : 0ull, tag_of(l, which), &best);
-        if (split_k) {  // partial results in the peers' inboxes: cross-GPU barrier
-          __threadfence_system();
-          __syncwarp();
-          if (lane == 0) grid_arrive(a, true, gpar, false);
-          gpar ^= 1;
-        } else if (which == kGateUp) {  // the long activation vector: grid barrier
+        if (which == kGateUp) {  // the long activation vector: grid barrier
           __threadfence();
           __syncwarp();
           if (lane == 0) grid_arrive(a, false, 0, false);
@@ -1300,7 +1323,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       {
         const NormWeights nw = load_norm_weights(l > 0 ? (const uint16_t*)(a.consts + layers[l - 1].post_ffn_norm) : nullptr,
                                                  (const uint16_t*)(a.consts + L->in_norm), a.H, tid);
-        if (l > 0 && a.tp > 1) wait_grid(true);  // the down projection's partial results come from every GPU
         trace_mark(a, blk, tid, mark);
         residual_norm<BT>(a, l > 0 ? (const uint32_t*)(a.scratch + a.d_off) : nullptr, tag_of(l - 1, kDown), a.inbox_d_off, nw, xs,
                           xin, xin_stride, red, tid, status, ok);
@@ -1337,7 +1359,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
       {
         const NormWeights nw = load_norm_weights((const uint16_t*)(a.consts + L->post_attn_norm),
                                                  (const uint16_t*)(a.consts + L->pre_ffn_norm), a.H, tid);
-        if (a.tp > 1) wait_grid(true);  // the o projection's partial results come from every GPU
         trace_mark(a, blk, tid, mark);
         residual_norm<BT>(a, (const uint32_t*)(a.scratch + a.o_off), tag_of(l, kO), a.inbox_o_off, nw, xs, xin, xin_stride, red, tid,
                           status, ok);
@@ -1356,7 +1377,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeSt
     {
       const NormWeights nw = load_norm_weights((const uint16_t*)(a.consts + layers[a.n_layers - 1].post_ffn_norm),
                                                (const uint16_t*)(a.consts + a.final_norm), a.H, tid);
-      if (a.tp > 1) wait_grid(true);
       trace_mark(a, blk, tid, mark);
       residual_norm<BT>(a, (const uint32_t*)(a.scratch + a.d_off), tag_of(a.n_layers - 1, kDown), a.inbox_d_off, nw, xs, xin,
                         xin_stride, red, tid, status, ok);
@@ -1457,8 +1477,8 @@ size_t decode_step_scratch_bytes(int B, int H, int n_q, int I, int n_layers, int
   // SM count, which are the same on every member (a shard's MLP width may differ from its peers').
   offsets->counter_off = take(256);
   offsets->amax_off = take((size_t)tp * sm_count * 8 * 8);
-  offsets->inbox_o_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
-  offsets->inbox_d_off = tp > 1 ? take((size_t)tp * B * H * 4) : 0;
+  offsets->inbox_o_off = tp > 1 ? take((size_t)tp * B * H * 8) : 0;  // tagged 64-bit words
+  offsets->inbox_d_off = tp > 1 ? take((size_t)tp * B * H * 8) : 0;
   // projection outputs as tagged 32-bit words
   offsets->qkv_off = take((size_t)B * (n_q + 2) * kD * 4);
   offsets->o_off = take((size_t)B * H * 4);

@@ -123,8 +123,20 @@ __device__ __forceinline__ void reciprocal_scale(uint32_t count, int32_t& mult, 
 }
 
 // ---- average pool: tosa.avg_pool2d acc_type=i32; count excludes padding ----
-template <int VEC>  // 4 or 1 channels per thread
+// The rescale depends only on the number of taps inside the image, so the block fills a table indexed by that
+// count once (one 64-bit division per entry instead of one per output). Entry {M, 2^(S-30), S-29, count}:
+// TOSA's (v * M + 2^(S-1)) >> S with S = 30 + k >= 30 equals (8v * M + 2^(S+2)) >> (S + 3), and since the constant
+// has a zero low word that is (mulhi(8v, M) + 2^(S-30)) >> (S - 29): exact, 32-bit.
+constexpr int kAvgMaxTaps = 256;
+template <int VEC>  // 16, 4 or 1 channels per thread
 __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
+  __shared__ int4 by_count[kAvgMaxTaps + 1];
+  for (int c = threadIdx.x; c <= a.KH * a.KW; c += blockDim.x) {
+    int32_t mult, shift;
+    reciprocal_scale(c ? (uint32_t)c : 1u, mult, shift);
+    by_count[c] = make_int4(mult, 1 << (shift - 30), shift - 29, c);
+  }
+  __syncthreads();
   const int groups = a.C / VEC;
   const long long total = (long long)a.N * a.OH * a.OW * groups;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -139,7 +151,7 @@ __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
     int acc[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; j++) acc[j] = 0;
-    uint32_t count = 0;
+    int count = 0;
     for (int kh = 0; kh < a.KH; kh++) {
       int ih = oh * a.stride_h - a.pad_t + kh;
       if (ih < 0 || ih >= a.H) continue;
@@ -147,21 +159,34 @@ __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
         int iw = ow * a.stride_w - a.pad_l + kw;
         if (iw < 0 || iw >= a.W) continue;
         count++;
-        if (VEC == 4) {
-          uint32_t v = *reinterpret_cast<const uint32_t*>(xin + ((size_t)ih * a.W + iw) * a.C);
+        const int8_t* px = xin + ((size_t)ih * a.W + iw) * a.C;
+        if (VEC == 16) {
+          const uint4 v = *reinterpret_cast<const uint4*>(px);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int j = 0; j < VEC; j++) acc[j] += sx8(v, j) - a.input_zp;
+          for (int j = 0; j < 16; j++) acc[j] = __dp4a((int)w[j >> 2], 1 << (8 * (j & 3)), acc[j]);  // adds byte j, sign-extended
+        } else if (VEC == 4) {
+          const uint32_t v = *reinterpret_cast<const uint32_t*>(px);
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[j] = __dp4a((int)v, 1 << (8 * j), acc[j]);
         } else {
-          acc[0] += (int)xin[((size_t)ih * a.W + iw) * a.C] - a.input_zp;
+          acc[0] += (int)px[0];
         }
       }
     }
-    int32_t mult, shift;
-    reciprocal_scale(count ? count : 1u, mult, shift);
+    const int4 k = by_count[count];
+    const int zsum = count * a.input_zp;
     int q[VEC];
 #pragma unroll
-    for (int j = 0; j < VEC; j++) q[j] = requant(acc[j], mult, shift, false, a.output_zp, -128, 127);
-    if (VEC == 4) *reinterpret_cast<uint32_t*>(a.out + (size_t)p * a.C + g * 4) = pack4(q[0], q[1], q[2], q[3]);
+    for (int j = 0; j < VEC; j++) {
+      const int r = ((__mulhi((acc[j] - zsum) * 8, k.x) + k.y) >> k.z) + a.output_zp;
+      q[j] = max(-128, min(127, r));
+    }
+    if (VEC == 16)
+      *reinterpret_cast<uint4*>(a.out + (size_t)p * a.C + g * 16) =
+          make_uint4(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]), pack4(q[8], q[9], q[10], q[11]),
+                     pack4(q[12], q[13], q[14], q[15]));
+    else if (VEC == 4) *reinterpret_cast<uint32_t*>(a.out + (size_t)p * a.C + g * 4) = pack4(q[0], q[1], q[2], q[3]);
     else a.out[(size_t)p * a.C + g] = (int8_t)q[0];
   }
 }
@@ -170,6 +195,9 @@ __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
 // An int8 operand takes 256 values, so its input-side rescale is a 256-entry table (filled here by the
 // same apply_scale_32, one entry per thread): per element two shared-memory loads replace two 64-bit
 // multiply-shift sequences; the output rescale stays arithmetic.
+// EPI: the output rescale, 0 = 64-bit arithmetic, 1 / 2 = the compact 32-bit record (common.cuh) with / without the sign
+// term, chosen by the planner when it can bound |operand sum or product| (it evaluates the same two tables).
+template <int EPI>
 __global__ void __launch_bounds__(kThreads) binary_kernel(BinaryArgs a) {
   __shared__ int ta[256], tb[256];  // indexed by the raw byte
   {
@@ -183,7 +211,9 @@ __global__ void __launch_bounds__(kThreads) binary_kernel(BinaryArgs a) {
   auto one = [&](uint32_t xa, uint32_t xb) {
     const int ra = ta[xa], rb = tb[xb];
     const int v = a.kind == 0 ? ra + rb : a.kind == 1 ? ra - rb : ra * rb;
-    return requant(v, a.out_mult, a.out_shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
+    if (EPI == 0) return requant(v, a.out_mult, a.out_shift, dr, a.out_zp, a.clamp_min, a.clamp_max);
+    const int r = EPI == 1 ? scale_q4_sign(v, a.q4) : scale_q4(v, a.q4);  // the output zero point rides in the record
+    return max(a.clamp_min, min(a.clamp_max, r));
   };
   const long long nvec = a.n >> 4;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -360,7 +390,10 @@ void launch_maxpool(const PoolArgs& a, cudaStream_t stream) {
 }
 
 void launch_avgpool(const PoolArgs& a, cudaStream_t stream) {
-  if ((a.C & 3) == 0) {
+  if ((a.C & 15) == 0 && ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0) {
+    long long total = (long long)a.N * a.OH * a.OW * (a.C / 16);
+    avgpool_kernel<16><<<grid_for(total), kThreads, 0, stream>>>(a);
+  } else if ((a.C & 3) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C / 4);
     avgpool_kernel<4><<<grid_for(total), kThreads, 0, stream>>>(a);
   } else {
@@ -370,7 +403,9 @@ void launch_avgpool(const PoolArgs& a, cudaStream_t stream) {
 }
 
 void launch_binary(const BinaryArgs& a, cudaStream_t stream) {
-  binary_kernel<<<grid_for((a.n + 15) / 16), kThreads, 0, stream>>>(a);
+  if (a.epi == 1) binary_kernel<1><<<grid_for((a.n + 15) / 16), kThreads, 0, stream>>>(a);
+  else if (a.epi == 2) binary_kernel<2><<<grid_for((a.n + 15) / 16), kThreads, 0, stream>>>(a);
+  else binary_kernel<0><<<grid_for((a.n + 15) / 16), kThreads, 0, stream>>>(a);
 }
 
 void launch_table(const int8_t* x, const int8_t* table, int8_t* out, long long n, cudaStream_t stream) {

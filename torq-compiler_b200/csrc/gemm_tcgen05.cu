@@ -72,6 +72,10 @@ struct GemmTcParams {
   int gpt, BNh;         // epilogue groups per accumulator (1 or 2) and the columns each of them drains (BN / gpt)
   // implicit-GEMM convolution (CONV kernels): tile = TH x TW output pixels, TW a power of two
   int tw_log2, TH, tiles_w, tiles_per_img, OH, OW, cstride, pad_t, pad_l, KW, icb_per_tap;
+  // khs > 1 (stride-1 convolutions, TW >= 8): one load per (kw, channel block) brings the TH + khs - 1 input rows all
+  // khs kernel rows of that column need; the operand of kernel row kh starts kh * TW rows into the stage, a whole
+  // number of 8-row swizzle atoms, so the descriptors stay the plain K-major ones. k_loads = stage loads per tile.
+  int khs, k_loads, patch_rows;
   const int32_t* corr;  // [row classes * col classes][n_tiles * BN] border corrections, or null
   const uint8_t* rcls;  // [OH] row class
   const uint8_t* ccls;  // [OW] column class
@@ -104,9 +108,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t a_stage_bytes = (uint32_t)kBM * p.row_bytes;
+  const bool shared_rows = CONV && p.khs > 1;
+  const uint32_t a_stage_bytes = (uint32_t)(shared_rows ? p.patch_rows : kBM) * p.row_bytes;
   const uint32_t w_tile_bytes = (uint32_t)p.BN * p.row_bytes;  // one (n tile, k block) of the weights
-  const uint32_t stage_bytes = a_stage_bytes + (p.w_resident ? 0u : w_tile_bytes);
+  const uint32_t stage_bytes = a_stage_bytes + (p.w_resident ? 0u : w_tile_bytes * (shared_rows ? (uint32_t)p.khs : 1u));
   const uint32_t smem_w = smem_base;  // resident weights: [n_tiles][k_blocks] tiles
   const uint32_t smem_ring = smem_base + (p.w_resident ? (uint32_t)p.n_tiles * p.k_blocks * w_tile_bytes : 0u);
   const int total_tiles = p.m_tiles * p.n_tiles;
@@ -161,24 +166,37 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           ih0 = ty * p.TH * p.cstride - p.pad_t;
           iw0 = (tx << p.tw_log2) * p.cstride - p.pad_l;
         }
-        for (int kb = 0; kb < p.k_blocks; kb++) {
+        for (int kb = 0; kb < p.k_loads; kb++) {
           if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1, p.status, 1, p.wait_ns))) break;
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_ring + (uint32_t)s * stage_bytes;
           mbar_expect_tx(full, stage_bytes);
-          if (CONV) {
-            // zero fill outside the frame; the channel coordinate is a multiple of 32 bytes
-            tma_load_4d(dst, &tmA, icb * p.row_bytes, iw0 + kw, ih0 + kh, img, full);
+          if (shared_rows) {
+            // one patch of TH + khs - 1 rows for this kernel column and channel block; the weights of its khs taps
+            tma_load_4d(dst, &tmA, icb * p.row_bytes, iw0 + kw, ih0, img, full);
+            if (!p.w_resident)
+              for (int r = 0; r < p.khs; r++)
+                tma_load_2d(dst + a_stage_bytes + (uint32_t)r * w_tile_bytes, &tmB,
+                            ((r * p.KW + kw) * p.icb_per_tap + icb) * p.row_bytes, n * p.BN, full);
             if (++icb == p.icb_per_tap) {
               icb = 0;
-              if (++kw == p.KW) {
-                kw = 0;
-                kh++;
-              }
+              kw++;
             }
-          } else
-            tma_load_2d(dst, &tmA, kb * p.row_bytes, m * kBM, full);
-          if (!p.w_resident) tma_load_2d(dst + a_stage_bytes, &tmB, kb * p.row_bytes, n * p.BN, full);
+          } else {
+            if (CONV) {
+              // zero fill outside the frame; the channel coordinate is a multiple of 32 bytes
+              tma_load_4d(dst, &tmA, icb * p.row_bytes, iw0 + kw, ih0 + kh, img, full);
+              if (++icb == p.icb_per_tap) {
+                icb = 0;
+                if (++kw == p.KW) {
+                  kw = 0;
+                  kh++;
+                }
+              }
+            } else
+              tma_load_2d(dst, &tmA, kb * p.row_bytes, m * kBM, full);
+            if (!p.w_resident) tma_load_2d(dst + a_stage_bytes, &tmB, kb * p.row_bytes, n * p.BN, full);
+          }
           if (++s == p.stages) {
             s = 0;
             phase ^= 1;
@@ -206,18 +224,34 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint64_t desc0_ring = make_smem_desc(smem_ring, p.row_bytes);
       const uint64_t desc0_w = make_smem_desc(p.w_resident ? smem_w : smem_ring + a_stage_bytes, p.row_bytes);
       const uint32_t stage_units = stage_bytes >> 4, w_tile_units = w_tile_bytes >> 4;
+      const uint32_t tap_units = CONV ? (uint32_t)((p.row_bytes << p.tw_log2) >> 4) : 0u;  // TW rows
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         if (!(ok = mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2, p.wait_ns))) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(as * p.acc_stride);
-        for (int kb = 0; kb < p.k_blocks; kb++) {
+        int kw = 0, icb = 0;
+        for (int kb = 0; kb < p.k_loads; kb++) {
           if (!(ok = mbar_wait(smem_u32(&bar_full[s]), phase, p.status, 3, p.wait_ns))) break;
           tc_fence_after();
-          const int steps = (kb == p.k_blocks - 1) ? p.k_last_steps : steps_full;
-          const uint64_t da = desc0_ring + (uint64_t)((uint32_t)s * stage_units);
-          const uint64_t db = p.w_resident ? desc0_w + (uint64_t)((uint32_t)(n * p.k_blocks + kb) * w_tile_units)
-                                           : desc0_w + (uint64_t)((uint32_t)s * stage_units);
-          for (int k = 0; k < steps; k++) mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          if (shared_rows) {
+            for (int r = 0; r < p.khs; r++) {
+              const uint64_t da = desc0_ring + (uint64_t)((uint32_t)s * stage_units + (uint32_t)r * tap_units);
+              const uint64_t db = p.w_resident
+                                      ? desc0_w + (uint64_t)((uint32_t)(n * p.k_blocks + (r * p.KW + kw) * p.icb_per_tap + icb) * w_tile_units)
+                                      : desc0_w + (uint64_t)((uint32_t)s * stage_units + (uint32_t)r * w_tile_units);
+              for (int k = 0; k < steps_full; k++) mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | r | k) != 0);
+            }
+            if (++icb == p.icb_per_tap) {
+              icb = 0;
+              kw++;
+            }
+          } else {
+            const int steps = (kb == p.k_blocks - 1) ? p.k_last_steps : steps_full;
+            const uint64_t da = desc0_ring + (uint64_t)((uint32_t)s * stage_units);
+            const uint64_t db = p.w_resident ? desc0_w + (uint64_t)((uint32_t)(n * p.k_blocks + kb) * w_tile_units)
+                                             : desc0_w + (uint64_t)((uint32_t)s * stage_units);
+            for (int k = 0; k < steps; k++) mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          }
           mma_commit(smem_u32(&bar_empty[s]));  // frees the stage once the MMAs have read it
           if (++s == p.stages) {
             s = 0;
@@ -592,6 +626,8 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   p.n_tiles = g.n_tiles;
   p.m_tiles = (int)((a.M + kBM - 1) / kBM);
   p.k_blocks = g.k_blocks;
+  p.k_loads = g.k_blocks;
+  p.khs = 1;
   p.k_last_steps = ((a.K - (g.k_blocks - 1) * g.row_bytes) + 31) / 32;
   p.row_bytes = g.row_bytes;
   const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
@@ -632,7 +668,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
 }
 
 // ---- convolution as implicit GEMM ----
-ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, int KW) {
+ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, int KW, int stride) {
   ConvTcGeometry g{};
   // channel block = swizzle width: the widest of 128 / 64 / 32 bytes with the least padding of IC. A last
   // block that reaches beyond IC is fine: the copy engine fills the missing channels with zeros and the
@@ -648,13 +684,18 @@ ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, i
   g.icb_per_tap = (IC + g.row_bytes - 1) / g.row_bytes;
   g.k_blocks = KH * KW * g.icb_per_tap;
   g.Kpad = g.k_blocks * g.row_bytes;
-  // patch shape: TW * TH = 128 with the least padded area (ties: the wider patch, longer contiguous runs)
+  // Patch shape TW * TH = 128. Stride-1 convolutions with more than one kernel row share one load of TH + KH - 1
+  // input rows among the KH taps of a kernel column (TW >= 8 so that a kernel row's operand starts on a whole
+  // 8-row swizzle atom): the shape with the fewest rows through the copy engine. Otherwise the least padded area
+  // (ties: the wider patch, longer contiguous runs).
+  g.khs = (stride == 1 && KH > 1) ? KH : 1;
   long long best = -1;
-  for (int tw = 128; tw >= 4; tw >>= 1) {
+  for (int tw = 128; tw >= (g.khs > 1 ? 8 : 4); tw >>= 1) {
     const int th = 128 / tw;
-    const long long area = (long long)((OW + tw - 1) / tw) * tw * ((OH + th - 1) / th) * th;
-    if (best < 0 || area < best) {
-      best = area;
+    const long long tiles = (long long)((OW + tw - 1) / tw) * ((OH + th - 1) / th);
+    const long long cost = g.khs > 1 ? tiles * (th + KH - 1) * tw : tiles * tw * th;
+    if (best < 0 || cost < best) {
+      best = cost;
       g.TW = tw;
       g.TH = th;
     }
@@ -673,16 +714,17 @@ bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int 
   if (IC % 16 != 0 || OC % 16 != 0 || stride_h != stride_w || stride_h < 1 || stride_h > 2 || dil_h != 1 || dil_w != 1 ||
       KH < 1 || KW < 1 || KH * KW > 49 || KH * KW == 1)
     return false;
-  const ConvTcGeometry g = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW);
+  const ConvTcGeometry g = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW, stride_h);
   if (g.TW * stride_w > 256 || g.TH * stride_h > 256) return false;  // TMA box extents
   if ((long long)N * g.tiles_w * g.tiles_h >= (1ll << 30)) return false;
   return H >= 1 && W >= 1;
 }
 
 cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t stream) {
-  const ConvTcGeometry g = conv_tc_geometry(a.N, a.OH, a.OW, a.IC, a.OC, a.KH, a.KW);
+  const ConvTcGeometry g = conv_tc_geometry(a.N, a.OH, a.OW, a.IC, a.OC, a.KH, a.KW, a.stride);
+  const int patch_h = g.khs > 1 ? g.TH + a.KH - 1 : g.TH;  // rows of one load
   if (st->a != a.x) {
-    if (!encode_conv_input(&st->tmA, a.x, a.N, a.H, a.W, a.IC, g.row_bytes, g.TW, g.TH, a.stride)) return cudaErrorInvalidValue;
+    if (!encode_conv_input(&st->tmA, a.x, a.N, a.H, a.W, a.IC, g.row_bytes, g.TW, patch_h, a.stride)) return cudaErrorInvalidValue;
     st->a = a.x;
   }
   if (st->w != a.w) {
@@ -715,10 +757,14 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   while ((1 << p.tw_log2) < g.TW) p.tw_log2++;
   p.OH = a.OH; p.OW = a.OW; p.cstride = a.stride; p.pad_t = a.pad_t; p.pad_l = a.pad_l; p.KW = a.KW;
   p.icb_per_tap = g.icb_per_tap;
+  p.khs = g.khs;
+  p.k_loads = g.khs > 1 ? a.KW * g.icb_per_tap : g.k_blocks;
+  p.patch_rows = patch_h * g.TW;
   p.corr = a.corr; p.rcls = a.rcls; p.ccls = a.ccls; p.cls_nonzero = a.cls_nonzero; p.ncc = a.ncc;
   const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
   p.w_resident = w_bytes <= (size_t)kResidentWeightBytes;
-  const size_t stage_bytes = (size_t)kBM * g.row_bytes + (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes);
+  const size_t stage_bytes = (size_t)(g.khs > 1 ? p.patch_rows : kBM) * g.row_bytes +
+                             (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes * g.khs);
   const size_t staging_bytes = (size_t)kEpiGroups * kBM * (g.BN / g.gpt);
   const size_t ring_budget = (size_t)kSmemBudget - 1024 - (p.w_resident ? w_bytes : 0) - staging_bytes;
   int stages = (int)(ring_budget / stage_bytes);

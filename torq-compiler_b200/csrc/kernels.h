@@ -32,6 +32,9 @@ struct ConvArgs {
   int double_round;
   int hi_shift;           // every rescale shift of the op is >= 32
   const int8_t* lut;      // 256-entry table applied to the int8 result (out = lut[q + 128]), or null
+  int epi;                // 0 = ChanParams arithmetic; 1 / 2 = compact Q4 records with / without the sign term (stem kernel)
+  const int4* q4;         // [OC] Q4 records (epi != 0); the output zero point rides in them
+  long long x_bytes;      // size of the input tensor: the stem kernel reads it in aligned words
 };
 void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream);
 
@@ -95,6 +98,8 @@ struct BinaryArgs {
   int a_zp, a_mult, a_shift, b_zp, b_mult, b_shift, out_mult, out_shift, out_zp;
   int double_round, clamp_min, clamp_max;
   int a_lshift, b_lshift;  // (x - zp) << lshift before the input rescale (two-stage input rescale), 0..22
+  int epi;                 // output rescale: 0 = 64-bit arithmetic, 1 / 2 = the compact 32-bit record q4 with / without the sign term
+  int4 q4;
 };
 void launch_binary(const BinaryArgs& a, cudaStream_t stream);
 
@@ -148,8 +153,9 @@ struct ConvTcGeometry {
   int row_bytes, icb_per_tap, k_blocks, Kpad;  // K = (kh, kw, ic): the OHWI row of a filter
   int BN, n_tiles, gpt;
   int TW, TH, tiles_w, tiles_h;                // output patch of a tile (TW * TH = 128)
+  int khs;                                     // kernel rows served by one load of TH + khs - 1 input rows (1 = a load per tap)
 };
-ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, int KW);
+ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, int KW, int stride);
 bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w,
                        int OH, int OW);
 struct ConvTcArgs {

@@ -201,6 +201,14 @@ struct Builder {
   }
 };
 
+// TOSA apply_scale_32 on the host (the device form is common.cuh's): value wrapped to int32 first, as the kernels do.
+long long host_apply_scale_32(long long value, int mult, int shift, bool double_round) {
+  const long long v = (long long)(int32_t)(uint32_t)(unsigned long long)value;
+  long long round = 1ll << (shift - 1);
+  if (double_round && shift > 31) round += v >= 0 ? (1ll << 30) : -(1ll << 30);
+  return (long long)(int32_t)(uint32_t)(unsigned long long)((v * (long long)mult + round) >> shift);
+}
+
 int conv_out_dim(int i, int k, int s, int d, int p0, int p1) { return (i + p0 + p1 - d * (k - 1) - 1) / s + 1; }
 
 bool force_simt() {
@@ -838,7 +846,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         // the direct dp4a kernel is faster there)
         if (!fc && !pointwise && op.weight_zp == 0 && !force_simt() && IC != 16 &&
             conv_tc_supported(N, H, W, IC, OC, KH, KW, op.stride_h, op.stride_w, op.dil_h, op.dil_w, OH, OW)) {
-          const ConvTcGeometry geo = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW);
+          const ConvTcGeometry geo = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW, op.stride_h);
           ConvTcArgs ca{};
           ca.N = N; ca.H = H; ca.W = W; ca.IC = IC; ca.OC = OC; ca.KH = KH; ca.KW = KW; ca.OH = OH; ca.OW = OW;
           ca.stride = op.stride_h; ca.pad_t = op.pad_t; ca.pad_l = op.pad_l;
@@ -957,6 +965,12 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max; a.double_round = dr; a.hi_shift = b.last_hi_shift;
         size_t w_off = b.add_const(packed.data(), packed.size());
         size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+        // the compact 32-bit records, for the CUDA-core kernels that take them (the 3x3x3 stem)
+        std::vector<int4> q4s;
+        a.epi = (fc || has_lut) ? 0 : Builder::q4_params(cp, acc_bound, dr != 0, op.out_zp, op.clamp_min, q4s);
+        const size_t q_off = a.epi ? b.add_const(q4s.data(), q4s.size() * sizeof(int4)) : 0;
+        const bool has_q4s = a.epi != 0;
+        a.x_bytes = (long long)b.numel(op.in0);
         Loc lx = loc(op.in0), lo = loc(result_id);
         step.kernel_name = conv2d_simt_kernel_name(a);
         step.launch = [=](const ExecContext& c) {
@@ -965,6 +979,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           k.out = (int8_t*)lo.resolve(c);
           k.w = (const int8_t*)(c.consts + w_off);
           k.chan = (const ChanParams*)(c.consts + c_off);
+          k.q4 = has_q4s ? (const int4*)(c.consts + q_off) : nullptr;
           k.lut = has_lut ? (const int8_t*)(c.consts + lut_off) : nullptr;
           launch_conv2d_simt(k, c.stream);
         };
@@ -1101,6 +1116,8 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         a.pad_value = op.pad_value; a.input_zp = op.in0_zp; a.output_zp = op.out_zp;
         Loc lx = loc(op.in0), lo = loc(op.out0);
         const bool is_max = op.kind == TB200_OP_MAXPOOL;
+        if (!is_max && (long long)a.KH * a.KW > 256)  // the kernel's per-count rescale table
+          return b.fail(TB200_UNIMPLEMENTED, "op %d: average pooling windows above 256 taps are not supported", i);
         step.kernel_name = is_max ? "maxpool" : "avgpool";
         step.launch = [=](const ExecContext& c) {
           PoolArgs k = a;
@@ -1132,6 +1149,24 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         if (op.i0 < 0 || op.i0 > 22 || op.i1 < 0 || op.i1 > 22)
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: input left shift outside [0,22]", i);
         a.a_lshift = op.i0; a.b_lshift = op.i1;
+        {
+          // The operand-side rescales are functions of one byte: evaluate both tables here as the kernel does, bound
+          // the value that reaches the output rescale, and take the 32-bit form of that rescale when it is exact.
+          long long ma = 0, mb = 0;
+          for (int v = -128; v < 128; v++) {
+            const long long ra = host_apply_scale_32((long long)(v - a.a_zp) * (1ll << a.a_lshift), a.a_mult, a.a_shift, op.double_round != 0);
+            const long long rb = host_apply_scale_32((long long)(v - a.b_zp) * (1ll << a.b_lshift), a.b_mult, a.b_shift, op.double_round != 0);
+            ma = std::max(ma, ra < 0 ? -ra : ra);
+            mb = std::max(mb, rb < 0 ? -rb : rb);
+          }
+          const long long bound = a.kind == 2 ? ma * mb : ma + mb;
+          ChanParams cp{};
+          cp.mult = a.out_mult; cp.shift = a.out_shift; cp.bias = 0;
+          std::vector<int4> q4;
+          a.epi = (ma < (1ll << 31) && mb < (1ll << 31) && bound < (1ll << 29))
+                      ? Builder::q4_params({cp}, {bound}, op.double_round != 0, a.out_zp, a.clamp_min, q4) : 0;
+          if (a.epi) a.q4 = q4[0];
+        }
         Loc la = loc(op.in0), lb = loc(op.in1), lo = loc(op.out0);
         step.kernel_name = "binary_rescale";
         step.launch = [=](const ExecContext& c) {
