@@ -564,9 +564,9 @@ def main():
     decoder_tp = None
     if world in (2, 4, 8) and args.decoder:
         decoder_tp = []
-        for bsz in [int(t) for t in args.decoder.split(",") if t]:
-            if bsz > 8:
-                continue  # the fused step kernel takes up to 8 sequences
+        # the tensor-parallel step kernel takes up to 8 sequences: larger requests are measured at 8
+        tp_batches = sorted({min(int(t), 8) for t in args.decoder.split(",") if t})
+        for bsz in tp_batches:
             try:
                 r = decoder_bench(dev, stream, bsz, args.decode_prompt, args.decode_gen, tp=world, rank=rank)
                 r["parity"] = decoder_parity(dev, bsz, tp=world, rank=rank)
@@ -662,7 +662,10 @@ def main():
                    "workload": "Gemma-3-1B architecture, random-init (embedding gain 6.0: peaked logits), 1024-token seeded prompt + 128 greedy tokens",
                    "hbm_peak_gbs": peaks["hbm_gbs"], "runs": []}
         ex.destroy()  # free the CNN arena first
-        for bsz in [int(t) for t in args.decoder.split(",") if t]:
+        one_gpu_batches = [int(t) for t in args.decoder.split(",") if t]
+        if decoder_tp:  # one GPU's ids for every batch the tensor-parallel runs used
+            one_gpu_batches += [r["batch"] for r in decoder_tp if r.get("batch") not in one_gpu_batches]
+        for bsz in one_gpu_batches:
             try:
                 r = decoder_bench(dev, stream, bsz, args.decode_prompt, args.decode_gen)
                 r["hbm_frac"] = r["hbm_gbs"] / peaks["hbm_gbs"]
