@@ -476,7 +476,11 @@ def main():
     from torq_b200.workloads.mobilenet_v2 import build_mobilenet_v2, synthetic_images
 
     torch.cuda.set_device(local_rank)
+    numa_cpus = []
     if world > 1:
+        # each rank next to its GPU: the pinned staging buffers allocated below are then node-local
+        from torq_b200.replicas import pin_rank_to_gpu_numa_node
+        numa_cpus = pin_rank_to_gpu_numa_node(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     def barrier():
@@ -703,6 +707,7 @@ def main():
         "dtype": "i8", "data": "synthetic",
         "config": {"workload": f"MobileNetV2-1.0 int8 224x224, batch {B} per GPU", "global_batch": B * world,
                    "parallelism": f"replicas x{world} (batch split, no collective)",
+                   "rank0_cpu_affinity": (f"{len(numa_cpus)} CPUs of the GPU's NUMA node" if numa_cpus else "unchanged"),
                    "l2": f"inputs rotate over {n_rot} resident batches ({n_rot * in_info.nbytes / 1e6:.0f} MB > L2); "
                          "activations per step exceed L2"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_info.nbytes, "d2h_bytes_per_step": out_info.nbytes,

@@ -65,3 +65,19 @@ def test_two_rank_replicas_match_single_rank():
         p.join(timeout=240)
         assert p.exitcode == 0
     assert q.get(timeout=5) is True
+
+
+def test_numa_cpus_of_gpu_reads_sysfs(tmp_path):
+    """The NUMA lookup against a fake sysfs tree: node of the PCI device -> that node's CPU list; absent or -1 -> empty."""
+    from torq_b200.replicas import _parse_cpulist, numa_cpus_of_gpu
+    dev = tmp_path / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("16-31,48-63\n")
+    assert numa_cpus_of_gpu(0, 0x1b, 0, str(tmp_path)) == set(range(16, 32)) | set(range(48, 64))
+    (dev / "numa_node").write_text("-1\n")
+    assert numa_cpus_of_gpu(0, 0x1b, 0, str(tmp_path)) == set()
+    assert numa_cpus_of_gpu(0, 0x3c, 0, str(tmp_path)) == set()
+    assert _parse_cpulist("0,2-3") == {0, 2, 3}

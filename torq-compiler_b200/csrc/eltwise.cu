@@ -191,6 +191,66 @@ __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
   }
 }
 
+// Large windows over few outputs (the global pool at the end of a classifier: 7x7 -> 1x1): a warp per output pixel
+// and group of 16 channels, the taps spread over the lanes, sums combined by shuffles. Same arithmetic as above.
+__global__ void __launch_bounds__(kThreads) avgpool_warp_kernel(PoolArgs a) {
+  __shared__ int4 by_count[kAvgMaxTaps + 1];
+  for (int c = threadIdx.x; c <= a.KH * a.KW; c += blockDim.x) {
+    int32_t mult, shift;
+    reciprocal_scale(c ? (uint32_t)c : 1u, mult, shift);
+    by_count[c] = make_int4(mult, 1 << (shift - 30), shift - 29, c);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int groups = a.C / 16;
+  const long long total = (long long)a.N * a.OH * a.OW * groups;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int taps = a.KH * a.KW;
+  for (long long idx = warp0; idx < total; idx += nwarps) {
+    const int g = (int)(idx % groups);
+    const long long p = idx / groups;
+    const int ow = (int)(p % a.OW);
+    const long long t = p / a.OW;
+    const int oh = (int)(t % a.OH);
+    const int n = (int)(t / a.OH);
+    const int8_t* xin = a.x + (size_t)n * a.H * a.W * a.C + g * 16;
+    int acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) acc[j] = 0;
+    int count = 0;
+    for (int tap = lane; tap < taps; tap += 32) {
+      const int kh = tap / a.KW, kw = tap - kh * a.KW;
+      const int ih = oh * a.stride_h - a.pad_t + kh, iw = ow * a.stride_w - a.pad_l + kw;
+      if (ih < 0 || ih >= a.H || iw < 0 || iw >= a.W) continue;
+      count++;
+      const uint4 v = *reinterpret_cast<const uint4*>(xin + ((size_t)ih * a.W + iw) * a.C);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 16; j++) acc[j] = __dp4a((int)w[j >> 2], 1 << (8 * (j & 3)), acc[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      count += __shfl_xor_sync(0xffffffffu, count, o);
+#pragma unroll
+      for (int j = 0; j < 16; j++) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    }
+    if (lane == 0) {
+      const int4 k = by_count[count];
+      const int zsum = count * a.input_zp;
+      int q[16];
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        const int r = ((__mulhi((acc[j] - zsum) * 8, k.x) + k.y) >> k.z) + a.output_zp;
+        q[j] = max(-128, min(127, r));
+      }
+      *reinterpret_cast<uint4*>(a.out + (size_t)p * a.C + g * 16) =
+          make_uint4(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]), pack4(q[8], q[9], q[10], q[11]),
+                     pack4(q[12], q[13], q[14], q[15]));
+    }
+  }
+}
+
 // ---- add / sub / mul in TOSA form (ElementWiseBinaryPattern.cpp:385-570, MulPattern.cpp:229-238) ----
 // An int8 operand takes 256 values, so its input-side rescale is a 256-entry table (filled here by the
 // same apply_scale_32, one entry per thread): per element two shared-memory loads replace two 64-bit
@@ -392,7 +452,9 @@ void launch_maxpool(const PoolArgs& a, cudaStream_t stream) {
 void launch_avgpool(const PoolArgs& a, cudaStream_t stream) {
   if ((a.C & 15) == 0 && ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C / 16);
-    avgpool_kernel<16><<<grid_for(total), kThreads, 0, stream>>>(a);
+    // few outputs with many taps each: spread the taps over a warp
+    if (a.KH * a.KW >= 16 && total < 148ll * 2048) avgpool_warp_kernel<<<grid_for(total * 32), kThreads, 0, stream>>>(a);
+    else avgpool_kernel<16><<<grid_for(total), kThreads, 0, stream>>>(a);
   } else if ((a.C & 3) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C / 4);
     avgpool_kernel<4><<<grid_for(total), kThreads, 0, stream>>>(a);

@@ -552,6 +552,20 @@ GemmTcGeometry gemm_tc_geometry(int N, int K, long long M) {
   g.BN = best_bn;
   g.n_tiles = best_tiles;
   g.gpt = 1;
+  // few rows and a small weight matrix (a classifier's FC): narrower column tiles until every SM has one. The A tile
+  // is then re-read by more CTAs out of L2, 128 / BN times the weight bytes in all, so this pays only while the
+  // whole product is latency-bound (measured: 1000 x 1280 at 256 rows 27 -> 19 us; 8192 x 8192 at one row 45 -> 70 us)
+  {
+    const long long m_tiles = (M + kBM - 1) / kBM;
+    if (m_tiles * g.n_tiles < 148 && (long long)npad * g.Kpad <= (2ll << 20)) {
+      int bn = g.BN;
+      while (bn > 32 && m_tiles * ((npad + bn - 1) / bn) < 148) bn -= 16;
+      if (bn != g.BN) {
+        g.n_tiles = (npad + bn - 1) / bn;
+        g.BN = ((npad + g.n_tiles - 1) / g.n_tiles + 15) / 16 * 16;
+      }
+    }
+  }
   // wide tiles: 160..256 columns (a multiple of 32), two accumulator stages, two epilogue groups per tile.
   // Each A tile then meets twice as many weight columns per load and the MMA reads less shared memory per
   // multiply-accumulate. Taken when it pads no more than 1/16 beyond the narrow choice.

@@ -71,3 +71,43 @@ def max_over_ranks(value: float, device: str = "cpu") -> float:
     if dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+def _parse_cpulist(text: str) -> set[int]:
+    cpus: set[int] = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def numa_cpus_of_gpu(pci_domain: int, pci_bus: int, pci_device: int, sysfs: str = "/sys") -> set[int]:
+    """CPUs of the NUMA node the GPU hangs off (empty when the platform does not say)."""
+    import os
+    dev = os.path.join(sysfs, "bus", "pci", "devices", f"{pci_domain:04x}:{pci_bus:02x}:{pci_device:02x}.0")
+    try:
+        node = int(open(os.path.join(dev, "numa_node")).read().strip())
+        if node < 0:
+            return set()
+        return _parse_cpulist(open(os.path.join(sysfs, "devices", "system", "node", f"node{node}", "cpulist")).read())
+    except (OSError, ValueError):
+        return set()
+
+
+def pin_rank_to_gpu_numa_node(cuda_ordinal: int, sysfs: str = "/sys") -> list[int]:
+    """Restricts this process to the CPUs next to its GPU, so that the pinned staging buffers it allocates afterwards
+    (first touch) and its copy submissions stay on that node: with eight ranks feeding eight GPUs from one host, remote
+    staging memory is what costs end-to-end throughput. Returns the CPUs now allowed ([] = nothing changed: the
+    platform gives no node, or none of its CPUs is in this process's allowed set)."""
+    import os
+    if not hasattr(os, "sched_setaffinity"):
+        return []
+    p = torch.cuda.get_device_properties(cuda_ordinal)
+    cpus = numa_cpus_of_gpu(getattr(p, "pci_domain_id", 0), getattr(p, "pci_bus_id", 0), getattr(p, "pci_device_id", 0), sysfs)
+    allowed = cpus & set(os.sched_getaffinity(0))
+    if not allowed:
+        return []
+    os.sched_setaffinity(0, allowed)
+    return sorted(allowed)
