@@ -253,7 +253,7 @@ def ops_bench(dev, stream, peaks, i8_peak_tops):
     return out
 
 
-def yolo_bench(dev, stream, batch: int = 64, steps: int = 5):
+def yolo_bench(dev, stream, batch: int = 64, steps: int = 5, parity: bool = False):
     """YOLOv8n-style int8 detector at 640x640 (the detector configuration of the benchmark set): images/s, inputs resident."""
     import torch
     from torq_b200.runtime import Executable
@@ -280,8 +280,34 @@ def yolo_bench(dev, stream, batch: int = 64, steps: int = 5):
     ex.destroy()
     for b in [d_in] + outs:
         b.free()
-    return {"workload": f"YOLOv8n-style int8 detector 640x640, batch {batch}", "images_per_s": batch / (ms * 1e-3),
-            "ms_per_step": ms, "gmac_per_image": macs / 1e9, "launches_per_step": launches, "kernels": kernels}
+    result = {"workload": f"YOLOv8n-style int8 detector 640x640, batch {batch}", "images_per_s": batch / (ms * 1e-3),
+              "ms_per_step": ms, "gmac_per_image": macs / 1e9, "launches_per_step": launches, "kernels": kernels}
+    if parity:
+        # one image through the same network on the GPU and on the CPU oracle (outside the timed region): bit-exact
+        # or not, and what the oracle's pass took (the CPU figure beside the GPU one)
+        from oracle import oracle as oc
+        from oracle_exec import run_graph
+        oc.set_num_threads(len(os.sched_getaffinity(0)))
+        g1, _ = build_yolov8n(1, 640)
+        x1 = synthetic_images(1, 640)
+        ex1 = Executable(dev, g1.serialize())
+        b_in = dev.alloc(x1.nbytes)
+        b_in.upload(x1)
+        b_out = [dev.alloc(o.nbytes) for o in ex1.outputs_info]
+        ex1.dispatch([b_in], b_out)
+        dev.wait(120.0)
+        got = [b.download(o.shape, o.np_dtype) for b, o in zip(b_out, ex1.outputs_info)]
+        t0 = time.perf_counter()
+        want = run_graph(g1, [x1])
+        cpu_s = time.perf_counter() - t0
+        result["parity"] = {"batch": 1, "bit_exact": bool(all((a == b).all() for a, b in zip(got, want))),
+                            "outputs": len(want), "checker": "CPU oracle (port of the reference's host arithmetic)"}
+        result["cpu_baseline"] = {"value": 1.0 / cpu_s, "unit": "images/s", "cores": oc.num_threads(), "kind": "port",
+                                  "sample": "one 640x640 image, one pass"}
+        ex1.destroy()
+        for b in [b_in] + b_out:
+            b.free()
+    return result
 
 
 def decoder_bench(dev, stream, batch: int, prompt_len: int = 1024, gen_len: int = 128, tp: int = 1, rank: int = 0):
@@ -697,7 +723,7 @@ def main():
     yolo = None
     if not args.no_yolo:
         try:
-            yolo = yolo_bench(dev, stream)
+            yolo = yolo_bench(dev, stream, parity=(world == 1 and not args.no_cpu_baseline))
         except Exception as e:
             yolo = {"error": repr(e)[:200]}
 

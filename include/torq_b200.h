@@ -195,6 +195,12 @@ int tb200_device_probe_bounded_wait(tb200_device_t* device, uint32_t limit_ms);
  * against. Synchronous; allocates a status word and a stream for its own use and frees them. */
 int tb200_measure_i8_mma_peak(int cuda_ordinal, int rounds, double* tera_ops_per_s, double* ms);
 
+/* No counterpart in the reference (a debugging aid). With TB200_GEMM_TRACE=1 in the environment, CTA 0 of every
+ * tcgen05 GEMM / convolution launch records time stamps of its roles (6 roles x 512 slots: producer, MMA issuer,
+ * four epilogue groups; each entry (nanoseconds << 8) | event tag, 0 = unused). This call waits for the current
+ * device, copies up to `n` entries to `out`, clears the record and returns the count (-1 on failure). */
+int tb200_debug_read_gemm_trace(unsigned long long* out, int n);
+
 #ifdef __cplusplus
 }
 #endif

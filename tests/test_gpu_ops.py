@@ -168,6 +168,52 @@ def test_fully_connected(device, M, K, N, azp):
     _check(device, g, [a])
 
 
+@pytest.mark.parametrize("kn", [512, 1024, 4096, 8192])
+@pytest.mark.parametrize("M", [1, 64, 512, 4096])
+@pytest.mark.parametrize("azp", [0, -7])
+def test_fully_connected_sweep_at_full_size(device, M, kn, azp):
+    """All 32 points of the FullyConnected sweep (M x K = N, both activation zero points) at their full sizes. The whole
+    result of the largest corner would cost the CPU oracle minutes, so the check is on a sample that does not depend
+    on the size: 4096 seeded output positions (every row class and column tile is hit), each recomputed as an exact
+    int64 dot product and passed through the numpy restatement of the rescale; plus whole rows 0 and M - 1."""
+    from oracle import oracle_np as onp
+    rng = np.random.default_rng(kn + M)
+    a = rng.integers(-128, 128, (M, kn), dtype=np.int8)
+    w = rng.integers(-127, 128, (kn, kn), dtype=np.int8)
+    bias = np.round(rng.normal(0, 1000, kn)).astype(np.int32)
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, kn) * 40.0 / (np.sqrt(kn) * 74 * 74))
+    g = Graph()
+    g.output(g.fully_connected(g.input((M, kn)), w, bias, m, s, input_zp=azp, out_zp=-3))
+    got = run_graph_gpu(device, g, [a])[0]
+    rows = np.concatenate([rng.integers(0, M, 4096), np.zeros(kn, np.int64), np.full(kn, M - 1)])
+    cols = np.concatenate([rng.integers(0, kn, 4096), np.arange(kn), np.arange(kn)])
+    want = np.empty(rows.size, np.int8)
+    for lo in range(0, rows.size, 1024):  # chunks keep the gathered int64 operands small
+        r, c = rows[lo:lo + 1024], cols[lo:lo + 1024]
+        acc = ((a[r].astype(np.int64) - azp) * w[c].astype(np.int64)).sum(1) + bias[c]
+        want[lo:lo + 1024] = [onp.requant(onp.wrap32(np.array([v])), m[j:j + 1], s[j:j + 1], -3, -128, 127)[0]
+                              for v, j in zip(acc, c)]
+    assert (got[rows, cols] == want).all(), int((got[rows, cols] != want).sum())
+    assert len(np.unique(got[rows, cols])) > 50
+
+
+def test_pools_and_table_at_benchmark_size(device):
+    """The pooling and table configurations at their full sizes: max / average pool 3x3 stride 2 on 64x112x112x64 and
+    the 256-entry table on 64x56x56x256, whole tensors against the oracle (the C restatement takes a second or two)."""
+    rng = np.random.default_rng(77)
+    x = rng.integers(-128, 128, (64, 112, 112, 64), dtype=np.int8)
+    g = Graph()
+    xi = g.input(x.shape)
+    g.output(g.maxpool2d(xi, (3, 3), (2, 2), (0, 1, 0, 1)))
+    g.output(g.avg_pool2d(xi, (3, 3), (2, 2), (0, 1, 0, 1), input_zp=-5, output_zp=3))
+    _check(device, g, [x])
+    t = rng.integers(-128, 128, (64, 56, 56, 256), dtype=np.int8)
+    table = rng.integers(-128, 128, 256).astype(np.int8)
+    g = Graph()
+    g.output(g.table(g.input(t.shape), table))
+    _check(device, g, [t])
+
+
 def test_matmul_int32(device):
     rng = np.random.default_rng(1234)
     a = rng.integers(-128, 128, (17, 70), dtype=np.int8)

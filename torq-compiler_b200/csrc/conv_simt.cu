@@ -390,11 +390,14 @@ __global__ void __launch_bounds__(256) matmul_int_kernel(const TIn* __restrict__
 // into 7 dp4a operands once and run against every output channel's 7 weight words (two 16-byte shared-memory loads
 // per channel, shared by the thread's pixels): 7 dp4a + about 7 instructions of rescale per output.
 constexpr int kStemPix = 4;
-template <int EPI>
+template <int EPI, bool LUT>
 __global__ void __launch_bounds__(128) conv2d_stem333_kernel(ConvArgs a) {
-  extern __shared__ __align__(16) uint32_t stem_s[];  // [OC][8] weight words (word 7 zero), then [OC] Q4 records
+  extern __shared__ __align__(16) uint32_t stem_s[];  // [OC][8] weight words (word 7 zero), [OC] Q4 records, 256-byte table
   uint4* w_s = reinterpret_cast<uint4*>(stem_s);
   int4* q_s = reinterpret_cast<int4*>(stem_s + (size_t)a.OC * 8);
+  const int8_t* lut_s = reinterpret_cast<const int8_t*>(stem_s + (size_t)a.OC * 12);
+  if (LUT)
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) reinterpret_cast<int8_t*>(stem_s + (size_t)a.OC * 12)[i] = a.lut[i];
   for (int i = threadIdx.x; i < a.OC * 8; i += blockDim.x) {
     const int oc = i >> 3, kw = i & 7;
     stem_s[i] = kw < 7 ? *reinterpret_cast<const uint32_t*>(a.w + (size_t)oc * a.Kpad + kw * 4) : 0u;
@@ -475,6 +478,7 @@ __global__ void __launch_bounds__(128) conv2d_stem333_kernel(ConvArgs a) {
           acc = __dp4a((int)patch[px][6], (int)wb.z, acc);
           const int r = EPI == 1 ? scale_q4_sign(acc, c) : scale_q4(acc, c);
           q[px][j] = max(a.clamp_min, min(a.clamp_max, r));
+          if (LUT) q[px][j] = lut_s[q[px][j] + 128];  // a fused 256-entry table
         }
       }
 #pragma unroll
@@ -537,14 +541,13 @@ static bool conv_c16_applies(const ConvArgs& a) {
   return a.IC == 16 && a.weight_zp == 0 && a.OC <= 256 && (taps == 9 || taps == 1 || taps == 25);
 }
 
-// the 3x3x3 stem with 32-bit epilogue records (the planner leaves epi at 0 when a table is fused), output channels in
-// whole 16-byte groups
+// the 3x3x3 stem with 32-bit epilogue records, output channels in whole 16-byte groups
 static bool conv_stem333_shape(const ConvArgs& a) {
   return a.IC == 3 && a.KH == 3 && a.KW == 3 && a.dil_h == 1 && a.dil_w == 1 && a.weight_zp == 0 && a.epi != 0 &&
          (a.OC & 15) == 0 && a.OC <= 256;
 }
 static bool conv_stem333_applies(const ConvArgs& a) {
-  return conv_stem333_shape(a) && a.q4 && !a.lut && ((uintptr_t)a.x & 3) == 0 && ((uintptr_t)a.out & 15) == 0;
+  return conv_stem333_shape(a) && a.q4 && ((uintptr_t)a.x & 3) == 0 && ((uintptr_t)a.out & 15) == 0;
 }
 
 const char* conv2d_simt_kernel_name(const ConvArgs& a) {
@@ -575,9 +578,14 @@ void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
   }
   if (conv_stem333_applies(a)) {
     const unsigned blocks = (unsigned)((P + 128 * kStemPix - 1) / (128 * kStemPix));
-    const size_t smem = (size_t)a.OC * (32 + 16);
-    if (a.epi == 1) conv2d_stem333_kernel<1><<<blocks, 128, smem, stream>>>(a);
-    else conv2d_stem333_kernel<2><<<blocks, 128, smem, stream>>>(a);
+    const size_t smem = (size_t)a.OC * (32 + 16) + 256;
+    if (a.lut) {
+      if (a.epi == 1) conv2d_stem333_kernel<1, true><<<blocks, 128, smem, stream>>>(a);
+      else conv2d_stem333_kernel<2, true><<<blocks, 128, smem, stream>>>(a);
+    } else {
+      if (a.epi == 1) conv2d_stem333_kernel<1, false><<<blocks, 128, smem, stream>>>(a);
+      else conv2d_stem333_kernel<2, false><<<blocks, 128, smem, stream>>>(a);
+    }
     return;
   }
   if (a.IC <= 4 && a.K <= 64 && a.OC <= 256 && a.weight_zp == 0) {

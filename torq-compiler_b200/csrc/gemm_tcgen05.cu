@@ -58,7 +58,20 @@ constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kSmemBudget = 216 * 1024;          // dynamic shared memory the kernel may use (227 KB less the static part)
 constexpr int kResidentWeightBytes = 64 * 1024;  // weights up to this size stay in shared memory
 
+// Debugging aid (TB200_GEMM_TRACE=1): CTA 0 records %globaltimer stamps of its roles, 512 slots per role
+// (0 producer, 1 MMA issuer, 2.. epilogue groups); tb200_debug_read_gemm_trace copies them out.
+constexpr int kTraceSlots = 512;
+__device__ unsigned long long g_gemm_trace[6 * kTraceSlots];
+__device__ __forceinline__ void trace_stamp(int on, int role, int& idx, unsigned tag) {
+  if (on && blockIdx.x == 0 && idx < kTraceSlots) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_gemm_trace[role * kTraceSlots + idx++] = (t << 8) | tag;
+  }
+}
+
 struct GemmTcParams {
+  int trace;
   const ChanParams* chan;
   int8_t* out;
   long long ldc;
@@ -155,6 +168,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int tr = 0;
       int n = blockIdx.x / p.m_tiles, m = blockIdx.x - n * p.m_tiles;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         // convolution: where the tile's patch starts in the input, and the tap / channel block of kb
@@ -168,6 +182,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         for (int kb = 0; kb < p.k_loads; kb++) {
           if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1, p.status, 1, p.wait_ns))) break;
+          trace_stamp(p.trace, 0, tr, 1);
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_ring + (uint32_t)s * stage_bytes;
           mbar_expect_tx(full, stage_bytes);
@@ -221,17 +236,20 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int n = blockIdx.x / p.m_tiles, m = blockIdx.x - n * p.m_tiles;
       int as = 0;
       uint32_t acc_phase = 0;
+      int tr = 0;
       const uint64_t desc0_ring = make_smem_desc(smem_ring, p.row_bytes);
       const uint64_t desc0_w = make_smem_desc(p.w_resident ? smem_w : smem_ring + a_stage_bytes, p.row_bytes);
       const uint32_t stage_units = stage_bytes >> 4, w_tile_units = w_tile_bytes >> 4;
       const uint32_t tap_units = CONV ? (uint32_t)((p.row_bytes << p.tw_log2) >> 4) : 0u;  // TW rows
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         if (!(ok = mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2, p.wait_ns))) break;
+        trace_stamp(p.trace, 1, tr, 1);
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(as * p.acc_stride);
         int kw = 0, icb = 0;
         for (int kb = 0; kb < p.k_loads; kb++) {
           if (!(ok = mbar_wait(smem_u32(&bar_full[s]), phase, p.status, 3, p.wait_ns))) break;
+          trace_stamp(p.trace, 1, tr, 2);
           tc_fence_after();
           if (shared_rows) {
             for (int r = 0; r < p.khs; r++) {
@@ -259,6 +277,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
         }
         if (ok) mma_commit(smem_u32(&bar_acc_full[as]));
+        trace_stamp(p.trace, 1, tr, 3);
         if (++as == p.acc_stages) {
           as = 0;
           acc_phase ^= 1;
@@ -295,6 +314,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int loaded_n = -1;
     uint32_t acc_phase = 0;
     bool ok = true;
+    int tr = 0;
+    const int tr_on = p.trace && e == 0;
     const int t_first = blockIdx.x + astage * gridDim.x;
     int n = t_first / p.m_tiles, m = t_first - n * p.m_tiles;
     for (int t = t_first; t < total_tiles; t += p.acc_stages * gridDim.x) {
@@ -305,7 +326,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         group_sync();
         loaded_n = n;
       }
+      trace_stamp(tr_on, 2 + group, tr, 1);
       if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[astage]), acc_phase, p.status, 4, p.wait_ns);
+      trace_stamp(tr_on, 2 + group, tr, 2);
       if (ok) {
         tc_fence_after();
         const int row = m * kBM + row_in_tile;
@@ -332,6 +355,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (e == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           group_sync();
         }
+        trace_stamp(tr_on, 2 + group, tr, 3);
 
         // requantise 16 accumulators starting at tile column c0 and store them
         auto emit16 = [&](const uint32_t* v, int c0) {
@@ -386,6 +410,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         tc_fence_before();
         __syncwarp();
+        trace_stamp(tr_on, 2 + group, tr, 4);
         if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[astage]));  // this warp's share of the TMEM stage is drained
         if (p.tma_store) {
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // staged bytes -> visible to the TMA engine
@@ -395,6 +420,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             else tma_store_2d(&tmC, ncol0, m * kBM, smem_u32(stage_tile));
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
+          trace_stamp(tr_on, 2 + group, tr, 5);
         }
       }
       acc_phase ^= 1;
@@ -500,6 +526,23 @@ bool encode_conv_output(CUtensorMap* map, const void* base, int N, int OH, int O
 
 }  // namespace
 
+
+namespace {
+int gemm_trace_on() {
+  const char* e = getenv("TB200_GEMM_TRACE");
+  return e && *e && *e != '0';
+}
+}  // namespace
+
+// Copies the role timestamps of the last traced launch's CTA 0 (6 roles x 512 slots, (ns << 8) | tag, 0 = unused).
+int read_gemm_trace(unsigned long long* out, int n) {
+  if (n > 6 * kTraceSlots) n = 6 * kTraceSlots;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(out, g_gemm_trace, (size_t)n * sizeof(unsigned long long)) != cudaSuccess) return -1;
+  static unsigned long long zeros[6 * kTraceSlots];
+  cudaMemcpyToSymbol(g_gemm_trace, zeros, sizeof(zeros));
+  return n;
+}
 
 namespace {
 typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, GemmTcParams);
@@ -666,6 +709,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
   p.wait_ns = wait_limit_ns();
+  p.trace = gemm_trace_on();
   p.lut = a.lut;
   p.staging_off = (uint32_t)((p.w_resident ? w_bytes : 0) + (size_t)stages * stage_bytes);
   const size_t smem = 1024 + p.staging_off + staging_bytes;
@@ -701,7 +745,9 @@ ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, i
   // Patch shape TW * TH = 128. Stride-1 convolutions with more than one kernel row share one load of TH + KH - 1
   // input rows among the KH taps of a kernel column (TW >= 8 so that a kernel row's operand starts on a whole
   // 8-row swizzle atom): the shape with the fewest rows through the copy engine. Otherwise the least padded area
-  // (ties: the wider patch, longer contiguous runs).
+  // (ties: the wider patch, longer contiguous runs). Measured on 3x3 convolutions of 32..128 channels at 48..112
+  // pixels: once the loads are shared, 8-, 16- and 32-pixel-wide patches take the same time (the kernel is then
+  // bound per tile, not by rows or runs of the copy engine), so the rule stays the simple one.
   g.khs = (stride == 1 && KH > 1) ? KH : 1;
   long long best = -1;
   for (int tw = 128; tw >= (g.khs > 1 ? 8 : 4); tw >>= 1) {
@@ -784,6 +830,11 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   int stages = (int)(ring_budget / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
+  {  // A/B aid: TB200_CONV_STAGES=<n> caps the ring depth (the convolution always stores through the TMA: the
+     // register store path indexes rows as a plain GEMM does and is not valid for patch tiles)
+    const char* e = getenv("TB200_CONV_STAGES");
+    if (e && atoi(e) >= 2 && atoi(e) < stages) stages = atoi(e);
+  }
   p.stages = stages;
   p.out_zp = a.out_zp; p.clamp_min = a.clamp_min; p.clamp_max = a.clamp_max; p.q4 = a.q4;
   int stride = 32;
@@ -795,6 +846,7 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   p.tmem_cols = p.acc_stages * stride;
   p.status = a.status;
   p.wait_ns = wait_limit_ns();
+  p.trace = gemm_trace_on();
   p.lut = a.lut;
   p.staging_off = (uint32_t)((p.w_resident ? w_bytes : 0) + (size_t)stages * stage_bytes);
   const size_t smem = 1024 + p.staging_off + staging_bytes;

@@ -149,6 +149,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
 
 // KH x KW convolution (stride 1 or 2, no dilation, symmetric weights, IC % 16 == 0, OC % 16 == 0)
 // as implicit GEMM on the same kernel: see gemm_tcgen05.cu.
+int read_gemm_trace(unsigned long long* out, int n);  // debugging aid, see gemm_tcgen05.cu
 struct ConvTcGeometry {
   int row_bytes, icb_per_tap, k_blocks, Kpad;  // K = (kh, kw, ic): the OHWI row of a filter
   int BN, n_tiles, gpt;

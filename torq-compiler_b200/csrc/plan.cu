@@ -967,7 +967,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
         // the compact 32-bit records, for the CUDA-core kernels that take them (the 3x3x3 stem)
         std::vector<int4> q4s;
-        a.epi = (fc || has_lut) ? 0 : Builder::q4_params(cp, acc_bound, dr != 0, op.out_zp, op.clamp_min, q4s);
+        a.epi = fc ? 0 : Builder::q4_params(cp, acc_bound, dr != 0, op.out_zp, op.clamp_min, q4s);
         const size_t q_off = a.epi ? b.add_const(q4s.data(), q4s.size() * sizeof(int4)) : 0;
         const bool has_q4s = a.epi != 0;
         a.x_bytes = (long long)b.numel(op.in0);

@@ -839,6 +839,11 @@ extern "C" int tb200_device_probe_bounded_wait(tb200_device_t* d, uint32_t limit
   return TB200_OK;
 }
 
+extern "C" int tb200_debug_read_gemm_trace(unsigned long long* out, int n) {
+  if (!out || n <= 0) return -1;
+  return tb200::read_gemm_trace(out, n);
+}
+
 extern "C" int tb200_invoke_host(tb200_executable_t* ex, const void* const* host_inputs,
                                  void* const* host_outputs) {
   int st = tb200_invoke_host_async(ex, host_inputs, host_outputs);

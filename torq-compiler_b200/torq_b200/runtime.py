@@ -79,6 +79,7 @@ _SIGNATURES = {
                                         C.c_int, C.c_int, C.c_int, C.c_int]),
     "tb200_device_probe_bounded_wait": (C.c_int, [C.c_void_p, C.c_uint32]),
     "tb200_measure_i8_mma_peak": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "tb200_debug_read_gemm_trace": (C.c_int, [C.POINTER(C.c_ulonglong), C.c_int]),
     "tb200_executable_profile_ops": (C.c_int, [C.c_void_p, C.POINTER(Binding), C.c_size_t, C.c_int, C.c_int,
                                                C.POINTER(C.c_float), C.c_uint32]),
 }
