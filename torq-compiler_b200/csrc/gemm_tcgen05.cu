@@ -270,6 +270,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                              : desc0_w + (uint64_t)((uint32_t)s * stage_units);
             for (int k = 0; k < steps; k++) mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
           }
+          trace_stamp(p.trace, 1, tr, 4);
           mma_commit(smem_u32(&bar_empty[s]));  // frees the stage once the MMAs have read it
           if (++s == p.stages) {
             s = 0;
