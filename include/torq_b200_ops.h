@@ -116,6 +116,14 @@ enum tb200_op_kind {
                                * {scale32 = false} that follows it: 64-bit accumulator + bias (i64[OC] or i64[1]), TOSA apply_scale_16
                                * (acc * multiplier + 2^(shift-1)) >> shift with a 16-bit multiplier, single rounding, + out_zp, clamp,
                                * int16 result. Attributes as CONV2D. */
+  TB200_OP_PERMUTE = 57,      /* a transpose of more than four dimensions (depth-to-space and the like: tosa.reshape -> tosa.transpose ->
+                               * tosa.reshape): the input, whatever its stored shape, is viewed as a dense tensor of rank r <= 6 with extents
+                               * i0 = d0 | d1 << 16, i1 = d2 | d3 << 16, i2 = d4 | d5 << 16, permuted by i3 = p0 | p1 << 4 | ... | r << 24 and
+                               * stored densely; the output tensor only needs the same element count */
+  TB200_OP_GATHER = 58,       /* tosa.gather: in0 values [N, K, C], in1 indices [N, W] (i32) -> [N, W, C]; out[n, w, :] = values[n, indices[n, w], :]
+                               * (doc/user-manual/ops.md: Gather i8 / i16 / i32). An index outside [0, K) reads as zero. */
+  TB200_OP_SCATTER = 59,      /* tosa.scatter: a copy of in0 values [N, K, C] in which row indices[n, w] (in1, i32 [N, W]) is replaced by in2
+                               * updates[n, w, :]; indices of one n are distinct (TOSA), an index outside [0, K) is skipped */
   TB200_OP_ALLREDUCE = 40,    /* sum of the fp32 partial results of the i0 GPUs of a tensor-parallel group
                                * (this one is rank i1), rounded to bf16; only inside the fused decode step */
 };

@@ -234,6 +234,19 @@ def conv2d_i16(x: np.ndarray, w: np.ndarray, bias: np.ndarray, mult, shift, *, s
     return np.clip(r + out_zp, clamp[0], clamp[1]).astype(np.int16)
 
 
+def gather(values: np.ndarray, indices: np.ndarray) -> np.ndarray:
+    """tosa.gather (TOSA 1.0: output[n, w, c] = values[n, indices[n, w], c])."""
+    return np.stack([values[n][indices[n]] for n in range(values.shape[0])])
+
+
+def scatter(values: np.ndarray, indices: np.ndarray, updates: np.ndarray) -> np.ndarray:
+    """tosa.scatter (TOSA 1.0: values_out = values_in with values_out[n, indices[n, w], c] = input[n, w, c])."""
+    out = values.copy()
+    for n in range(values.shape[0]):
+        out[n][indices[n]] = updates[n]
+    return out
+
+
 def table16(x: np.ndarray, table: np.ndarray) -> np.ndarray:
     """tosa.table, int16 in, 513-entry int16 table, int32 out: linear interpolation over the low 7 bits."""
     v = x.astype(np.int64)

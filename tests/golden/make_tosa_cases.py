@@ -91,6 +91,22 @@ GENERIC_CASES = [
     "tosa_ops/identity-stride-offset-6x6xi8", "tosa_ops/matmul-in-int8-out-int16",
     "tosa_ops/matmul-in-int16-out-int16", "tosa_ops/matmul-in-int16-out-int32",
     "tosa_ops/matmul-in-int8-out-int16-64x128x2048", "gen_ops/conv2d_64x64_i16",
+    # transposes of five and six dimensions (depth-to-space, space-to-depth), gather / scatter, and fixtures that only
+    # needed a collapsed view or a larger size limit
+    "tosa_ops/Elementwise_max_broadcast_clip-i8", "tosa_ops/Elementwise_min_broadcast_clip-i8", "tosa_ops/add-32x32x128xi16",
+    "tosa_ops/add-56x56x256", "tosa_ops/add-bf16", "tosa_ops/add-i32",
+    "tosa_ops/clamp-bf16", "tosa_ops/css_scalar", "tosa_ops/d2s_16x16x128xi16_crd",
+    "tosa_ops/d2s_16x16x128xi16_dcr", "tosa_ops/d2s_16x16x128xi8_crd", "tosa_ops/d2s_16x16x128xi8_dcr",
+    "tosa_ops/d2s_8x8x128xi16_crd", "tosa_ops/d2s_8x8x128xi16_dcr", "tosa_ops/d2s_8x8x128xi8_crd",
+    "tosa_ops/d2s_8x8x128xi8_dcr", "tosa_ops/d2s_8x8x4xi16", "tosa_ops/d2s_8x8x4xi8",
+    "tosa_ops/d2s_9x9x128xi16_dcr", "tosa_ops/disable-maxpool-tile", "tosa_ops/gather-i16",
+    "tosa_ops/gather-i32", "tosa_ops/gather", "tosa_ops/identity-2x5x2x16x8x2-i16",
+    "tosa_ops/identity-2x5x2x16x8x2-i32", "tosa_ops/identity-2x5x2x16x8x2-i8", "tosa_ops/identity-stride-offset-3x4x2x70xi8",
+    "tosa_ops/matmul-in-int8-out-int16-1024x128x1024", "tosa_ops/matmul-notile", "tosa_ops/s2d_16x16x1xi8",
+    "tosa_ops/scatter-single-channel", "tosa_ops/scatter", "tosa_ops/scatter_1",
+    "tosa_ops/sub-56x56x256xi8", "tosa_ops/sub-bf16", "tosa_ops/sub-i32",
+    "tosa_ops/sub-rescale-scalar-bis", "tosa_ops/sub-rescale-scalar", "tosa_ops/transpose-5dim",
+    "tosa_ops/transpose-5dim_1", "tosa_ops/transpose-5dim_2", "tosa_ops/transpose-5dim_3",
     "tosa_ops/mul-1hw1-in-int8-out-int32", "tosa_ops/mul-1hwc-in-int16-out-int32",
     "tosa_ops/mul-1hwc-in-int8-out-int32-1", "tosa_ops/mul-1hwc-in-int8-out-int32-2dim",
     "tosa_ops/mul-1hwc-in-int8-out-int32-3dim", "tosa_ops/mul-1hwc-in-int8-out-int32", "tosa_ops/mul-bf16",
@@ -149,6 +165,29 @@ def numpy_replay(g, inputs):
             y = onp.ew_elementwise(EW_NAMES[a["i0"]], x, op.inputs[0].dtype, second, op.inputs[1].dtype if second is not None else None,
                                    op.outputs[0].dtype, op.outputs[0].shape, arg=a["i1"], in_zp=a["in0_zp"], out_zp=a["out_zp"],
                                    clamp=(a["clamp_min"], a["clamp_max"]), fclamp=(a["f0"], a["f1"]), bool_result=bool(a.get("flags", 0) & 4))
+        elif k == "gather":
+            idx = vals[op.inputs[1].id]
+            y = np.empty(op.outputs[0].shape, x.dtype)
+            for n_ in range(idx.shape[0]):
+                for w_ in range(idx.shape[1]):
+                    y[n_, w_, :] = x[n_, int(idx[n_, w_]), :]
+        elif k == "scatter":
+            idx, upd = vals[op.inputs[1].id], vals[op.inputs[2].id]
+            y = x.copy()
+            for n_ in range(idx.shape[0]):
+                for w_ in range(idx.shape[1]):
+                    y[n_, int(idx[n_, w_]), :] = upd[n_, w_, :]
+        elif k == "permute":  # element by element through flat indices
+            r = (a["i3"] >> 24) & 15
+            d6 = [a["i0"] & 0xffff, a["i0"] >> 16, a["i1"] & 0xffff, a["i1"] >> 16, a["i2"] & 0xffff, a["i2"] >> 16][:r]
+            perm = [(a["i3"] >> (4 * i)) & 15 for i in range(r)]
+            in_str = [int(np.prod(d6[i + 1:])) for i in range(r)]
+            flat_in = x.reshape(-1)
+            flat_out = np.empty(flat_in.size, x.dtype)
+            out_dims = [d6[pd] for pd in perm]
+            for o, idx in enumerate(np.ndindex(*out_dims)):
+                flat_out[o] = flat_in[sum(idx[d] * in_str[perm[d]] for d in range(r))]
+            y = flat_out.reshape(op.outputs[0].shape)
         elif k == "transpose":
             perm = [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim]
             y = np.empty(op.outputs[0].shape, x.dtype)

@@ -73,6 +73,14 @@ def run_graph(graph, inputs, keep_all=False):
             y = np.broadcast_to(y, op.outputs[0].shape) if y.shape != tuple(op.outputs[0].shape) else y
         elif k == "transpose":
             y = np.transpose(x, [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim])
+        elif k == "gather":
+            y = gops.gather(x, vals[op.inputs[1].id])
+        elif k == "scatter":
+            y = gops.scatter(x, vals[op.inputs[1].id], vals[op.inputs[2].id])
+        elif k == "permute":
+            r = (a["i3"] >> 24) & 15
+            d6 = [a["i0"] & 0xffff, a["i0"] >> 16, a["i1"] & 0xffff, a["i1"] >> 16, a["i2"] & 0xffff, a["i2"] >> 16]
+            y = x.reshape(d6[:r]).transpose([(a["i3"] >> (4 * i)) & 15 for i in range(r)]).reshape(op.outputs[0].shape)
         elif k == "slice":
             start = [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim]
             y = x[tuple(slice(s, s + n) for s, n in zip(start, op.outputs[0].shape))]

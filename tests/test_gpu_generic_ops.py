@@ -217,3 +217,32 @@ def test_conv2d_int16_activations(device, shape, oc, k, stride, dil, pad, per_ch
                           dilation=(dil, dil), pad=pad, input_zp=0, weight_zp=0, out_zp=-11))
     got = _same(device, g, [x])
     assert len(np.unique(got[0])) > 16
+
+
+@pytest.mark.parametrize("dtype", ["i8", "i16", "i32"])
+def test_gather_and_scatter(device, dtype):
+    rng = np.random.default_rng(6)
+    N, K, C, W = 3, 50, 7, 12
+    values = rng.integers(-100, 100, (N, K, C)).astype(NP[dtype])
+    idx = np.stack([rng.permutation(K)[:W] for _ in range(N)]).astype(np.int32)   # distinct per batch, as TOSA asks
+    upd = rng.integers(-100, 100, (N, W, C)).astype(NP[dtype])
+    g = Graph()
+    v, i, u = g.input(values.shape, dtype), g.input(idx.shape, "i32"), g.input(upd.shape, dtype)
+    g.output(g.gather(v, i))
+    g.output(g.scatter(v, i, u))
+    _same(device, g, [values, idx, upd])
+
+
+@pytest.mark.parametrize("view,perm", [((2, 4, 4, 2, 2, 8), (0, 1, 3, 2, 4, 5)), ((1, 8, 8, 2, 2, 32), (0, 1, 3, 2, 4, 5)),
+                                        ((1, 8, 8, 32, 2, 2), (0, 1, 4, 2, 5, 3)), ((3, 5, 2, 7, 4), (0, 3, 1, 4, 2)),
+                                        ((2, 3, 4, 5, 6), (4, 3, 2, 1, 0))])
+def test_permute_of_five_and_six_dimensions(device, view, perm):
+    """Depth-to-space forms (block in the channel's high or low part) and general five-dimensional transposes, the last
+    one a full reversal that no merging of neighbours shortens."""
+    rng = np.random.default_rng(len(view))
+    n = int(np.prod(view))
+    x = rng.integers(-128, 128, n).astype(np.int8).reshape(-1, view[-1])
+    g = Graph()
+    out_shape = (int(np.prod([view[p] for p in perm[:-1]])), view[perm[-1]])
+    g.output(g.permute(g.input(x.shape), view, perm, out_shape))
+    _same(device, g, [x])

@@ -72,7 +72,7 @@ def test_add_chain_and_unsupported_ops():
     assert [op.kind for op in g2.ops] == ["rescale", "rescale", "ew", "rescale"]
     assert g2.ops[0].outputs[0].dtype == "i32" and g2.ops[3].outputs[0].dtype == "i8"
     with pytest.raises(NotImplementedError):
-        tosa_frontend.build_graph(ADD.replace("tosa.add", "tosa.scatter"))
+        tosa_frontend.build_graph(ADD.replace("tosa.add", "tosa.erf"))
 
 
 TWO_STAGE = '''

@@ -179,7 +179,8 @@ template <> __device__ __forceinline__ uint4 pad_piece<uint4>(int value, int eb)
 
 // out[o] = in[in_offset + sum (o_d - lo_d) * in_str_d] when every (o_d - lo_d) lies in [0, in_dims_d), else the pad
 // value; the output element sits at out_offset + sum o_d * out_str_d. One kernel for transpose, slice, pad and concat.
-template <typename T>
+// ND = dimensions walked (4 when the two leading slots are 1: the common case keeps its shorter index arithmetic)
+template <typename T, int ND>
 __global__ void __launch_bounds__(256) strided_copy_kernel(StridedCopyArgs a) {
   const long long stride = (long long)gridDim.x * blockDim.x;
   const T* src = (const T*)a.in;
@@ -188,7 +189,7 @@ __global__ void __launch_bounds__(256) strided_copy_kernel(StridedCopyArgs a) {
     long long r = i, si = a.in_offset, di = a.out_offset;
     bool inside = true;
 #pragma unroll
-    for (int d = 3; d >= 0; d--) {
+    for (int d = 5; d >= 6 - ND; d--) {
       const int c = (int)(r % a.dims[d]);
       r /= a.dims[d];
       const int ci = c - a.lo[d];
@@ -276,24 +277,31 @@ void launch_rescale_generic(const RescaleGenericArgs& a, cudaStream_t stream) {
   rescale_generic_kernel<<<grid_for(a.n), 256, 0, stream>>>(a);
 }
 void launch_strided_copy(const StridedCopyArgs& a, cudaStream_t stream) {
-  if (a.elem_bytes == 1) strided_copy_kernel<uint8_t><<<grid_for(a.n), 256, 0, stream>>>(a);
-  else if (a.elem_bytes == 2) strided_copy_kernel<uint16_t><<<grid_for(a.n), 256, 0, stream>>>(a);
-  else if (a.elem_bytes == 4) strided_copy_kernel<uint32_t><<<grid_for(a.n), 256, 0, stream>>>(a);
-  else if (a.elem_bytes == 8) strided_copy_kernel<uint2><<<grid_for(a.n), 256, 0, stream>>>(a);
-  else strided_copy_kernel<uint4><<<grid_for(a.n), 256, 0, stream>>>(a);
+  const bool six = a.dims[0] != 1 || a.dims[1] != 1;
+#define TB200_COPY(T)                                                                  \
+  do {                                                                                 \
+    if (six) strided_copy_kernel<T, 6><<<grid_for(a.n), 256, 0, stream>>>(a);          \
+    else strided_copy_kernel<T, 4><<<grid_for(a.n), 256, 0, stream>>>(a);              \
+  } while (0)
+  if (a.elem_bytes == 1) TB200_COPY(uint8_t);
+  else if (a.elem_bytes == 2) TB200_COPY(uint16_t);
+  else if (a.elem_bytes == 4) TB200_COPY(uint32_t);
+  else if (a.elem_bytes == 8) TB200_COPY(uint2);
+  else TB200_COPY(uint4);
+#undef TB200_COPY
 }
 void widen_strided_copy(StridedCopyArgs& a) {
-  if (a.in_str[3] != 1 || a.out_str[3] != 1) return;
+  if (a.in_str[5] != 1 || a.out_str[5] != 1) return;
   for (int bytes = 16; bytes > a.elem_bytes; bytes >>= 1) {
     const int v = bytes / a.elem_bytes;
-    bool fits = a.dims[3] % v == 0 && a.lo[3] % v == 0 && (a.in_dims[3] == (1 << 30) || a.in_dims[3] % v == 0) &&
+    bool fits = a.dims[5] % v == 0 && a.lo[5] % v == 0 && (a.in_dims[5] == (1 << 30) || a.in_dims[5] % v == 0) &&
                 a.in_offset % v == 0 && a.out_offset % v == 0;
-    for (int d = 0; d < 3 && fits; d++) fits = a.in_str[d] % v == 0 && a.out_str[d] % v == 0;
+    for (int d = 0; d < 5 && fits; d++) fits = a.in_str[d] % v == 0 && a.out_str[d] % v == 0;
     if (!fits) continue;
-    a.dims[3] /= v;
-    a.lo[3] /= v;
-    if (a.in_dims[3] != (1 << 30)) a.in_dims[3] /= v;
-    for (int d = 0; d < 3; d++) {
+    a.dims[5] /= v;
+    a.lo[5] /= v;
+    if (a.in_dims[5] != (1 << 30)) a.in_dims[5] /= v;
+    for (int d = 0; d < 5; d++) {
       a.in_str[d] /= v;
       a.out_str[d] /= v;
     }
@@ -303,6 +311,33 @@ void widen_strided_copy(StridedCopyArgs& a) {
     a.elem_bytes = bytes;
     return;
   }
+}
+namespace {
+// one thread per byte of the W rows; rows are short (a few channels), so byte granularity keeps every type and alignment
+template <bool SCATTER>
+__global__ void __launch_bounds__(256) rows_by_index_kernel(const uint8_t* __restrict__ src, const int32_t* __restrict__ idx,
+                                                            uint8_t* __restrict__ out, int N, int K, int W, int row_bytes) {
+  const long long total = (long long)N * W * row_bytes;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % row_bytes);
+    const long long nw = i / row_bytes;
+    const int n = (int)(nw / W);
+    const int k = __ldg(idx + nw);
+    const bool inside = k >= 0 && k < K;
+    if (SCATTER) {
+      if (inside) out[((long long)n * K + k) * row_bytes + c] = src[i];
+    } else {
+      out[i] = inside ? src[((long long)n * K + k) * row_bytes + c] : (uint8_t)0;
+    }
+  }
+}
+}  // namespace
+
+void launch_gather_rows(const void* values, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream) {
+  rows_by_index_kernel<false><<<grid_for((long long)N * W * row_bytes), 256, 0, stream>>>((const uint8_t*)values, idx, (uint8_t*)out, N, K, W, row_bytes);
+}
+void launch_scatter_rows(const void* updates, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream) {
+  rows_by_index_kernel<true><<<grid_for((long long)N * W * row_bytes), 256, 0, stream>>>((const uint8_t*)updates, idx, (uint8_t*)out, N, K, W, row_bytes);
 }
 void launch_softmax(const void* x, void* out, long long rows, int cols, int dtype, cudaStream_t stream) {
   softmax_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(x, out, rows, cols, dtype);

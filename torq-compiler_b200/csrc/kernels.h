@@ -299,9 +299,9 @@ struct StridedCopyArgs {
   long long n;            // elements visited = product of dims
   int elem_bytes;         // bytes moved per index: 1, 2 or 4 (the element), or 8 / 16 after widen_strided_copy
   int pad_elem_bytes;     // the tensor's element size (pad_value is one such element)
-  int dims[4];            // extents of the index space (of the output region written)
-  int lo[4], in_dims[4];  // input coordinate = index - lo, valid inside [0, in_dims)
-  long long in_str[4], out_str[4], in_offset, out_offset;  // in elements
+  int dims[6];            // extents of the index space (of the output region written); slot 5 is the innermost, unused leading slots are 1
+  int lo[6], in_dims[6];  // input coordinate = index - lo, valid inside [0, in_dims)
+  long long in_str[6], out_str[6], in_offset, out_offset;  // in elements
   int pad_value;
 };
 void launch_strided_copy(const StridedCopyArgs& a, cudaStream_t stream);
@@ -316,6 +316,10 @@ struct ReduceArgs {
   int in_dtype, out_dtype;
 };
 void launch_reduce(const ReduceArgs& a, cudaStream_t stream);
+// tosa.gather / tosa.scatter rows of `row_bytes` bytes: gather out[n, w] = values[n, idx[n, w]]; scatter out[n, idx[n, w]] = updates[n, w]
+// (the caller has copied values to out first). Indices outside [0, K) give zero rows / are skipped.
+void launch_gather_rows(const void* values, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream);
+void launch_scatter_rows(const void* updates, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream);
 void launch_softmax(const void* x, void* out, long long rows, int cols, int dtype, cudaStream_t stream);
 void launch_table16(const int16_t* x, const int16_t* table, int32_t* out, long long n, cudaStream_t stream);
 

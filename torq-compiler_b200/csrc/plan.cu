@@ -1599,21 +1599,21 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: wants tensors of one element type (1, 2 or 4 bytes) and equal rank", i);
         const int r = (int)ti.rank;
         const int arg[4] = {op.i0, op.i1, op.i2, op.i3};
-        // strides (elements) of a dense tensor, dimensions right-aligned in 4 slots
-        auto dense = [&](const tb200_tensor_t& t, long long (&str)[4], int (&dims)[4]) {
-          for (int d = 0; d < 4; d++) { str[d] = 0; dims[d] = 1; }
+        // strides (elements) of a dense tensor, dimensions right-aligned in 6 slots
+        auto dense = [&](const tb200_tensor_t& t, long long (&str)[6], int (&dims)[6]) {
+          for (int d = 0; d < 6; d++) { str[d] = 0; dims[d] = 1; }
           long long s2 = 1;
-          for (int d = (int)t.rank - 1; d >= 0; d--) { str[4 - t.rank + d] = s2; dims[4 - t.rank + d] = t.shape[d]; s2 *= t.shape[d]; }
+          for (int d = (int)t.rank - 1; d >= 0; d--) { str[6 - t.rank + d] = s2; dims[6 - t.rank + d] = t.shape[d]; s2 *= t.shape[d]; }
         };
         std::vector<StridedCopyArgs> parts;
         StridedCopyArgs a{};
         a.elem_bytes = esz; a.pad_elem_bytes = esz; a.pad_value = op.pad_value;
-        long long istr[4], ostr[4];
-        int idims[4], odims[4];
+        long long istr[6], ostr[6];
+        int idims[6], odims[6];
         dense(ti, istr, idims);
         dense(to, ostr, odims);
-        for (int d = 0; d < 4; d++) { a.lo[d] = 0; a.in_dims[d] = 1 << 30; a.out_str[d] = ostr[d]; a.dims[d] = odims[d]; a.in_str[d] = 0; }
-        const int o = 4 - r;  // first used slot
+        for (int d = 0; d < 6; d++) { a.lo[d] = 0; a.in_dims[d] = 1 << 30; a.out_str[d] = ostr[d]; a.dims[d] = odims[d]; a.in_str[d] = 0; }
+        const int o = 6 - r;  // first used slot
         if (op.kind == TB200_OP_TRANSPOSE) {
           bool seen[4] = {false, false, false, false};
           for (int d = 0; d < r; d++) {
@@ -1648,15 +1648,15 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           for (int which = 0; which < 2; which++) {
             const auto& t = which ? t1 : ti;
             StridedCopyArgs c2 = a;
-            long long s1[4];
-            int d1[4];
+            long long s1[6];
+            int d1[6];
             dense(t, s1, d1);
-            for (int d = 0; d < 4; d++) { c2.in_str[d] = s1[d]; c2.dims[d] = d1[d]; }
+            for (int d = 0; d < 6; d++) { c2.in_str[d] = s1[d]; c2.dims[d] = d1[d]; }
             c2.out_offset = which ? (long long)ti.shape[axis] * ostr[o + axis] : 0;
             parts.push_back(c2);
           }
         }
-        for (auto& pt : parts) { pt.n = 1; for (int d = 0; d < 4; d++) pt.n *= pt.dims[d]; widen_strided_copy(pt); }
+        for (auto& pt : parts) { pt.n = 1; for (int d = 0; d < 6; d++) pt.n *= pt.dims[d]; widen_strided_copy(pt); }
         Loc l0 = loc(op.in0), l1 = concat ? loc(op.in1) : Loc{}, lo = loc(op.out0);
         step.kernel_name = op.kind == TB200_OP_TRANSPOSE ? "transpose" : op.kind == TB200_OP_SLICE ? "slice"
                            : op.kind == TB200_OP_PAD ? "pad" : "concat_axis";
@@ -1668,6 +1668,100 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             k.out = lo.resolve(c);
             launch_strided_copy(k, c.stream);
           }
+        };
+        break;
+      }
+      case TB200_OP_GATHER:
+      case TB200_OP_SCATTER: {
+        const bool sc = op.kind == TB200_OP_SCATTER;
+        if (!b.valid_id(op.in0) || !b.valid_id(op.in1) || !b.valid_id(op.out0) || (sc && !b.valid_id(op.in2)))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad tensor id", i);
+        const auto& tv = tensors[op.in0]; const auto& tix = tensors[op.in1]; const auto& to = tensors[op.out0];
+        if (tv.rank != 3 || tix.rank != 2 || tix.dtype != TB200_I32 || to.rank != 3 || to.dtype != tv.dtype || tix.shape[0] != tv.shape[0])
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: wants values [N, K, C], i32 indices [N, W] and a result of the values' type", i);
+        const int N = tv.shape[0], K = tv.shape[1], Cc = tv.shape[2], W = tix.shape[1];
+        const int esz = (int)bytes_of(op.in0) / (int)std::max<size_t>(1, b.numel(op.in0));
+        const int row_bytes = Cc * esz;
+        if (sc) {
+          const auto& tu = tensors[op.in2];
+          if (tu.rank != 3 || tu.dtype != tv.dtype || tu.shape[0] != N || tu.shape[1] != W || tu.shape[2] != Cc || to.shape[0] != N ||
+              to.shape[1] != K || to.shape[2] != Cc)
+            return b.fail(TB200_INVALID_ARGUMENT, "op %d: scatter wants updates [N, W, C] and a result shaped like the values", i);
+        } else if (to.shape[0] != N || to.shape[1] != W || to.shape[2] != Cc) {
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: gather result is not [N, W, C]", i);
+        }
+        Loc lv = loc(op.in0), li = loc(op.in1), lu = sc ? loc(op.in2) : Loc{}, lo = loc(op.out0);
+        const size_t value_bytes = bytes_of(op.in0);
+        step.kernel_name = sc ? "scatter" : "gather";
+        step.launches = sc ? 2 : 1;
+        step.launch = [=](const ExecContext& c) {
+          if (sc) {
+            cudaMemcpyAsync(lo.resolve(c), lv.resolve(c), value_bytes, cudaMemcpyDeviceToDevice, c.stream);
+            launch_scatter_rows(lu.resolve(c), (const int32_t*)li.resolve(c), lo.resolve(c), N, K, W, row_bytes, c.stream);
+          } else {
+            launch_gather_rows(lv.resolve(c), (const int32_t*)li.resolve(c), lo.resolve(c), N, K, W, row_bytes, c.stream);
+          }
+        };
+        break;
+      }
+      case TB200_OP_PERMUTE: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.out0) || tensors[op.in0].dtype != tensors[op.out0].dtype ||
+            b.numel(op.in0) != b.numel(op.out0))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: permute wants input and output of the same type and element count", i);
+        const int r = (op.i3 >> 24) & 15;
+        const int d6[6] = {op.i0 & 0xffff, (op.i0 >> 16) & 0xffff, op.i1 & 0xffff, (op.i1 >> 16) & 0xffff, op.i2 & 0xffff,
+                           (op.i2 >> 16) & 0xffff};
+        if (r < 1 || r > 6) return b.fail(TB200_INVALID_ARGUMENT, "op %d: permute rank %d outside 1..6", i, r);
+        long long in_str[6], total = 1;
+        for (int d = r - 1; d >= 0; d--) { in_str[d] = total; total *= d6[d]; }
+        bool seen[6] = {false, false, false, false, false, false};
+        long long odim[6], ostr_in[6];  // output dimensions in order, each with the input stride it walks
+        for (int d = 0; d < r; d++) {
+          const int pd = (op.i3 >> (4 * d)) & 15;
+          if (pd >= r || seen[pd] || d6[pd] < 1) return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad permutation or extent", i);
+          seen[pd] = true;
+          odim[d] = d6[pd];
+          ostr_in[d] = in_str[pd];
+        }
+        if ((size_t)total != b.numel(op.in0)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: permute view does not match the tensor", i);
+        // drop extents of 1, then merge neighbours that are also neighbours in the input
+        int m = 0;
+        for (int d = 0; d < r; d++) {
+          if (odim[d] == 1) continue;
+          if (m > 0 && ostr_in[m - 1] == ostr_in[d] * odim[d]) {
+            odim[m - 1] *= odim[d];
+            ostr_in[m - 1] = ostr_in[d];
+          } else {
+            odim[m] = odim[d];
+            ostr_in[m] = ostr_in[d];
+            m++;
+          }
+        }
+        if (m == 0) { odim[0] = 1; ostr_in[0] = 1; m = 1; }
+
+        StridedCopyArgs a{};
+        const int esz = (int)bytes_of(op.in0) / (int)std::max<size_t>(1, b.numel(op.in0));
+        if (esz != 1 && esz != 2 && esz != 4) return b.fail(TB200_INVALID_ARGUMENT, "op %d: permute wants 1-, 2- or 4-byte elements", i);
+        a.elem_bytes = esz; a.pad_elem_bytes = esz;
+        long long ostr = 1;
+        for (int d = 0; d < 6; d++) { a.dims[d] = 1; a.lo[d] = 0; a.in_dims[d] = 1 << 30; a.in_str[d] = 0; a.out_str[d] = 0; }
+        for (int d = m - 1; d >= 0; d--) {
+          const int slot = 6 - m + d;
+          if (odim[d] > INT32_MAX) return b.fail(TB200_UNIMPLEMENTED, "op %d: permute extent too large", i);
+          a.dims[slot] = (int)odim[d];
+          a.in_str[slot] = ostr_in[d];
+          a.out_str[slot] = ostr;
+          ostr *= odim[d];
+        }
+        a.n = total;
+        widen_strided_copy(a);
+        Loc lx = loc(op.in0), lo = loc(op.out0);
+        step.kernel_name = "transpose";
+        step.launch = [=](const ExecContext& c) {
+          StridedCopyArgs k = a;
+          k.in = lx.resolve(c);
+          k.out = lo.resolve(c);
+          launch_strided_copy(k, c.stream);
         };
         break;
       }

@@ -29,7 +29,7 @@ OP_KINDS = {
     "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
     "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
     "add_bf16": 38, "argmax": 39, "allreduce": 40, "act_bf16": 41, "gemv_q8b": 42,
-    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55, "conv2d_i16": 56,
+    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55, "conv2d_i16": 56, "permute": 57, "gather": 58, "scatter": 59,
 }
 
 EW_FN = {"cast": 0, "abs": 1, "negate": 2, "bitwise_not": 3, "logical_not": 4, "clz": 5, "clamp": 6, "ceil": 7, "floor": 8,
@@ -328,6 +328,33 @@ class Graph:
             raise ValueError("perm must be a permutation of the dimensions")
         p4 = perm + list(range(len(perm), 4))
         return self._emit("transpose", [x], tuple(x.shape[p] for p in perm), x.dtype, i0=p4[0], i1=p4[1], i2=p4[2], i3=p4[3])
+
+    def gather(self, values, indices):
+        """tosa.gather: values [N, K, C], indices [N, W] (i32) -> [N, W, C], out[n, w] = values[n, indices[n, w]]."""
+        if len(values.shape) != 3 or len(indices.shape) != 2 or indices.dtype != "i32" or indices.shape[0] != values.shape[0]:
+            raise ValueError("gather wants values [N, K, C] and i32 indices [N, W]")
+        return self._emit("gather", [values, indices], (values.shape[0], indices.shape[1], values.shape[2]), values.dtype)
+
+    def scatter(self, values, indices, updates):
+        """tosa.scatter: a copy of values [N, K, C] with rows indices[n, w] replaced by updates[n, w] ([N, W, C])."""
+        if len(values.shape) != 3 or len(indices.shape) != 2 or indices.dtype != "i32" or updates.dtype != values.dtype or \
+                tuple(updates.shape) != (values.shape[0], indices.shape[1], values.shape[2]):
+            raise ValueError("scatter wants values [N, K, C], i32 indices [N, W] and updates [N, W, C]")
+        return self._emit("scatter", [values, indices, updates], tuple(values.shape), values.dtype)
+
+    def permute(self, x, view_shape, perm, out_shape):
+        """Transpose of a view of up to six dimensions (x holds prod(view_shape) elements in any stored shape)."""
+        view = [int(d) for d in view_shape]
+        perm = [int(p) for p in perm]
+        r = len(view)
+        if r > 6 or sorted(perm) != list(range(r)) or any(d < 1 or d > 65535 for d in view):
+            raise ValueError("permute wants at most six dimensions of at most 65535 and a permutation of them")
+        if int(np.prod(view)) != int(np.prod(x.shape)) or int(np.prod(out_shape)) != int(np.prod(view)):
+            raise ValueError("permute: element counts differ")
+        d6 = view + [1] * (6 - r)
+        packed = sum(p << (4 * i) for i, p in enumerate(perm)) | (r << 24)
+        return self._emit("permute", [x], tuple(int(d) for d in out_shape), x.dtype, i0=d6[0] | d6[1] << 16,
+                          i1=d6[2] | d6[3] << 16, i2=d6[4] | d6[5] << 16, i3=packed)
 
     def slice(self, x, start, size):
         if any(s < 0 or s + n > d for s, n, d in zip(start, size, x.shape)):

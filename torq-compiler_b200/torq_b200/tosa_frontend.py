@@ -258,9 +258,12 @@ def build_graph(text: str) -> Graph:
         elif n == "transpose":
             x = op.operands[0]
             perm = [int(v) for v in op.attrs["perms"]]
-            if len(x.shape) > 4:
+            if len(x.shape) > 6:
                 raise NotImplementedError(f"rank {len(x.shape)} transpose")
-            env[res.name] = g.transpose(get(x), perm)
+            if len(x.shape) > 4:  # the stored tensor is the collapsed view of the same elements
+                env[res.name] = g.permute(get(x), x.shape, perm, oshape)
+            else:
+                env[res.name] = g.transpose(get(x), perm)
         elif n in ("slice", "extract_slice"):
             x = op.operands[0]
             if len(x.shape) > 4:
@@ -291,6 +294,16 @@ def build_graph(text: str) -> Graph:
             fn = {"reduce_sum": "sum", "reduce_max": "max", "reduce_min": "min", "argmax": "argmax"}[n]
             t = g.reduce(fn, get(x), int(op.attrs["axis"]), keep_axis=n != "argmax", out_dtype=odt)
             env[res.name] = t if t.shape == oshape else g.reshape(t, oshape)
+        elif n == "gather":
+            vals_t, idx = op.operands
+            if len(vals_t.shape) != 3 or idx.dtype != "i32":
+                raise NotImplementedError("tosa.gather other than [N, K, C] values with i32 [N, W] indices")
+            env[res.name] = g.gather(get(vals_t), get(idx))
+        elif n == "scatter":
+            vals_t, idx, upd = op.operands
+            if len(vals_t.shape) != 3 or idx.dtype != "i32":
+                raise NotImplementedError("tosa.scatter other than [N, K, C] values with i32 [N, W] indices")
+            env[res.name] = g.scatter(get(vals_t), get(idx), get(upd))
         elif n == "identity":
             env[res.name] = g.reshape(get(op.operands[0]), oshape)
         elif n == "reshape":
@@ -436,7 +449,7 @@ def build_graph(text: str) -> Graph:
             env[op.result.name] = g.avg_pool2d(get(x), tuple(op.attrs["kernel"]), tuple(op.attrs["stride"]),
                                                tuple(op.attrs["pad"]), _scalar(izp), _scalar(ozp))
         elif n == "reshape":
-            env[op.result.name] = g.reshape(get(op.operands[0]), op.result.shape)
+            env[op.result.name] = g.reshape(get(op.operands[0]), _collapse(op.result.shape))
         elif n == "resize":
             x = op.operands[0]
             if op.attrs.get("mode") != "NEAREST_NEIGHBOR" or op.result.shape[1] != 2 * x.shape[1] or op.result.shape[2] != 2 * x.shape[2]:
@@ -466,7 +479,7 @@ def build_graph(text: str) -> Graph:
                                             double_round=False)
         elif n == "identity":
             x = op.operands[0]
-            env[op.result.name] = g.reshape(get(x), x.shape)
+            env[op.result.name] = g.reshape(get(x), _collapse(x.shape))
         else:
             raise NotImplementedError(f"tosa.{n}")
 
