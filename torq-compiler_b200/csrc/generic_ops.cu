@@ -1,6 +1,7 @@
 // Tensor ops outside the layer set (TB200_OP_EW, the generic tosa.rescale, TRANSPOSE / SLICE / PAD /
-// CONCAT_AXIS, REDUCE): what the reference's op fixtures exercise around the layers
-// (tests/testdata/tosa_ops: cast-*, Elementwise_*, rescale-*, transpose-*, pad_*, reduce-*, argmax-*).
+// CONCAT_AXIS / PERMUTE, REDUCE, TABLE16, SOFTMAX, GATHER / SCATTER): what the reference's op fixtures exercise
+// around the layers (tests/testdata/tosa_ops: cast-*, Elementwise_*, rescale-*, transpose-*, d2s_*, pad_*, reduce-*,
+// argmax-*, gather*, scatter*, mbv2-softmax-i8).
 // All are bandwidth-bound index arithmetic on dense row-major tensors of rank <= 4 with element types
 // i8 / i16 / i32 / f32 / bf16. Integers are computed in int32 with wrap-around and truncated to the result
 // type; floats in fp32, rounded once to nearest even; float -> int casts round to nearest even and saturate.
