@@ -124,6 +124,8 @@ enum tb200_op_kind {
                                * (doc/user-manual/ops.md: Gather i8 / i16 / i32). An index outside [0, K) reads as zero. */
   TB200_OP_SCATTER = 59,      /* tosa.scatter: a copy of in0 values [N, K, C] in which row indices[n, w] (in1, i32 [N, W]) is replaced by in2
                                * updates[n, w, :]; indices of one n are distinct (TOSA), an index outside [0, K) is skipped */
+  TB200_OP_MATMUL_F = 60,     /* tosa.matmul on floats (doc/user-manual/ops.md: MatMul bf16 x bf16 -> f32): in0 [M, K] x in1 [K, N], bf16 or f32
+                               * operands, products and sums in fp32, each rounded, added in index order of k; result f32 or bf16 */
   TB200_OP_ALLREDUCE = 40,    /* sum of the fp32 partial results of the i0 GPUs of a tensor-parallel group
                                * (this one is rank i1), rounded to bf16; only inside the fused decode step */
 };
@@ -132,6 +134,9 @@ enum tb200_ew_fn {
   /* unary */
   TB200_EW_CAST = 0, TB200_EW_ABS = 1, TB200_EW_NEGATE = 2, TB200_EW_BITWISE_NOT = 3, TB200_EW_LOGICAL_NOT = 4,
   TB200_EW_CLZ = 5, TB200_EW_CLAMP = 6, TB200_EW_CEIL = 7, TB200_EW_FLOOR = 8,
+  /* unary, floats only, evaluated in fp32 (tolerance class: the function's last bits differ between math libraries) */
+  TB200_EW_EXP = 9, TB200_EW_LOG = 10, TB200_EW_RECIPROCAL = 11, TB200_EW_RSQRT = 12, TB200_EW_TANH = 13,
+  TB200_EW_SIGMOID = 14, TB200_EW_ERF = 15,
   /* binary */
   TB200_EW_ADD = 16, TB200_EW_SUB = 17, TB200_EW_MUL = 18, TB200_EW_MAX = 19, TB200_EW_MIN = 20,
   TB200_EW_AND = 21, TB200_EW_OR = 22, TB200_EW_XOR = 23, TB200_EW_LSL = 24, TB200_EW_ASR = 25,

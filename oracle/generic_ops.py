@@ -16,9 +16,19 @@ import numpy as np
 
 INT_BITS = {"i8": 8, "i16": 16, "i32": 32}
 EW_NAMES = {0: "cast", 1: "abs", 2: "negate", 3: "bitwise_not", 4: "logical_not", 5: "clz", 6: "clamp", 7: "ceil", 8: "floor",
+            9: "exp", 10: "log", 11: "reciprocal", 12: "rsqrt", 13: "tanh", 14: "sigmoid", 15: "erf",
             16: "add", 17: "sub", 18: "mul", 19: "maximum", 20: "minimum", 21: "bitwise_and", 22: "bitwise_or",
             23: "bitwise_xor", 24: "logical_left_shift", 25: "arithmetic_right_shift", 26: "equal", 27: "greater",
             28: "greater_equal", 29: "logical_and", 30: "logical_or", 31: "logical_xor"}
+
+
+def _erf32(x):
+    import math
+    return np.vectorize(math.erf, otypes=[np.float64])(x.astype(np.float64))
+
+
+FLOAT_FUNCTIONS = {"exp": np.exp, "log": np.log, "reciprocal": lambda v: np.float32(1.0) / v, "rsqrt": lambda v: np.float32(1.0) / np.sqrt(v),
+                   "tanh": np.tanh, "sigmoid": lambda v: np.float32(1.0) / (np.float32(1.0) + np.exp(-v)), "erf": _erf32}
 
 
 def bf16_to_f32(u16: np.ndarray) -> np.ndarray:
@@ -106,6 +116,9 @@ def ew(fn: int, a: np.ndarray, a_dtype: str, b, b_dtype, out_dtype: str, *, arg=
         r = np.ceil(x)
     elif name == "floor":
         r = np.floor(x)
+    elif name in FLOAT_FUNCTIONS:  # fp32 in and out; tolerance class (the last bits are the math library's)
+        with np.errstate(all="ignore"):
+            r = FLOAT_FUNCTIONS[name](x.astype(np.float32)).astype(np.float32)
     elif name == "add":
         r = x + y
     elif name == "sub":
@@ -232,6 +245,18 @@ def conv2d_i16(x: np.ndarray, w: np.ndarray, bias: np.ndarray, mult, shift, *, s
     s = np.asarray(shift, np.int64).reshape(-1)
     r = (acc * m + (np.int64(1) << (s - 1))) >> s
     return np.clip(r + out_zp, clamp[0], clamp[1]).astype(np.int16)
+
+
+def matmul_f(a: np.ndarray, b: np.ndarray, dtype: str, out_dtype: str) -> np.ndarray:
+    """tosa.matmul on floats: fp32 products, each rounded, added one k at a time in fp32 (index order), then stored as
+    f32 or rounded once to bf16."""
+    x, _ = _load(a, dtype)
+    y, _ = _load(b, dtype)
+    x, y = x.astype(np.float32), y.astype(np.float32)
+    acc = np.zeros((x.shape[0], y.shape[1]), np.float32)
+    for k in range(x.shape[1]):
+        acc = (acc + (x[:, k, None] * y[None, k, :]).astype(np.float32)).astype(np.float32)
+    return _store(acc, True, out_dtype)
 
 
 def gather(values: np.ndarray, indices: np.ndarray) -> np.ndarray:

@@ -246,7 +246,13 @@ def ew_elementwise(fn_name, a, a_dtype, b, b_dtype, out_dtype, out_shape, *, arg
                  "floor": lambda: math.copysign(float(math.floor(x)), x) if math.floor(x) == 0 else float(math.floor(x)), "clamp": lambda: min(max(x, _f32(fclamp[0])), _f32(fclamp[1])),
                  "add": lambda: _f32(x + y), "sub": lambda: _f32(x - y), "mul": lambda: _f32(x * y), "maximum": lambda: max(x, y),
                  "minimum": lambda: min(x, y), "equal": lambda: int(x == y), "greater": lambda: int(x > y),
-                 "greater_equal": lambda: int(x >= y)}[fn_name]()
+                 "greater_equal": lambda: int(x >= y),
+                 # the float functions through Python's double-precision math, rounded to fp32 (tolerance class)
+                 "exp": lambda: _f32(math.exp(min(x, 700.0))), "log": lambda: _f32(math.log(x)) if x > 0 else (float("-inf") if x == 0 else float("nan")),
+                 "reciprocal": lambda: _f32(1.0 / x) if x != 0 else math.copysign(float("inf"), x),
+                 "rsqrt": lambda: _f32(1.0 / math.sqrt(x)) if x > 0 else (float("inf") if x == 0 else float("nan")),
+                 "tanh": lambda: _f32(math.tanh(x)), "sigmoid": lambda: _f32(1.0 / (1.0 + math.exp(-x))) if x > -700 else 0.0,
+                 "erf": lambda: _f32(math.erf(x))}[fn_name]()
             if fn_name in ("equal", "greater", "greater_equal"):
                 out.append(r)
             elif fn_name == "cast" and bool_result:

@@ -20,7 +20,7 @@ for p in (ROOT, os.path.join(ROOT, "torq-compiler_b200"), os.path.join(ROOT, "te
     sys.path.insert(0, p)
 
 from oracle import oracle_np as onp  # noqa: E402
-from oracle_exec import run_graph  # noqa: E402
+from oracle_exec import outputs_match, run_graph, uses_float_functions  # noqa: E402
 from torq_b200 import tosa_frontend  # noqa: E402
 from torq_b200.oplist import NP_DTYPE  # noqa: E402
 
@@ -107,6 +107,9 @@ GENERIC_CASES = [
     "tosa_ops/sub-56x56x256xi8", "tosa_ops/sub-bf16", "tosa_ops/sub-i32",
     "tosa_ops/sub-rescale-scalar-bis", "tosa_ops/sub-rescale-scalar", "tosa_ops/transpose-5dim",
     "tosa_ops/transpose-5dim_1", "tosa_ops/transpose-5dim_2", "tosa_ops/transpose-5dim_3",
+    # float matmul (fp32 products and sums in index order: bit-exact) and the float functions (tolerance class)
+    "tosa_ops/disable-matmul-bf16", "tosa_ops/disable-matmul-in-bf16-out-bf16_207x207", "tosa_ops/matmul-fp32",
+    "tosa_ops/matmul-in-bf16-out-fp32_207x207", "tosa_ops/matmul-in-bf16-out-fp32_2x2", "tosa_ops/softmax-1x1000xi8",
     "tosa_ops/mul-1hw1-in-int8-out-int32", "tosa_ops/mul-1hwc-in-int16-out-int32",
     "tosa_ops/mul-1hwc-in-int8-out-int32-1", "tosa_ops/mul-1hwc-in-int8-out-int32-2dim",
     "tosa_ops/mul-1hwc-in-int8-out-int32-3dim", "tosa_ops/mul-1hwc-in-int8-out-int32", "tosa_ops/mul-bf16",
@@ -165,6 +168,20 @@ def numpy_replay(g, inputs):
             y = onp.ew_elementwise(EW_NAMES[a["i0"]], x, op.inputs[0].dtype, second, op.inputs[1].dtype if second is not None else None,
                                    op.outputs[0].dtype, op.outputs[0].shape, arg=a["i1"], in_zp=a["in0_zp"], out_zp=a["out_zp"],
                                    clamp=(a["clamp_min"], a["clamp_max"]), fclamp=(a["f0"], a["f1"]), bool_result=bool(a.get("flags", 0) & 4))
+        elif k == "matmul_f":  # one output at a time, numpy float32 scalars: every product and every sum rounded
+            bmat = vals[op.inputs[1].id]
+            to_f = (lambda v: (v.astype(np.uint32) << 16).view(np.float32)) if op.inputs[0].dtype == "bf16" else (lambda v: v.astype(np.float32))
+            xa, xb = to_f(x), to_f(bmat)
+            acc = np.zeros((xa.shape[0], xb.shape[1]), np.float32)
+            for m_ in range(xa.shape[0]):
+                for n_ in range(xb.shape[1]):
+                    s_ = np.float32(0)
+                    col = xb[:, n_]
+                    row = xa[m_]
+                    for k_ in range(row.size):
+                        s_ = np.float32(s_ + np.float32(row[k_] * col[k_]))
+                    acc[m_, n_] = s_
+            y = tosa_frontend._to_bf16_bits(acc) if op.outputs[0].dtype == "bf16" else acc
         elif k == "gather":
             idx = vals[op.inputs[1].id]
             y = np.empty(op.outputs[0].shape, x.dtype)
@@ -211,7 +228,15 @@ def numpy_replay(g, inputs):
             moved = np.moveaxis(x, a["i1"], -1).reshape(-1, x.shape[a["i1"]])
             if op.inputs[0].dtype == "bf16":
                 moved = (moved.astype(np.uint32) << 16).view(np.float32)
-            if a["i0"] == 0:
+            if a["i0"] in (0, 4) and moved.dtype == np.float32:  # one element at a time in fp32, every sum rounded
+                sums = []
+                for row in moved:
+                    s_ = np.float32(0)
+                    for v in row:
+                        s_ = np.float32(s_ + v)
+                    sums.append(np.float32(s_ / np.float32(row.size)) if a["i0"] == 4 else s_)
+                y = np.array(sums, np.float32)
+            elif a["i0"] == 0:
                 y = np.array([int(sum(int(v) for v in row)) & 0xFFFFFFFF for row in moved], np.uint32).view(np.int32)
             elif a["i0"] == 3:
                 y = np.array([int(np.argmax(row)) for row in moved], np.int32)
@@ -265,8 +290,9 @@ def main(ref_root):
             inputs.append(np.ascontiguousarray(x).reshape(t.shape))
         want_c = run_graph(g, inputs)
         want_np = numpy_replay(g, inputs)
-        for a, b in zip(want_c, want_np):
-            assert a.shape == b.shape and (a == b).all(), case
+        tolerant = uses_float_functions(g)
+        for a, b, t in zip(want_c, want_np, g.outputs):
+            assert outputs_match(a, b, tolerant, t.dtype), case
         name = "tosa_" + os.path.basename(case).replace("-", "_")
         with open(os.path.join(out_dir, name + ".b200ops"), "wb") as f:
             f.write(g.serialize())

@@ -73,6 +73,8 @@ def run_graph(graph, inputs, keep_all=False):
             y = np.broadcast_to(y, op.outputs[0].shape) if y.shape != tuple(op.outputs[0].shape) else y
         elif k == "transpose":
             y = np.transpose(x, [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim])
+        elif k == "matmul_f":
+            y = gops.matmul_f(x, vals[op.inputs[1].id], op.inputs[0].dtype, op.outputs[0].dtype)
         elif k == "gather":
             y = gops.gather(x, vals[op.inputs[1].id])
         elif k == "scatter":
@@ -109,3 +111,24 @@ def run_graph(graph, inputs, keep_all=False):
         vals[op.outputs[0].id] = np.ascontiguousarray(y)
     outs = [vals[t.id] for t in graph.outputs]
     return (outs, vals) if keep_all else outs
+
+
+def uses_float_functions(graph) -> bool:
+    """Graphs with exp / log / reciprocal / ... or softmax are tolerance-class: the last bits of those functions belong to
+    the math library (the reference's own tests compare engines at +-1 LSB, python/torq/testing/comparison.py:42-49)."""
+    return any((op.kind == "ew" and 9 <= op.attrs.get("i0", 0) <= 15) or op.kind == "softmax" for op in graph.ops)
+
+
+def outputs_match(got, want, tolerant: bool, dtype: str = "") -> bool:
+    """Bit-exact, or for tolerance-class graphs: integers within 1, bf16 within 2 ulp of the value, f32 within 1e-5 relative."""
+    if got.shape != want.shape:
+        return False
+    if not tolerant:
+        return bool((got.view(np.uint8) == want.view(np.uint8)).all()) if got.dtype == want.dtype else False
+    if dtype == "bf16":
+        a = (got.astype(np.uint32) << 16).view(np.float32)
+        b = (want.astype(np.uint32) << 16).view(np.float32)
+        return bool(np.all(np.abs(a - b) <= 2.0 ** -7 * np.maximum(np.abs(b), 1e-30)))
+    if got.dtype.kind == "f":
+        return bool(np.all(np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), 1e-30) + 1e-30))
+    return bool(np.all(np.abs(got.astype(np.int64) - want.astype(np.int64)) <= 1))

@@ -246,3 +246,43 @@ def test_permute_of_five_and_six_dimensions(device, view, perm):
     out_shape = (int(np.prod([view[p] for p in perm[:-1]])), view[perm[-1]])
     g.output(g.permute(g.input(x.shape), view, perm, out_shape))
     _same(device, g, [x])
+
+
+@pytest.mark.parametrize("fn", ["exp", "log", "reciprocal", "rsqrt", "tanh", "sigmoid", "erf"])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_float_functions_against_torch(device, fn, dtype):
+    """Tolerance class: the function's last bits belong to the math library. f32 within 4 ulp-ish (4e-6 relative, 1e-7
+    absolute near zero), bf16 within one ulp of the fp32 torch value rounded."""
+    rng = np.random.default_rng(3)
+    v = rng.uniform(0.05, 8.0, (3, 1001)).astype(np.float32) if fn in ("log", "rsqrt", "reciprocal") else \
+        rng.uniform(-6.0, 6.0, (3, 1001)).astype(np.float32)
+    x = to_bf16(v) if dtype == "bf16" else v
+    g = Graph()
+    g.output(g.ew(fn, g.input(x.shape, dtype)))
+    got = run_graph_gpu(device, g, [x])[0]
+    t = torch.from_numpy(from_bf16(x) if dtype == "bf16" else x)
+    ref = {"exp": torch.exp, "log": torch.log, "reciprocal": torch.reciprocal, "rsqrt": torch.rsqrt, "tanh": torch.tanh,
+           "sigmoid": torch.sigmoid, "erf": torch.erf}[fn](t).numpy()
+    if dtype == "bf16":
+        assert np.all(np.abs(from_bf16(got) - ref) <= 2.0 ** -7 * np.abs(ref) + 1e-30)
+    else:
+        assert np.all(np.abs(got - ref) <= 4e-6 * np.abs(ref) + 1e-7)
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 128, 256), (207, 36, 207), (2, 2, 2), (33, 70, 5)])
+@pytest.mark.parametrize("dtype,out_dtype", [("bf16", "f32"), ("bf16", "bf16"), ("f32", "f32")])
+def test_float_matmul(device, M, K, N, dtype, out_dtype):
+    """fp32 products and sums, each rounded, in index order of k: bit-exact against the oracle, close to torch."""
+    rng = np.random.default_rng(M + N)
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    b = rng.normal(0, 1, (K, N)).astype(np.float32)
+    if dtype == "bf16":
+        a, b = to_bf16(a), to_bf16(b)
+    g = Graph()
+    g.output(g.matmul_f(g.input(a.shape, dtype), g.input(b.shape, dtype), out_dtype))
+    got = _same(device, g, [a, b])[0]
+    fa, fb = (from_bf16(a), from_bf16(b)) if dtype == "bf16" else (a, b)
+    ref = (torch.from_numpy(fa).double() @ torch.from_numpy(fb).double()).numpy()
+    gf = from_bf16(got) if out_dtype == "bf16" else got
+    tol = 2.0 ** -7 if out_dtype == "bf16" else 1e-5
+    assert np.all(np.abs(gf - ref) <= tol * np.abs(ref) + 1e-4 * np.sqrt(K))

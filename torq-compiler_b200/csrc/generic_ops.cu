@@ -85,6 +85,13 @@ __global__ void __launch_bounds__(256) ew_kernel(EwArgs a) {
         case TB200_EW_CLAMP: r = fminf(fmaxf(x, a.fmin), a.fmax); break;
         case TB200_EW_CEIL: r = ceilf(x); break;
         case TB200_EW_FLOOR: r = floorf(x); break;
+        case TB200_EW_EXP: r = expf(x); break;
+        case TB200_EW_LOG: r = logf(x); break;
+        case TB200_EW_RECIPROCAL: r = 1.0f / x; break;
+        case TB200_EW_RSQRT: r = 1.0f / sqrtf(x); break;
+        case TB200_EW_TANH: r = tanhf(x); break;
+        case TB200_EW_SIGMOID: r = 1.0f / (1.0f + expf(-x)); break;
+        case TB200_EW_ERF: r = erff(x); break;
         case TB200_EW_ADD: r = x + y; break;
         case TB200_EW_SUB: r = x - y; break;
         case TB200_EW_MUL: r = x * y; break;
@@ -333,6 +340,24 @@ __global__ void __launch_bounds__(256) rows_by_index_kernel(const uint8_t* __res
   }
 }
 }  // namespace
+
+namespace {
+// tosa.matmul on floats: one thread per output, products and sums rounded separately (no fused multiply-add), k in order
+__global__ void __launch_bounds__(256) matmul_f_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
+                                                       int M, int K, int N, int in_dtype, int out_dtype) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)M * N) return;
+  const int n = (int)(idx % N), m = (int)(idx / N);
+  float acc = 0.f;
+  for (int k = 0; k < K; k++)
+    acc = __fadd_rn(acc, __fmul_rn(load_float(a, in_dtype, (long long)m * K + k), load_float(b, in_dtype, (long long)k * N + n)));
+  store_float(out, out_dtype, idx, acc);
+}
+}  // namespace
+
+void launch_matmul_f(const void* a, const void* b, void* out, int M, int K, int N, int in_dtype, int out_dtype, cudaStream_t stream) {
+  matmul_f_kernel<<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(a, b, out, M, K, N, in_dtype, out_dtype);
+}
 
 void launch_gather_rows(const void* values, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream) {
   rows_by_index_kernel<false><<<grid_for((long long)N * W * row_bytes), 256, 0, stream>>>((const uint8_t*)values, idx, (uint8_t*)out, N, K, W, row_bytes);

@@ -320,6 +320,7 @@ void launch_reduce(const ReduceArgs& a, cudaStream_t stream);
 // (the caller has copied values to out first). Indices outside [0, K) give zero rows / are skipped.
 void launch_gather_rows(const void* values, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream);
 void launch_scatter_rows(const void* updates, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream);
+void launch_matmul_f(const void* a, const void* b, void* out, int M, int K, int N, int in_dtype, int out_dtype, cudaStream_t stream);
 void launch_softmax(const void* x, void* out, long long rows, int cols, int dtype, cudaStream_t stream);
 void launch_table16(const int16_t* x, const int16_t* table, int32_t* out, long long n, cudaStream_t stream);
 

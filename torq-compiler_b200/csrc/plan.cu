@@ -1559,6 +1559,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             (tb && tb->rank != to.rank))
           return b.fail(TB200_INVALID_ARGUMENT, "op %d: elementwise op wants i8/i16/i32/f32/bf16 tensors of equal rank", i);
         EwArgs a{};
+        if (op.i0 >= TB200_EW_EXP && op.i0 <= TB200_EW_ERF &&
+            (tensors[op.in0].dtype != TB200_F32 && tensors[op.in0].dtype != TB200_BF16))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: exp / log / reciprocal / rsqrt / tanh / sigmoid / erf want a float tensor", i);
         a.n = (long long)b.numel(op.out0); a.fn = op.i0; a.arg = op.i1;
         a.a_dtype = ta.dtype; a.b_dtype = tb ? tb->dtype : ta.dtype; a.out_dtype = to.dtype;
         a.in_zp = op.in0_zp; a.out_zp = op.out_zp; a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
@@ -1669,6 +1672,19 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             launch_strided_copy(k, c.stream);
           }
         };
+        break;
+      }
+      case TB200_OP_MATMUL_F: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.in1) || !b.valid_id(op.out0)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad tensor id", i);
+        const auto& ta = tensors[op.in0]; const auto& tb = tensors[op.in1]; const auto& to = tensors[op.out0];
+        const bool in_ok = ta.dtype == TB200_BF16 || ta.dtype == TB200_F32, out_ok = to.dtype == TB200_BF16 || to.dtype == TB200_F32;
+        if (!in_ok || !out_ok || tb.dtype != ta.dtype || ta.rank != 2 || tb.rank != 2 || to.rank != 2 || tb.shape[0] != ta.shape[1] ||
+            to.shape[0] != ta.shape[0] || to.shape[1] != tb.shape[1])
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: matmul_f wants [M, K] x [K, N] of bf16 or f32 -> [M, N] of f32 or bf16", i);
+        const int M = ta.shape[0], K = ta.shape[1], N = tb.shape[1], idt = (int)ta.dtype, odt = (int)to.dtype;
+        Loc la = loc(op.in0), lb = loc(op.in1), lo = loc(op.out0);
+        step.kernel_name = "matmul_f";
+        step.launch = [=](const ExecContext& c) { launch_matmul_f(la.resolve(c), lb.resolve(c), lo.resolve(c), M, K, N, idt, odt, c.stream); };
         break;
       }
       case TB200_OP_GATHER:

@@ -29,10 +29,11 @@ OP_KINDS = {
     "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
     "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
     "add_bf16": 38, "argmax": 39, "allreduce": 40, "act_bf16": 41, "gemv_q8b": 42,
-    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55, "conv2d_i16": 56, "permute": 57, "gather": 58, "scatter": 59,
+    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55, "conv2d_i16": 56, "permute": 57, "gather": 58, "scatter": 59, "matmul_f": 60,
 }
 
 EW_FN = {"cast": 0, "abs": 1, "negate": 2, "bitwise_not": 3, "logical_not": 4, "clz": 5, "clamp": 6, "ceil": 7, "floor": 8,
+         "exp": 9, "log": 10, "reciprocal": 11, "rsqrt": 12, "tanh": 13, "sigmoid": 14, "erf": 15,
          "add": 16, "sub": 17, "mul": 18, "maximum": 19, "minimum": 20, "bitwise_and": 21, "bitwise_or": 22,
          "bitwise_xor": 23, "logical_left_shift": 24, "arithmetic_right_shift": 25, "equal": 26, "greater": 27,
          "greater_equal": 28, "logical_and": 29, "logical_or": 30, "logical_xor": 31}
@@ -328,6 +329,13 @@ class Graph:
             raise ValueError("perm must be a permutation of the dimensions")
         p4 = perm + list(range(len(perm), 4))
         return self._emit("transpose", [x], tuple(x.shape[p] for p in perm), x.dtype, i0=p4[0], i1=p4[1], i2=p4[2], i3=p4[3])
+
+    def matmul_f(self, a, b, out_dtype="f32"):
+        """tosa.matmul on bf16 / f32 tensors: a [M, K] x b [K, N] -> f32 or bf16, fp32 products and sums in index order of k."""
+        if len(a.shape) != 2 or len(b.shape) != 2 or a.shape[1] != b.shape[0] or a.dtype not in ("bf16", "f32") or \
+                b.dtype != a.dtype or out_dtype not in ("bf16", "f32"):
+            raise ValueError("matmul_f wants [M, K] x [K, N] of bf16 or f32")
+        return self._emit("matmul_f", [a, b], (a.shape[0], b.shape[1]), out_dtype)
 
     def gather(self, values, indices):
         """tosa.gather: values [N, K, C], indices [N, W] (i32) -> [N, W, C], out[n, w] = values[n, indices[n, w]]."""

@@ -231,6 +231,19 @@ def build_graph(text: str) -> Graph:
             env[res.name] = g.rescale(x, mult, shift, input_zp=izp, out_zp=ozp, double_round=p["double_round"], out_dtype=odt,
                                       input_unsigned=bool(op.attrs.get("input_unsigned", False)),
                                       output_unsigned=bool(op.attrs.get("output_unsigned", False)))
+        elif n in ("exp", "log", "reciprocal", "rsqrt", "tanh", "sigmoid", "erf"):
+            if op.operands[0].dtype not in ("f32", "bf16"):
+                raise NotImplementedError(f"tosa.{n} on {op.operands[0].dtype}")
+            env[res.name] = g.ew(n, get(op.operands[0]), out_dtype=odt)
+        elif n == "matmul":
+            a, b = op.operands[0], op.operands[1]
+            if a.dtype not in ("bf16", "f32") or b.dtype != a.dtype or res.dtype not in ("bf16", "f32") or len(a.shape) != 3 or a.shape[0] != 1:
+                raise NotImplementedError("tosa.matmul on these types")
+            zps = [np.asarray(v.const).reshape(-1) for v in op.operands[2:4] if v.const is not None]
+            if any(z.view(np.uint16 if a.dtype == "bf16" else np.uint32).any() for z in zps):
+                raise NotImplementedError("float tosa.matmul with a zero point")
+            y = g.matmul_f(g.reshape(get(a), a.shape[1:]), g.reshape(get(b), b.shape[1:]), out_dtype=odt)
+            env[res.name] = g.reshape(y, oshape)
         elif n in ("abs", "bitwise_not", "logical_not", "clz", "ceil", "floor", "cast"):
             env[res.name] = g.ew(n, get(op.operands[0]), out_dtype=odt, bool_result=res.dtype == "i1" and n == "cast")
         elif n == "negate":
