@@ -107,6 +107,7 @@ GENERIC_CASES = [
     "tosa_ops/sub-56x56x256xi8", "tosa_ops/sub-bf16", "tosa_ops/sub-i32",
     "tosa_ops/sub-rescale-scalar-bis", "tosa_ops/sub-rescale-scalar", "tosa_ops/transpose-5dim",
     "tosa_ops/transpose-5dim_1", "tosa_ops/transpose-5dim_2", "tosa_ops/transpose-5dim_3",
+    "tosa_ops/add-scalar", "tosa_ops/concat-b", "tosa_ops/sub-rescale-tensor-int8",
     # float matmul (fp32 products and sums in index order: bit-exact) and the float functions (tolerance class)
     "tosa_ops/disable-matmul-bf16", "tosa_ops/disable-matmul-in-bf16-out-bf16_207x207", "tosa_ops/matmul-fp32",
     "tosa_ops/matmul-in-bf16-out-fp32_207x207", "tosa_ops/matmul-in-bf16-out-fp32_2x2", "tosa_ops/softmax-1x1000xi8",

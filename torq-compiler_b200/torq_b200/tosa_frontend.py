@@ -185,6 +185,8 @@ def _collapse(shape) -> tuple:
     """Tensors of the op list have at most four dimensions: the leading dimensions of a longer shape are merged
     (valid for the elementwise ops, the only ones the front end lets through with such shapes)."""
     shape = tuple(int(d) for d in shape)
+    if len(shape) == 0:
+        return (1,)  # a scalar tensor is one element
     if len(shape) <= 4:
         return shape
     return (int(np.prod(shape[:-3])),) + shape[-3:]
@@ -500,12 +502,18 @@ def build_graph(text: str) -> Graph:
         if id(op) in done:
             continue
         saved = set(done)
+        mark = (len(g.ops), len(g.tensors), set(env))
         try:
             fused(op)
-        except NotImplementedError:
+        except (NotImplementedError, ValueError):
+            # not one of the fused layer forms: undo whatever the attempt emitted and read the op on its own
             done.clear()
             done.update(saved)
             deferred.pop(op.result.name, None)
+            del g.ops[mark[0]:]
+            del g.tensors[mark[1]:]
+            for name in set(env) - mark[2]:
+                del env[name]
             generic(op)
     for v in returned:
         g.output(get(v))
