@@ -168,6 +168,34 @@ def test_fully_connected(device, M, K, N, azp):
     _check(device, g, [a])
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 16, 8), (2, 1280, 1000), (3, 4096, 1031), (4, 12288, 520), (4, 64, 4096)])
+@pytest.mark.parametrize("double_round", [True, False])
+@pytest.mark.parametrize("with_table", [False, True])
+def test_fully_connected_few_rows(device, M, K, N, double_round, with_table):
+    """At most four rows take the weight-streaming kernel (one warp per output channel): every row count, the largest K
+    it accepts, N not a multiple of the 8 channels of a block, both roundings, a clamp inside int8, shifts below 32 on
+    some channels, and a table behind it."""
+    rng = np.random.default_rng(M * 7 + K)
+    a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    bias = np.round(rng.normal(0, 1000, N)).astype(np.int32)
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, N) * 40.0 / (np.sqrt(K) * 74 * 74))
+    if K == 1280:  # low shifts: the general 64-bit form of the rescale
+        m, s = quantize_multipliers(rng.uniform(0.5, 1.5, N) * 40.0 / (np.sqrt(K) * 74 * 74))
+        m = (m >> 8).astype(np.int32); s = (s - 8).astype(np.int32)
+    g = Graph()
+    y = g.fully_connected(g.input((M, K)), w, bias, m, s, input_zp=5, out_zp=-3, clamp=(-100, 90),
+                          double_round=double_round)
+    if with_table:
+        y = g.table(y, rng.integers(-128, 128, 256, dtype=np.int8))
+    g.output(y)
+    _check(device, g, [a])
+    from torq_b200.runtime import Executable
+    ex = Executable(device, g.serialize())
+    assert ex.op_kernels()[0] == "fc_rows_dp4a", ex.op_kernels()
+    ex.destroy()
+
+
 @pytest.mark.parametrize("kn", [512, 1024, 4096, 8192])
 @pytest.mark.parametrize("M", [1, 64, 512, 4096])
 @pytest.mark.parametrize("azp", [0, -7])
@@ -343,7 +371,7 @@ def test_pointwise_conv_tensor_core_sweep(device, M, K, N):
     got = _check(device, g, [a])[0]
     from torq_b200.runtime import Executable
     ex = Executable(device, g.serialize())
-    assert ex.op_kernels() == ["gemm_i8_tcgen05"]
+    assert ex.op_kernels() == ["gemm_i8_tcgen05" if M > 4 or K % 16 else "fc_rows_dp4a"]
     ex.destroy()
     os.environ["TB200_FORCE_SIMT"] = "1"
     try:

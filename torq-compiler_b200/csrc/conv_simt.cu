@@ -493,6 +493,53 @@ __global__ void __launch_bounds__(128) conv2d_stem333_kernel(ConvArgs a) {
   }
 }
 
+// FullyConnected on at most MR rows: one warp per output channel. The row(s) of x sit in shared memory (K bytes each);
+// a lane takes 16 weights per step with one 16-byte load and runs them against the staged activations with dp4a;
+// the warp adds its lanes' sums and lane 0 applies the exact rescale. Weights are read once, coalesced: HBM-bound.
+template <int MR>
+__global__ void __launch_bounds__(256) fc_rows_kernel(FcRowsArgs a) {
+  extern __shared__ __align__(16) int8_t fc_x[];  // [MR][K]
+  for (int i = threadIdx.x * 16; i < MR * a.K; i += blockDim.x * 16) {
+    const int m = i / a.K, k = i - m * a.K;
+    *reinterpret_cast<uint4*>(fc_x + i) = m < a.M ? *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.K + k) : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= a.N) return;
+  const int8_t* wrow = a.w + (size_t)n * a.K;
+  int acc[MR];
+#pragma unroll
+  for (int m = 0; m < MR; m++) acc[m] = 0;
+#pragma unroll 4
+  for (int k = lane * 16; k < a.K; k += 32 * 16) {
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + k));
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(fc_x + m * a.K + k);
+      acc[m] = __dp4a((int)xv.x, (int)wv.x, acc[m]);
+      acc[m] = __dp4a((int)xv.y, (int)wv.y, acc[m]);
+      acc[m] = __dp4a((int)xv.z, (int)wv.z, acc[m]);
+      acc[m] = __dp4a((int)xv.w, (int)wv.w, acc[m]);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MR; m++)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+  if (lane == 0) {
+    const ChanParams cp = a.chan[n];
+#pragma unroll
+    for (int m = 0; m < MR; m++)
+      if (m < a.M) {
+        int q = a.hi_shift ? requant_cp<true>(acc[m] + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max)
+                           : requant_cp<false>(acc[m] + cp.bias, cp, a.out_zp, a.clamp_min, a.clamp_max);
+        if (a.lut) q = __ldg(a.lut + q + 128);
+        a.out[(size_t)m * a.N + n] = (int8_t)q;
+      }
+  }
+}
+
 // Conv2D i16 x i8 (TB200_OP_CONV2D_I16): one thread per output; consecutive threads take consecutive output channels
 // of a pixel, so the pixel's input window is read by the whole group and the weights stream per thread. 64-bit
 // accumulation (TOSA's 48-bit accumulator never leaves it), then apply_scale_16:
@@ -604,6 +651,13 @@ void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
     conv2d_simt_kernel<true><<<grid, 256, 0, stream>>>(a);
   else
     conv2d_simt_kernel<false><<<grid, 256, 0, stream>>>(a);
+}
+
+void launch_fc_rows(const FcRowsArgs& a, cudaStream_t stream) {
+  const unsigned blocks = (unsigned)((a.N + 7) / 8);
+  if (a.M <= 1) fc_rows_kernel<1><<<blocks, 256, (size_t)a.K, stream>>>(a);
+  else if (a.M <= 2) fc_rows_kernel<2><<<blocks, 256, (size_t)2 * a.K, stream>>>(a);
+  else fc_rows_kernel<4><<<blocks, 256, (size_t)4 * a.K, stream>>>(a);
 }
 
 void launch_conv2d_i16(const ConvI16Args& a, cudaStream_t stream) {

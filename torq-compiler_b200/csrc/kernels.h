@@ -38,6 +38,19 @@ struct ConvArgs {
 };
 void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream);
 
+// FullyConnected / 1x1 convolution on at most 4 rows (a classifier at batch 1, GEMV-shaped calls): the weights are
+// streamed once at HBM rate by one warp per output channel (dp4a), instead of through 128-row tensor-core tiles.
+struct FcRowsArgs {
+  const int8_t* x;         // [M, K]
+  const int8_t* w;         // [N, K]
+  const ChanParams* chan;  // [N]
+  int8_t* out;             // [M, N]
+  int M, N, K;             // M <= 4, K a multiple of 16
+  int out_zp, clamp_min, clamp_max, hi_shift;
+  const int8_t* lut;       // fused table or null
+};
+void launch_fc_rows(const FcRowsArgs& a, cudaStream_t stream);
+
 // Conv2D on int16 activations with int8 weights and the 16-bit rescale that follows it (TB200_OP_CONV2D_I16).
 struct ConvI16Args {
   const int16_t* x;         // NHWC

@@ -775,6 +775,27 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         const bool pointwise = fc || (KH == 1 && KW == 1 && op.stride_h == 1 && op.stride_w == 1 && op.pad_t == 0 &&
                                       op.pad_b == 0 && op.pad_l == 0 && op.pad_r == 0);
         const long long M = (long long)N * OH * OW;
+        // At most four rows: a weight-streaming dp4a kernel instead of 128-row tensor-core tiles (the weights are the
+        // only traffic that counts there; 4 x K bytes of activations fit any SM's shared memory up to K = 12288)
+        if (pointwise && op.weight_zp == 0 && !force_simt() && M <= 4 && K % 16 == 0 && K <= 12288) {
+          FcRowsArgs fa{};
+          fa.M = (int)M; fa.N = OC; fa.K = (int)K;
+          fa.out_zp = op.out_zp; fa.clamp_min = op.clamp_min; fa.clamp_max = op.clamp_max; fa.hi_shift = b.last_hi_shift;
+          const size_t w_off = b.add_const(w, (size_t)OC * K);
+          const size_t c_off = b.add_const(cp.data(), cp.size() * sizeof(ChanParams));
+          Loc lx = loc(op.in0), lo = loc(result_id);
+          step.kernel_name = "fc_rows_dp4a";
+          step.launch = [=](const ExecContext& c) {
+            FcRowsArgs k = fa;
+            k.x = (const int8_t*)lx.resolve(c);
+            k.out = (int8_t*)lo.resolve(c);
+            k.w = (const int8_t*)(c.consts + w_off);
+            k.chan = (const ChanParams*)(c.consts + c_off);
+            k.lut = has_lut ? (const int8_t*)(c.consts + lut_off) : nullptr;
+            launch_fc_rows(k, c.stream);
+          };
+          break;
+        }
         // TMA wants a row pitch that is a multiple of 16 bytes. When K is not, r consecutive
         // rows are read as one row of r*K bytes against block-diagonal weights: row m' of the
         // product then holds the outputs of pixels r*m' .. r*m'+r-1 back to back, which is
