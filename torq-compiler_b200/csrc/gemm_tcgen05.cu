@@ -38,6 +38,7 @@
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the device
 // status word and every role drains to the common exit, where TMEM is freed.
 #include <cuda.h>
+#include <type_traits>
 #include <cuda_runtime.h>
 
 #include <cstdlib>
@@ -226,68 +227,98 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
+    // One thread issues every tcgen05.mma of the CTA, and at N <= 128 an instruction takes the tensor pipe only
+    // 27-36 ns (about 50-70 cycles): the scalar work between two issues must stay below that or the pipe idles.
+    // So the descriptors are kept as 32-bit low words (the shared-memory address field cannot carry out of its
+    // 14 bits), stepped by additions, and the K steps of a row are unrolled at compile time.
     if (lane == 0) {
       const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       const int steps_full = p.row_bytes / 32;
-      int s = 0;
-      uint32_t phase = 0;
       bool ok = true;
       if (p.w_resident) ok = mbar_wait(smem_u32(&bar_w), 0, p.status, 5, p.wait_ns);
-      int n = blockIdx.x / p.m_tiles, m = blockIdx.x - n * p.m_tiles;
-      int as = 0;
-      uint32_t acc_phase = 0;
-      int tr = 0;
       const uint64_t desc0_ring = make_smem_desc(smem_ring, p.row_bytes);
       const uint64_t desc0_w = make_smem_desc(p.w_resident ? smem_w : smem_ring + a_stage_bytes, p.row_bytes);
+      const uint32_t desc_hi = (uint32_t)(desc0_ring >> 32);
+      const uint32_t ring_lo = (uint32_t)desc0_ring, w_lo = (uint32_t)desc0_w;
       const uint32_t stage_units = stage_bytes >> 4, w_tile_units = w_tile_bytes >> 4;
       const uint32_t tap_units = CONV ? (uint32_t)((p.row_bytes << p.tw_log2) >> 4) : 0u;  // TW rows
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        if (!(ok = mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2, p.wait_ns))) break;
-        trace_stamp(p.trace, 1, tr, 1);
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(as * p.acc_stride);
-        int kw = 0, icb = 0;
-        for (int kb = 0; kb < p.k_loads; kb++) {
-          if (!(ok = mbar_wait(smem_u32(&bar_full[s]), phase, p.status, 3, p.wait_ns))) break;
-          trace_stamp(p.trace, 1, tr, 2);
+      // weights of kernel row r + 1 relative to row r: KW * icb_per_tap k blocks on (resident), or the next tile of the stage
+      const uint32_t w_row_units = p.w_resident ? (uint32_t)(p.KW * p.icb_per_tap) * w_tile_units : w_tile_units;
+      auto run = [&](auto steps_c) {
+        constexpr int STEPS = decltype(steps_c)::value;
+        int s = 0;
+        uint32_t phase = 0;
+        int n = blockIdx.x / p.m_tiles, m = blockIdx.x - n * p.m_tiles;
+        int as = 0;
+        uint32_t acc_phase = 0;
+        int tr = 0;
+        uint32_t a_lo = ring_lo;                   // descriptor of stage s
+        uint32_t bar = smem_u32(&bar_full[0]);     // full barrier of stage s (the empty one is kMaxStages words on)
+        const uint32_t bar_empty_off = smem_u32(&bar_empty[0]) - smem_u32(&bar_full[0]);
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+          if (!(ok = mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2, p.wait_ns))) break;
+          trace_stamp(p.trace, 1, tr, 1);
           tc_fence_after();
-          if (shared_rows) {
-            for (int r = 0; r < p.khs; r++) {
-              const uint64_t da = desc0_ring + (uint64_t)((uint32_t)s * stage_units + (uint32_t)r * tap_units);
-              const uint64_t db = p.w_resident
-                                      ? desc0_w + (uint64_t)((uint32_t)(n * p.k_blocks + (r * p.KW + kw) * p.icb_per_tap + icb) * w_tile_units)
-                                      : desc0_w + (uint64_t)((uint32_t)s * stage_units + (uint32_t)r * w_tile_units);
-              for (int k = 0; k < steps_full; k++) mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | r | k) != 0);
+          const uint32_t tmem_d = tmem_base + (uint32_t)(as * p.acc_stride);
+          uint32_t accum = 0;
+          uint32_t b_kb = w_lo + (uint32_t)(n * p.k_blocks) * w_tile_units;  // resident weights: k block kb of this n tile
+          for (int kb = 0; kb < p.k_loads; kb++) {
+            if (!(ok = mbar_wait(bar, phase, p.status, 3, p.wait_ns))) break;
+            trace_stamp(p.trace, 1, tr, 2);
+            tc_fence_after();
+            uint32_t b_lo = p.w_resident ? b_kb : w_lo + (a_lo - ring_lo);
+            if (shared_rows) {
+              uint32_t ar = a_lo;
+              for (int r = 0; r < p.khs; r++) {
+#pragma unroll
+                for (int k = 0; k < STEPS; k++) {
+                  mma_i8_lo(tmem_d, ar + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
+                  accum = 1;
+                }
+                ar += tap_units;
+                b_lo += w_row_units;
+              }
+            } else if (kb == p.k_blocks - 1 && p.k_last_steps != STEPS) {
+              for (int k = 0; k < p.k_last_steps; k++) {
+                mma_i8_lo(tmem_d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
+                accum = 1;
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < STEPS; k++) {
+                mma_i8_lo(tmem_d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
+                accum = 1;
+              }
             }
-            if (++icb == p.icb_per_tap) {
-              icb = 0;
-              kw++;
+            trace_stamp(p.trace, 1, tr, 4);
+            mma_commit(bar + bar_empty_off);  // frees the stage once the MMAs have read it
+            b_kb += w_tile_units;
+            a_lo += stage_units;
+            bar += 8;
+            if (++s == p.stages) {
+              s = 0;
+              phase ^= 1;
+              a_lo = ring_lo;
+              bar = smem_u32(&bar_full[0]);
             }
-          } else {
-            const int steps = (kb == p.k_blocks - 1) ? p.k_last_steps : steps_full;
-            const uint64_t da = desc0_ring + (uint64_t)((uint32_t)s * stage_units);
-            const uint64_t db = p.w_resident ? desc0_w + (uint64_t)((uint32_t)(n * p.k_blocks + kb) * w_tile_units)
-                                             : desc0_w + (uint64_t)((uint32_t)s * stage_units);
-            for (int k = 0; k < steps; k++) mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
           }
-          trace_stamp(p.trace, 1, tr, 4);
-          mma_commit(smem_u32(&bar_empty[s]));  // frees the stage once the MMAs have read it
-          if (++s == p.stages) {
-            s = 0;
-            phase ^= 1;
+          if (ok) mma_commit(smem_u32(&bar_acc_full[as]));
+          trace_stamp(p.trace, 1, tr, 3);
+          if (++as == p.acc_stages) {
+            as = 0;
+            acc_phase ^= 1;
+          }
+          m += gridDim.x;
+          while (m >= p.m_tiles) {
+            m -= p.m_tiles;
+            n++;
           }
         }
-        if (ok) mma_commit(smem_u32(&bar_acc_full[as]));
-        trace_stamp(p.trace, 1, tr, 3);
-        if (++as == p.acc_stages) {
-          as = 0;
-          acc_phase ^= 1;
-        }
-        m += gridDim.x;
-        while (m >= p.m_tiles) {
-          m -= p.m_tiles;
-          n++;
-        }
+      };
+      if (ok) {
+        if (steps_full == 4) run(std::integral_constant<int, 4>{});
+        else if (steps_full == 2) run(std::integral_constant<int, 2>{});
+        else run(std::integral_constant<int, 1>{});
       }
     }
   } else {
