@@ -227,15 +227,15 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
-    // One thread issues every tcgen05.mma of the CTA, and at N <= 128 an instruction takes the tensor pipe only
-    // 27-36 ns (about 50-70 cycles): the scalar work between two issues must stay below that or the pipe idles.
-    // So the descriptors are kept as 32-bit low words (the shared-memory address field cannot carry out of its
-    // 14 bits), stepped by additions, and the K steps of a row are unrolled at compile time.
-    if (lane == 0) {
+    // At N <= 128 an instruction takes the tensor pipe only 27-36 ns (about 50-70 cycles): the work between two
+    // issues must stay below that or the pipe idles. So the whole warp walks the loop with warp-uniform values (one
+    // elected lane issues), the descriptors are kept as 32-bit low words (the shared-memory address field cannot
+    // carry out of its 14 bits) stepped by additions, and the K steps of a row are unrolled at compile time.
+    {
       const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       const int steps_full = p.row_bytes / 32;
       bool ok = true;
-      if (p.w_resident) ok = mbar_wait(smem_u32(&bar_w), 0, p.status, 5, p.wait_ns);
+      if (p.w_resident) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_w), 0, p.status, 5, p.wait_ns));
       const uint64_t desc0_ring = make_smem_desc(smem_ring, p.row_bytes);
       const uint64_t desc0_w = make_smem_desc(p.w_resident ? smem_w : smem_ring + a_stage_bytes, p.row_bytes);
       const uint32_t desc_hi = (uint32_t)(desc0_ring >> 32);
@@ -244,7 +244,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t tap_units = CONV ? (uint32_t)((p.row_bytes << p.tw_log2) >> 4) : 0u;  // TW rows
       // weights of kernel row r + 1 relative to row r: KW * icb_per_tap k blocks on (resident), or the next tile of the stage
       const uint32_t w_row_units = p.w_resident ? (uint32_t)(p.KW * p.icb_per_tap) * w_tile_units : w_tile_units;
-      // The waits of the hot loop are single polls; a poll that fails leaves the loop, the bounded wait runs out here
+      // The waits of the hot loop are short polls; a poll that fails leaves the loop, the bounded wait runs out here
       // and the loop is entered again where it stopped. (With the bounded wait's loop inside, the same issue sequence
       // ran at 86 ns per instruction instead of 49: measured with resident operands.)
       auto run = [&](auto steps_c) {
@@ -265,7 +265,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           int failed = 0;  // 1: the accumulator stage is not drained yet, 2: the operand stage has not landed yet
           while (t < total_tiles) {
             if (!tile_open) {
-              if (!mbar_try_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1)) {
+              if (!__all_sync(0xffffffffu, mbar_poll(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, 8))) {
                 failed = 1;
                 break;
               }
@@ -275,7 +275,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               accum = 0;
               b_kb = w_lo + (uint32_t)(n * p.k_blocks) * w_tile_units;  // resident weights: k block 0 of this n tile
             }
-            if (!mbar_try_wait(bar, phase)) {
+            if (!__all_sync(0xffffffffu, mbar_poll(bar, phase, 8))) {
               failed = 2;
               break;
             }
@@ -286,7 +286,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               for (int r = 0; r < p.khs; r++) {
 #pragma unroll
                 for (int k = 0; k < STEPS; k++) {
-                  mma_i8_lo(tmem_d, ar + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
+                  mma_i8_lo_elect(tmem_d, ar + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
                   accum = 1;
                 }
                 ar += tap_units;
@@ -294,17 +294,17 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               }
             } else if (kb == p.k_blocks - 1 && p.k_last_steps != STEPS) {
               for (int k = 0; k < p.k_last_steps; k++) {
-                mma_i8_lo(tmem_d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
+                mma_i8_lo_elect(tmem_d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
                 accum = 1;
               }
             } else {
 #pragma unroll
               for (int k = 0; k < STEPS; k++) {
-                mma_i8_lo(tmem_d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
+                mma_i8_lo_elect(tmem_d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
                 accum = 1;
               }
             }
-            mma_commit(bar + bar_empty_off);  // frees the stage once the MMAs have read it
+            mma_commit_elect(bar + bar_empty_off);  // frees the stage once the MMAs have read it
             b_kb += w_tile_units;
             a_lo += stage_units;
             bar += 8;
@@ -315,7 +315,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               bar = smem_u32(&bar_full[0]);
             }
             if (++kb == p.k_loads) {
-              mma_commit(smem_u32(&bar_acc_full[as]));
+              mma_commit_elect(smem_u32(&bar_acc_full[as]));
               trace_stamp(p.trace, 1, tr, 3);
               kb = 0;
               tile_open = false;
@@ -332,8 +332,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
           }
           if (!failed) break;
-          ok = failed == 1 ? mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2, p.wait_ns)
-                           : mbar_wait(bar, phase, p.status, 3, p.wait_ns);
+          ok = __all_sync(0xffffffffu, failed == 1 ? mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2, p.wait_ns)
+                                                   : mbar_wait(bar, phase, p.status, 3, p.wait_ns));
           if (!ok) break;
         }
       };

@@ -115,6 +115,49 @@ __device__ __forceinline__ void mma_i8_lo(uint32_t tmem_d, uint32_t a_lo, uint32
       ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Whole-warp forms: every lane of a converged warp executes the statement with warp-uniform operands and one elected
+// lane issues the instruction. Keeping the issuing loop warp-uniform lets the descriptors live in uniform registers
+// (measured with resident operands, N = 64: 39 ns per instruction against 50 ns from a single-lane branch).
+__device__ __forceinline__ void mma_i8_lo_elect(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar)
+      : "memory");
+}
+// A short bounded poll as one statement (no control flow the compiler sees): 1 when the phase completed within
+// `tries` polls. The caller falls back to mbar_wait, which is bounded in time.
+__device__ __forceinline__ uint32_t mbar_poll(uint32_t bar, uint32_t parity, uint32_t tries) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
+      "mov.u32 n, %3;\n\t"
+      "POLL_%=:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra DONE_%=;\n\t"
+      "sub.u32 n, n, 1;\n\t"
+      "setp.ne.u32 p, n, 0;\n\t"
+      "@p bra POLL_%=;\n\t"
+      "DONE_%=:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(tries)
+      : "memory");
+  return ok;
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
