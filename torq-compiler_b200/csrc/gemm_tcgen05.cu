@@ -90,6 +90,11 @@ struct GemmTcParams {
   // khs kernel rows of that column need; the operand of kernel row kh starts kh * TW rows into the stage, a whole
   // number of 8-row swizzle atoms, so the descriptors stay the plain K-major ones. k_loads = stage loads per tile.
   int khs, k_loads, patch_rows;
+  // halo (stride 1, resident weights): the tile's patch is 16 pixels wide and TH + KH - 1 rows high, loaded once per
+  // channel block; tap (kh, kw) reads it kh * 16 + kw rows in, so the last KW - 1 pixels of every 16 (whose operand
+  // rows run into the next patch row) are computed and dropped: tw_valid = 16 - (KW - 1) output columns per tile.
+  // kcols = kernel columns the issuer walks inside one stage (KW with halo, else 1).
+  int halo, tw_valid, kcols;
   const int32_t* corr;  // [row classes * col classes][n_tiles * BN] border corrections, or null
   const uint8_t* rcls;  // [OH] row class
   const uint8_t* ccls;  // [OW] column class
@@ -179,7 +184,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const int r = m - img * p.tiles_per_img;
           const int ty = r / p.tiles_w, tx = r - ty * p.tiles_w;
           ih0 = ty * p.TH * p.cstride - p.pad_t;
-          iw0 = (tx << p.tw_log2) * p.cstride - p.pad_l;
+          iw0 = tx * p.tw_valid * p.cstride - p.pad_l;
         }
         for (int kb = 0; kb < p.k_loads; kb++) {
           if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1, p.status, 1, p.wait_ns))) break;
@@ -244,6 +249,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t tap_units = CONV ? (uint32_t)((p.row_bytes << p.tw_log2) >> 4) : 0u;  // TW rows
       // weights of kernel row r + 1 relative to row r: KW * icb_per_tap k blocks on (resident), or the next tile of the stage
       const uint32_t w_row_units = p.w_resident ? (uint32_t)(p.KW * p.icb_per_tap) * w_tile_units : w_tile_units;
+      const uint32_t w_col_units = (uint32_t)p.icb_per_tap * w_tile_units;  // halo: the next kernel column's weights
+      const uint32_t row_units = (uint32_t)p.row_bytes >> 4;                // halo: the patch one pixel further
+      const bool halo33 = p.halo && p.khs == 3 && p.kcols == 3;
+      const bool rows3 = shared_rows && !p.halo && p.khs == 3;
       // The waits of the hot loop are short polls; a poll that fails leaves the loop, the bounded wait runs out here
       // and the loop is entered again where it stopped. (With the bounded wait's loop inside, the same issue sequence
       // ran at 86 ns per instruction instead of 49: measured with resident operands.)
@@ -281,13 +290,44 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
             tc_fence_after();
             uint32_t b_lo = p.w_resident ? b_kb : w_lo + (a_lo - ring_lo);
-            if (shared_rows) {
-              uint32_t ar = a_lo;
-              for (int r = 0; r < p.khs; r++) {
+            if (CONV && halo33) {
+              // 3x3 over a halo patch, the common case, fully unrolled: the operand of tap (r, c) starts r * 16 + c
+              // rows into the patch, a compile-time distance once the row width (32 * STEPS bytes) is one
+              uint32_t bc = b_lo;
+#pragma unroll
+              for (int r = 0; r < 3; r++)
+#pragma unroll
+                for (int c = 0; c < 3; c++) {
+#pragma unroll
+                  for (int k = 0; k < STEPS; k++) {
+                    mma_i8_lo_elect(tmem_d, a_lo + (uint32_t)((r * 16 + c) * 2 * STEPS + 2 * k), bc + 2 * k, desc_hi, idesc, accum);
+                    accum = 1;
+                  }
+                  bc += w_col_units;
+                }
+            } else if (CONV && rows3) {
+              // three kernel rows sharing one load per kernel column, unrolled
+#pragma unroll
+              for (int r = 0; r < 3; r++) {
 #pragma unroll
                 for (int k = 0; k < STEPS; k++) {
-                  mma_i8_lo_elect(tmem_d, ar + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
+                  mma_i8_lo_elect(tmem_d, a_lo + (uint32_t)r * tap_units + 2 * k, b_lo + 2 * k, desc_hi, idesc, accum);
                   accum = 1;
+                }
+                b_lo += w_row_units;
+              }
+            } else if (shared_rows) {
+              uint32_t ar = a_lo;
+              for (int r = 0; r < p.khs; r++) {
+                uint32_t ac = ar, bc = b_lo;
+                for (int c = 0; c < p.kcols; c++) {
+#pragma unroll
+                  for (int k = 0; k < STEPS; k++) {
+                    mma_i8_lo_elect(tmem_d, ac + 2 * k, bc + 2 * k, desc_hi, idesc, accum);
+                    accum = 1;
+                  }
+                  ac += row_units;
+                  bc += w_col_units;
                 }
                 ar += tap_units;
                 b_lo += w_row_units;
@@ -332,9 +372,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
           }
           if (!failed) break;
+          trace_stamp(p.trace, 1, tr, 4 + failed);  // 5: waited for an accumulator, 6: waited for operands
           ok = __all_sync(0xffffffffu, failed == 1 ? mbar_wait(smem_u32(&bar_acc_empty[as]), acc_phase ^ 1, p.status, 2, p.wait_ns)
                                                    : mbar_wait(bar, phase, p.status, 3, p.wait_ns));
           if (!ok) break;
+          trace_stamp(p.trace, 1, tr, 7);
         }
       };
       if (ok) {
@@ -362,7 +404,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // one staging tile per group for the TMA store of the output
     uint8_t* const stage_tile = smem_raw + (smem_base - smem_u32(smem_raw)) + p.staging_off + (size_t)group * tile_bytes;
     const int row_in_tile = q * 32 + lane;
-    uint8_t* const srow = stage_tile + (size_t)row_in_tile * p.BNh;
+    // convolution: the pixel of this accumulator row inside the tile; with a halo patch only tw_valid of its 16
+    // columns are outputs, and the staged tile holds just those
+    const int px_x = CONV ? (row_in_tile & ((1 << p.tw_log2) - 1)) : 0, px_y = CONV ? (row_in_tile >> p.tw_log2) : 0;
+    const bool px_valid = !CONV || px_x < p.tw_valid;
+    uint8_t* const srow = stage_tile + (size_t)(CONV ? px_y * p.tw_valid + px_x : row_in_tile) * p.BNh;
     const int bar_id = 1 + group;
     auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory"); };
     int loaded_n = -1;
@@ -394,9 +440,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const int r = m - img * p.tiles_per_img;
           const int ty = r / p.tiles_w, tx = r - ty * p.tiles_w;
           oh0 = ty * p.TH;
-          ow0 = tx << p.tw_log2;
-          const int oh = oh0 + (row_in_tile >> p.tw_log2), ow = ow0 + (row_in_tile & ((1 << p.tw_log2) - 1));
-          if (p.corr && oh < p.OH && ow < p.OW) {
+          ow0 = tx * p.tw_valid;
+          const int oh = oh0 + px_y, ow = ow0 + px_x;
+          if (p.corr && px_valid && oh < p.OH && ow < p.OW) {
             const int cls = p.rcls[oh] * p.ncc + p.ccls[ow];
             if (p.cls_nonzero[cls]) corr_row = p.corr + (size_t)cls * p.n_tiles * p.BN + (size_t)n * p.BN + col_half;
           }
@@ -438,7 +484,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
           }
           if (p.tma_store) {
-            *reinterpret_cast<uint4*>(srow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            if (px_valid) *reinterpret_cast<uint4*>(srow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
           } else if (row < p.M) {
             if (vec_ok && ncol0 + c0 + 16 <= p.N) {
               *reinterpret_cast<uint4*>(orow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
@@ -739,6 +785,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   p.k_blocks = g.k_blocks;
   p.k_loads = g.k_blocks;
   p.khs = 1;
+  p.kcols = 1;
   p.k_last_steps = ((a.K - (g.k_blocks - 1) * g.row_bytes) + 31) / 32;
   p.row_bytes = g.row_bytes;
   const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
@@ -814,9 +861,35 @@ ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, i
       g.TH = th;
     }
   }
+  g.TWv = g.TW;
   g.tiles_w = (OW + g.TW - 1) / g.TW;
   g.tiles_h = (OH + g.TH - 1) / g.TH;
-  const GemmTcGeometry n = gemm_tc_geometry(OC, g.Kpad, (long long)N * g.tiles_w * g.tiles_h * kBM);
+  GemmTcGeometry n = gemm_tc_geometry(OC, g.Kpad, (long long)N * g.tiles_w * g.tiles_h * kBM);
+  // Halo patches: the copy engine works row by row (a pixel's channel block is a row), and a load per kernel
+  // column moves every input pixel KW times. With the weights resident in shared memory one 16-pixel-wide patch
+  // per tile and channel block serves all KH * KW taps: tap (kh, kw) is the same patch read kh * 16 + kw rows in.
+  // Taken when it moves fewer rows than the per-column loads.
+  static int no_halo = -1;  // TB200_CONV_NO_HALO=1: A/B aid
+  if (no_halo < 0) { const char* e = getenv("TB200_CONV_NO_HALO"); no_halo = e && *e && *e != '0'; }
+  if (!no_halo && stride == 1 && KH > 1 && KW > 1 && KW <= 5) {
+    const int twv = 16 - (KW - 1), th = 8;
+    const int tiles_w = (OW + twv - 1) / twv, tiles_h = (OH + th - 1) / th;
+    const GemmTcGeometry nh = gemm_tc_geometry(OC, g.Kpad, (long long)N * tiles_w * tiles_h * kBM);
+    const long long rows_halo = (long long)tiles_w * tiles_h * (th + KH - 1) * 16;
+    const long long rows_cols = (long long)g.tiles_w * g.tiles_h * (g.TH + KH - 1) * g.TW * KW;
+    // the weights must stay in shared memory beside the output staging tiles and at least three patches
+    const size_t need = (size_t)nh.n_tiles * nh.BN * g.Kpad + (size_t)kEpiGroups * kBM * (nh.BN / nh.gpt) +
+                        3 * (size_t)(th + KH - 1) * 16 * g.row_bytes + 1024;
+    if (need <= (size_t)kSmemBudget && rows_halo < rows_cols) {
+      g.halo = 1;
+      g.TW = 16;
+      g.TWv = twv;
+      g.TH = th;
+      g.tiles_w = tiles_w;
+      g.tiles_h = tiles_h;
+      n = nh;
+    }
+  }
   g.BN = n.BN;
   g.n_tiles = n.n_tiles;
   g.gpt = n.gpt;
@@ -848,7 +921,7 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   }
   if (((uintptr_t)a.out % 16) != 0) return cudaErrorInvalidValue;
   if (st->c != a.out) {
-    if (!encode_conv_output(&st->tmC, a.out, a.N, a.OH, a.OW, a.OC, g.BN / g.gpt, g.TW, g.TH)) return cudaErrorInvalidValue;
+    if (!encode_conv_output(&st->tmC, a.out, a.N, a.OH, a.OW, a.OC, g.BN / g.gpt, g.TWv, g.TH)) return cudaErrorInvalidValue;
     st->c = a.out;
   }
   GemmTcParams p{};
@@ -872,11 +945,14 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   p.OH = a.OH; p.OW = a.OW; p.cstride = a.stride; p.pad_t = a.pad_t; p.pad_l = a.pad_l; p.KW = a.KW;
   p.icb_per_tap = g.icb_per_tap;
   p.khs = g.khs;
-  p.k_loads = g.khs > 1 ? a.KW * g.icb_per_tap : g.k_blocks;
+  p.halo = g.halo;
+  p.tw_valid = g.TWv;
+  p.kcols = g.halo ? a.KW : 1;
+  p.k_loads = g.halo ? g.icb_per_tap : g.khs > 1 ? a.KW * g.icb_per_tap : g.k_blocks;
   p.patch_rows = patch_h * g.TW;
   p.corr = a.corr; p.rcls = a.rcls; p.ccls = a.ccls; p.cls_nonzero = a.cls_nonzero; p.ncc = a.ncc;
   const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
-  p.w_resident = w_bytes <= (size_t)kResidentWeightBytes;
+  p.w_resident = g.halo || w_bytes <= (size_t)kResidentWeightBytes;
   const size_t stage_bytes = (size_t)(g.khs > 1 ? p.patch_rows : kBM) * g.row_bytes +
                              (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes * g.khs);
   const size_t staging_bytes = (size_t)kEpiGroups * kBM * (g.BN / g.gpt);

@@ -168,6 +168,8 @@ struct ConvTcGeometry {
   int BN, n_tiles, gpt;
   int TW, TH, tiles_w, tiles_h;                // output patch of a tile (TW * TH = 128)
   int khs;                                     // kernel rows served by one load of TH + khs - 1 input rows (1 = a load per tap)
+  int halo;                                    // 1: one load per tile and channel block serves every tap (TWv valid columns of TW = 16)
+  int TWv;                                     // output columns a tile produces (TW unless halo)
 };
 ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, int KW, int stride);
 bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w,
