@@ -72,7 +72,10 @@ IGEMM_CASES = [
     ((1, 12, 12, 64), 64, (3, 3), 1, (1, 1, 1, 1), 0),       # zero input zero point: no correction table
     ((1, 9, 140, 32), 32, (1, 7), 1, (0, 0, 3, 3), -20),     # one-row window, wide frame
     ((2, 20, 20, 80), 80, (3, 3), 1, (1, 1, 1, 1), 3),       # 80 channels: the last 32-byte block is half zero fill
-    ((1, 30, 34, 16), 32, (3, 3), 2, (0, 1, 0, 1), -6),      # 16 channels (dp4a kernel)
+    ((1, 30, 34, 16), 32, (3, 3), 2, (0, 1, 0, 1), -6),      # 16 channels, stride 2 (dp4a kernel)
+    ((2, 37, 45, 16), 16, (3, 3), 1, (1, 1, 1, 1), -6),      # 16 channels, stride 1: halo patches, rows half zero fill
+    ((1, 23, 31, 64), 32, (5, 5), 1, (2, 2, 2, 2), 9),       # 5x5 over halo patches (12 output columns per tile)
+    ((1, 19, 33, 128), 64, (3, 3), 1, (1, 1, 1, 1), -2),     # 128-byte rows over halo patches, weights 72 KB resident
     ((1, 11, 11, 48), 16, (3, 3), 1, (1, 1, 1, 1), 8),       # 48 channels in one 64-byte block
 ]
 
@@ -93,8 +96,8 @@ def test_conv2d_implicit_gemm(device, case, mode):
                  requant_mode=mode)
     g.output(y)
     ex = Executable(device, g.serialize())
-    # 16 input channels make 16-byte operand rows: the direct dp4a kernel is faster and takes those
-    assert ex.op_kernels() == ["conv2d_c16_dp4a" if shape[3] == 16 else "conv_igemm_i8_tcgen05"]
+    # 16 input channels make 16-byte operand rows: without halo patches (stride 2) the direct dp4a kernel takes those
+    assert ex.op_kernels() == ["conv2d_c16_dp4a" if shape[3] == 16 and stride == 2 else "conv_igemm_i8_tcgen05"]
     ex.destroy()
     _check(device, g, [x])
 

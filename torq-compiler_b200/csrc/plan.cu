@@ -863,10 +863,12 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
 
         // KH x KW convolution with symmetric weights: implicit GEMM on the tensor cores (one TMA box per
         // tap and channel block, taps accumulated in TMEM; see gemm_tcgen05.cu)
-        // (16 input channels: the copy engine's per-row cost makes 16-byte rows a poor tensor-core operand;
-        // the direct dp4a kernel is faster there)
-        if (!fc && !pointwise && op.weight_zp == 0 && !force_simt() && IC != 16 &&
-            conv_tc_supported(N, H, W, IC, OC, KH, KW, op.stride_h, op.stride_w, op.dil_h, op.dil_w, OH, OW)) {
+        // (16 input channels with a load per tap or per kernel column: the copy engine's per-row cost makes 16-byte
+        // rows a poor tensor-core operand and the direct dp4a kernel is faster; with one halo patch per tile the
+        // row count no longer depends on the kernel size and the tensor cores take those too)
+        if (!fc && !pointwise && op.weight_zp == 0 && !force_simt() &&
+            conv_tc_supported(N, H, W, IC, OC, KH, KW, op.stride_h, op.stride_w, op.dil_h, op.dil_w, OH, OW) &&
+            (IC != 16 || conv_tc_geometry(N, OH, OW, IC, OC, KH, KW, op.stride_h).halo)) {
           const ConvTcGeometry geo = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW, op.stride_h);
           ConvTcArgs ca{};
           ca.N = N; ca.H = H; ca.W = W; ca.IC = IC; ca.OC = OC; ca.KH = KH; ca.KW = KW; ca.OH = OH; ca.OW = OW;
