@@ -72,7 +72,11 @@ IGEMM_CASES = [
     ((1, 12, 12, 64), 64, (3, 3), 1, (1, 1, 1, 1), 0),       # zero input zero point: no correction table
     ((1, 9, 140, 32), 32, (1, 7), 1, (0, 0, 3, 3), -20),     # one-row window, wide frame
     ((2, 20, 20, 80), 80, (3, 3), 1, (1, 1, 1, 1), 3),       # 80 channels: the last 32-byte block is half zero fill
-    ((1, 30, 34, 16), 32, (3, 3), 2, (0, 1, 0, 1), -6),      # 16 channels, stride 2 (dp4a kernel)
+    ((1, 30, 34, 16), 32, (3, 3), 2, (0, 1, 0, 1), -6),      # 16 channels, stride 2: pixel pairs of 32 bytes, left pad 0
+    ((2, 41, 38, 16), 16, (3, 3), 2, (1, 1, 1, 1), 4),       # the same with left pad 1 and an odd height
+    ((1, 30, 33, 16), 32, (3, 3), 2, (1, 1, 1, 1), -6),      # odd width: no pixel pairs (dp4a kernel)
+    ((3, 36, 52, 32), 64, (3, 3), 2, (1, 0, 1, 0), 12),      # 32 channels, stride 2, pairs of 64 bytes
+    ((1, 64, 64, 64), 64, (3, 3), 2, (1, 1, 1, 1), -1),      # 64 channels, stride 2, pairs of 128 bytes, two K steps
     ((2, 37, 45, 16), 16, (3, 3), 1, (1, 1, 1, 1), -6),      # 16 channels, stride 1: halo patches, rows half zero fill
     ((1, 23, 31, 64), 32, (5, 5), 1, (2, 2, 2, 2), 9),       # 5x5 over halo patches (12 output columns per tile)
     ((1, 19, 33, 128), 64, (3, 3), 1, (1, 1, 1, 1), -2),     # 128-byte rows over halo patches, weights 72 KB resident
@@ -96,8 +100,8 @@ def test_conv2d_implicit_gemm(device, case, mode):
                  requant_mode=mode)
     g.output(y)
     ex = Executable(device, g.serialize())
-    # 16 input channels make 16-byte operand rows: without halo patches (stride 2) the direct dp4a kernel takes those
-    assert ex.op_kernels() == ["conv2d_c16_dp4a" if shape[3] == 16 and stride == 2 else "conv_igemm_i8_tcgen05"]
+    # 16 input channels make 16-byte operand rows: where neither halo patches nor pixel pairs apply, the dp4a kernel takes those
+    assert ex.op_kernels() == ["conv2d_c16_dp4a" if shape[3] == 16 and stride == 2 and shape[2] % 2 else "conv_igemm_i8_tcgen05"]
     ex.destroy()
     _check(device, g, [x])
 

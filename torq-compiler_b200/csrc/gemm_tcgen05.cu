@@ -95,6 +95,12 @@ struct GemmTcParams {
   // rows run into the next patch row) are computed and dropped: tw_valid = 16 - (KW - 1) output columns per tile.
   // kcols = kernel columns the issuer walks inside one stage (KW with halo, else 1).
   int halo, tw_valid, kcols;
+  // s2 (3x3 at stride 2, IC 16 / 32 / 64, even width, resident weights): the input is read as pixel PAIRS - rows of
+  // 2 * IC bytes, two horizontally adjacent pixels - one patch of 33 input rows x 9 pairs per tile of 16 x 8 outputs.
+  // Output column ox of tap kw reads pixel 2 * ox + kw - pad_l: pair ox + a, half b, so the tap's operand starts
+  // (kh * 9 + a) rows and b * IC bytes into the patch; the eight outputs of a tile row are eight consecutive pairs
+  // (one 8-row group) and the next tile row is two input rows = 18 pairs further (the descriptor's group stride).
+  int s2, a_row_bytes, s2_stage_bytes, s2_pair0;  // pair width, bytes of a stage, pair offset of the patch origin (-1 or 0)
   const int32_t* corr;  // [row classes * col classes][n_tiles * BN] border corrections, or null
   const uint8_t* rcls;  // [OH] row class
   const uint8_t* ccls;  // [OW] column class
@@ -128,7 +134,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const bool shared_rows = CONV && p.khs > 1;
-  const uint32_t a_stage_bytes = (uint32_t)(shared_rows ? p.patch_rows : kBM) * p.row_bytes;
+  const uint32_t a_stage_bytes = CONV && p.s2 ? (uint32_t)p.s2_stage_bytes : (uint32_t)(shared_rows ? p.patch_rows : kBM) * p.row_bytes;
   const uint32_t w_tile_bytes = (uint32_t)p.BN * p.row_bytes;  // one (n tile, k block) of the weights
   const uint32_t stage_bytes = a_stage_bytes + (p.w_resident ? 0u : w_tile_bytes * (shared_rows ? (uint32_t)p.khs : 1u));
   const uint32_t smem_w = smem_base;  // resident weights: [n_tiles][k_blocks] tiles
@@ -191,8 +197,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           trace_stamp(p.trace, 0, tr, 1);
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_ring + (uint32_t)s * stage_bytes;
-          mbar_expect_tx(full, stage_bytes);
-          if (shared_rows) {
+          mbar_expect_tx(full, CONV && p.s2 ? (uint32_t)(33 * 9 * p.a_row_bytes) : stage_bytes);  // s2: the stage is padded to 1 KB
+          if (CONV && p.s2) {
+            // one patch of pixel pairs per tile: 9 pairs from pair (first output column + s2_pair0), 33 input rows
+            tma_load_4d(dst, &tmA, 0, (iw0 + p.pad_l) / 2 + p.s2_pair0, ih0, img, full);
+          } else if (shared_rows) {
             // one patch of TH + khs - 1 rows for this kernel column and channel block; the weights of its khs taps
             tma_load_4d(dst, &tmA, icb * p.row_bytes, iw0 + kw, ih0, img, full);
             if (!p.w_resident)
@@ -252,6 +261,22 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t w_col_units = (uint32_t)p.icb_per_tap * w_tile_units;  // halo: the next kernel column's weights
       const uint32_t row_units = (uint32_t)p.row_bytes >> 4;                // halo: the patch one pixel further
       const bool halo33 = p.halo && p.khs == 3 && p.kcols == 3;
+      // s2: the A descriptor has its own width (pairs) and a group stride of two input rows (18 pairs); column kw of a
+      // tap starts a pairs and b pixels into the patch row: kw - pad_l + 2 = 2 * (a + 1) + b
+      uint32_t s2_a_hi = 0, s2_col0 = 0, s2_col1 = 0, s2_col2 = 0, s2_row_units = 0;
+      if (CONV && p.s2) {
+        uint64_t d = make_smem_desc(0, p.a_row_bytes);
+        d &= ~((uint64_t)0x3FFF << 32);
+        d |= (uint64_t)((18 * p.a_row_bytes) >> 4) << 32;
+        s2_a_hi = (uint32_t)(d >> 32);
+        const uint32_t pair_units = (uint32_t)p.a_row_bytes >> 4, pix_units = pair_units >> 1;
+        auto col = [&](int kw) {
+          const int v = kw - p.pad_l - 2 * p.s2_pair0;  // pixels from the patch origin
+          return (uint32_t)(v >> 1) * pair_units + (uint32_t)(v & 1) * pix_units;
+        };
+        s2_col0 = col(0); s2_col1 = col(1); s2_col2 = col(2);
+        s2_row_units = 9 * pair_units;
+      }
       const bool rows3 = shared_rows && !p.halo && p.khs == 3;
       // The waits of the hot loop are short polls; a poll that fails leaves the loop, the bounded wait runs out here
       // and the loop is entered again where it stopped. (With the bounded wait's loop inside, the same issue sequence
@@ -290,7 +315,23 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
             tc_fence_after();
             uint32_t b_lo = p.w_resident ? b_kb : w_lo + (a_lo - ring_lo);
-            if (CONV && halo33) {
+            if (CONV && p.s2) {
+              uint32_t ar = a_lo, bc = b_lo;
+#pragma unroll
+              for (int r = 0; r < 3; r++) {
+#pragma unroll
+                for (int c = 0; c < 3; c++) {
+                  const uint32_t ac = ar + (c == 0 ? s2_col0 : c == 1 ? s2_col1 : s2_col2);
+#pragma unroll
+                  for (int k = 0; k < STEPS; k++) {
+                    mma_i8_ab_elect(tmem_d, ac + 2 * k, s2_a_hi, bc + 2 * k, desc_hi, idesc, accum);
+                    accum = 1;
+                  }
+                  bc += w_col_units;
+                }
+                ar += s2_row_units;
+              }
+            } else if (CONV && halo33) {
               // 3x3 over a halo patch, the common case, fully unrolled: the operand of tap (r, c) starts r * 16 + c
               // rows into the patch, a compile-time distance once the row width (32 * STEPS bytes) is one
               uint32_t bc = b_lo;
@@ -611,6 +652,20 @@ bool encode_conv_input(CUtensorMap* map, const void* base, int N, int H, int W, 
             CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+// Input of a stride-2 convolution as pixel pairs {2C, W / 2, H, N} (W even): box = {2C bytes, 9 pairs, 33 rows, 1 image}.
+bool encode_conv_input_pairs(CUtensorMap* map, const void* base, int N, int H, int W, int C) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const int rb = 2 * C;
+  cuuint64_t dims[4] = {(cuuint64_t)rb, (cuuint64_t)(W / 2), (cuuint64_t)H, (cuuint64_t)N};
+  cuuint64_t strides[3] = {(cuuint64_t)rb, (cuuint64_t)W * C, (cuuint64_t)H * W * C};
+  cuuint32_t box[4] = {(cuuint32_t)rb, 9, 33, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapSwizzle sw = rb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : rb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 // Output {OC, OW, OH, N}: box = {BN, TW, TH, 1}, dense in shared memory; the store clips ragged edges.
 bool encode_conv_output(CUtensorMap* map, const void* base, int N, int OH, int OW, int OC, int BN, int TW, int TH) {
   EncodeTiledFn fn = encode_fn();
@@ -896,6 +951,30 @@ ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, i
   return g;
 }
 
+// Stride-2 3x3 over pixel pairs (see GemmTcParams::s2): what the launch needs beyond the geometry.
+static bool conv_s2_eligible(int W, int IC, int KH, int KW, int stride, int pad_l) {
+  static int off = -1;  // TB200_CONV_NO_S2=1: A/B aid
+  if (off < 0) { const char* e = getenv("TB200_CONV_NO_S2"); off = e && *e && *e != '0'; }
+  return !off && stride == 2 && KH == 3 && KW == 3 && (W % 2) == 0 && (IC == 16 || IC == 32 || IC == 64) && (pad_l == 0 || pad_l == 1);
+}
+
+ConvTcGeometry conv_tc_geometry_padded(int N, int OH, int OW, int W, int IC, int OC, int KH, int KW, int stride, int pad_l) {
+  ConvTcGeometry g = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW, stride);
+  if (!conv_s2_eligible(W, IC, KH, KW, stride, pad_l)) return g;
+  const int tiles_w = (OW + 7) / 8, tiles_h = (OH + 15) / 16;
+  const GemmTcGeometry n = gemm_tc_geometry(OC, g.Kpad, (long long)N * tiles_w * tiles_h * kBM);
+  const size_t stage = ((size_t)33 * 9 * 2 * IC + 1023) / 1024 * 1024;
+  const size_t need = (size_t)n.n_tiles * n.BN * g.Kpad + (size_t)kEpiGroups * kBM * (n.BN / n.gpt) + 3 * stage + 1024;
+  if (need > (size_t)kSmemBudget) return g;
+  g.s2 = 1;
+  g.halo = 0;
+  g.khs = 1;
+  g.TW = 8; g.TWv = 8; g.TH = 16;
+  g.tiles_w = tiles_w; g.tiles_h = tiles_h;
+  g.BN = n.BN; g.n_tiles = n.n_tiles; g.gpt = n.gpt;
+  return g;
+}
+
 bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w,
                        int OH, int OW) {
   if (IC % 16 != 0 || OC % 16 != 0 || stride_h != stride_w || stride_h < 1 || stride_h > 2 || dil_h != 1 || dil_w != 1 ||
@@ -908,10 +987,12 @@ bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int 
 }
 
 cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t stream) {
-  const ConvTcGeometry g = conv_tc_geometry(a.N, a.OH, a.OW, a.IC, a.OC, a.KH, a.KW, a.stride);
+  const ConvTcGeometry g = conv_tc_geometry_padded(a.N, a.OH, a.OW, a.W, a.IC, a.OC, a.KH, a.KW, a.stride, a.pad_l);
   const int patch_h = g.khs > 1 ? g.TH + a.KH - 1 : g.TH;  // rows of one load
   if (st->a != a.x) {
-    if (!encode_conv_input(&st->tmA, a.x, a.N, a.H, a.W, a.IC, g.row_bytes, g.TW, patch_h, a.stride)) return cudaErrorInvalidValue;
+    if (g.s2 ? !encode_conv_input_pairs(&st->tmA, a.x, a.N, a.H, a.W, a.IC)
+             : !encode_conv_input(&st->tmA, a.x, a.N, a.H, a.W, a.IC, g.row_bytes, g.TW, patch_h, a.stride))
+      return cudaErrorInvalidValue;
     st->a = a.x;
   }
   if (st->w != a.w) {
@@ -948,13 +1029,18 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   p.halo = g.halo;
   p.tw_valid = g.TWv;
   p.kcols = g.halo ? a.KW : 1;
-  p.k_loads = g.halo ? g.icb_per_tap : g.khs > 1 ? a.KW * g.icb_per_tap : g.k_blocks;
+  p.k_loads = g.s2 ? 1 : g.halo ? g.icb_per_tap : g.khs > 1 ? a.KW * g.icb_per_tap : g.k_blocks;
   p.patch_rows = patch_h * g.TW;
+  p.s2 = g.s2;
+  p.a_row_bytes = 2 * a.IC;
+  p.s2_stage_bytes = (int)(((size_t)33 * 9 * 2 * a.IC + 1023) / 1024 * 1024);
+  p.s2_pair0 = a.pad_l == 1 ? -1 : 0;
   p.corr = a.corr; p.rcls = a.rcls; p.ccls = a.ccls; p.cls_nonzero = a.cls_nonzero; p.ncc = a.ncc;
   const size_t w_bytes = (size_t)g.n_tiles * g.BN * g.Kpad;
-  p.w_resident = g.halo || w_bytes <= (size_t)kResidentWeightBytes;
-  const size_t stage_bytes = (size_t)(g.khs > 1 ? p.patch_rows : kBM) * g.row_bytes +
-                             (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes * g.khs);
+  p.w_resident = g.halo || g.s2 || w_bytes <= (size_t)kResidentWeightBytes;
+  const size_t stage_bytes = g.s2 ? (size_t)p.s2_stage_bytes
+                                  : (size_t)(g.khs > 1 ? p.patch_rows : kBM) * g.row_bytes +
+                                        (p.w_resident ? 0 : (size_t)g.BN * g.row_bytes * g.khs);
   const size_t staging_bytes = (size_t)kEpiGroups * kBM * (g.BN / g.gpt);
   const size_t ring_budget = (size_t)kSmemBudget - 1024 - (p.w_resident ? w_bytes : 0) - staging_bytes;
   int stages = (int)(ring_budget / stage_bytes);

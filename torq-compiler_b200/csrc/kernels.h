@@ -170,8 +170,11 @@ struct ConvTcGeometry {
   int khs;                                     // kernel rows served by one load of TH + khs - 1 input rows (1 = a load per tap)
   int halo;                                    // 1: one load per tile and channel block serves every tap (TWv valid columns of TW = 16)
   int TWv;                                     // output columns a tile produces (TW unless halo)
+  int s2;                                      // 1: stride-2 3x3 over one patch of pixel pairs per tile (16 x 8 outputs)
 };
 ConvTcGeometry conv_tc_geometry(int N, int OH, int OW, int IC, int OC, int KH, int KW, int stride);
+// The geometry the launch uses: as above, plus the stride-2 pixel-pair form, which depends on the input width and the left pad.
+ConvTcGeometry conv_tc_geometry_padded(int N, int OH, int OW, int W, int IC, int OC, int KH, int KW, int stride, int pad_l);
 bool conv_tc_supported(int N, int H, int W, int IC, int OC, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w,
                        int OH, int OW);
 struct ConvTcArgs {

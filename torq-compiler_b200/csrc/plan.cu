@@ -868,8 +868,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         // row count no longer depends on the kernel size and the tensor cores take those too)
         if (!fc && !pointwise && op.weight_zp == 0 && !force_simt() &&
             conv_tc_supported(N, H, W, IC, OC, KH, KW, op.stride_h, op.stride_w, op.dil_h, op.dil_w, OH, OW) &&
-            (IC != 16 || conv_tc_geometry(N, OH, OW, IC, OC, KH, KW, op.stride_h).halo)) {
-          const ConvTcGeometry geo = conv_tc_geometry(N, OH, OW, IC, OC, KH, KW, op.stride_h);
+            (IC != 16 || conv_tc_geometry_padded(N, OH, OW, W, IC, OC, KH, KW, op.stride_h, op.pad_l).halo ||
+             conv_tc_geometry_padded(N, OH, OW, W, IC, OC, KH, KW, op.stride_h, op.pad_l).s2)) {
+          const ConvTcGeometry geo = conv_tc_geometry_padded(N, OH, OW, W, IC, OC, KH, KW, op.stride_h, op.pad_l);
           ConvTcArgs ca{};
           ca.N = N; ca.H = H; ca.W = W; ca.IC = IC; ca.OC = OC; ca.KH = KH; ca.KW = KW; ca.OH = OH; ca.OW = OW;
           ca.stride = op.stride_h; ca.pad_t = op.pad_t; ca.pad_l = op.pad_l;
