@@ -9,6 +9,7 @@
 // with sums over ALL K taps; the izp terms are constants per output channel and
 // arrive folded into ChanParams::bias. int32 wrap-around keeps this exact.
 #include "kernels.h"
+#include "dependent_launch.cuh"
 
 namespace tb200 {
 
@@ -281,6 +282,8 @@ __global__ void __launch_bounds__(128) conv2d_smallic_kernel(ConvArgs a) {
 // Weight rows are Kpad bytes apart (K = TAPS * 16 is a multiple of 16, Kpad of 32).
 template <int TAPS>
 __global__ void __launch_bounds__(128) conv2d_c16_kernel(ConvArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   extern __shared__ uint4 w16[];  // [OC][TAPS]
   for (int i = threadIdx.x; i < a.OC * TAPS; i += blockDim.x) {
     const int oc = i / TAPS, t = i - oc * TAPS;
@@ -392,6 +395,8 @@ __global__ void __launch_bounds__(256) matmul_int_kernel(const TIn* __restrict__
 constexpr int kStemPix = 4;
 template <int EPI, bool LUT>
 __global__ void __launch_bounds__(128) conv2d_stem333_kernel(ConvArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   extern __shared__ __align__(16) uint32_t stem_s[];  // [OC][8] weight words (word 7 zero), [OC] Q4 records, 256-byte table
   uint4* w_s = reinterpret_cast<uint4*>(stem_s);
   int4* q_s = reinterpret_cast<int4*>(stem_s + (size_t)a.OC * 8);
@@ -610,16 +615,16 @@ void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
     const int taps = a.KH * a.KW;
     const size_t smem = (size_t)a.OC * taps * 16;
     if (taps == 9) {
-      conv2d_c16_kernel<9><<<blocks, 128, smem, stream>>>(a);
+      launch_dependent(conv2d_c16_kernel<9>, dim3(blocks), dim3(128), smem, stream, a);
     } else if (taps == 1) {
-      conv2d_c16_kernel<1><<<blocks, 128, smem, stream>>>(a);
+      launch_dependent(conv2d_c16_kernel<1>, dim3(blocks), dim3(128), smem, stream, a);
     } else {
       static std::atomic<unsigned long long> attr{0};  // function attributes are per device
       if (first_use_on_device(attr)) {
         cudaFuncSetAttribute(conv2d_c16_kernel<25>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 25 * 16);
         mark_used_on_device(attr);
       }
-      conv2d_c16_kernel<25><<<blocks, 128, smem, stream>>>(a);
+      launch_dependent(conv2d_c16_kernel<25>, dim3(blocks), dim3(128), smem, stream, a);
     }
     return;
   }
@@ -627,11 +632,11 @@ void launch_conv2d_simt(const ConvArgs& a, cudaStream_t stream) {
     const unsigned blocks = (unsigned)((P + 128 * kStemPix - 1) / (128 * kStemPix));
     const size_t smem = (size_t)a.OC * (32 + 16) + 256;
     if (a.lut) {
-      if (a.epi == 1) conv2d_stem333_kernel<1, true><<<blocks, 128, smem, stream>>>(a);
-      else conv2d_stem333_kernel<2, true><<<blocks, 128, smem, stream>>>(a);
+      if (a.epi == 1) launch_dependent(conv2d_stem333_kernel<1, true>, dim3(blocks), dim3(128), smem, stream, a);
+      else launch_dependent(conv2d_stem333_kernel<2, true>, dim3(blocks), dim3(128), smem, stream, a);
     } else {
-      if (a.epi == 1) conv2d_stem333_kernel<1, false><<<blocks, 128, smem, stream>>>(a);
-      else conv2d_stem333_kernel<2, false><<<blocks, 128, smem, stream>>>(a);
+      if (a.epi == 1) launch_dependent(conv2d_stem333_kernel<1, false>, dim3(blocks), dim3(128), smem, stream, a);
+      else launch_dependent(conv2d_stem333_kernel<2, false>, dim3(blocks), dim3(128), smem, stream, a);
     }
     return;
   }

@@ -18,6 +18,7 @@
 #include <cstdlib>
 
 #include "kernels.h"
+#include "dependent_launch.cuh"
 
 namespace tb200 {
 
@@ -188,6 +189,8 @@ __global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
 // reads its own 4 channels of its 3 or 4 columns from the tile and proceeds exactly as dw3x3_kernel.
 template <int STRIDE, int EPI>
 __global__ void __launch_bounds__(128, STRIDE == 1 ? 6 : 8) dw3x3_tile_kernel(DwArgs a, int cg_log2, int cchunks) {
+  grid_dependency_release();
+  grid_dependency_wait();
   constexpr int TW = STRIDE == 1 ? 2 : 1;
   constexpr int NCOL = STRIDE == 1 ? 4 : 3;
   constexpr int NR = (kRows - 1) * STRIDE + 3;
@@ -422,13 +425,13 @@ void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
     const size_t smem = (size_t)nr * iwt * (4 << cg_log2);
     const dim3 grid((unsigned)(tiles * cchunks), (unsigned)((a.OH + kRows - 1) / kRows), (unsigned)a.N);
     if (S == 1) {
-      if (a.epi == 1) dw3x3_tile_kernel<1, 1><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
-      else if (a.epi == 2) dw3x3_tile_kernel<1, 2><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
-      else dw3x3_tile_kernel<1, 0><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      if (a.epi == 1) launch_dependent(dw3x3_tile_kernel<1, 1>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
+      else if (a.epi == 2) launch_dependent(dw3x3_tile_kernel<1, 2>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
+      else launch_dependent(dw3x3_tile_kernel<1, 0>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
     } else {
-      if (a.epi == 1) dw3x3_tile_kernel<2, 1><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
-      else if (a.epi == 2) dw3x3_tile_kernel<2, 2><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
-      else dw3x3_tile_kernel<2, 0><<<grid, 128, smem, stream>>>(a, cg_log2, cchunks);
+      if (a.epi == 1) launch_dependent(dw3x3_tile_kernel<2, 1>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
+      else if (a.epi == 2) launch_dependent(dw3x3_tile_kernel<2, 2>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
+      else launch_dependent(dw3x3_tile_kernel<2, 0>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
     }
   } else if (a.wq && depthwise3x3_supported(a)) {
     const int tw = a.stride_h == 1 ? 2 : 1;

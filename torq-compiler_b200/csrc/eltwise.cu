@@ -3,6 +3,7 @@
 // resize. 128-bit accesses wherever the channel count allows; grids sized in
 // whole multiples of the SM count with grid-stride loops.
 #include "kernels.h"
+#include "dependent_launch.cuh"
 
 namespace tb200 {
 
@@ -21,6 +22,8 @@ inline unsigned grid_for(long long work_items, int per_block = kThreads) {
 // ---- max pool: torq_hl.maxpool2d (PoolingPattern.cpp:128-258) ----
 template <int VEC>  // channels per thread: 16 (uint4) or 1
 __global__ void __launch_bounds__(kThreads) maxpool_kernel(PoolArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   const int groups = a.C / VEC;
   const long long total = (long long)a.N * a.OH * a.OW * groups;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -130,6 +133,8 @@ __device__ __forceinline__ void reciprocal_scale(uint32_t count, int32_t& mult, 
 constexpr int kAvgMaxTaps = 256;
 template <int VEC>  // 16, 4 or 1 channels per thread
 __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ int4 by_count[kAvgMaxTaps + 1];
   for (int c = threadIdx.x; c <= a.KH * a.KW; c += blockDim.x) {
     int32_t mult, shift;
@@ -194,6 +199,8 @@ __global__ void __launch_bounds__(kThreads) avgpool_kernel(PoolArgs a) {
 // Large windows over few outputs (the global pool at the end of a classifier: 7x7 -> 1x1): a warp per output pixel
 // and group of 16 channels, the taps spread over the lanes, sums combined by shuffles. Same arithmetic as above.
 __global__ void __launch_bounds__(kThreads) avgpool_warp_kernel(PoolArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ int4 by_count[kAvgMaxTaps + 1];
   for (int c = threadIdx.x; c <= a.KH * a.KW; c += blockDim.x) {
     int32_t mult, shift;
@@ -259,6 +266,8 @@ __global__ void __launch_bounds__(kThreads) avgpool_warp_kernel(PoolArgs a) {
 // term, chosen by the planner when it can bound |operand sum or product| (it evaluates the same two tables).
 template <int EPI>
 __global__ void __launch_bounds__(kThreads) binary_kernel(BinaryArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ int ta[256], tb[256];  // indexed by the raw byte
   {
     const bool dr = a.double_round != 0;
@@ -301,6 +310,8 @@ __global__ void __launch_bounds__(kThreads) binary_kernel(BinaryArgs a) {
 __global__ void __launch_bounds__(kThreads) table_kernel(const int8_t* __restrict__ x,
                                                          const int8_t* __restrict__ table,
                                                          int8_t* __restrict__ out, long long n) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ uint8_t lut[256];
   // index by the raw byte: entry for byte b is table[(int8)b + 128]
   lut[threadIdx.x] = (uint8_t)table[(int)(int8_t)threadIdx.x + 128];
@@ -325,6 +336,8 @@ __global__ void __launch_bounds__(kThreads) table_kernel(const int8_t* __restric
 
 // ---- standalone rescale i8 -> i8 (PatternUtils.cpp:426-435,3441-3451) ----
 __global__ void __launch_bounds__(kThreads) rescale_kernel(RescaleArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   const long long total = a.rows * a.C;
   const bool dr = a.double_round != 0;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -342,6 +355,8 @@ __global__ void __launch_bounds__(kThreads) rescale_kernel(RescaleArgs a) {
 // (multiplier 2^30, shift 30, equal zero points, full clamp range), i.e. a strided copy
 template <bool IDENT>
 __global__ void __launch_bounds__(kThreads) rescale_vec16_kernel(RescaleArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   const int cv = a.C >> 4;
   const long long total = a.rows * cv;
   const bool dr = a.double_round != 0;
@@ -371,6 +386,8 @@ __global__ void __launch_bounds__(kThreads) rescale_vec16_kernel(RescaleArgs a) 
 // Per-tensor constants: the rescale is a function of the input byte alone, so it runs as a 256-entry table
 // in shared memory (one entry per thread, filled by the same requant), 16 channels per thread.
 __global__ void __launch_bounds__(kThreads) rescale_lut_vec16_kernel(RescaleArgs a) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ uint8_t lut[256];  // indexed by the raw byte
   {
     const ChanParams cp = a.chan[0];
@@ -401,6 +418,8 @@ __global__ void __launch_bounds__(kThreads) rescale_lut_vec16_kernel(RescaleArgs
 // ---- nearest 2x (PatternUtils.cpp:489-491): out[y,x] = in[y/2, x/2] ----
 __global__ void __launch_bounds__(kThreads) resize_nn2x_vec16_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ out,
                                                                      int N, int H, int W, int C) {
+  grid_dependency_release();
+  grid_dependency_wait();
   const int cv = C >> 4;
   const long long total = (long long)N * 2 * H * 2 * W * cv;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -442,10 +461,10 @@ void launch_maxpool(const PoolArgs& a, cudaStream_t stream) {
   }
   if ((a.C & 15) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C / 16);
-    maxpool_kernel<16><<<grid_for(total), kThreads, 0, stream>>>(a);
+    launch_dependent(maxpool_kernel<16>, dim3(grid_for(total)), dim3(kThreads), 0, stream, a);
   } else {
     long long total = (long long)a.N * a.OH * a.OW * a.C;
-    maxpool_kernel<1><<<grid_for(total), kThreads, 0, stream>>>(a);
+    launch_dependent(maxpool_kernel<1>, dim3(grid_for(total)), dim3(kThreads), 0, stream, a);
   }
 }
 
@@ -453,39 +472,39 @@ void launch_avgpool(const PoolArgs& a, cudaStream_t stream) {
   if ((a.C & 15) == 0 && ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C / 16);
     // few outputs with many taps each: spread the taps over a warp
-    if (a.KH * a.KW >= 16 && total < 148ll * 2048) avgpool_warp_kernel<<<grid_for(total * 32), kThreads, 0, stream>>>(a);
-    else avgpool_kernel<16><<<grid_for(total), kThreads, 0, stream>>>(a);
+    if (a.KH * a.KW >= 16 && total < 148ll * 2048) launch_dependent(avgpool_warp_kernel, dim3(grid_for(total * 32)), dim3(kThreads), 0, stream, a);
+    else launch_dependent(avgpool_kernel<16>, dim3(grid_for(total)), dim3(kThreads), 0, stream, a);
   } else if ((a.C & 3) == 0) {
     long long total = (long long)a.N * a.OH * a.OW * (a.C / 4);
-    avgpool_kernel<4><<<grid_for(total), kThreads, 0, stream>>>(a);
+    launch_dependent(avgpool_kernel<4>, dim3(grid_for(total)), dim3(kThreads), 0, stream, a);
   } else {
     long long total = (long long)a.N * a.OH * a.OW * a.C;
-    avgpool_kernel<1><<<grid_for(total), kThreads, 0, stream>>>(a);
+    launch_dependent(avgpool_kernel<1>, dim3(grid_for(total)), dim3(kThreads), 0, stream, a);
   }
 }
 
 void launch_binary(const BinaryArgs& a, cudaStream_t stream) {
-  if (a.epi == 1) binary_kernel<1><<<grid_for((a.n + 15) / 16), kThreads, 0, stream>>>(a);
-  else if (a.epi == 2) binary_kernel<2><<<grid_for((a.n + 15) / 16), kThreads, 0, stream>>>(a);
-  else binary_kernel<0><<<grid_for((a.n + 15) / 16), kThreads, 0, stream>>>(a);
+  if (a.epi == 1) launch_dependent(binary_kernel<1>, dim3(grid_for((a.n + 15) / 16)), dim3(kThreads), 0, stream, a);
+  else if (a.epi == 2) launch_dependent(binary_kernel<2>, dim3(grid_for((a.n + 15) / 16)), dim3(kThreads), 0, stream, a);
+  else launch_dependent(binary_kernel<0>, dim3(grid_for((a.n + 15) / 16)), dim3(kThreads), 0, stream, a);
 }
 
 void launch_table(const int8_t* x, const int8_t* table, int8_t* out, long long n, cudaStream_t stream) {
-  table_kernel<<<grid_for((n + 15) / 16), kThreads, 0, stream>>>(x, table, out, n);
+  launch_dependent(table_kernel, dim3(grid_for((n + 15) / 16)), dim3(kThreads), 0, stream, x, table, out, n);
 }
 
 void launch_rescale(const RescaleArgs& a, cudaStream_t stream) {
   const bool vec = (a.C & 15) == 0 && (a.out_row_stride & 15) == 0 && (a.out_col_offset & 15) == 0 &&
                    ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0;
-  if (vec && a.identity) rescale_vec16_kernel<true><<<grid_for(a.rows * (a.C >> 4)), kThreads, 0, stream>>>(a);
-  else if (vec && !a.per_channel) rescale_lut_vec16_kernel<<<grid_for(a.rows * (a.C >> 4)), kThreads, 0, stream>>>(a);
-  else if (vec) rescale_vec16_kernel<false><<<grid_for(a.rows * (a.C >> 4)), kThreads, 0, stream>>>(a);
-  else rescale_kernel<<<grid_for(a.rows * a.C), kThreads, 0, stream>>>(a);
+  if (vec && a.identity) launch_dependent(rescale_vec16_kernel<true>, dim3(grid_for(a.rows * (a.C >> 4))), dim3(kThreads), 0, stream, a);
+  else if (vec && !a.per_channel) launch_dependent(rescale_lut_vec16_kernel, dim3(grid_for(a.rows * (a.C >> 4))), dim3(kThreads), 0, stream, a);
+  else if (vec) launch_dependent(rescale_vec16_kernel<false>, dim3(grid_for(a.rows * (a.C >> 4))), dim3(kThreads), 0, stream, a);
+  else launch_dependent(rescale_kernel, dim3(grid_for(a.rows * a.C)), dim3(kThreads), 0, stream, a);
 }
 
 void launch_resize_nn2x(const int8_t* x, int8_t* out, int N, int H, int W, int C, cudaStream_t stream) {
   if ((C & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
-    resize_nn2x_vec16_kernel<<<grid_for((long long)N * 4 * H * W * (C >> 4)), kThreads, 0, stream>>>(x, out, N, H, W, C);
+    launch_dependent(resize_nn2x_vec16_kernel, dim3(grid_for((long long)N * 4 * H * W * (C >> 4))), dim3(kThreads), 0, stream, x, out, N, H, W, C);
     return;
   }
   resize_nn2x_kernel<<<grid_for((long long)N * 4 * H * W * C), kThreads, 0, stream>>>(x, out, N, H, W, C);

@@ -46,6 +46,7 @@
 
 #include "kernels.h"
 #include "tcgen05_ptx.cuh"
+#include "dependent_launch.cuh"
 
 namespace tb200 {
 
@@ -165,6 +166,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  // everything above touched only shared memory, TMEM and constants; the next kernel may be scheduled from here on,
+  // and what follows waits for the kernel before this one (the producer first sends for the resident weights)
+  if (threadIdx.x == 0) grid_dependency_release();
+  if (threadIdx.x != 0) grid_dependency_wait();
 
   // tile t -> (n, m) with n the slow index: a CTA keeps one n tile (its constants) for a long run
   if (warp == 0) {
@@ -177,6 +182,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           for (int kb = 0; kb < p.k_blocks; kb++)
             tma_load_2d(smem_w + (uint32_t)(n * p.k_blocks + kb) * w_tile_bytes, &tmB, kb * p.row_bytes, n * p.BN, bw);
       }
+      grid_dependency_wait();
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -877,8 +883,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
-  gemm_kernel_for(false, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr)<<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  return cudaGetLastError();
+  return launch_dependent(gemm_kernel_for(false, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr), dim3(grid), dim3(kThreads), smem, stream, st->tmA, st->tmB, st->tmC, p);
 }
 
 // ---- convolution as implicit GEMM ----
@@ -1074,8 +1079,7 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
-  gemm_kernel_for(true, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr)<<<grid, kThreads, smem, stream>>>(st->tmA, st->tmB, st->tmC, p);
-  return cudaGetLastError();
+  return launch_dependent(gemm_kernel_for(true, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr), dim3(grid), dim3(kThreads), smem, stream, st->tmA, st->tmB, st->tmC, p);
 }
 
 }  // namespace tb200
