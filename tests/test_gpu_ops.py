@@ -353,6 +353,58 @@ def test_chain_with_intermediates_and_host_call(device):
     _check(device, g, [x], host_call=True)
 
 
+@pytest.mark.parametrize("shape,OC,conv_first,double_round", [
+    ((2, 28, 28, 96), 32, True, True),      # the residual connection of an inverted-residual block
+    ((2, 28, 28, 96), 32, False, True),     # the convolution's result as the add's second operand
+    ((1, 56, 56, 48), 24, True, True),      # 24 channels: grouped rows
+    ((3, 14, 14, 64), 64, True, False),     # single rounding: the record without the sign term
+    ((1, 9, 7, 160), 80, False, True),      # ragged last tile
+])
+def test_pointwise_conv_with_fused_residual_add(device, shape, OC, conv_first, double_round):
+    """With TB200_ADD_FUSION=1 a rescaled add whose one operand is the only use of a 1x1 convolution's result runs in
+    that convolution's epilogue (one launch, the product never stored): bit-exact against the oracle, which runs the
+    two ops apart, and against the default plan (two launches); a product with a second reader keeps its own launch."""
+    import os
+    from torq_b200.runtime import Executable
+    rng = np.random.default_rng(shape[1] * 31 + OC)
+    x = rng.integers(-128, 128, shape, dtype=np.int8)
+    r = rng.integers(-128, 128, shape[:3] + (OC,), dtype=np.int8)
+    w = rng.integers(-127, 128, (OC, 1, 1, shape[3]), dtype=np.int8)
+    m, s = quantize_multipliers(rng.uniform(0.5, 1.5, OC) * 40.0 / (np.sqrt(shape[3]) * 74 * 74))
+
+    def build(second_reader):
+        g = Graph()
+        xi, ri = g.input(shape), g.input(r.shape)
+        h = g.conv2d(xi, w, np.round(rng.normal(0, 500, OC)).astype(np.int32) * 0 + 77, m, s, input_zp=-5, out_zp=4)
+        kw = dict(a_zp=4 if conv_first else -2, a_ms=(1 << 30, 11), b_zp=-2 if conv_first else 4, b_ms=(1395864371, 12),
+                  out_ms=(1093202297, 49), out_zp=-3, clamp=(-110, 120), double_round=double_round)
+        y = g.add(h, ri, **kw) if conv_first else g.add(ri, h, **kw)
+        g.output(y)
+        if second_reader:
+            g.output(g.table(h, np.arange(-128, 128, dtype=np.int8)[::-1].copy()))
+        return g
+
+    g = build(False)
+    apart = _check(device, g, [x, r])[0]
+    ex = Executable(device, g.serialize())
+    assert ex.op_kernels() == ["gemm_i8_tcgen05", "binary_rescale"]
+    ex.destroy()
+    os.environ["TB200_ADD_FUSION"] = "1"
+    try:
+        ex = Executable(device, g.serialize())
+        assert ex.op_kernels() == ["gemm_i8_tcgen05", "(add in the convolution's epilogue)"] and ex.launch_count == 1, ex.op_kernels()
+        ex.destroy()
+        got = _check(device, g, [x, r])[0]
+        assert (apart == got).all()
+        g2 = build(True)
+        _check(device, g2, [x, r])
+        ex = Executable(device, g2.serialize())
+        assert "binary_rescale" in ex.op_kernels()
+        ex.destroy()
+    finally:
+        del os.environ["TB200_ADD_FUSION"]
+
+
 GEMM_CASES = [
     # M, K, N : the tensor-core path (K % 16 == 0); tails in M, N and K all appear
     (1, 16, 16), (127, 16, 24), (128, 32, 192), (129, 48, 16), (300, 144, 24), (1000, 160, 960), (513, 960, 320),

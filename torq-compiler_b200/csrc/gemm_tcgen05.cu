@@ -108,6 +108,12 @@ struct GemmTcParams {
   const uint8_t* cls_nonzero;  // [classes] 1 when the class has a non-zero correction
   int ncc;              // column classes
   const int8_t* lut;    // 256-entry table applied to the int8 result (a fused tosa.table), or null
+  // ADD kernels: out = clamp(q4(t_self[result] + t_other[res])), the operand tables built in the prologue by the
+  // same apply_scale_32 as binary_kernel; res is laid out like out
+  const int8_t* res;
+  int self_zp, self_mult, self_shift, self_lshift, other_zp, other_mult, other_shift, other_lshift, add_dr, add_sign;
+  int add_clamp_min, add_clamp_max;
+  int4 add_q4;
   int tma_store;        // stage the output tile in shared memory and write it with one TMA store
   uint32_t staging_off; // byte offset of the staging buffers inside dynamic shared memory
   int* status;
@@ -120,7 +126,7 @@ struct GemmTcParams {
 // the sign term of DOUBLE_ROUND; 3 = as 1 with the clamp being the whole int8 range (two saturating packs).
 // LUT: a 256-entry table is applied to the result. Integer instructions issue at half rate on this machine,
 // so whatever the epilogue does per output is a template choice, not a branch.
-template <int EPI, bool CONV, bool LUT>
+template <int EPI, bool CONV, bool LUT, bool ADD = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, GemmTcParams p) {
@@ -130,6 +136,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(16) int4 cp_s[kEpiGroups][128];  // per epilogue group: the Q4 records of its current n tile
   __shared__ __align__(16) uint8_t lut_s[256];           // fused table, indexed by value + 128
+  __shared__ int add_t[ADD ? 512 : 1];                   // fused add: operand tables by raw byte, [0..255] own result, [256..511] other
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -156,6 +163,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (LUT && threadIdx.x >= 64 && threadIdx.x < 64 + 256) lut_s[threadIdx.x - 64] = (uint8_t)p.lut[threadIdx.x - 64];
+  if (ADD && threadIdx.x >= 64 && threadIdx.x < 64 + 256) {
+    const int v = (int)(int8_t)(threadIdx.x - 64);
+    add_t[threadIdx.x - 64] = apply_scale_32((v - p.self_zp) * (1 << p.self_lshift), p.self_mult, p.self_shift, p.add_dr != 0);
+    add_t[256 + threadIdx.x - 64] = apply_scale_32((v - p.other_zp) * (1 << p.other_lshift), p.other_mult, p.other_shift, p.add_dr != 0);
+  }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                  "r"((uint32_t)p.tmem_cols)
@@ -496,6 +508,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(astage * p.acc_stride + col_half);
         int8_t* orow = p.out + (long long)row * p.ldc + (long long)n * p.BN + col_half;
+        const int8_t* rrow = ADD ? p.res + (long long)row * p.ldc + (long long)n * p.BN + col_half : nullptr;
         const int ncol0 = n * p.BN + col_half;
         if (p.tma_store) {
           // this group's previous store must have read the staging tile before it is overwritten
@@ -524,6 +537,29 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               }
             }
             w4[g] = EPI == 3 ? sat_pack4(r[0], r[1], r[2], r[3]) : clamp_pack4(r[0], r[1], r[2], r[3], lo2, hi2);
+            if (ADD) {
+              // the other operand's four bytes (same row and columns of a tensor laid out like the result)
+              uint32_t xo = 0;
+              if (row < p.M) {
+                if (vec_ok && ncol0 + c0 + g * 4 + 4 <= p.N) {
+                  xo = *reinterpret_cast<const uint32_t*>(rrow + c0 + g * 4);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 4; j++)
+                    if (ncol0 + c0 + g * 4 + j < p.N) xo |= (uint32_t)(uint8_t)rrow[c0 + g * 4 + j] << (8 * j);
+                }
+              }
+              int s4[4];
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                const int v = add_t[(w4[g] >> (8 * j)) & 0xff] + add_t[256 + ((xo >> (8 * j)) & 0xff)];
+                const int v4 = v * 4 + p.add_q4.x;
+                const int neg = p.add_sign ? (v4 >> 31) : 0;
+                const int r1 = (__mulhi(v4, p.add_q4.y) + p.add_q4.z + neg + neg) >> p.add_q4.w;
+                s4[j] = max(p.add_clamp_min, min(p.add_clamp_max, r1));
+              }
+              w4[g] = (uint32_t)(s4[0] & 0xff) | ((uint32_t)(s4[1] & 0xff) << 8) | ((uint32_t)(s4[2] & 0xff) << 16) | ((uint32_t)s4[3] << 24);
+            }
             if (LUT) {  // out = table[value + 128], byte by byte
               const uint32_t x = w4[g] ^ 0x80808080u;
               w4[g] = (uint32_t)lut_s[x & 0xff] | ((uint32_t)lut_s[(x >> 8) & 0xff] << 8) |
@@ -708,7 +744,11 @@ int read_gemm_trace(unsigned long long* out, int n) {
 namespace {
 typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, GemmTcParams);
 // [EPI][LUT] for the plain GEMM and for the implicit-GEMM convolution
-GemmKernelFn gemm_kernel_for(bool conv, int epi, bool lut) {
+GemmKernelFn gemm_kernel_for(bool conv, int epi, bool lut, bool add = false) {
+  // the fused residual add exists for the plain GEMM without a table
+  static const GemmKernelFn addk[4] = {gemm_i8_tc_kernel<0, false, false, true>, gemm_i8_tc_kernel<1, false, false, true>,
+                                       gemm_i8_tc_kernel<2, false, false, true>, gemm_i8_tc_kernel<3, false, false, true>};
+  if (add) return addk[epi];
   static const GemmKernelFn plain[4][2] = {
       {gemm_i8_tc_kernel<0, false, false>, gemm_i8_tc_kernel<0, false, true>},
       {gemm_i8_tc_kernel<1, false, false>, gemm_i8_tc_kernel<1, false, true>},
@@ -730,6 +770,10 @@ cudaError_t gemm_kernels_set_smem(bool conv) {
       const cudaError_t err = cudaFuncSetAttribute(gemm_kernel_for(conv, e, l != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
       if (err != cudaSuccess) return err;
     }
+  for (int e = 0; e < 4 && !conv; e++) {
+    const cudaError_t err = cudaFuncSetAttribute(gemm_kernel_for(false, e, false, true), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (err != cudaSuccess) return err;
+  }
   return cudaSuccess;
 }
 // EPI 1 with a clamp that is the whole int8 range packs with two saturating conversions (EPI 3)
@@ -883,7 +927,22 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
-  return launch_dependent(gemm_kernel_for(false, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr), dim3(grid), dim3(kThreads), smem, stream, st->tmA, st->tmB, st->tmC, p);
+  const bool fused_add = a.res != nullptr;
+  if (fused_add) {
+    if (a.lut || a.add.kind != 0 || a.add.epi == 0) return cudaErrorInvalidValue;
+    const BinaryArgs& d = a.add;
+    p.res = a.res;
+    const bool sa = a.add_self_is_a != 0;
+    p.self_zp = sa ? d.a_zp : d.b_zp; p.self_mult = sa ? d.a_mult : d.b_mult; p.self_shift = sa ? d.a_shift : d.b_shift;
+    p.self_lshift = sa ? d.a_lshift : d.b_lshift;
+    p.other_zp = sa ? d.b_zp : d.a_zp; p.other_mult = sa ? d.b_mult : d.a_mult; p.other_shift = sa ? d.b_shift : d.a_shift;
+    p.other_lshift = sa ? d.b_lshift : d.a_lshift;
+    p.add_dr = d.double_round;
+    p.add_sign = d.epi == 1;
+    p.add_clamp_min = d.clamp_min; p.add_clamp_max = d.clamp_max;
+    p.add_q4 = d.q4;
+  }
+  return launch_dependent(gemm_kernel_for(false, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr, fused_add), dim3(grid), dim3(kThreads), smem, stream, st->tmA, st->tmB, st->tmC, p);
 }
 
 // ---- convolution as implicit GEMM ----

@@ -153,6 +153,11 @@ struct GemmTcArgs {
   const int4* q4;         // [n_tiles * BN] Q4 records when epi != 0 (common.cuh); the output zero point rides in them
   int* status;            // device status word: a kernel whose bounded wait expires writes a code here
   const int8_t* lut;      // 256-entry table applied to the int8 result, or null
+  // A rescaled add fused behind the product (a residual connection): out = rescale(t_self[product] + t_other[res]),
+  // the operand-side rescales as tables exactly as binary_kernel builds them. res has the layout of out.
+  const int8_t* res;      // the other operand of the add, or null
+  BinaryArgs add;         // its parameters (kind 0, epi 1 or 2); a_* belong to the product when add_self_is_a
+  int add_self_is_a;
 };
 struct GemmTcState;       // cached tensor maps of one GEMM step
 GemmTcState* gemm_tc_state_new();

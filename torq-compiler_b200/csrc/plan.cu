@@ -209,6 +209,37 @@ long long host_apply_scale_32(long long value, int mult, int shift, bool double_
   return (long long)(int32_t)(uint32_t)(unsigned long long)((v * (long long)mult + round) >> shift);
 }
 
+// The parameters of a rescaled add / sub / mul without its pointers and size. The operand-side rescales are functions
+// of one byte: both tables are evaluated here as the kernel does, the value that reaches the output rescale is
+// bounded, and the 32-bit form of that rescale is taken when it is exact. False: a left shift outside [0, 22].
+static bool binary_args_of(const tb200_op_t& op, BinaryArgs& a) {
+  a = BinaryArgs{};
+  a.kind = op.kind == TB200_OP_ADD ? 0 : op.kind == TB200_OP_SUB ? 1 : 2;
+  a.a_zp = op.in0_zp; a.a_mult = op.in0_mult; a.a_shift = op.in0_shift;
+  a.b_zp = op.in1_zp; a.b_mult = op.in1_mult; a.b_shift = op.in1_shift;
+  a.out_mult = op.out_mult; a.out_shift = op.out_shift; a.out_zp = op.out_zp;
+  a.double_round = op.double_round; a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
+  if (op.i0 < 0 || op.i0 > 22 || op.i1 < 0 || op.i1 > 22) return false;
+  for (int s : {op.in0_shift, op.in1_shift, op.out_shift})
+    if (s < 2 || s > 62) return false;
+  a.a_lshift = op.i0; a.b_lshift = op.i1;
+  long long ma = 0, mb = 0;
+  for (int v = -128; v < 128; v++) {
+    const long long ra = host_apply_scale_32((long long)(v - a.a_zp) * (1ll << a.a_lshift), a.a_mult, a.a_shift, op.double_round != 0);
+    const long long rb = host_apply_scale_32((long long)(v - a.b_zp) * (1ll << a.b_lshift), a.b_mult, a.b_shift, op.double_round != 0);
+    ma = std::max(ma, ra < 0 ? -ra : ra);
+    mb = std::max(mb, rb < 0 ? -rb : rb);
+  }
+  const long long bound = a.kind == 2 ? ma * mb : ma + mb;
+  ChanParams cp{};
+  cp.mult = a.out_mult; cp.shift = a.out_shift; cp.bias = 0;
+  std::vector<int4> q4;
+  a.epi = (ma < (1ll << 31) && mb < (1ll << 31) && bound < (1ll << 29))
+              ? Builder::q4_params({cp}, {bound}, op.double_round != 0, a.out_zp, a.clamp_min, q4) : 0;
+  if (a.epi) a.q4 = q4[0];
+  return true;
+}
+
 int conv_out_dim(int i, int k, int s, int d, int p0, int p1) { return (i + p0 + p1 - d * (k - 1) - 1) / s + 1; }
 
 bool force_simt() {
@@ -216,6 +247,37 @@ bool force_simt() {
   return e && *e && *e != '0';
 }
 
+
+// Rows of a 1x1 convolution / FullyConnected product that are read as one row against block-diagonal weights
+// (row m' of the product then holds the outputs of pixels r*m' .. r*m'+r-1 back to back, which is exactly their dense
+// NHWC placement, so nothing else changes).
+static int pointwise_row_group(long long M, long long K, int OC) {
+  // TMA wants a row pitch that is a multiple of 16 bytes
+  int rgroup = 1;
+  if (K % 16 != 0) {
+    int g16 = 16;
+    while (K % g16 != 0) g16 >>= 1;  // gcd(K, 16)
+    rgroup = 16 / g16;
+  }
+  // Short rows make poor TMA boxes (the copy engine works row by row): widen them the same way while the grouped
+  // row stays within one 128-byte swizzle row.
+  while (rgroup * 2 <= 8 && K * rgroup * 2 <= 128 && M % (rgroup * 2) == 0 && OC * rgroup * 2 <= 512) rgroup *= 2;
+  // An output row pitch that is no multiple of 16 bytes (24 channels) would leave the tile through byte stores
+  // from registers (measured: 56x56 x 96 -> 24 at batch 256 took 88 us, 2 us per tile); grouped rows make the
+  // pitch r * OC and the tile leaves as one TMA store. The block-diagonal weights multiply the tensor-core work
+  // by r, which costs nothing here.
+  while ((OC * rgroup) % 16 != 0 && rgroup * 2 <= 8 && M % (rgroup * 2) == 0 && OC * rgroup * 2 <= 512 &&
+         K * rgroup * 2 <= 2048)
+    rgroup *= 2;
+  return rgroup;
+}
+// Whether that product runs on the tcgen05 GEMM (the few-row kernel and the CUDA-core convolution take the rest).
+static bool pointwise_takes_gemm_tc(long long M, long long K, int OC, int weight_zp) {
+  if (weight_zp != 0 || force_simt()) return false;
+  if (M <= 4 && K % 16 == 0 && K <= 12288) return false;  // fc_rows_dp4a
+  const int r = pointwise_row_group(M, K, OC);
+  return r <= 8 && M % r == 0 && (long long)OC * r <= 65536 && gemm_tc_supported(M / r, OC * r, (int)K * r, K * r);
+}
 
 bool decode_per_op() {
   const char* e = getenv("TB200_DECODE_PER_OP");
@@ -466,6 +528,8 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
   // pair: OptimizeSwishActivationPattern.cpp:100-190) is applied in the convolution's epilogue.
   std::vector<int> table_after(ops.size(), -1);  // conv op -> index of its fused table op
   std::vector<char> fused_away(ops.size(), 0);
+  std::vector<int> add_after(ops.size(), -1);      // conv op -> index of the add fused into its epilogue
+  std::vector<char> add_self_is_a(ops.size(), 0);  // the convolution's result is the add's first operand
   // Decoder graphs run op by op: (1) a split-K gemv_w8 whose only reader is the next op (rmsnorm, rope_kv or
   // geglu) leaves its per-slice sums in scratch and the reader finalizes them as it loads; (2) an rmsnorm
   // directly followed by an rmsnorm of its result runs as one launch. Same arithmetic, fewer launches.
@@ -502,6 +566,53 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
       table_after[pc] = i;
       fused_away[i] = 1;
       extra_out[pc] = op.out0;
+    }
+    // A rescaled add whose one operand is the only use of a 1x1 convolution's result (a residual connection) runs
+    // in that convolution's epilogue when the convolution takes the tensor-core GEMM: the other operand is read
+    // there, the product never goes to memory. The add's own checks (and its 32-bit output rescale, which the
+    // fused form requires) happen when the convolution is planned; what cannot be fused there fails the plan
+    // no differently from the stand-alone op.
+    // Off unless TB200_ADD_FUSION=1: measured on MobileNetV2 at batch 256 the fused form is no faster (1.693 ms per
+    // step against 1.678 with the ten adds as their own launches) - the step is bound by integer issue slots, and the
+    // add's table look-ups, rescale and repacking cost the same slots wherever they run.
+    const char* do_add = getenv("TB200_ADD_FUSION");
+    for (int i = 0; i < (int)ops.size() && do_add && *do_add && *do_add != '0'; i++) {
+      const auto& op = ops[i];
+      if (op.kind != TB200_OP_ADD || op.in0 < 0 || op.in0 >= nt || op.in1 < 0 || op.in1 >= nt || op.out0 < 0 || op.out0 >= nt ||
+          op.in0 == op.in1)
+        continue;
+      for (int side = 0; side < 2; side++) {
+        const int src = side == 0 ? op.in0 : op.in1, other = side == 0 ? op.in1 : op.in0;
+        const int pc = producer[src];
+        if (pc < 0 || pc >= i || ops[pc].kind != TB200_OP_CONV2D || uses[src] != 1 || table_after[pc] >= 0 || add_after[pc] >= 0 ||
+            tensors[src].kind != TB200_TENSOR_ACTIVATION || tensors[src].dtype != TB200_I8 || tensors[op.out0].dtype != TB200_I8 ||
+            tensors[other].dtype != TB200_I8 || tensors[other].kind == TB200_TENSOR_CONSTANT)
+          continue;
+        // the other operand must exist when the convolution runs
+        if (tensors[other].kind != TB200_TENSOR_INPUT && (producer[other] < 0 || producer[other] >= pc)) continue;
+        const auto& cv = ops[pc];
+        if (cv.in0 < 0 || cv.in0 >= nt || cv.weights < 0 || cv.weights >= nt || tensors[cv.in0].rank != 4 ||
+            tensors[cv.weights].rank != 4 || tensors[src].rank != 4)
+          continue;
+        const auto& x = tensors[cv.in0]; const auto& w = tensors[cv.weights]; const auto& o = tensors[src];
+        if (w.shape[1] != 1 || w.shape[2] != 1 || cv.stride_h != 1 || cv.stride_w != 1 || cv.pad_t || cv.pad_b || cv.pad_l || cv.pad_r)
+          continue;
+        const long long M = (long long)x.shape[0] * x.shape[1] * x.shape[2];
+        const int OC = w.shape[0];
+        if (!pointwise_takes_gemm_tc(M, x.shape[3], OC, cv.weight_zp)) continue;
+        if ((long long)o.shape[0] * o.shape[1] * o.shape[2] != M || o.shape[3] != OC) continue;
+        bool same = tensors[other].rank == 4 && tensors[op.out0].rank == 4;
+        for (int d = 0; d < 4 && same; d++) same = tensors[other].shape[d] == o.shape[d] && tensors[op.out0].shape[d] == o.shape[d];
+        if (!same) continue;
+        // the fused form exists for the 32-bit output rescale only
+        BinaryArgs probe{};
+        if (!binary_args_of(op, probe) || probe.epi == 0) continue;
+        add_after[pc] = i;
+        add_self_is_a[pc] = side == 0;
+        fused_away[i] = 1;
+        extra_out[pc] = op.out0;
+        break;
+      }
     }
     const char* no_dec = getenv("TB200_NO_DECODER_FUSION");
     for (int i = 0; i + 1 < (int)ops.size() && !(no_dec && *no_dec && *no_dec != '0'); i++) {
@@ -649,7 +760,9 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         return b.fail(TB200_INVALID_ARGUMENT, "op %d reads tensor %d before anything wrote it", i, id);
 
     if (fused_away[i]) {
-      step.kernel_name = op.kind == TB200_OP_RMSNORM ? "(norm fused into the previous norm)" : "(table in the convolution's epilogue)";
+      step.kernel_name = op.kind == TB200_OP_RMSNORM ? "(norm fused into the previous norm)"
+                         : op.kind == TB200_OP_ADD   ? "(add in the convolution's epilogue)"
+                                                     : "(table in the convolution's epilogue)";
       step.launches = 0;
       step.launch = [](const ExecContext&) {};
       plan.steps.push_back(std::move(step));
@@ -796,29 +909,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
           };
           break;
         }
-        // TMA wants a row pitch that is a multiple of 16 bytes. When K is not, r consecutive
-        // rows are read as one row of r*K bytes against block-diagonal weights: row m' of the
-        // product then holds the outputs of pixels r*m' .. r*m'+r-1 back to back, which is
-        // exactly their dense NHWC placement, so nothing else changes.
-        int rgroup = 1;
-        if (K % 16 != 0) {
-          int g16 = 16;
-          while (K % g16 != 0) g16 >>= 1;  // gcd(K, 16)
-          rgroup = 16 / g16;
-        }
-        // Short rows make poor TMA boxes (the copy engine works row by row): widen them the same
-        // way while the grouped row stays within one 128-byte swizzle row.
-        {
-          while (rgroup * 2 <= 8 && K * rgroup * 2 <= 128 && M % (rgroup * 2) == 0 && OC * rgroup * 2 <= 512)
-            rgroup *= 2;
-        }
-        // An output row pitch that is no multiple of 16 bytes (24 channels) would leave the tile through byte stores
-        // from registers (measured: 56x56 x 96 -> 24 at batch 256 took 88 us, 2 us per tile); grouped rows make the
-        // pitch r * OC and the tile leaves as one TMA store. The block-diagonal weights multiply the tensor-core work
-        // by r, which costs nothing here.
-        while ((OC * rgroup) % 16 != 0 && rgroup * 2 <= 8 && M % (rgroup * 2) == 0 && OC * rgroup * 2 <= 512 &&
-               K * rgroup * 2 <= 2048)
-          rgroup *= 2;
+        const int rgroup = pointwise_row_group(M, K, OC);
         if (pointwise && op.weight_zp == 0 && !force_simt() && rgroup <= 8 && M % rgroup == 0 &&
             (long long)OC * rgroup <= 65536 && gemm_tc_supported(M / rgroup, OC * rgroup, (int)K * rgroup, K * rgroup)) {
           GemmTcArgs ga{};
@@ -851,7 +942,18 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             q_off = b.add_const(rep.data(), rep.size() * sizeof(int4));
           }
           const bool has_q4 = ga.epi != 0;
-          Loc lx = loc(op.in0), lo = loc(result_id);
+          // a residual add fused behind the product: the result is the add's, the other operand is read in the epilogue
+          const int fused_add = add_after[i];
+          int out_id = result_id;
+          Loc lres{};
+          if (fused_add >= 0) {
+            if (!binary_args_of(ops[fused_add], ga.add) || ga.add.epi == 0)
+              return b.fail(TB200_INTERNAL, "op %d: fused add lost its 32-bit rescale", fused_add);
+            ga.add_self_is_a = add_self_is_a[i];
+            out_id = ops[fused_add].out0;
+            lres = loc(add_self_is_a[i] ? ops[fused_add].in1 : ops[fused_add].in0);
+          }
+          Loc lx = loc(op.in0), lo = loc(out_id);
           std::shared_ptr<GemmTcState> st(gemm_tc_state_new(), gemm_tc_state_free);
           step.kernel_name = "gemm_i8_tcgen05";
           step.launch = [=](const ExecContext& c) {
@@ -863,11 +965,13 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             k.q4 = has_q4 ? (const int4*)(c.consts + q_off) : nullptr;
             k.status = c.status;
             k.lut = has_lut ? (const int8_t*)(c.consts + lut_off) : nullptr;
+            k.res = fused_add >= 0 ? (const int8_t*)lres.resolve(c) : nullptr;
             launch_gemm_i8_tc(k, st.get(), c.stream);
           };
           break;
         }
 
+        if (add_after[i] >= 0) return b.fail(TB200_INTERNAL, "op %d: an add was fused into a convolution that does not take the GEMM", i);
         // KH x KW convolution with symmetric weights: implicit GEMM on the tensor cores (one TMA box per
         // tap and channel block, taps accumulated in TMEM; see gemm_tcgen05.cu)
         // (16 input channels with a load per tap or per kernel column: the copy engine's per-row cost makes 16-byte
@@ -1171,33 +1275,8 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         for (int s : {op.in0_shift, op.in1_shift, op.out_shift})
           if (s < 2 || s > 62) return b.fail(TB200_INVALID_ARGUMENT, "op %d: rescale shift %d outside [2,62]", i, s);
         BinaryArgs a{};
+        if (!binary_args_of(op, a)) return b.fail(TB200_INVALID_ARGUMENT, "op %d: input left shift outside [0,22]", i);
         a.n = (long long)n;
-        a.kind = op.kind == TB200_OP_ADD ? 0 : op.kind == TB200_OP_SUB ? 1 : 2;
-        a.a_zp = op.in0_zp; a.a_mult = op.in0_mult; a.a_shift = op.in0_shift;
-        a.b_zp = op.in1_zp; a.b_mult = op.in1_mult; a.b_shift = op.in1_shift;
-        a.out_mult = op.out_mult; a.out_shift = op.out_shift; a.out_zp = op.out_zp;
-        a.double_round = op.double_round; a.clamp_min = op.clamp_min; a.clamp_max = op.clamp_max;
-        if (op.i0 < 0 || op.i0 > 22 || op.i1 < 0 || op.i1 > 22)
-          return b.fail(TB200_INVALID_ARGUMENT, "op %d: input left shift outside [0,22]", i);
-        a.a_lshift = op.i0; a.b_lshift = op.i1;
-        {
-          // The operand-side rescales are functions of one byte: evaluate both tables here as the kernel does, bound
-          // the value that reaches the output rescale, and take the 32-bit form of that rescale when it is exact.
-          long long ma = 0, mb = 0;
-          for (int v = -128; v < 128; v++) {
-            const long long ra = host_apply_scale_32((long long)(v - a.a_zp) * (1ll << a.a_lshift), a.a_mult, a.a_shift, op.double_round != 0);
-            const long long rb = host_apply_scale_32((long long)(v - a.b_zp) * (1ll << a.b_lshift), a.b_mult, a.b_shift, op.double_round != 0);
-            ma = std::max(ma, ra < 0 ? -ra : ra);
-            mb = std::max(mb, rb < 0 ? -rb : rb);
-          }
-          const long long bound = a.kind == 2 ? ma * mb : ma + mb;
-          ChanParams cp{};
-          cp.mult = a.out_mult; cp.shift = a.out_shift; cp.bias = 0;
-          std::vector<int4> q4;
-          a.epi = (ma < (1ll << 31) && mb < (1ll << 31) && bound < (1ll << 29))
-                      ? Builder::q4_params({cp}, {bound}, op.double_round != 0, a.out_zp, a.clamp_min, q4) : 0;
-          if (a.epi) a.q4 = q4[0];
-        }
         Loc la = loc(op.in0), lb = loc(op.in1), lo = loc(op.out0);
         step.kernel_name = "binary_rescale";
         step.launch = [=](const ExecContext& c) {
