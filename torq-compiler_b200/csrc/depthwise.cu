@@ -187,13 +187,15 @@ __global__ void __launch_bounds__(128, 4) dw3x3_kernel(DwArgs a) {
 // thread and row instead of four 4-byte copies per thread and row, and no 64-bit index arithmetic per
 // thread); pieces outside the image are stored as the input zero point. After one barrier every thread
 // reads its own 4 channels of its 3 or 4 columns from the tile and proceeds exactly as dw3x3_kernel.
-template <int STRIDE, int EPI>
+// ROWS: output rows per thread: 8, or 14 where the frame height is a multiple of 14 (112, 56, 28, 14): the two halo
+// rows, the weights and the per-channel records are then paid once per 14 rows instead of once per 8.
+template <int STRIDE, int EPI, int ROWS>
 __global__ void __launch_bounds__(128, STRIDE == 1 ? 6 : 8) dw3x3_tile_kernel(DwArgs a, int cg_log2, int cchunks) {
   grid_dependency_release();
   grid_dependency_wait();
   constexpr int TW = STRIDE == 1 ? 2 : 1;
   constexpr int NCOL = STRIDE == 1 ? 4 : 3;
-  constexpr int NR = (kRows - 1) * STRIDE + 3;
+  constexpr int NR = (ROWS - 1) * STRIDE + 3;
   extern __shared__ __align__(16) uint32_t tile[];  // [NR][IWT][CG] words
   const int CG = 1 << cg_log2, SW = 128 >> cg_log2;
   const int IWT = (SW * TW - 1) * STRIDE + 3;  // input columns of the tile
@@ -203,8 +205,8 @@ __global__ void __launch_bounds__(128, STRIDE == 1 ? 6 : 8) dw3x3_tile_kernel(Dw
   const int c0 = cc << (cg_log2 + 2);        // first channel of the block
   const int ow_tile = wt * SW * TW;          // first output column of the block
   const int iw_tile = ow_tile * STRIDE - a.pad_l;
-  const int oh_begin = rb * kRows;
-  const int n_rows = min(a.OH - oh_begin, kRows);
+  const int oh_begin = rb * ROWS;
+  const int n_rows = min(a.OH - oh_begin, ROWS);
   const int nr_live = (n_rows - 1) * STRIDE + 3;
   const int ih_base = oh_begin * STRIDE - a.pad_t;
   const uint32_t zpw = (uint32_t)(a.input_zp & 0xff) * 0x01010101u;
@@ -277,7 +279,7 @@ __global__ void __launch_bounds__(128, STRIDE == 1 ? 6 : 8) dw3x3_tile_kernel(Dw
   const int out_row_words = a.OW * Cw;
   const bool second = TW == 2 && ow0 + 1 < a.OW;
 #pragma unroll
-  for (int r = 0; r < kRows; r++) {
+  for (int r = 0; r < ROWS; r++) {
     if (r < n_rows) {
       // keep the tile reads of later rows behind this row's arithmetic: hoisted to the top they cost
       // 30-40 registers and two resident blocks per SM
@@ -421,17 +423,30 @@ void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
   int cg_log2 = 0, tiles = 0, cchunks = 0;
   if (a.wq && depthwise3x3_supported(a) && dw_tile_shape(a, cg_log2, tiles, cchunks)) {
     const int S = a.stride_h, tw = S == 1 ? 2 : 1, sw = 128 >> cg_log2;
-    const int nr = (kRows - 1) * S + 3, iwt = (sw * tw - 1) * S + 3;
+    static const bool rows8 = getenv("TB200_DW_ROWS8") != nullptr;  // A/B switch
+    const int rows = (a.OH % 14 == 0 && !rows8) ? 14 : kRows;
+    const int nr = (rows - 1) * S + 3, iwt = (sw * tw - 1) * S + 3;
     const size_t smem = (size_t)nr * iwt * (4 << cg_log2);
-    const dim3 grid((unsigned)(tiles * cchunks), (unsigned)((a.OH + kRows - 1) / kRows), (unsigned)a.N);
-    if (S == 1) {
-      if (a.epi == 1) launch_dependent(dw3x3_tile_kernel<1, 1>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
-      else if (a.epi == 2) launch_dependent(dw3x3_tile_kernel<1, 2>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
-      else launch_dependent(dw3x3_tile_kernel<1, 0>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
+    const dim3 grid((unsigned)(tiles * cchunks), (unsigned)((a.OH + rows - 1) / rows), (unsigned)a.N);
+    auto go = [&](auto kern) { launch_dependent(kern, grid, dim3(128), smem, stream, a, cg_log2, cchunks); };
+    if (rows == 14) {
+      if (S == 1) {
+        if (a.epi == 1) go(dw3x3_tile_kernel<1, 1, 14>);
+        else if (a.epi == 2) go(dw3x3_tile_kernel<1, 2, 14>);
+        else go(dw3x3_tile_kernel<1, 0, 14>);
+      } else {
+        if (a.epi == 1) go(dw3x3_tile_kernel<2, 1, 14>);
+        else if (a.epi == 2) go(dw3x3_tile_kernel<2, 2, 14>);
+        else go(dw3x3_tile_kernel<2, 0, 14>);
+      }
+    } else if (S == 1) {
+      if (a.epi == 1) go(dw3x3_tile_kernel<1, 1, kRows>);
+      else if (a.epi == 2) go(dw3x3_tile_kernel<1, 2, kRows>);
+      else go(dw3x3_tile_kernel<1, 0, kRows>);
     } else {
-      if (a.epi == 1) launch_dependent(dw3x3_tile_kernel<2, 1>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
-      else if (a.epi == 2) launch_dependent(dw3x3_tile_kernel<2, 2>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
-      else launch_dependent(dw3x3_tile_kernel<2, 0>, grid, dim3(128), smem, stream, a, cg_log2, cchunks);
+      if (a.epi == 1) go(dw3x3_tile_kernel<2, 1, kRows>);
+      else if (a.epi == 2) go(dw3x3_tile_kernel<2, 2, kRows>);
+      else go(dw3x3_tile_kernel<2, 0, kRows>);
     }
   } else if (a.wq && depthwise3x3_supported(a)) {
     const int tw = a.stride_h == 1 ? 2 : 1;
