@@ -424,7 +424,9 @@ void launch_depthwise(const DwArgs& a, cudaStream_t stream) {
   if (a.wq && depthwise3x3_supported(a) && dw_tile_shape(a, cg_log2, tiles, cchunks)) {
     const int S = a.stride_h, tw = S == 1 ? 2 : 1, sw = 128 >> cg_log2;
     static const bool rows8 = getenv("TB200_DW_ROWS8") != nullptr;  // A/B switch
-    const int rows = (a.OH % 14 == 0 && !rows8) ? 14 : kRows;
+    // 14 rows per thread only while that still leaves a few blocks per SM (a batch-1 frame wants the parallelism)
+    const long long blocks14 = (long long)tiles * cchunks * ((a.OH + 13) / 14) * a.N;
+    const int rows = (a.OH % 14 == 0 && !rows8 && blocks14 >= 148 * 16) ? 14 : kRows;
     const int nr = (rows - 1) * S + 3, iwt = (sw * tw - 1) * S + 3;
     const size_t smem = (size_t)nr * iwt * (4 << cg_log2);
     const dim3 grid((unsigned)(tiles * cchunks), (unsigned)((a.OH + rows - 1) / rows), (unsigned)a.N);

@@ -942,7 +942,7 @@ cudaError_t launch_gemm_i8_tc(const GemmTcArgs& a, GemmTcState* st, cudaStream_t
     p.add_clamp_min = d.clamp_min; p.add_clamp_max = d.clamp_max;
     p.add_q4 = d.q4;
   }
-  return launch_dependent(gemm_kernel_for(false, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr, fused_add), dim3(grid), dim3(kThreads), smem, stream, st->tmA, st->tmB, st->tmC, p);
+  return launch_dependent_if(tiles >= kDependentMinBlocks / 2, gemm_kernel_for(false, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr, fused_add), dim3(grid), dim3(kThreads), smem, stream, st->tmA, st->tmB, st->tmC, p);
 }
 
 // ---- convolution as implicit GEMM ----
@@ -1138,7 +1138,7 @@ cudaError_t launch_conv_i8_tc(const ConvTcArgs& a, GemmTcState* st, cudaStream_t
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < current_sm_count() ? tiles : current_sm_count();
-  return launch_dependent(gemm_kernel_for(true, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr), dim3(grid), dim3(kThreads), smem, stream, st->tmA, st->tmB, st->tmC, p);
+  return launch_dependent_if(tiles >= kDependentMinBlocks / 2, gemm_kernel_for(true, gemm_epi_variant(a.epi, a.clamp_min, a.clamp_max), a.lut != nullptr), dim3(grid), dim3(kThreads), smem, stream, st->tmA, st->tmB, st->tmC, p);
 }
 
 }  // namespace tb200
