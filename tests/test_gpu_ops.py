@@ -78,6 +78,10 @@ IGEMM_CASES = [
     ((3, 36, 52, 32), 64, (3, 3), 2, (1, 0, 1, 0), 12),      # 32 channels, stride 2, pairs of 64 bytes
     ((1, 64, 64, 64), 64, (3, 3), 2, (1, 1, 1, 1), -1),      # 64 channels, stride 2, pairs of 128 bytes, two K steps
     ((2, 37, 45, 16), 16, (3, 3), 1, (1, 1, 1, 1), -6),      # 16 channels, stride 1: halo patches, rows half zero fill
+    ((2, 36, 44, 16), 16, (3, 3), 1, (1, 1, 1, 1), -6),      # the same with an even width: read as pixel pairs (32 channels)
+    ((1, 22, 30, 32), 48, (3, 3), 1, (1, 1, 1, 1), 9),       # 32 channels as pairs of 64, 48 filters as 96
+    ((2, 17, 26, 16), 32, (5, 3), 1, (2, 2, 1, 1), -11),     # five kernel rows over pixel pairs
+    ((1, 20, 28, 32), 32, (3, 3), 1, (0, 0, 1, 1), 3),       # pairs, no padding above and below
     ((1, 23, 31, 64), 32, (5, 5), 1, (2, 2, 2, 2), 9),       # 5x5 over halo patches (12 output columns per tile)
     ((1, 19, 33, 128), 64, (3, 3), 1, (1, 1, 1, 1), -2),     # 128-byte rows over halo patches, weights 72 KB resident
     ((1, 11, 11, 48), 16, (3, 3), 1, (1, 1, 1, 1), 8),       # 48 channels in one 64-byte block
