@@ -78,7 +78,8 @@ IGEMM_CASES = [
     ((3, 36, 52, 32), 64, (3, 3), 2, (1, 0, 1, 0), 12),      # 32 channels, stride 2, pairs of 64 bytes
     ((1, 64, 64, 64), 64, (3, 3), 2, (1, 1, 1, 1), -1),      # 64 channels, stride 2, pairs of 128 bytes, two K steps
     ((2, 37, 45, 16), 16, (3, 3), 1, (1, 1, 1, 1), -6),      # 16 channels, stride 1: halo patches, rows half zero fill
-    ((2, 36, 44, 16), 16, (3, 3), 1, (1, 1, 1, 1), -6),      # the same with an even width: read as pixel pairs (32 channels)
+    ((2, 36, 44, 16), 16, (3, 3), 1, (1, 1, 1, 1), -6),      # the same with a width of 4 k: read as groups of four pixels (64 channels)
+    ((2, 21, 42, 16), 32, (3, 3), 1, (1, 1, 1, 1), 5),       # an even width that is no multiple of 4: pixel pairs (32 channels)
     ((1, 22, 30, 32), 48, (3, 3), 1, (1, 1, 1, 1), 9),       # 32 channels as pairs of 64, 48 filters as 96
     ((2, 17, 26, 16), 32, (5, 3), 1, (2, 2, 1, 1), -11),     # five kernel rows over pixel pairs
     ((1, 20, 28, 32), 32, (3, 3), 1, (0, 0, 1, 1), 3),       # pairs, no padding above and below

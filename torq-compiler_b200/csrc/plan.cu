@@ -972,36 +972,46 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         }
 
         if (add_after[i] >= 0) return b.fail(TB200_INTERNAL, "op %d: an add was fused into a convolution that does not take the GEMM", i);
-        // Pixel pairs for narrow stride-1 3-wide kernels (16 or 32 input channels, even width, one pixel of padding
-        // left and right): the copy engine works row by row, a row being one pixel's channels, so 16- and 32-byte
-        // pixels cost as much per row as 128-byte ones. The same convolution on the tensors read as [N, H, W / 2, 2C]
-        // -> [N, OH, OW / 2, 2 OC] (identical memory) is again a KH x 3 convolution with one pair of padding: output
-        // pixel 2P + j reads input pixel 2 (P + kp - 1) + h for kw = 2 kp + h - j - 1, so its weights are the
-        // original ones placed at [(j, oc)][kh][kp][(h, c)] and zero elsewhere. Half the rows per pixel through the
-        // copy engine; the zero halves cost tensor-core work that is free here. Border classes, bias folding and the
+        // Pixel groups for narrow stride-1 3-wide kernels (16 or 32 input channels, width a multiple of the group, one
+        // pixel of padding left and right): the copy engine works row by row, a row being one pixel's channels, so 16-
+        // and 32-byte pixels cost as much per row as 128-byte ones. The same convolution on the tensors read as
+        // [N, H, W / G, G C] -> [N, OH, OW / G, G OC] (identical memory) is again a KH x 3 convolution with one group
+        // of padding, its weights the original ones placed at [(j, oc)][kh][kp][(h, c)] and zero elsewhere. 1 / G of
+        // the rows per pixel through the copy engine; the zero parts cost tensor-core work that is free here. Border classes, bias folding and the
         // epilogue constants follow from the transformed op as for any convolution.
         std::vector<int8_t> w_pairs;
         static const bool no_pairs = getenv("TB200_CONV_NO_PAIRS") != nullptr;  // A/B switch
+        int group = 0;  // pixels per row of the rewritten convolution: 4 for 16 channels where the width allows, else 2
         if (!fc && !pointwise && !no_pairs && op.weight_zp == 0 && !force_simt() && op.stride_h == 1 && op.stride_w == 1 &&
-            op.dil_h == 1 && op.dil_w == 1 && KW == 3 && KH <= 5 && op.pad_l == 1 && op.pad_r == 1 && (W % 2) == 0 &&
-            (IC == 16 || IC == 32) && OC % 16 == 0 && OC <= 128 &&
-            conv_tc_supported(N, H, W / 2, 2 * IC, 2 * OC, KH, 3, 1, 1, 1, 1, OH, OW / 2) &&
-            conv_tc_geometry_padded(N, OH, OW / 2, W / 2, 2 * IC, 2 * OC, KH, 3, 1, 1).halo) {
-          w_pairs.assign((size_t)2 * OC * KH * 3 * 2 * IC, 0);
-          for (int j = 0; j < 2; j++)
+            op.dil_h == 1 && op.dil_w == 1 && KW == 3 && KH <= 5 && op.pad_l == 1 && op.pad_r == 1 && (IC == 16 || IC == 32) &&
+            OC % 16 == 0) {
+          for (int g : {4, 2}) {
+            if (W % g != 0 || IC * g > 64 || OC * g > 256) continue;
+            if (conv_tc_supported(N, H, W / g, g * IC, g * OC, KH, 3, 1, 1, 1, 1, OH, OW / g) &&
+                conv_tc_geometry_padded(N, OH, OW / g, W / g, g * IC, g * OC, KH, 3, 1, 1).halo) {
+              group = g;
+              break;
+            }
+          }
+        }
+        if (group) {
+          const int G = group;
+          // output pixel G P + j reads input pixel G (P + kp - 1) + h for kw = G (kp - 1) + h - j + 1
+          w_pairs.assign((size_t)G * OC * KH * 3 * G * IC, 0);
+          for (int j = 0; j < G; j++)
             for (int oc = 0; oc < OC; oc++)
               for (int kh = 0; kh < KH; kh++)
                 for (int kp = 0; kp < 3; kp++)
-                  for (int h = 0; h < 2; h++) {
-                    const int kw = 2 * kp + h - j - 1;
+                  for (int h = 0; h < G; h++) {
+                    const int kw = G * (kp - 1) + h - j + 1;
                     if (kw < 0 || kw >= 3) continue;
-                    memcpy(w_pairs.data() + ((((size_t)(j * OC + oc) * KH + kh) * 3 + kp) * 2 + h) * IC,
+                    memcpy(w_pairs.data() + ((((size_t)(j * OC + oc) * KH + kh) * 3 + kp) * G + h) * IC,
                            w + (((size_t)oc * KH + kh) * 3 + kw) * IC, (size_t)IC);
                   }
           {
-            std::vector<ChanParams> cp2((size_t)2 * OC);
-            std::vector<long long> ab2((size_t)2 * OC);
-            for (int j = 0; j < 2; j++)
+            std::vector<ChanParams> cp2((size_t)G * OC);
+            std::vector<long long> ab2((size_t)G * OC);
+            for (int j = 0; j < G; j++)
               for (int oc = 0; oc < OC; oc++) {
                 cp2[(size_t)j * OC + oc] = cp[oc];
                 ab2[(size_t)j * OC + oc] = acc_bound[oc];
@@ -1010,7 +1020,7 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
             acc_bound.swap(ab2);
           }
           w = w_pairs.data();
-          IC *= 2; OC *= 2; W /= 2; OW /= 2;
+          IC *= G; OC *= G; W /= G; OW /= G;
         }
         // KH x KW convolution with symmetric weights: implicit GEMM on the tensor cores (one TMA box per
         // tap and channel block, taps accumulated in TMEM; see gemm_tcgen05.cu)
