@@ -126,6 +126,9 @@ enum tb200_op_kind {
                                * updates[n, w, :]; indices of one n are distinct (TOSA), an index outside [0, K) is skipped */
   TB200_OP_MATMUL_F = 60,     /* tosa.matmul on floats (doc/user-manual/ops.md: MatMul bf16 x bf16 -> f32): in0 [M, K] x in1 [K, N], bf16 or f32
                                * operands, products and sums in fp32, each rounded, added in index order of k; result f32 or bf16 */
+  TB200_OP_DEPTHWISE_F = 61,  /* tosa.depthwise_conv2d on floats (doc/user-manual/ops.md: DepthwiseConv2D bf16): in0 [N, H, W, C], in1 weights
+                               * [KH, KW, C, M], in2 bias [C * M], all bf16 or all f32 -> [N, OH, OW, C * M]; fp32 products, each rounded,
+                               * added tap by tap in (kh, kw) order (taps outside the frame skipped), the bias last; kh, kw, stride, pad, dil as for depthwise */
   TB200_OP_ALLREDUCE = 40,    /* sum of the fp32 partial results of the i0 GPUs of a tensor-parallel group
                                * (this one is rank i1), rounded to bf16; only inside the fused decode step */
 };

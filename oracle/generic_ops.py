@@ -259,6 +259,35 @@ def matmul_f(a: np.ndarray, b: np.ndarray, dtype: str, out_dtype: str) -> np.nda
     return _store(acc, True, out_dtype)
 
 
+def depthwise_f(x: np.ndarray, w: np.ndarray, bias: np.ndarray, dtype: str, stride, dilation, pad) -> np.ndarray:
+    """tosa.depthwise_conv2d on floats (reference semantics: doc/user-manual/ops.md, DepthwiseConv2D bf16; TOSA: the
+    accumulator is fp32): fp32 products, each rounded, added tap by tap in (kh, kw) order, taps outside the frame
+    skipped, the bias last; stored in the operands' type. x [N, H, W, C], w [KH, KW, C, M], bias [C * M]."""
+    xf, _ = _load(x, dtype)
+    wf, _ = _load(w, dtype)
+    bf, _ = _load(bias, dtype)
+    xf, wf, bf = xf.astype(np.float32), wf.astype(np.float32), bf.astype(np.float32).reshape(-1)
+    N, H, W, C = xf.shape
+    KH, KW, _, M = wf.shape
+    OH = (H + pad[0] + pad[1] - dilation[0] * (KH - 1) - 1) // stride[0] + 1
+    OW = (W + pad[2] + pad[3] - dilation[1] * (KW - 1) - 1) // stride[1] + 1
+    acc = np.zeros((N, OH, OW, C, M), np.float32)
+    for kh in range(KH):
+        for kw in range(KW):
+            for oh in range(OH):
+                ih = oh * stride[0] - pad[0] + kh * dilation[0]
+                if ih < 0 or ih >= H:
+                    continue
+                ows = [ow for ow in range(OW) if 0 <= ow * stride[1] - pad[2] + kw * dilation[1] < W]
+                if not ows:
+                    continue
+                iws = [ow * stride[1] - pad[2] + kw * dilation[1] for ow in ows]
+                prod = (xf[:, ih, iws, :, None] * wf[kh, kw][None, None]).astype(np.float32)
+                acc[:, oh, ows] = (acc[:, oh, ows] + prod).astype(np.float32)
+    out = (acc.reshape(N, OH, OW, C * M) + bf[None, None, None, :]).astype(np.float32)
+    return _store(out, True, dtype)
+
+
 def gather(values: np.ndarray, indices: np.ndarray) -> np.ndarray:
     """tosa.gather (TOSA 1.0: output[n, w, c] = values[n, indices[n, w], c])."""
     return np.stack([values[n][indices[n]] for n in range(values.shape[0])])

@@ -73,6 +73,10 @@ def run_graph(graph, inputs, keep_all=False):
             y = np.broadcast_to(y, op.outputs[0].shape) if y.shape != tuple(op.outputs[0].shape) else y
         elif k == "transpose":
             y = np.transpose(x, [a["i0"], a["i1"], a["i2"], a["i3"]][:x.ndim])
+        elif k == "depthwise_f":
+            a = op.attrs
+            y = gops.depthwise_f(x, vals[op.inputs[1].id], vals[op.inputs[2].id], op.inputs[0].dtype, (a["stride_h"], a["stride_w"]),
+                                 (a["dil_h"], a["dil_w"]), (a["pad_t"], a["pad_b"], a["pad_l"], a["pad_r"]))
         elif k == "matmul_f":
             y = gops.matmul_f(x, vals[op.inputs[1].id], op.inputs[0].dtype, op.outputs[0].dtype)
         elif k == "gather":

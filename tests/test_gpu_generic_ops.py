@@ -286,3 +286,32 @@ def test_float_matmul(device, M, K, N, dtype, out_dtype):
     gf = from_bf16(got) if out_dtype == "bf16" else got
     tol = 2.0 ** -7 if out_dtype == "bf16" else 1e-5
     assert np.all(np.abs(gf - ref) <= tol * np.abs(ref) + 1e-4 * np.sqrt(K))
+
+
+@pytest.mark.parametrize("shape,kernel,M,stride,dil,pad", [
+    ((1, 16, 16, 2), (3, 3), 1, (1, 1), (1, 1), (1, 1, 1, 1)),     # the reference's dw_16x16-bf16 fixture shape
+    ((2, 13, 17, 5), (5, 5), 1, (1, 1), (1, 1), (2, 2, 2, 2)),
+    ((1, 20, 14, 8), (3, 3), 2, (2, 2), (1, 1), (0, 1, 0, 1)),     # stride 2, channel multiplier 2
+    ((1, 12, 12, 3), (3, 2), 1, (1, 2), (2, 1), (2, 2, 0, 1)),     # dilation, asymmetric window
+])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_float_depthwise(device, shape, kernel, M, stride, dil, pad, dtype):
+    """tosa.depthwise_conv2d on floats: fp32 products and sums, each rounded, taps in (kh, kw) order, the bias last:
+    bit-exact against the oracle, close to a float64 torch convolution."""
+    rng = np.random.default_rng(shape[1] + kernel[0])
+    C = shape[3]
+    x = rng.normal(0, 1, shape).astype(np.float32)
+    w = rng.normal(0, 1, kernel + (C, M)).astype(np.float32)
+    bias = rng.normal(0, 1, (C * M,)).astype(np.float32)
+    if dtype == "bf16":
+        x, w, bias = to_bf16(x), to_bf16(w), to_bf16(bias)
+    g = Graph()
+    g.output(g.depthwise_conv2d_f(g.input(x.shape, dtype), g.const(w, dtype), g.const(bias, dtype), stride=stride, dilation=dil, pad=pad))
+    got = _same(device, g, [x])[0]
+    fx, fw, fb = (from_bf16(x), from_bf16(w), from_bf16(bias)) if dtype == "bf16" else (x, w, bias)
+    xt = torch.nn.functional.pad(torch.from_numpy(fx).double().permute(0, 3, 1, 2), (pad[2], pad[3], pad[0], pad[1]))
+    wt = torch.from_numpy(fw).double().permute(2, 3, 0, 1).reshape(C * M, 1, kernel[0], kernel[1])
+    ref = torch.nn.functional.conv2d(xt, wt, torch.from_numpy(fb).double(), stride=stride, dilation=dil, groups=C).permute(0, 2, 3, 1).numpy()
+    gf = from_bf16(got) if dtype == "bf16" else got
+    tol = 2.0 ** -7 if dtype == "bf16" else 1e-5
+    assert gf.shape == ref.shape and np.all(np.abs(gf - ref) <= tol * np.abs(ref) + 1e-4 * kernel[0] * kernel[1])

@@ -355,6 +355,41 @@ __global__ void __launch_bounds__(256) matmul_f_kernel(const void* __restrict__ 
 }
 }  // namespace
 
+namespace {
+// tosa.depthwise_conv2d on floats: one thread per output; products and sums rounded separately, taps in (kh, kw) order,
+// taps outside the frame skipped, the bias added last
+__global__ void __launch_bounds__(256) depthwise_f_kernel(DepthwiseFArgs a) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)a.N * a.OH * a.OW * a.C * a.M;
+  if (idx >= total) return;
+  const int CM = a.C * a.M;
+  const int cm = (int)(idx % CM);
+  long long t = idx / CM;
+  const int ow = (int)(t % a.OW); t /= a.OW;
+  const int oh = (int)(t % a.OH);
+  const int n = (int)(t / a.OH);
+  const int c = cm / a.M, m = cm - c * a.M;
+  float acc = 0.f;
+  for (int kh = 0; kh < a.KH; kh++) {
+    const int ih = oh * a.stride_h - a.pad_t + kh * a.dil_h;
+    if (ih < 0 || ih >= a.H) continue;
+    for (int kw = 0; kw < a.KW; kw++) {
+      const int iw = ow * a.stride_w - a.pad_l + kw * a.dil_w;
+      if (iw < 0 || iw >= a.W) continue;
+      const float xv = load_float(a.x, a.dtype, (((long long)n * a.H + ih) * a.W + iw) * a.C + c);
+      const float wv = load_float(a.w, a.dtype, (((long long)kh * a.KW + kw) * a.C + c) * a.M + m);
+      acc = __fadd_rn(acc, __fmul_rn(xv, wv));
+    }
+  }
+  store_float(a.out, a.dtype, idx, __fadd_rn(acc, load_float(a.bias, a.dtype, cm)));
+}
+}  // namespace
+
+void launch_depthwise_f(const DepthwiseFArgs& a, cudaStream_t stream) {
+  const long long total = (long long)a.N * a.OH * a.OW * a.C * a.M;
+  depthwise_f_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
+}
+
 void launch_matmul_f(const void* a, const void* b, void* out, int M, int K, int N, int in_dtype, int out_dtype, cudaStream_t stream) {
   matmul_f_kernel<<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(a, b, out, M, K, N, in_dtype, out_dtype);
 }

@@ -344,6 +344,15 @@ void launch_reduce(const ReduceArgs& a, cudaStream_t stream);
 void launch_gather_rows(const void* values, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream);
 void launch_scatter_rows(const void* updates, const int32_t* idx, void* out, int N, int K, int W, int row_bytes, cudaStream_t stream);
 void launch_matmul_f(const void* a, const void* b, void* out, int M, int K, int N, int in_dtype, int out_dtype, cudaStream_t stream);
+struct DepthwiseFArgs {
+  const void* x;     // [N, H, W, C]
+  const void* w;     // [KH, KW, C, M]
+  const void* bias;  // [C * M]
+  void* out;         // [N, OH, OW, C * M]
+  int dtype;         // TB200_BF16 or TB200_F32, all four tensors
+  int N, H, W, C, M, KH, KW, OH, OW, stride_h, stride_w, dil_h, dil_w, pad_t, pad_l;
+};
+void launch_depthwise_f(const DepthwiseFArgs& a, cudaStream_t stream);
 void launch_softmax(const void* x, void* out, long long rows, int cols, int dtype, cudaStream_t stream);
 void launch_table16(const int16_t* x, const int16_t* table, int32_t* out, long long n, cudaStream_t stream);
 

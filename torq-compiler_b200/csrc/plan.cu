@@ -1847,6 +1847,33 @@ int build_plan(const std::vector<tb200_tensor_t>& tensors, const std::vector<tb2
         step.launch = [=](const ExecContext& c) { launch_matmul_f(la.resolve(c), lb.resolve(c), lo.resolve(c), M, K, N, idt, odt, c.stream); };
         break;
       }
+      case TB200_OP_DEPTHWISE_F: {
+        if (!b.valid_id(op.in0) || !b.valid_id(op.in1) || !b.valid_id(op.in2) || !b.valid_id(op.out0))
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: bad tensor id", i);
+        const auto& tx = tensors[op.in0]; const auto& tw = tensors[op.in1]; const auto& tb = tensors[op.in2]; const auto& to = tensors[op.out0];
+        DepthwiseFArgs a{};
+        a.dtype = (int)tx.dtype;
+        if ((tx.dtype != TB200_BF16 && tx.dtype != TB200_F32) || tw.dtype != tx.dtype || tb.dtype != tx.dtype || to.dtype != tx.dtype ||
+            tx.rank != 4 || tw.rank != 4 || to.rank != 4 || tw.shape[2] != tx.shape[3] || op.stride_h < 1 || op.stride_w < 1 ||
+            op.dil_h < 1 || op.dil_w < 1 || op.pad_t < 0 || op.pad_b < 0 || op.pad_l < 0 || op.pad_r < 0)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: depthwise_f wants bf16 or f32 x [N,H,W,C], weights [KH,KW,C,M], bias [C*M]", i);
+        a.N = tx.shape[0]; a.H = tx.shape[1]; a.W = tx.shape[2]; a.C = tx.shape[3];
+        a.KH = tw.shape[0]; a.KW = tw.shape[1]; a.M = tw.shape[3];
+        a.stride_h = op.stride_h; a.stride_w = op.stride_w; a.dil_h = op.dil_h; a.dil_w = op.dil_w; a.pad_t = op.pad_t; a.pad_l = op.pad_l;
+        a.OH = conv_out_dim(a.H, a.KH, op.stride_h, op.dil_h, op.pad_t, op.pad_b);
+        a.OW = conv_out_dim(a.W, a.KW, op.stride_w, op.dil_w, op.pad_l, op.pad_r);
+        if (b.numel(op.in2) != (size_t)a.C * a.M || to.shape[0] != a.N || to.shape[1] != a.OH || to.shape[2] != a.OW ||
+            to.shape[3] != a.C * a.M)
+          return b.fail(TB200_INVALID_ARGUMENT, "op %d: depthwise_f output shape is not %dx%dx%dx%d", i, a.N, a.OH, a.OW, a.C * a.M);
+        Loc lx = loc(op.in0), lw = loc(op.in1), lb = loc(op.in2), lo = loc(op.out0);
+        step.kernel_name = "depthwise_f";
+        step.launch = [=](const ExecContext& c) {
+          DepthwiseFArgs k = a;
+          k.x = lx.resolve(c); k.w = lw.resolve(c); k.bias = lb.resolve(c); k.out = lo.resolve(c);
+          launch_depthwise_f(k, c.stream);
+        };
+        break;
+      }
       case TB200_OP_GATHER:
       case TB200_OP_SCATTER: {
         const bool sc = op.kind == TB200_OP_SCATTER;

@@ -29,7 +29,7 @@ OP_KINDS = {
     "rescale": 9, "resize_nn2x": 10, "concat": 11, "sub": 12, "matmul_i32": 13, "reshape": 14,
     "embed": 32, "rmsnorm": 33, "gemv_w8": 34, "rope_kv": 35, "attn_decode": 36, "geglu": 37,
     "add_bf16": 38, "argmax": 39, "allreduce": 40, "act_bf16": 41, "gemv_q8b": 42,
-    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55, "conv2d_i16": 56, "permute": 57, "gather": 58, "scatter": 59, "matmul_f": 60,
+    "ew": 48, "transpose": 49, "slice": 50, "pad": 51, "concat_axis": 52, "reduce": 53, "table16": 54, "softmax": 55, "conv2d_i16": 56, "permute": 57, "gather": 58, "scatter": 59, "matmul_f": 60, "depthwise_f": 61,
 }
 
 EW_FN = {"cast": 0, "abs": 1, "negate": 2, "bitwise_not": 3, "logical_not": 4, "clz": 5, "clamp": 6, "ceil": 7, "floor": 8,
@@ -207,6 +207,19 @@ class Graph:
                           pad_l=pad[2], pad_r=pad[3], in0_zp=input_zp, weight_zp=weight_zp, out_zp=out_zp,
                           clamp_min=clamp[0], clamp_max=clamp[1], per_channel=pc, double_round=int(double_round),
                           requant_mode=requant_mode)
+
+    def depthwise_conv2d_f(self, x, weights, bias, *, stride=(1, 1), dilation=(1, 1), pad=(0, 0, 0, 0)):
+        """tosa.depthwise_conv2d on bf16 / f32: x [N, H, W, C], weights [KH, KW, C, M] and bias [C * M] tensors of x's type."""
+        N, H, W, Cc = x.shape
+        KH, KW, C2, M = weights.shape
+        if Cc != C2 or int(np.prod(bias.shape)) != Cc * M or weights.dtype != x.dtype or bias.dtype != x.dtype or \
+                x.dtype not in ("bf16", "f32"):
+            raise ValueError("depthwise_conv2d_f wants bf16 or f32 x [N,H,W,C], weights [KH,KW,C,M], bias [C*M]")
+        OH = _out_dim(H, KH, stride[0], dilation[0], pad[0], pad[1])
+        OW = _out_dim(W, KW, stride[1], dilation[1], pad[2], pad[3])
+        return self._emit("depthwise_f", [x, weights, bias], (N, OH, OW, Cc * M), x.dtype, kh=KH, kw=KW, stride_h=stride[0],
+                          stride_w=stride[1], dil_h=dilation[0], dil_w=dilation[1], pad_t=pad[0], pad_b=pad[1],
+                          pad_l=pad[2], pad_r=pad[3])
 
     def fully_connected(self, x, weights, bias, multiplier, shift, *, input_zp=0, weight_zp=0, out_zp=0,
                         clamp=(-128, 127), double_round=True, requant_mode=0):

@@ -20,7 +20,7 @@ from dataclasses import dataclass, field
 
 import numpy as np
 
-from .oplist import Graph, TensorRef
+from .oplist import ACTIVATION, Graph, TensorRef
 
 _NP = {"i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64, "index": np.int64, "f32": np.float32,
        "i1": np.int8, "ui8": np.uint8, "ui16": np.uint16, "bf16": np.uint16, "i48": np.int64}
@@ -64,10 +64,12 @@ def _parse_type(t: str):
         if m2:
             return (int(m2.group(1)),), "index"
         raise ValueError(f"unsupported type {t}")
-    mm = re.match(r"^((?:\d+x)*)(\w+)$", m.group(1))
+    # a dynamic extent is specialised to 1, as the reference's test harness does when it draws the inputs of such a
+    # function (python/torq/testing/iree.py:385): an executable of this backend has static shapes
+    mm = re.match(r"^((?:(?:\d+|\?)x)*)(\w+)$", m.group(1))
     if not mm:
         raise NotImplementedError(f"unsupported tensor type {t}")
-    return tuple(int(p) for p in mm.group(1).split("x") if p), mm.group(2)
+    return tuple(1 if p == "?" else int(p) for p in mm.group(1).split("x") if p), mm.group(2)
 
 
 def _parse_dense(body: str, shape, dtype):
@@ -323,6 +325,40 @@ def build_graph(text: str) -> Graph:
             env[res.name] = g.reshape(get(op.operands[0]), oshape)
         elif n == "reshape":
             env[res.name] = g.reshape(get(op.operands[0]), oshape)
+        elif n == "depthwise_conv2d" and op.operands[0].dtype in ("bf16", "f32"):
+            x, w, bias, izp, wzp = op.operands
+            if w.dtype != x.dtype or bias.dtype != x.dtype or res.dtype != x.dtype or len(x.shape) != 4 or len(w.shape) != 4:
+                raise NotImplementedError("float tosa.depthwise_conv2d of mixed types")
+            for z in (izp, wzp):
+                if z.const is None or np.any(np.asarray(z.const)):
+                    raise NotImplementedError("float tosa.depthwise_conv2d with a zero point")
+            bt = get(bias)
+            cm = int(w.shape[2]) * int(w.shape[3])
+            if int(np.prod(bias.shape)) == 1 and cm != 1:  # a size-1 bias broadcasts over the channels
+                if bias.const is None:
+                    raise NotImplementedError("broadcast of a runtime bias")
+                bt = g.const(np.repeat(np.asarray(get(bias).data).reshape(-1)[:1], cm), graph_dtype(x.dtype))
+            pad = [int(v) for v in op.attrs.get("pad", [0] * 4)]
+            env[res.name] = g.depthwise_conv2d_f(get(x), g.reshape(get(w), tuple(int(d) for d in w.shape)) if tuple(get(w).shape) != tuple(w.shape) else get(w),
+                                                 bt, stride=[int(v) for v in op.attrs.get("stride", [1, 1])],
+                                                 dilation=[int(v) for v in op.attrs.get("dilation", [1, 1])], pad=pad)
+        elif n == "conv2d":
+            # a 1x1 convolution whose weights are a second runtime tensor (a TFLite FULLY_CONNECTED / batch matmul of
+            # two activations arrives like this): the matrix product of the pixels with the transposed weights
+            x, w, bias, izp, wzp = op.operands
+            if w.name not in env and w.name not in deferred:
+                raise NotImplementedError("tosa.conv2d")
+            if x.dtype != "i8" or w.dtype != "i8" or op.result.dtype != "i32" or tuple(w.shape[1:3]) != (1, 1) or \
+                    [int(v) for v in op.attrs.get("stride", [1, 1])] != [1, 1] or any(int(v) for v in op.attrs.get("pad", [0] * 4)) or \
+                    [int(v) for v in op.attrs.get("dilation", [1, 1])] != [1, 1]:
+                raise NotImplementedError("tosa.conv2d with runtime weights other than 1x1 i8 x i8 -> i32")
+            if bias.const is None or np.any(np.asarray(bias.const)):
+                raise NotImplementedError("tosa.conv2d with runtime weights and a bias")
+            K, OC = int(x.shape[-1]), int(w.shape[0])
+            rows = int(np.prod(x.shape[:-1]))
+            wt = g.transpose(g.reshape(get(w), (OC, K)), (1, 0))
+            y = g.matmul_i32(g.reshape(get(x), (rows, K)), wt, a_zp=_scalar(izp), b_zp=_scalar(wzp))
+            env[res.name] = g.reshape(y, oshape)
         else:
             raise NotImplementedError(f"tosa.{n}")
 
@@ -516,7 +552,11 @@ def build_graph(text: str) -> Graph:
                 del env[name]
             generic(op)
     for v in returned:
-        g.output(get(v))
+        t = get(v)
+        if t.kind != ACTIVATION:
+            # a value returned twice (or an input returned as it is): the further output is a copy of it
+            t = g.reshape(t, t.shape)
+        g.output(t)
     return g
 
 
