@@ -387,7 +387,7 @@ def decoder_parity(dev, batch: int, steps: int = 12, tp: int = 1, rank: int = 0)
     """Outside any timed region: the same weights, `steps` teacher-forced seeded tokens, logits of every
     step against the fp32 torch reference of the unsharded model (tests/ref_decoder.py): relative max-abs
     error of the logits and whether every greedy id agrees. With tp > 1 every rank calls this; the logits
-    shards are gathered to rank 0, which alone holds the reference and returns the verdict."""
+    shards are gathered to rank 0, which alone holds the reference and returns the outcome."""
     import torch
     from torq_b200.runtime import Executable
     from torq_b200.workloads import gemma3

@@ -1,7 +1,7 @@
 """One rank of the tensor-parallel decode check (run under torch.distributed.run, one process
 per GPU): every rank builds its shard of the decode step, the shards connect through each
 other's memory, and the group decodes teacher-forced tokens. Rank 0 compares the greedy ids and
-the gathered logits with the fp32 torch reference of the unsharded model and writes the verdict
+the gathered logits with the fp32 torch reference of the unsharded model and writes the outcome
 as one JSON line."""
 import json
 import os

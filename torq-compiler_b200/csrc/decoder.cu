@@ -417,7 +417,7 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const uint16_t* __res
 #pragma unroll
   for (int j = 0; j < 8; j++) acc[j] = 0.f;
   // four keys per round: their score reductions interleave and one rescale serves all four
-  // and the next round's rows are loaded before this round's arithmetic (registers as the second buffer)
+  // and the next pass's rows are loaded before this pass's arithmetic (registers as the second buffer)
   uint4 kk[4], vv[4], nk[4], nv[4];
   auto load_round = [&](int t, uint4 (&kd)[4], uint4 (&vd)[4]) {
 #pragma unroll
