@@ -119,3 +119,88 @@ def test_two_stage_input_rescale_becomes_a_left_shift(name):
     v = r0 + r1 if name == "add" else r0 - r1
     want = np.clip(onp.apply_scale_32(v, 1100000000, 50, True) - 100, -128, 127).astype(np.int8)
     assert (got == want).all() and len(np.unique(got)) > 20
+
+
+DYNAMIC = '''
+module {
+  func.func @main(%arg0: tensor<?x5x3xi32>) -> tensor<?x5x3xi32> {
+    %0 = tosa.abs %arg0 : (tensor<?x5x3xi32>) -> tensor<?x5x3xi32>
+    return %0 : tensor<?x5x3xi32>
+  }
+}
+'''
+
+TWICE = '''
+module {
+  func.func @main(%arg0: tensor<1x6x4xi8>, %arg1: tensor<1x4x5xi8>) -> (tensor<1x6x5xi32>, tensor<1x6x5xi32>) {
+    %z = arith.constant dense<0> : tensor<1xi8>
+    %0 = tosa.matmul %arg0, %arg1, %z, %z : (tensor<1x6x4xi8>, tensor<1x4x5xi8>, tensor<1xi8>, tensor<1xi8>) -> tensor<1x6x5xi32>
+    return %0, %0 : tensor<1x6x5xi32>, tensor<1x6x5xi32>
+  }
+}
+'''
+
+RUNTIME_WEIGHTS = '''
+module {
+  func.func @main(%arg0: tensor<6x8xi8>, %arg1: tensor<5x8xi8>) -> tensor<6x1x1x5xi32> {
+    %sx = tosa.const_shape {values = dense<[6, 1, 1, 8]> : tensor<4xindex>} : () -> !tosa.shape<4>
+    %sw = tosa.const_shape {values = dense<[5, 1, 1, 8]> : tensor<4xindex>} : () -> !tosa.shape<4>
+    %b = "tosa.const"() <{values = dense<0> : tensor<1xi32>}> : () -> tensor<1xi32>
+    %zx = "tosa.const"() <{values = dense<-3> : tensor<1xi8>}> : () -> tensor<1xi8>
+    %zw = "tosa.const"() <{values = dense<2> : tensor<1xi8>}> : () -> tensor<1xi8>
+    %0 = tosa.reshape %arg0, %sx : (tensor<6x8xi8>, !tosa.shape<4>) -> tensor<6x1x1x8xi8>
+    %1 = tosa.reshape %arg1, %sw : (tensor<5x8xi8>, !tosa.shape<4>) -> tensor<5x1x1x8xi8>
+    %2 = tosa.conv2d %0, %1, %b, %zx, %zw {acc_type = i32, dilation = array<i64: 1, 1>, pad = array<i64: 0, 0, 0, 0>, stride = array<i64: 1, 1>} : (tensor<6x1x1x8xi8>, tensor<5x1x1x8xi8>, tensor<1xi32>, tensor<1xi8>, tensor<1xi8>) -> tensor<6x1x1x5xi32>
+    return %2 : tensor<6x1x1x5xi32>
+  }
+}
+'''
+
+FLOAT_DEPTHWISE = '''
+module {
+  func.func @main(%arg0: tensor<1x5x4x2xbf16>) -> tensor<1x5x4x2xbf16> {
+    %b = "tosa.const"() <{values = dense<[1.000000e+00, -2.000000e+00]> : tensor<2xbf16>}> : () -> tensor<2xbf16>
+    %w = "tosa.const"() <{values = dense<5.000000e-01> : tensor<3x3x2x1xbf16>}> : () -> tensor<3x3x2x1xbf16>
+    %z = arith.constant dense<0.000000e+00> : tensor<1xbf16>
+    %0 = tosa.depthwise_conv2d %arg0, %w, %b, %z, %z {acc_type = f32, dilation = array<i64: 1, 1>, pad = array<i64: 1, 1, 1, 1>, stride = array<i64: 1, 1>} : (tensor<1x5x4x2xbf16>, tensor<3x3x2x1xbf16>, tensor<2xbf16>, tensor<1xbf16>, tensor<1xbf16>) -> tensor<1x5x4x2xbf16>
+    return %0 : tensor<1x5x4x2xbf16>
+  }
+}
+'''
+
+
+def test_dynamic_extent_is_specialised_to_one():
+    g = tosa_frontend.build_graph(DYNAMIC)
+    assert [op.kind for op in g.ops] == ["ew"] and int(np.prod(g.inputs[0].shape)) == 15
+    x = np.arange(-7, 8, dtype=np.int32).reshape(g.inputs[0].shape)
+    assert (run_graph(g, [x])[0].ravel() == np.abs(x).ravel()).all()
+
+
+def test_a_value_returned_twice_gets_a_copy():
+    g = tosa_frontend.build_graph(TWICE)
+    assert len(g.outputs) == 2 and g.outputs[0].id != g.outputs[1].id
+    rng = np.random.default_rng(3)
+    a, b = rng.integers(-128, 128, (1, 6, 4), dtype=np.int8), rng.integers(-128, 128, (1, 4, 5), dtype=np.int8)
+    o0, o1 = run_graph(g, [a.reshape(g.inputs[0].shape), b.reshape(g.inputs[1].shape)])
+    want = a[0].astype(np.int32) @ b[0].astype(np.int32)
+    assert (o0.reshape(6, 5) == want).all() and (o1.reshape(6, 5) == want).all()
+
+
+def test_convolution_of_two_runtime_tensors_is_a_matmul():
+    g = tosa_frontend.build_graph(RUNTIME_WEIGHTS)
+    assert "matmul_i32" in [op.kind for op in g.ops] and "conv2d" not in [op.kind for op in g.ops]
+    rng = np.random.default_rng(4)
+    x, w = rng.integers(-128, 128, (6, 8), dtype=np.int8), rng.integers(-128, 128, (5, 8), dtype=np.int8)
+    out = run_graph(g, [x, w])[0]
+    want = (x.astype(np.int32) + 3) @ (w.astype(np.int32) - 2).T
+    assert (out.reshape(6, 5) == want).all()
+
+
+def test_float_depthwise_accumulates_in_fp32():
+    g = tosa_frontend.build_graph(FLOAT_DEPTHWISE)
+    assert [op.kind for op in g.ops] == ["depthwise_f"]
+    x = np.ones((1, 5, 4, 2), np.float32)
+    out = run_graph(g, [tosa_frontend._to_bf16_bits(x)])[0]
+    got = (out.astype(np.uint32) << 16).view(np.float32)
+    # an inner pixel sees nine taps of 0.5, a corner four; then the bias
+    assert got[0, 2, 1, 0] == 9 * 0.5 + 1.0 and got[0, 0, 0, 1] == 4 * 0.5 - 2.0
